@@ -1,0 +1,252 @@
+/*
+ * mimir_b200.h — C ABI of the B200 (sm_100a) forward-inference backend for Mímir.
+ *
+ * Everything here is plain C: pointers, sizes and ints.  No C++ or torch type crosses the
+ * boundary.  Every function returns a MimirB200Status; on a non-zero status
+ * mimir_b200_last_error() gives a thread-local message.  The library never throws and never
+ * falls back to the CPU: an op it cannot run returns MIMIR_B200_E_UNSUPPORTED.
+ *
+ * Three groups of entry points:
+ *   1. life cycle and device-memory budget  (mirror of MemoryGuard's verbs)
+ *   2. per-op calls with HOST pointers      (mirror of ComputeEngine::linearForward,
+ *      one call per `case LayerType::X` of Model::forwardPassView)
+ *   3. whole-graph calls                    (mirror of Model::forwardPassView itself: the
+ *      layer list is translated once, weights are uploaded once, activations stay in HBM)
+ *
+ * Layout conventions are the reference's: every activation is a flat row-major fp32 vector for
+ * one sample (images CHW, sequences [seq, dim]); `batch` is a leading dimension added by this
+ * backend and means "apply the reference op independently to each sample".
+ */
+#ifndef MIMIR_B200_H
+#define MIMIR_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MIMIR_B200_ABI_VERSION 1
+#define MIMIR_B200_MAX_INPUTS 8
+#define MIMIR_B200_MAX_DIMS 8
+
+typedef enum MimirB200Status {
+  MIMIR_B200_OK = 0,
+  MIMIR_B200_E_INVALID = 1,     /* bad argument / shape (reference: RUNTIME_CHECK -> throw, RuntimeAllocator.hpp:344-358) */
+  MIMIR_B200_E_UNSUPPORTED = 2, /* layer type or shape this backend does not run; there is no CPU fallback */
+  MIMIR_B200_E_OOM_BUDGET = 3,  /* device budget refused (reference: MemoryGuard::requestAllocation false, MemoryGuard.hpp:75-130) */
+  MIMIR_B200_E_CUDA = 4,        /* a CUDA call failed; message carries cudaGetErrorString */
+  MIMIR_B200_E_TIMEOUT = 5,     /* a bounded device-side wait gave up (kernel returned an error word) */
+  MIMIR_B200_E_NOT_INIT = 6
+} MimirB200Status;
+
+/* GEMM operand precision.  All modes accumulate in fp32 in tensor memory.
+ *   BF16X2 : both operands split into bf16 hi+lo, three MMAs (hi*hi + lo*hi + hi*lo); error ~2^-16
+ *            per product — the default for fp32 graphs (within rel 1e-3 / abs 1e-4 of the CPU path).
+ *   BF16W  : weights stored as single bf16 (exact when the checkpoint was pre-rounded to bf16),
+ *            activations split hi+lo, two MMAs.
+ *   BF16   : both operands rounded to bf16, one MMA (fastest, not within the fp32 tolerance). */
+typedef enum MimirB200Precision {
+  MIMIR_B200_PREC_BF16X2 = 0,
+  MIMIR_B200_PREC_BF16W = 1,
+  MIMIR_B200_PREC_BF16 = 2
+} MimirB200Precision;
+
+/* Element-wise ops of mimir_b200_eltwise (reference: LayerOps.hpp:142-230, 556-623). */
+typedef enum MimirB200Eltwise {
+  MIMIR_B200_ELT_ADD = 0,      /* add_forward incl. scalar and `i % small_n` broadcast */
+  MIMIR_B200_ELT_MULTIPLY = 1, /* multiply_forward (equal sizes only) */
+  MIMIR_B200_ELT_GELU = 2,     /* tanh form, c = sqrt(2/3.14159265359f) */
+  MIMIR_B200_ELT_SILU = 3,
+  MIMIR_B200_ELT_RELU = 4,
+  MIMIR_B200_ELT_TANH = 5,
+  MIMIR_B200_ELT_SIGMOID = 6
+} MimirB200Eltwise;
+
+/* ---------------------------------------------------------------------------------------------
+ * 1. Life cycle and budget
+ * ------------------------------------------------------------------------------------------ */
+
+/* Binds the calling process to CUDA device `device` and sets the HBM budget that arena plans and
+ * weight uploads are checked against (0 = 90 % of the device's total memory).  Idempotent and
+ * thread-safe.  Replaces the engine construction in Model::Model() (Model.cpp:690-698, 753-878)
+ * and MemoryGuard::setLimit (MemoryGuard.hpp:47-60). */
+int mimir_b200_init(int device, size_t hbm_budget_bytes);
+/* Releases every model handle, the arena and the per-op cache.  Replaces the engine teardown in
+ * Model::~Model() (Model.cpp:726-741). */
+int mimir_b200_shutdown(void);
+const char* mimir_b200_last_error(void);
+int mimir_b200_abi_version(void);
+
+/* MemoryGuard verbs against the HBM budget (MemoryGuard.hpp:47-60 setLimit, 75-130
+ * requestAllocation, 132-150 releaseAllocation, getCurrentUsage/getPeakUsage/getLimit). */
+int mimir_b200_guard_set_limit(size_t bytes);
+int mimir_b200_guard_request(size_t bytes, const char* tag); /* OK or E_OOM_BUDGET */
+int mimir_b200_guard_release(size_t bytes);
+int mimir_b200_guard_stats(size_t* limit, size_t* current, size_t* peak);
+
+/* ---------------------------------------------------------------------------------------------
+ * 2. Per-op entry points, HOST pointers, synchronous (copy in, run, copy out).
+ *    Drop-in for the Vulkan/OpenCL hook `bool ComputeEngine::linearForward(const float* input,
+ *    const float* weights, const float* bias_or_null, float* output, int batch, int in_f,
+ *    int out_f)` (VulkanCompute.hpp:209-210, OpenCLCompute.hpp:114-122), one per switch case.
+ * ------------------------------------------------------------------------------------------ */
+
+/* y[t,o] = sum_i W[o,i] x[t,i] (+ b[o]).  Replaces LayerOps::linear_forward (LayerOps.hpp:24-111)
+ * and the accelerator call sites Model.cpp:5136-5144, 5184-5192.  `batch` = rows. */
+int mimir_b200_linear_forward(const float* input, const float* weights, const float* bias_or_null,
+                              float* output, int batch, int in_f, int out_f);
+/* Same with the precision mode and a fused activation (MIMIR_B200_ELT_GELU/SILU/RELU or -1). */
+int mimir_b200_linear_forward_ex(const float* input, const float* weights, const float* bias_or_null,
+                                 float* output, int batch, int in_f, int out_f, int precision,
+                                 int activation);
+/* C[M,N] = A[M,K] B[K,N], row-major.  Replaces LayerOps::matmul_forward (LayerOps.hpp:692-724) /
+ * HardwareOpt::matmul_fma_saturated (HardwareOpt.hpp:95-149). */
+int mimir_b200_matmul(const float* A, const float* B, float* C, int M, int K, int N);
+/* Self / multi-head attention on `batch` samples of [seq, embed].  Weight block = Wqkv[E][3E]
+ * then Wout[E][E], no biases.  Replaces LayerOps::self_attention_forward (LayerOps.hpp:1004-1097)
+ * as dispatched at Model.cpp:5904-5933. */
+int mimir_b200_attention(const float* x, const float* wqkv_wout, float* y, int batch, int seq,
+                         int embed, int heads, int causal);
+/* NCHW x OIHW, square kernel, no bias, optional ReLU.  Replaces the inline Conv2d case
+ * (Model.cpp:4897-5089). */
+int mimir_b200_conv2d(const float* x, const float* w, float* y, int batch, int ic, int oc, int h,
+                      int wd, int k, int stride, int pad, int relu);
+/* `rows` independent groups of n; gamma/beta may be NULL.  Replaces LayerOps::layernorm_forward
+ * (LayerOps.hpp:264-319). */
+int mimir_b200_layernorm(const float* x, const float* gamma, const float* beta, float* y,
+                         long long rows, int n, float eps);
+/* One RMS over each sample's whole vector of n; gamma applied to flat indices < n_gamma.
+ * Replaces LayerOpsExt::rms_norm_forward (LayerOpsExt.hpp:345-378). */
+int mimir_b200_rmsnorm(const float* x, const float* gamma, long long n_gamma, float* y, int batch,
+                       long long n, float eps);
+/* CHW samples, G contiguous channel groups; act = -1 or MIMIR_B200_ELT_SILU (fused).
+ * Replaces LayerOps::groupnorm_forward (LayerOps.hpp:488-550). */
+int mimir_b200_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int batch,
+                         int channels, int h, int w, int groups, float eps, int act);
+/* Softmax / log-softmax over each sample's whole vector (axis ignored, as in the reference).
+ * Replaces LayerOps::softmax_forward (LayerOps.hpp:325-361). */
+int mimir_b200_softmax(const float* x, float* y, int batch, long long n, int log_softmax);
+/* Unary ops read `a` only; ADD/MULTIPLY read `b` of nb elements per sample
+ * (nb == n, 1, or a divisor of n).  Replaces LayerOps.hpp:142-230, 556-623. */
+int mimir_b200_eltwise(int op, const float* a, const float* b, float* y, int batch, long long n,
+                       long long nb);
+/* Row gather; ids given as floats are rounded like llround; id == padding_idx (when >= 0) or out
+ * of range gives a zero row.  Replaces the Embedding case (Model.cpp:5301-5334; int ids:
+ * Model.cpp:1152-1205).  Exactly one of ids_f32 / ids_i32 is non-NULL. */
+int mimir_b200_embedding(const float* ids_f32, const int32_t* ids_i32, const float* table, float* y,
+                         long long n_ids, int vocab, int dim, int padding_idx);
+/* Nearest-neighbour upsample of CHW samples by integer factors.  Replaces
+ * LayerOps::upsample_nearest_forward (LayerOps.hpp:802-827) as called at Model.cpp:6002-6017. */
+int mimir_b200_upsample_nearest(const float* x, float* y, int batch, int channels, int in_h,
+                                int in_w, int scale_h, int scale_w);
+/* General permutation of a tensor of `ndim` dims (per sample).  Replaces
+ * LayerOps::permute_forward (LayerOps.hpp:880-945). */
+int mimir_b200_permute(const float* x, float* y, int batch, int ndim, const int* shape,
+                       const int* dims);
+/* mean over seq of [seq, dim] (Model.cpp:5571-5589) and mean over HxW per channel
+ * (LayerOps.hpp:459-482). */
+int mimir_b200_token_mean_pool(const float* x, float* y, int batch, int seq, int dim);
+int mimir_b200_global_avgpool(const float* x, float* y, int batch, int channels, int h, int w);
+
+/* ---------------------------------------------------------------------------------------------
+ * 3. Whole-graph entry points (activations stay on the device between layers)
+ * ------------------------------------------------------------------------------------------ */
+
+/* POD mirror of the `struct Layer` fields the forward ops read (Layers.hpp:86-309).  `type` is
+ * the reference's normalised type string ("Linear", "Conv2d", "MultiHeadAttention", ...,
+ * LayerTypes.hpp:13-120).  Strings are copied by model_create.  Zero / negative values keep the
+ * reference's "unset" meaning (e.g. in_features == 0 => whole input). */
+typedef struct MimirLayerDesc {
+  const char* name;
+  const char* type;
+  const char* inputs[MIMIR_B200_MAX_INPUTS]; /* n_inputs == 0 => {"x"} (Model.cpp:4802) */
+  int32_t n_inputs;
+  const char* output;                        /* NULL or "" => "x" (Model.cpp:6655) */
+  uint64_t params_count;
+  int32_t in_features, out_features, in_channels, out_channels;
+  int32_t input_height, input_width;
+  int32_t kernel, stride, padding;           /* already resolved: get_kernel_h / get_stride_h / get_pad_h (Layers.hpp:250-257) */
+  float eps;
+  int32_t num_groups, affine, use_bias;
+  int32_t vocab_size, embed_dim, padding_idx;
+  int32_t num_heads, seq_len, causal;
+  int32_t out_h, out_w, scale_h, scale_w;    /* UpsampleNearest reads out_h/out_w as the INPUT size (Model.cpp:6008-6009) */
+  int32_t activation;                        /* != 0 => ReLU after Conv2d (Model.cpp:5081-5086) */
+  int32_t n_dims;
+  int32_t shape[MIMIR_B200_MAX_DIMS];        /* Permute */
+  int32_t permute_dims[MIMIR_B200_MAX_DIMS];
+} MimirLayerDesc;
+
+typedef struct MimirNamedInput {
+  const char* name;   /* "x" / "__input__" is the main input (Model.cpp:4640-4642); others e.g. "mag", "mod" */
+  const float* data;  /* host (model_forward) or device (model_forward_device) pointer */
+  uint64_t per_sample;/* elements per sample */
+  int32_t broadcast;  /* 1 => one copy shared by every sample of the batch (e.g. "mag"/"mod") */
+} MimirNamedInput;
+
+typedef struct MimirB200Stats {
+  uint64_t arena_peak_bytes;   /* planned activation arena for the last plan */
+  uint64_t weight_bytes;       /* device bytes held by uploaded weights */
+  uint64_t kernels_launched;   /* kernels of this library launched since init */
+  uint64_t flops_last_forward; /* algorithmic flops of the contraction layers in the last forward */
+  uint64_t bytes_last_forward; /* algorithmic bytes (inputs + outputs + weights) of the HBM-bound layers */
+  float    ms_last_forward;    /* device time of the last forward (CUDA events), 0 if not measured */
+} MimirB200Stats;
+
+typedef struct MimirB200Model* MimirB200ModelHandle;
+
+/* Translates the layer list once.  Replaces the per-forward walk of `std::vector<Layer>`
+ * (Model.cpp:4795-4891). */
+int mimir_b200_model_create(const MimirLayerDesc* layers, int n_layers, MimirB200ModelHandle* out);
+int mimir_b200_model_destroy(MimirB200ModelHandle m);
+/* Sets the GEMM operand precision for this model (before upload_weights). */
+int mimir_b200_model_set_precision(MimirB200ModelHandle m, int precision);
+/* Copies one layer's flat fp32 weight block (layout = the reference's, Layer::getWeights()).  The
+ * host pointer is not kept (it may move: DynamicTensorAllocator.hpp:171-200).  Call again after
+ * the weights change. */
+int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, const float* host,
+                                    uint64_t n);
+/* Declares the per-sample size of a named graph input, then plans the activation arena for
+ * `batch` samples: liveness over the layer list, offsets reused after the last consumer, peak
+ * checked against the budget BEFORE anything is launched (E_OOM_BUDGET).  Mirrors
+ * RuntimeAllocator::allocate_tensor / get_scratchpad (RuntimeAllocator.hpp:191-280). */
+int mimir_b200_model_plan(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs,
+                          int batch, uint64_t* arena_peak_bytes);
+/* Host in, host out: H2D of the inputs, the layer loop, D2H of tensor "x".  Replaces
+ * Model::forwardPassView (Model.cpp:4621-6824).  *out_len = per-sample output length. */
+int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs,
+                             int batch, float* out_host, uint64_t out_capacity, uint64_t* out_len);
+/* Device in, device out, asynchronous on `stream` (a cudaStream_t, NULL = default stream). */
+int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInput* inputs,
+                                    int n_inputs, int batch, float* out_dev, uint64_t out_capacity,
+                                    uint64_t* out_len, void* stream);
+/* Per-position argmax over rows of `n` (first maximum wins), for token ids.  No counterpart layer
+ * in the reference (harness step of the decoder config). */
+int mimir_b200_argmax_rows_device(const float* x_dev, int32_t* ids_dev, long long rows, int n,
+                                  void* stream);
+int mimir_b200_get_stats(MimirB200Stats* out);
+
+/* ---------------------------------------------------------------------------------------------
+ * Device-pointer forms of the per-op calls (inputs already resident in HBM, asynchronous on
+ * `stream`).  The host-pointer forms above are these plus the copies.
+ * ------------------------------------------------------------------------------------------ */
+int mimir_b200_dev_linear(const float* x, const float* w, const float* bias_or_null, float* y,
+                          int rows, int in_f, int out_f, int precision, int activation, void* stream);
+int mimir_b200_dev_layernorm(const float* x, const float* gamma, const float* beta, float* y,
+                             long long rows, int n, float eps, void* stream);
+int mimir_b200_dev_rmsnorm(const float* x, const float* gamma, long long n_gamma, float* y,
+                           int batch, long long n, float eps, void* stream);
+int mimir_b200_dev_groupnorm(const float* x, const float* gamma, const float* beta, float* y,
+                             int batch, int channels, int h, int w, int groups, float eps, int act,
+                             void* stream);
+int mimir_b200_dev_softmax(const float* x, float* y, int batch, long long n, int log_softmax,
+                           void* stream);
+int mimir_b200_dev_eltwise(int op, const float* a, const float* b, float* y, int batch, long long n,
+                           long long nb, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIMIR_B200_H */

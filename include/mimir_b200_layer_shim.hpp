@@ -1,0 +1,121 @@
+// mimir_b200_layer_shim.hpp — the only piece that is compiled against Mímir's own headers.
+//
+// Translates Mímir's `struct Layer` (Layers.hpp:86-309) into the POD MimirLayerDesc that the
+// C ABI takes, resolving the helper accessors the forward ops use (get_kernel_h / get_stride_h /
+// get_pad_h, Layers.hpp:250-257) so that the backend never needs Mímir's headers.
+//
+// Usage inside Mímir (or any program that links Mímir):
+//     mimir_b200::GraphDescs g(model.getLayers());
+//     mimir_b200_model_create(g.data(), g.size(), &handle);
+//     for (i...) mimir_b200_model_upload_weights(handle, i, layers[i].getWeights(), layers[i].getWeightsSize());
+#pragma once
+
+#include <string>
+#include <vector>
+#include <cstring>
+
+#include "Layers.hpp"     // Mímir
+#include "mimir_b200.h"
+
+namespace mimir_b200 {
+
+inline MimirLayerDesc describe(const Layer& L) {
+  MimirLayerDesc d;
+  std::memset(&d, 0, sizeof(d));
+  d.name = L.name.c_str();
+  d.type = L.type.c_str();  // normalised by Layer's constructor (Layers.hpp:229-235)
+  d.n_inputs = 0;
+  for (const auto& in : L.inputs) {
+    if (d.n_inputs >= MIMIR_B200_MAX_INPUTS) break;
+    d.inputs[d.n_inputs++] = in.c_str();
+  }
+  d.output = L.output.c_str();
+  d.params_count = L.params_count;
+  d.in_features = L.in_features;
+  d.out_features = L.out_features;
+  d.in_channels = L.in_channels;
+  d.out_channels = L.out_channels;
+  d.input_height = L.input_height;
+  d.input_width = L.input_width;
+  d.kernel = L.get_kernel_h();
+  d.stride = L.get_stride_h();
+  d.padding = L.get_pad_h();
+  d.eps = L.eps;
+  d.num_groups = L.num_groups;
+  d.affine = L.affine ? 1 : 0;
+  d.use_bias = L.use_bias ? 1 : 0;
+  d.vocab_size = L.vocab_size;
+  d.embed_dim = L.embed_dim;
+  d.padding_idx = L.padding_idx;
+  d.num_heads = L.num_heads;
+  d.seq_len = L.seq_len;
+  d.causal = L.causal ? 1 : 0;
+  d.out_h = L.out_h;
+  d.out_w = L.out_w;
+  // UpsampleNearest truncates the float factors to int and treats <= 0 as 2 (Model.cpp:6011-6012)
+  d.scale_h = static_cast<int>(L.scale_h);
+  d.scale_w = static_cast<int>(L.scale_w);
+  d.activation = (L.activation != ActivationType::NONE) ? 1 : 0;
+  d.n_dims = 0;
+  const size_t nd = L.permute_dims.size();
+  if (nd <= MIMIR_B200_MAX_DIMS && L.shape.size() == nd) {
+    d.n_dims = static_cast<int32_t>(nd);
+    for (size_t i = 0; i < nd; ++i) {
+      d.shape[i] = L.shape[i];
+      d.permute_dims[i] = L.permute_dims[i];
+    }
+  }
+  return d;
+}
+
+// Holds the descriptors for a whole layer list.  The strings stay owned by the Layers, so the
+// Layer vector must outlive this object (model_create copies them).
+class GraphDescs {
+ public:
+  explicit GraphDescs(const std::vector<Layer>& layers) {
+    descs_.reserve(layers.size());
+    for (const auto& L : layers) descs_.push_back(describe(L));
+  }
+  const MimirLayerDesc* data() const { return descs_.data(); }
+  int size() const { return static_cast<int>(descs_.size()); }
+
+ private:
+  std::vector<MimirLayerDesc> descs_;
+};
+
+// The inverse, used by tools that build a Mímir graph from descriptors (e.g. to run the CPU path
+// on exactly the graph the backend was given).
+inline void apply(const MimirLayerDesc& d, Layer& L) {
+  L.inputs.clear();
+  for (int i = 0; i < d.n_inputs; ++i) L.inputs.emplace_back(d.inputs[i] ? d.inputs[i] : "x");
+  L.output = (d.output && d.output[0]) ? d.output : "x";
+  L.params_count = static_cast<size_t>(d.params_count);
+  L.in_features = d.in_features;
+  L.out_features = d.out_features;
+  L.in_channels = d.in_channels;
+  L.out_channels = d.out_channels;
+  L.input_height = d.input_height;
+  L.input_width = d.input_width;
+  L.kernel_size = d.kernel;
+  L.stride = d.stride > 0 ? d.stride : 1;
+  L.padding = d.padding;
+  L.eps = d.eps;
+  L.num_groups = d.num_groups > 0 ? d.num_groups : 1;
+  L.affine = d.affine != 0;
+  L.use_bias = d.use_bias != 0;
+  L.vocab_size = d.vocab_size;
+  L.embed_dim = d.embed_dim;
+  L.padding_idx = d.padding_idx;
+  L.num_heads = d.num_heads;
+  L.seq_len = d.seq_len;
+  L.causal = d.causal != 0;
+  L.out_h = d.out_h;
+  L.out_w = d.out_w;
+  L.scale_h = static_cast<float>(d.scale_h);
+  L.scale_w = static_cast<float>(d.scale_w);
+  L.activation = d.activation ? ActivationType::RELU : ActivationType::NONE;
+  L.shape.assign(d.shape, d.shape + d.n_dims);
+  L.permute_dims.assign(d.permute_dims, d.permute_dims + d.n_dims);
+}
+
+}  // namespace mimir_b200

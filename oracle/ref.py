@@ -1,0 +1,120 @@
+"""TEST INFRASTRUCTURE — ctypes binding of ``oracle/_ref/libmimir_ref.so``.
+
+That library is the reference's own CPU implementation (compiled from its sources by
+``oracle/Makefile``) behind ``oracle/ref_shim.cpp``.  Only tests, the fixture generator, the smoke
+check and the benchmark's CPU arm import this module; the product never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from mimir_framework_b200.abi import MimirLayerDesc, MimirNamedInput, desc_array
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_ref", "libmimir_ref.so")
+
+_lib = None
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not available():
+            raise RuntimeError(f"{LIB_PATH} not built: run `make -C oracle ref` where the reference is mounted")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.mimir_ref_last_error.restype = C.c_char_p
+    return _lib
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise RuntimeError("reference: " + lib().mimir_ref_last_error().decode(errors="replace"))
+
+
+def set_threads(n: int) -> int:
+    return lib().mimir_ref_set_threads(C.c_int(n))
+
+
+def set_guard_limit(nbytes: int):
+    lib().mimir_ref_set_guard_limit(C.c_ulonglong(nbytes))
+
+
+class RefModel:
+    """A reference ``Model`` built from descriptors or through the reference's registry."""
+
+    def __init__(self, descs=None, registry=None, cfg_json: str = ""):
+        self._h = C.c_void_p()
+        if descs is not None:
+            self._arr = desc_array(descs)
+            _check(lib().mimir_ref_model_create(self._arr, C.c_int(len(descs)), C.byref(self._h)))
+        else:
+            _check(lib().mimir_ref_model_create_registry(registry.encode(), cfg_json.encode(), C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().mimir_ref_model_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def num_layers(self) -> int:
+        return lib().mimir_ref_model_num_layers(self._h)
+
+    def layer_desc(self, i: int) -> MimirLayerDesc:
+        d = MimirLayerDesc()
+        _check(lib().mimir_ref_model_layer_desc(self._h, C.c_int(i), C.byref(d)))
+        return d
+
+    def layer_descs(self):
+        return [self.layer_desc(i) for i in range(self.num_layers)]
+
+    def set_weights(self, i: int, w: np.ndarray):
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        _check(lib().mimir_ref_model_set_weights(self._h, C.c_int(i), w.ctypes.data_as(C.c_void_p), C.c_ulonglong(w.size)))
+
+    def get_weights(self, i: int) -> np.ndarray:
+        n = int(self.layer_desc(i).params_count)
+        w = np.empty(n, dtype=np.float32)
+        _check(lib().mimir_ref_model_get_weights(self._h, C.c_int(i), w.ctypes.data_as(C.c_void_p), C.c_ulonglong(n)))
+        return w
+
+    def mag_mod(self, cap: int = 65536):
+        mag = np.zeros(cap, dtype=np.float32)
+        mod = np.zeros(cap, dtype=np.float32)
+        n = C.c_int(0)
+        _check(lib().mimir_ref_model_get_mag_mod(self._h, mag.ctypes.data_as(C.c_void_p), mod.ctypes.data_as(C.c_void_p), C.c_int(cap), C.byref(n)))
+        return mag[: n.value].copy(), mod[: n.value].copy()
+
+    def forward(self, inputs: dict, out_cap: int | None = None, return_seconds: bool = False):
+        """One sample.  ``inputs`` maps tensor name -> 1-D float32 array ("x" is the main input)."""
+        keep = []
+        arr = (MimirNamedInput * len(inputs))()
+        for i, (k, v) in enumerate(inputs.items()):
+            v = np.ascontiguousarray(v, dtype=np.float32).ravel()
+            keep.append(v)
+            arr[i].name = k.encode()
+            arr[i].data = v.ctypes.data
+            arr[i].per_sample = v.size
+            arr[i].broadcast = 0
+        n = C.c_ulonglong(0)
+        secs = C.c_double(0)
+        if out_cap is None:
+            # first call sizes the output
+            _check(lib().mimir_ref_model_forward(self._h, arr, C.c_int(len(inputs)), None, C.c_ulonglong(0), C.byref(n), C.byref(secs)))
+            out_cap = n.value
+        out = np.empty(out_cap, dtype=np.float32)
+        _check(lib().mimir_ref_model_forward(self._h, arr, C.c_int(len(inputs)), out.ctypes.data_as(C.c_void_p), C.c_ulonglong(out_cap), C.byref(n), C.byref(secs)))
+        out = out[: n.value]
+        return (out, secs.value) if return_seconds else out
