@@ -1,0 +1,353 @@
+/*
+ * mimir_oracle.c — TEST INFRASTRUCTURE.  Plain-C restatement of Mímir's CPU fp32 forward ops.
+ *
+ * Each function restates one reference routine for ONE sample (the reference has no batch
+ * dimension) and cites the file:line it follows.  The restatement keeps the reference's
+ * accumulation structure where it changes the fp32 result (8-lane partial sums + horizontal add
+ * in Linear, k-sequential FMA in matmul) so that it lands within a few ulp of the compiled
+ * reference; it is pinned against the reference's own test vectors and against outputs of the
+ * compiled reference (tests/golden).  Only tests, the smoke check and the benchmark's CPU arm
+ * may use it; the CUDA backend never links or calls it.
+ */
+#include "mimir_oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* LayerOps::linear_forward, LayerOps.hpp:24-111.  Sequence mode (rows > 1) and vector mode share
+ * the same per-output dot product: eight interleaved partial sums (the AVX2 lanes, :56-61),
+ * reduced as (lane i + lane i+4), then two horizontal adds (:62-67), then the scalar tail
+ * (:70-72), then the bias (:73). */
+void mo_linear(const float* x, const float* w, const float* bias, float* y, long rows, int in_f, int out_f) {
+#pragma omp parallel for schedule(static) if ((long long)rows * out_f * in_f > 262144)
+  for (long t = 0; t < rows; ++t) {
+    const float* xr = x + (size_t)t * in_f;
+    float* yr = y + (size_t)t * out_f;
+    for (int o = 0; o < out_f; ++o) {
+      const float* wr = w + (size_t)o * in_f;
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      int i = 0;
+      for (; i + 8 <= in_f; i += 8)
+        for (int l = 0; l < 8; ++l) acc[l] = fmaf(wr[i + l], xr[i + l], acc[l]);
+      float s4[4];
+      for (int l = 0; l < 4; ++l) s4[l] = acc[l + 4] + acc[l]; /* hi + lo */
+      float h0 = s4[0] + s4[1], h1 = s4[2] + s4[3];            /* hadd */
+      float sum = h0 + h1;                                     /* hadd */
+      for (; i < in_f; ++i) sum += wr[i] * xr[i];
+      if (bias) sum += bias[o];
+      yr[o] = sum;
+    }
+  }
+}
+
+/* HardwareOpt::matmul_fma_saturated, HardwareOpt.hpp:95-149: C[M,N] = A[M,K] B[K,N]; every output
+ * is one k-sequential chain (FMA for the vector columns j < N&~7, mul+add for the scalar tail). */
+void mo_matmul(const float* A, const float* B, float* C, long M, long K, long N) {
+  const long vecN8 = N & ~7L;
+#pragma omp parallel for schedule(static) if ((long long)M * N * K > 262144)
+  for (long i = 0; i < M; ++i) {
+    for (long j = 0; j < N; ++j) {
+      float acc = 0.0f;
+      if (j < vecN8) {
+        for (long k = 0; k < K; ++k) acc = fmaf(A[i * K + k], B[k * N + j], acc);
+      } else {
+        for (long k = 0; k < K; ++k) acc += A[i * K + k] * B[k * N + j];
+      }
+      C[i * N + j] = acc;
+    }
+  }
+}
+
+/* LayerOps::self_attention_forward, LayerOps.hpp:1004-1097 (multihead_attention_forward is an
+ * alias, :1100-1113).  wqkv is [E][3E] input-major, wout [E][E]; no biases (Model.cpp:5916-5921). */
+void mo_attention(const float* x, const float* wqkv, const float* wout, float* y, int seq, int E, int heads,
+                  int causal) {
+  const int hd = E / heads;
+  const int qd = 3 * E;
+  float* qkv = (float*)malloc(sizeof(float) * (size_t)seq * qd);
+  float* att = (float*)calloc((size_t)seq * E, sizeof(float));
+  mo_matmul(x, wqkv, qkv, seq, E, qd);
+  const float scale = 1.0f / sqrtf((float)hd);
+  /* the reference runs the head loop on one thread (:1049); rows are independent, so threading
+   * over (h, i) changes nothing numerically */
+#pragma omp parallel
+  {
+    float* row = (float*)malloc(sizeof(float) * (size_t)seq);
+#pragma omp for collapse(2) schedule(static)
+    for (int h = 0; h < heads; ++h) {
+      for (int i = 0; i < seq; ++i) {
+        const int ho = h * hd;
+        float mx = -1e30f;
+        for (int j = 0; j < seq; ++j) {
+          if (causal && j > i) {
+            row[j] = -1e9f; /* masked, and not part of the max (:1054-1057) */
+            continue;
+          }
+          float dot = 0.0f;
+          const float* q = qkv + (size_t)i * qd + ho;
+          const float* k = qkv + (size_t)j * qd + E + ho;
+          for (int d = 0; d < hd; ++d) dot += q[d] * k[d];
+          const float s = dot * scale;
+          row[j] = s;
+          if (s > mx) mx = s;
+        }
+        float sum = 0.0f;
+        for (int j = 0; j < seq; ++j) {
+          const float e = expf(row[j] - mx);
+          row[j] = e;
+          sum += e;
+        }
+        const float inv = 1.0f / (sum + 1e-9f); /* :1076 */
+        for (int j = 0; j < seq; ++j) row[j] *= inv;
+        for (int d = 0; d < hd; ++d) {
+          float acc = 0.0f;
+          for (int j = 0; j < seq; ++j) acc += row[j] * qkv[(size_t)j * qd + 2 * E + ho + d];
+          att[(size_t)i * E + ho + d] = acc;
+        }
+      }
+    }
+    free(row);
+  }
+  mo_matmul(att, wout, y, seq, E, E);
+  free(qkv);
+  free(att);
+}
+
+/* Inline Conv2d case, Model.cpp:4897-5089: OIHW weights, CHW activations, square kernel, zero
+ * padding, NO bias, optional ReLU (:5081-5086).  The fast path (:4971-5046) is im2col rows
+ * ordered (ic, kh, kw) times W^T through matmul_fma_saturated, i.e. one k-sequential FMA chain per
+ * output over k = (ic, kh, kw) including the zero-padded taps (vector columns oc < oc&~7) or
+ * mul+add (scalar tail). */
+void mo_conv2d(const float* x, const float* w, float* y, int ic, int oc, int h, int wd, int k, int stride, int pad,
+               int relu) {
+  const int oh = (h + 2 * pad - k) / stride + 1;
+  const int ow = (wd + 2 * pad - k) / stride + 1;
+  const int K = ic * k * k;
+  const int vec8 = oc & ~7;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int o = 0; o < oc; ++o) {
+    for (int r = 0; r < oh; ++r) {
+      for (int c = 0; c < ow; ++c) {
+        float acc = 0.0f;
+        const float* wo = w + (size_t)o * K;
+        int col = 0;
+        for (int i = 0; i < ic; ++i)
+          for (int kh = 0; kh < k; ++kh) {
+            const int ih = r * stride + kh - pad;
+            for (int kw = 0; kw < k; ++kw, ++col) {
+              const int iw = c * stride + kw - pad;
+              float v = 0.0f;
+              if (ih >= 0 && ih < h && iw >= 0 && iw < wd) v = x[(size_t)i * h * wd + (size_t)ih * wd + iw];
+              if (o < vec8)
+                acc = fmaf(v, wo[col], acc);
+              else
+                acc += v * wo[col];
+            }
+          }
+        if (relu && acc < 0.0f) acc = 0.0f;
+        y[(size_t)o * oh * ow + (size_t)r * ow + c] = acc;
+      }
+    }
+  }
+}
+
+/* pairwise-free helper: the reference's `#pragma omp simd reduction(+)` loops are compiled to
+ * 8-lane partial sums with -mavx2; the restatement sums in double and rounds once, which is
+ * within the vectorised fp32 sum's own error of the true value. */
+static float mean_f(const float* v, long n) {
+  double s = 0.0;
+  for (long i = 0; i < n; ++i) s += v[i];
+  return (float)(s / (double)n);
+}
+
+/* LayerOps::layernorm_forward, LayerOps.hpp:264-319: groups of n, biased variance,
+ * inv_std = 1/sqrt(var+eps), gamma then beta. */
+void mo_layernorm(const float* x, const float* gamma, const float* beta, float* y, long rows, int n, float eps) {
+  for (long g = 0; g < rows; ++g) {
+    const float* xi = x + (size_t)g * n;
+    float* yo = y + (size_t)g * n;
+    const float mean = mean_f(xi, n);
+    double vs = 0.0;
+    for (int i = 0; i < n; ++i) {
+      const float d = xi[i] - mean;
+      vs += (double)(d * d);
+    }
+    const float var = (float)(vs / (double)n);
+    const float inv = 1.0f / sqrtf(var + eps);
+    for (int i = 0; i < n; ++i) {
+      float v = (xi[i] - mean) * inv;
+      if (gamma) {
+        v *= gamma[i];
+        if (beta) v += beta[i];
+      }
+      yo[i] = v;
+    }
+  }
+}
+
+/* LayerOpsExt::rms_norm_forward, LayerOpsExt.hpp:345-378: ONE rms over the whole vector,
+ * y = x / rms, times gamma[i] for i < n_gamma only. */
+void mo_rmsnorm(const float* x, const float* gamma, long n_gamma, float* y, long n, float eps) {
+  double s = 0.0;
+  for (long i = 0; i < n; ++i) s += (double)(x[i] * x[i]);
+  const float rms = sqrtf((float)(s / (double)n) + eps);
+  for (long i = 0; i < n; ++i) {
+    float v = x[i] / rms;
+    if (gamma && i < n_gamma) v *= gamma[i];
+    y[i] = v;
+  }
+}
+
+/* LayerOps::groupnorm_forward, LayerOps.hpp:488-550: group g = contiguous slab of
+ * (C/G)*H*W elements; gamma/beta per channel (:538-543). */
+void mo_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int C_, int h, int w, int G,
+                  float eps) {
+  const long hw = (long)h * w;
+  const long gs = (long)(C_ / G) * hw;
+  for (int g = 0; g < G; ++g) {
+    const float* xi = x + (size_t)g * gs;
+    float* yo = y + (size_t)g * gs;
+    const float mean = mean_f(xi, gs);
+    double vs = 0.0;
+    for (long i = 0; i < gs; ++i) {
+      const float d = xi[i] - mean;
+      vs += (double)(d * d);
+    }
+    const float var = (float)(vs / (double)gs);
+    const float inv = 1.0f / sqrtf(var + eps);
+    for (long i = 0; i < gs; ++i) {
+      float v = (xi[i] - mean) * inv;
+      if (gamma) {
+        const long c = (((long)g * gs + i) / hw) % C_;
+        v = v * gamma[c];
+        if (beta) v += beta[c];
+      }
+      yo[i] = v;
+    }
+  }
+}
+
+/* LayerOps::softmax_forward, LayerOps.hpp:325-361: over the WHOLE vector; log variant
+ * (x - max) - log(sum). */
+void mo_softmax(const float* x, float* y, long n, int log_softmax) {
+  float mx = x[0];
+  for (long i = 1; i < n; ++i)
+    if (x[i] > mx) mx = x[i];
+  double s = 0.0;
+  for (long i = 0; i < n; ++i) {
+    y[i] = expf(x[i] - mx);
+    s += (double)y[i];
+  }
+  const float sum = (float)s;
+  if (log_softmax) {
+    const float ld = logf(sum);
+    for (long i = 0; i < n; ++i) y[i] = (x[i] - mx) - ld;
+    return;
+  }
+  const float inv = 1.0f / sum;
+  for (long i = 0; i < n; ++i) y[i] *= inv;
+}
+
+/* LayerOps.hpp:142-230 (add with scalar / `i % small_n` broadcast; multiply equal sizes) and
+ * :556-623 (GELU tanh form with sqrt(2.0f/3.14159265359f); SiLU = x * 1/(1+exp(-x)); ReLU;
+ * tanh; sigmoid).  Returns non-zero where the reference throws. */
+int mo_eltwise(int op, const float* a, const float* b, float* y, long n, long nb) {
+  switch (op) {
+    case 0: /* add */
+      if (n <= 0 || nb <= 0) return 1;
+      if (nb != n && nb != 1 && (n % nb) != 0) return 1;
+      for (long i = 0; i < n; ++i) y[i] = a[i] + b[nb == n ? i : (nb == 1 ? 0 : i % nb)];
+      return 0;
+    case 1: /* multiply */
+      if (nb != n) return 1;
+      for (long i = 0; i < n; ++i) y[i] = a[i] * b[i];
+      return 0;
+    case 2: { /* gelu */
+      const float c = sqrtf(2.0f / 3.14159265359f);
+      for (long i = 0; i < n; ++i) {
+        const float v = a[i];
+        const float cdf = 0.5f * (1.0f + tanhf(c * (v + 0.044715f * v * v * v)));
+        y[i] = v * cdf;
+      }
+      return 0;
+    }
+    case 3: /* silu */
+      for (long i = 0; i < n; ++i) {
+        const float s = 1.0f / (1.0f + expf(-a[i]));
+        y[i] = a[i] * s;
+      }
+      return 0;
+    case 4:
+      for (long i = 0; i < n; ++i) y[i] = a[i] > 0.0f ? a[i] : 0.0f;
+      return 0;
+    case 5:
+      for (long i = 0; i < n; ++i) y[i] = tanhf(a[i]);
+      return 0;
+    case 6:
+      for (long i = 0; i < n; ++i) y[i] = 1.0f / (1.0f + expf(-a[i]));
+      return 0;
+  }
+  return 1;
+}
+
+/* Embedding case, Model.cpp:5301-5334: id = llround(x); id == padding_idx (when >= 0) or out of
+ * range leaves a zero row. */
+void mo_embedding(const float* ids, const float* table, float* y, long n_ids, int vocab, int dim, int padding_idx) {
+  memset(y, 0, sizeof(float) * (size_t)n_ids * dim);
+  for (long t = 0; t < n_ids; ++t) {
+    const long long id = llround((double)ids[t]);
+    if (padding_idx >= 0 && id == padding_idx) continue;
+    if (id < 0 || id >= vocab) continue;
+    memcpy(y + (size_t)t * dim, table + (size_t)id * dim, sizeof(float) * dim);
+  }
+}
+
+/* LayerOps::upsample_nearest_forward, LayerOps.hpp:802-827. */
+void mo_upsample_nearest(const float* x, float* y, int ch, int in_h, int in_w, int sh, int sw) {
+  const int oh = in_h * sh, ow = in_w * sw;
+  for (int c = 0; c < ch; ++c)
+    for (int r = 0; r < oh; ++r)
+      for (int q = 0; q < ow; ++q)
+        y[(size_t)c * oh * ow + (size_t)r * ow + q] = x[(size_t)c * in_h * in_w + (size_t)(r / sh) * in_w + q / sw];
+}
+
+/* LayerOps::permute_forward, LayerOps.hpp:880-945: out_shape[i] = shape[dims[i]];
+ * in_coords[dims[i]] = out_coords[i]. */
+void mo_permute(const float* x, float* y, int nd, const int* shape, const int* dims) {
+  long in_str[8], out_shape[8], total = 1;
+  in_str[nd - 1] = 1;
+  for (int i = nd - 2; i >= 0; --i) in_str[i] = in_str[i + 1] * shape[i + 1];
+  for (int i = 0; i < nd; ++i) {
+    out_shape[i] = shape[dims[i]];
+    total *= shape[i];
+  }
+  for (long o = 0; o < total; ++o) {
+    long t = o, in_idx = 0;
+    for (int i = nd - 1; i >= 0; --i) {
+      const long c = t % out_shape[i];
+      t /= out_shape[i];
+      in_idx += c * in_str[dims[i]];
+    }
+    y[o] = x[in_idx];
+  }
+}
+
+/* TokenMeanPool, Model.cpp:5571-5589: sequential sum over tokens, then * (1/seq). */
+void mo_token_mean_pool(const float* x, float* y, int seq, int dim) {
+  for (int d = 0; d < dim; ++d) y[d] = 0.0f;
+  for (int t = 0; t < seq; ++t)
+    for (int d = 0; d < dim; ++d) y[d] += x[(size_t)t * dim + d];
+  const float inv = 1.0f / (float)seq;
+  for (int d = 0; d < dim; ++d) y[d] *= inv;
+}
+
+/* LayerOps::global_avgpool2d_forward, LayerOps.hpp:459-482. */
+void mo_global_avgpool(const float* x, float* y, int ch, int h, int w) {
+  const float area = (float)(h * w);
+  for (int c = 0; c < ch; ++c) {
+    float s = 0.0f;
+    for (long i = 0; i < (long)h * w; ++i) s += x[(size_t)c * h * w + i];
+    y[c] = s / area;
+  }
+}

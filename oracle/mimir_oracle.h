@@ -1,0 +1,25 @@
+/* mimir_oracle.h — TEST INFRASTRUCTURE: prototypes of the plain-C restatement (mimir_oracle.c).
+ * One sample per call; see the .c file for the reference file:line each function follows. */
+#ifndef MIMIR_ORACLE_H
+#define MIMIR_ORACLE_H
+#ifdef __cplusplus
+extern "C" {
+#endif
+void mo_linear(const float* x, const float* w, const float* bias, float* y, long rows, int in_f, int out_f);
+void mo_matmul(const float* A, const float* B, float* C, long M, long K, long N);
+void mo_attention(const float* x, const float* wqkv, const float* wout, float* y, int seq, int E, int heads, int causal);
+void mo_conv2d(const float* x, const float* w, float* y, int ic, int oc, int h, int wd, int k, int stride, int pad, int relu);
+void mo_layernorm(const float* x, const float* gamma, const float* beta, float* y, long rows, int n, float eps);
+void mo_rmsnorm(const float* x, const float* gamma, long n_gamma, float* y, long n, float eps);
+void mo_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int C_, int h, int w, int G, float eps);
+void mo_softmax(const float* x, float* y, long n, int log_softmax);
+int  mo_eltwise(int op, const float* a, const float* b, float* y, long n, long nb);
+void mo_embedding(const float* ids, const float* table, float* y, long n_ids, int vocab, int dim, int padding_idx);
+void mo_upsample_nearest(const float* x, float* y, int ch, int in_h, int in_w, int sh, int sw);
+void mo_permute(const float* x, float* y, int nd, const int* shape, const int* dims);
+void mo_token_mean_pool(const float* x, float* y, int seq, int dim);
+void mo_global_avgpool(const float* x, float* y, int ch, int h, int w);
+#ifdef __cplusplus
+}
+#endif
+#endif

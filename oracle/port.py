@@ -1,0 +1,250 @@
+"""TEST INFRASTRUCTURE — ctypes binding of the plain-C restatement (``libmimir_oracle.so``) and a
+restatement of the reference's graph walk.
+
+``run_graph`` follows ``Model::forwardPassView`` (Model.cpp:4621-6824): a tensor store keyed by
+name, initialised with the main input under ``"x"`` and ``"__input__"`` (:4640-4642) plus the extra
+named inputs (:4663-4667); each layer reads ``inputs`` (empty => ``{"x"}``, :4802), runs its op,
+and stores under ``output`` (empty => ``"x"``, :6655); the result is ``store["x"]`` (:6823).
+One sample per call, like the reference.  Never imported by the product.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmimir_oracle.so")
+_lib = None
+
+ELT = {"Add": 0, "Multiply": 1, "GELU": 2, "SiLU": 3, "ReLU": 4, "Tanh": 5, "Sigmoid": 6}
+
+
+def build():
+    subprocess.run(["make", "-C", _HERE, "port"], check=True, capture_output=True)
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            build()
+        _lib = C.CDLL(LIB_PATH)
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p) if a is not None else None
+
+
+def _f(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def linear(x, w, bias, rows, in_f, out_f):
+    x, w = _f(x), _f(w)
+    bias = _f(bias) if bias is not None else None
+    y = np.empty(rows * out_f, np.float32)
+    lib().mo_linear(_p(x), _p(w), _p(bias), _p(y), C.c_long(rows), C.c_int(in_f), C.c_int(out_f))
+    return y
+
+
+def matmul(a, b, M, K, N):
+    a, b = _f(a), _f(b)
+    y = np.empty(M * N, np.float32)
+    lib().mo_matmul(_p(a), _p(b), _p(y), C.c_long(M), C.c_long(K), C.c_long(N))
+    return y
+
+
+def attention(x, wblock, seq, E, heads, causal):
+    x, wblock = _f(x), _f(wblock)
+    wqkv, wout = wblock[: 3 * E * E], np.ascontiguousarray(wblock[3 * E * E : 4 * E * E])
+    y = np.empty(seq * E, np.float32)
+    lib().mo_attention(_p(x), _p(wqkv), _p(wout), _p(y), C.c_int(seq), C.c_int(E), C.c_int(heads), C.c_int(int(causal)))
+    return y
+
+
+def conv2d(x, w, ic, oc, h, wd, k, stride, pad, relu):
+    x, w = _f(x), _f(w)
+    oh = (h + 2 * pad - k) // stride + 1
+    ow = (wd + 2 * pad - k) // stride + 1
+    y = np.empty(oc * oh * ow, np.float32)
+    lib().mo_conv2d(_p(x), _p(w), _p(y), *(C.c_int(v) for v in (ic, oc, h, wd, k, stride, pad, int(relu))))
+    return y
+
+
+def layernorm(x, gamma, beta, rows, n, eps):
+    x = _f(x)
+    gamma = _f(gamma) if gamma is not None else None
+    beta = _f(beta) if beta is not None else None
+    y = np.empty_like(x)
+    lib().mo_layernorm(_p(x), _p(gamma), _p(beta), _p(y), C.c_long(rows), C.c_int(n), C.c_float(eps))
+    return y
+
+
+def rmsnorm(x, gamma, eps):
+    x = _f(x)
+    gamma = _f(gamma) if gamma is not None and len(gamma) else None
+    y = np.empty_like(x)
+    lib().mo_rmsnorm(_p(x), _p(gamma), C.c_long(0 if gamma is None else gamma.size), _p(y), C.c_long(x.size), C.c_float(eps))
+    return y
+
+
+def groupnorm(x, gamma, beta, ch, h, w, groups, eps):
+    x = _f(x)
+    gamma = _f(gamma) if gamma is not None else None
+    beta = _f(beta) if beta is not None else None
+    y = np.empty_like(x)
+    lib().mo_groupnorm(_p(x), _p(gamma), _p(beta), _p(y), C.c_int(ch), C.c_int(h), C.c_int(w), C.c_int(groups), C.c_float(eps))
+    return y
+
+
+def softmax(x, log=False):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().mo_softmax(_p(x), _p(y), C.c_long(x.size), C.c_int(int(log)))
+    return y
+
+
+def eltwise(op, a, b=None):
+    a = _f(a)
+    b = _f(b) if b is not None else None
+    if b is not None and b.size > a.size:
+        a, b = b, a  # add_forward swaps so that `big` is first (LayerOps.hpp:171-176)
+    y = np.empty_like(a)
+    rc = lib().mo_eltwise(C.c_int(op), _p(a), _p(b), _p(y), C.c_long(a.size), C.c_long(0 if b is None else b.size))
+    if rc:
+        raise RuntimeError("eltwise: sizes not broadcastable")
+    return y
+
+
+def embedding(ids, table, vocab, dim, padding_idx):
+    ids, table = _f(ids), _f(table)
+    y = np.empty(ids.size * dim, np.float32)
+    lib().mo_embedding(_p(ids), _p(table), _p(y), C.c_long(ids.size), C.c_int(vocab), C.c_int(dim), C.c_int(padding_idx))
+    return y
+
+
+def upsample_nearest(x, ch, in_h, in_w, sh, sw):
+    x = _f(x)
+    y = np.empty(ch * in_h * sh * in_w * sw, np.float32)
+    lib().mo_upsample_nearest(_p(x), _p(y), *(C.c_int(v) for v in (ch, in_h, in_w, sh, sw)))
+    return y
+
+
+def permute(x, shape, dims):
+    x = _f(x)
+    y = np.empty_like(x)
+    sh = (C.c_int * len(shape))(*shape)
+    dm = (C.c_int * len(dims))(*dims)
+    lib().mo_permute(_p(x), _p(y), C.c_int(len(shape)), sh, dm)
+    return y
+
+
+def token_mean_pool(x, seq, dim):
+    x = _f(x)
+    y = np.empty(dim, np.float32)
+    lib().mo_token_mean_pool(_p(x), _p(y), C.c_int(seq), C.c_int(dim))
+    return y
+
+
+def global_avgpool(x, ch, h, w):
+    x = _f(x)
+    y = np.empty(ch, np.float32)
+    lib().mo_global_avgpool(_p(x), _p(y), C.c_int(ch), C.c_int(h), C.c_int(w))
+    return y
+
+
+def run_layer(d, ins, w):
+    """One layer of the switch in Model::forwardPassView (Model.cpp:4891-6291) on one sample."""
+    t = d.type.decode()
+    x = ins[0]
+    if t == "Linear":
+        in_f = d.in_features if d.in_features > 0 else x.size
+        rows = d.seq_len if (d.seq_len > 0 and x.size == d.seq_len * in_f) else 1
+        if rows == 1 and x.size != in_f:
+            raise RuntimeError("Linear: input size mismatch")
+        bias = w[in_f * d.out_features : in_f * d.out_features + d.out_features] if d.use_bias else None
+        return linear(x, w[: in_f * d.out_features], bias, rows, in_f, d.out_features)
+    if t in ("SelfAttention", "MultiHeadAttention"):
+        seq = d.seq_len if d.seq_len > 0 else 1
+        E = d.embed_dim if d.embed_dim > 0 else x.size
+        heads = d.num_heads if d.num_heads > 0 else 1
+        return attention(x, w, seq, E, heads, d.causal)
+    if t == "Conv2d":
+        ic = d.in_channels
+        h = d.input_height if d.input_height > 0 else 64
+        wd = d.input_width if d.input_width > 0 else 64
+        if h * wd * ic != x.size:  # Model.cpp:4916-4944
+            hw = x.size // ic
+            if d.input_height > 0 and hw % d.input_height == 0:
+                h, wd = d.input_height, hw // d.input_height
+            elif d.input_width > 0 and hw % d.input_width == 0:
+                wd, h = d.input_width, hw // d.input_width
+            else:
+                s = int(round(hw ** 0.5))
+                if s * s == hw:
+                    h = wd = s
+        return conv2d(x, w, ic, d.out_channels, h, wd, d.kernel, d.stride, d.padding, d.activation != 0)
+    if t == "LayerNorm":
+        n = d.in_features if d.in_features > 0 else x.size
+        gamma = w[:n] if d.affine else None
+        beta = w[n : 2 * n] if (d.affine and d.use_bias) else None
+        return layernorm(x, gamma, beta, x.size // n, n, d.eps)
+    if t == "RMSNorm":
+        return rmsnorm(x, w if (d.affine and w is not None) else None, d.eps)
+    if t == "GroupNorm":
+        ch = d.in_channels if d.in_channels > 0 else 64
+        h = d.input_height if d.input_height > 0 else 32
+        wd = d.input_width if d.input_width > 0 else 32
+        gamma = w[:ch] if d.affine else None
+        beta = w[ch : 2 * ch] if (d.affine and d.use_bias) else None
+        return groupnorm(x, gamma, beta, ch, h, wd, d.num_groups, d.eps)
+    if t in ("Softmax", "LogSoftmax"):
+        return softmax(x, t == "LogSoftmax")
+    if t in ("GELU", "SiLU", "ReLU", "Tanh", "Sigmoid"):
+        return eltwise(ELT[t], x)
+    if t in ("Add", "Multiply"):
+        if len(ins) < 2:
+            raise RuntimeError(f"{t} layer requires 2 inputs")
+        return eltwise(ELT[t], ins[0], ins[1])
+    if t == "Embedding":
+        return embedding(x, w, max(1, d.vocab_size), max(1, d.embed_dim), d.padding_idx)
+    if t == "UpsampleNearest":
+        sh = d.scale_h if d.scale_h > 0 else 2
+        sw = d.scale_w if d.scale_w > 0 else 2
+        return upsample_nearest(x, d.in_channels, d.out_h, d.out_w, sh, sw)
+    if t == "Permute":
+        return permute(x, list(d.shape[: d.n_dims]), list(d.permute_dims[: d.n_dims]))
+    if t == "Concat":
+        return np.concatenate([_f(i) for i in ins])
+    if t in ("Identity", "Reshape", "Flatten", "View", "Dropout", "Dropout2d"):
+        return _f(x).copy()
+    if t == "TokenMeanPool":
+        return token_mean_pool(x, d.seq_len, d.embed_dim)
+    if t in ("GlobalAvgPool2d", "AdaptiveAvgPool2d"):
+        ch = d.in_channels if d.in_channels > 0 else 64
+        h = d.input_height if d.input_height > 0 else 32
+        wd = d.input_width if d.input_width > 0 else 32
+        return global_avgpool(x, ch, h, wd)
+    raise NotImplementedError(t)
+
+
+def run_graph(descs, weights, inputs):
+    """descs: list of MimirLayerDesc; weights: list of arrays (or None); inputs: name -> array."""
+    store = {}
+    main = inputs.get("x", inputs.get("__input__"))
+    store["x"] = _f(main)
+    store["__input__"] = _f(main)
+    for k, v in inputs.items():
+        store[k] = _f(v)
+    for d, w in zip(descs, weights):
+        names = [d.inputs[i].decode() for i in range(d.n_inputs)] or ["x"]
+        for n in names:
+            if n not in store:
+                raise RuntimeError("Missing input tensor: " + n)
+        out = run_layer(d, [store[n] for n in names], None if w is None else _f(w))
+        store[(d.output or b"x").decode() or "x"] = out
+    return store["x"]
