@@ -227,13 +227,19 @@ int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInpu
 int mimir_b200_argmax_rows_device(const float* x_dev, int32_t* ids_dev, long long rows, int n,
                                   void* stream);
 int mimir_b200_get_stats(MimirB200Stats* out);
+/* Reads (and clears) the device word that bounded in-kernel waits set when they give up:
+ * OK, or E_TIMEOUT.  model_forward and the host-pointer calls check it themselves. */
+int mimir_b200_check_device(void* stream);
+/* Live timing of the contraction (GEMM) kernel: while enabled, every launch is bracketed by CUDA
+ * events on the launching stream; profile_read synchronises, returns the summed duration and the
+ * number of launches, and clears the record.  No counterpart in the reference. */
+int mimir_b200_profile_gemm(int enable);
+int mimir_b200_profile_read(float* total_ms, int* launches);
 
 /* ---------------------------------------------------------------------------------------------
  * Device-pointer forms of the per-op calls (inputs already resident in HBM, asynchronous on
  * `stream`).  The host-pointer forms above are these plus the copies.
  * ------------------------------------------------------------------------------------------ */
-int mimir_b200_dev_linear(const float* x, const float* w, const float* bias_or_null, float* y,
-                          int rows, int in_f, int out_f, int precision, int activation, void* stream);
 int mimir_b200_dev_layernorm(const float* x, const float* gamma, const float* beta, float* y,
                              long long rows, int n, float eps, void* stream);
 int mimir_b200_dev_rmsnorm(const float* x, const float* gamma, long long n_gamma, float* y,

@@ -1,0 +1,257 @@
+// attention.cu — the attention core between the QKV projection and the output projection.
+// Replaces steps 3-5 of LayerOps::self_attention_forward (LayerOps.hpp:1044-1090): per head h and
+// query row i, s_j = (Q_i . K_j) / sqrt(hd); causal rows skip j > i (the reference scores them
+// -1e9 and keeps them out of the max, so they contribute exp(-1e9 - max) = 0); p = exp(s - max);
+// p *= 1 / (sum p + 1e-9); O_i = sum_j p_j V_j.
+//
+// Flash-style: a CTA owns 64 query rows of one (sample, head) and walks the keys in tiles of 64
+// with an online softmax, so the seq x seq score matrix never exists in memory.  fp32 arithmetic
+// on the CUDA cores; K and Q tiles are held d-major in shared memory so that the 4x4 register
+// blocks read them as conflict-free 128-bit vectors.
+#include "common.h"
+
+namespace mb {
+namespace {
+
+constexpr int BQ = 64, BKV = 64, LDT = 68;  // LDT: padded leading dimension of the d-major tiles
+
+template <int HD>
+__global__ void __launch_bounds__(256)
+flash_attn_fp32_kernel(const float* __restrict__ qkv, float* __restrict__ out, int seq, int embed, int heads, int causal,
+                       float scale) {
+  constexpr int CPT = HD / 16;  // output columns per thread
+  extern __shared__ __align__(16) float sm[];
+  float* Qt = sm;                 // [HD][LDT]   Qt[d][row]
+  float* Kt = Qt + HD * LDT;      // [HD][LDT]   Kt[d][key]
+  float* Vs = Kt + HD * LDT;      // [BKV][HD]
+  float* Pt = Vs + BKV * HD;      // [BKV][LDT]  Pt[key][row]
+
+  const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qt * BQ;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const long long ld = 3LL * embed;
+  const float* base = qkv + static_cast<long long>(b) * seq * ld + h * HD;
+
+  // Q tile, transposed into Qt (rows past seq are zero)
+  for (int i = tid; i < BQ * (HD / 4); i += 256) {
+    const int r = i / (HD / 4), c4 = (i - r * (HD / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (q0 + r < seq) v = __ldg(reinterpret_cast<const float4*>(base + (q0 + r) * ld + c4));
+    Qt[(c4 + 0) * LDT + r] = v.x; Qt[(c4 + 1) * LDT + r] = v.y; Qt[(c4 + 2) * LDT + r] = v.z; Qt[(c4 + 3) * LDT + r] = v.w;
+  }
+
+  float m_run[4], l_run[4], o_acc[4][CPT];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m_run[i] = -1e30f;  // the reference's initial max (LayerOps.hpp:1052)
+    l_run[i] = 0.0f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) o_acc[i][c] = 0.0f;
+  }
+
+  const int kv_end = causal ? min(seq, q0 + BQ) : seq;
+  for (int k0 = 0; k0 < kv_end; k0 += BKV) {
+    __syncthreads();  // previous tile fully consumed (also orders the Qt writes before first use)
+    for (int i = tid; i < BKV * (HD / 4); i += 256) {
+      const int r = i / (HD / 4), c4 = (i - r * (HD / 4)) * 4;
+      float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+      if (k0 + r < seq) {
+        kv = __ldg(reinterpret_cast<const float4*>(base + (k0 + r) * ld + embed + c4));
+        vv = __ldg(reinterpret_cast<const float4*>(base + (k0 + r) * ld + 2 * embed + c4));
+      }
+      Kt[(c4 + 0) * LDT + r] = kv.x; Kt[(c4 + 1) * LDT + r] = kv.y; Kt[(c4 + 2) * LDT + r] = kv.z; Kt[(c4 + 3) * LDT + r] = kv.w;
+      *reinterpret_cast<float4*>(Vs + r * HD + c4) = vv;
+    }
+    __syncthreads();
+
+    // S = Q K^T for this thread's 4 rows x 4 keys
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.0f;
+#pragma unroll 8
+    for (int d = 0; d < HD; ++d) {
+      const float4 q4 = *reinterpret_cast<const float4*>(Qt + d * LDT + ty * 4);
+      const float4 k4 = *reinterpret_cast<const float4*>(Kt + d * LDT + tx * 4);
+      const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] += qa[i] * ka[j];
+    }
+
+    // online softmax over the 64 keys of this tile (16 threads share a row)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qi = q0 + ty * 4 + i;
+      float mx = -1e30f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kj = k0 + tx * 4 + j;
+        const bool valid = (kj < seq) && (!causal || kj <= qi);
+        s[i][j] = valid ? s[i][j] * scale : -INFINITY;
+        if (valid) mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_new = fmaxf(m_run[i], mx);
+      const float corr = expf(m_run[i] - m_new);
+      float rs = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float p = (s[i][j] == -INFINITY) ? 0.0f : expf(s[i][j] - m_new);
+        s[i][j] = p;
+        rs += p;
+      }
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
+      l_run[i] = l_run[i] * corr + rs;
+      m_run[i] = m_new;
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) o_acc[i][c] *= corr;
+    }
+    // P^T to shared memory: Pt[key][row]
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      *reinterpret_cast<float4*>(Pt + (tx * 4 + j) * LDT + ty * 4) = make_float4(s[0][j], s[1][j], s[2][j], s[3][j]);
+    __syncthreads();
+
+    // O += P V
+#pragma unroll 4
+    for (int j = 0; j < BKV; ++j) {
+      const float4 p4 = *reinterpret_cast<const float4*>(Pt + j * LDT + ty * 4);
+      const float pa[4] = {p4.x, p4.y, p4.z, p4.w};
+      float va[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; c += 2) {
+        const float2 v2 = *reinterpret_cast<const float2*>(Vs + j * HD + tx * CPT + c);
+        va[c] = v2.x;
+        va[c + 1] = v2.y;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) o_acc[i][c] += pa[i] * va[c];
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int qi = q0 + ty * 4 + i;
+    if (qi >= seq) continue;
+    const float inv = 1.0f / (l_run[i] + 1e-9f);  // LayerOps.hpp:1076
+    float* o = out + (static_cast<long long>(b) * seq + qi) * embed + h * HD + tx * CPT;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) o[c] = o_acc[i][c] * inv;
+  }
+}
+
+// Any head dimension: one CTA per (sample, head, query row); the score row lives in shared memory.
+__global__ void attn_row_kernel(const float* __restrict__ qkv, float* __restrict__ out, int seq, int embed, int heads, int hd,
+                                int causal, float scale) {
+  extern __shared__ __align__(16) float sm[];
+  float* q = sm;         // [hd]
+  float* p = sm + hd;    // [seq]
+  __shared__ float red[33];
+  const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const long long ld = 3LL * embed;
+  const float* base = qkv + static_cast<long long>(b) * seq * ld + h * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) q[d] = base[i * ld + d];
+  __syncthreads();
+  const int n_keys = causal ? (i + 1) : seq;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  float mx = -1e30f;
+  for (int j = w; j < n_keys; j += nw) {  // one warp per key: coalesced reads of the K row
+    const float* kr = base + j * ld + embed;
+    float dot = 0.0f;
+    for (int d = lane; d < hd; d += 32) dot += q[d] * __ldg(kr + d);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float s = dot * scale;
+    if (lane == 0) p[j] = s;
+    mx = fmaxf(mx, s);
+  }
+  // block max
+  __syncthreads();
+  if (lane == 0) red[w] = mx;
+  __syncthreads();
+  if (w == 0) {
+    float t = (lane < nw) ? red[lane] : -1e30f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  mx = red[32];
+  float acc = 0.0f;
+  for (int j = threadIdx.x; j < n_keys; j += blockDim.x) {
+    const float e = expf(p[j] - mx);
+    p[j] = e;
+    acc += e;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __syncthreads();
+  if (lane == 0) red[w] = acc;
+  __syncthreads();
+  if (w == 0) {
+    float t = (lane < nw) ? red[lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  const float inv = 1.0f / (red[32] + 1e-9f);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    const float* vr = base + 2 * embed + d;
+    float o = 0.0f;
+    for (int j = 0; j < n_keys; ++j) o += p[j] * __ldg(vr + j * ld);
+    out[(static_cast<long long>(b) * seq + i) * embed + h * hd + d] = o * inv;
+  }
+}
+
+template <int HD>
+int launch_flash(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, float scale,
+                 cudaStream_t st) {
+  constexpr int SMEM = (2 * HD * LDT + BKV * HD + BKV * LDT) * 4;
+  static bool attr = false;
+  if (!attr) {
+    MB_CUDA(cudaFuncSetAttribute(flash_attn_fp32_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    attr = true;
+  }
+  dim3 grid((seq + BQ - 1) / BQ, heads, batch);
+  flash_attn_fp32_kernel<HD><<<grid, 256, SMEM, st>>>(qkv, out, seq, embed, heads, causal, scale);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+}  // namespace
+
+int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
+                          cudaStream_t st) {
+  if (batch <= 0 || seq <= 0 || embed <= 0 || heads <= 0 || embed % heads != 0)
+    return fail(MIMIR_B200_E_INVALID, "SelfAttention: embed_dim must be divisible by num_heads");
+  const int hd = embed / heads;
+  const float scale = 1.0f / sqrtf(static_cast<float>(hd));
+  const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) & 15) == 0) && (embed % 4 == 0);
+  if (aligned && hd == 32) return launch_flash<32>(qkv, out, batch, seq, embed, heads, causal, scale, st);
+  if (aligned && hd == 64) return launch_flash<64>(qkv, out, batch, seq, embed, heads, causal, scale, st);
+  if (aligned && hd == 128) return launch_flash<128>(qkv, out, batch, seq, embed, heads, causal, scale, st);
+  const size_t smem = static_cast<size_t>(hd + seq) * 4;
+  if (smem > 200 * 1024 || batch > 65535 || heads > 65535)
+    return fail(MIMIR_B200_E_UNSUPPORTED, "attention: seq %d with head_dim %d exceeds the row kernel's shared memory", seq, hd);
+  static size_t attr_bytes = 0;
+  if (smem > 48 * 1024 && smem > attr_bytes) {
+    MB_CUDA(cudaFuncSetAttribute(attn_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    attr_bytes = smem;
+  }
+  dim3 grid(seq, heads, batch);
+  attn_row_kernel<<<grid, 256, smem, st>>>(qkv, out, seq, embed, heads, hd, causal, scale);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+}  // namespace mb

@@ -1,0 +1,614 @@
+// capi.cu — the C ABI of include/mimir_b200.h: process context and HBM budget guard, the per-op
+// entry points with host pointers (drop-in for ComputeEngine::linearForward,
+// VulkanCompute.hpp:209-210), and their device-pointer forms.  The whole-graph entry points live
+// in graph.cu.  No function here throws; none falls back to the CPU.
+#include "ops.h"
+
+#include <cstdlib>
+#include <cstring>
+#include <vector>
+
+namespace mb {
+
+// ---------------------------------------------------------------------------------------------
+// context, errors, guard
+// ---------------------------------------------------------------------------------------------
+std::string& last_error() {
+  thread_local std::string e;
+  return e;
+}
+
+int fail(int status, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  last_error() = buf;
+  return status;
+}
+
+Context& ctx() {
+  static Context c;
+  return c;
+}
+
+bool Guard::request(size_t bytes) {
+  std::lock_guard<std::mutex> lk(mu);
+  if (limit != 0 && current + bytes > limit) return false;
+  current += bytes;
+  if (current > peak) peak = current;
+  return true;
+}
+void Guard::release(size_t bytes) {
+  std::lock_guard<std::mutex> lk(mu);
+  current = (bytes > current) ? 0 : current - bytes;
+}
+
+int dev_alloc(void** p, size_t bytes, const char* tag) {
+  *p = nullptr;
+  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
+  if (bytes == 0) return MIMIR_B200_OK;
+  if (!ctx().guard.request(bytes))
+    return fail(MIMIR_B200_E_OOM_BUDGET, "HBM budget refused %zu bytes for %s (limit %zu, in use %zu)", bytes, tag,
+                ctx().guard.limit, ctx().guard.current);
+  cudaError_t e = cudaMalloc(p, bytes);
+  if (e != cudaSuccess) {
+    ctx().guard.release(bytes);
+    *p = nullptr;
+    return fail(MIMIR_B200_E_CUDA, "cudaMalloc(%zu) for %s failed: %s", bytes, tag, cudaGetErrorString(e));
+  }
+  return MIMIR_B200_OK;
+}
+
+void dev_free(void* p, size_t bytes) {
+  if (!p) return;
+  cudaFree(p);
+  ctx().guard.release(bytes);
+}
+
+// Reads (and clears) the word that kernels with bounded waits set when a wait gave up.
+int check_device_error_word(cudaStream_t st) {
+  int w = 0;
+  MB_CUDA(cudaMemcpyAsync(&w, ctx().dev_error_word, sizeof(int), cudaMemcpyDeviceToHost, st));
+  MB_CUDA(cudaStreamSynchronize(st));
+  if (w != 0) {
+    cudaMemsetAsync(ctx().dev_error_word, 0, sizeof(int), st);
+    cudaStreamSynchronize(st);
+    return fail(MIMIR_B200_E_TIMEOUT, "a device-side wait gave up (site %d)", w);
+  }
+  return MIMIR_B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// op sequences on device pointers (shared by the per-op ABI and the graph executor)
+// ---------------------------------------------------------------------------------------------
+void precision_planes(int precision, int* a_planes, int* w_planes) {
+  *a_planes = (precision == MIMIR_B200_PREC_BF16) ? 1 : 2;
+  *w_planes = (precision == MIMIR_B200_PREC_BF16X2) ? 2 : 1;
+}
+
+size_t split_bytes(int64_t rows, int k, int planes) {
+  return static_cast<size_t>(planes) * static_cast<size_t>(plane_elems(rows, k)) * sizeof(__nv_bfloat16);
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+bool linear_uses_skinny(int rows, int precision) { return rows <= 16 && precision == MIMIR_B200_PREC_BF16X2; }
+
+size_t linear_ws_bytes(int rows, int in_f, int out_f, int precision, bool a_presplit) {
+  if (linear_uses_skinny(rows, precision)) return align256(skinny_scratch_bytes(rows, in_f, out_f));
+  if (a_presplit) return 0;
+  int ap, wp;
+  precision_planes(precision, &ap, &wp);
+  return align256(split_bytes(rows, in_f, ap));
+}
+
+int linear_exec(const LinearExec& e, cudaStream_t st) {
+  if (linear_uses_skinny(e.rows, e.precision)) {
+    if (!e.x_f32 || !e.w_f32 || !e.y_f32) return fail(MIMIR_B200_E_INVALID, "linear: skinny path needs fp32 operands");
+    MB_TRY(launch_skinny_linear(e.x_f32, e.w_f32, e.bias, e.y_f32, e.rows, e.in_f, e.out_f, e.activation,
+                                static_cast<float*>(e.ws), e.ws_bytes, st));
+    if (e.residual) MB_TRY(launch_eltwise(MIMIR_B200_ELT_ADD, e.y_f32, e.residual, e.y_f32, 1,
+                                          static_cast<int64_t>(e.rows) * e.out_f, static_cast<int64_t>(e.rows) * e.out_f, st));
+    return MIMIR_B200_OK;
+  }
+  int ap, wp;
+  precision_planes(e.precision, &ap, &wp);
+  const __nv_bfloat16* a = e.x_split;
+  if (!a) {
+    if (!e.x_f32 || !e.ws) return fail(MIMIR_B200_E_INVALID, "linear: no activation operand");
+    MB_TRY(launch_split(e.x_f32, static_cast<__nv_bfloat16*>(e.ws), e.rows, e.in_f, ap, st));
+    a = static_cast<const __nv_bfloat16*>(e.ws);
+  }
+  GemmArgs g;
+  g.a = a;
+  g.w = e.w_split;
+  g.a_planes = ap;
+  g.w_planes = wp;
+  g.m = e.rows;
+  g.n = e.out_f;
+  g.k = e.in_f;
+  g.bias = e.bias;
+  g.residual = e.residual;
+  g.activation = e.activation;
+  g.out_f32 = e.y_f32;
+  g.ldo = e.out_f;
+  g.out_nchw_hw = e.out_nchw_hw;
+  g.out_split = e.y_split;
+  return launch_gemm(g, st);
+}
+
+// Attention = QKV projection (GEMM) -> flash core -> output projection (GEMM).
+// Workspace: split(x) | qkv fp32 | attended fp32 | split(attended)
+size_t attention_ws_bytes(int rows, int embed, int precision) {
+  int ap, wp;
+  precision_planes(precision, &ap, &wp);
+  return align256(split_bytes(rows, embed, ap)) + align256(static_cast<size_t>(rows) * 3 * embed * 4) +
+         align256(static_cast<size_t>(rows) * embed * 4);
+}
+
+int attention_exec(const AttentionExec& e, cudaStream_t st) {
+  int ap, wp;
+  precision_planes(e.precision, &ap, &wp);
+  const int rows = e.batch * e.seq;
+  uint8_t* ws = static_cast<uint8_t*>(e.ws);
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ws);
+  float* qkv = reinterpret_cast<float*>(ws + align256(split_bytes(rows, e.embed, ap)));
+  float* att = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(qkv) + align256(static_cast<size_t>(rows) * 3 * e.embed * 4));
+  MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
+  GemmArgs g;
+  g.a = xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
+  g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
+  MB_TRY(launch_gemm(g, st));
+  MB_TRY(launch_attention_core(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, st));
+  MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));  // the x planes are dead by now
+  GemmArgs o;
+  o.a = xs; o.w = e.wout_split; o.a_planes = ap; o.w_planes = wp;
+  o.m = rows; o.n = e.embed; o.k = e.embed; o.out_f32 = e.y; o.ldo = e.embed; o.residual = e.residual;
+  return launch_gemm(o, st);
+}
+
+// Conv2d = im2col planes (per batch chunk) -> GEMM with an NCHW epilogue.
+int conv_chunk_samples(int batch, int ohw, int k, int precision) {
+  int ap, wp;
+  precision_planes(precision, &ap, &wp);
+  const size_t per_sample = split_bytes(ohw, k, ap);
+  const size_t target = size_t(1) << 30;  // ~1 GB of im2col planes in flight
+  long long c = static_cast<long long>(target / (per_sample ? per_sample : 1));
+  if (c < 1) c = 1;
+  if (c > batch) c = batch;
+  return static_cast<int>(c);
+}
+
+size_t conv_ws_bytes(int batch, int ohw, int k, int precision) {
+  int ap, wp;
+  precision_planes(precision, &ap, &wp);
+  return align256(split_bytes(static_cast<int64_t>(conv_chunk_samples(batch, ohw, k, precision)) * ohw, k, ap));
+}
+
+int conv_exec(const ConvExec& e, cudaStream_t st) {
+  int ap, wp;
+  precision_planes(e.precision, &ap, &wp);
+  const int oh = (e.h + 2 * e.pad - e.ks) / e.stride + 1;
+  const int ow = (e.w + 2 * e.pad - e.ks) / e.stride + 1;
+  if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: empty output");
+  const int ohw = oh * ow, k = e.ic * e.ks * e.ks;
+  const int chunk = conv_chunk_samples(e.batch, ohw, k, e.precision);
+  for (int b0 = 0; b0 < e.batch; b0 += chunk) {
+    const int bc = (e.batch - b0 < chunk) ? (e.batch - b0) : chunk;
+    MB_TRY(launch_im2col_split(e.x + static_cast<size_t>(b0) * e.ic * e.h * e.w, static_cast<__nv_bfloat16*>(e.ws), bc, e.ic,
+                               e.h, e.w, e.ks, e.stride, e.pad, oh, ow, ap, st));
+    GemmArgs g;
+    g.a = static_cast<const __nv_bfloat16*>(e.ws);
+    g.w = e.w_split;
+    g.a_planes = ap; g.w_planes = wp;
+    g.m = bc * ohw; g.n = e.oc; g.k = k;
+    g.activation = e.activation;
+    g.out_f32 = e.y + static_cast<size_t>(b0) * e.oc * ohw;
+    g.residual = e.residual ? e.residual + static_cast<size_t>(b0) * e.oc * ohw : nullptr;
+    g.out_nchw_hw = ohw;
+    g.ldo = e.oc;
+    MB_TRY(launch_gemm(g, st));
+  }
+  return MIMIR_B200_OK;
+}
+
+}  // namespace mb
+
+// ---------------------------------------------------------------------------------------------
+// extern "C": life cycle, guard, per-op entry points
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+using namespace mb;
+
+std::mutex g_init_mu;
+
+// Device buffers of one host-pointer call; everything is released when the call returns.
+struct Temps {
+  std::vector<std::pair<void*, size_t>> bufs;
+  ~Temps() {
+    for (auto& b : bufs) dev_free(b.first, b.second);
+  }
+  int alloc(void** p, size_t bytes, const char* tag) {
+    MB_TRY(dev_alloc(p, bytes ? bytes : 4, tag));
+    bufs.emplace_back(*p, bytes ? bytes : 4);
+    return MIMIR_B200_OK;
+  }
+  int upload(const float** dev, const float* host, size_t n, const char* tag) {
+    void* p;
+    MB_TRY(alloc(&p, n * sizeof(float), tag));
+    MB_CUDA(cudaMemcpy(p, host, n * sizeof(float), cudaMemcpyHostToDevice));
+    *dev = static_cast<const float*>(p);
+    return MIMIR_B200_OK;
+  }
+  int out(float** dev, size_t n, const char* tag) {
+    void* p;
+    MB_TRY(alloc(&p, n * sizeof(float), tag));
+    *dev = static_cast<float*>(p);
+    return MIMIR_B200_OK;
+  }
+};
+
+int finish_download(float* host, const float* dev, size_t n) {
+  MB_TRY(check_device_error_word(nullptr));
+  MB_CUDA(cudaMemcpy(host, dev, n * sizeof(float), cudaMemcpyDeviceToHost));
+  return MIMIR_B200_OK;
+}
+
+#define MB_REQUIRE_INIT() \
+  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called")
+
+}  // namespace
+
+extern "C" {
+
+int mimir_b200_abi_version(void) { return MIMIR_B200_ABI_VERSION; }
+const char* mimir_b200_last_error(void) { return mb::last_error().c_str(); }
+
+int mimir_b200_init(int device, size_t hbm_budget_bytes) {
+  std::lock_guard<std::mutex> lk(g_init_mu);
+  Context& c = ctx();
+  if (c.initialised) {
+    if (device != c.device) return fail(MIMIR_B200_E_INVALID, "already initialised on device %d", c.device);
+    if (hbm_budget_bytes) c.guard.limit = hbm_budget_bytes;
+    return MIMIR_B200_OK;
+  }
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count <= 0)
+    return fail(MIMIR_B200_E_CUDA, "no CUDA device: %s (this backend has no CPU fallback)", cudaGetErrorString(e));
+  if (device < 0 || device >= count) return fail(MIMIR_B200_E_INVALID, "device %d out of range (0..%d)", device, count - 1);
+  MB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  MB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(MIMIR_B200_E_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                prop.minor);
+  c.device = device;
+  c.sm_count = prop.multiProcessorCount;
+  size_t free_b = 0, total_b = 0;
+  MB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+  c.guard.limit = hbm_budget_bytes ? hbm_budget_bytes : static_cast<size_t>(total_b * 0.9);
+  c.guard.current = 0;
+  c.guard.peak = 0;
+  c.initialised = true;
+  void* w = nullptr;
+  int s = dev_alloc(&w, 256, "error_word");
+  if (s != MIMIR_B200_OK) {
+    c.initialised = false;
+    return s;
+  }
+  c.dev_error_word = static_cast<int*>(w);
+  MB_CUDA(cudaMemset(c.dev_error_word, 0, 256));
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_guard_set_limit(size_t bytes) {
+  MB_REQUIRE_INIT();
+  std::lock_guard<std::mutex> lk(ctx().guard.mu);
+  ctx().guard.limit = bytes;
+  return MIMIR_B200_OK;
+}
+int mimir_b200_guard_request(size_t bytes, const char* tag) {
+  MB_REQUIRE_INIT();
+  if (!ctx().guard.request(bytes))
+    return fail(MIMIR_B200_E_OOM_BUDGET, "HBM budget refused %zu bytes for %s", bytes, tag ? tag : "?");
+  return MIMIR_B200_OK;
+}
+int mimir_b200_guard_release(size_t bytes) {
+  MB_REQUIRE_INIT();
+  ctx().guard.release(bytes);
+  return MIMIR_B200_OK;
+}
+int mimir_b200_guard_stats(size_t* limit, size_t* current, size_t* peak) {
+  MB_REQUIRE_INIT();
+  std::lock_guard<std::mutex> lk(ctx().guard.mu);
+  if (limit) *limit = ctx().guard.limit;
+  if (current) *current = ctx().guard.current;
+  if (peak) *peak = ctx().guard.peak;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_linear_forward_ex(const float* input, const float* weights, const float* bias_or_null, float* output,
+                                 int batch, int in_f, int out_f, int precision, int activation) {
+  MB_REQUIRE_INIT();
+  if (!input || !weights || !output || batch <= 0 || in_f <= 0) return fail(MIMIR_B200_E_INVALID, "Linear: bad arguments");
+  if (out_f <= 0) return fail(MIMIR_B200_E_INVALID, "Linear: out_features not set");
+  Temps t;
+  LinearExec e;
+  e.rows = batch; e.in_f = in_f; e.out_f = out_f; e.precision = precision; e.activation = activation;
+  MB_TRY(t.upload(&e.x_f32, input, static_cast<size_t>(batch) * in_f, "linear.x"));
+  MB_TRY(t.upload(&e.w_f32, weights, static_cast<size_t>(out_f) * in_f, "linear.w"));
+  if (bias_or_null) MB_TRY(t.upload(&e.bias, bias_or_null, out_f, "linear.b"));
+  MB_TRY(t.out(&e.y_f32, static_cast<size_t>(batch) * out_f, "linear.y"));
+  e.ws_bytes = linear_ws_bytes(batch, in_f, out_f, precision, false);
+  MB_TRY(t.alloc(&e.ws, e.ws_bytes, "linear.ws"));
+  if (!linear_uses_skinny(batch, precision)) {
+    int ap, wp;
+    precision_planes(precision, &ap, &wp);
+    void* wsplit;
+    MB_TRY(t.alloc(&wsplit, split_bytes(out_f, in_f, wp), "linear.wsplit"));
+    MB_TRY(launch_split(e.w_f32, static_cast<__nv_bfloat16*>(wsplit), out_f, in_f, wp, nullptr));
+    e.w_split = static_cast<const __nv_bfloat16*>(wsplit);
+  }
+  MB_TRY(linear_exec(e, nullptr));
+  return finish_download(output, e.y_f32, static_cast<size_t>(batch) * out_f);
+}
+
+int mimir_b200_linear_forward(const float* input, const float* weights, const float* bias_or_null, float* output, int batch,
+                              int in_f, int out_f) {
+  return mimir_b200_linear_forward_ex(input, weights, bias_or_null, output, batch, in_f, out_f, MIMIR_B200_PREC_BF16X2, -1);
+}
+
+int mimir_b200_matmul(const float* A, const float* B, float* C, int M, int K, int N) {
+  MB_REQUIRE_INIT();
+  if (!A || !B || !C || M <= 0 || K <= 0 || N <= 0) return fail(MIMIR_B200_E_INVALID, "MatMul: dimension mismatch");
+  Temps t;
+  const float *a, *b;
+  float* c;
+  MB_TRY(t.upload(&a, A, static_cast<size_t>(M) * K, "matmul.a"));
+  MB_TRY(t.upload(&b, B, static_cast<size_t>(K) * N, "matmul.b"));
+  MB_TRY(t.out(&c, static_cast<size_t>(M) * N, "matmul.c"));
+  void *as, *bs;
+  MB_TRY(t.alloc(&as, split_bytes(M, K, 2), "matmul.as"));
+  MB_TRY(t.alloc(&bs, split_bytes(N, K, 2), "matmul.bs"));
+  MB_TRY(launch_split(a, static_cast<__nv_bfloat16*>(as), M, K, 2, nullptr));
+  MB_TRY(launch_split_transposed(b, static_cast<__nv_bfloat16*>(bs), K, N, 2, nullptr));
+  GemmArgs g;
+  g.a = static_cast<const __nv_bfloat16*>(as);
+  g.w = static_cast<const __nv_bfloat16*>(bs);
+  g.m = M; g.n = N; g.k = K; g.out_f32 = c; g.ldo = N;
+  MB_TRY(launch_gemm(g, nullptr));
+  return finish_download(C, c, static_cast<size_t>(M) * N);
+}
+
+int mimir_b200_attention(const float* x, const float* wqkv_wout, float* y, int batch, int seq, int embed, int heads,
+                         int causal) {
+  MB_REQUIRE_INIT();
+  if (!x || !wqkv_wout || !y || batch <= 0 || seq <= 0 || embed <= 0 || heads <= 0)
+    return fail(MIMIR_B200_E_INVALID, "Attention: bad arguments");
+  if (embed % heads != 0) return fail(MIMIR_B200_E_INVALID, "SelfAttention: embed_dim must be divisible by num_heads");
+  Temps t;
+  const size_t E = embed, rows = static_cast<size_t>(batch) * seq;
+  AttentionExec e;
+  e.batch = batch; e.seq = seq; e.embed = embed; e.heads = heads; e.causal = causal;
+  const float* w;
+  MB_TRY(t.upload(&e.x, x, rows * E, "attn.x"));
+  MB_TRY(t.upload(&w, wqkv_wout, 4 * E * E, "attn.w"));
+  MB_TRY(t.out(&e.y, rows * E, "attn.y"));
+  void *wq, *wo;
+  MB_TRY(t.alloc(&wq, split_bytes(3 * embed, embed, 2), "attn.wqkv"));
+  MB_TRY(t.alloc(&wo, split_bytes(embed, embed, 2), "attn.wout"));
+  MB_TRY(launch_split_transposed(w, static_cast<__nv_bfloat16*>(wq), embed, 3 * embed, 2, nullptr));
+  MB_TRY(launch_split_transposed(w + 3 * E * E, static_cast<__nv_bfloat16*>(wo), embed, embed, 2, nullptr));
+  e.wqkv_split = static_cast<const __nv_bfloat16*>(wq);
+  e.wout_split = static_cast<const __nv_bfloat16*>(wo);
+  MB_TRY(t.alloc(&e.ws, attention_ws_bytes(static_cast<int>(rows), embed, e.precision), "attn.ws"));
+  MB_TRY(attention_exec(e, nullptr));
+  return finish_download(y, e.y, rows * E);
+}
+
+int mimir_b200_conv2d(const float* x, const float* w, float* y, int batch, int ic, int oc, int h, int wd, int k, int stride,
+                      int pad, int relu) {
+  MB_REQUIRE_INIT();
+  if (!x || !w || !y || batch <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad arguments");
+  if (ic <= 0 || oc <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: in_channels and out_channels must be set");
+  if (k <= 0 || stride <= 0 || pad < 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: kernel_size must be set");
+  const int oh = (h + 2 * pad - k) / stride + 1, ow = (wd + 2 * pad - k) / stride + 1;
+  if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: empty output");
+  Temps t;
+  ConvExec e;
+  e.batch = batch; e.ic = ic; e.oc = oc; e.h = h; e.w = wd; e.ks = k; e.stride = stride; e.pad = pad;
+  e.activation = relu ? MIMIR_B200_ELT_RELU : -1;
+  const float* wdv;
+  MB_TRY(t.upload(&e.x, x, static_cast<size_t>(batch) * ic * h * wd, "conv.x"));
+  MB_TRY(t.upload(&wdv, w, static_cast<size_t>(oc) * ic * k * k, "conv.w"));
+  MB_TRY(t.out(&e.y, static_cast<size_t>(batch) * oc * oh * ow, "conv.y"));
+  void* ws;
+  MB_TRY(t.alloc(&ws, split_bytes(oc, ic * k * k, 2), "conv.wsplit"));
+  MB_TRY(launch_split(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic * k * k, 2, nullptr));
+  e.w_split = static_cast<const __nv_bfloat16*>(ws);
+  MB_TRY(t.alloc(&e.ws, conv_ws_bytes(batch, oh * ow, ic * k * k, e.precision), "conv.ws"));
+  MB_TRY(conv_exec(e, nullptr));
+  return finish_download(y, e.y, static_cast<size_t>(batch) * oc * oh * ow);
+}
+
+int mimir_b200_layernorm(const float* x, const float* gamma, const float* beta, float* y, long long rows, int n, float eps) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || rows <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "LayerNorm: invalid normalized_size");
+  Temps t;
+  const float *dx, *dg = nullptr, *db = nullptr;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, static_cast<size_t>(rows) * n, "ln.x"));
+  if (gamma) MB_TRY(t.upload(&dg, gamma, n, "ln.g"));
+  if (gamma && beta) MB_TRY(t.upload(&db, beta, n, "ln.b"));
+  MB_TRY(t.out(&dy, static_cast<size_t>(rows) * n, "ln.y"));
+  MB_TRY(launch_layernorm(dx, dg, db, dy, rows, n, eps, nullptr));
+  return finish_download(y, dy, static_cast<size_t>(rows) * n);
+}
+
+int mimir_b200_rmsnorm(const float* x, const float* gamma, long long n_gamma, float* y, int batch, long long n, float eps) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "RMSNorm: empty input");
+  Temps t;
+  const float *dx, *dg = nullptr;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, static_cast<size_t>(batch) * n, "rms.x"));
+  if (gamma && n_gamma > 0) MB_TRY(t.upload(&dg, gamma, static_cast<size_t>(n_gamma), "rms.g"));
+  MB_TRY(t.out(&dy, static_cast<size_t>(batch) * n, "rms.y"));
+  MB_TRY(launch_rmsnorm(dx, dg, dg ? n_gamma : 0, dy, batch, n, eps, nullptr));
+  return finish_download(y, dy, static_cast<size_t>(batch) * n);
+}
+
+int mimir_b200_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels, int h,
+                         int w, int groups, float eps, int act) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || batch <= 0 || channels <= 0 || h <= 0 || w <= 0) return fail(MIMIR_B200_E_INVALID, "GroupNorm: bad arguments");
+  Temps t;
+  const size_t n = static_cast<size_t>(batch) * channels * h * w;
+  const float *dx, *dg = nullptr, *db = nullptr;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, n, "gn.x"));
+  if (gamma) MB_TRY(t.upload(&dg, gamma, channels, "gn.g"));
+  if (gamma && beta) MB_TRY(t.upload(&db, beta, channels, "gn.b"));
+  MB_TRY(t.out(&dy, n, "gn.y"));
+  MB_TRY(launch_groupnorm(dx, dg, db, dy, batch, channels, h * w, groups, eps, act, nullptr, nullptr));
+  return finish_download(y, dy, n);
+}
+
+int mimir_b200_softmax(const float* x, float* y, int batch, long long n, int log_softmax) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "Softmax: empty input");
+  Temps t;
+  const float* dx;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, static_cast<size_t>(batch) * n, "sm.x"));
+  MB_TRY(t.out(&dy, static_cast<size_t>(batch) * n, "sm.y"));
+  MB_TRY(launch_softmax(dx, dy, batch, n, log_softmax, nullptr));
+  return finish_download(y, dy, static_cast<size_t>(batch) * n);
+}
+
+int mimir_b200_eltwise(int op, const float* a, const float* b, float* y, int batch, long long n, long long nb) {
+  MB_REQUIRE_INIT();
+  if (!a || !y || batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "eltwise: inputs must be non-empty");
+  Temps t;
+  const float *da, *db = nullptr;
+  float* dy;
+  MB_TRY(t.upload(&da, a, static_cast<size_t>(batch) * n, "elt.a"));
+  if (b && nb > 0) MB_TRY(t.upload(&db, b, static_cast<size_t>(batch) * nb, "elt.b"));
+  MB_TRY(t.out(&dy, static_cast<size_t>(batch) * n, "elt.y"));
+  MB_TRY(launch_eltwise(op, da, db, dy, batch, n, nb, nullptr));
+  return finish_download(y, dy, static_cast<size_t>(batch) * n);
+}
+
+int mimir_b200_embedding(const float* ids_f32, const int32_t* ids_i32, const float* table, float* y, long long n_ids,
+                         int vocab, int dim, int padding_idx) {
+  MB_REQUIRE_INIT();
+  if (!table || !y || n_ids <= 0 || vocab <= 0 || dim <= 0) return fail(MIMIR_B200_E_INVALID, "Embedding: bad arguments");
+  if ((ids_f32 == nullptr) == (ids_i32 == nullptr)) return fail(MIMIR_B200_E_INVALID, "Embedding: give exactly one id array");
+  Temps t;
+  const float *dt, *df = nullptr;
+  const int32_t* di = nullptr;
+  float* dy;
+  MB_TRY(t.upload(&dt, table, static_cast<size_t>(vocab) * dim, "emb.table"));
+  if (ids_f32) {
+    MB_TRY(t.upload(&df, ids_f32, static_cast<size_t>(n_ids), "emb.ids"));
+  } else {
+    void* p;
+    MB_TRY(t.alloc(&p, static_cast<size_t>(n_ids) * 4, "emb.ids"));
+    MB_CUDA(cudaMemcpy(p, ids_i32, static_cast<size_t>(n_ids) * 4, cudaMemcpyHostToDevice));
+    di = static_cast<const int32_t*>(p);
+  }
+  MB_TRY(t.out(&dy, static_cast<size_t>(n_ids) * dim, "emb.y"));
+  MB_TRY(launch_embedding(df, di, dt, dy, n_ids, vocab, dim, padding_idx, nullptr));
+  return finish_download(y, dy, static_cast<size_t>(n_ids) * dim);
+}
+
+int mimir_b200_upsample_nearest(const float* x, float* y, int batch, int channels, int in_h, int in_w, int scale_h,
+                                int scale_w) {
+  MB_REQUIRE_INIT();
+  if (!x || !y) return fail(MIMIR_B200_E_INVALID, "UpsampleNearest: bad arguments");
+  Temps t;
+  const size_t n = static_cast<size_t>(batch) * channels * in_h * in_w;
+  const float* dx;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, n, "up.x"));
+  MB_TRY(t.out(&dy, n * scale_h * scale_w, "up.y"));
+  MB_TRY(launch_upsample_nearest(dx, dy, batch, channels, in_h, in_w, scale_h, scale_w, nullptr));
+  return finish_download(y, dy, n * scale_h * scale_w);
+}
+
+int mimir_b200_permute(const float* x, float* y, int batch, int ndim, const int* shape, const int* dims) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || !shape || !dims || ndim <= 0 || ndim > MIMIR_B200_MAX_DIMS)
+    return fail(MIMIR_B200_E_INVALID, "Permute: dims and shape cannot be empty");
+  size_t per = 1;
+  for (int i = 0; i < ndim; ++i) per *= static_cast<size_t>(shape[i] > 0 ? shape[i] : 0);
+  if (per == 0) return fail(MIMIR_B200_E_INVALID, "Permute: bad shape");
+  Temps t;
+  const float* dx;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, per * batch, "perm.x"));
+  MB_TRY(t.out(&dy, per * batch, "perm.y"));
+  MB_TRY(launch_permute(dx, dy, batch, ndim, shape, dims, nullptr));
+  return finish_download(y, dy, per * batch);
+}
+
+int mimir_b200_token_mean_pool(const float* x, float* y, int batch, int seq, int dim) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || batch <= 0 || seq <= 0 || dim <= 0)
+    return fail(MIMIR_B200_E_INVALID, "TokenMeanPool: seq_len and embed_dim must be set");
+  Temps t;
+  const float* dx;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, static_cast<size_t>(batch) * seq * dim, "tmp.x"));
+  MB_TRY(t.out(&dy, static_cast<size_t>(batch) * dim, "tmp.y"));
+  MB_TRY(launch_token_mean_pool(dx, dy, batch, seq, dim, nullptr));
+  return finish_download(y, dy, static_cast<size_t>(batch) * dim);
+}
+
+int mimir_b200_global_avgpool(const float* x, float* y, int batch, int channels, int h, int w) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || batch <= 0 || channels <= 0 || h <= 0 || w <= 0) return fail(MIMIR_B200_E_INVALID, "GlobalAvgPool: bad arguments");
+  Temps t;
+  const float* dx;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, static_cast<size_t>(batch) * channels * h * w, "gap.x"));
+  MB_TRY(t.out(&dy, static_cast<size_t>(batch) * channels, "gap.y"));
+  MB_TRY(launch_global_avgpool(dx, dy, batch, channels, h * w, nullptr));
+  return finish_download(y, dy, static_cast<size_t>(batch) * channels);
+}
+
+// ---- device-pointer forms -------------------------------------------------------------------
+int mimir_b200_dev_layernorm(const float* x, const float* gamma, const float* beta, float* y, long long rows, int n,
+                             float eps, void* stream) {
+  MB_REQUIRE_INIT();
+  return launch_layernorm(x, gamma, beta, y, rows, n, eps, static_cast<cudaStream_t>(stream));
+}
+int mimir_b200_dev_rmsnorm(const float* x, const float* gamma, long long n_gamma, float* y, int batch, long long n, float eps,
+                           void* stream) {
+  MB_REQUIRE_INIT();
+  return launch_rmsnorm(x, gamma, n_gamma, y, batch, n, eps, static_cast<cudaStream_t>(stream));
+}
+int mimir_b200_dev_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels, int h,
+                             int w, int groups, float eps, int act, void* stream) {
+  MB_REQUIRE_INIT();
+  return launch_groupnorm(x, gamma, beta, y, batch, channels, h * w, groups, eps, act, nullptr, static_cast<cudaStream_t>(stream));
+}
+int mimir_b200_dev_softmax(const float* x, float* y, int batch, long long n, int log_softmax, void* stream) {
+  MB_REQUIRE_INIT();
+  return launch_softmax(x, y, batch, n, log_softmax, static_cast<cudaStream_t>(stream));
+}
+int mimir_b200_dev_eltwise(int op, const float* a, const float* b, float* y, int batch, long long n, long long nb,
+                           void* stream) {
+  MB_REQUIRE_INIT();
+  return launch_eltwise(op, a, b, y, batch, n, nb, static_cast<cudaStream_t>(stream));
+}
+int mimir_b200_argmax_rows_device(const float* x_dev, int32_t* ids_dev, long long rows, int n, void* stream) {
+  MB_REQUIRE_INIT();
+  return launch_argmax_rows(x_dev, ids_dev, rows, n, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,134 @@
+// common.h — shared host-side plumbing of the backend: status codes, error text, the process-wide
+// context (device, budget guard, launch counter) and the launch prototypes of every kernel file.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "mimir_b200.h"
+
+namespace mb {
+
+// ---- error text (thread-local, read through mimir_b200_last_error) -------------------------
+std::string& last_error();
+int fail(int status, const char* fmt, ...);
+
+#define MB_CUDA(expr)                                                                         \
+  do {                                                                                        \
+    cudaError_t _e = (expr);                                                                  \
+    if (_e != cudaSuccess)                                                                    \
+      return ::mb::fail(MIMIR_B200_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                        __FILE__, __LINE__);                                                  \
+  } while (0)
+
+#define MB_TRY(expr)              \
+  do {                            \
+    int _s = (expr);              \
+    if (_s != MIMIR_B200_OK) return _s; \
+  } while (0)
+
+// ---- budget guard: the device-side counterpart of MemoryGuard (MemoryGuard.hpp:16-206) -----
+struct Guard {
+  std::mutex mu;
+  size_t limit = 0, current = 0, peak = 0;
+  bool request(size_t bytes);
+  void release(size_t bytes);
+};
+
+struct Context {
+  bool initialised = false;
+  int device = 0;
+  int sm_count = 148;
+  Guard guard;
+  std::atomic<uint64_t> launches{0};
+  // One device word that kernels with bounded waits set when a wait gives up.
+  int* dev_error_word = nullptr;
+  // Optional live timing of the contraction kernel: pairs of events recorded on the launching
+  // stream around every GEMM launch while enabled (read back by mimir_b200_profile_read).
+  bool prof_gemm = false;
+  std::vector<cudaEvent_t> prof_events;
+};
+Context& ctx();
+
+// Budgeted device allocation: every cudaMalloc of the backend goes through these.
+int dev_alloc(void** p, size_t bytes, const char* tag);
+void dev_free(void* p, size_t bytes);
+
+inline void count_launch(int n = 1) { ctx().launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
+
+// ---- kernel launchers (device pointers, asynchronous on `st`) -------------------------------
+// Activation codes follow MimirB200Eltwise; -1 = none.
+
+// gemm_sm100.cu --------------------------------------------------------------------------------
+// Split planes: bf16 [planes][rows][kp] with kp = round_up(k, 64), zero padded.
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+inline int64_t plane_elems(int64_t rows, int k) { return rows * static_cast<int64_t>(round_up(k, 64)); }
+// fp32 [rows, k] -> planes (hi, and lo when planes == 2)
+int launch_split(const float* src, __nv_bfloat16* dst, int64_t rows, int k, int planes, cudaStream_t st);
+// fp32 [k, n] (row-major, "input-major") -> planes of its transpose [n, kp]
+int launch_split_transposed(const float* src, __nv_bfloat16* dst, int k, int n, int planes, cudaStream_t st);
+
+struct GemmArgs {
+  const __nv_bfloat16* a = nullptr;  // [a_planes][m][kp]
+  const __nv_bfloat16* w = nullptr;  // [w_planes][n][kp]
+  int a_planes = 2, w_planes = 2;
+  int m = 0, n = 0, k = 0;           // logical sizes; kp = round_up(k, 64)
+  const float* bias = nullptr;       // [n] or null
+  const float* residual = nullptr;   // fp32 [m, n] added after the activation, or null
+  int activation = -1;
+  float* out_f32 = nullptr;          // fp32 [m, ldo] or null
+  int64_t ldo = 0;
+  int out_nchw_hw = 0;               // > 0: out_f32/residual are [m / hw][n][hw] (conv output), ldo unused
+  __nv_bfloat16* out_split = nullptr;  // planes [2][m][round_up(n,64)] for the next GEMM, or null
+};
+// y = act(a · wᵀ + bias) (+ residual); tcgen05 / TMEM / TMA.
+int launch_gemm(const GemmArgs& g, cudaStream_t st);
+// fp32 weight-streaming kernel for very small m (<= 16 rows): y[m,n] = x[m,k] · w[n,k]ᵀ + bias.
+int launch_skinny_linear(const float* x, const float* w, const float* bias, float* y, int m, int k, int n,
+                         int activation, float* scratch, size_t scratch_bytes, cudaStream_t st);
+size_t skinny_scratch_bytes(int m, int k, int n);
+
+// pointwise.cu ---------------------------------------------------------------------------------
+int launch_eltwise(int op, const float* a, const float* b, float* y, int batch, int64_t n, int64_t nb,
+                   cudaStream_t st);
+int launch_embedding(const float* ids_f32, const int32_t* ids_i32, const float* table, float* y, int64_t n_ids,
+                     int vocab, int dim, int padding_idx, cudaStream_t st);
+int launch_upsample_nearest(const float* x, float* y, int batch, int ch, int in_h, int in_w, int sh, int sw,
+                            cudaStream_t st);
+int launch_permute(const float* x, float* y, int batch, int nd, const int* shape, const int* dims, cudaStream_t st);
+int launch_token_mean_pool(const float* x, float* y, int batch, int seq, int dim, cudaStream_t st);
+int launch_global_avgpool(const float* x, float* y, int batch, int ch, int hw, cudaStream_t st);
+int launch_argmax_rows(const float* x, int32_t* ids, int64_t rows, int n, cudaStream_t st);
+// copies `n` floats per sample from src (per-sample stride n) into dst at offset `off` of a
+// per-sample vector of `total` floats (Concat)
+int launch_copy_strided(const float* src, float* dst, int batch, int64_t n, int64_t total, int64_t off,
+                        cudaStream_t st);
+int launch_broadcast_rows(const float* src, float* dst, int batch, int64_t n, cudaStream_t st);
+
+// norms.cu -------------------------------------------------------------------------------------
+int launch_layernorm(const float* x, const float* gamma, const float* beta, float* y, int64_t rows, int64_t n,
+                     float eps, cudaStream_t st);
+int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y, int batch, int64_t n, float eps,
+                   cudaStream_t st);
+int launch_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int batch, int ch, int hw,
+                     int groups, float eps, int act, const float* residual, cudaStream_t st);
+int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softmax, cudaStream_t st);
+
+// attention.cu ---------------------------------------------------------------------------------
+// qkv fp32 [batch*seq, 3E] (Q | K | V thirds) -> attended fp32 [batch*seq, E]
+int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
+                          cudaStream_t st);
+
+// conv2d.cu ------------------------------------------------------------------------------------
+// im2col of NCHW fp32 into split planes [planes][batch*oh*ow][kp], k = ic*ks*ks ordered (ic, kh, kw)
+int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, int h, int w, int ks, int stride,
+                        int pad, int oh, int ow, int planes, cudaStream_t st);
+}  // namespace mb

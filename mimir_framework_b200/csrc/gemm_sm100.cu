@@ -1,0 +1,622 @@
+// gemm_sm100.cu — the contraction kernel every dense layer funnels into (Linear, the attention
+// projections, Conv2d lowered to GEMM).  Replaces LayerOps::linear_forward (LayerOps.hpp:24-111)
+// and HardwareOpt::matmul_fma_saturated (HardwareOpt.hpp:95-149).
+//
+//   Y[m, n] = act( sum_k A[m, k] * W[n, k] + bias[n] ) (+ residual[m, n])
+//
+// Both operands are K-major ("TN"), which is the reference's Linear layout (W is [out][in]).
+// fp32 operands are carried as bf16 planes: x = hi + lo with hi = bf16(x), lo = bf16(x - hi).
+// The kernel issues hi*hi + lo*hi + hi*lo (the lo*lo term, ~2^-18 relative, is dropped) with fp32
+// accumulation in tensor memory, which keeps the result within ~2^-16 per product of the fp32
+// CPU path while running on the bf16 tensor pipe.
+//
+// sm_100a structure (one CTA per SM, persistent over output tiles):
+//   warp 0      : TMA producer  — cp.async.bulk.tensor (no multicast) into a ring of smem stages
+//   warp 1      : MMA issuer    — one thread issues tcgen05.mma, operands from smem descriptors,
+//                                 accumulators in TMEM (2 x 256 columns, double buffered)
+//   warps 2..5  : epilogue      — tcgen05.ld TMEM -> registers, bias / activation / residual,
+//                                 stores fp32 rows and/or the bf16 hi/lo planes of the next layer
+// Every mbarrier wait is bounded: after ~2 s it sets the device error word and the CTA drains.
+#include "common.h"
+
+#include <cuda.h>
+
+namespace mb {
+
+namespace {
+
+constexpr int BM = 128;        // rows of the output tile (TMEM lanes)
+constexpr int BN = 256;        // columns of the output tile (one MMA, N = 256)
+constexpr int UMMA_K = 16;     // bf16 K per tcgen05.mma
+constexpr int NUM_ACC = 2;     // TMEM accumulator buffers
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 192;  // 6 warps
+constexpr int EPI_WARPS = 4;
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait.  Returns false when it gave up (error word set, abort flag raised).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err_word,
+                                          int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0x3FF) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > 2000000000ull) {
+        *abort_flag = 1;
+        atomicExch(err_word, where);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; kind::f16 covers bf16 inputs with fp32 accumulate.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on `bar` once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// 32 lanes x 32 columns of fp32: thread t gets row (lane base + t), columns col .. col+31.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor, K-major operand, rows of `swizzle_bytes` (64 or 128) bytes,
+// 8-row swizzle atoms stacked every 8 * swizzle_bytes.  Field layout: start address >> 4 in
+// bits [0,14), leading byte offset >> 4 in [16,30) (unused for swizzled K-major), stride byte
+// offset >> 4 in [32,46), descriptor version 1 in [46,48), swizzle mode in [61,64)
+// (2 = 128-byte, 4 = 64-byte).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int swizzle_bytes) {
+  const uint64_t sbo = static_cast<uint64_t>(8 * swizzle_bytes) >> 4;
+  const uint64_t layout = (swizzle_bytes == 128) ? 2ull : 4ull;
+  return static_cast<uint64_t>((saddr & 0x3FFFF) >> 4) | (sbo << 32) | (1ull << 46) | (layout << 61);
+}
+
+// Instruction descriptor for kind::f16: D fp32 (bits [4,6) = 1), A and B bf16 (bits [7,10) and
+// [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// GELU in the reference's tanh form (LayerOps.hpp:556-568); the constant is
+// sqrt(2.0f / 3.14159265359f) evaluated in fp32.
+__device__ __forceinline__ float gelu_ref(float x) {
+  const float c = 0.7978845608f;
+  return x * (0.5f * (1.0f + tanhf(c * (x + 0.044715f * x * x * x))));
+}
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case MIMIR_B200_ELT_GELU: return gelu_ref(v);
+    case MIMIR_B200_ELT_SILU: return v * (1.0f / (1.0f + expf(-v)));
+    case MIMIR_B200_ELT_RELU: return fmaxf(v, 0.0f);
+    case MIMIR_B200_ELT_TANH: return tanhf(v);
+    case MIMIR_B200_ELT_SIGMOID: return 1.0f / (1.0f + expf(-v));
+    default: return v;
+  }
+}
+
+struct GemmParams {
+  int m, n, kblocks;         // kblocks = kp / BK
+  int a_planes, w_planes;
+  int tiles_m, tiles_n, group_n;
+  const float* bias;
+  const float* residual;
+  int activation;
+  float* out_f32;
+  long long ldo;
+  __nv_bfloat16* out_split;  // [2][m][np]
+  long long np;              // round_up(n, 64)
+  int ohw;                   // > 0: fp32 output (and residual) are NCHW, row = sample * ohw + pixel
+  int* err_word;
+};
+
+// Tile order: groups of `group_n` column tiles; inside a group the row tile runs fastest, so the
+// CTAs resident at one time share a few W column tiles (kept in L2) while A streams through.
+__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& tm, int& tn) {
+  const int per_group = p.group_n * p.tiles_m;
+  const int g = t / per_group;
+  const int r = t - g * per_group;
+  const int gn0 = g * p.group_n;
+  const int gw = min(p.group_n, p.tiles_n - gn0);
+  tn = gn0 + r % gw;
+  tm = r / gw;
+}
+
+template <int BK>
+struct SmemLayout {
+  static constexpr int kATile = BM * BK * 2;
+  static constexpr int kWTile = BN * BK * 2;
+};
+
+template <int BK, int STAGES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         const GemmParams p) {
+  constexpr int SWZ = BK * 2;                      // bytes per smem row = swizzle span
+  constexpr int A_TILE = BM * BK * 2;
+  constexpr int W_TILE = BN * BK * 2;
+  constexpr int STAGE_BYTES = 2 * A_TILE + 2 * W_TILE;  // room for both planes of both operands
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + NUM_ACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < NUM_ACC; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], EPI_WARPS);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const uint32_t tx_bytes = static_cast<uint32_t>(p.a_planes * A_TILE + p.w_planes * W_TILE);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p, tm, tn);
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err_word, 1)) { ok = false; break; }
+          uint8_t* sbase = smem + stage * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], tx_bytes);
+          for (int pl = 0; pl < p.a_planes; ++pl)
+            tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], kb * BK, tm * BM, pl);
+          for (int pl = 0; pl < p.w_planes; ++pl)
+            tma_load_3d(sbase + 2 * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * BN, pl);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      // Drain: every stage this thread filled must have landed and been consumed (or the abort
+      // flag is up) before the CTA may exit with copies in flight.
+      for (int s = 0; s < STAGES; ++s) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err_word, 2)) break;
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.err_word, 3)) break;
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err_word, 4)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sw = sa + 2 * A_TILE;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t koff = k * UMMA_K * 2;  // bytes along K inside the swizzled row
+            const uint64_t a_hi = make_smem_desc(sa + koff, SWZ);
+            const uint64_t w_hi = make_smem_desc(sw + koff, SWZ);
+            umma_bf16(d_tmem, a_hi, w_hi, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (p.a_planes == 2) {
+              const uint64_t a_lo = make_smem_desc(sa + A_TILE + koff, SWZ);
+              umma_bf16(d_tmem, a_lo, w_hi, idesc, 1u);
+            }
+            if (p.w_planes == 2) {
+              const uint64_t w_lo = make_smem_desc(sw + W_TILE + koff, SWZ);
+              umma_bf16(d_tmem, a_hi, w_lo, idesc, 1u);
+            }
+          }
+          umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&acc_full[acc]);
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ---------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, p, tm, tn);
+      // lane 0 does the bounded wait; the verdict is made warp-uniform because tcgen05.ld below
+      // is a warp-collective instruction
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.err_word, 5) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      while (!mbar_try_wait(&acc_full[acc], acc_phase)) {}  // completes at once: lane 0 saw the phase
+      tcgen05_fence_after();
+      const int row = tm * BM + quad * 32 + lane;
+      const bool row_ok = row < p.m;
+      const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      const int col_limit = (p.out_split != nullptr) ? static_cast<int>(p.np) : p.n;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int col0 = tn * BN + c0;
+        if (col0 >= col_limit) break;  // warp-uniform
+        float v[32];
+        tmem_ld_32x32(taddr0 + c0, v);
+        const bool full_cols = (col0 + 32 <= p.n);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float b = 0.0f;
+          if (p.bias != nullptr && (full_cols || col0 + j < p.n)) b = __ldg(p.bias + col0 + j);
+          v[j] = apply_act(v[j] + b, p.activation);
+        }
+        if (row_ok && p.ohw > 0) {
+          // channel-major output: lane <-> pixel, so each column is a coalesced 128-byte store
+          const long long smp = row / p.ohw;
+          const long long o0 = (smp * p.n + col0) * p.ohw + (row - smp * p.ohw);
+#pragma unroll 4
+          for (int j = 0; j < 32; ++j) {
+            if (full_cols || col0 + j < p.n) {
+              const long long oi = o0 + static_cast<long long>(j) * p.ohw;
+              float r = v[j];
+              if (p.residual != nullptr) r += __ldg(p.residual + oi);
+              p.out_f32[oi] = r;
+            }
+          }
+        } else if (row_ok) {
+          if (p.residual != nullptr) {
+            const float* rr = p.residual + static_cast<long long>(row) * p.ldo + col0;
+            if (full_cols && ((reinterpret_cast<uintptr_t>(rr) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float4 r4 = *reinterpret_cast<const float4*>(rr + j);
+                v[j] += r4.x; v[j + 1] += r4.y; v[j + 2] += r4.z; v[j + 3] += r4.w;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) v[j] += rr[j];
+            }
+          }
+          if (p.out_f32 != nullptr) {
+            float* o = p.out_f32 + static_cast<long long>(row) * p.ldo + col0;
+            if (full_cols && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.n) o[j] = v[j];
+            }
+          }
+          if (p.out_split != nullptr) {
+            // hi/lo planes for the next GEMM; columns n..np-1 are written as zero so that the
+            // padded K of the consumer stays zero
+            __nv_bfloat16* oh = p.out_split + static_cast<long long>(row) * p.np + col0;
+            __nv_bfloat16* ol = oh + static_cast<long long>(p.m) * p.np;
+            if (col0 + 32 <= p.np) {
+              __align__(16) __nv_bfloat16 h[32];
+              __align__(16) __nv_bfloat16 l[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float x = (full_cols || col0 + j < p.n) ? v[j] : 0.0f;
+                h[j] = __float2bfloat16_rn(x);
+                l[j] = __float2bfloat16_rn(x - __bfloat162float(h[j]));
+              }
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                *reinterpret_cast<uint4*>(oh + j) = *reinterpret_cast<const uint4*>(h + j);
+                *reinterpret_cast<uint4*>(ol + j) = *reinterpret_cast<const uint4*>(l + j);
+              }
+            }
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------
+// fp32 -> bf16 hi/lo planes
+// ------------------------------------------------------------------------------------------
+namespace {
+
+__device__ __forceinline__ void split1(float x, __nv_bfloat16& h, __nv_bfloat16& l) {
+  h = __float2bfloat16_rn(x);
+  l = __float2bfloat16_rn(x - __bfloat162float(h));
+}
+
+// One thread per 8 consecutive K elements of one row; the padded tail kp > k is written as zero.
+__global__ void split_rows_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows, int k,
+                                  int kp, int planes) {
+  const int chunks = kp >> 3;
+  const long long total = rows * chunks;
+  const long long plane_stride = rows * static_cast<long long>(kp);
+  const bool vec_ok = ((k & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / chunks;
+    const int c = static_cast<int>(i - r * chunks) << 3;
+    float v[8];
+    const float* s = src + r * k + c;
+    if (vec_ok && c + 8 <= k) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(s));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(s + 4));
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (c + j < k) ? __ldg(s + j) : 0.0f;
+    }
+    __align__(16) __nv_bfloat16 h[8];
+    __align__(16) __nv_bfloat16 l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) split1(v[j], h[j], l[j]);
+    __nv_bfloat16* d = dst + r * kp + c;
+    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(h);
+    if (planes == 2) *reinterpret_cast<uint4*>(d + plane_stride) = *reinterpret_cast<const uint4*>(l);
+  }
+}
+
+// src fp32 [k, n] row-major -> planes of the transpose [n, kp].  32x32 tiles through shared memory.
+__global__ void split_transposed_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int k, int n,
+                                        int kp, int planes) {
+  __shared__ float tile[32][33];
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int kk = k0 + i, nn = n0 + threadIdx.x;
+    tile[i][threadIdx.x] = (kk < k && nn < n) ? __ldg(src + static_cast<long long>(kk) * n + nn) : 0.0f;
+  }
+  __syncthreads();
+  const long long plane_stride = static_cast<long long>(n) * kp;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int nn = n0 + i, kk = k0 + threadIdx.x;
+    if (nn < n && kk < kp) {
+      __nv_bfloat16 h, l;
+      split1(tile[threadIdx.x][i], h, l);
+      dst[static_cast<long long>(nn) * kp + kk] = h;
+      if (planes == 2) dst[plane_stride + static_cast<long long>(nn) * kp + kk] = l;
+    }
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 3-D map over bf16 planes [planes][rows][kp]; box = {bk, box_rows, 1}; swizzle span = bk * 2 bytes.
+int make_plane_map(CUtensorMap* map, const void* base, int planes, long long rows, int kp, int bk, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(MIMIR_B200_E_INVALID, "GEMM operand not 16-byte aligned");
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(kp), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(planes)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(kp) * 2, static_cast<cuuint64_t>(rows) * kp * 2};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapSwizzle sw = (bk == 64) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return MIMIR_B200_OK;
+}
+
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+template <int BK, int STAGES>
+int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
+  const int kp = round_up(g.k, 64);
+  CUtensorMap map_a, map_w;
+  MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, kp, BK, BM));
+  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, BN));
+  GemmParams p;
+  p.m = g.m;
+  p.n = g.n;
+  p.kblocks = kp / BK;
+  p.a_planes = g.a_planes;
+  p.w_planes = g.w_planes;
+  p.tiles_m = (g.m + BM - 1) / BM;
+  p.tiles_n = (g.n + BN - 1) / BN;
+  p.group_n = env_int("MIMIR_B200_GEMM_GROUP_N", 8);
+  if (p.group_n < 1) p.group_n = 1;
+  if (p.group_n > p.tiles_n) p.group_n = p.tiles_n;
+  p.bias = g.bias;
+  p.residual = g.residual;
+  p.activation = g.activation;
+  p.out_f32 = g.out_f32;
+  p.ldo = g.ldo;
+  p.out_split = g.out_split;
+  p.np = round_up(g.n, 64);
+  p.ohw = g.out_nchw_hw;
+  p.err_word = ctx().dev_error_word;
+  constexpr int STAGE_BYTES = 2 * BM * BK * 2 + 2 * BN * BK * 2;
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  auto kern = gemm_tn_bf16split_kernel<BK, STAGES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    MB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    attr_set = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (ctx().prof_gemm) {
+    MB_CUDA(cudaEventCreate(&e0));
+    MB_CUDA(cudaEventCreate(&e1));
+    MB_CUDA(cudaEventRecord(e0, st));
+  }
+  kern<<<grid, NUM_THREADS, SMEM, st>>>(map_a, map_w, p);
+  MB_CUDA(cudaGetLastError());
+  if (e0) {
+    MB_CUDA(cudaEventRecord(e1, st));
+    ctx().prof_events.push_back(e0);
+    ctx().prof_events.push_back(e1);
+  }
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+}  // namespace
+
+int launch_split(const float* src, __nv_bfloat16* dst, int64_t rows, int k, int planes, cudaStream_t st) {
+  if (rows <= 0 || k <= 0) return MIMIR_B200_OK;
+  const int kp = round_up(k, 64);
+  const long long total = rows * (kp >> 3);
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  const long long cap = static_cast<long long>(ctx().sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  split_rows_kernel<<<static_cast<int>(blocks), threads, 0, st>>>(src, dst, rows, k, kp, planes);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+int launch_split_transposed(const float* src, __nv_bfloat16* dst, int k, int n, int planes, cudaStream_t st) {
+  if (n <= 0 || k <= 0) return MIMIR_B200_OK;
+  const int kp = round_up(k, 64);
+  dim3 grid((n + 31) / 32, kp / 32), block(32, 8);
+  split_transposed_kernel<<<grid, block, 0, st>>>(src, dst, k, n, kp, planes);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+int launch_gemm(const GemmArgs& g, cudaStream_t st) {
+  if (g.m <= 0 || g.n <= 0 || g.k <= 0) return fail(MIMIR_B200_E_INVALID, "gemm: empty dimension");
+  if (!g.a || !g.w) return fail(MIMIR_B200_E_INVALID, "gemm: null operand");
+  if (!g.out_f32 && !g.out_split) return fail(MIMIR_B200_E_INVALID, "gemm: no output");
+  if (g.residual && !g.out_f32) return fail(MIMIR_B200_E_INVALID, "gemm: residual needs the fp32 output stride");
+  // BK = 32 keeps four 48 KB stages in flight, BK = 64 two 96 KB stages.
+  const int bk = env_int("MIMIR_B200_GEMM_BK", 32);
+  if (bk == 64) return launch_gemm_t<64, 2>(g, st);
+  return launch_gemm_t<32, 4>(g, st);
+}
+
+}  // namespace mb

@@ -1,0 +1,942 @@
+// graph.cu — whole-graph execution: the device-side counterpart of Model::forwardPassView
+// (Model.cpp:4621-6824) and of the activation-memory subsystems (RuntimeAllocator.hpp:181-316,
+// MemoryGuard.hpp:16-206).
+//
+//   model_create   copies the layer descriptors (the translated `std::vector<Layer>`).
+//   upload_weights copies one layer's flat fp32 block to the device (the host pointer is never
+//                  kept: it may move, DynamicTensorAllocator.hpp:171-200).
+//   plan           resolves the name routing into tensor versions (a name may be redefined, e.g.
+//                  "x"), infers every per-sample size, fuses what the graph allows (activation into
+//                  the producing GEMM / GroupNorm, hi/lo planes straight from one GEMM to the next),
+//                  computes liveness and assigns arena offsets that are reused after the last
+//                  consumer, and checks the arena peak against the HBM budget before any launch.
+//   forward        stages the inputs, runs the layers in index order on one stream, returns "x".
+#include "ops.h"
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <set>
+#include <string>
+#include <vector>
+
+namespace mb {
+namespace {
+
+enum class LT {
+  Linear, Attention, Conv2d, LayerNorm, RMSNorm, GroupNorm, Softmax, LogSoftmax, Act, Add, Multiply, Embedding,
+  UpsampleNearest, Permute, Concat, Alias, TokenMeanPool, GlobalAvgPool, Unsupported
+};
+
+struct TypeInfo { LT lt; int act; };
+
+TypeInfo classify(const std::string& t) {
+  if (t == "Linear") return {LT::Linear, -1};
+  if (t == "SelfAttention" || t == "MultiHeadAttention") return {LT::Attention, -1};
+  if (t == "Conv2d") return {LT::Conv2d, -1};
+  if (t == "LayerNorm") return {LT::LayerNorm, -1};
+  if (t == "RMSNorm") return {LT::RMSNorm, -1};
+  if (t == "GroupNorm") return {LT::GroupNorm, -1};
+  if (t == "Softmax") return {LT::Softmax, -1};
+  if (t == "LogSoftmax") return {LT::LogSoftmax, -1};
+  if (t == "GELU") return {LT::Act, MIMIR_B200_ELT_GELU};
+  if (t == "SiLU") return {LT::Act, MIMIR_B200_ELT_SILU};
+  if (t == "ReLU") return {LT::Act, MIMIR_B200_ELT_RELU};
+  if (t == "Tanh") return {LT::Act, MIMIR_B200_ELT_TANH};
+  if (t == "Sigmoid") return {LT::Act, MIMIR_B200_ELT_SIGMOID};
+  if (t == "Add") return {LT::Add, -1};
+  if (t == "Multiply") return {LT::Multiply, -1};
+  if (t == "Embedding") return {LT::Embedding, -1};
+  if (t == "UpsampleNearest") return {LT::UpsampleNearest, -1};
+  if (t == "Permute") return {LT::Permute, -1};
+  if (t == "Concat") return {LT::Concat, -1};
+  // pass-through layers at inference (LayerOps.hpp:117-136, 629-662)
+  if (t == "Identity" || t == "Reshape" || t == "Flatten" || t == "View" || t == "Dropout" || t == "Dropout2d" ||
+      t == "AlphaDropout")
+    return {LT::Alias, -1};
+  if (t == "TokenMeanPool") return {LT::TokenMeanPool, -1};
+  if (t == "GlobalAvgPool2d" || t == "AdaptiveAvgPool2d") return {LT::GlobalAvgPool, -1};
+  return {LT::Unsupported, -1};
+}
+
+struct LayerRT {
+  // descriptor (strings owned here)
+  std::string name, type, output;
+  std::vector<std::string> inputs;
+  MimirLayerDesc d{};
+  LT lt = LT::Unsupported;
+  int act_of_type = -1;
+  // weights
+  float* w_f32 = nullptr;
+  size_t w_count = 0;
+  __nv_bfloat16* w_split = nullptr;   // Linear / Conv2d operand, or Wqkv^T for attention
+  size_t w_split_bytes = 0;
+  __nv_bfloat16* w_split2 = nullptr;  // Wout^T for attention
+  size_t w_split2_bytes = 0;
+  int w_split_k = -1;                 // K the planes were built for (Linear in_features may be implicit)
+  // plan
+  std::vector<int> in_v;              // tensor versions read
+  int out_v = -1;
+  bool skip = false;                  // activation folded into its producer
+  int fused_act = -1;                 // activation folded into this layer
+  bool emit_split = false;            // GEMM writes hi/lo planes for the consuming Linear
+  bool emit_f32 = true;
+  bool read_split = false;            // Linear reads the producer's planes
+  size_t ws_off = 0, ws_bytes = 0;
+  // resolved shapes (per sample)
+  int rows_ps = 1, in_f = 0, out_f = 0;       // Linear
+  int seq = 0, embed = 0, heads = 1;          // Attention
+  int h = 0, w = 0, oh = 0, ow = 0;           // Conv2d / GroupNorm / Upsample
+  int ch = 0;
+  int64_t norm_n = 0;                         // LayerNorm group size
+};
+
+struct TensorV {
+  std::string name;
+  int64_t n = 0;          // per-sample elements
+  int producer = -1;      // layer index, -1 = graph input
+  std::vector<int> consumers;
+  int alias_of = -1;
+  bool broadcast_input = false;
+  bool want_f32 = true, want_split = false;
+  int64_t split_rows_ps = 0;
+  int split_k = 0;
+  size_t off_f32 = 0, off_split = 0;
+  int first = 0, last = 0;
+};
+
+struct Block { size_t off, size; };
+
+// First-fit free list over one linear arena; freed ranges are merged with their neighbours.
+struct ArenaSim {
+  std::vector<Block> free_list;
+  size_t end = 0, peak = 0;
+  size_t alloc(size_t bytes) {
+    bytes = (bytes + 255) & ~size_t(255);
+    if (bytes == 0) bytes = 256;
+    for (size_t i = 0; i < free_list.size(); ++i) {
+      if (free_list[i].size >= bytes) {
+        const size_t off = free_list[i].off;
+        free_list[i].off += bytes;
+        free_list[i].size -= bytes;
+        if (free_list[i].size == 0) free_list.erase(free_list.begin() + i);
+        return off;
+      }
+    }
+    // extend; if the last free block touches the end, grow from it
+    if (!free_list.empty() && free_list.back().off + free_list.back().size == end) {
+      const size_t off = free_list.back().off;
+      end = off + bytes;
+      free_list.pop_back();
+      peak = std::max(peak, end);
+      return off;
+    }
+    const size_t off = end;
+    end += bytes;
+    peak = std::max(peak, end);
+    return off;
+  }
+  void release(size_t off, size_t bytes) {
+    bytes = (bytes + 255) & ~size_t(255);
+    if (bytes == 0) bytes = 256;
+    Block b{off, bytes};
+    auto it = std::lower_bound(free_list.begin(), free_list.end(), b, [](const Block& a, const Block& c) { return a.off < c.off; });
+    it = free_list.insert(it, b);
+    if (it + 1 != free_list.end() && it->off + it->size == (it + 1)->off) {
+      it->size += (it + 1)->size;
+      free_list.erase(it + 1);
+    }
+    if (it != free_list.begin() && (it - 1)->off + (it - 1)->size == it->off) {
+      (it - 1)->size += it->size;
+      free_list.erase(it);
+    }
+  }
+};
+
+}  // namespace
+}  // namespace mb
+
+struct MimirB200Model {
+  std::vector<mb::LayerRT> layers;
+  std::vector<mb::TensorV> tensors;
+  std::map<std::string, int> input_v;  // graph input name -> tensor version
+  int precision = MIMIR_B200_PREC_BF16X2;
+  int planned_batch = 0;
+  int out_v = -1;
+  uint8_t* arena = nullptr;
+  size_t arena_bytes = 0;
+  size_t weight_bytes = 0;
+  uint64_t flops = 0, hbm_bytes = 0;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float last_ms = 0.f;
+};
+
+namespace mb {
+namespace {
+
+std::mutex g_models_mu;
+std::set<MimirB200Model*> g_models;
+MimirB200Stats g_stats{};
+
+int root_of(const std::vector<TensorV>& ts, int v) {
+  while (ts[v].alias_of >= 0) v = ts[v].alias_of;
+  return v;
+}
+
+void free_layer_weights(LayerRT& L, MimirB200Model* m) {
+  if (L.w_f32) { dev_free(L.w_f32, L.w_count * 4); m->weight_bytes -= L.w_count * 4; L.w_f32 = nullptr; }
+  if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
+  if (L.w_split2) { dev_free(L.w_split2, L.w_split2_bytes); m->weight_bytes -= L.w_split2_bytes; L.w_split2 = nullptr; }
+  L.w_split_k = -1;
+}
+
+// Builds the tensor-core operand planes of a layer's weights once its K is known.
+int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
+  int ap, wp;
+  precision_planes(m->precision, &ap, &wp);
+  if (L.lt == LT::Linear) {
+    if (linear_uses_skinny(L.rows_ps * m->planned_batch, m->precision)) return MIMIR_B200_OK;
+    if (L.w_split && L.w_split_k == L.in_f) return MIMIR_B200_OK;
+    if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
+    L.w_split_bytes = split_bytes(L.out_f, L.in_f, wp);
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split), L.w_split_bytes, "linear.w_planes"));
+    m->weight_bytes += L.w_split_bytes;
+    MB_TRY(launch_split(L.w_f32, L.w_split, L.out_f, L.in_f, wp, st));
+    L.w_split_k = L.in_f;
+  } else if (L.lt == LT::Conv2d) {
+    const int k = L.d.in_channels * L.d.kernel * L.d.kernel;
+    if (L.w_split && L.w_split_k == k) return MIMIR_B200_OK;
+    L.w_split_bytes = split_bytes(L.d.out_channels, k, wp);
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split), L.w_split_bytes, "conv.w_planes"));
+    m->weight_bytes += L.w_split_bytes;
+    MB_TRY(launch_split(L.w_f32, L.w_split, L.d.out_channels, k, wp, st));
+    L.w_split_k = k;
+  } else if (L.lt == LT::Attention) {
+    const int E = L.embed;
+    if (L.w_split && L.w_split_k == E) return MIMIR_B200_OK;
+    if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
+    if (L.w_split2) { dev_free(L.w_split2, L.w_split2_bytes); m->weight_bytes -= L.w_split2_bytes; L.w_split2 = nullptr; }
+    L.w_split_bytes = split_bytes(3 * E, E, wp);
+    L.w_split2_bytes = split_bytes(E, E, wp);
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split), L.w_split_bytes, "attn.wqkv_planes"));
+    m->weight_bytes += L.w_split_bytes;
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split2), L.w_split2_bytes, "attn.wout_planes"));
+    m->weight_bytes += L.w_split2_bytes;
+    MB_TRY(launch_split_transposed(L.w_f32, L.w_split, E, 3 * E, wp, st));
+    MB_TRY(launch_split_transposed(L.w_f32 + static_cast<size_t>(3) * E * E, L.w_split2, E, E, wp, st));
+    L.w_split_k = E;
+  }
+  return MIMIR_B200_OK;
+}
+
+// Per-sample output size of layer L given its input sizes; fills the resolved shape fields.
+// Error texts follow the reference's RUNTIME_CHECK / throw messages where it has one.
+int infer_layer(LayerRT& L, const std::vector<int64_t>& in_n, int64_t* out_n) {
+  const MimirLayerDesc& d = L.d;
+  const int64_t n0 = in_n.empty() ? 0 : in_n[0];
+  switch (L.lt) {
+    case LT::Linear: {
+      if (d.out_features <= 0) return fail(MIMIR_B200_E_INVALID, "Linear: out_features not set");
+      const int64_t in_f = d.in_features > 0 ? d.in_features : n0;
+      L.in_f = static_cast<int>(in_f);
+      L.out_f = d.out_features;
+      if (d.seq_len > 0 && n0 == static_cast<int64_t>(d.seq_len) * in_f) L.rows_ps = d.seq_len;
+      else if (n0 == in_f) L.rows_ps = 1;
+      else return fail(MIMIR_B200_E_INVALID, "Linear (%s): input size %lld does not match in_features %lld", L.name.c_str(),
+                       static_cast<long long>(n0), static_cast<long long>(in_f));
+      const size_t need = static_cast<size_t>(in_f) * L.out_f + (d.use_bias ? L.out_f : 0);
+      if (L.w_count < need) return fail(MIMIR_B200_E_INVALID, "Linear (%s): weights not uploaded or too small", L.name.c_str());
+      *out_n = static_cast<int64_t>(L.rows_ps) * L.out_f;
+      return MIMIR_B200_OK;
+    }
+    case LT::Attention: {
+      L.seq = d.seq_len > 0 ? d.seq_len : 1;
+      L.embed = d.embed_dim > 0 ? d.embed_dim : static_cast<int>(n0);
+      L.heads = d.num_heads > 0 ? d.num_heads : 1;
+      if (L.embed % L.heads != 0) return fail(MIMIR_B200_E_INVALID, "SelfAttention: embed_dim must be divisible by num_heads");
+      if (n0 != static_cast<int64_t>(L.seq) * L.embed) return fail(MIMIR_B200_E_INVALID, "SelfAttention: input size mismatch");
+      if (L.w_count < static_cast<size_t>(4) * L.embed * L.embed)
+        return fail(MIMIR_B200_E_INVALID, "Attention: weights not initialized. Call allocateParams() first.");
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::Conv2d: {
+      if (d.in_channels <= 0 || d.out_channels <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: in_channels and out_channels must be set");
+      if (d.kernel <= 0 || d.stride <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: kernel_size must be set");
+      int h = d.input_height > 0 ? d.input_height : 64, w = d.input_width > 0 ? d.input_width : 64;
+      // size re-inference of Model.cpp:4916-4944
+      if (n0 % d.in_channels == 0) {
+        const int64_t hw = n0 / d.in_channels;
+        if (static_cast<int64_t>(h) * w != hw) {
+          if (d.input_height > 0 && hw % d.input_height == 0) { h = d.input_height; w = static_cast<int>(hw / h); }
+          else if (d.input_width > 0 && hw % d.input_width == 0) { w = d.input_width; h = static_cast<int>(hw / w); }
+          else {
+            const int64_t s = llround(sqrt(static_cast<double>(hw)));
+            if (s > 0 && s * s == hw) { h = static_cast<int>(s); w = static_cast<int>(s); }
+          }
+        }
+      }
+      if (static_cast<int64_t>(d.in_channels) * h * w != n0) return fail(MIMIR_B200_E_INVALID, "Conv2d (%s): input size mismatch", L.name.c_str());
+      L.h = h; L.w = w; L.ch = d.in_channels;
+      L.oh = (h + 2 * d.padding - d.kernel) / d.stride + 1;
+      L.ow = (w + 2 * d.padding - d.kernel) / d.stride + 1;
+      if (L.oh <= 0 || L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d (%s): empty output", L.name.c_str());
+      if (L.w_count < static_cast<size_t>(d.out_channels) * d.in_channels * d.kernel * d.kernel)
+        return fail(MIMIR_B200_E_INVALID, "Conv2d: weights invalid");
+      *out_n = static_cast<int64_t>(d.out_channels) * L.oh * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::LayerNorm: {
+      L.norm_n = d.in_features > 0 ? d.in_features : n0;
+      if (L.norm_n <= 0 || n0 % L.norm_n != 0) return fail(MIMIR_B200_E_INVALID, "LayerNorm: invalid normalized_size");
+      if (d.affine && L.w_count < static_cast<size_t>(L.norm_n) * (d.use_bias ? 2 : 1))
+        return fail(MIMIR_B200_E_INVALID, "LayerNorm (%s): weights not uploaded or too small", L.name.c_str());
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::RMSNorm:
+    case LT::Softmax:
+    case LT::LogSoftmax:
+    case LT::Act:
+    case LT::Alias:
+      if (n0 <= 0) return fail(MIMIR_B200_E_INVALID, "%s: empty input", L.type.c_str());
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    case LT::GroupNorm: {
+      L.ch = d.in_channels > 0 ? d.in_channels : 64;
+      L.h = d.input_height > 0 ? d.input_height : 32;
+      L.w = d.input_width > 0 ? d.input_width : 32;
+      if (d.num_groups <= 0 || L.ch % d.num_groups != 0) return fail(MIMIR_B200_E_INVALID, "GroupNorm: channels must be divisible by num_groups");
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "GroupNorm (%s): input size mismatch", L.name.c_str());
+      if (d.affine && L.w_count < static_cast<size_t>(L.ch) * (d.use_bias ? 2 : 1))
+        return fail(MIMIR_B200_E_INVALID, "GroupNorm (%s): weights not uploaded or too small", L.name.c_str());
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::Add:
+    case LT::Multiply: {
+      if (in_n.size() < 2) return fail(MIMIR_B200_E_INVALID, "%s layer requires 2 inputs, got %zu", L.type.c_str(), in_n.size());
+      const int64_t a = in_n[0], b = in_n[1];
+      if (a <= 0 || b <= 0) return fail(MIMIR_B200_E_INVALID, "Add: inputs must be non-empty");
+      if (L.lt == LT::Multiply && a != b) return fail(MIMIR_B200_E_INVALID, "Multiply: input sizes must match");
+      const int64_t big = std::max(a, b), small = std::min(a, b);
+      if (big != small && small != 1 && big % small != 0)
+        return fail(MIMIR_B200_E_INVALID, "Add: input sizes must match or be broadcastable");
+      *out_n = big;
+      return MIMIR_B200_OK;
+    }
+    case LT::Embedding: {
+      if (L.w_count < static_cast<size_t>(std::max(1, d.vocab_size)) * std::max(1, d.embed_dim))
+        return fail(MIMIR_B200_E_INVALID, "Embedding: invalid weight size");
+      *out_n = n0 * std::max(1, d.embed_dim);
+      return MIMIR_B200_OK;
+    }
+    case LT::UpsampleNearest: {
+      if (d.out_h <= 0 || d.out_w <= 0 || d.in_channels <= 0)
+        return fail(MIMIR_B200_E_INVALID, "UpsampleNearest: dimensions (out_h, out_w, in_channels) must be set");
+      L.h = d.out_h; L.w = d.out_w; L.ch = d.in_channels;  // out_h/out_w are the INPUT size (Model.cpp:6008-6009)
+      const int sh = d.scale_h > 0 ? d.scale_h : 2, sw = d.scale_w > 0 ? d.scale_w : 2;
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "UpsampleNearest (%s): input size mismatch", L.name.c_str());
+      L.oh = L.h * sh; L.ow = L.w * sw;
+      *out_n = static_cast<int64_t>(L.ch) * L.oh * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::Permute: {
+      if (d.n_dims <= 0) return fail(MIMIR_B200_E_INVALID, "Permute: permute_dims must be configured");
+      int64_t tot = 1;
+      for (int i = 0; i < d.n_dims; ++i) tot *= d.shape[i];
+      if (tot != n0) return fail(MIMIR_B200_E_INVALID, "Permute (%s): shape does not match the input size", L.name.c_str());
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::Concat: {
+      if (in_n.size() < 2) return fail(MIMIR_B200_E_INVALID, "Concat requires at least 2 inputs, got %zu", in_n.size());
+      int64_t s = 0;
+      for (int64_t v : in_n) s += v;
+      *out_n = s;
+      return MIMIR_B200_OK;
+    }
+    case LT::TokenMeanPool:
+      if (d.seq_len <= 0 || d.embed_dim <= 0) return fail(MIMIR_B200_E_INVALID, "TokenMeanPool: seq_len and embed_dim must be set");
+      if (n0 != static_cast<int64_t>(d.seq_len) * d.embed_dim) return fail(MIMIR_B200_E_INVALID, "TokenMeanPool: input size mismatch");
+      *out_n = d.embed_dim;
+      return MIMIR_B200_OK;
+    case LT::GlobalAvgPool: {
+      L.ch = d.in_channels > 0 ? d.in_channels : 64;
+      L.h = d.input_height > 0 ? d.input_height : 32;
+      L.w = d.input_width > 0 ? d.input_width : 32;
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "GlobalAvgPool2d (%s): input size mismatch", L.name.c_str());
+      *out_n = L.ch;
+      return MIMIR_B200_OK;
+    }
+    default:
+      return fail(MIMIR_B200_E_UNSUPPORTED, "layer type '%s' (%s) is not supported by the B200 backend", L.type.c_str(), L.name.c_str());
+  }
+}
+
+}  // namespace
+}  // namespace mb
+
+namespace mb {
+namespace {
+
+size_t f32_bytes(const TensorV& t, int batch) { return static_cast<size_t>(batch) * static_cast<size_t>(t.n) * 4; }
+size_t splitv_bytes(const TensorV& t, int batch) { return split_bytes(static_cast<int64_t>(batch) * t.split_rows_ps, t.split_k, 2); }
+
+int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, int batch) {
+  if (batch <= 0) return fail(MIMIR_B200_E_INVALID, "plan: batch must be positive");
+  const int nl = static_cast<int>(m->layers.size());
+  m->tensors.clear();
+  m->input_v.clear();
+  m->planned_batch = 0;
+  std::map<std::string, int> cur;
+  for (int i = 0; i < n_inputs; ++i) {
+    std::string name = (inputs[i].name && inputs[i].name[0]) ? inputs[i].name : "x";
+    if (name == "__input__") name = "x";
+    if (inputs[i].per_sample == 0) return fail(MIMIR_B200_E_INVALID, "plan: input '%s' is empty", name.c_str());
+    TensorV t;
+    t.name = name;
+    t.n = static_cast<int64_t>(inputs[i].per_sample);
+    t.broadcast_input = inputs[i].broadcast != 0;
+    m->tensors.push_back(t);
+    const int v = static_cast<int>(m->tensors.size()) - 1;
+    cur[name] = v;
+    m->input_v[name] = v;
+    if (name == "x") cur["__input__"] = v;  // Model.cpp:4640-4642
+  }
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& L = m->layers[li];
+    L.in_v.clear();
+    L.out_v = -1;
+    L.skip = false; L.fused_act = -1; L.emit_split = false; L.emit_f32 = true; L.read_split = false;
+    L.ws_off = 0; L.ws_bytes = 0;
+    std::vector<std::string> names = L.inputs;
+    if (names.empty()) names.push_back("x");
+    std::vector<int64_t> in_n;
+    for (const auto& nm : names) {
+      auto it = cur.find(nm);
+      if (it == cur.end()) return fail(MIMIR_B200_E_INVALID, "Missing input tensor: %s (layer %d, %s)", nm.c_str(), li, L.name.c_str());
+      L.in_v.push_back(it->second);
+      in_n.push_back(m->tensors[it->second].n);
+    }
+    int64_t out_n = 0;
+    MB_TRY(infer_layer(L, in_n, &out_n));
+    TensorV t;
+    t.name = L.output.empty() ? "x" : L.output;
+    t.n = out_n;
+    t.producer = li;
+    if (L.lt == LT::Alias) t.alias_of = root_of(m->tensors, L.in_v[0]);
+    m->tensors.push_back(t);
+    L.out_v = static_cast<int>(m->tensors.size()) - 1;
+    for (int v : L.in_v) m->tensors[v].consumers.push_back(li);
+    cur[t.name] = L.out_v;
+  }
+  auto itx = cur.find("x");
+  if (itx == cur.end()) return fail(MIMIR_B200_E_INVALID, "graph defines no tensor 'x'");
+  m->out_v = itx->second;
+  const int out_root = root_of(m->tensors, m->out_v);
+
+  // consumers through aliases count for the root
+  auto total_consumers = [&](int v) {
+    size_t c = m->tensors[v].consumers.size();
+    for (size_t a = 0; a < m->tensors.size(); ++a)
+      if (m->tensors[a].alias_of == v) c += m->tensors[a].consumers.size() + 1;  // +1: the alias layer itself holds it
+    return c;
+  };
+
+  // ---- fusion 1: activation into the producing GEMM / GroupNorm ---------------------------------
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& A = m->layers[li];
+    if (A.lt != LT::Act) continue;
+    const int pv = A.in_v[0];
+    TensorV& pt = m->tensors[pv];
+    if (pt.alias_of >= 0 || pt.producer < 0 || pv == out_root || total_consumers(pv) != 1) continue;
+    LayerRT& P = m->layers[pt.producer];
+    if (P.fused_act >= 0 || P.out_v != pv) continue;
+    const bool ok = (P.lt == LT::Linear) || (P.lt == LT::Conv2d && P.d.activation == 0) ||
+                    (P.lt == LT::GroupNorm && A.act_of_type == MIMIR_B200_ELT_SILU);
+    if (!ok) continue;
+    P.fused_act = A.act_of_type;
+    P.out_v = A.out_v;
+    m->tensors[A.out_v].producer = pt.producer;
+    pt.consumers.clear();
+    pt.want_f32 = false;
+    pt.producer = -2;  // dead
+    A.skip = true;
+  }
+  // ---- fusion 2: hi/lo planes straight from one GEMM epilogue into the next Linear -------------
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& C = m->layers[li];
+    if (C.lt != LT::Linear || C.skip) continue;
+    if (linear_uses_skinny(C.rows_ps * batch, m->precision)) continue;
+    const int v = C.in_v[0];
+    TensorV& t = m->tensors[v];
+    if (t.alias_of >= 0 || t.producer < 0 || v == out_root || total_consumers(v) != 1) continue;
+    LayerRT& P = m->layers[t.producer];
+    if (P.lt != LT::Linear || P.out_v != v || P.out_f != C.in_f || P.rows_ps != C.rows_ps) continue;
+    if (linear_uses_skinny(P.rows_ps * batch, m->precision)) continue;
+    P.emit_split = true;
+    P.emit_f32 = false;
+    C.read_split = true;
+    t.want_f32 = false;
+    t.want_split = true;
+    t.split_rows_ps = P.rows_ps;
+    t.split_k = P.out_f;
+  }
+
+  // ---- liveness ------------------------------------------------------------------------------------
+  const int nt = static_cast<int>(m->tensors.size());
+  for (int v = 0; v < nt; ++v) {
+    TensorV& t = m->tensors[v];
+    t.first = (t.producer >= 0) ? t.producer : -1;
+    t.last = t.first;
+  }
+  for (int v = 0; v < nt; ++v) {
+    const int r = root_of(m->tensors, v);
+    TensorV& rt = m->tensors[r];
+    for (int c : m->tensors[v].consumers)
+      if (!m->layers[c].skip) rt.last = std::max(rt.last, c);
+    if (m->tensors[v].alias_of >= 0) rt.last = std::max(rt.last, m->tensors[v].producer);
+  }
+  m->tensors[out_root].last = nl;
+
+  // ---- offsets ---------------------------------------------------------------------------------------
+  ArenaSim sim;
+  auto place = [&](int v) {
+    TensorV& t = m->tensors[v];
+    if (t.alias_of >= 0 || t.producer == -2) return;
+    if (t.want_f32) t.off_f32 = sim.alloc(f32_bytes(t, batch));
+    if (t.want_split) t.off_split = sim.alloc(splitv_bytes(t, batch));
+  };
+  auto drop = [&](int v) {
+    TensorV& t = m->tensors[v];
+    if (t.alias_of >= 0 || t.producer == -2) return;
+    if (t.want_f32) sim.release(t.off_f32, f32_bytes(t, batch));
+    if (t.want_split) sim.release(t.off_split, splitv_bytes(t, batch));
+  };
+  for (int v = 0; v < nt; ++v)
+    if (m->tensors[v].first == -1 && m->tensors[v].producer == -1) place(v);
+  for (int v = 0; v < nt; ++v)
+    if (m->tensors[v].producer == -1 && m->tensors[v].last == -1 && root_of(m->tensors, v) != out_root) drop(v);
+  uint64_t flops = 0, hbm = 0;
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& L = m->layers[li];
+    if (!L.skip && L.lt != LT::Alias) {
+      place(L.out_v);
+      const int64_t rows = static_cast<int64_t>(batch) * L.rows_ps;
+      switch (L.lt) {
+        case LT::Linear:
+          L.ws_bytes = linear_ws_bytes(static_cast<int>(rows), L.in_f, L.out_f, m->precision, L.read_split);
+          flops += 2ull * rows * L.in_f * L.out_f;
+          break;
+        case LT::Attention: {
+          const int64_t r = static_cast<int64_t>(batch) * L.seq;
+          L.ws_bytes = attention_ws_bytes(static_cast<int>(r), L.embed, m->precision);
+          const uint64_t core = 4ull * batch * L.seq * L.seq * L.embed;
+          flops += 2ull * r * L.embed * 4 * L.embed + (L.d.causal ? core / 2 : core);
+          break;
+        }
+        case LT::Conv2d: {
+          const int k = L.d.in_channels * L.d.kernel * L.d.kernel;
+          L.ws_bytes = conv_ws_bytes(batch, L.oh * L.ow, k, m->precision);
+          flops += 2ull * batch * L.oh * L.ow * k * L.d.out_channels;
+          break;
+        }
+        default:
+          L.ws_bytes = 0;
+          for (int v : L.in_v) hbm += f32_bytes(m->tensors[v], batch);
+          hbm += f32_bytes(m->tensors[L.out_v], batch);
+          break;
+      }
+      if (L.ws_bytes) {
+        L.ws_off = sim.alloc(L.ws_bytes);
+        sim.release(L.ws_off, L.ws_bytes);
+      }
+    }
+    for (int v = 0; v < nt; ++v) {
+      const TensorV& t = m->tensors[v];
+      if (t.alias_of < 0 && t.producer != -2 && t.last == li) drop(v);
+    }
+  }
+  m->flops = flops;
+  m->hbm_bytes = hbm;
+
+  // ---- budget check before anything is launched, then (re)allocate the arena -------------------------
+  const size_t need = sim.peak + 256;
+  if (m->arena && m->arena_bytes < need) {
+    dev_free(m->arena, m->arena_bytes);
+    m->arena = nullptr;
+    m->arena_bytes = 0;
+  }
+  if (!m->arena) {
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&m->arena), need, "activation arena"));
+    m->arena_bytes = need;
+  }
+  m->planned_batch = batch;
+  for (auto& L : m->layers) MB_TRY(prepare_weight_planes(m, L, nullptr));
+  MB_CUDA(cudaStreamSynchronize(nullptr));
+  g_stats.arena_peak_bytes = need;
+  return MIMIR_B200_OK;
+}
+
+struct Bound {
+  std::vector<const float*> in_ptr;  // per tensor version: user device pointer overriding the arena
+  float* out_ptr = nullptr;
+};
+
+int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st) {
+  auto f32p = [&](int v) -> float* {
+    const int r = root_of(m->tensors, v);
+    if (r < static_cast<int>(bnd.in_ptr.size()) && bnd.in_ptr[r]) return const_cast<float*>(bnd.in_ptr[r]);
+    if (r == root_of(m->tensors, m->out_v) && bnd.out_ptr) return bnd.out_ptr;
+    return reinterpret_cast<float*>(m->arena + m->tensors[r].off_f32);
+  };
+  auto splitp = [&](int v) -> __nv_bfloat16* { return reinterpret_cast<__nv_bfloat16*>(m->arena + m->tensors[v].off_split); };
+  const int nl = static_cast<int>(m->layers.size());
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& L = m->layers[li];
+    if (L.skip || L.lt == LT::Alias) continue;
+    const MimirLayerDesc& d = L.d;
+    void* ws = L.ws_bytes ? static_cast<void*>(m->arena + L.ws_off) : nullptr;
+    int s = MIMIR_B200_OK;
+    switch (L.lt) {
+      case LT::Linear: {
+        LinearExec e;
+        e.rows = batch * L.rows_ps; e.in_f = L.in_f; e.out_f = L.out_f; e.precision = m->precision;
+        if (L.read_split) e.x_split = splitp(L.in_v[0]); else e.x_f32 = f32p(L.in_v[0]);
+        e.w_f32 = L.w_f32;
+        e.w_split = L.w_split;
+        e.bias = d.use_bias ? L.w_f32 + static_cast<size_t>(L.in_f) * L.out_f : nullptr;
+        e.activation = L.fused_act;
+        if (L.emit_f32) e.y_f32 = f32p(L.out_v);
+        if (L.emit_split) e.y_split = splitp(L.out_v);
+        e.ws = ws; e.ws_bytes = L.ws_bytes;
+        s = linear_exec(e, st);
+        break;
+      }
+      case LT::Attention: {
+        AttentionExec e;
+        e.batch = batch; e.seq = L.seq; e.embed = L.embed; e.heads = L.heads; e.causal = d.causal;
+        e.precision = m->precision;
+        e.x = f32p(L.in_v[0]); e.wqkv_split = L.w_split; e.wout_split = L.w_split2; e.y = f32p(L.out_v); e.ws = ws;
+        s = attention_exec(e, st);
+        break;
+      }
+      case LT::Conv2d: {
+        ConvExec e;
+        e.batch = batch; e.ic = d.in_channels; e.oc = d.out_channels; e.h = L.h; e.w = L.w; e.ks = d.kernel;
+        e.stride = d.stride; e.pad = d.padding; e.precision = m->precision;
+        e.activation = d.activation ? MIMIR_B200_ELT_RELU : L.fused_act;
+        e.x = f32p(L.in_v[0]); e.w_split = L.w_split; e.y = f32p(L.out_v); e.ws = ws;
+        s = conv_exec(e, st);
+        break;
+      }
+      case LT::LayerNorm: {
+        const float* g = d.affine ? L.w_f32 : nullptr;
+        const float* b = (d.affine && d.use_bias) ? L.w_f32 + L.norm_n : nullptr;
+        const int64_t rows = static_cast<int64_t>(batch) * (m->tensors[L.in_v[0]].n / L.norm_n);
+        s = launch_layernorm(f32p(L.in_v[0]), g, b, f32p(L.out_v), rows, L.norm_n, d.eps, st);
+        break;
+      }
+      case LT::RMSNorm: {
+        const bool aff = d.affine && L.w_f32 && L.w_count > 0;
+        s = launch_rmsnorm(f32p(L.in_v[0]), aff ? L.w_f32 : nullptr, aff ? static_cast<int64_t>(L.w_count) : 0, f32p(L.out_v),
+                           batch, m->tensors[L.in_v[0]].n, d.eps, st);
+        break;
+      }
+      case LT::GroupNorm: {
+        const float* g = d.affine ? L.w_f32 : nullptr;
+        const float* b = (d.affine && d.use_bias) ? L.w_f32 + L.ch : nullptr;
+        s = launch_groupnorm(f32p(L.in_v[0]), g, b, f32p(L.out_v), batch, L.ch, L.h * L.w, d.num_groups, d.eps, L.fused_act,
+                             nullptr, st);
+        break;
+      }
+      case LT::Softmax:
+      case LT::LogSoftmax:
+        s = launch_softmax(f32p(L.in_v[0]), f32p(L.out_v), batch, m->tensors[L.in_v[0]].n, L.lt == LT::LogSoftmax, st);
+        break;
+      case LT::Act:
+        s = launch_eltwise(L.act_of_type, f32p(L.in_v[0]), nullptr, f32p(L.out_v), batch, m->tensors[L.in_v[0]].n, 0, st);
+        break;
+      case LT::Add:
+      case LT::Multiply: {
+        int a = L.in_v[0], b = L.in_v[1];
+        if (m->tensors[b].n > m->tensors[a].n) std::swap(a, b);  // `big` first (LayerOps.hpp:171-176)
+        s = launch_eltwise(L.lt == LT::Add ? MIMIR_B200_ELT_ADD : MIMIR_B200_ELT_MULTIPLY, f32p(a), f32p(b), f32p(L.out_v), batch,
+                           m->tensors[a].n, m->tensors[b].n, st);
+        break;
+      }
+      case LT::Embedding:
+        s = launch_embedding(f32p(L.in_v[0]), nullptr, L.w_f32, f32p(L.out_v), static_cast<int64_t>(batch) * m->tensors[L.in_v[0]].n,
+                             std::max(1, d.vocab_size), std::max(1, d.embed_dim), d.padding_idx, st);
+        break;
+      case LT::UpsampleNearest:
+        s = launch_upsample_nearest(f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.oh / L.h, L.ow / L.w, st);
+        break;
+      case LT::Permute:
+        s = launch_permute(f32p(L.in_v[0]), f32p(L.out_v), batch, d.n_dims, d.shape, d.permute_dims, st);
+        break;
+      case LT::Concat: {
+        int64_t off = 0;
+        const int64_t total = m->tensors[L.out_v].n;
+        for (int v : L.in_v) {
+          s = launch_copy_strided(f32p(v), f32p(L.out_v), batch, m->tensors[v].n, total, off, st);
+          if (s != MIMIR_B200_OK) break;
+          off += m->tensors[v].n;
+        }
+        break;
+      }
+      case LT::TokenMeanPool:
+        s = launch_token_mean_pool(f32p(L.in_v[0]), f32p(L.out_v), batch, d.seq_len, d.embed_dim, st);
+        break;
+      case LT::GlobalAvgPool:
+        s = launch_global_avgpool(f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h * L.w, st);
+        break;
+      default:
+        return fail(MIMIR_B200_E_UNSUPPORTED, "layer type '%s' is not supported by the B200 backend", L.type.c_str());
+    }
+    if (s != MIMIR_B200_OK) return s;
+  }
+  return MIMIR_B200_OK;
+}
+
+int check_inputs(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, int batch, std::vector<int>* vs) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (m->planned_batch != batch) return fail(MIMIR_B200_E_INVALID, "forward: model is planned for batch %d, not %d", m->planned_batch, batch);
+  if (static_cast<size_t>(n_inputs) != m->input_v.size()) return fail(MIMIR_B200_E_INVALID, "forward: expected %zu inputs, got %d", m->input_v.size(), n_inputs);
+  for (int i = 0; i < n_inputs; ++i) {
+    std::string name = (inputs[i].name && inputs[i].name[0]) ? inputs[i].name : "x";
+    if (name == "__input__") name = "x";
+    auto it = m->input_v.find(name);
+    if (it == m->input_v.end()) return fail(MIMIR_B200_E_INVALID, "forward: input '%s' was not declared to plan", name.c_str());
+    const TensorV& t = m->tensors[it->second];
+    if (static_cast<uint64_t>(t.n) != inputs[i].per_sample || t.broadcast_input != (inputs[i].broadcast != 0))
+      return fail(MIMIR_B200_E_INVALID, "forward: input '%s' does not match the planned size", name.c_str());
+    if (!inputs[i].data) return fail(MIMIR_B200_E_INVALID, "forward: input '%s' has no data", name.c_str());
+    vs->push_back(it->second);
+  }
+  return MIMIR_B200_OK;
+}
+
+}  // namespace
+}  // namespace mb
+
+extern "C" {
+
+using namespace mb;
+
+int mimir_b200_model_create(const MimirLayerDesc* layers, int n_layers, MimirB200ModelHandle* out) {
+  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
+  if (!layers || n_layers <= 0 || !out) return fail(MIMIR_B200_E_INVALID, "model_create: no layers defined");
+  auto m = std::make_unique<MimirB200Model>();
+  m->layers.resize(static_cast<size_t>(n_layers));
+  for (int i = 0; i < n_layers; ++i) {
+    const MimirLayerDesc& d = layers[i];
+    LayerRT& L = m->layers[static_cast<size_t>(i)];
+    L.name = d.name ? d.name : ("layer" + std::to_string(i));
+    L.type = d.type ? d.type : "";
+    L.output = (d.output && d.output[0]) ? d.output : "x";
+    if (d.n_inputs < 0 || d.n_inputs > MIMIR_B200_MAX_INPUTS) return fail(MIMIR_B200_E_INVALID, "layer %d: bad n_inputs", i);
+    for (int j = 0; j < d.n_inputs; ++j) L.inputs.emplace_back(d.inputs[j] ? d.inputs[j] : "x");
+    L.d = d;
+    L.d.name = L.d.type = L.d.output = nullptr;
+    for (auto& p : L.d.inputs) p = nullptr;
+    if (L.d.n_dims < 0 || L.d.n_dims > MIMIR_B200_MAX_DIMS) return fail(MIMIR_B200_E_INVALID, "layer %d: bad n_dims", i);
+    const TypeInfo ti = classify(L.type);
+    L.lt = ti.lt;
+    L.act_of_type = ti.act;
+    if (L.lt == LT::Unsupported)
+      return fail(MIMIR_B200_E_UNSUPPORTED, "layer %d (%s): type '%s' is not supported by the B200 backend (no CPU fallback)", i,
+                  L.name.c_str(), L.type.c_str());
+  }
+  MimirB200Model* raw = m.release();
+  {
+    std::lock_guard<std::mutex> lk(g_models_mu);
+    g_models.insert(raw);
+  }
+  *out = raw;
+  return MIMIR_B200_OK;
+}
+
+static void destroy_model(MimirB200Model* m) {
+  for (auto& L : m->layers) free_layer_weights(L, m);
+  if (m->arena) dev_free(m->arena, m->arena_bytes);
+  if (m->ev0) cudaEventDestroy(m->ev0);
+  if (m->ev1) cudaEventDestroy(m->ev1);
+  delete m;
+}
+
+int mimir_b200_model_destroy(MimirB200ModelHandle m) {
+  if (!m) return MIMIR_B200_OK;
+  {
+    std::lock_guard<std::mutex> lk(g_models_mu);
+    if (!g_models.erase(m)) return fail(MIMIR_B200_E_INVALID, "model_destroy: unknown handle");
+  }
+  cudaDeviceSynchronize();
+  destroy_model(m);
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_set_precision(MimirB200ModelHandle m, int precision) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (precision < MIMIR_B200_PREC_BF16X2 || precision > MIMIR_B200_PREC_BF16) return fail(MIMIR_B200_E_INVALID, "unknown precision %d", precision);
+  if (precision != m->precision) {
+    // operand planes depend on the precision: drop them, plan() rebuilds
+    for (auto& L : m->layers) {
+      if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
+      if (L.w_split2) { dev_free(L.w_split2, L.w_split2_bytes); m->weight_bytes -= L.w_split2_bytes; L.w_split2 = nullptr; }
+      L.w_split_k = -1;
+    }
+    m->planned_batch = 0;
+  }
+  m->precision = precision;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, const float* host, uint64_t n) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (layer_index < 0 || layer_index >= static_cast<int>(m->layers.size())) return fail(MIMIR_B200_E_INVALID, "upload_weights: layer index out of range");
+  LayerRT& L = m->layers[static_cast<size_t>(layer_index)];
+  if (n != L.d.params_count) return fail(MIMIR_B200_E_INVALID, "upload_weights: %llu values given, layer '%s' has params_count %llu",
+                                          static_cast<unsigned long long>(n), L.name.c_str(), static_cast<unsigned long long>(L.d.params_count));
+  cudaDeviceSynchronize();
+  free_layer_weights(L, m);
+  L.w_count = 0;
+  if (n == 0) return MIMIR_B200_OK;
+  if (!host) return fail(MIMIR_B200_E_INVALID, "upload_weights: null host pointer");
+  MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_f32), n * 4, "layer weights"));
+  L.w_count = n;
+  m->weight_bytes += n * 4;
+  MB_CUDA(cudaMemcpy(L.w_f32, host, n * 4, cudaMemcpyHostToDevice));
+  m->planned_batch = 0;  // planes are rebuilt by the next plan
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_plan(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, uint64_t* arena_peak_bytes) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (!inputs || n_inputs <= 0) return fail(MIMIR_B200_E_INVALID, "plan: no inputs declared");
+  MB_TRY(plan_model(m, inputs, n_inputs, batch));
+  if (arena_peak_bytes) *arena_peak_bytes = m->arena_bytes;
+  g_stats.weight_bytes = m->weight_bytes;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, float* out_dev,
+                                    uint64_t out_capacity, uint64_t* out_len, void* stream) {
+  std::vector<int> vs;
+  MB_TRY(check_inputs(m, inputs, n_inputs, batch, &vs));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const TensorV& ot = m->tensors[root_of(m->tensors, m->out_v)];
+  if (out_len) *out_len = static_cast<uint64_t>(ot.n);
+  if (!out_dev || out_capacity < static_cast<uint64_t>(ot.n) * batch) return fail(MIMIR_B200_E_INVALID, "forward: output capacity too small");
+  Bound b;
+  b.in_ptr.assign(m->tensors.size(), nullptr);
+  for (int i = 0; i < n_inputs; ++i) {
+    const TensorV& t = m->tensors[vs[i]];
+    if (t.broadcast_input) {
+      float* slot = reinterpret_cast<float*>(m->arena + t.off_f32);
+      MB_TRY(launch_broadcast_rows(static_cast<const float*>(inputs[i].data), slot, batch, t.n, st));
+    } else {
+      b.in_ptr[vs[i]] = static_cast<const float*>(inputs[i].data);
+    }
+  }
+  if (ot.producer >= 0) b.out_ptr = out_dev;
+  MB_TRY(run_layers(m, batch, b, st));
+  if (ot.producer < 0) {  // graph returns one of its inputs
+    const float* src = b.in_ptr[root_of(m->tensors, m->out_v)] ? b.in_ptr[root_of(m->tensors, m->out_v)]
+                                                               : reinterpret_cast<float*>(m->arena + ot.off_f32);
+    MB_CUDA(cudaMemcpyAsync(out_dev, src, static_cast<size_t>(ot.n) * batch * 4, cudaMemcpyDeviceToDevice, st));
+  }
+  g_stats.flops_last_forward = m->flops;
+  g_stats.bytes_last_forward = m->hbm_bytes;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, float* out_host,
+                             uint64_t out_capacity, uint64_t* out_len) {
+  std::vector<int> vs;
+  MB_TRY(check_inputs(m, inputs, n_inputs, batch, &vs));
+  cudaStream_t st = nullptr;
+  const TensorV& ot = m->tensors[root_of(m->tensors, m->out_v)];
+  if (out_len) *out_len = static_cast<uint64_t>(ot.n);
+  if (!out_host || out_capacity < static_cast<uint64_t>(ot.n) * batch) return fail(MIMIR_B200_E_INVALID, "forward: output capacity too small");
+  if (!m->ev0) {
+    MB_CUDA(cudaEventCreate(&m->ev0));
+    MB_CUDA(cudaEventCreate(&m->ev1));
+  }
+  for (int i = 0; i < n_inputs; ++i) {
+    const TensorV& t = m->tensors[vs[i]];
+    float* slot = reinterpret_cast<float*>(m->arena + t.off_f32);
+    if (t.broadcast_input) {
+      MB_CUDA(cudaMemcpyAsync(slot, inputs[i].data, static_cast<size_t>(t.n) * 4, cudaMemcpyHostToDevice, st));
+      if (batch > 1) MB_TRY(launch_broadcast_rows(slot, slot + t.n, batch - 1, t.n, st));
+    } else {
+      MB_CUDA(cudaMemcpyAsync(slot, inputs[i].data, static_cast<size_t>(t.n) * batch * 4, cudaMemcpyHostToDevice, st));
+    }
+  }
+  Bound b;
+  MB_CUDA(cudaEventRecord(m->ev0, st));
+  MB_TRY(run_layers(m, batch, b, st));
+  MB_CUDA(cudaEventRecord(m->ev1, st));
+  MB_CUDA(cudaMemcpyAsync(out_host, m->arena + ot.off_f32, static_cast<size_t>(ot.n) * batch * 4, cudaMemcpyDeviceToHost, st));
+  MB_TRY(check_device_error_word(st));
+  cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1);
+  g_stats.ms_last_forward = m->last_ms;
+  g_stats.flops_last_forward = m->flops;
+  g_stats.bytes_last_forward = m->hbm_bytes;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_get_stats(MimirB200Stats* out) {
+  if (!out) return fail(MIMIR_B200_E_INVALID, "get_stats: null output");
+  *out = g_stats;
+  out->kernels_launched = ctx().launches.load();
+  return MIMIR_B200_OK;
+}
+
+// Reads the device error word that bounded waits set; OK when no wait gave up.
+int mimir_b200_check_device(void* stream) {
+  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
+  return check_device_error_word(static_cast<cudaStream_t>(stream));
+}
+
+// Live timing of the contraction kernel with CUDA events on the launching stream.
+int mimir_b200_profile_gemm(int enable) {
+  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
+  ctx().prof_gemm = enable != 0;
+  return MIMIR_B200_OK;
+}
+// Synchronises the device, sums the recorded GEMM durations and clears the record.
+int mimir_b200_profile_read(float* total_ms, int* launches) {
+  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
+  MB_CUDA(cudaDeviceSynchronize());
+  float tot = 0.f;
+  auto& ev = ctx().prof_events;
+  for (size_t i = 0; i + 1 < ev.size(); i += 2) {
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+    tot += ms;
+    cudaEventDestroy(ev[i]);
+    cudaEventDestroy(ev[i + 1]);
+  }
+  if (total_ms) *total_ms = tot;
+  if (launches) *launches = static_cast<int>(ev.size() / 2);
+  ev.clear();
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_shutdown(void) {
+  Context& c = ctx();
+  if (!c.initialised) return MIMIR_B200_OK;
+  cudaDeviceSynchronize();
+  std::set<MimirB200Model*> models;
+  {
+    std::lock_guard<std::mutex> lk(g_models_mu);
+    models.swap(g_models);
+  }
+  for (auto* m : models) destroy_model(m);
+  return MIMIR_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,60 @@
+// ops.h — device-pointer op sequences shared by the per-op C ABI (capi.cu) and the graph
+// executor (graph.cu): each `*_ws_bytes` says how much workspace the sequence needs and each
+// `*_exec` runs it asynchronously on a stream.
+#pragma once
+
+#include "common.h"
+
+namespace mb {
+
+void precision_planes(int precision, int* a_planes, int* w_planes);
+size_t split_bytes(int64_t rows, int k, int planes);
+int check_device_error_word(cudaStream_t st);
+
+struct LinearExec {
+  int rows = 0, in_f = 0, out_f = 0;
+  int precision = MIMIR_B200_PREC_BF16X2;
+  const float* x_f32 = nullptr;             // fp32 [rows, in_f] (needed unless x_split is given)
+  const __nv_bfloat16* x_split = nullptr;   // planes produced by an upstream GEMM epilogue
+  const float* w_f32 = nullptr;             // fp32 [out_f, in_f] (skinny path)
+  const __nv_bfloat16* w_split = nullptr;   // planes [w_planes][out_f][kp] (tensor-core path)
+  const float* bias = nullptr;
+  const float* residual = nullptr;          // same layout as y_f32
+  int activation = -1;
+  float* y_f32 = nullptr;
+  __nv_bfloat16* y_split = nullptr;         // planes [2][rows][round_up(out_f, 64)]
+  int out_nchw_hw = 0;
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
+};
+bool linear_uses_skinny(int rows, int precision);
+size_t linear_ws_bytes(int rows, int in_f, int out_f, int precision, bool a_presplit);
+int linear_exec(const LinearExec& e, cudaStream_t st);
+
+struct AttentionExec {
+  int batch = 0, seq = 0, embed = 0, heads = 1, causal = 0;
+  int precision = MIMIR_B200_PREC_BF16X2;
+  const float* x = nullptr;                    // fp32 [batch*seq, embed]
+  const __nv_bfloat16* wqkv_split = nullptr;   // planes of Wqkv^T: [3E][round_up(E,64)]
+  const __nv_bfloat16* wout_split = nullptr;   // planes of Wout^T: [E][round_up(E,64)]
+  const float* residual = nullptr;
+  float* y = nullptr;
+  void* ws = nullptr;
+};
+size_t attention_ws_bytes(int rows, int embed, int precision);
+int attention_exec(const AttentionExec& e, cudaStream_t st);
+
+struct ConvExec {
+  int batch = 0, ic = 0, oc = 0, h = 0, w = 0, ks = 3, stride = 1, pad = 0;
+  int precision = MIMIR_B200_PREC_BF16X2;
+  int activation = -1;                         // MIMIR_B200_ELT_RELU when the layer asks for it
+  const float* x = nullptr;                    // NCHW
+  const __nv_bfloat16* w_split = nullptr;      // planes [oc][round_up(ic*ks*ks, 64)]
+  const float* residual = nullptr;             // NCHW, same shape as y
+  float* y = nullptr;
+  void* ws = nullptr;
+};
+size_t conv_ws_bytes(int batch, int ohw, int k, int precision);
+int conv_exec(const ConvExec& e, cudaStream_t st);
+
+}  // namespace mb

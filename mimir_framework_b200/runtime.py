@@ -1,0 +1,321 @@
+"""Thin Python driver over the C ABI (``include/mimir_b200.h``), used by the tests and the benchmark.
+
+Everything here calls ``libmimir_b200.so``; nothing computes in Python.  Host-pointer calls take
+numpy arrays, device-pointer calls take raw addresses (e.g. ``torch.Tensor.data_ptr()``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import abi
+from .abi import MimirB200Stats, MimirLayerDesc, MimirNamedInput, desc_array
+
+
+class MimirB200Error(RuntimeError):
+    def __init__(self, status: int, message: str):
+        self.status = status
+        name = abi.STATUS_NAMES[status] if 0 <= status < len(abi.STATUS_NAMES) else str(status)
+        super().__init__(f"{name}: {message}")
+
+
+_P = C.c_void_p
+_SIGS = {
+    "mimir_b200_init": [C.c_int, C.c_size_t],
+    "mimir_b200_shutdown": [],
+    "mimir_b200_abi_version": [],
+    "mimir_b200_guard_set_limit": [C.c_size_t],
+    "mimir_b200_guard_request": [C.c_size_t, C.c_char_p],
+    "mimir_b200_guard_release": [C.c_size_t],
+    "mimir_b200_guard_stats": [_P, _P, _P],
+    "mimir_b200_linear_forward": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_linear_forward_ex": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_matmul": [_P, _P, _P, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_attention": [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_conv2d": [_P, _P, _P] + [C.c_int] * 9,
+    "mimir_b200_layernorm": [_P, _P, _P, _P, C.c_longlong, C.c_int, C.c_float],
+    "mimir_b200_rmsnorm": [_P, _P, C.c_longlong, _P, C.c_int, C.c_longlong, C.c_float],
+    "mimir_b200_groupnorm": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int],
+    "mimir_b200_softmax": [_P, _P, C.c_int, C.c_longlong, C.c_int],
+    "mimir_b200_eltwise": [C.c_int, _P, _P, _P, C.c_int, C.c_longlong, C.c_longlong],
+    "mimir_b200_embedding": [_P, _P, _P, _P, C.c_longlong, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_upsample_nearest": [_P, _P] + [C.c_int] * 6,
+    "mimir_b200_permute": [_P, _P, C.c_int, C.c_int, _P, _P],
+    "mimir_b200_token_mean_pool": [_P, _P, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_global_avgpool": [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_model_create": [_P, C.c_int, _P],
+    "mimir_b200_model_destroy": [_P],
+    "mimir_b200_model_set_precision": [_P, C.c_int],
+    "mimir_b200_model_upload_weights": [_P, C.c_int, _P, C.c_uint64],
+    "mimir_b200_model_plan": [_P, _P, C.c_int, C.c_int, _P],
+    "mimir_b200_model_forward": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P],
+    "mimir_b200_model_forward_device": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P, _P],
+    "mimir_b200_argmax_rows_device": [_P, _P, C.c_longlong, C.c_int, _P],
+    "mimir_b200_get_stats": [_P],
+    "mimir_b200_check_device": [_P],
+    "mimir_b200_profile_gemm": [C.c_int],
+    "mimir_b200_profile_read": [_P, _P],
+    "mimir_b200_dev_layernorm": [_P, _P, _P, _P, C.c_longlong, C.c_int, C.c_float, _P],
+    "mimir_b200_dev_rmsnorm": [_P, _P, C.c_longlong, _P, C.c_int, C.c_longlong, C.c_float, _P],
+    "mimir_b200_dev_groupnorm": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _P],
+    "mimir_b200_dev_softmax": [_P, _P, C.c_int, C.c_longlong, C.c_int, _P],
+    "mimir_b200_dev_eltwise": [C.c_int, _P, _P, _P, C.c_int, C.c_longlong, C.c_longlong, _P],
+}
+
+EXPORTED_SYMBOLS = sorted(list(_SIGS) + ["mimir_b200_last_error"])
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        l = abi.load()
+        for name, args in _SIGS.items():
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+        _lib = l
+    return _lib
+
+
+def check(status: int):
+    if status != abi.OK:
+        raise MimirB200Error(status, lib().mimir_b200_last_error().decode(errors="replace"))
+
+
+def init(device: int = 0, hbm_budget_bytes: int = 0):
+    check(lib().mimir_b200_init(device, hbm_budget_bytes))
+
+
+def shutdown():
+    check(lib().mimir_b200_shutdown())
+
+
+def guard_stats():
+    a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    check(lib().mimir_b200_guard_stats(C.byref(a), C.byref(b), C.byref(c)))
+    return dict(limit=a.value, current=b.value, peak=c.value)
+
+
+def stats() -> dict:
+    s = MimirB200Stats()
+    check(lib().mimir_b200_get_stats(C.byref(s)))
+    return {k: getattr(s, k) for k, _ in MimirB200Stats._fields_}
+
+
+def profile_gemm(enable: bool):
+    check(lib().mimir_b200_profile_gemm(int(enable)))
+
+
+def profile_read():
+    ms, n = C.c_float(0), C.c_int(0)
+    check(lib().mimir_b200_profile_read(C.byref(ms), C.byref(n)))
+    return ms.value, n.value
+
+
+def _f(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data
+
+
+# ---- per-op calls, host arrays -------------------------------------------------------------------
+def linear_forward(x, w, bias, batch, in_f, out_f, precision=None, activation=-1):
+    x, w, bias = _f(x), _f(w), _f(bias)
+    y = np.empty(batch * out_f, np.float32)
+    if precision is None and activation == -1:
+        check(lib().mimir_b200_linear_forward(_p(x), _p(w), _p(bias), _p(y), batch, in_f, out_f))
+    else:
+        check(lib().mimir_b200_linear_forward_ex(_p(x), _p(w), _p(bias), _p(y), batch, in_f, out_f,
+                                                 abi.PREC_BF16X2 if precision is None else precision, activation))
+    return y
+
+
+def matmul(a, b, M, K, N):
+    a, b = _f(a), _f(b)
+    y = np.empty(M * N, np.float32)
+    check(lib().mimir_b200_matmul(_p(a), _p(b), _p(y), M, K, N))
+    return y
+
+
+def attention(x, w, batch, seq, embed, heads, causal):
+    x, w = _f(x), _f(w)
+    y = np.empty(batch * seq * embed, np.float32)
+    check(lib().mimir_b200_attention(_p(x), _p(w), _p(y), batch, seq, embed, heads, int(causal)))
+    return y
+
+
+def conv2d(x, w, batch, ic, oc, h, wd, k, stride, pad, relu=False):
+    x, w = _f(x), _f(w)
+    oh = (h + 2 * pad - k) // stride + 1
+    ow = (wd + 2 * pad - k) // stride + 1
+    y = np.empty(batch * oc * max(oh, 0) * max(ow, 0), np.float32)
+    check(lib().mimir_b200_conv2d(_p(x), _p(w), _p(y), batch, ic, oc, h, wd, k, stride, pad, int(relu)))
+    return y
+
+
+def layernorm(x, gamma, beta, rows, n, eps=1e-5):
+    x, gamma, beta = _f(x), _f(gamma), _f(beta)
+    y = np.empty(rows * n, np.float32)
+    check(lib().mimir_b200_layernorm(_p(x), _p(gamma), _p(beta), _p(y), rows, n, eps))
+    return y
+
+
+def rmsnorm(x, gamma, batch, n, eps=1e-5):
+    x, gamma = _f(x), _f(gamma)
+    y = np.empty(batch * n, np.float32)
+    check(lib().mimir_b200_rmsnorm(_p(x), _p(gamma), 0 if gamma is None else gamma.size, _p(y), batch, n, eps))
+    return y
+
+
+def groupnorm(x, gamma, beta, batch, ch, h, w, groups, eps=1e-5, act=-1):
+    x, gamma, beta = _f(x), _f(gamma), _f(beta)
+    y = np.empty(batch * ch * h * w, np.float32)
+    check(lib().mimir_b200_groupnorm(_p(x), _p(gamma), _p(beta), _p(y), batch, ch, h, w, groups, eps, act))
+    return y
+
+
+def softmax(x, batch, n, log=False):
+    x = _f(x)
+    y = np.empty(batch * n, np.float32)
+    check(lib().mimir_b200_softmax(_p(x), _p(y), batch, n, int(log)))
+    return y
+
+
+def eltwise(op, a, b=None, batch=1):
+    a, b = _f(a), _f(b)
+    n = a.size // batch
+    nb = 0 if b is None else b.size // batch
+    y = np.empty(a.size, np.float32)
+    check(lib().mimir_b200_eltwise(op, _p(a), _p(b), _p(y), batch, n, nb))
+    return y
+
+
+def embedding(ids, table, vocab, dim, padding_idx=-1):
+    table = _f(table)
+    ids = np.ascontiguousarray(ids)
+    y = np.empty(ids.size * dim, np.float32)
+    if ids.dtype == np.int32:
+        check(lib().mimir_b200_embedding(None, _p(ids), _p(table), _p(y), ids.size, vocab, dim, padding_idx))
+    else:
+        ids = _f(ids)
+        check(lib().mimir_b200_embedding(_p(ids), None, _p(table), _p(y), ids.size, vocab, dim, padding_idx))
+    return y
+
+
+def upsample_nearest(x, batch, ch, in_h, in_w, sh, sw):
+    x = _f(x)
+    y = np.empty(x.size * sh * sw, np.float32)
+    check(lib().mimir_b200_upsample_nearest(_p(x), _p(y), batch, ch, in_h, in_w, sh, sw))
+    return y
+
+
+def permute(x, shape, dims, batch=1):
+    x = _f(x)
+    y = np.empty_like(x)
+    sh = (C.c_int * len(shape))(*shape)
+    dm = (C.c_int * len(dims))(*dims)
+    check(lib().mimir_b200_permute(_p(x), _p(y), batch, len(shape), C.addressof(sh), C.addressof(dm)))
+    return y
+
+
+def token_mean_pool(x, batch, seq, dim):
+    x = _f(x)
+    y = np.empty(batch * dim, np.float32)
+    check(lib().mimir_b200_token_mean_pool(_p(x), _p(y), batch, seq, dim))
+    return y
+
+
+def global_avgpool(x, batch, ch, h, w):
+    x = _f(x)
+    y = np.empty(batch * ch, np.float32)
+    check(lib().mimir_b200_global_avgpool(_p(x), _p(y), batch, ch, h, w))
+    return y
+
+
+# ---- whole graph -----------------------------------------------------------------------------------
+class GraphModel:
+    """A layer graph on the device: ``mimir_b200_model_*``."""
+
+    def __init__(self, descs, precision: int = abi.PREC_BF16X2):
+        self._descs = list(descs)
+        self._arr = desc_array(self._descs)
+        self._h = C.c_void_p()
+        check(lib().mimir_b200_model_create(C.addressof(self._arr), len(self._descs), C.byref(self._h)))
+        check(lib().mimir_b200_model_set_precision(self._h, precision))
+        self.batch = 0
+        self.arena_bytes = 0
+
+    def close(self):
+        if self._h:
+            lib().mimir_b200_model_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def upload_weights(self, i: int, w):
+        if w is None:
+            return
+        w = _f(w)
+        check(lib().mimir_b200_model_upload_weights(self._h, i, _p(w), w.size))
+
+    @staticmethod
+    def _inputs(spec):
+        """spec: name -> (address_or_array, per_sample, broadcast)"""
+        arr = (MimirNamedInput * len(spec))()
+        keep = []
+        for i, (name, (data, per, bc)) in enumerate(spec.items()):
+            arr[i].name = name.encode()
+            if isinstance(data, np.ndarray):
+                data = _f(data)
+                keep.append(data)
+                arr[i].data = data.ctypes.data
+            else:
+                arr[i].data = data
+            arr[i].per_sample = per
+            arr[i].broadcast = int(bc)
+        arr._keep = keep
+        return arr
+
+    def plan(self, spec: dict, batch: int) -> int:
+        arr = self._inputs({k: (0, per, bc) for k, (per, bc) in spec.items()})
+        peak = C.c_uint64(0)
+        check(lib().mimir_b200_model_plan(self._h, C.addressof(arr), len(spec), batch, C.byref(peak)))
+        self.batch = batch
+        self.arena_bytes = peak.value
+        return peak.value
+
+    def forward(self, inputs: dict, batch: int, out_per_sample: int) -> np.ndarray:
+        """inputs: name -> (numpy array, broadcast flag).  Host in, host out."""
+        spec = {}
+        for k, (a, bc) in inputs.items():
+            a = _f(a)
+            spec[k] = (a, a.size if bc else a.size // batch, bc)
+        arr = self._inputs(spec)
+        out = np.empty(batch * out_per_sample, np.float32)
+        n = C.c_uint64(0)
+        check(lib().mimir_b200_model_forward(self._h, C.addressof(arr), len(spec), batch, _p(out), out.size, C.byref(n)))
+        return out.reshape(batch, n.value) if n.value * batch == out.size else out
+
+    def forward_host_ptrs(self, spec: dict, batch: int, out_ptr: int, out_capacity: int) -> int:
+        """spec: name -> (host address, per_sample, broadcast).  For pinned buffers."""
+        arr = self._inputs(spec)
+        n = C.c_uint64(0)
+        check(lib().mimir_b200_model_forward(self._h, C.addressof(arr), len(spec), batch, out_ptr, out_capacity, C.byref(n)))
+        return n.value
+
+    def forward_device(self, spec: dict, batch: int, out_ptr: int, out_capacity: int, stream: int = 0) -> int:
+        """spec: name -> (device address, per_sample, broadcast).  Asynchronous on ``stream``."""
+        arr = self._inputs(spec)
+        n = C.c_uint64(0)
+        check(lib().mimir_b200_model_forward_device(self._h, C.addressof(arr), len(spec), batch, out_ptr, out_capacity,
+                                                    C.byref(n), stream))
+        return n.value

@@ -1,0 +1,244 @@
+"""Parity of every per-op C-ABI entry point against the CPU oracle, on seeded inputs.
+
+The checker is ``oracle/port.py`` (plain-C restatement) and, where it is built, the reference's own
+compiled CPU code (``oracle/_ref``).  Integer/index work (embedding, argmax, data movement) must be
+bit-exact; floating point must satisfy |gpu - cpu| <= 1e-4 + 1e-3 |cpu|.
+"""
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from mimir_framework_b200 import abi
+from oracle import port
+
+pytestmark = pytest.mark.gpu
+
+
+def rng(seed):
+    return np.random.default_rng(seed)
+
+
+@pytest.mark.parametrize("rows,in_f,out_f,bias", [
+    (1, 2, 3, True),          # the reference's own Linear test shape (test_layers_all_types.cpp:71-100)
+    (37, 50, 29, True),       # ragged everything, skinny path excluded (rows > 16)
+    (8, 300, 70, True),       # skinny (weight-streaming) path
+    (16, 4096, 130, False),   # skinny path, several K slices
+    (128, 64, 256, True),     # exactly one tile
+    (129, 65, 257, True),     # one past a tile in every dimension
+    (300, 1000, 515, True),
+    (1024, 4096, 512, True),  # K of the headline config
+])
+def test_linear(backend, rows, in_f, out_f, bias):
+    r = rng(rows * 7 + in_f)
+    x = r.standard_normal(rows * in_f).astype(np.float32)
+    w = r.uniform(-1, 1, out_f * in_f).astype(np.float32) / np.float32(np.sqrt(in_f))
+    b = r.uniform(-0.1, 0.1, out_f).astype(np.float32) if bias else None
+    want = port.linear(x, w, b, rows, in_f, out_f)
+    got = backend.linear_forward(x, w, b, rows, in_f, out_f)
+    assert_close(got, want, f"linear {rows}x{in_f}x{out_f}")
+
+
+def test_linear_reference_known_answer(backend):
+    # Tests/test_layers_all_types.cpp:71-100
+    w = np.array([1, 2, 0, 1, -1, 0], np.float32)
+    b = np.array([0, 1, 0], np.float32)
+    got = backend.linear_forward(np.array([1, 2], np.float32), w, b, 1, 2, 3)
+    np.testing.assert_allclose(got, [5, 3, -1], atol=1e-6)
+
+
+@pytest.mark.parametrize("act", [abi.ELT_GELU, abi.ELT_SILU, abi.ELT_RELU])
+@pytest.mark.parametrize("rows", [8, 200])
+def test_linear_fused_activation(backend, act, rows):
+    r = rng(act + rows)
+    in_f, out_f = 192, 320
+    x = r.standard_normal(rows * in_f).astype(np.float32)
+    w = (r.standard_normal(out_f * in_f) / np.sqrt(in_f)).astype(np.float32)
+    b = r.uniform(-0.1, 0.1, out_f).astype(np.float32)
+    want = port.eltwise(act, port.linear(x, w, b, rows, in_f, out_f))
+    got = backend.linear_forward(x, w, b, rows, in_f, out_f, activation=act)
+    assert_close(got, want, f"linear+act{act}")
+
+
+def test_linear_bf16_weight_mode(backend):
+    # weights already representable in bf16: the two-MMA mode must meet the same tolerance
+    r = rng(5)
+    rows, in_f, out_f = 260, 768, 384
+    x = r.standard_normal(rows * in_f).astype(np.float32)
+    w = (r.standard_normal(out_f * in_f) * 0.02).astype(np.float32)
+    w = (w.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)  # truncate to bf16
+    want = port.linear(x, w, None, rows, in_f, out_f)
+    got = backend.linear_forward(x, w, None, rows, in_f, out_f, precision=abi.PREC_BF16W)
+    assert_close(got, want, "linear bf16-weight mode")
+
+
+@pytest.mark.parametrize("M,K,N", [(2, 3, 2), (40, 64, 192), (130, 70, 33), (256, 256, 768)])
+def test_matmul(backend, M, K, N):
+    r = rng(M + K + N)
+    a = r.standard_normal(M * K).astype(np.float32)
+    b = (r.standard_normal(K * N) / np.sqrt(K)).astype(np.float32)
+    assert_close(backend.matmul(a, b, M, K, N), port.matmul(a, b, M, K, N), f"matmul {M}x{K}x{N}")
+
+
+def test_matmul_reference_known_answer(backend):
+    # Tests/test_layers_all_types.cpp:473-506: [[1,2,3],[4,5,6]] x [[7,8],[9,10],[11,12]]
+    got = backend.matmul(np.arange(1, 7, dtype=np.float32), np.arange(7, 13, dtype=np.float32), 2, 3, 2)
+    np.testing.assert_allclose(got, [58, 64, 139, 154], rtol=1e-6)
+
+
+@pytest.mark.parametrize("batch,seq,E,heads,causal", [
+    (1, 40, 64, 4, 0), (1, 40, 64, 4, 1),     # head_dim 16 -> row kernel
+    (2, 128, 256, 4, 0),                      # config-1 attention shape (head_dim 64)
+    (2, 200, 128, 2, 1),                      # ragged seq, causal, head_dim 64
+    (1, 96, 128, 4, 1),                       # head_dim 32
+    (1, 70, 256, 2, 0),                       # head_dim 128
+    (1, 64, 512, 1, 0),                       # single head, head_dim 512 (UNet mid-block shape class)
+])
+def test_attention(backend, batch, seq, E, heads, causal):
+    r = rng(seq + E + heads + causal)
+    x = r.standard_normal(batch * seq * E).astype(np.float32)
+    w = (r.standard_normal(4 * E * E) / np.sqrt(E)).astype(np.float32)
+    want = np.concatenate([port.attention(x[i * seq * E:(i + 1) * seq * E], w, seq, E, heads, causal) for i in range(batch)])
+    got = backend.attention(x, w, batch, seq, E, heads, causal)
+    assert_close(got, want, f"attention b{batch} s{seq} E{E} h{heads} c{causal}")
+
+
+def test_attention_identity_weights(backend):
+    # hand-checkable: Wq=Wk=0 makes every score 0 -> uniform attention -> each output row is the mean
+    # of V rows (all rows for non-causal); Wv = Wout = I.
+    seq, E = 5, 8
+    w = np.zeros(4 * E * E, np.float32)
+    wqkv = w[:3 * E * E].reshape(E, 3 * E)
+    wqkv[:, 2 * E:] = np.eye(E)
+    w[3 * E * E:] = np.eye(E).ravel()
+    x = rng(1).standard_normal(seq * E).astype(np.float32)
+    got = backend.attention(x, w, 1, seq, E, 2, 0).reshape(seq, E)
+    want = np.tile(x.reshape(seq, E).mean(0), (seq, 1))
+    assert_close(got, want, "attention identity")
+
+
+@pytest.mark.parametrize("batch,ic,oc,h,w,k,s,p,relu", [
+    (1, 1, 1, 2, 2, 1, 1, 0, 0),      # the reference's Conv2d test (test_layers_all_types.cpp:105-133)
+    (2, 5, 13, 11, 9, 3, 1, 1, 0),
+    (1, 3, 64, 32, 32, 7, 2, 3, 0),   # stem shape class
+    (2, 16, 24, 14, 14, 3, 1, 1, 1),
+    (1, 64, 128, 28, 28, 3, 1, 1, 0),
+    (1, 32, 48, 10, 10, 1, 1, 0, 0),  # 1x1 skip conv
+])
+def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
+    r = rng(ic * oc + h)
+    x = r.random(batch * ic * h * w).astype(np.float32)
+    wt = (r.standard_normal(oc * ic * k * k) * np.sqrt(2.0 / (ic * k * k))).astype(np.float32)
+    if (ic, oc, k) == (1, 1, 1):
+        x = np.array([1, 2, 3, 4], np.float32)
+        wt = np.array([2.0], np.float32)
+    per = ic * h * w
+    want = np.concatenate([port.conv2d(x[i * per:(i + 1) * per], wt, ic, oc, h, w, k, s, p, relu) for i in range(batch)])
+    got = backend.conv2d(x, wt, batch, ic, oc, h, w, k, s, p, relu)
+    assert_close(got, want, f"conv {ic}->{oc} k{k} s{s}")
+    if (ic, oc, k) == (1, 1, 1):
+        np.testing.assert_allclose(got, [2, 4, 6, 8], atol=1e-6)
+
+
+@pytest.mark.parametrize("rows,n", [(4, 300), (3, 768), (2, 32768), (1, 40000), (9, 5)])
+def test_layernorm(backend, rows, n):
+    r = rng(n)
+    x = (r.standard_normal(rows * n) * 2 + 0.5).astype(np.float32)
+    g, b = r.standard_normal(n).astype(np.float32), r.standard_normal(n).astype(np.float32)
+    assert_close(backend.layernorm(x, g, b, rows, n), port.layernorm(x, g, b, rows, n, 1e-5), f"layernorm {rows}x{n}")
+    assert_close(backend.layernorm(x, None, None, rows, n), port.layernorm(x, None, None, rows, n, 1e-5), "layernorm no affine")
+
+
+@pytest.mark.parametrize("batch,n,ng", [(2, 1200, 700), (1, 16384, 16384), (3, 50000, 50000), (2, 786432, 786432)])
+def test_rmsnorm(backend, batch, n, ng):
+    r = rng(n)
+    x = r.standard_normal(batch * n).astype(np.float32)
+    g = r.standard_normal(ng).astype(np.float32)
+    want = np.concatenate([port.rmsnorm(x[i * n:(i + 1) * n], g, 1e-5) for i in range(batch)])
+    assert_close(backend.rmsnorm(x, g, batch, n), want, f"rmsnorm {batch}x{n}")
+
+
+def test_rmsnorm_reference_known_answer(backend):
+    # Tests/test_layers_all_types.cpp:306-323: x = [3, 4], gamma = 1 -> x / sqrt(12.5 + eps)
+    got = backend.rmsnorm(np.array([3, 4], np.float32), np.ones(2, np.float32), 1, 2, 1e-5)
+    rms = np.sqrt(np.float32(12.5) + np.float32(1e-5))
+    np.testing.assert_allclose(got, [3 / rms, 4 / rms], rtol=1e-6)
+
+
+@pytest.mark.parametrize("batch,ch,h,w,groups,act", [
+    (1, 4, 2, 2, 2, -1), (2, 16, 9, 9, 4, -1), (2, 64, 28, 28, 32, abi.ELT_SILU), (1, 256, 56, 56, 32, abi.ELT_SILU),
+])
+def test_groupnorm(backend, batch, ch, h, w, groups, act):
+    r = rng(ch + h)
+    per = ch * h * w
+    x = (r.standard_normal(batch * per) * 1.5 + 0.3).astype(np.float32)
+    g, b = r.standard_normal(ch).astype(np.float32), r.standard_normal(ch).astype(np.float32)
+    want = np.concatenate([port.groupnorm(x[i * per:(i + 1) * per], g, b, ch, h, w, groups, 1e-5) for i in range(batch)])
+    if act >= 0:
+        want = port.eltwise(act, want)
+    assert_close(backend.groupnorm(x, g, b, batch, ch, h, w, groups, 1e-5, act), want, f"groupnorm C{ch} {h}x{w}")
+
+
+@pytest.mark.parametrize("batch,n,log", [(3, 7, False), (2, 1200, True), (2, 32000, False), (1, 70000, False), (1, 70000, True)])
+def test_softmax(backend, batch, n, log):
+    x = (rng(n).standard_normal(batch * n) * 3).astype(np.float32)
+    want = np.concatenate([port.softmax(x[i * n:(i + 1) * n], log) for i in range(batch)])
+    assert_close(backend.softmax(x, batch, n, log), want, f"softmax {batch}x{n} log={log}")
+
+
+@pytest.mark.parametrize("op", [abi.ELT_GELU, abi.ELT_SILU, abi.ELT_RELU, abi.ELT_TANH, abi.ELT_SIGMOID])
+def test_activations(backend, op):
+    x = np.concatenate([(rng(op).standard_normal(4099) * 4).astype(np.float32), np.array([0, -0.0, 1, -1, 20, -20, 88, -88], np.float32)])
+    assert_close(backend.eltwise(op, x), port.eltwise(op, x), f"activation {op}", abs_tol=1e-6, rel_tol=1e-5)
+
+
+def test_add_multiply_bitexact(backend):
+    r = rng(9)
+    a, b = r.standard_normal(3 * 1000).astype(np.float32), r.standard_normal(3 * 1000).astype(np.float32)
+    assert np.array_equal(backend.eltwise(abi.ELT_ADD, a, b, batch=3), a + b)
+    assert np.array_equal(backend.eltwise(abi.ELT_MULTIPLY, a, b, batch=3), a * b)
+    # `i % small_n` broadcast per sample (LayerOps.hpp:190-197) and scalar broadcast
+    small = r.standard_normal(3 * 250).astype(np.float32)
+    want = (a.reshape(3, 4, 250) + small.reshape(3, 1, 250)).ravel()
+    assert np.array_equal(backend.eltwise(abi.ELT_ADD, a, small, batch=3), want)
+    assert np.array_equal(backend.eltwise(abi.ELT_ADD, a[:1000], np.array([2.5], np.float32)), a[:1000] + np.float32(2.5))
+    with pytest.raises(backend.MimirB200Error):
+        backend.eltwise(abi.ELT_ADD, a[:1000], a[:333])  # "Add: input sizes must match or be broadcastable"
+    with pytest.raises(backend.MimirB200Error):
+        backend.eltwise(abi.ELT_MULTIPLY, a[:1000], a[:500])
+
+
+def test_embedding_bitexact(backend):
+    r = rng(3)
+    vocab, dim = 50, 24
+    table = r.standard_normal(vocab * dim).astype(np.float32)
+    ids = np.array([0, 3, 49, 50, -1, 7.4, 7.5, 8.5, 2.5, -0.4], np.float32)  # padding, out of range, llround ties
+    want = port.embedding(ids, table, vocab, dim, 0)
+    assert np.array_equal(backend.embedding(ids, table, vocab, dim, 0), want)
+    # int ids, padding_idx -> zero row (Tests/test_runtime_embedding_int_inputs.cpp:44-74)
+    iids = np.array([1, 0, 2, 49, 77], np.int32)
+    got = backend.embedding(iids, table, vocab, dim, 0).reshape(5, dim)
+    assert np.array_equal(got[0], table.reshape(vocab, dim)[1]) and not got[1].any() and not got[4].any()
+    # odd dim (scalar path), no padding index
+    table3 = r.standard_normal(10 * 3).astype(np.float32)
+    assert np.array_equal(backend.embedding(np.array([9, 0], np.float32), table3, 10, 3, -1), port.embedding([9, 0], table3, 10, 3, -1))
+
+
+def test_data_movement_bitexact(backend):
+    r = rng(4)
+    x = r.standard_normal(2 * 3 * 4 * 5).astype(np.float32)
+    want = np.concatenate([port.upsample_nearest(x[i * 60:(i + 1) * 60], 3, 4, 5, 2, 3) for i in range(2)])
+    assert np.array_equal(backend.upsample_nearest(x, 2, 3, 4, 5, 2, 3), want)
+    for dims in ([2, 0, 1], [0, 2, 1], [1, 0, 2]):
+        want = np.concatenate([port.permute(x[i * 60:(i + 1) * 60], [3, 4, 5], dims) for i in range(2)])
+        assert np.array_equal(backend.permute(x, [3, 4, 5], dims, batch=2), want)
+    with pytest.raises(backend.MimirB200Error):
+        backend.permute(x[:60], [3, 4, 5], [0, 0, 1])
+
+
+def test_pools(backend):
+    r = rng(6)
+    x = r.standard_normal(2 * 7 * 12).astype(np.float32)
+    want = np.concatenate([port.token_mean_pool(x[i * 84:(i + 1) * 84], 7, 12) for i in range(2)])
+    assert_close(backend.token_mean_pool(x, 2, 7, 12), want, "token mean pool", abs_tol=1e-6, rel_tol=1e-6)
+    want = np.concatenate([port.global_avgpool(x[i * 84:(i + 1) * 84], 3, 4, 7) for i in range(2)])
+    assert_close(backend.global_avgpool(x, 2, 3, 4, 7), want, "global avgpool", abs_tol=1e-6, rel_tol=1e-5)
