@@ -1,0 +1,202 @@
+"""Whole-graph parity through the model C ABI (create / upload_weights / plan / forward) against the
+CPU oracle walking the same descriptors, plus planner behaviour (budget refusal, name routing)."""
+import json
+
+import numpy as np
+import pytest
+
+from conftest import assert_close
+from mimir_framework_b200 import abi, configs
+from mimir_framework_b200.abi import make_desc
+from oracle import port, ref
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_batch(descs, weights, inputs, batch):
+    outs = []
+    for s in range(batch):
+        one = {k: (a if bc else a.reshape(batch, -1)[s]) for k, (a, bc) in inputs.items()}
+        outs.append(port.run_graph(descs, weights, one))
+    return np.stack(outs)
+
+
+def gpu_batch(backend, descs, weights, inputs, batch, out_n, precision=abi.PREC_BF16X2):
+    m = backend.GraphModel(descs, precision)
+    for i, w in enumerate(weights):
+        m.upload_weights(i, w)
+    spec = {k: ((a.size if bc else a.size // batch), bc) for k, (a, bc) in inputs.items()}
+    m.plan(spec, batch)
+    out = m.forward(inputs, batch, out_n)
+    m.close()
+    return out
+
+
+@pytest.mark.parametrize("rows,k", [(300, 256), (1024, 512)])
+def test_linear_gelu_stack(backend, rows, k):
+    """Configuration 2 at reduced size: activation fused into the GEMM epilogue, hi/lo planes handed
+    from one GEMM to the next."""
+    descs = configs.linear_gelu_stack(rows, k)
+    weights = configs.linear_gelu_stack_weights(k)
+    x = configs.linear_gelu_stack_input(rows, k)
+    want = port.run_graph(descs, weights, {"x": x.ravel()})
+    got = gpu_batch(backend, descs, weights, {"x": (x.ravel(), False)}, 1, rows * k)
+    assert_close(got, want, f"linear+gelu stack {rows}x{k}")
+    if ref.available():
+        m = ref.RefModel(descs)
+        for i, w in enumerate(weights):
+            if w is not None:
+                m.set_weights(i, w)
+        assert_close(got, m.forward({"x": x.ravel()}), "linear+gelu stack vs compiled reference")
+
+
+def test_linear_gelu_stack_full_k_rows_subset(backend):
+    """K = N = 4096 like the headline configuration, 2048 rows; the oracle is run on a seeded subset
+    of rows (rows are independent)."""
+    rows, k = 2048, 4096
+    descs = configs.linear_gelu_stack(rows, k)
+    weights = configs.linear_gelu_stack_weights(k)
+    x = configs.linear_gelu_stack_input(rows, k)
+    got = gpu_batch(backend, descs, weights, {"x": (x.ravel(), False)}, 1, rows * k).reshape(rows, k)
+    pick = np.sort(np.random.default_rng(0).choice(rows, 48, replace=False))
+    sub = configs.linear_gelu_stack(len(pick), k)
+    want = port.run_graph(sub, weights, {"x": x[pick].ravel()}).reshape(len(pick), k)
+    assert_close(got[pick], want, "linear+gelu stack K=4096")
+    err = np.abs(got[pick] - want)
+    bound = 1e-4 + 1e-3 * np.abs(want)
+    assert float((err / bound).max()) < 0.8, f"margin to the tolerance too thin: {float((err / bound).max()):.2f}"
+
+
+def test_transformer_encoder_registry_graph(backend):
+    """Configuration 1: the registry transformer graph (small width so the oracle is quick), batch 3,
+    ids with padding (id 0) and out-of-range entries, mag/mod broadcast inputs."""
+    cfg = dict(seq_len=32, d_model=64, vocab_size=500, num_layers=2, num_heads=4, mlp_hidden=96, output_dim=40)
+    descs = configs.transformer_encoder(**cfg)
+    weights = configs.seeded_weights(descs, seed=1, std=0.05)
+    r = np.random.default_rng(0)
+    batch = 3
+    ids = r.integers(0, 500, (batch, 32)).astype(np.float32)
+    ids[0, 3] = 0
+    ids[1, 5] = 777
+    mag = (r.standard_normal(64) * 0.02).astype(np.float32)
+    mod = (r.standard_normal(64) * 0.02).astype(np.float32)
+    inputs = {"x": (ids.ravel(), False), "mag": (mag, True), "mod": (mod, True)}
+    want = oracle_batch(descs, weights, inputs, batch)
+    got = gpu_batch(backend, descs, weights, inputs, batch, 40)
+    assert_close(got, want, "transformer encoder graph")
+    if ref.available():
+        # the same graph built by the reference's own registry must give the same descriptors
+        m = ref.RefModel(registry="transformer", cfg_json=json.dumps(dict(cfg, causal=False)))
+        rd = m.layer_descs()
+        assert [d.type for d in rd] == [d.type for d in descs]
+        assert [int(d.params_count) for d in rd] == [int(d.params_count) for d in descs]
+        for i, w in enumerate(weights):
+            if w is not None:
+                m.set_weights(i, w)
+        want_ref = np.stack([m.forward({"x": ids[s], "mag": mag, "mod": mod}) for s in range(batch)])
+        assert_close(got, want_ref, "transformer encoder graph vs compiled reference")
+
+
+def test_named_routing_and_missing_input(backend):
+    # Tests/test_layers_named_routing.cpp:14-51: a+b -> sum, sum*c -> x; a missing input is an error
+    descs = [make_desc("add", "Add", inputs=["a", "b"], output="sum"), make_desc("mul", "Multiply", inputs=["sum", "c"], output="x")]
+    a, b, c = (np.array(v, np.float32) for v in ([1, 2, 3], [10, 20, 30], [2, 2, 2]))
+    got = gpu_batch(backend, descs, [None, None], {"a": (a, False), "b": (b, False), "c": (c, False)}, 1, 3)
+    assert np.array_equal(got.ravel(), (a + b) * c)
+    m = backend.GraphModel(descs)
+    with pytest.raises(backend.MimirB200Error, match="Missing input tensor"):
+        m.plan({"a": (3, False), "b": (3, False)}, 1)
+    m.close()
+
+
+def test_unsupported_layer_type_is_an_error_not_a_fallback(backend):
+    with pytest.raises(backend.MimirB200Error) as e:
+        backend.GraphModel([make_desc("l", "LSTM")])
+    assert e.value.status == abi.E_UNSUPPORTED
+
+
+def test_budget_refusal_happens_at_plan_time(backend):
+    # Tests/test_memory_guard.cpp:6-29 for the device arena: a plan above the limit is refused
+    # before anything is launched, and the guard's counters are unchanged afterwards.
+    descs = configs.linear_gelu_stack(4096, 256)
+    m = backend.GraphModel(descs)
+    for i, w in enumerate(configs.linear_gelu_stack_weights(256)):
+        m.upload_weights(i, w)
+    before = backend.guard_stats()
+    launches = backend.stats()["kernels_launched"]
+    backend.check(backend.lib().mimir_b200_guard_set_limit(before["current"] + (1 << 20)))
+    try:
+        with pytest.raises(backend.MimirB200Error) as e:
+            m.plan({"x": (4096 * 256, False)}, 1)
+        assert e.value.status == abi.E_OOM_BUDGET
+        assert backend.stats()["kernels_launched"] == launches
+        assert backend.guard_stats()["current"] == before["current"]
+    finally:
+        backend.check(backend.lib().mimir_b200_guard_set_limit(before["limit"]))
+    m.plan({"x": (4096 * 256, False)}, 1)  # fits again
+    m.close()
+
+
+def test_arena_reuses_memory_after_last_consumer(backend):
+    # a long chain of same-sized activations must not need one buffer per layer
+    n, depth = 1 << 16, 24
+    descs = []
+    prev = "x"
+    for i in range(depth):
+        out = "x" if i == depth - 1 else f"t{i}"
+        descs.append(make_desc(f"r{i}", "ReLU" if i % 2 else "Tanh", inputs=[prev], output=out))
+        prev = out
+    m = backend.GraphModel(descs)
+    peak = m.plan({"x": (n, False)}, 4)
+    assert peak <= 3 * 4 * n * 4 + 4096, peak
+    x = np.random.default_rng(0).standard_normal((4, n)).astype(np.float32)
+    got = m.forward({"x": (x.ravel(), False)}, 4, n)
+    want = x.copy()
+    for i in range(depth):
+        want = np.maximum(want, 0) if i % 2 else np.tanh(want)
+    assert_close(got, want, "relu/tanh chain", abs_tol=1e-6, rel_tol=1e-5)
+    m.close()
+
+
+def test_conv_groupnorm_silu_residual_block(backend):
+    """One block of configuration 4: Conv3x3 -> GroupNorm(32) -> SiLU -> Add(skip 1x1 conv)."""
+    ic, oc, hw, batch = 64, 128, 12, 2
+    descs = [
+        make_desc("conv", "Conv2d", inputs=["x"], output="c", in_channels=ic, out_channels=oc, input_height=hw, input_width=hw,
+                  kernel=3, stride=1, padding=1, params_count=oc * ic * 9),
+        make_desc("gn", "GroupNorm", inputs=["c"], output="g", in_channels=oc, input_height=hw, input_width=hw, num_groups=32,
+                  params_count=2 * oc),
+        make_desc("act", "SiLU", inputs=["g"], output="a"),
+        make_desc("skip", "Conv2d", inputs=["__input__"], output="s", in_channels=ic, out_channels=oc, input_height=hw,
+                  input_width=hw, kernel=1, stride=1, padding=0, params_count=oc * ic),
+        make_desc("add", "Add", inputs=["a", "s"], output="x"),
+    ]
+    r = np.random.default_rng(2)
+    weights = [(r.standard_normal(oc * ic * 9) * np.sqrt(2 / (ic * 9))).astype(np.float32),
+               np.concatenate([np.ones(oc), np.zeros(oc)]).astype(np.float32), None,
+               (r.standard_normal(oc * ic) * np.sqrt(2 / ic)).astype(np.float32), None]
+    x = r.random((batch, ic * hw * hw)).astype(np.float32)
+    inputs = {"x": (x.ravel(), False)}
+    assert_close(gpu_batch(backend, descs, weights, inputs, batch, oc * hw * hw), oracle_batch(descs, weights, inputs, batch), "conv block")
+
+
+def test_decoder_block_bf16_weights(backend):
+    """One block of configuration 3 at reduced size: RMSNorm (whole-tensor) -> causal attention ->
+    Add -> RMSNorm -> Linear -> GELU -> Linear -> Add, weights pre-rounded to bf16, BF16W precision."""
+    S, E, H, F = 64, 128, 2, 256
+    descs = [
+        make_desc("n1", "RMSNorm", inputs=["x"], output="h1", params_count=S * E),
+        make_desc("attn", "MultiHeadAttention", inputs=["h1"], output="a", seq_len=S, embed_dim=E, num_heads=H, causal=1, params_count=4 * E * E),
+        make_desc("add1", "Add", inputs=["__input__", "a"], output="r1"),
+        make_desc("n2", "RMSNorm", inputs=["r1"], output="h2", params_count=S * E),
+        make_desc("fc1", "Linear", inputs=["h2"], output="f1", in_features=E, out_features=F, seq_len=S, params_count=E * F + F),
+        make_desc("gelu", "GELU", inputs=["f1"], output="f1a"),
+        make_desc("fc2", "Linear", inputs=["f1a"], output="f2", in_features=F, out_features=E, seq_len=S, params_count=F * E + E),
+        make_desc("add2", "Add", inputs=["r1", "f2"], output="x"),
+    ]
+    weights = configs.seeded_weights(descs, seed=1, std=0.05, bf16=True)
+    x = np.random.default_rng(0).standard_normal((2, S * E)).astype(np.float32)
+    inputs = {"x": (x.ravel(), False)}
+    want = oracle_batch(descs, weights, inputs, 2)
+    assert_close(gpu_batch(backend, descs, weights, inputs, 2, S * E, precision=abi.PREC_BF16W), want, "decoder block bf16 weights")
+    assert_close(gpu_batch(backend, descs, weights, inputs, 2, S * E), want, "decoder block split weights")
