@@ -244,6 +244,19 @@ int mimir_b200_dev_layernorm(const float* x, const float* gamma, const float* be
                              long long rows, int n, float eps, void* stream);
 int mimir_b200_dev_rmsnorm(const float* x, const float* gamma, long long n_gamma, float* y,
                            int batch, long long n, float eps, void* stream);
+/* RMSNorm with device pointers that allocates nothing, for callers that cannot call cudaMalloc:
+ * a step of a latency-critical serving loop (an allocation synchronises the device), a process
+ * that has given all free device memory to its own pool, a plugin whose host forbids allocation.
+ * This entry point has no counterpart in the reference.  Same arithmetic as
+ * mimir_b200_dev_rmsnorm's long-row path (per-chunk sums of squares, then normalise), but the
+ * partial sums live in a fixed 64 KB array inside the library (held on every GPU that loads it).
+ * Limit: batch * ceil(n / 8192) <= 16384 and batch <= 65535, else E_INVALID.  It neither needs nor
+ * calls mimir_b200_init.  The first call on each device looks up the array's device address, so
+ * make that first call outside any stream capture.  All calls share the array: calls that may
+ * overlap on the GPU (different streams, or threads) race on it; calls on one stream are safe, and
+ * nothing needs clearing between calls. */
+int mimir_b200_dev_rmsnorm_noalloc(const float* x, const float* gamma, long long n_gamma, float* y,
+                                   int batch, long long n, float eps, void* stream);
 int mimir_b200_dev_groupnorm(const float* x, const float* gamma, const float* beta, float* y,
                              int batch, int channels, int h, int w, int groups, float eps, int act,
                              void* stream);

@@ -444,4 +444,67 @@ int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softm
   return MIMIR_B200_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm for callers that must not allocate
+// ---------------------------------------------------------------------------------------------
+// The chunked RMSNorm above keeps its per-chunk partial sums in a buffer obtained from cudaMalloc.
+// Some callers cannot afford that: code running between the launches of a latency-critical
+// serving loop (cudaMalloc synchronises the device), code that has handed all free device memory
+// to its own pool, and plugins whose host forbids them to allocate.  For them the same two kernels
+// run with the partial sums in this fixed array instead.  Every GPU that loads the library carries
+// these 64 KB until the process exits.
+namespace {
+
+constexpr int NOALLOC_MAX_PARTIALS = 16384;  // floats; batch * ceil(n / 8192) must not exceed it
+static __device__ __align__(256) float g_rms_noalloc_scratch[NOALLOC_MAX_PARTIALS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+std::mutex g_noalloc_mu;
+float* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device
+
+// `g_rms_noalloc_scratch` in host code is only a handle for the runtime, not something a kernel may
+// dereference; the address kernels can use comes from cudaGetSymbolAddress, asked once per device
+// while that device is current.
+int noalloc_scratch_for_current_device(float** out) {
+  int dev = -1;
+  MB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fail(MIMIR_B200_E_UNSUPPORTED, "rmsnorm_noalloc: device index %d not supported", dev);
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_addr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_rms_noalloc_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(MIMIR_B200_E_CUDA, "rmsnorm_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+    g_noalloc_addr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_addr[dev];
+  return MIMIR_B200_OK;
+}
+
+}  // namespace
 }  // namespace mb
+
+extern "C" int mimir_b200_dev_rmsnorm_noalloc(const float* x, const float* gamma, long long n_gamma, float* y, int batch,
+                                              long long n, float eps, void* stream) {
+  using namespace mb;
+  if (!x || !y || batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "rmsnorm_noalloc: empty input");
+  const long long chunks = (n + CHUNK - 1) / CHUNK;
+  if (batch > 65535 || chunks * batch > NOALLOC_MAX_PARTIALS)
+    return fail(MIMIR_B200_E_INVALID,
+                "rmsnorm_noalloc: batch %d x %lld elements needs %lld partial sums, the fixed scratch holds %d "
+                "(batch * ceil(n / %d) <= %d, batch <= 65535)",
+                batch, n, chunks * batch, NOALLOC_MAX_PARTIALS, CHUNK, NOALLOC_MAX_PARTIALS);
+  float* part = nullptr;
+  MB_TRY(noalloc_scratch_for_current_device(&part));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const float* g = (gamma && n_gamma > 0) ? gamma : nullptr;
+  dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(batch));
+  // every partial that pass 2 reads is written by pass 1 of the same call: nothing has to be cleared
+  rms_chunk_stats_kernel<<<grid, 256, 0, st>>>(x, part, n, static_cast<int>(chunks), CHUNK);
+  MB_CUDA(cudaGetLastError());
+  rms_chunk_apply_kernel<<<grid, 256, 0, st>>>(x, g, g ? n_gamma : 0, y, part, n, static_cast<int>(chunks), CHUNK, eps);
+  MB_CUDA(cudaGetLastError());
+  count_launch(2);
+  return MIMIR_B200_OK;
+}

@@ -58,6 +58,7 @@ _SIGS = {
     "mimir_b200_profile_read": [_P, _P],
     "mimir_b200_dev_layernorm": [_P, _P, _P, _P, C.c_longlong, C.c_int, C.c_float, _P],
     "mimir_b200_dev_rmsnorm": [_P, _P, C.c_longlong, _P, C.c_int, C.c_longlong, C.c_float, _P],
+    "mimir_b200_dev_rmsnorm_noalloc": [_P, _P, C.c_longlong, _P, C.c_int, C.c_longlong, C.c_float, _P],
     "mimir_b200_dev_groupnorm": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, _P],
     "mimir_b200_dev_softmax": [_P, _P, C.c_int, C.c_longlong, C.c_int, _P],
     "mimir_b200_dev_eltwise": [C.c_int, _P, _P, _P, C.c_int, C.c_longlong, C.c_longlong, _P],

@@ -1,0 +1,62 @@
+"""The allocation-free RMSNorm entry point, called through the C ABI.
+
+Some users of this library cannot allocate device memory at the point where they need an op: a
+serving loop between latency-critical launches (cudaMalloc synchronises the device), a process whose
+own pool already owns all free HBM, a plugin whose host forbids allocation.
+``mimir_b200_dev_rmsnorm_noalloc`` serves them with a fixed scratch array inside the library.  This
+file checks it against the regular entry point (``mimir_b200_dev_rmsnorm``, which takes its scratch
+from cudaMalloc) on two consecutive calls with different data, and checks the size limit.  It is
+named so that pytest collects it last.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_rmsnorm_noalloc_matches_regular_entry_point_twice():
+    import torch
+
+    from mimir_framework_b200 import abi, runtime as rt
+
+    lib = rt.lib()
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    batch, n = 3, 100000  # 13 chunks per row: the long-row path that needs scratch
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    gamma = torch.randn(n, device="cuda", generator=gen)
+    results = []
+    xs = []
+    for call in range(2):
+        # the caller owns inputs and outputs; the entry point under test allocates nothing
+        x = torch.randn(batch, n, device="cuda", generator=gen) * (1.0 + 3.0 * call)
+        y = torch.full((batch, n), float("nan"), device="cuda")
+        rt.check(lib.mimir_b200_dev_rmsnorm_noalloc(x.data_ptr(), gamma.data_ptr(), n, y.data_ptr(), batch, n, 1e-5, stream))
+        torch.cuda.synchronize()
+        xs.append(x)
+        results.append(y)
+    rt.init(0, 0)  # the regular entry point needs the context (idempotent when already initialised)
+    for call in range(2):
+        want = torch.empty_like(xs[call])
+        rt.check(lib.mimir_b200_dev_rmsnorm(xs[call].data_ptr(), gamma.data_ptr(), n, want.data_ptr(), batch, n, 1e-5, stream))
+        torch.cuda.synchronize()
+        got, ref = results[call].cpu().numpy(), want.cpu().numpy()
+        assert np.all(np.isfinite(got)), f"call {call}: non-finite output"
+        err = np.abs(got - ref)
+        assert np.all(err <= 1e-4 + 1e-3 * np.abs(ref)), f"call {call}: max err {err.max():.3e}"
+        # same kernels, same partial sums, same order: identical
+        assert np.array_equal(got, ref), f"call {call}: differs from the regular entry point"
+
+
+def test_rmsnorm_noalloc_rejects_sizes_beyond_its_scratch():
+    import torch
+
+    from mimir_framework_b200 import abi, runtime as rt
+
+    lib = rt.lib()
+    x = torch.zeros(16, device="cuda")
+    # 3 rows of 2**26 elements would need 3 * 8192 = 24576 partial sums > 16384: refused before any launch
+    status = lib.mimir_b200_dev_rmsnorm_noalloc(x.data_ptr(), None, 0, x.data_ptr(), 3, 1 << 26, 1e-5, None)
+    assert status == abi.E_INVALID
+    msg = lib.mimir_b200_last_error().decode()
+    assert "16384" in msg and "scratch" in msg, msg
