@@ -144,3 +144,23 @@ def load() -> C.CDLL:
     _lib = C.CDLL(path)
     _lib.mimir_b200_last_error.restype = C.c_char_p
     return _lib
+
+
+_SCALAR_FIELDS = [n for n, _ in MimirLayerDesc._fields_ if n not in ("name", "type", "inputs", "n_inputs", "output", "n_dims", "shape", "permute_dims")]
+
+
+def desc_to_dict(d: MimirLayerDesc) -> dict:
+    """JSON-friendly form of a descriptor (used by the golden fixtures)."""
+    out = {"name": (d.name or b"").decode(), "type": (d.type or b"").decode(),
+           "inputs": [d.inputs[i].decode() for i in range(d.n_inputs)], "output": (d.output or b"x").decode() or "x",
+           "shape": [int(d.shape[i]) for i in range(d.n_dims)], "permute_dims": [int(d.permute_dims[i]) for i in range(d.n_dims)]}
+    for f in _SCALAR_FIELDS:
+        v = getattr(d, f)
+        out[f] = float(v) if f == "eps" else int(v)
+    return out
+
+
+def desc_from_dict(j: dict) -> MimirLayerDesc:
+    kw = {f: j[f] for f in _SCALAR_FIELDS if f in j}
+    return make_desc(j["name"], j["type"], inputs=j.get("inputs", []), output=j.get("output", "x"), shape=j.get("shape", []),
+                     permute_dims=j.get("permute_dims", []), **kw)

@@ -1,0 +1,119 @@
+"""Generates the golden vectors under tests/golden/ by running the REFERENCE's own CPU code.
+
+    python tests/golden/make_golden.py          # needs oracle/_ref/libmimir_ref.so (make -C oracle ref)
+
+Each case is a small layer graph (descriptors as JSON), seeded weights and inputs, and the output of
+the compiled reference (`Model::forwardPassNamed`, training = false) on them.  The fixtures pin the
+plain-C oracle (CPU test) and the CUDA backend (GPU test) to the reference's actual behaviour; the
+tests never need the reference itself.
+"""
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from mimir_framework_b200 import configs  # noqa: E402
+from mimir_framework_b200.abi import desc_to_dict, make_desc  # noqa: E402
+from oracle import ref  # noqa: E402
+
+
+def cases():
+    r = np.random.default_rng(2024)
+    f = lambda *s, scale=1.0: (r.standard_normal(s) * scale).astype(np.float32)  # noqa: E731
+    out = []
+
+    def add(name, descs, weights, inputs):
+        out.append((name, descs, weights, inputs))
+
+    w = r.uniform(-0.2, 0.2, 50 * 29 + 29).astype(np.float32)
+    add("linear_seq", [make_desc("l", "Linear", in_features=50, out_features=29, seq_len=37, params_count=w.size)], [w], {"x": f(37 * 50)})
+    add("linear_vec", [make_desc("l", "Linear", in_features=50, out_features=29, params_count=w.size)], [w], {"x": f(50)})
+    add("linear_implicit_in_nobias", [make_desc("l", "Linear", out_features=7, use_bias=0, params_count=7 * 33)], [f(7 * 33, scale=0.3)], {"x": f(33)})
+    E, S = 32, 24
+    wa = f(4 * E * E, scale=0.15)
+    for causal in (0, 1):
+        add(f"attention_causal{causal}", [make_desc("a", "MultiHeadAttention", embed_dim=E, seq_len=S, num_heads=4, causal=causal, params_count=wa.size)], [wa], {"x": f(S * E)})
+    add("self_attention_1head", [make_desc("a", "SelfAttention", embed_dim=E, seq_len=S, num_heads=1, params_count=wa.size)], [wa], {"x": f(S * E)})
+    ic, oc, h = 5, 13, 11
+    add("conv3x3_p1", [make_desc("c", "Conv2d", in_channels=ic, out_channels=oc, input_height=h, input_width=h, kernel=3, stride=1, padding=1, params_count=oc * ic * 9)], [f(oc * ic * 9, scale=0.2)], {"x": r.random(ic * h * h).astype(np.float32)})
+    add("conv7x7_s2_p3_relu", [make_desc("c", "Conv2d", in_channels=ic, out_channels=oc, input_height=h, input_width=h, kernel=7, stride=2, padding=3, activation=1, params_count=oc * ic * 49)], [f(oc * ic * 49, scale=0.1)], {"x": r.random(ic * h * h).astype(np.float32)})
+    add("conv1x1_rect", [make_desc("c", "Conv2d", in_channels=4, out_channels=6, input_height=5, input_width=9, kernel=1, stride=1, padding=0, params_count=24)], [f(24)], {"x": f(4 * 5 * 9)})
+    n = 96
+    add("layernorm_groups", [make_desc("n", "LayerNorm", in_features=n, params_count=2 * n)], [f(2 * n)], {"x": f(5 * n, scale=2.0) + 0.5})
+    add("layernorm_whole", [make_desc("n", "LayerNorm", params_count=2 * 5 * n)], [f(10 * n)], {"x": f(5 * n)})
+    add("layernorm_no_affine", [make_desc("n", "LayerNorm", in_features=n, affine=0)], [None], {"x": f(3 * n)})
+    add("rmsnorm_partial_gamma", [make_desc("n", "RMSNorm", params_count=100)], [f(100)], {"x": f(300)})
+    C = 16
+    add("groupnorm", [make_desc("n", "GroupNorm", in_channels=C, input_height=7, input_width=9, num_groups=4, params_count=2 * C)], [f(2 * C)], {"x": f(C * 63, scale=1.5) + 0.3})
+    for t in ("Softmax", "LogSoftmax", "GELU", "SiLU", "ReLU", "Tanh", "Sigmoid"):
+        add(t.lower(), [make_desc("n", t)], [None], {"x": f(257, scale=3.0)})
+    add("add_broadcast", [make_desc("n", "Add", inputs=["x", "b"])], [None], {"x": f(6 * 40), "b": f(40)})
+    add("add_scalar", [make_desc("n", "Add", inputs=["x", "b"])], [None], {"x": f(33), "b": f(1)})
+    add("multiply", [make_desc("n", "Multiply", inputs=["x", "b"])], [None], {"x": f(33), "b": f(33)})
+    add("embedding_pad_oob_round", [make_desc("e", "Embedding", vocab_size=50, embed_dim=8, padding_idx=0, params_count=400)], [f(400)], {"x": np.array([0, 3, 49, 50, -1, 7.4, 7.5, 8.5, 2.5], np.float32)})
+    add("upsample_nearest", [make_desc("u", "UpsampleNearest", in_channels=3, out_h=4, out_w=5, scale_h=2, scale_w=3)], [None], {"x": f(60)})
+    add("permute_201", [make_desc("p", "Permute", shape=[3, 4, 5], permute_dims=[2, 0, 1])], [None], {"x": f(60)})
+    add("concat3", [make_desc("c", "Concat", inputs=["x", "y", "z"])], [None], {"x": f(2), "y": f(1), "z": f(2)})
+    add("token_mean_pool", [make_desc("t", "TokenMeanPool", seq_len=7, embed_dim=12)], [None], {"x": f(84)})
+    add("global_avgpool", [make_desc("g", "GlobalAvgPool2d", in_channels=3, input_height=4, input_width=7)], [None], {"x": f(84)})
+    d = configs.linear_gelu_stack(16, 64)
+    add("linear_gelu_stack_16x64", d, configs.linear_gelu_stack_weights(64), {"x": configs.linear_gelu_stack_input(16, 64).ravel()})
+    return out
+
+
+def transformer_case():
+    """The registry transformer at a small width, built by the reference's own ModelArchitectures::create;
+    mag / mod are the Encoder's defaults as the reference computes them."""
+    cfg = dict(seq_len=8, d_model=16, vocab_size=50, num_layers=1, num_heads=2, mlp_hidden=24, output_dim=8, causal=False)
+    m = ref.RefModel(registry="transformer", cfg_json=json.dumps(cfg))
+    descs = m.layer_descs()
+    ours = configs.transformer_encoder(**cfg)
+    assert [desc_to_dict(a) for a in descs] == [desc_to_dict(b) for b in ours], "registry graph differs from configs.transformer_encoder"
+    weights = configs.seeded_weights(ours, seed=1, std=0.1)
+    for i, w in enumerate(weights):
+        if w is not None:
+            m.set_weights(i, w)
+    mag, mod = m.mag_mod()
+    ids = np.array([5, 0, 49, 17, 3, 3, 21, 8], np.float32)
+    y = m.forward({"x": ids, "mag": mag, "mod": mod})
+    return "transformer_registry_tiny", ours, weights, {"x": ids, "mag": mag, "mod": mod}, y
+
+
+def main():
+    index = []
+    arrays = {}
+    for name, descs, weights, inputs in cases():
+        m = ref.RefModel(descs)
+        for i, w in enumerate(weights):
+            if w is not None:
+                m.set_weights(i, w)
+        y = m.forward(inputs)
+        m.close()
+        index.append(_store(arrays, name, descs, weights, inputs, y))
+    name, descs, weights, inputs, y = transformer_case()
+    index.append(_store(arrays, name, descs, weights, inputs, y))
+    np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **arrays)
+    with open(os.path.join(HERE, "reference_vectors.json"), "w") as fh:
+        json.dump({"generator": "tests/golden/make_golden.py", "source": "compiled reference (oracle/_ref), forwardPassNamed(training=false)",
+                   "cases": index}, fh, indent=1)
+    print(f"wrote {len(index)} cases, {sum(a.nbytes for a in arrays.values())} bytes of arrays")
+
+
+def _store(arrays, name, descs, weights, inputs, y):
+    for i, w in enumerate(weights):
+        if w is not None:
+            arrays[f"{name}/w{i}"] = np.asarray(w, np.float32)
+    for k, v in inputs.items():
+        arrays[f"{name}/in/{k}"] = np.asarray(v, np.float32)
+    arrays[f"{name}/out"] = np.asarray(y, np.float32)
+    return {"name": name, "layers": [desc_to_dict(d) for d in descs], "inputs": list(inputs.keys()),
+            "weights": [w is not None for w in weights]}
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,71 @@
+"""Pins the plain-C oracle (oracle/mimir_oracle.c through oracle/port.py) before it is trusted:
+  1. against every known-answer test the reference's own test-suite holds for the path;
+  2. against golden vectors produced by the compiled reference (tests/golden/make_golden.py);
+  3. where the compiled reference is present, that it still reproduces the committed vectors.
+CPU only."""
+import numpy as np
+import pytest
+
+from golden_cases import layernorm_property_case, load_golden, reference_kats
+from oracle import port, ref
+
+GOLDEN = load_golden()
+KATS = reference_kats()
+# integer / index / pure data-movement cases must be bit-exact
+BITEXACT = {"embedding_pad_oob_round", "upsample_nearest", "permute_201", "concat3", "relu", "add_broadcast", "add_scalar", "multiply"}
+
+
+@pytest.mark.parametrize("case", KATS, ids=[k[0] for k in KATS])
+def test_port_reproduces_reference_known_answers(case):
+    name, descs, weights, inputs, want, atol = case
+    got = port.run_graph(descs, weights, inputs)
+    assert got.shape == want.shape
+    np.testing.assert_allclose(got, want, atol=atol, rtol=0)
+
+
+def test_port_layernorm_mean_variance_property():
+    descs, weights, inputs = layernorm_property_case()
+    out = port.run_graph(descs, weights, inputs)
+    assert abs(out.mean()) < 1e-5 and abs(out.var() - 1.0) < 1e-4
+
+
+@pytest.mark.parametrize("case", GOLDEN, ids=[g[0] for g in GOLDEN])
+def test_port_matches_golden_vectors(case):
+    name, descs, weights, inputs, want = case
+    got = port.run_graph(descs, weights, inputs)
+    assert got.shape == want.shape
+    if name in BITEXACT:
+        assert np.array_equal(got, want), name
+    else:
+        # the restatement sums in a slightly different order than the AVX2/OpenMP build: a few ulp
+        np.testing.assert_allclose(got, want, atol=5e-6, rtol=2e-5, err_msg=name)
+
+
+def test_port_error_behaviour():
+    from mimir_framework_b200.abi import make_desc
+    x = np.ones(10, np.float32)
+    with pytest.raises(RuntimeError, match="Missing input tensor"):
+        port.run_graph([make_desc("a", "Add", inputs=["x", "nope"])], [None], {"x": x})
+    with pytest.raises(RuntimeError):  # "Add: input sizes must match or be broadcastable"
+        port.run_graph([make_desc("a", "Add", inputs=["x", "b"])], [None], {"x": x, "b": np.ones(3, np.float32)})
+
+
+@pytest.mark.skipif(not ref.available(), reason="compiled reference (oracle/_ref) not built here")
+@pytest.mark.parametrize("case", GOLDEN[:12] + GOLDEN[-2:], ids=[g[0] for g in GOLDEN[:12] + GOLDEN[-2:]])
+def test_compiled_reference_reproduces_committed_vectors(case):
+    name, descs, weights, inputs, want = case
+    m = ref.RefModel(descs)
+    for i, w in enumerate(weights):
+        if w is not None:
+            m.set_weights(i, w)
+    assert np.array_equal(m.forward(inputs), want), name
+
+
+@pytest.mark.skipif(not ref.available(), reason="compiled reference (oracle/_ref) not built here")
+def test_compiled_reference_passes_its_own_known_answers():
+    for name, descs, weights, inputs, want, atol in KATS:
+        m = ref.RefModel(descs)
+        for i, w in enumerate(weights):
+            if w is not None:
+                m.set_weights(i, w)
+        np.testing.assert_allclose(m.forward(inputs), want, atol=max(atol, 1e-7), rtol=0, err_msg=name)
