@@ -203,6 +203,11 @@ int mimir_b200_model_create(const MimirLayerDesc* layers, int n_layers, MimirB20
 int mimir_b200_model_destroy(MimirB200ModelHandle m);
 /* Sets the GEMM operand precision for this model (before upload_weights). */
 int mimir_b200_model_set_precision(MimirB200ModelHandle m, int precision);
+/* Cuts the batch of mimir_b200_model_forward (host pointers) into `micro_batches` pieces whose
+ * host->device copy, layer loop and device->host copy overlap on three streams over two arena
+ * buffers.  Takes effect at the next plan; the planned batch must be a multiple.  The reference has
+ * no counterpart (it has no device boundary on its default path). */
+int mimir_b200_model_set_pipeline(MimirB200ModelHandle m, int micro_batches);
 /* Copies one layer's flat fp32 weight block (layout = the reference's, Layer::getWeights()).  The
  * host pointer is not kept (it may move: DynamicTensorAllocator.hpp:171-200).  Call again after
  * the weights change. */

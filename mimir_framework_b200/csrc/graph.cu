@@ -170,6 +170,13 @@ struct MimirB200Model {
   uint64_t flops = 0, hbm_bytes = 0;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   float last_ms = 0.f;
+  // Host-pointer forwards can be pipelined: the batch is cut into `pipeline` micro-batches that
+  // flow through copy-in / compute / copy-out streams over two arena buffers.
+  int pipeline = 1;
+  int planned_micro = 0;
+  uint8_t* arena2 = nullptr;
+  cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_d2h = nullptr;
+  std::vector<cudaEvent_t> ev_h2d, ev_comp, ev_d2h;
 };
 
 namespace mb {
@@ -196,7 +203,7 @@ int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
   int ap, wp;
   precision_planes(m->precision, &ap, &wp);
   if (L.lt == LT::Linear) {
-    if (linear_uses_skinny(L.rows_ps * m->planned_batch, m->precision)) return MIMIR_B200_OK;
+    if (linear_uses_skinny(L.rows_ps * m->planned_micro, m->precision)) return MIMIR_B200_OK;
     if (L.w_split && L.w_split_k == L.in_f) return MIMIR_B200_OK;
     if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
     L.w_split_bytes = split_bytes(L.out_f, L.in_f, wp);
@@ -386,6 +393,10 @@ size_t splitv_bytes(const TensorV& t, int batch) { return split_bytes(static_cas
 
 int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, int batch) {
   if (batch <= 0) return fail(MIMIR_B200_E_INVALID, "plan: batch must be positive");
+  if (batch % m->pipeline != 0)
+    return fail(MIMIR_B200_E_INVALID, "plan: batch %d is not a multiple of the %d pipeline micro-batches", batch, m->pipeline);
+  const int full_batch = batch;
+  batch = batch / m->pipeline;  // everything below is sized for one micro-batch
   const int nl = static_cast<int>(m->layers.size());
   m->tensors.clear();
   m->input_v.clear();
@@ -566,17 +577,27 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
   const size_t need = sim.peak + 256;
   if (m->arena && m->arena_bytes < need) {
     dev_free(m->arena, m->arena_bytes);
-    m->arena = nullptr;
+    if (m->arena2) dev_free(m->arena2, m->arena_bytes);
+    m->arena = m->arena2 = nullptr;
     m->arena_bytes = 0;
   }
   if (!m->arena) {
     MB_TRY(dev_alloc(reinterpret_cast<void**>(&m->arena), need, "activation arena"));
     m->arena_bytes = need;
   }
-  m->planned_batch = batch;
+  if (m->pipeline > 1 && !m->arena2) {
+    int s2 = dev_alloc(reinterpret_cast<void**>(&m->arena2), m->arena_bytes, "activation arena (second pipeline buffer)");
+    if (s2 != MIMIR_B200_OK) return s2;
+  }
+  if (m->pipeline == 1 && m->arena2) {
+    dev_free(m->arena2, m->arena_bytes);
+    m->arena2 = nullptr;
+  }
+  m->planned_batch = full_batch;
+  m->planned_micro = batch;
   for (auto& L : m->layers) MB_TRY(prepare_weight_planes(m, L, nullptr));
   MB_CUDA(cudaStreamSynchronize(nullptr));
-  g_stats.arena_peak_bytes = need;
+  g_stats.arena_peak_bytes = need * (m->pipeline > 1 ? 2 : 1);
   return MIMIR_B200_OK;
 }
 
@@ -585,20 +606,20 @@ struct Bound {
   float* out_ptr = nullptr;
 };
 
-int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st) {
+int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, uint8_t* arena) {
   auto f32p = [&](int v) -> float* {
     const int r = root_of(m->tensors, v);
     if (r < static_cast<int>(bnd.in_ptr.size()) && bnd.in_ptr[r]) return const_cast<float*>(bnd.in_ptr[r]);
     if (r == root_of(m->tensors, m->out_v) && bnd.out_ptr) return bnd.out_ptr;
-    return reinterpret_cast<float*>(m->arena + m->tensors[r].off_f32);
+    return reinterpret_cast<float*>(arena + m->tensors[r].off_f32);
   };
-  auto splitp = [&](int v) -> __nv_bfloat16* { return reinterpret_cast<__nv_bfloat16*>(m->arena + m->tensors[v].off_split); };
+  auto splitp = [&](int v) -> __nv_bfloat16* { return reinterpret_cast<__nv_bfloat16*>(arena + m->tensors[v].off_split); };
   const int nl = static_cast<int>(m->layers.size());
   for (int li = 0; li < nl; ++li) {
     LayerRT& L = m->layers[li];
     if (L.skip || L.lt == LT::Alias) continue;
     const MimirLayerDesc& d = L.d;
-    void* ws = L.ws_bytes ? static_cast<void*>(m->arena + L.ws_off) : nullptr;
+    void* ws = L.ws_bytes ? static_cast<void*>(arena + L.ws_off) : nullptr;
     int s = MIMIR_B200_OK;
     switch (L.lt) {
       case LT::Linear: {
@@ -762,6 +783,13 @@ int mimir_b200_model_create(const MimirLayerDesc* layers, int n_layers, MimirB20
 static void destroy_model(MimirB200Model* m) {
   for (auto& L : m->layers) free_layer_weights(L, m);
   if (m->arena) dev_free(m->arena, m->arena_bytes);
+  if (m->arena2) dev_free(m->arena2, m->arena_bytes);
+  for (auto e : m->ev_h2d) cudaEventDestroy(e);
+  for (auto e : m->ev_comp) cudaEventDestroy(e);
+  for (auto e : m->ev_d2h) cudaEventDestroy(e);
+  if (m->s_h2d) cudaStreamDestroy(m->s_h2d);
+  if (m->s_comp) cudaStreamDestroy(m->s_comp);
+  if (m->s_d2h) cudaStreamDestroy(m->s_d2h);
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
   delete m;
@@ -817,7 +845,7 @@ int mimir_b200_model_plan(MimirB200ModelHandle m, const MimirNamedInput* inputs,
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (!inputs || n_inputs <= 0) return fail(MIMIR_B200_E_INVALID, "plan: no inputs declared");
   MB_TRY(plan_model(m, inputs, n_inputs, batch));
-  if (arena_peak_bytes) *arena_peak_bytes = m->arena_bytes;
+  if (arena_peak_bytes) *arena_peak_bytes = m->arena_bytes * (m->arena2 ? 2 : 1);
   g_stats.weight_bytes = m->weight_bytes;
   return MIMIR_B200_OK;
 }
@@ -827,29 +855,54 @@ int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInpu
   std::vector<int> vs;
   MB_TRY(check_inputs(m, inputs, n_inputs, batch, &vs));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const TensorV& ot = m->tensors[root_of(m->tensors, m->out_v)];
+  const int out_root = root_of(m->tensors, m->out_v);
+  const TensorV& ot = m->tensors[out_root];
   if (out_len) *out_len = static_cast<uint64_t>(ot.n);
   if (!out_dev || out_capacity < static_cast<uint64_t>(ot.n) * batch) return fail(MIMIR_B200_E_INVALID, "forward: output capacity too small");
-  Bound b;
-  b.in_ptr.assign(m->tensors.size(), nullptr);
-  for (int i = 0; i < n_inputs; ++i) {
-    const TensorV& t = m->tensors[vs[i]];
-    if (t.broadcast_input) {
-      float* slot = reinterpret_cast<float*>(m->arena + t.off_f32);
-      MB_TRY(launch_broadcast_rows(static_cast<const float*>(inputs[i].data), slot, batch, t.n, st));
-    } else {
-      b.in_ptr[vs[i]] = static_cast<const float*>(inputs[i].data);
+  const int micro = m->planned_micro;
+  // micro-batches run back to back on the caller's stream over the first arena buffer
+  for (int c = 0; c < m->pipeline; ++c) {
+    Bound b;
+    b.in_ptr.assign(m->tensors.size(), nullptr);
+    for (int i = 0; i < n_inputs; ++i) {
+      const TensorV& t = m->tensors[vs[i]];
+      if (t.broadcast_input) {
+        // staged again for every micro-batch: the planner may hand the slot to a later tensor once
+        // the input's last consumer has run
+        float* slot = reinterpret_cast<float*>(m->arena + t.off_f32);
+        MB_TRY(launch_broadcast_rows(static_cast<const float*>(inputs[i].data), slot, micro, t.n, st));
+      } else {
+        b.in_ptr[vs[i]] = static_cast<const float*>(inputs[i].data) + static_cast<size_t>(c) * micro * t.n;
+      }
+    }
+    float* out_c = out_dev + static_cast<size_t>(c) * micro * ot.n;
+    if (ot.producer >= 0) b.out_ptr = out_c;
+    MB_TRY(run_layers(m, micro, b, st, m->arena));
+    if (ot.producer < 0) {  // the graph returns one of its inputs
+      const float* src = b.in_ptr[out_root] ? b.in_ptr[out_root] : reinterpret_cast<float*>(m->arena + ot.off_f32);
+      MB_CUDA(cudaMemcpyAsync(out_c, src, static_cast<size_t>(ot.n) * micro * 4, cudaMemcpyDeviceToDevice, st));
     }
   }
-  if (ot.producer >= 0) b.out_ptr = out_dev;
-  MB_TRY(run_layers(m, batch, b, st));
-  if (ot.producer < 0) {  // graph returns one of its inputs
-    const float* src = b.in_ptr[root_of(m->tensors, m->out_v)] ? b.in_ptr[root_of(m->tensors, m->out_v)]
-                                                               : reinterpret_cast<float*>(m->arena + ot.off_f32);
-    MB_CUDA(cudaMemcpyAsync(out_dev, src, static_cast<size_t>(ot.n) * batch * 4, cudaMemcpyDeviceToDevice, st));
+  g_stats.flops_last_forward = m->flops * m->pipeline;
+  g_stats.bytes_last_forward = m->hbm_bytes * m->pipeline;
+  return MIMIR_B200_OK;
+}
+
+static int ensure_pipeline_objects(MimirB200Model* m) {
+  if (!m->s_comp) {
+    MB_CUDA(cudaStreamCreateWithFlags(&m->s_h2d, cudaStreamNonBlocking));
+    MB_CUDA(cudaStreamCreateWithFlags(&m->s_comp, cudaStreamNonBlocking));
+    MB_CUDA(cudaStreamCreateWithFlags(&m->s_d2h, cudaStreamNonBlocking));
   }
-  g_stats.flops_last_forward = m->flops;
-  g_stats.bytes_last_forward = m->hbm_bytes;
+  while (static_cast<int>(m->ev_h2d.size()) < m->pipeline) {
+    cudaEvent_t a, b, c;
+    MB_CUDA(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+    MB_CUDA(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+    MB_CUDA(cudaEventCreateWithFlags(&c, cudaEventDisableTiming));
+    m->ev_h2d.push_back(a);
+    m->ev_comp.push_back(b);
+    m->ev_d2h.push_back(c);
+  }
   return MIMIR_B200_OK;
 }
 
@@ -857,7 +910,6 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
                              uint64_t out_capacity, uint64_t* out_len) {
   std::vector<int> vs;
   MB_TRY(check_inputs(m, inputs, n_inputs, batch, &vs));
-  cudaStream_t st = nullptr;
   const TensorV& ot = m->tensors[root_of(m->tensors, m->out_v)];
   if (out_len) *out_len = static_cast<uint64_t>(ot.n);
   if (!out_host || out_capacity < static_cast<uint64_t>(ot.n) * batch) return fail(MIMIR_B200_E_INVALID, "forward: output capacity too small");
@@ -865,26 +917,56 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
     MB_CUDA(cudaEventCreate(&m->ev0));
     MB_CUDA(cudaEventCreate(&m->ev1));
   }
-  for (int i = 0; i < n_inputs; ++i) {
-    const TensorV& t = m->tensors[vs[i]];
-    float* slot = reinterpret_cast<float*>(m->arena + t.off_f32);
-    if (t.broadcast_input) {
-      MB_CUDA(cudaMemcpyAsync(slot, inputs[i].data, static_cast<size_t>(t.n) * 4, cudaMemcpyHostToDevice, st));
-      if (batch > 1) MB_TRY(launch_broadcast_rows(slot, slot + t.n, batch - 1, t.n, st));
-    } else {
-      MB_CUDA(cudaMemcpyAsync(slot, inputs[i].data, static_cast<size_t>(t.n) * batch * 4, cudaMemcpyHostToDevice, st));
+  MB_TRY(ensure_pipeline_objects(m));
+  const int micro = m->planned_micro, P = m->pipeline;
+  uint8_t* bufs[2] = {m->arena, m->arena2 ? m->arena2 : m->arena};
+  MB_CUDA(cudaEventRecord(m->ev0, m->s_comp));
+  // copy-in, compute and copy-out of consecutive micro-batches overlap; buffer c & 1 is reused by
+  // micro-batch c + 2 only after its compute (inputs) and its copy-out (output) have finished
+  for (int c = 0; c < P; ++c) {
+    uint8_t* arena = bufs[c & 1];
+    if (c >= 2) MB_CUDA(cudaStreamWaitEvent(m->s_h2d, m->ev_comp[c - 2], 0));
+    for (int i = 0; i < n_inputs; ++i) {
+      const TensorV& t = m->tensors[vs[i]];
+      float* slot = reinterpret_cast<float*>(arena + t.off_f32);
+      if (t.broadcast_input) {
+        // every micro-batch: the slot may have been reused after the input's last consumer
+        MB_CUDA(cudaMemcpyAsync(slot, inputs[i].data, static_cast<size_t>(t.n) * 4, cudaMemcpyHostToDevice, m->s_h2d));
+        if (micro > 1) MB_TRY(launch_broadcast_rows(slot, slot + t.n, micro - 1, t.n, m->s_h2d));
+      } else {
+        const float* src = static_cast<const float*>(inputs[i].data) + static_cast<size_t>(c) * micro * t.n;
+        MB_CUDA(cudaMemcpyAsync(slot, src, static_cast<size_t>(t.n) * micro * 4, cudaMemcpyHostToDevice, m->s_h2d));
+      }
     }
+    MB_CUDA(cudaEventRecord(m->ev_h2d[c], m->s_h2d));
+    MB_CUDA(cudaStreamWaitEvent(m->s_comp, m->ev_h2d[c], 0));
+    if (c >= 2) MB_CUDA(cudaStreamWaitEvent(m->s_comp, m->ev_d2h[c - 2], 0));
+    Bound b;
+    MB_TRY(run_layers(m, micro, b, m->s_comp, arena));
+    MB_CUDA(cudaEventRecord(m->ev_comp[c], m->s_comp));
+    MB_CUDA(cudaStreamWaitEvent(m->s_d2h, m->ev_comp[c], 0));
+    MB_CUDA(cudaMemcpyAsync(out_host + static_cast<size_t>(c) * micro * ot.n, arena + ot.off_f32, static_cast<size_t>(ot.n) * micro * 4,
+                            cudaMemcpyDeviceToHost, m->s_d2h));
+    MB_CUDA(cudaEventRecord(m->ev_d2h[c], m->s_d2h));
   }
-  Bound b;
-  MB_CUDA(cudaEventRecord(m->ev0, st));
-  MB_TRY(run_layers(m, batch, b, st));
-  MB_CUDA(cudaEventRecord(m->ev1, st));
-  MB_CUDA(cudaMemcpyAsync(out_host, m->arena + ot.off_f32, static_cast<size_t>(ot.n) * batch * 4, cudaMemcpyDeviceToHost, st));
-  MB_TRY(check_device_error_word(st));
+  MB_CUDA(cudaEventRecord(m->ev1, m->s_comp));
+  MB_CUDA(cudaStreamSynchronize(m->s_d2h));
+  MB_CUDA(cudaStreamSynchronize(m->s_comp));
+  MB_TRY(check_device_error_word(m->s_comp));
   cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1);
   g_stats.ms_last_forward = m->last_ms;
-  g_stats.flops_last_forward = m->flops;
-  g_stats.bytes_last_forward = m->hbm_bytes;
+  g_stats.flops_last_forward = m->flops * P;
+  g_stats.bytes_last_forward = m->hbm_bytes * P;
+  return MIMIR_B200_OK;
+}
+
+// Cuts the batch of the host-pointer forward into `micro_batches` pieces that overlap their
+// copy-in, compute and copy-out (takes effect at the next plan; batch must be a multiple).
+int mimir_b200_model_set_pipeline(MimirB200ModelHandle m, int micro_batches) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (micro_batches < 1 || micro_batches > 1024) return fail(MIMIR_B200_E_INVALID, "set_pipeline: micro_batches must be in 1..1024");
+  if (micro_batches != m->pipeline) m->planned_batch = 0;
+  m->pipeline = micro_batches;
   return MIMIR_B200_OK;
 }
 

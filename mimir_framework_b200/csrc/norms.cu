@@ -4,18 +4,19 @@
 //   RMSNorm   : LayerOpsExt::rms_norm_forward (LayerOpsExt.hpp:345-378) row = the whole sample
 //   Softmax   : LayerOps::softmax_forward    (LayerOps.hpp:325-361)  row = the whole sample
 //
-// Two shapes of kernel per op:
-//   * "row" kernels: one CTA per row, the row staged once in shared memory (<= 64 KB), statistics
-//     by warp-shuffle + shared-memory reduction, one HBM read and one HBM write per element;
-//   * "chunk" kernels for long rows: pass 1 reduces 8192-element chunks to partial statistics in a
-//     small global scratch, pass 2 combines the partials of its row and writes the result, so that
-//     a handful of very long rows (RMSNorm over a whole sample) still fills every SM.
+// Three shapes of kernel:
+//   * warp-per-row (LayerNorm rows <= 1024): the row lives in registers, shuffles only;
+//   * CTA-per-row streaming sweeps (at least one row per SM): first sweep from HBM, later sweeps from
+//     L2, one HBM read and one HBM write per element;
+//   * "chunk" kernels when there are only a few (long) rows: pass 1 reduces 8192-element chunks to
+//     partial statistics in a small global scratch, pass 2 combines the partials of its row and
+//     writes the result; rows are processed in groups that fit in L2 so that pass 2 reads from L2.
 #include "common.h"
+
 
 namespace mb {
 namespace {
 
-constexpr int ROW_CACHE_FLOATS = 16384;  // 64 KB
 constexpr int CHUNK = 8192;
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -60,13 +61,22 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 __device__ __forceinline__ float silu(float v) { return v * (1.0f / (1.0f + expf(-v))); }
 
-// Copies `len` floats global -> shared (128-bit when aligned) and returns this thread's partial sum.
+// Copies `len` floats global -> shared and returns this thread's partial sum.  128-bit loads, four
+// in flight per thread before the first shared-memory store, so that a CTA keeps ~32 KB in flight.
 __device__ __forceinline__ float stage_and_sum(const float* __restrict__ g, float* s, long long len) {
   float acc = 0.0f;
   if (((reinterpret_cast<uintptr_t>(g) & 15) == 0) && ((len & 3) == 0)) {
     const float4* g4 = reinterpret_cast<const float4*>(g);
     float4* s4 = reinterpret_cast<float4*>(s);
-    for (long long i = threadIdx.x; i < (len >> 2); i += blockDim.x) {
+    const long long n4 = len >> 2;
+    const long long step = blockDim.x;
+    long long i = threadIdx.x;
+    for (; i + 3 * step < n4; i += 4 * step) {
+      const float4 a = __ldg(g4 + i), b = __ldg(g4 + i + step), c = __ldg(g4 + i + 2 * step), d = __ldg(g4 + i + 3 * step);
+      s4[i] = a; s4[i + step] = b; s4[i + 2 * step] = c; s4[i + 3 * step] = d;
+      acc += ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w)) + ((c.x + c.y) + (c.z + c.w)) + ((d.x + d.y) + (d.z + d.w));
+    }
+    for (; i < n4; i += step) {
       const float4 v = __ldg(g4 + i);
       s4[i] = v;
       acc += (v.x + v.y) + (v.z + v.w);
@@ -95,7 +105,7 @@ struct Affine {
 __device__ __forceinline__ float finish(float xn, long long i, long long row, long long base, const Affine& a) {
   float v = xn;
   if (a.gamma != nullptr) {
-    const long long gi = a.per_channel ? (static_cast<long long>(row % a.groups) * a.cpg + i / a.hw) : i;
+    const long long gi = a.per_channel ? static_cast<long long>(static_cast<int>(row % a.groups) * a.cpg + static_cast<int>(static_cast<unsigned>(i) / static_cast<unsigned>(a.hw))) : i;
     v *= __ldg(a.gamma + gi);
     if (a.beta != nullptr) v += __ldg(a.beta + gi);
   }
@@ -104,27 +114,7 @@ __device__ __forceinline__ float finish(float xn, long long i, long long row, lo
   return v;
 }
 
-// ---- mean / variance family ------------------------------------------------------------------
-__global__ void meanvar_row_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows, int len, float eps,
-                                   Affine a) {
-  extern __shared__ __align__(16) float srow[];
-  __shared__ float red[33];
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const long long base = row * len;
-    __syncthreads();
-    const float mean = block_sum(stage_and_sum(x + base, srow, len), red) / static_cast<float>(len);
-    float acc = 0.0f;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) {
-      const float d = srow[i] - mean;
-      acc += d * d;
-    }
-    const float var = block_sum(acc, red) / static_cast<float>(len);
-    const float inv = 1.0f / sqrtf(var + eps);
-    for (int i = threadIdx.x; i < len; i += blockDim.x)
-      y[base + i] = finish((srow[i] - mean) * inv, i, row, base, a);
-  }
-}
-
+// ---- chunk kernels (mean / variance) ----------------------------------------------------------
 // pass 1: per chunk (count, mean, M2)
 __global__ void meanvar_chunk_stats_kernel(const float* __restrict__ x, float* __restrict__ part, long long len, int chunks,
                                            int chunk_len) {
@@ -150,65 +140,7 @@ __global__ void meanvar_chunk_stats_kernel(const float* __restrict__ x, float* _
   }
 }
 
-// pass 2: combine the row's partials (pairwise-update formula of Chan et al.), normalise the chunk
-__global__ void meanvar_chunk_apply_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ part,
-                                           long long len, int chunks, int chunk_len, float eps, Affine a) {
-  const long long row = blockIdx.y;
-  const int c = blockIdx.x;
-  float n = 0.0f, mean = 0.0f, m2 = 0.0f;
-  for (int j = 0; j < chunks; ++j) {
-    const float* p = part + (row * chunks + j) * 3;
-    const float nb = p[0], mb_ = p[1], m2b = p[2];
-    const float nt = n + nb;
-    const float delta = mb_ - mean;
-    mean += delta * (nb / nt);
-    m2 += m2b + delta * delta * (n * nb / nt);
-    n = nt;
-  }
-  const float inv = 1.0f / sqrtf(m2 / n + eps);
-  const long long off = static_cast<long long>(c) * chunk_len;
-  const long long cn = min(static_cast<long long>(chunk_len), len - off);
-  const long long base = row * len;
-  const float* g = x + base + off;
-  float* o = y + base + off;
-  if (((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(o)) & 15) == 0 && (cn & 3) == 0 &&
-      (!a.per_channel || (a.hw & 3) == 0) && (a.residual == nullptr || (reinterpret_cast<uintptr_t>(a.residual + base + off) & 15) == 0)) {
-    for (long long i = threadIdx.x; i < (cn >> 2); i += blockDim.x) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(g) + i);
-      const long long e = off + (i << 2);
-      float4 r;
-      r.x = finish((v.x - mean) * inv, e, row, base, a);
-      r.y = finish((v.y - mean) * inv, e + 1, row, base, a);
-      r.z = finish((v.z - mean) * inv, e + 2, row, base, a);
-      r.w = finish((v.w - mean) * inv, e + 3, row, base, a);
-      reinterpret_cast<float4*>(o)[i] = r;
-    }
-  } else {
-    for (long long i = threadIdx.x; i < cn; i += blockDim.x) o[i] = finish((__ldg(g + i) - mean) * inv, off + i, row, base, a);
-  }
-}
-
-// ---- RMS family ------------------------------------------------------------------------------
-__global__ void rms_row_kernel(const float* __restrict__ x, const float* __restrict__ gamma, long long n_gamma,
-                               float* __restrict__ y, long long rows, int len, float eps) {
-  extern __shared__ __align__(16) float srow[];
-  __shared__ float red[33];
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const long long base = row * len;
-    __syncthreads();
-    stage_and_sum(x + base, srow, len);
-    __syncthreads();
-    float acc = 0.0f;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) acc += srow[i] * srow[i];
-    const float rms = sqrtf(block_sum(acc, red) / static_cast<float>(len) + eps);
-    for (int i = threadIdx.x; i < len; i += blockDim.x) {
-      float v = srow[i] / rms;
-      if (gamma != nullptr && i < n_gamma) v *= __ldg(gamma + i);
-      y[base + i] = v;
-    }
-  }
-}
-
+// ---- chunk kernels (RMS) ---------------------------------------------------------------------
 __global__ void rms_chunk_stats_kernel(const float* __restrict__ x, float* __restrict__ part, long long len, int chunks,
                                        int chunk_len) {
   __shared__ float red[33];
@@ -218,6 +150,7 @@ __global__ void rms_chunk_stats_kernel(const float* __restrict__ x, float* __res
   const float* g = x + row * len + off;
   float acc = 0.0f;
   if ((reinterpret_cast<uintptr_t>(g) & 15) == 0 && (n & 3) == 0) {
+#pragma unroll 8
     for (long long i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
       const float4 v = __ldg(reinterpret_cast<const float4*>(g) + i);
       acc += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
@@ -260,35 +193,7 @@ __global__ void rms_chunk_apply_kernel(const float* __restrict__ x, const float*
   }
 }
 
-// ---- softmax family --------------------------------------------------------------------------
-__global__ void softmax_row_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows, int len, int log_softmax) {
-  extern __shared__ __align__(16) float srow[];
-  __shared__ float red[33];
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const long long base = row * len;
-    __syncthreads();
-    stage_and_sum(x + base, srow, len);
-    __syncthreads();
-    float m = -INFINITY;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) m = fmaxf(m, srow[i]);
-    m = block_max(m, red);
-    float acc = 0.0f;
-    for (int i = threadIdx.x; i < len; i += blockDim.x) {
-      const float e = expf(srow[i] - m);
-      acc += e;
-      if (!log_softmax) srow[i] = e;
-    }
-    const float sum = block_sum(acc, red);
-    if (log_softmax) {
-      const float ld = logf(sum);
-      for (int i = threadIdx.x; i < len; i += blockDim.x) y[base + i] = (srow[i] - m) - ld;
-    } else {
-      const float inv = 1.0f / sum;
-      for (int i = threadIdx.x; i < len; i += blockDim.x) y[base + i] = srow[i] * inv;
-    }
-  }
-}
-
+// ---- chunk kernels (softmax) -------------------------------------------------------------------
 // pass 1: per chunk (max, sum of exp(x - max))
 __global__ void softmax_chunk_stats_kernel(const float* __restrict__ x, float* __restrict__ part, long long len, int chunks,
                                            int chunk_len) {
@@ -303,7 +208,7 @@ __global__ void softmax_chunk_stats_kernel(const float* __restrict__ x, float* _
   for (long long i = threadIdx.x; i < n; i += blockDim.x) m = fmaxf(m, sch[i]);
   m = block_max(m, red);
   float acc = 0.0f;
-  for (long long i = threadIdx.x; i < n; i += blockDim.x) acc += expf(sch[i] - m);
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) acc += __expf(sch[i] - m);
   const float s = block_sum(acc, red);
   if (threadIdx.x == 0) {
     part[(row * chunks + blockIdx.x) * 2] = m;
@@ -325,8 +230,350 @@ __global__ void softmax_chunk_apply_kernel(const float* __restrict__ x, float* _
   float* o = y + row * len + off;
   for (long long i = threadIdx.x; i < cn; i += blockDim.x) {
     const float v = __ldg(g + i);
-    o[i] = log_softmax ? ((v - m) - ld) : expf(v - m) * inv;
+    o[i] = log_softmax ? ((v - m) - ld) : __expf(v - m) * inv;
   }
+}
+
+// ---- CTA-per-row streaming kernels -----------------------------------------------------------
+// For many rows of any length: one CTA owns a row and sweeps it two or three times with unrolled
+// 128-bit loads — the first sweep comes from HBM, the later ones hit L2 (a CTA re-reads what it
+// read a few hundred KB ago) — so HBM sees one read and one write per element while loads stay in
+// flight through every phase; the only barriers are the block reductions between sweeps.
+// The per-element work is kept far below the ~40 lane-operations a B200 can spend per element of
+// an 8-byte-per-element stream: fast exp2-based exponentials, channel indices advanced
+// incrementally instead of divided, gamma / beta read as 128-bit vectors.
+enum { FAM_MEANVAR = 0, FAM_RMS = 1, FAM_SOFTMAX = 2 };
+
+struct RowParams {
+  const float* x;
+  float* y;
+  long long rows;
+  long long len;
+  float eps;
+  Affine aff;            // FAM_MEANVAR
+  const float* gamma;    // FAM_RMS
+  long long n_gamma;     // FAM_RMS
+  int log_softmax;       // FAM_SOFTMAX
+};
+
+__device__ __forceinline__ float silu_fast(float v) { return v * __fdividef(1.0f, 1.0f + __expf(-v)); }
+
+template <class F>
+__device__ __forceinline__ void sweep_read(const float* __restrict__ g, long long n, bool vec, F f) {
+  if (vec) {
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    const int n4 = static_cast<int>(n >> 2);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = __ldg(g4 + i);
+      f(v.x); f(v.y); f(v.z); f(v.w);
+    }
+  } else {
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) f(__ldg(g + i));
+  }
+}
+
+template <class F>
+__device__ __forceinline__ void sweep_write(const float* __restrict__ g, float* __restrict__ o, long long n, bool vec, F f) {
+  if (vec) {
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    float4* o4 = reinterpret_cast<float4*>(o);
+    const int n4 = static_cast<int>(n >> 2);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = __ldcs(g4 + i);
+      const long long e = static_cast<long long>(i) << 2;
+      float4 r;
+      r.x = f(v.x, e); r.y = f(v.y, e + 1); r.z = f(v.z, e + 2); r.w = f(v.w, e + 3);
+      __stcs(o4 + i, r);
+    }
+  } else {
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) o[i] = f(__ldg(g + i), i);
+  }
+}
+
+// normalise + affine + activation + residual for one row, vector paths for the two affine layouts
+// (g, o point at element `off` of the row; n elements are written)
+__device__ __forceinline__ void meanvar_write_row(const float* __restrict__ g, float* __restrict__ o, long long n, bool vec,
+                                                  float mean, float inv, long long row, long long base, const Affine& a,
+                                                  long long off = 0) {
+  const float* gam = (a.gamma && !a.per_channel) ? a.gamma + off : a.gamma;
+  const float* bet = (a.beta && !a.per_channel) ? a.beta + off : a.beta;
+  const float* res = a.residual ? a.residual + base + off : nullptr;
+  const bool silu_on = a.act == MIMIR_B200_ELT_SILU;
+  if (vec && !a.per_channel && (gam == nullptr || ((reinterpret_cast<uintptr_t>(gam) & 15) == 0 &&
+                                                   (bet == nullptr || (reinterpret_cast<uintptr_t>(bet) & 15) == 0)))) {
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    float4* o4 = reinterpret_cast<float4*>(o);
+    const int n4 = static_cast<int>(n >> 2);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = __ldcs(g4 + i);
+      float4 r = make_float4((v.x - mean) * inv, (v.y - mean) * inv, (v.z - mean) * inv, (v.w - mean) * inv);
+      if (gam != nullptr) {
+        const float4 w = __ldg(reinterpret_cast<const float4*>(gam) + i);
+        r.x *= w.x; r.y *= w.y; r.z *= w.z; r.w *= w.w;
+        if (bet != nullptr) {
+          const float4 b = __ldg(reinterpret_cast<const float4*>(bet) + i);
+          r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+        }
+      }
+      if (silu_on) { r.x = silu_fast(r.x); r.y = silu_fast(r.y); r.z = silu_fast(r.z); r.w = silu_fast(r.w); }
+      if (res != nullptr) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(res) + i);
+        r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w;
+      }
+      __stcs(o4 + i, r);
+    }
+    return;
+  }
+  if (vec && a.per_channel && (a.hw & 3) == 0) {
+    // the four elements of a vector share a channel; the channel advances incrementally
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    float4* o4 = reinterpret_cast<float4*>(o);
+    const int n4 = static_cast<int>(n >> 2);
+    const unsigned hw = static_cast<unsigned>(a.hw), estep = blockDim.x * 4u;
+    unsigned c = static_cast<unsigned>((off + threadIdx.x * 4u) / hw), rem = static_cast<unsigned>((off + threadIdx.x * 4u) % hw);
+    const int c0 = static_cast<int>(row % a.groups) * a.cpg;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = __ldcs(g4 + i);
+      float sc = inv, sh = -mean * inv;
+      if (gam != nullptr) {
+        const float w = __ldg(gam + c0 + c);
+        sc *= w;
+        sh *= w;
+        if (bet != nullptr) sh += __ldg(bet + c0 + c);
+      }
+      float4 r = make_float4(fmaf(v.x, sc, sh), fmaf(v.y, sc, sh), fmaf(v.z, sc, sh), fmaf(v.w, sc, sh));
+      if (silu_on) { r.x = silu_fast(r.x); r.y = silu_fast(r.y); r.z = silu_fast(r.z); r.w = silu_fast(r.w); }
+      if (res != nullptr) {
+        const float4 q = __ldg(reinterpret_cast<const float4*>(res) + i);
+        r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w;
+      }
+      __stcs(o4 + i, r);
+      rem += estep;
+      while (rem >= hw) { rem -= hw; ++c; }
+    }
+    return;
+  }
+  for (long long i = threadIdx.x; i < n; i += blockDim.x) o[i] = finish((__ldg(g + i) - mean) * inv, off + i, row, base, a);
+}
+
+// pass 2 of the mean/variance chunk path: combine the row's partials (pairwise-update formula of
+// Chan et al.), normalise the chunk
+__global__ void meanvar_chunk_apply_kernel(const float* __restrict__ x, float* __restrict__ y, const float* __restrict__ part,
+                                           long long len, int chunks, int chunk_len, float eps, Affine a, long long row0) {
+  const long long row = blockIdx.y;
+  const int c = blockIdx.x;
+  float n = 0.0f, mean = 0.0f, m2 = 0.0f;
+  for (int j = 0; j < chunks; ++j) {
+    const float* p = part + (row * chunks + j) * 3;
+    const float nb = p[0], mb_ = p[1], m2b = p[2];
+    const float nt = n + nb;
+    const float delta = mb_ - mean;
+    mean += delta * (nb / nt);
+    m2 += m2b + delta * delta * (n * nb / nt);
+    n = nt;
+  }
+  const float inv = 1.0f / sqrtf(m2 / n + eps);
+  const long long off = static_cast<long long>(c) * chunk_len;
+  const long long cn = min(static_cast<long long>(chunk_len), len - off);
+  const long long base = (row + row0) * len;  // x, y were advanced by row0 rows; gamma / residual are absolute
+  const float* g = x + row * len + off;
+  float* o = y + row * len + off;
+  Affine al = a;
+  if (al.residual) al.residual = a.residual;  // indexed with the absolute base below
+  const bool vec = (((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(o)) & 15) == 0) && ((cn & 3) == 0) &&
+                   (a.residual == nullptr || (reinterpret_cast<uintptr_t>(a.residual + base + off) & 15) == 0) &&
+                   (a.per_channel || a.gamma == nullptr || (off & 3) == 0);
+  meanvar_write_row(g, o, cn, vec, mean, inv, row + row0, base, al, off);
+}
+
+template <int FAM, int THREADS>
+__global__ void __launch_bounds__(THREADS, (THREADS <= 512) ? 2 : 1) sweep_row_kernel(RowParams p) {
+  __shared__ float red[33];
+  const long long n = p.len;
+  for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const long long base = row * n;
+    const float* g = p.x + base;
+    float* o = p.y + base;
+    bool vec = (((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(o)) & 15) == 0) && ((n & 3) == 0) &&
+               (n < (1LL << 31));
+    if (FAM == FAM_MEANVAR) {
+      if (p.aff.residual != nullptr && (reinterpret_cast<uintptr_t>(p.aff.residual + base) & 15) != 0) vec = false;
+      float s = 0.0f;
+      sweep_read(g, n, vec, [&](float v) { s += v; });
+      const float mean = block_sum(s, red) / static_cast<float>(n);
+      float q = 0.0f;
+      sweep_read(g, n, vec, [&](float v) { const float d = v - mean; q = fmaf(d, d, q); });
+      const float inv = 1.0f / sqrtf(block_sum(q, red) / static_cast<float>(n) + p.eps);
+      meanvar_write_row(g, o, n, vec, mean, inv, row, base, p.aff);
+    } else if (FAM == FAM_RMS) {
+      float q = 0.0f;
+      sweep_read(g, n, vec, [&](float v) { q = fmaf(v, v, q); });
+      const float rinv = 1.0f / sqrtf(block_sum(q, red) / static_cast<float>(n) + p.eps);
+      const float* gam = p.gamma;
+      const long long ng = p.n_gamma;
+      if (vec && (gam == nullptr || (ng >= n && (reinterpret_cast<uintptr_t>(gam) & 15) == 0))) {
+        const float4* g4 = reinterpret_cast<const float4*>(g);
+        float4* o4 = reinterpret_cast<float4*>(o);
+        const int n4 = static_cast<int>(n >> 2);
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+          float4 v = __ldcs(g4 + i);
+          v.x *= rinv; v.y *= rinv; v.z *= rinv; v.w *= rinv;
+          if (gam != nullptr) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(gam) + i);
+            v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
+          }
+          __stcs(o4 + i, v);
+        }
+      } else {
+        sweep_write(g, o, n, false, [&](float v, long long e) {
+          float r = v * rinv;
+          if (gam != nullptr && e < ng) r *= __ldg(gam + e);
+          return r;
+        });
+      }
+    } else {
+      // online (max, sum of exp) per thread without a data-dependent branch
+      // running (max, sum of exp) per thread, rescaled once per 128-bit vector: 5 exponentials per 4
+      // elements keep the transcendental unit below the memory time
+      float m = -3.0e38f, sum = 0.0f;
+      if (vec) {
+        const float4* g4 = reinterpret_cast<const float4*>(g);
+        const int n4 = static_cast<int>(n >> 2);
+#pragma unroll 4
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+          const float4 v = __ldg(g4 + i);
+          const float mn = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+          sum = sum * __expf(m - mn) + ((__expf(v.x - mn) + __expf(v.y - mn)) + (__expf(v.z - mn) + __expf(v.w - mn)));
+          m = mn;
+        }
+      } else {
+        sweep_read(g, n, false, [&](float v) {
+          const float mn = fmaxf(m, v);
+          sum = sum * __expf(m - mn) + __expf(v - mn);
+          m = mn;
+        });
+      }
+      const float gm = block_max(m, red);
+      const float tot = block_sum(sum * __expf(m - gm), red);
+      if (p.log_softmax) {
+        const float ld = logf(tot);
+        sweep_write(g, o, n, vec, [&](float v, long long) { return (v - gm) - ld; });
+      } else {
+        const float inv = 1.0f / tot;
+        sweep_write(g, o, n, vec, [&](float v, long long) { return __expf(v - gm) * inv; });
+      }
+    }
+  }
+}
+
+template <int FAM>
+int launch_sweep_rows(const RowParams& p, cudaStream_t st) {
+  const long long sms = ctx().sm_count;
+  // rows in flight are re-read from L2: keep their footprint well inside it
+  const bool big = p.len * 4 * 2 * sms > (40ll << 20);
+  if (big) {
+    long long blocks = sms < p.rows ? sms : p.rows;
+    sweep_row_kernel<FAM, 1024><<<static_cast<int>(blocks), 1024, 0, st>>>(p);
+  } else {
+    int threads = 512;
+    while (threads > 128 && static_cast<long long>(threads) * 16 > p.len) threads >>= 1;  // >= 4 vectors per thread
+    long long blocks = sms * (1024 / threads) * 2;
+    if (blocks > p.rows) blocks = p.rows;
+    sweep_row_kernel<FAM, 512><<<static_cast<int>(blocks), threads, 0, st>>>(p);
+  }
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+// The sweeps pay off when every SM has rows of its own and the rows in flight (re-read from L2)
+// stay well inside L2; otherwise the chunk path (L2-sized row groups) is used.
+// MIMIR_B200_NORM_PATH=sweep|chunk overrides the choice (measurement aid).
+inline bool use_sweeps(long long rows, long long len) {
+  const char* v = getenv("MIMIR_B200_NORM_PATH");
+  if (v && v[0] == 's') return true;
+  if (v && v[0] == 'c') return false;
+  const long long sms = ctx().sm_count;
+  const long long in_flight = (rows < sms ? rows : sms) * len * 4;
+  return rows >= sms && in_flight <= (72ll << 20);
+}
+
+// ---- warp-per-row LayerNorm for short rows (token-wise norms): no block barrier at all --------
+constexpr int WARP_ROW_MAX = 1024;  // floats
+
+template <int NV>  // 128-bit vectors per lane
+__global__ void __launch_bounds__(256) meanvar_warp_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows,
+                                                           int len, float eps, Affine a) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int n4 = len >> 2;  // len is a multiple of 4 on this path
+  const bool gvec = a.gamma == nullptr || ((reinterpret_cast<uintptr_t>(a.gamma) & 15) == 0 &&
+                                           (a.beta == nullptr || (reinterpret_cast<uintptr_t>(a.beta) & 15) == 0));
+  for (long long row = warp; row < rows; row += nwarps) {
+    const long long base = row * len;
+    const float4* g4 = reinterpret_cast<const float4*>(x + base);
+    float4 v[NV];
+    float s = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      v[j] = (i < n4) ? __ldg(g4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    const float mean = warp_sum(s) / static_cast<float>(len);
+    float q = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if (lane + 32 * j < n4) {
+        const float dx = v[j].x - mean, dy = v[j].y - mean, dz = v[j].z - mean, dw = v[j].w - mean;
+        q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+      }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(q) / static_cast<float>(len) + eps);
+    float4* o4 = reinterpret_cast<float4*>(y + base);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = lane + 32 * j;
+      if (i < n4) {
+        float4 r;
+        if (!a.per_channel && gvec && a.act < 0 && a.residual == nullptr) {
+          r = make_float4((v[j].x - mean) * inv, (v[j].y - mean) * inv, (v[j].z - mean) * inv, (v[j].w - mean) * inv);
+          if (a.gamma != nullptr) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(a.gamma) + i);
+            r.x *= w.x; r.y *= w.y; r.z *= w.z; r.w *= w.w;
+            if (a.beta != nullptr) {
+              const float4 b = __ldg(reinterpret_cast<const float4*>(a.beta) + i);
+              r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+            }
+          }
+        } else {
+          const long long e = static_cast<long long>(i) << 2;
+          r.x = finish((v[j].x - mean) * inv, e, row, base, a);
+          r.y = finish((v[j].y - mean) * inv, e + 1, row, base, a);
+          r.z = finish((v[j].z - mean) * inv, e + 2, row, base, a);
+          r.w = finish((v[j].w - mean) * inv, e + 3, row, base, a);
+        }
+        o4[i] = r;
+      }
+    }
+  }
+}
+
+template <int NV>
+int launch_warp_rows(const float* x, float* y, long long rows, int len, float eps, const Affine& a, cudaStream_t st) {
+  long long blocks = (rows + 7) / 8;
+  const long long cap = static_cast<long long>(ctx().sm_count) * 8;
+  if (blocks > cap) blocks = cap;
+  meanvar_warp_kernel<NV><<<static_cast<int>(blocks), 256, 0, st>>>(x, y, rows, len, eps, a);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
 }
 
 // ---- scratch for the chunk kernels -------------------------------------------------------------
@@ -339,37 +586,47 @@ int norm_scratch(float** out) {
   return MIMIR_B200_OK;
 }
 
-int threads_for(long long len) { return len <= 1024 ? 128 : (len <= 4096 ? 256 : 512); }
-
-int grid_rows(long long rows) {
-  const long long cap = static_cast<long long>(ctx().sm_count) * 8;
-  return static_cast<int>(rows < cap ? rows : cap);
-}
+// Rows longer than a cluster can hold go through the two-pass chunk kernels in groups of rows whose
+// footprint stays inside L2 (so the second pass reads x from L2, not from HBM).
+constexpr long long L2_GROUP_BYTES = 64ll << 20;
 
 int meanvar_dispatch(const float* x, float* y, long long rows, long long len, float eps, const Affine& a, cudaStream_t st) {
   if (rows <= 0 || len <= 0) return fail(MIMIR_B200_E_INVALID, "norm: empty input");
-  if (len <= ROW_CACHE_FLOATS) {
-    static bool attr = false;
-    if (!attr) {
-      MB_CUDA(cudaFuncSetAttribute(meanvar_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ROW_CACHE_FLOATS * 4));
-      attr = true;
-    }
-    meanvar_row_kernel<<<grid_rows(rows), threads_for(len), static_cast<size_t>(len) * 4, st>>>(x, y, rows, static_cast<int>(len), eps, a);
-    MB_CUDA(cudaGetLastError());
-    count_launch();
-    return MIMIR_B200_OK;
+  const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0 &&
+                    (a.residual == nullptr || (reinterpret_cast<uintptr_t>(a.residual) & 15) == 0);
+  if (len <= WARP_ROW_MAX && (len & 3) == 0 && al16 && rows >= 64) {
+    const int nv = static_cast<int>((len / 4 + 31) / 32);
+    const int l = static_cast<int>(len);
+    if (nv <= 2) return launch_warp_rows<2>(x, y, rows, l, eps, a, st);
+    if (nv <= 4) return launch_warp_rows<4>(x, y, rows, l, eps, a, st);
+    if (nv <= 6) return launch_warp_rows<6>(x, y, rows, l, eps, a, st);
+    return launch_warp_rows<8>(x, y, rows, l, eps, a, st);
+  }
+  if (use_sweeps(rows, len)) {
+    RowParams p{};
+    p.x = x; p.y = y; p.rows = rows; p.len = len; p.eps = eps; p.aff = a;
+    return launch_sweep_rows<FAM_MEANVAR>(p, st);
   }
   const int chunks = static_cast<int>((len + CHUNK - 1) / CHUNK);
-  if (static_cast<size_t>(rows) * chunks * 3 * sizeof(float) > NORM_SCRATCH_BYTES || rows > 65535)
-    return fail(MIMIR_B200_E_UNSUPPORTED, "norm: %lld rows of %lld exceed the partial-statistics scratch", rows, len);
   float* part;
   MB_TRY(norm_scratch(&part));
-  dim3 grid(chunks, static_cast<unsigned>(rows));
-  meanvar_chunk_stats_kernel<<<grid, 256, CHUNK * 4, st>>>(x, part, len, chunks, CHUNK);
-  MB_CUDA(cudaGetLastError());
-  meanvar_chunk_apply_kernel<<<grid, 256, 0, st>>>(x, y, part, len, chunks, CHUNK, eps, a);
-  MB_CUDA(cudaGetLastError());
-  count_launch(2);
+  long long group = L2_GROUP_BYTES / (len * 4);
+  if (group < 1) group = 1;
+  const long long cap_rows = static_cast<long long>(NORM_SCRATCH_BYTES / (sizeof(float) * 3)) / chunks;
+  if (cap_rows < 1) return fail(MIMIR_B200_E_UNSUPPORTED, "norm: a row of %lld elements exceeds the partial-statistics scratch", len);
+  if (group > cap_rows) group = cap_rows;
+  if (group > 65535) group = 65535;
+  for (long long r0 = 0; r0 < rows; r0 += group) {
+    const long long nr = (rows - r0 < group) ? rows - r0 : group;
+    dim3 grid(chunks, static_cast<unsigned>(nr));
+    Affine ag = a;
+    // the kernels index gamma / residual by absolute row: shift the pointers, keep row numbering
+    meanvar_chunk_stats_kernel<<<grid, 256, CHUNK * 4, st>>>(x + r0 * len, part, len, chunks, CHUNK);
+    MB_CUDA(cudaGetLastError());
+    meanvar_chunk_apply_kernel<<<grid, 256, 0, st>>>(x + r0 * len, y + r0 * len, part, len, chunks, CHUNK, eps, ag, r0);
+    MB_CUDA(cudaGetLastError());
+    count_launch(2);
+  }
   return MIMIR_B200_OK;
 }
 
@@ -392,58 +649,59 @@ int launch_groupnorm(const float* x, const float* gamma, const float* beta, floa
 int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y, int batch, int64_t n, float eps,
                    cudaStream_t st) {
   if (batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "RMSNorm: empty input");
-  if (n <= ROW_CACHE_FLOATS) {
-    static bool attr = false;
-    if (!attr) {
-      MB_CUDA(cudaFuncSetAttribute(rms_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ROW_CACHE_FLOATS * 4));
-      attr = true;
-    }
-    rms_row_kernel<<<grid_rows(batch), threads_for(n), static_cast<size_t>(n) * 4, st>>>(x, gamma, n_gamma, y, batch, static_cast<int>(n), eps);
-    MB_CUDA(cudaGetLastError());
-    count_launch();
-    return MIMIR_B200_OK;
+  if (use_sweeps(batch, n)) {
+    RowParams p{};
+    p.x = x; p.y = y; p.rows = batch; p.len = n; p.eps = eps; p.gamma = gamma; p.n_gamma = gamma ? n_gamma : 0;
+    return launch_sweep_rows<FAM_RMS>(p, st);
   }
   const int chunks = static_cast<int>((n + CHUNK - 1) / CHUNK);
-  if (static_cast<size_t>(batch) * chunks * sizeof(float) > NORM_SCRATCH_BYTES || batch > 65535)
-    return fail(MIMIR_B200_E_UNSUPPORTED, "RMSNorm: input exceeds the partial-statistics scratch");
   float* part;
   MB_TRY(norm_scratch(&part));
-  dim3 grid(chunks, static_cast<unsigned>(batch));
-  rms_chunk_stats_kernel<<<grid, 256, 0, st>>>(x, part, n, chunks, CHUNK);
-  MB_CUDA(cudaGetLastError());
-  rms_chunk_apply_kernel<<<grid, 256, 0, st>>>(x, gamma, n_gamma, y, part, n, chunks, CHUNK, eps);
-  MB_CUDA(cudaGetLastError());
-  count_launch(2);
+  long long group = L2_GROUP_BYTES / (n * 4);
+  if (group < 1) group = 1;
+  const long long cap_rows = static_cast<long long>(NORM_SCRATCH_BYTES / sizeof(float)) / chunks;
+  if (cap_rows < 1) return fail(MIMIR_B200_E_UNSUPPORTED, "RMSNorm: a row of %lld elements exceeds the partial-statistics scratch", static_cast<long long>(n));
+  if (group > cap_rows) group = cap_rows;
+  if (group > 65535) group = 65535;
+  for (long long r0 = 0; r0 < batch; r0 += group) {
+    const long long nr = (batch - r0 < group) ? batch - r0 : group;
+    dim3 grid(chunks, static_cast<unsigned>(nr));
+    rms_chunk_stats_kernel<<<grid, 256, 0, st>>>(x + r0 * n, part, n, chunks, CHUNK);
+    MB_CUDA(cudaGetLastError());
+    rms_chunk_apply_kernel<<<grid, 256, 0, st>>>(x + r0 * n, gamma, gamma ? n_gamma : 0, y + r0 * n, part, n, chunks, CHUNK, eps);
+    MB_CUDA(cudaGetLastError());
+    count_launch(2);
+  }
   return MIMIR_B200_OK;
 }
 
 int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softmax, cudaStream_t st) {
   if (batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "Softmax: empty input");
-  if (n <= ROW_CACHE_FLOATS) {
-    static bool attr = false;
-    if (!attr) {
-      MB_CUDA(cudaFuncSetAttribute(softmax_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ROW_CACHE_FLOATS * 4));
-      attr = true;
-    }
-    softmax_row_kernel<<<grid_rows(batch), threads_for(n), static_cast<size_t>(n) * 4, st>>>(x, y, batch, static_cast<int>(n), log_softmax);
-    MB_CUDA(cudaGetLastError());
-    count_launch();
-    return MIMIR_B200_OK;
+  if (use_sweeps(batch, n)) {
+    RowParams p{};
+    p.x = x; p.y = y; p.rows = batch; p.len = n; p.log_softmax = log_softmax;
+    return launch_sweep_rows<FAM_SOFTMAX>(p, st);
   }
   const int chunks = static_cast<int>((n + CHUNK - 1) / CHUNK);
-  if (static_cast<size_t>(batch) * chunks * 2 * sizeof(float) > NORM_SCRATCH_BYTES || batch > 65535)
-    return fail(MIMIR_B200_E_UNSUPPORTED, "Softmax: input exceeds the partial-statistics scratch");
   float* part;
   MB_TRY(norm_scratch(&part));
-  dim3 grid(chunks, static_cast<unsigned>(batch));
-  softmax_chunk_stats_kernel<<<grid, 256, CHUNK * 4, st>>>(x, part, n, chunks, CHUNK);
-  MB_CUDA(cudaGetLastError());
-  softmax_chunk_apply_kernel<<<grid, 256, 0, st>>>(x, y, part, n, chunks, CHUNK, log_softmax);
-  MB_CUDA(cudaGetLastError());
-  count_launch(2);
+  long long group = L2_GROUP_BYTES / (n * 4);
+  if (group < 1) group = 1;
+  const long long cap_rows = static_cast<long long>(NORM_SCRATCH_BYTES / (2 * sizeof(float))) / chunks;
+  if (cap_rows < 1) return fail(MIMIR_B200_E_UNSUPPORTED, "Softmax: a row of %lld elements exceeds the partial-statistics scratch", static_cast<long long>(n));
+  if (group > cap_rows) group = cap_rows;
+  if (group > 65535) group = 65535;
+  for (long long r0 = 0; r0 < batch; r0 += group) {
+    const long long nr = (batch - r0 < group) ? batch - r0 : group;
+    dim3 grid(chunks, static_cast<unsigned>(nr));
+    softmax_chunk_stats_kernel<<<grid, 256, CHUNK * 4, st>>>(x + r0 * n, part, n, chunks, CHUNK);
+    MB_CUDA(cudaGetLastError());
+    softmax_chunk_apply_kernel<<<grid, 256, 0, st>>>(x + r0 * n, y + r0 * n, part, n, chunks, CHUNK, log_softmax);
+    MB_CUDA(cudaGetLastError());
+    count_launch(2);
+  }
   return MIMIR_B200_OK;
 }
-
 
 // ---------------------------------------------------------------------------------------------
 // RMSNorm for callers that must not allocate

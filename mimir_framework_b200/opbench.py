@@ -1,0 +1,180 @@
+"""Per-kernel and per-configuration measurements beside the headline benchmark.
+
+    python -m mimir_framework_b200.opbench [--only norms|configs] [--no-cpu]
+
+Prints one JSON line per measurement:
+  * the HBM-bound kernels (LayerNorm, RMSNorm, GroupNorm+SiLU, Softmax, GELU, Add) at the sizes the
+    configurations use, as achieved GB/s of algorithmic bytes (read + write) against the measured
+    HBM copy bandwidth;
+  * the other configurations (registry transformer encoder at batch 8, ...) as samples/s, with the
+    reference's CPU path timed on the host cores when the compiled reference is present.
+Device-resident inputs, CUDA events on the launching stream, 3 warm-up + 10 timed launches; every
+input is larger than L2 or the L2 is flushed between launches (stated per line).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from mimir_framework_b200 import abi, configs, runtime as rt  # noqa: E402
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f)["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+def time_launches(fn, warmup=3, iters=10, flush=None):
+    import torch
+
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return float(np.median(times)), times
+
+
+def bench_norms():
+    import torch
+
+    lib = rt.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    peak, src = hbm_peak()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # 256 MB > L2
+    g = torch.Generator(device="cuda").manual_seed(3)
+
+    def report(name, ms, nbytes, shape, flushed):
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        print(json.dumps({"kernel": name, "shape": shape, "ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs,
+                          "peak_gbs": peak, "frac": gbs / peak, "peak_source": src,
+                          "l2": "flushed between launches" if flushed else "input larger than L2"}), flush=True)
+
+    def run(name, shape, n_elems, call, param_elems=0):
+        x = torch.randn(n_elems, device="cuda", generator=g)
+        y = torch.empty_like(x)
+        flushed = n_elems * 4 < (300 << 20)
+        ms, _ = time_launches(lambda: rt.check(call(x, y)), flush=flush if flushed else None)
+        report(name, ms, 4 * (2 * n_elems + param_elems), shape, flushed)
+        del x, y
+
+    # LayerNorm: token-wise rows and the registry transformer's whole-vector rows
+    for rows, n in ((32768, 768), (8, 32768), (524288, 768)):
+        gam = torch.ones(n, device="cuda")
+        bet = torch.zeros(n, device="cuda")
+        run("layernorm", f"{rows}x{n}", rows * n,
+            lambda x, y: lib.mimir_b200_dev_layernorm(x.data_ptr(), gam.data_ptr(), bet.data_ptr(), y.data_ptr(), rows, n, 1e-5, st), 2 * n)
+    # RMSNorm over whole samples (decoder config: 32 x 1024*768)
+    n = 1024 * 768
+    gam = torch.ones(n, device="cuda")
+    for b in (32, 256):
+        run("rmsnorm", f"{b}x{n}", b * n, lambda x, y: lib.mimir_b200_dev_rmsnorm(x.data_ptr(), gam.data_ptr(), n, y.data_ptr(), b, n, 1e-5, st), n)
+    # GroupNorm(32) + SiLU on 64 x 256 x 112 x 112
+    C_, H = 256, 112
+    gam = torch.ones(C_, device="cuda")
+    bet = torch.zeros(C_, device="cuda")
+    run("groupnorm+silu", f"64x{C_}x{H}x{H} G32", 64 * C_ * H * H,
+        lambda x, y: lib.mimir_b200_dev_groupnorm(x.data_ptr(), gam.data_ptr(), bet.data_ptr(), y.data_ptr(), 64, C_, H, H, 32, 1e-5, abi.ELT_SILU, st))
+    # Softmax: 4096 independent samples of 32000
+    run("softmax", "4096x32000", 4096 * 32000, lambda x, y: lib.mimir_b200_dev_softmax(x.data_ptr(), y.data_ptr(), 4096, 32000, 0, st))
+    # element-wise
+    n = 1 << 28
+    run("gelu", f"{n}", n, lambda x, y: lib.mimir_b200_dev_eltwise(abi.ELT_GELU, x.data_ptr(), None, y.data_ptr(), 1, n, 0, st))
+    b = torch.randn(n, device="cuda", generator=g)
+    x = torch.randn(n, device="cuda", generator=g)
+    y = torch.empty_like(x)
+    ms, _ = time_launches(lambda: rt.check(lib.mimir_b200_dev_eltwise(abi.ELT_ADD, x.data_ptr(), b.data_ptr(), y.data_ptr(), 1, n, n, st)))
+    report("add", ms, 12 * n, f"{n}", False)
+
+
+def bench_transformer(no_cpu: bool):
+    """Configuration 1: registry transformer encoder, batch 8, fp32, ids seed 0, weights N(0, 0.02) seed 1."""
+    import torch
+
+    cfg = configs.TRANSFORMER_CFG
+    descs = configs.transformer_encoder(**cfg)
+    weights = configs.seeded_weights(descs, seed=1, std=0.02)
+    batch, S, D = 8, cfg["seq_len"], cfg["d_model"]
+    ids = np.random.default_rng(0).integers(0, cfg["vocab_size"], (batch, S)).astype(np.float32)
+    r = np.random.default_rng(2)
+    mag, mod = (r.standard_normal(D) * 0.02).astype(np.float32), (r.standard_normal(D) * 0.02).astype(np.float32)
+    want, cpu_ms, cores = None, None, None
+    if not no_cpu:
+        from oracle import ref
+        if ref.available():
+            cores = ref.set_threads(os.cpu_count() or 1)
+            m = ref.RefModel(registry="transformer", cfg_json=json.dumps(cfg))
+            for i, w in enumerate(weights):
+                if w is not None:
+                    m.set_weights(i, w)
+            mag, mod = m.mag_mod()  # the Encoder's own vectors
+            outs, ts = [], []
+            for s in range(batch):
+                y, secs = m.forward({"x": ids[s], "mag": mag, "mod": mod}, return_seconds=True)
+                outs.append(y)
+                ts.append(secs)
+            want = np.stack(outs)
+            cpu_ms = 1e3 * float(np.median(ts[1:]))
+            m.close()
+    model = rt.GraphModel(descs)
+    for i, w in enumerate(weights):
+        model.upload_weights(i, w)
+    model.plan({"x": (S, False), "mag": (D, True), "mod": (D, True)}, batch)
+    got = model.forward({"x": (ids.ravel(), False), "mag": (mag, True), "mod": (mod, True)}, batch, cfg["output_dim"])
+    parity = None
+    if want is not None:
+        err = np.abs(got - want)
+        parity = {"max_abs": float(err.max()), "outside_tolerance": int((err > 1e-4 + 1e-3 * np.abs(want)).sum()), "n": int(want.size)}
+    d_ids, d_mag, d_mod = (torch.from_numpy(a).cuda() for a in (ids, mag, mod))
+    d_out = torch.empty(batch, cfg["output_dim"], device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    spec = {"x": (d_ids.data_ptr(), S, False), "mag": (d_mag.data_ptr(), D, True), "mod": (d_mod.data_ptr(), D, True)}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    ms, _ = time_launches(lambda: model.forward_device(spec, batch, d_out.data_ptr(), d_out.numel(), st), flush=None)
+    weight_bytes = 4 * sum(int(d.params_count) for d in descs if d.type.decode() != "Embedding")
+    peak, src = hbm_peak()
+    print(json.dumps({"config": "1 transformer encoder (registry graph), batch 8, fp32", "ms_per_batch": ms,
+                      "samples_per_s": batch / (ms * 1e-3), "weight_stream_bytes": weight_bytes,
+                      "achieved_gbs": weight_bytes / (ms * 1e-3) / 1e9, "peak_gbs": peak, "frac": weight_bytes / (ms * 1e-3) / 1e9 / peak,
+                      "peak_source": src, "l2": "574 MB of weights per forward, larger than L2",
+                      "cpu_reference_ms_per_sample": cpu_ms, "cpu_reference_samples_per_s": (1e3 / cpu_ms) if cpu_ms else None,
+                      "cpu_cores": cores, "parity": parity}), flush=True)
+    model.close()
+    del flush
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="all", choices=["all", "norms", "configs"])
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rt.init(0, 0)
+    if args.only in ("all", "norms"):
+        bench_norms()
+    if args.only in ("all", "configs"):
+        bench_transformer(args.no_cpu)
+    rt.shutdown()
+
+
+if __name__ == "__main__":
+    main()

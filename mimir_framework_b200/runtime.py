@@ -47,6 +47,7 @@ _SIGS = {
     "mimir_b200_model_create": [_P, C.c_int, _P],
     "mimir_b200_model_destroy": [_P],
     "mimir_b200_model_set_precision": [_P, C.c_int],
+    "mimir_b200_model_set_pipeline": [_P, C.c_int],
     "mimir_b200_model_upload_weights": [_P, C.c_int, _P, C.c_uint64],
     "mimir_b200_model_plan": [_P, _P, C.c_int, C.c_int, _P],
     "mimir_b200_model_forward": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P],
@@ -242,12 +243,14 @@ def global_avgpool(x, batch, ch, h, w):
 class GraphModel:
     """A layer graph on the device: ``mimir_b200_model_*``."""
 
-    def __init__(self, descs, precision: int = abi.PREC_BF16X2):
+    def __init__(self, descs, precision: int = abi.PREC_BF16X2, pipeline: int = 1):
         self._descs = list(descs)
         self._arr = desc_array(self._descs)
         self._h = C.c_void_p()
         check(lib().mimir_b200_model_create(C.addressof(self._arr), len(self._descs), C.byref(self._h)))
         check(lib().mimir_b200_model_set_precision(self._h, precision))
+        if pipeline != 1:
+            check(lib().mimir_b200_model_set_pipeline(self._h, pipeline))
         self.batch = 0
         self.arena_bytes = 0
 

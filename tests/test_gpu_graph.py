@@ -200,3 +200,41 @@ def test_decoder_block_bf16_weights(backend):
     want = oracle_batch(descs, weights, inputs, 2)
     assert_close(gpu_batch(backend, descs, weights, inputs, 2, S * E, precision=abi.PREC_BF16W), want, "decoder block bf16 weights")
     assert_close(gpu_batch(backend, descs, weights, inputs, 2, S * E), want, "decoder block split weights")
+
+
+def test_pipelined_forward_equals_single_pass(backend):
+    """model_set_pipeline: micro-batches overlapped over three streams and two arena buffers must give
+    exactly the bytes of the un-pipelined forward (broadcast inputs included), for the host-pointer and
+    the device-pointer entry points."""
+    import torch
+
+    cfg = dict(seq_len=16, d_model=32, vocab_size=100, num_layers=1, num_heads=2, mlp_hidden=48, output_dim=24)
+    descs = configs.transformer_encoder(**cfg)
+    weights = configs.seeded_weights(descs, seed=1, std=0.05)
+    r = np.random.default_rng(0)
+    batch = 12
+    ids = r.integers(0, 100, (batch, 16)).astype(np.float32)
+    mag, mod = (r.standard_normal(32) * 0.02).astype(np.float32), (r.standard_normal(32) * 0.02).astype(np.float32)
+    inputs = {"x": (ids.ravel(), False), "mag": (mag, True), "mod": (mod, True)}
+    spec = {"x": (16, False), "mag": (32, True), "mod": (32, True)}
+    outs = {}
+    for pipe in (1, 3, 4, 12):
+        m = backend.GraphModel(descs, pipeline=pipe)
+        for i, w in enumerate(weights):
+            m.upload_weights(i, w)
+        m.plan(spec, batch)
+        outs[pipe] = m.forward(inputs, batch, 24).copy()
+        # device-pointer path on the same model
+        d_ids, d_mag, d_mod = (torch.from_numpy(a).cuda() for a in (ids, mag, mod))
+        d_out = torch.empty(batch, 24, device="cuda")
+        m.forward_device({"x": (d_ids.data_ptr(), 16, False), "mag": (d_mag.data_ptr(), 32, True), "mod": (d_mod.data_ptr(), 32, True)},
+                         batch, d_out.data_ptr(), batch * 24, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert np.array_equal(d_out.cpu().numpy(), outs[pipe]), f"device path differs at pipeline {pipe}"
+        m.close()
+    for pipe in (3, 4, 12):
+        assert np.array_equal(outs[pipe], outs[1]), f"pipeline {pipe} differs from the single pass"
+    m = backend.GraphModel(descs, pipeline=5)
+    with pytest.raises(backend.MimirB200Error, match="multiple"):
+        m.plan(spec, batch)
+    m.close()
