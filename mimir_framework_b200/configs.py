@@ -128,3 +128,165 @@ def round_to_bf16(a: np.ndarray) -> np.ndarray:
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
     u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
     return u.astype(np.uint32).view(np.float32)
+
+
+# ---- configuration 3: GPT-style causal decoder, prefill only -------------------------------------
+DECODER_CFG = dict(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=1024)
+
+
+def gpt_decoder(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=1024):
+    """Embedding -> layers x [RMSNorm -> MultiHeadAttention(causal) -> Add -> RMSNorm -> Linear -> GELU ->
+    Linear -> Add] -> RMSNorm -> Linear (LM head), token-wise layers (`seq_len` set) like the
+    reference's ViT / SD3.5 builders.  RMSNorm is the reference's whole-tensor form with one gamma per
+    element (`params_count = seq * d_model`)."""
+    E, S = d_model, seq
+    d = [make_desc("dec/tok_embed", "Embedding", inputs=["__input__"], output="dec/h0", vocab_size=vocab, embed_dim=E,
+                   padding_idx=-1, params_count=vocab * E)]
+    x = "dec/h0"
+    for i in range(layers):
+        b = f"dec/block{i}"
+        d += [
+            make_desc(f"{b}/norm1", "RMSNorm", inputs=[x], output=f"{b}/n1", params_count=S * E),
+            make_desc(f"{b}/attn", "MultiHeadAttention", inputs=[f"{b}/n1"], output=f"{b}/a", seq_len=S, embed_dim=E,
+                      num_heads=heads, causal=1, params_count=4 * E * E),
+            make_desc(f"{b}/add1", "Add", inputs=[x, f"{b}/a"], output=f"{b}/r1"),
+            make_desc(f"{b}/norm2", "RMSNorm", inputs=[f"{b}/r1"], output=f"{b}/n2", params_count=S * E),
+            make_desc(f"{b}/fc1", "Linear", inputs=[f"{b}/n2"], output=f"{b}/f1", in_features=E, out_features=ffn, seq_len=S,
+                      use_bias=1, params_count=E * ffn + ffn),
+            make_desc(f"{b}/gelu", "GELU", inputs=[f"{b}/f1"], output=f"{b}/f1a"),
+            make_desc(f"{b}/fc2", "Linear", inputs=[f"{b}/f1a"], output=f"{b}/f2", in_features=ffn, out_features=E, seq_len=S,
+                      use_bias=1, params_count=ffn * E + E),
+            make_desc(f"{b}/add2", "Add", inputs=[f"{b}/r1", f"{b}/f2"], output=f"{b}/r2"),
+        ]
+        x = f"{b}/r2"
+    d += [make_desc("dec/norm_f", "RMSNorm", inputs=[x], output="dec/nf", params_count=S * E),
+          make_desc("dec/lm_head", "Linear", inputs=["dec/nf"], output="x", in_features=E, out_features=vocab, seq_len=S,
+                    use_bias=0, params_count=E * vocab)]
+    return d
+
+
+def gpt_decoder_flops(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=1024):
+    """Algorithmic flops per sample; attention counted on the causal half."""
+    E, S = d_model, seq
+    per_layer = 2 * S * E * 3 * E + 2 * S * S * E + 2 * S * E * E + 2 * 2 * S * E * ffn
+    return layers * per_layer + 2 * S * E * vocab
+
+
+# ---- configuration 4: conv vision block stack ------------------------------------------------------
+def conv_stack(image=224, channels=(64, 128, 128, 256, 256), groups=32):
+    """Stem Conv 7x7 s2 p3 3->C0, then per block [Conv 3x3 s1 p1 -> GroupNorm -> SiLU -> Add residual]; where
+    the channel count changes the skip is a 1x1 conv (no bias anywhere: the reference never adds conv bias)."""
+    hw = (image + 2 * 3 - 7) // 2 + 1
+    d = [make_desc("cv/stem", "Conv2d", inputs=["x"], output="cv/s", in_channels=3, out_channels=channels[0], input_height=image,
+                   input_width=image, kernel=7, stride=2, padding=3, params_count=channels[0] * 3 * 49)]
+    x, c_in = "cv/s", channels[0]
+    for i, c_out in enumerate(channels[1:]):
+        b = f"cv/b{i}"
+        last = i == len(channels) - 2
+        d += [
+            make_desc(f"{b}/conv", "Conv2d", inputs=[x], output=f"{b}/c", in_channels=c_in, out_channels=c_out, input_height=hw,
+                      input_width=hw, kernel=3, stride=1, padding=1, params_count=c_out * c_in * 9),
+            make_desc(f"{b}/gn", "GroupNorm", inputs=[f"{b}/c"], output=f"{b}/g", in_channels=c_out, input_height=hw, input_width=hw,
+                      num_groups=groups, params_count=2 * c_out),
+            make_desc(f"{b}/act", "SiLU", inputs=[f"{b}/g"], output=f"{b}/a"),
+        ]
+        skip = x
+        if c_in != c_out:
+            d.append(make_desc(f"{b}/skip", "Conv2d", inputs=[x], output=f"{b}/s", in_channels=c_in, out_channels=c_out,
+                               input_height=hw, input_width=hw, kernel=1, stride=1, padding=0, params_count=c_out * c_in))
+            skip = f"{b}/s"
+        d.append(make_desc(f"{b}/add", "Add", inputs=[f"{b}/a", skip], output="x" if last else f"{b}/o"))
+        x, c_in = f"{b}/o", c_out
+    return d
+
+
+def conv_stack_weights(descs, seed=1):
+    """Kaiming-normal conv weights N(0, sqrt(2 / (ic k^2))), GroupNorm gamma = 1, beta = 0."""
+    r = np.random.default_rng(seed)
+    out = []
+    for d in descs:
+        t, n = d.type.decode(), int(d.params_count)
+        if t == "Conv2d":
+            fan = d.in_channels * d.kernel * d.kernel
+            out.append((r.standard_normal(n, dtype=np.float32) * np.float32(np.sqrt(2.0 / fan))).astype(np.float32))
+        elif t == "GroupNorm":
+            out.append(np.concatenate([np.ones(n // 2, np.float32), np.zeros(n - n // 2, np.float32)]))
+        else:
+            out.append(None)
+    return out
+
+
+def conv_flops(descs):
+    """Sum of 2 * oc * ic * k^2 * H_out * W_out over the Conv2d layers (per sample)."""
+    f = 0
+    for d in descs:
+        if d.type.decode() == "Conv2d":
+            oh = (d.input_height + 2 * d.padding - d.kernel) // d.stride + 1
+            ow = (d.input_width + 2 * d.padding - d.kernel) // d.stride + 1
+            f += 2 * d.out_channels * d.in_channels * d.kernel * d.kernel * oh * ow
+    return f
+
+
+# ---- configuration 5: UNet / VAE-decoder style mid + up path ----------------------------------------
+def unet_mid_up(latent=64, base=512, groups=32):
+    """Frozen interpretation of the loosely specified configuration: conv_in 4->512 @latent^2; two stride-2
+    3x3 convs down to (latent/4)^2; mid = ResBlock -> [GroupNorm -> Permute CHW->[tokens, C] ->
+    SelfAttention(1 head) -> Permute back -> Add] -> ResBlock; up = 4 x [UpsampleNearest 2x -> ResBlock]
+    with channels 512 -> 512 -> 256 -> 128 -> 128; GroupNorm -> SiLU -> conv_out 128 -> 3.
+    ResBlock = GN -> SiLU -> Conv3x3 -> GN -> SiLU -> Conv3x3 + skip (1x1 conv when channels change)."""
+    d = []
+    n = [0]
+
+    def conv(x, out, ic, oc, hw, k=3, s=1, p=1):
+        n[0] += 1
+        d.append(make_desc(f"u/conv{n[0]}", "Conv2d", inputs=[x], output=out, in_channels=ic, out_channels=oc, input_height=hw,
+                           input_width=hw, kernel=k, stride=s, padding=p, params_count=oc * ic * k * k))
+
+    def gn_silu(x, out, c, hw):
+        n[0] += 1
+        d.append(make_desc(f"u/gn{n[0]}", "GroupNorm", inputs=[x], output=out + "_g", in_channels=c, input_height=hw, input_width=hw,
+                           num_groups=groups, params_count=2 * c))
+        d.append(make_desc(f"u/silu{n[0]}", "SiLU", inputs=[out + "_g"], output=out))
+
+    def resblock(x, out, ic, oc, hw):
+        t = out + "_t"
+        gn_silu(x, t + "1", ic, hw)
+        conv(t + "1", t + "2", ic, oc, hw)
+        gn_silu(t + "2", t + "3", oc, hw)
+        conv(t + "3", t + "4", oc, oc, hw)
+        skip = x
+        if ic != oc:
+            conv(x, t + "s", ic, oc, hw, k=1, s=1, p=0)
+            skip = t + "s"
+        n[0] += 1
+        d.append(make_desc(f"u/add{n[0]}", "Add", inputs=[t + "4", skip], output=out))
+
+    hw = latent
+    conv("x", "u/in", 4, base, hw)
+    conv("u/in", "u/d1", base, base, hw, s=2)
+    hw //= 2
+    conv("u/d1", "u/d2", base, base, hw, s=2)
+    hw //= 2
+    resblock("u/d2", "u/m1", base, base, hw)
+    tokens = hw * hw
+    n[0] += 1
+    d.append(make_desc(f"u/gn{n[0]}", "GroupNorm", inputs=["u/m1"], output="u/an", in_channels=base, input_height=hw, input_width=hw,
+                       num_groups=groups, params_count=2 * base))
+    d.append(make_desc("u/to_tokens", "Permute", inputs=["u/an"], output="u/at", shape=[base, tokens], permute_dims=[1, 0]))
+    d.append(make_desc("u/attn", "SelfAttention", inputs=["u/at"], output="u/ao", seq_len=tokens, embed_dim=base, num_heads=1,
+                       params_count=4 * base * base))
+    d.append(make_desc("u/to_chw", "Permute", inputs=["u/ao"], output="u/ac", shape=[tokens, base], permute_dims=[1, 0]))
+    d.append(make_desc("u/attn_add", "Add", inputs=["u/m1", "u/ac"], output="u/m2"))
+    resblock("u/m2", "u/m3", base, base, hw)
+    x, c = "u/m3", base
+    for i, oc in enumerate((base, base // 2, base // 4, base // 4)):
+        d.append(make_desc(f"u/up{i}", "UpsampleNearest", inputs=[x], output=f"u/up{i}o", in_channels=c, out_h=hw, out_w=hw,
+                           scale_h=2, scale_w=2))
+        hw *= 2
+        resblock(f"u/up{i}o", f"u/r{i}", c, oc, hw)
+        x, c = f"u/r{i}", oc
+    gn_silu(x, "u/fin", c, hw)
+    n[0] += 1
+    d.append(make_desc("u/conv_out", "Conv2d", inputs=["u/fin"], output="x", in_channels=c, out_channels=3, input_height=hw,
+                       input_width=hw, kernel=3, stride=1, padding=1, params_count=3 * c * 9))
+    return d

@@ -162,13 +162,80 @@ __global__ void rms_chunk_stats_kernel(const float* __restrict__ x, float* __res
   if (threadIdx.x == 0) part[row * chunks + blockIdx.x] = s;
 }
 
+// The reference sums the squares in ONE sequential fp32 chain, s = fma(x, x, s) (LayerOpsExt.hpp:353-356).
+// Over a whole sample (786 432 elements in the decoder configuration) that chain loses a systematic
+// 3.7e-4 of the sum, because addends far below the running sum's ulp are rounded on the sum's grid.
+// The rounding error of one step depends only on the addend and on the binade of the running sum,
+// so it can be reproduced in parallel: every thread replays a short stretch of the chain seeded with
+// the (exact) prefix sum at its first element and accumulates the rounding errors of its steps.
+// sequential result = exact sum + sum of these rounding errors.
+constexpr int SEQ_PER_THREAD = 32;  // CHUNK / 256 threads
+
+__global__ void __launch_bounds__(256) rms_seq_err_kernel(const float* __restrict__ x, const float* __restrict__ part,
+                                                          double* __restrict__ seq_err, long long len, int chunks, int chunk_len) {
+  __shared__ float sx[CHUNK + CHUNK / 32];  // padded: thread t reads sx[t * 33 + j]
+  __shared__ double sscan[256];
+  const long long row = blockIdx.y;
+  const int c = blockIdx.x;
+  const long long off = static_cast<long long>(c) * chunk_len;
+  const int n = static_cast<int>(min(static_cast<long long>(chunk_len), len - off));
+  const float* g = x + row * len + off;
+  for (int i = threadIdx.x; i < chunk_len; i += blockDim.x) sx[i + i / SEQ_PER_THREAD] = (i < n) ? __ldg(g + i) : 0.0f;
+  double prefix = 0.0;  // exact sum of the squares before this chunk
+  for (int j = 0; j < c; ++j) prefix += static_cast<double>(part[row * chunks + j]);
+  __syncthreads();
+  const float* mine = sx + threadIdx.x * (SEQ_PER_THREAD + 1);
+  double local = 0.0;
+#pragma unroll
+  for (int j = 0; j < SEQ_PER_THREAD; ++j) local += static_cast<double>(mine[j]) * static_cast<double>(mine[j]);
+  // exclusive scan of the per-thread sums (Hillis-Steele over 256 entries)
+  sscan[threadIdx.x] = local;
+  __syncthreads();
+  for (int d = 1; d < 256; d <<= 1) {
+    const double v = (threadIdx.x >= d) ? sscan[threadIdx.x - d] : 0.0;
+    __syncthreads();
+    sscan[threadIdx.x] += v;
+    __syncthreads();
+  }
+  const double before = prefix + sscan[threadIdx.x] - local;
+  float sf = static_cast<float>(before);  // on the chain's grid: same binade as the true running sum
+  double err = 0.0;
+  const int first = threadIdx.x * SEQ_PER_THREAD;
+#pragma unroll 8
+  for (int j = 0; j < SEQ_PER_THREAD; ++j) {
+    if (first + j < n) {
+      const float v = mine[j];
+      const float nf = fmaf(v, v, sf);
+      err += static_cast<double>(nf) - (static_cast<double>(sf) + static_cast<double>(v) * static_cast<double>(v));
+      sf = nf;
+    }
+  }
+  // block sum of the errors
+  __syncthreads();
+  sscan[threadIdx.x] = err;
+  __syncthreads();
+  for (int d = 128; d > 0; d >>= 1) {
+    if (threadIdx.x < d) sscan[threadIdx.x] += sscan[threadIdx.x + d];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) seq_err[row * chunks + c] = sscan[0];
+}
+
 __global__ void rms_chunk_apply_kernel(const float* __restrict__ x, const float* __restrict__ gamma, long long n_gamma,
                                        float* __restrict__ y, const float* __restrict__ part, long long len, int chunks,
-                                       int chunk_len, float eps) {
+                                       int chunk_len, float eps, const double* __restrict__ seq_err = nullptr) {
   const long long row = blockIdx.y;
-  float s = 0.0f;
-  for (int j = 0; j < chunks; ++j) s += part[row * chunks + j];
-  const float rms = sqrtf(s / static_cast<float>(len) + eps);
+  float rms;
+  if (seq_err != nullptr) {
+    // sum of squares as the reference's sequential fp32 loop produces it: exact sum + its rounding errors
+    double sd = 0.0;
+    for (int j = 0; j < chunks; ++j) sd += static_cast<double>(part[row * chunks + j]) + seq_err[row * chunks + j];
+    rms = sqrtf(static_cast<float>(sd) / static_cast<float>(len) + eps);
+  } else {
+    float s = 0.0f;
+    for (int j = 0; j < chunks; ++j) s += part[row * chunks + j];
+    rms = sqrtf(s / static_cast<float>(len) + eps);
+  }
   const long long off = static_cast<long long>(blockIdx.x) * chunk_len;
   const long long cn = min(static_cast<long long>(chunk_len), len - off);
   const float* g = x + row * len + off;
@@ -649,7 +716,10 @@ int launch_groupnorm(const float* x, const float* gamma, const float* beta, floa
 int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y, int batch, int64_t n, float eps,
                    cudaStream_t st) {
   if (batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "RMSNorm: empty input");
-  if (use_sweeps(batch, n)) {
+  // Below this length the sequential chain's rounding loss is < 1e-6 of the sum and any summation order
+  // agrees with the reference; above it the chain is reproduced (rms_seq_err_kernel).
+  constexpr long long FAITHFUL_FROM = 16384;
+  if (n <= FAITHFUL_FROM && use_sweeps(batch, n)) {
     RowParams p{};
     p.x = x; p.y = y; p.rows = batch; p.len = n; p.eps = eps; p.gamma = gamma; p.n_gamma = gamma ? n_gamma : 0;
     return launch_sweep_rows<FAM_RMS>(p, st);
@@ -657,18 +727,29 @@ int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y
   const int chunks = static_cast<int>((n + CHUNK - 1) / CHUNK);
   float* part;
   MB_TRY(norm_scratch(&part));
+  // scratch: [floats: partial sums | doubles: rounding errors], a third and two thirds of the buffer
+  constexpr size_t ERR_OFFSET = (NORM_SCRATCH_BYTES / 3) & ~size_t(255);  // doubles start 256-byte aligned
+  const long long cap_rows = static_cast<long long>(ERR_OFFSET / sizeof(float)) / chunks;
+  if (cap_rows < 1) return fail(MIMIR_B200_E_UNSUPPORTED, "RMSNorm: a row of %lld elements exceeds the partial-statistics scratch", static_cast<long long>(n));
+  static_assert((NORM_SCRATCH_BYTES - ERR_OFFSET) / sizeof(double) >= ERR_OFFSET / sizeof(float), "error region too small");
+  double* errs = reinterpret_cast<double*>(reinterpret_cast<uint8_t*>(part) + ERR_OFFSET);
   long long group = L2_GROUP_BYTES / (n * 4);
   if (group < 1) group = 1;
-  const long long cap_rows = static_cast<long long>(NORM_SCRATCH_BYTES / sizeof(float)) / chunks;
-  if (cap_rows < 1) return fail(MIMIR_B200_E_UNSUPPORTED, "RMSNorm: a row of %lld elements exceeds the partial-statistics scratch", static_cast<long long>(n));
   if (group > cap_rows) group = cap_rows;
   if (group > 65535) group = 65535;
+  const bool faithful = n > FAITHFUL_FROM;
   for (long long r0 = 0; r0 < batch; r0 += group) {
     const long long nr = (batch - r0 < group) ? batch - r0 : group;
     dim3 grid(chunks, static_cast<unsigned>(nr));
     rms_chunk_stats_kernel<<<grid, 256, 0, st>>>(x + r0 * n, part, n, chunks, CHUNK);
     MB_CUDA(cudaGetLastError());
-    rms_chunk_apply_kernel<<<grid, 256, 0, st>>>(x + r0 * n, gamma, gamma ? n_gamma : 0, y + r0 * n, part, n, chunks, CHUNK, eps);
+    if (faithful) {
+      rms_seq_err_kernel<<<grid, 256, 0, st>>>(x + r0 * n, part, errs, n, chunks, CHUNK);
+      MB_CUDA(cudaGetLastError());
+      count_launch();
+    }
+    rms_chunk_apply_kernel<<<grid, 256, 0, st>>>(x + r0 * n, gamma, gamma ? n_gamma : 0, y + r0 * n, part, n, chunks, CHUNK, eps,
+                                                 faithful ? errs : nullptr);
     MB_CUDA(cudaGetLastError());
     count_launch(2);
   }

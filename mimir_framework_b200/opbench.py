@@ -163,16 +163,116 @@ def bench_transformer(no_cpu: bool):
     del flush
 
 
+def _time_graph(model, spec, batch, out, stream, iters=5):
+    ms, _ = time_launches(lambda: model.forward_device(spec, batch, out.data_ptr(), out.numel(), stream), warmup=2, iters=iters)
+    return ms
+
+
+def _cpu_sample(descs, weights, inputs, no_cpu, repeats=1):
+    """One sample through the compiled reference: (output, seconds, threads) or (None, None, None)."""
+    if no_cpu:
+        return None, None, None
+    from oracle import ref
+    if not ref.available():
+        return None, None, None
+    cores = ref.set_threads(os.cpu_count() or 1)
+    ref.set_guard_limit(64 << 30)
+    m = ref.RefModel(descs)
+    for i, w in enumerate(weights):
+        if w is not None:
+            m.set_weights(i, w)
+    best, y = None, None
+    for _ in range(repeats):
+        y, secs = m.forward(inputs, return_seconds=True)
+        best = secs if best is None else min(best, secs)
+    m.close()
+    return y, best, cores
+
+
+def _parity(got, want):
+    if want is None:
+        return None
+    err = np.abs(got.ravel() - want.ravel())
+    return {"max_abs": float(err.max()), "outside_tolerance": int((err > 1e-4 + 1e-3 * np.abs(want.ravel())).sum()), "n": int(want.size)}
+
+
+def bench_graph_config(name, descs, weights, x, batch, out_n, flops_per_sample, precision, no_cpu, cpu_note):
+    """Times `batch` samples device-resident; parity of sample 0 against the compiled reference."""
+    import torch
+
+    model = rt.GraphModel(descs, precision)
+    for i, w in enumerate(weights):
+        model.upload_weights(i, w)
+    per = x.size // batch
+    model.plan({"x": (per, False)}, batch)
+    d_x = torch.from_numpy(x).cuda()
+    d_out = torch.empty(batch * out_n, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    spec = {"x": (d_x.data_ptr(), per, False)}
+    rt.profile_gemm(True)
+    ms = _time_graph(model, spec, batch, d_out, st)
+    gemm_ms, gemm_n = rt.profile_read()
+    rt.profile_gemm(False)
+    rt.check(rt.lib().mimir_b200_check_device(None))
+    got0 = d_out[:out_n].cpu().numpy()
+    want, secs, cores = _cpu_sample(descs, weights, {"x": x.reshape(batch, per)[0]}, no_cpu)
+    runs = 2 + 5
+    print(json.dumps({"config": name, "batch": batch, "ms_per_batch": ms, "samples_per_s": batch / (ms * 1e-3),
+                      "tflops_algorithmic": flops_per_sample * batch / (ms * 1e-3) / 1e12,
+                      "gemm_share_of_step": (gemm_ms / runs) / ms if gemm_n else None,
+                      "arena_bytes": model.arena_bytes, "precision": precision,
+                      "cpu_reference_s_per_sample": secs, "cpu_reference_samples_per_s": (1.0 / secs) if secs else None,
+                      "cpu_cores": cores, "cpu_note": cpu_note, "parity_sample0": _parity(got0, want)}), flush=True)
+    model.close()
+    del d_x, d_out
+
+
+def bench_decoder(no_cpu):
+    cfg = configs.DECODER_CFG
+    descs = configs.gpt_decoder(**cfg)
+    weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
+    batch = 32
+    ids = np.random.default_rng(0).integers(0, cfg["vocab"], (batch, cfg["seq"])).astype(np.float32)
+    bench_graph_config("3 GPT decoder prefill, 12 layers d768 h12 ffn3072 vocab32000 seq1024, bf16-exact weights", descs, weights, ids,
+                       batch, cfg["seq"] * cfg["vocab"], configs.gpt_decoder_flops(**cfg), abi.PREC_BF16W, no_cpu,
+                       "one sample through the reference CPU path")
+
+
+def bench_conv_stack(no_cpu):
+    descs = configs.conv_stack()
+    weights = configs.conv_stack_weights(descs)
+    batch = 64
+    x = np.random.default_rng(0).random((batch, 3 * 224 * 224), dtype=np.float32)
+    bench_graph_config("4 conv vision stack, stem 7x7 s2 + 4 x [conv3x3, GroupNorm(32), SiLU, residual], 64..256 ch @112^2", descs,
+                       weights, x, batch, 256 * 112 * 112, configs.conv_flops(descs), abi.PREC_BF16X2, no_cpu,
+                       "one sample through the reference CPU path")
+
+
+def bench_unet(no_cpu):
+    descs = configs.unet_mid_up()
+    weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
+    batch = 16
+    x = np.random.default_rng(0).standard_normal((batch, 4 * 64 * 64), dtype=np.float32)
+    bench_graph_config("5 UNet mid+up, latent 4x64x64 -> 3x256x256, channels 512/256/128, bf16-exact weights", descs, weights, x, batch,
+                       3 * 256 * 256, configs.conv_flops(descs), abi.PREC_BF16W, no_cpu, "one sample through the reference CPU path")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="all", choices=["all", "norms", "configs"])
+    ap.add_argument("--only", default="all", choices=["all", "norms", "configs", "c1", "c3", "c4", "c5"])
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     rt.init(0, 0)
     if args.only in ("all", "norms"):
         bench_norms()
-    if args.only in ("all", "configs"):
+    if args.only in ("all", "configs", "c1"):
         bench_transformer(args.no_cpu)
+    if args.only in ("all", "configs", "c3"):
+        bench_decoder(args.no_cpu)
+    if args.only in ("all", "configs", "c4"):
+        bench_conv_stack(args.no_cpu)
+    if args.only in ("all", "configs", "c5"):
+        bench_unet(args.no_cpu)
     rt.shutdown()
 
 

@@ -238,3 +238,47 @@ def test_pipelined_forward_equals_single_pass(backend):
     with pytest.raises(backend.MimirB200Error, match="multiple"):
         m.plan(spec, batch)
     m.close()
+
+
+def test_gpt_decoder_reduced(backend):
+    """Configuration 3 at reduced size (2 layers, d 128, 4 heads of 32, seq 96, vocab 300), bf16-rounded
+    weights, both precision modes; logits within tolerance and argmax ids equal wherever the CPU top-2
+    margin exceeds the tolerance."""
+    cfg = dict(layers=2, d_model=128, heads=4, ffn=256, vocab=300, seq=96)
+    descs = configs.gpt_decoder(**cfg)
+    weights = configs.seeded_weights(descs, seed=1, std=0.05, bf16=True)
+    batch = 2
+    ids = np.random.default_rng(0).integers(0, 300, (batch, 96)).astype(np.float32)
+    inputs = {"x": (ids.ravel(), False)}
+    want = oracle_batch(descs, weights, inputs, batch)
+    for prec in (abi.PREC_BF16W, abi.PREC_BF16X2):
+        got = gpu_batch(backend, descs, weights, inputs, batch, 96 * 300, precision=prec)
+        assert_close(got, want, f"decoder logits precision {prec}")
+        w = want.reshape(batch * 96, 300)
+        g = got.reshape(batch * 96, 300)
+        top2 = np.sort(w, axis=1)[:, -2:]
+        decided = (top2[:, 1] - top2[:, 0]) > 2 * (1e-4 + 1e-3 * np.abs(top2[:, 1]))
+        assert decided.sum() > 0.9 * decided.size
+        assert np.array_equal(g.argmax(1)[decided], w.argmax(1)[decided])
+
+
+def test_conv_stack_reduced(backend):
+    """Configuration 4 at reduced size: stem 7x7 s2 + three residual blocks with GroupNorm + SiLU."""
+    descs = configs.conv_stack(image=40, channels=(16, 32, 32, 64), groups=8)
+    weights = configs.conv_stack_weights(descs)
+    batch = 2
+    x = np.random.default_rng(0).random((batch, 3 * 40 * 40)).astype(np.float32)
+    inputs = {"x": (x.ravel(), False)}
+    assert_close(gpu_batch(backend, descs, weights, inputs, batch, 64 * 20 * 20), oracle_batch(descs, weights, inputs, batch), "conv stack")
+
+
+def test_unet_mid_up_reduced(backend):
+    """Configuration 5 at reduced size: strided convs, ResBlocks, single-head attention over the tokens of
+    the mid block (Permute in and out), nearest upsampling x4, bf16-rounded weights."""
+    descs = configs.unet_mid_up(latent=16, base=64, groups=8)
+    weights = configs.seeded_weights(descs, seed=1, std=0.05, bf16=True)
+    batch = 2
+    x = np.random.default_rng(0).standard_normal((batch, 4 * 16 * 16)).astype(np.float32)
+    inputs = {"x": (x.ravel(), False)}
+    want = oracle_batch(descs, weights, inputs, batch)
+    assert_close(gpu_batch(backend, descs, weights, inputs, batch, 3 * 64 * 64, precision=abi.PREC_BF16W), want, "unet mid+up")
