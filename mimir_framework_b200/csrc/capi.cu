@@ -181,10 +181,20 @@ int conv_chunk_samples(int batch, int ohw, int k, int precision) {
   return static_cast<int>(c);
 }
 
-size_t conv_ws_bytes(int batch, int ohw, int k, int precision) {
+bool conv_uses_shifted(int ic, int ks, int stride, int pad) {
+  const char* off = getenv("MIMIR_B200_CONV_IM2COL");
+  if (off && off[0] == '1') return false;
+  return stride == 1 && (ks & 1) == 1 && pad == ks / 2 && ic % 32 == 0 && ks <= 7;
+}
+
+size_t conv_ws_bytes(int batch, int ic, int h, int w, int ks, int stride, int pad, int precision) {
   int ap, wp;
   precision_planes(precision, &ap, &wp);
-  return align256(split_bytes(static_cast<int64_t>(conv_chunk_samples(batch, ohw, k, precision)) * ohw, k, ap));
+  if (conv_uses_shifted(ic, ks, stride, pad))
+    return align256(static_cast<size_t>(ap) * batch * (h + 2 * pad) * (w + 2 * pad) * ic * sizeof(__nv_bfloat16));
+  const int oh = (h + 2 * pad - ks) / stride + 1, ow = (w + 2 * pad - ks) / stride + 1;
+  const int k = ic * ks * ks;
+  return align256(split_bytes(static_cast<int64_t>(conv_chunk_samples(batch, oh * ow, k, precision)) * oh * ow, k, ap));
 }
 
 int conv_exec(const ConvExec& e, cudaStream_t st) {
@@ -194,6 +204,23 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
   const int ow = (e.w + 2 * e.pad - e.ks) / e.stride + 1;
   if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: empty output");
   const int ohw = oh * ow, k = e.ic * e.ks * e.ks;
+  if (conv_uses_shifted(e.ic, e.ks, e.stride, e.pad)) {
+    // NCHW fp32 -> zero-padded NHWC planes, then one GEMM that walks the taps as shifted row offsets
+    const long long rows = static_cast<long long>(e.batch) * (e.h + 2 * e.pad) * (e.w + 2 * e.pad);
+    if (rows > 0x7fffffffLL) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: batch too large for one launch");
+    MB_TRY(launch_nchw_to_padded_nhwc_split(e.x, static_cast<__nv_bfloat16*>(e.ws), e.batch, e.ic, e.h, e.w, e.pad, ap, st));
+    GemmArgs g;
+    g.a = static_cast<const __nv_bfloat16*>(e.ws);
+    g.w = e.w_split;
+    g.a_planes = ap; g.w_planes = wp;
+    g.m = static_cast<int>(rows); g.n = e.oc; g.k = k;
+    g.activation = e.activation;
+    g.out_f32 = e.y;
+    g.residual = e.residual;
+    g.ldo = e.oc;
+    g.conv_ks = e.ks; g.conv_c = e.ic; g.conv_pad = e.pad; g.conv_h = e.h; g.conv_w = e.w;
+    return launch_gemm(g, st);
+  }
   const int chunk = conv_chunk_samples(e.batch, ohw, k, e.precision);
   for (int b0 = 0; b0 < e.batch; b0 += chunk) {
     const int bc = (e.batch - b0 < chunk) ? (e.batch - b0) : chunk;
@@ -428,9 +455,10 @@ int mimir_b200_conv2d(const float* x, const float* w, float* y, int batch, int i
   MB_TRY(t.out(&e.y, static_cast<size_t>(batch) * oc * oh * ow, "conv.y"));
   void* ws;
   MB_TRY(t.alloc(&ws, split_bytes(oc, ic * k * k, 2), "conv.wsplit"));
-  MB_TRY(launch_split(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic * k * k, 2, nullptr));
+  if (conv_uses_shifted(ic, k, stride, pad)) MB_TRY(launch_conv_weight_planes(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic, k, 2, nullptr));
+  else MB_TRY(launch_split(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic * k * k, 2, nullptr));
   e.w_split = static_cast<const __nv_bfloat16*>(ws);
-  MB_TRY(t.alloc(&e.ws, conv_ws_bytes(batch, oh * ow, ic * k * k, e.precision), "conv.ws"));
+  MB_TRY(t.alloc(&e.ws, conv_ws_bytes(batch, ic, h, wd, k, stride, pad, e.precision), "conv.ws"));
   MB_TRY(conv_exec(e, nullptr));
   return finish_download(y, e.y, static_cast<size_t>(batch) * oc * oh * ow);
 }

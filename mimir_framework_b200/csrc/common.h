@@ -88,6 +88,9 @@ struct GemmArgs {
   int64_t ldo = 0;
   int out_nchw_hw = 0;               // > 0: out_f32/residual are [m / hw][n][hw] (conv output), ldo unused
   __nv_bfloat16* out_split = nullptr;  // planes [2][m][round_up(n,64)] for the next GEMM, or null
+  // Shifted-GEMM convolution (conv_ks > 0): `a` is the zero-padded NHWC activation [samples*(h+2p)*(w+2p)][conv_c],
+  // m counts padded-grid rows, k = conv_ks^2 * conv_c ordered (tap, channel), output is NCHW [samples][n][h][w].
+  int conv_ks = 0, conv_c = 0, conv_pad = 0, conv_h = 0, conv_w = 0;
 };
 // y = act(a · wᵀ + bias) (+ residual); tcgen05 / TMEM / TMA.
 int launch_gemm(const GemmArgs& g, cudaStream_t st);
@@ -131,4 +134,9 @@ int launch_attention_core(const float* qkv, float* out, int batch, int seq, int 
 // im2col of NCHW fp32 into split planes [planes][batch*oh*ow][kp], k = ic*ks*ks ordered (ic, kh, kw)
 int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, int h, int w, int ks, int stride,
                         int pad, int oh, int ow, int planes, cudaStream_t st);
+// NCHW fp32 -> zero-padded NHWC planes [planes][batch*(h+2p)*(w+2p)][c] (borders written as zero)
+int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int batch, int c, int h, int w, int pad, int planes,
+                                     cudaStream_t st);
+// OIHW fp32 -> planes [planes][oc][round_up(ks*ks*ic, 64)] with K ordered (kh, kw, ic)
+int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st);
 }  // namespace mb

@@ -66,3 +66,92 @@ int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, i
 }
 
 }  // namespace mb
+
+// ---------------------------------------------------------------------------------------------
+// Stride-1 "same" convolutions without a materialised im2col: the GEMM kernel sums one shifted
+// GEMM per filter tap over the zero-padded NHWC activation matrix (see GemmParams::conv_*).  The
+// two kernels below produce its operands.
+// ---------------------------------------------------------------------------------------------
+namespace mb {
+namespace {
+
+// One CTA per (sample, padded row yp, 32-channel block): 32x32 tiles through shared memory turn the
+// W-contiguous NCHW row into C-contiguous NHWC pixels; border pixels are written as zeros.
+__global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
+                                                                  int c, int h, int w, int pad, int planes, long long plane_stride) {
+  __shared__ float tile[32][33];
+  const int hp = h + 2 * pad, wp = w + 2 * pad;
+  const int cb = blockIdx.x * 32;
+  const int yp = blockIdx.y;
+  const int n = blockIdx.z;
+  const int y = yp - pad;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const bool row_in = y >= 0 && y < h;
+  for (int x0 = 0; x0 < wp; x0 += 32) {
+    // load tile[cc][xx] = x[n, cb + cc, y, x0 + xx - pad]
+    for (int cc = ty; cc < 32; cc += 8) {
+      const int xs = x0 + tx - pad;
+      float v = 0.0f;
+      if (row_in && xs >= 0 && xs < w && cb + cc < c) v = __ldg(x + ((static_cast<long long>(n) * c + cb + cc) * h + y) * w + xs);
+      tile[cc][tx] = v;
+    }
+    __syncthreads();
+    for (int xx = ty; xx < 32; xx += 8) {
+      const int xp = x0 + xx;
+      if (xp < wp && cb + tx < c) {
+        const float v = tile[tx][xx];
+        const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+        const long long o = ((static_cast<long long>(n) * hp + yp) * wp + xp) * c + cb + tx;
+        dst[o] = hi;
+        if (planes == 2) dst[o + plane_stride] = __float2bfloat16_rn(v - __bfloat162float(hi));
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// dst[pl][o][(kh*ks + kw)*ic + i] = split(w[o][i][kh][kw]); the padded tail of K is zero
+__global__ void conv_weight_planes_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ dst, int oc, int ic, int ks,
+                                          int kp, int planes) {
+  const int k = ks * ks * ic;
+  const long long total = static_cast<long long>(oc) * kp;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int o = static_cast<int>(i / kp), kk = static_cast<int>(i - static_cast<long long>(o) * kp);
+    float v = 0.0f;
+    if (kk < k) {
+      const int t = kk / ic, ci = kk - t * ic;
+      v = __ldg(w + (static_cast<long long>(o) * ic + ci) * ks * ks + t);
+    }
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    dst[i] = hi;
+    if (planes == 2) dst[i + total] = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
+}
+
+}  // namespace
+
+int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int batch, int c, int h, int w, int pad, int planes,
+                                     cudaStream_t st) {
+  if (batch <= 0 || c <= 0 || h <= 0 || w <= 0 || pad < 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad activation shape");
+  const int hp = h + 2 * pad, wp = w + 2 * pad;
+  if (hp > 65535 || batch > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: image too tall for the layout kernel");
+  dim3 grid((c + 31) / 32, hp, batch);
+  nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, static_cast<long long>(batch) * hp * wp * c);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st) {
+  const int kp = round_up(ks * ks * ic, 64);
+  const long long total = static_cast<long long>(oc) * kp;
+  long long blocks = (total + 255) / 256;
+  if (blocks > ctx().sm_count * 16) blocks = ctx().sm_count * 16;
+  conv_weight_planes_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(w, dst, oc, ic, ks, kp, planes);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+}  // namespace mb

@@ -183,6 +183,10 @@ struct GemmParams {
   __nv_bfloat16* out_split;  // [2][m][np]
   long long np;              // round_up(n, 64)
   int ohw;                   // > 0: fp32 output (and residual) are NCHW, row = sample * ohw + pixel
+  // Convolution as a sum of shifted GEMMs (conv_ks > 0): A is the zero-padded NHWC activation matrix
+  // [samples * hp * wp, C]; k-block kb belongs to tap t = kb / conv_cblocks and reads A rows shifted by
+  // (kh - pad) * wp + (kw - pad); output rows live on the padded grid, border rows are dropped.
+  int conv_ks, conv_cblocks, conv_pad, conv_hp, conv_wp, conv_h, conv_w;
   int* err_word;
 };
 
@@ -263,8 +267,15 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err_word, 1)) { ok = false; break; }
           uint8_t* sbase = smem + stage * STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], tx_bytes);
+          int a_col = kb * BK, a_row = tm * BM;
+          if (p.conv_ks > 0) {
+            const int t = kb / p.conv_cblocks, cb = kb - t * p.conv_cblocks;
+            const int kh = t / p.conv_ks, kw = t - kh * p.conv_ks;
+            a_row += (kh - p.conv_pad) * p.conv_wp + (kw - p.conv_pad);  // may be negative: TMA zero-fills
+            a_col = cb * BK;
+          }
           for (int pl = 0; pl < p.a_planes; ++pl)
-            tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], kb * BK, tm * BM, pl);
+            tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
           for (int pl = 0; pl < p.w_planes; ++pl)
             tma_load_3d(sbase + 2 * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * BN, pl);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -351,17 +362,31 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (p.bias != nullptr && (full_cols || col0 + j < p.n)) b = __ldg(p.bias + col0 + j);
           v[j] = apply_act(v[j] + b, p.activation);
         }
-        if (row_ok && p.ohw > 0) {
-          // channel-major output: lane <-> pixel, so each column is a coalesced 128-byte store
-          const long long smp = row / p.ohw;
-          const long long o0 = (smp * p.n + col0) * p.ohw + (row - smp * p.ohw);
+        if (p.ohw > 0 || p.conv_ks > 0) {
+          // channel-major (NCHW) output: lane <-> pixel, so each column is a coalesced store
+          bool ok = row_ok;
+          long long o0 = 0, cstride = 0;
+          if (p.conv_ks > 0) {
+            const int per = p.conv_hp * p.conv_wp;
+            const int smp = row / per, rem = row - smp * per;
+            const int yy = rem / p.conv_wp - p.conv_pad, xx = rem - (rem / p.conv_wp) * p.conv_wp - p.conv_pad;
+            ok = ok && yy >= 0 && yy < p.conv_h && xx >= 0 && xx < p.conv_w;
+            cstride = static_cast<long long>(p.conv_h) * p.conv_w;
+            o0 = (static_cast<long long>(smp) * p.n + col0) * cstride + static_cast<long long>(yy) * p.conv_w + xx;
+          } else {
+            const long long smp = row / p.ohw;
+            cstride = p.ohw;
+            o0 = (smp * p.n + col0) * cstride + (row - smp * p.ohw);
+          }
+          if (ok) {
 #pragma unroll 4
-          for (int j = 0; j < 32; ++j) {
-            if (full_cols || col0 + j < p.n) {
-              const long long oi = o0 + static_cast<long long>(j) * p.ohw;
-              float r = v[j];
-              if (p.residual != nullptr) r += __ldg(p.residual + oi);
-              p.out_f32[oi] = r;
+            for (int j = 0; j < 32; ++j) {
+              if (full_cols || col0 + j < p.n) {
+                const long long oi = o0 + static_cast<long long>(j) * cstride;
+                float r = v[j];
+                if (p.residual != nullptr) r += __ldg(p.residual + oi);
+                p.out_f32[oi] = r;
+              }
             }
           }
         } else if (row_ok) {
@@ -532,13 +557,22 @@ int env_int(const char* name, int dflt) {
 template <int BK, int STAGES>
 int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   const int kp = round_up(g.k, 64);
+  const bool conv = g.conv_ks > 0;
   CUtensorMap map_a, map_w;
-  MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, kp, BK, BM));
+  // conv: A rows are `conv_c` channels long and K = taps * conv_c runs over (tap, channel)
+  MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, conv ? g.conv_c : kp, BK, BM));
   MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, BN));
   GemmParams p;
   p.m = g.m;
   p.n = g.n;
-  p.kblocks = kp / BK;
+  p.kblocks = conv ? g.conv_ks * g.conv_ks * (g.conv_c / BK) : kp / BK;
+  p.conv_ks = g.conv_ks;
+  p.conv_cblocks = conv ? g.conv_c / BK : 1;
+  p.conv_pad = g.conv_pad;
+  p.conv_hp = g.conv_h + 2 * g.conv_pad;
+  p.conv_wp = g.conv_w + 2 * g.conv_pad;
+  p.conv_h = g.conv_h;
+  p.conv_w = g.conv_w;
   p.a_planes = g.a_planes;
   p.w_planes = g.w_planes;
   p.tiles_m = (g.m + BM - 1) / BM;
@@ -614,8 +648,12 @@ int launch_gemm(const GemmArgs& g, cudaStream_t st) {
   if (!g.out_f32 && !g.out_split) return fail(MIMIR_B200_E_INVALID, "gemm: no output");
   if (g.residual && !g.out_f32) return fail(MIMIR_B200_E_INVALID, "gemm: residual needs the fp32 output stride");
   // BK = 32 keeps four 48 KB stages in flight, BK = 64 two 96 KB stages.
+  if (g.conv_ks > 0) {
+    if (g.conv_c <= 0 || g.conv_c % 32 != 0 || g.k != g.conv_ks * g.conv_ks * g.conv_c || g.out_split || !g.out_f32)
+      return fail(MIMIR_B200_E_INVALID, "gemm: bad shifted-convolution arguments");
+  }
   const int bk = env_int("MIMIR_B200_GEMM_BK", 32);
-  if (bk == 64) return launch_gemm_t<64, 2>(g, st);
+  if (bk == 64 && (g.conv_ks == 0 || g.conv_c % 64 == 0)) return launch_gemm_t<64, 2>(g, st);
   return launch_gemm_t<32, 4>(g, st);
 }
 

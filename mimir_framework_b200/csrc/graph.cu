@@ -217,7 +217,10 @@ int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
     L.w_split_bytes = split_bytes(L.d.out_channels, k, wp);
     MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split), L.w_split_bytes, "conv.w_planes"));
     m->weight_bytes += L.w_split_bytes;
-    MB_TRY(launch_split(L.w_f32, L.w_split, L.d.out_channels, k, wp, st));
+    if (conv_uses_shifted(L.d.in_channels, L.d.kernel, L.d.stride, L.d.padding))
+      MB_TRY(launch_conv_weight_planes(L.w_f32, L.w_split, L.d.out_channels, L.d.in_channels, L.d.kernel, wp, st));
+    else
+      MB_TRY(launch_split(L.w_f32, L.w_split, L.d.out_channels, k, wp, st));
     L.w_split_k = k;
   } else if (L.lt == LT::Attention) {
     const int E = L.embed;
@@ -550,7 +553,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
         }
         case LT::Conv2d: {
           const int k = L.d.in_channels * L.d.kernel * L.d.kernel;
-          L.ws_bytes = conv_ws_bytes(batch, L.oh * L.ow, k, m->precision);
+          L.ws_bytes = conv_ws_bytes(batch, L.d.in_channels, L.h, L.w, L.d.kernel, L.d.stride, L.d.padding, m->precision);
           flops += 2ull * batch * L.oh * L.ow * k * L.d.out_channels;
           break;
         }

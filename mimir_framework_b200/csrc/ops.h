@@ -54,7 +54,11 @@ struct ConvExec {
   float* y = nullptr;
   void* ws = nullptr;
 };
-size_t conv_ws_bytes(int batch, int ohw, int k, int precision);
+// stride-1 "same" convolutions with a channel count that is a multiple of 32 run as shifted GEMMs over the
+// padded NHWC activation; everything else goes through im2col planes.  The two paths want different
+// weight-plane orders ((kh, kw, ic) vs (ic, kh, kw)).
+bool conv_uses_shifted(int ic, int ks, int stride, int pad);
+size_t conv_ws_bytes(int batch, int ic, int h, int w, int ks, int stride, int pad, int precision);
 int conv_exec(const ConvExec& e, cudaStream_t st);
 
 }  // namespace mb

@@ -163,7 +163,7 @@ def bench_transformer(no_cpu: bool):
     del flush
 
 
-def _time_graph(model, spec, batch, out, stream, iters=5):
+def _time_graph(model, spec, batch, out, stream, iters=int(os.environ.get('OPBENCH_ITERS', '5'))):
     ms, _ = time_launches(lambda: model.forward_device(spec, batch, out.data_ptr(), out.numel(), stream), warmup=2, iters=iters)
     return ms
 
@@ -216,7 +216,7 @@ def bench_graph_config(name, descs, weights, x, batch, out_n, flops_per_sample, 
     rt.check(rt.lib().mimir_b200_check_device(None))
     got0 = d_out[:out_n].cpu().numpy()
     want, secs, cores = _cpu_sample(descs, weights, {"x": x.reshape(batch, per)[0]}, no_cpu)
-    runs = 2 + 5
+    runs = 2 + int(os.environ.get('OPBENCH_ITERS', '5'))
     print(json.dumps({"config": name, "batch": batch, "ms_per_batch": ms, "samples_per_s": batch / (ms * 1e-3),
                       "tflops_algorithmic": flops_per_sample * batch / (ms * 1e-3) / 1e12,
                       "gemm_share_of_step": (gemm_ms / runs) / ms if gemm_n else None,

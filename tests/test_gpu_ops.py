@@ -122,7 +122,11 @@ def test_attention_identity_weights(backend):
     (1, 3, 64, 32, 32, 7, 2, 3, 0),   # stem shape class
     (2, 16, 24, 14, 14, 3, 1, 1, 1),
     (1, 64, 128, 28, 28, 3, 1, 1, 0),
-    (1, 32, 48, 10, 10, 1, 1, 0, 0),  # 1x1 skip conv
+    (1, 32, 48, 10, 10, 1, 1, 0, 0),  # 1x1 skip conv (shifted-GEMM path, one tap)
+    (3, 32, 40, 13, 9, 3, 1, 1, 1),   # shifted-GEMM path: several samples, odd sizes, ReLU
+    (2, 64, 24, 7, 11, 5, 1, 2, 0),   # shifted-GEMM path, 5x5 taps
+    (1, 256, 300, 20, 20, 3, 1, 1, 0),  # shifted-GEMM path, two column tiles
+    (2, 32, 16, 12, 12, 3, 2, 1, 0),  # stride 2 stays on the im2col path
 ])
 def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
     r = rng(ic * oc + h)
