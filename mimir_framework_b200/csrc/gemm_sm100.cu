@@ -14,8 +14,9 @@
 //   warp 0      : TMA producer  — cp.async.bulk.tensor (no multicast) into a ring of smem stages
 //   warp 1      : MMA issuer    — one thread issues tcgen05.mma, operands from smem descriptors,
 //                                 accumulators in TMEM (2 x 256 columns, double buffered)
-//   warps 2..5  : epilogue      — tcgen05.ld TMEM -> registers, bias / activation / residual,
-//                                 stores fp32 rows and/or the bf16 hi/lo planes of the next layer
+//   warps 2..9  : epilogue      — tcgen05.ld TMEM -> registers -> 32x33 shared-memory transpose, bias /
+//                                 activation / residual, coalesced stores of fp32 rows and/or the bf16
+//                                 hi/lo planes of the next layer (or channel-major NCHW for convs)
 // Every mbarrier wait is bounded: after ~2 s it sets the device error word and the CTA drains.
 #include "common.h"
 
@@ -30,8 +31,9 @@ constexpr int BN = 256;        // columns of the output tile (one MMA, N = 256)
 constexpr int UMMA_K = 16;     // bf16 K per tcgen05.mma
 constexpr int NUM_ACC = 2;     // TMEM accumulator buffers
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_THREADS = 192;  // 6 warps
-constexpr int EPI_WARPS = 4;
+constexpr int NUM_THREADS = 320;  // 10 warps: TMA, MMA, 8 epilogue
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_PATCH_BYTES = EPI_WARPS * 32 * 33 * 4;
 
 // ------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -225,6 +227,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint64_t* acc_empty = acc_full + NUM_ACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* epi_patch = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -330,8 +333,17 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
     }
   } else {
-    // ------------------------------ epilogue (warps 2..5) ---------------------------------
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    // ------------------------------ epilogue (warps 2..9) ---------------------------------
+    // Two warps per TMEM lane quadrant, each owning half of the tile's columns.  Row-major outputs are
+    // transposed through a 32 x 33 shared-memory patch so that a warp instruction writes one full
+    // 128-byte row segment (lane <-> column); bias, activation and residual are applied on that side,
+    // where their loads are coalesced too.  Channel-major (NCHW) outputs are already coalesced with
+    // lane <-> pixel and skip the patch.
+    const int ew = warp - 2;
+    const int quad = warp & 3;   // TMEM lane quadrant this warp may read
+    const int half = ew >> 2;    // which half of the columns
+    float* patch = epi_patch + ew * (32 * 33);
+    const bool chan_major = (p.ohw > 0 || p.conv_ks > 0);
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -345,95 +357,72 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (!ok) break;
       while (!mbar_try_wait(&acc_full[acc], acc_phase)) {}  // completes at once: lane 0 saw the phase
       tcgen05_fence_after();
-      const int row = tm * BM + quad * 32 + lane;
-      const bool row_ok = row < p.m;
+      const int row0 = tm * BM + quad * 32;
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
       const int col_limit = (p.out_split != nullptr) ? static_cast<int>(p.np) : p.n;
+      // channel-major addressing of this lane's row
+      bool cm_ok = false;
+      long long cm_o0 = 0, cm_stride = 0;
+      if (chan_major) {
+        const int row = row0 + lane;
+        cm_ok = row < p.m;
+        if (p.conv_ks > 0) {
+          const int per = p.conv_hp * p.conv_wp;
+          const int smp = row / per, rem = row - smp * per;
+          const int yq = rem / p.conv_wp;
+          const int yy = yq - p.conv_pad, xx = rem - yq * p.conv_wp - p.conv_pad;
+          cm_ok = cm_ok && yy >= 0 && yy < p.conv_h && xx >= 0 && xx < p.conv_w;
+          cm_stride = static_cast<long long>(p.conv_h) * p.conv_w;
+          cm_o0 = static_cast<long long>(smp) * p.n * cm_stride + static_cast<long long>(yy) * p.conv_w + xx;
+        } else {
+          const long long smp = row / p.ohw;
+          cm_stride = p.ohw;
+          cm_o0 = smp * p.n * cm_stride + (row - smp * p.ohw);
+        }
+      }
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int ci = 0; ci < (BN / 32) / 2; ++ci) {
+        const int c0 = (half * (BN / 64) + ci) * 32;
         const int col0 = tn * BN + c0;
         if (col0 >= col_limit) break;  // warp-uniform
         float v[32];
         tmem_ld_32x32(taddr0 + c0, v);
-        const bool full_cols = (col0 + 32 <= p.n);
+        const int col = col0 + lane;  // this lane's column on the transposed side
+        const float bias_l = (p.bias != nullptr && col < p.n) ? __ldg(p.bias + col) : 0.0f;
+        if (chan_major) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float b = 0.0f;
-          if (p.bias != nullptr && (full_cols || col0 + j < p.n)) b = __ldg(p.bias + col0 + j);
-          v[j] = apply_act(v[j] + b, p.activation);
-        }
-        if (p.ohw > 0 || p.conv_ks > 0) {
-          // channel-major (NCHW) output: lane <-> pixel, so each column is a coalesced store
-          bool ok = row_ok;
-          long long o0 = 0, cstride = 0;
-          if (p.conv_ks > 0) {
-            const int per = p.conv_hp * p.conv_wp;
-            const int smp = row / per, rem = row - smp * per;
-            const int yy = rem / p.conv_wp - p.conv_pad, xx = rem - (rem / p.conv_wp) * p.conv_wp - p.conv_pad;
-            ok = ok && yy >= 0 && yy < p.conv_h && xx >= 0 && xx < p.conv_w;
-            cstride = static_cast<long long>(p.conv_h) * p.conv_w;
-            o0 = (static_cast<long long>(smp) * p.n + col0) * cstride + static_cast<long long>(yy) * p.conv_w + xx;
-          } else {
-            const long long smp = row / p.ohw;
-            cstride = p.ohw;
-            o0 = (smp * p.n + col0) * cstride + (row - smp * p.ohw);
+          for (int j = 0; j < 32; ++j) {
+            const float b = __shfl_sync(0xffffffffu, bias_l, j);
+            if (cm_ok && col0 + j < p.n) {
+              const long long oi = cm_o0 + static_cast<long long>(col0 + j) * cm_stride;
+              float r = apply_act(v[j] + b, p.activation);
+              if (p.residual != nullptr) r += __ldg(p.residual + oi);
+              p.out_f32[oi] = r;
+            }
           }
-          if (ok) {
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = v[j];
+          __syncwarp();
+          const bool col_ok = col < p.n;
+          const int rows_here = min(32, p.m - row0);
 #pragma unroll 4
-            for (int j = 0; j < 32; ++j) {
-              if (full_cols || col0 + j < p.n) {
-                const long long oi = o0 + static_cast<long long>(j) * cstride;
-                float r = v[j];
-                if (p.residual != nullptr) r += __ldg(p.residual + oi);
-                p.out_f32[oi] = r;
-              }
+          for (int i = 0; i < rows_here; ++i) {
+            float r = apply_act(patch[i * 33 + lane] + bias_l, p.activation);
+            const long long row = row0 + i;
+            if (p.residual != nullptr && col_ok) r += __ldg(p.residual + row * p.ldo + col);
+            if (p.out_f32 != nullptr && col_ok) p.out_f32[row * p.ldo + col] = r;
+            if (p.out_split != nullptr) {
+              // hi/lo planes for the next GEMM; columns n..np-1 are written as zero so that the padded
+              // K of the consumer stays zero
+              const float x = col_ok ? r : 0.0f;
+              const __nv_bfloat16 hi = __float2bfloat16_rn(x);
+              __nv_bfloat16* oh = p.out_split + row * p.np + col;
+              oh[0] = hi;
+              oh[static_cast<long long>(p.m) * p.np] = __float2bfloat16_rn(x - __bfloat162float(hi));
             }
           }
-        } else if (row_ok) {
-          if (p.residual != nullptr) {
-            const float* rr = p.residual + static_cast<long long>(row) * p.ldo + col0;
-            if (full_cols && ((reinterpret_cast<uintptr_t>(rr) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const float4 r4 = *reinterpret_cast<const float4*>(rr + j);
-                v[j] += r4.x; v[j + 1] += r4.y; v[j + 2] += r4.z; v[j + 3] += r4.w;
-              }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) v[j] += rr[j];
-            }
-          }
-          if (p.out_f32 != nullptr) {
-            float* o = p.out_f32 + static_cast<long long>(row) * p.ldo + col0;
-            if (full_cols && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.n) o[j] = v[j];
-            }
-          }
-          if (p.out_split != nullptr) {
-            // hi/lo planes for the next GEMM; columns n..np-1 are written as zero so that the
-            // padded K of the consumer stays zero
-            __nv_bfloat16* oh = p.out_split + static_cast<long long>(row) * p.np + col0;
-            __nv_bfloat16* ol = oh + static_cast<long long>(p.m) * p.np;
-            if (col0 + 32 <= p.np) {
-              __align__(16) __nv_bfloat16 h[32];
-              __align__(16) __nv_bfloat16 l[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float x = (full_cols || col0 + j < p.n) ? v[j] : 0.0f;
-                h[j] = __float2bfloat16_rn(x);
-                l[j] = __float2bfloat16_rn(x - __bfloat162float(h[j]));
-              }
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                *reinterpret_cast<uint4*>(oh + j) = *reinterpret_cast<const uint4*>(h + j);
-                *reinterpret_cast<uint4*>(ol + j) = *reinterpret_cast<const uint4*>(l + j);
-              }
-            }
-          }
+          __syncwarp();
         }
       }
       tcgen05_fence_before();
@@ -590,7 +579,8 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.ohw = g.out_nchw_hw;
   p.err_word = ctx().dev_error_word;
   constexpr int STAGE_BYTES = 2 * BM * BK * 2 + 2 * BN * BK * 2;
-  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_PATCH_BYTES;
+  static_assert(SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   auto kern = gemm_tn_bf16split_kernel<BK, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {

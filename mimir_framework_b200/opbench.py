@@ -231,7 +231,7 @@ def bench_decoder(no_cpu):
     cfg = configs.DECODER_CFG
     descs = configs.gpt_decoder(**cfg)
     weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
-    batch = 32
+    batch = int(os.environ.get('OPBENCH_BATCH', '32'))
     ids = np.random.default_rng(0).integers(0, cfg["vocab"], (batch, cfg["seq"])).astype(np.float32)
     bench_graph_config("3 GPT decoder prefill, 12 layers d768 h12 ffn3072 vocab32000 seq1024, bf16-exact weights", descs, weights, ids,
                        batch, cfg["seq"] * cfg["vocab"], configs.gpt_decoder_flops(**cfg), abi.PREC_BF16W, no_cpu,
