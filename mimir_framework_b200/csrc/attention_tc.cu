@@ -1,0 +1,369 @@
+// attention_tc.cu — the attention core on the tensor cores (head_dim 64).
+// Same arithmetic contract as attention.cu (LayerOps::self_attention_forward, LayerOps.hpp:1044-1090):
+// s = (Q.K) / sqrt(hd), causal rows skip j > i, p = exp(s - max), p *= 1 / (sum p + 1e-9), O = P V.
+//
+// Flash-style with QK^T and PV on tcgen05 and the online softmax in registers:
+//   * a pre-pass turns the fp32 QKV matrix into bf16 hi/lo planes laid out per (sample, head):
+//     Q and K as [seq][64] (K-major for Q K^T) and V transposed as [64][seq] (K-major for P V);
+//   * one CTA owns 128 query rows of one (sample, head) and walks the keys in tiles of 64:
+//       warp 0    TMA producer (Q once, then K_j, V_j; single-buffered, refilled as soon as the MMA
+//                 that read them has completed)
+//       warp 1    MMA issuer: S_j = Q K_j^T (hi*hi + lo*hi + hi*lo) into TMEM, later
+//                 PV_j = P_j V_j (same three products) into a second TMEM tile
+//       warps 2-5 one thread per query row: tcgen05.ld S_j, running max / sum, P_j written to shared
+//                 memory as bf16 hi/lo in the 128-byte-swizzled K-major layout the MMA reads, then
+//                 O = O * exp(m_old - m_new) + PV_j in registers (no TMEM read-modify-write)
+//   * 96 KB of shared memory and 128 TMEM columns per CTA, so two CTAs share an SM and one's softmax
+//     overlaps the other's MMAs.
+// Every mbarrier wait is bounded; on expiry the CTA raises its abort flag, sets the device error word,
+// leaves all loops and frees its TMEM.
+#include "common.h"
+#include "sm100_ptx.cuh"
+
+namespace mb {
+namespace {
+
+constexpr int AT_HD = 64;     // head dimension this kernel is written for
+constexpr int AT_BQ = 128;    // query rows per CTA (TMEM lanes)
+constexpr int AT_BK = 64;     // keys per tile
+constexpr int AT_THREADS = 192;
+constexpr int AT_TMEM_COLS = 128;  // S tile (64) + PV tile (64)
+
+constexpr int AT_Q_BYTES = AT_BQ * AT_HD * 2;   // one plane
+constexpr int AT_K_BYTES = AT_BK * AT_HD * 2;
+constexpr int AT_V_BYTES = AT_HD * AT_BK * 2;
+constexpr int AT_P_BYTES = AT_BQ * AT_BK * 2;
+constexpr int AT_SMEM = 2 * AT_Q_BYTES + 2 * AT_K_BYTES + 2 * AT_V_BYTES + 2 * AT_P_BYTES + 256 + 1024;
+
+struct AttnParams {
+  float* out;        // fp32 [batch*seq][embed]
+  int seq, embed, heads, causal;
+  int bh;            // batch * heads
+  float scale;
+  int* err_word;
+};
+
+// fp32 QKV [batch*seq][3E] -> bf16 planes: Q, K as [plane][bh][seq][64]; V^T as [plane][bh][64][seqp]
+__global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ qp,
+                                                        __nv_bfloat16* __restrict__ kp, __nv_bfloat16* __restrict__ vt, int seq,
+                                                        int seqp, int embed, int heads, int bh) {
+  __shared__ float tile[64][65];
+  const int s0 = blockIdx.x * 64;       // 64 sequence positions
+  const int b = blockIdx.y / heads, h = blockIdx.y - b * heads;
+  const long long ld = 3LL * embed;
+  const float* base = qkv + (static_cast<long long>(b) * seq) * ld + h * AT_HD;
+  const long long qk_plane = static_cast<long long>(bh) * seq * AT_HD;
+  const long long v_plane = static_cast<long long>(bh) * AT_HD * seqp;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
+  // Q and K: straight copies with the split
+  for (int r = ty; r < 64; r += 4) {
+    const int sidx = s0 + r;
+    if (sidx < seq) {
+      const float q = __ldg(base + sidx * ld + tx), k = __ldg(base + sidx * ld + embed + tx);
+      const long long o = (static_cast<long long>(blockIdx.y) * seq + sidx) * AT_HD + tx;
+      const __nv_bfloat16 qh = __float2bfloat16_rn(q), kh = __float2bfloat16_rn(k);
+      qp[o] = qh;
+      qp[o + qk_plane] = __float2bfloat16_rn(q - __bfloat162float(qh));
+      kp[o] = kh;
+      kp[o + qk_plane] = __float2bfloat16_rn(k - __bfloat162float(kh));
+    }
+    tile[r][tx] = (sidx < seq) ? __ldg(base + sidx * ld + 2 * embed + tx) : 0.0f;
+  }
+  __syncthreads();
+  // V transposed: vt[bh][d][s]; positions past seq (up to seqp) are zero
+  for (int d = ty; d < 64; d += 4) {
+    const int sidx = s0 + tx;
+    if (sidx < seqp) {
+      const float v = tile[tx][d];
+      const long long o = (static_cast<long long>(blockIdx.y) * AT_HD + d) * seqp + sidx;
+      const __nv_bfloat16 vh = __float2bfloat16_rn(v);
+      vt[o] = vh;
+      vt[o + v_plane] = __float2bfloat16_rn(v - __bfloat162float(vh));
+    }
+  }
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                       // [2 planes][128][64] bf16, 128B-swizzled rows
+  uint8_t* sK = sQ + 2 * AT_Q_BYTES;        // [2][64 keys][64]
+  uint8_t* sV = sK + 2 * AT_K_BYTES;        // [2][64 d][64 keys]
+  uint8_t* sP = sV + 2 * AT_V_BYTES;        // [2][128][64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * AT_P_BYTES);
+  uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 2, *v_full = bars + 3, *v_empty = bars + 4,
+           *s_full = bars + 5, *s_empty = bars + 6, *p_full = bars + 7, *o_full = bars + 8, *o_empty = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = blockIdx.x, bhi = blockIdx.y;
+  const int q0 = qt * AT_BQ;
+  int n_tiles = (p.seq + AT_BK - 1) / AT_BK;
+  if (p.causal) n_tiles = min(n_tiles, (min(p.seq, q0 + AT_BQ) + AT_BK - 1) / AT_BK);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1);
+    mbar_init(k_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, 4);
+    mbar_init(p_full, 4);
+    mbar_init(o_full, 1);
+    mbar_init(o_empty, 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, AT_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + AT_BK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * AT_Q_BYTES);
+      tma_load_3d(sQ, &map_q, q_full, 0, q0, bhi);
+      tma_load_3d(sQ + AT_Q_BYTES, &map_q, q_full, 0, q0, p.bh + bhi);
+      for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(k_empty, ph ^ 1, abort_flag, p.err_word, 11)) break;
+        mbar_expect_tx(k_full, 2 * AT_K_BYTES);
+        tma_load_3d(sK, &map_k, k_full, 0, j * AT_BK, bhi);
+        tma_load_3d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, p.bh + bhi);
+        if (!mbar_wait(v_empty, ph ^ 1, abort_flag, p.err_word, 12)) break;
+        mbar_expect_tx(v_full, 2 * AT_V_BYTES);
+        tma_load_3d(sV, &map_v, v_full, j * AT_BK, 0, bhi);
+        tma_load_3d(sV + AT_V_BYTES, &map_v, v_full, j * AT_BK, 0, p.bh + bhi);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(AT_BQ, AT_BK);  // M = 128, N = 64 for both products
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err_word, 13);
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t ph = j & 1;
+        if (!mbar_wait(k_full, ph, abort_flag, p.err_word, 14)) break;
+        if (!mbar_wait(s_empty, ph ^ 1, abort_flag, p.err_word, 15)) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int k = 0; k < AT_HD / 16; ++k) {
+          const uint32_t ko = k * 32;
+          const uint64_t qh = make_smem_desc(aQ + ko, 128), ql = make_smem_desc(aQ + AT_Q_BYTES + ko, 128);
+          const uint64_t kh = make_smem_desc(aK + ko, 128), kl = make_smem_desc(aK + AT_K_BYTES + ko, 128);
+          umma_bf16(tmem_s, qh, kh, idesc, k != 0 ? 1u : 0u);
+          umma_bf16(tmem_s, ql, kh, idesc, 1u);
+          umma_bf16(tmem_s, qh, kl, idesc, 1u);
+        }
+        umma_commit(s_full);
+        umma_commit(k_empty);
+        if (!mbar_wait(p_full, ph, abort_flag, p.err_word, 16)) break;
+        if (!mbar_wait(v_full, ph, abort_flag, p.err_word, 17)) break;
+        if (!mbar_wait(o_empty, ph ^ 1, abort_flag, p.err_word, 18)) break;
+        tcgen05_fence_after();
+#pragma unroll
+        for (int k = 0; k < AT_BK / 16; ++k) {
+          const uint32_t ko = k * 32;
+          const uint64_t ph_ = make_smem_desc(aP + ko, 128), pl = make_smem_desc(aP + AT_P_BYTES + ko, 128);
+          const uint64_t vh = make_smem_desc(aV + ko, 128), vl = make_smem_desc(aV + AT_V_BYTES + ko, 128);
+          umma_bf16(tmem_o, ph_, vh, idesc, k != 0 ? 1u : 0u);
+          umma_bf16(tmem_o, pl, vh, idesc, 1u);
+          umma_bf16(tmem_o, ph_, vl, idesc, 1u);
+        }
+        umma_commit(o_full);
+        umma_commit(v_empty);
+      }
+    }
+  } else {
+    // ------------------------------ softmax / accumulate: one thread per query row ----------------
+    const int quad = warp & 3;
+    const int r_local = quad * 32 + lane;
+    const int row = q0 + r_local;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    float m_run = -1e30f, l_run = 0.0f;  // the reference's initial max (LayerOps.hpp:1052)
+    float o_acc[AT_HD];
+#pragma unroll
+    for (int c = 0; c < AT_HD; ++c) o_acc[c] = 0.0f;
+    uint8_t* p_row_hi = sP + r_local * 128;
+    uint8_t* p_row_lo = p_row_hi + AT_P_BYTES;
+    const int sw = r_local & 7;  // 128-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ (r % 8)
+    bool alive = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const uint32_t ph = j & 1;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(s_full, ph, abort_flag, p.err_word, 19) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { alive = false; break; }
+      while (!mbar_try_wait(s_full, ph)) {}
+      tcgen05_fence_after();
+      const int key0 = j * AT_BK;
+      // pass 1: row maximum of the valid scores
+      float mx = -1e30f;
+      float v[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_ld_32x32(tmem_s + lane_base + half * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + half * 32 + i;
+          const bool valid = key < p.seq && (!p.causal || key <= row);
+          if (valid) mx = fmaxf(mx, v[i] * p.scale);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = __expf(m_run - m_new);
+      float rs = 0.0f;
+      // pass 2: probabilities, written as bf16 hi / lo in the layout the PV MMA reads
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_ld_32x32(tmem_s + lane_base + half * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = key0 + half * 32 + i;
+          const bool valid = key < p.seq && (!p.causal || key <= row);
+          v[i] = valid ? __expf(v[i] * p.scale - m_new) : 0.0f;
+          rs += v[i];
+        }
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {  // four 16-byte chunks of 8 keys per 32 keys
+          __align__(16) __nv_bfloat16 hi[8];
+          __align__(16) __nv_bfloat16 lo[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            hi[e] = __float2bfloat16_rn(v[c8 * 8 + e]);
+            lo[e] = __float2bfloat16_rn(v[c8 * 8 + e] - __bfloat162float(hi[e]));
+          }
+          const int chunk = (half * 4 + c8) ^ sw;
+          *reinterpret_cast<uint4*>(p_row_hi + chunk * 16) = *reinterpret_cast<const uint4*>(hi);
+          *reinterpret_cast<uint4*>(p_row_lo + chunk * 16) = *reinterpret_cast<const uint4*>(lo);
+        }
+      }
+      l_run = l_run * corr + rs;
+      m_run = m_new;
+      // S has been read twice and P is in shared memory: publish both
+      tcgen05_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_empty);
+        mbar_arrive(p_full);
+      }
+      // PV_j -> registers
+      if (lane == 0) ok = mbar_wait(o_full, ph, abort_flag, p.err_word, 20) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { alive = false; break; }
+      while (!mbar_try_wait(o_full, ph)) {}
+      tcgen05_fence_after();
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        tmem_ld_32x32(tmem_o + lane_base + half * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[half * 32 + i] = fmaf(o_acc[half * 32 + i], corr, v[i]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_empty);
+    }
+    if (alive && row < p.seq) {
+      const float inv = 1.0f / (l_run + 1e-9f);  // LayerOps.hpp:1076
+      const int b = bhi / p.heads, h = bhi - b * p.heads;
+      float* o = p.out + (static_cast<long long>(b) * p.seq + row) * p.embed + h * AT_HD;
+#pragma unroll
+      for (int c = 0; c < AT_HD; c += 4)
+        *reinterpret_cast<float4*>(o + c) = make_float4(o_acc[c] * inv, o_acc[c + 1] * inv, o_acc[c + 2] * inv, o_acc[c + 3] * inv);
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, AT_TMEM_COLS);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int make_map3(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1) {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  if (!fn) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return MIMIR_B200_OK;
+}
+
+}  // namespace
+
+bool attention_tc_supported(int seq, int embed, int heads) {
+  const char* off = getenv("MIMIR_B200_ATTN_FP32");
+  if (off && off[0] == '1') return false;
+  return heads > 0 && embed == heads * AT_HD && seq >= 1;
+}
+
+size_t attention_tc_ws_bytes(int batch, int seq, int embed) {
+  const size_t seqp = static_cast<size_t>(round_up(seq, 64));
+  const size_t qk = 2ull * batch * seq * embed * 2;      // two planes of bf16
+  const size_t v = 2ull * batch * embed * seqp * 2;
+  return ((2 * qk + 255) & ~size_t(255)) + ((v + 255) & ~size_t(255)) + 512;
+}
+
+int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, void* ws,
+                             cudaStream_t st) {
+  if (!attention_tc_supported(seq, embed, heads)) return fail(MIMIR_B200_E_UNSUPPORTED, "attention: tensor-core core needs head_dim 64");
+  const int bh = batch * heads;
+  const int seqp = round_up(seq, 64);
+  if (bh > 65535 / 2) return fail(MIMIR_B200_E_UNSUPPORTED, "attention: batch * heads too large for one launch");
+  uint8_t* w = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
+  const size_t qk_bytes = 2ull * batch * seq * embed * 2;
+  __nv_bfloat16* qp = reinterpret_cast<__nv_bfloat16*>(w);
+  __nv_bfloat16* kp = reinterpret_cast<__nv_bfloat16*>(w + qk_bytes);
+  __nv_bfloat16* vt = reinterpret_cast<__nv_bfloat16*>(w + ((2 * qk_bytes + 255) & ~size_t(255)));
+  dim3 pgrid(seqp / 64, bh);
+  attn_prep_kernel<<<pgrid, 256, 0, st>>>(qkv, qp, kp, vt, seq, seqp, embed, heads, bh);
+  MB_CUDA(cudaGetLastError());
+  CUtensorMap mq, mk, mv;
+  MB_TRY(make_map3(&mq, qp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BQ));
+  MB_TRY(make_map3(&mk, kp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BK));
+  MB_TRY(make_map3(&mv, vt, static_cast<uint64_t>(seqp), AT_HD, 2ull * bh, AT_BK, AT_HD));
+  static bool attr = false;
+  if (!attr) {
+    MB_CUDA(cudaFuncSetAttribute(flash_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
+    attr = true;
+  }
+  AttnParams p;
+  p.out = out;
+  p.seq = seq; p.embed = embed; p.heads = heads; p.causal = causal; p.bh = bh;
+  p.scale = 1.0f / sqrtf(static_cast<float>(AT_HD));
+  p.err_word = ctx().dev_error_word;
+  dim3 grid((seq + AT_BQ - 1) / AT_BQ, bh);
+  flash_attn_tc_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(mq, mk, mv, p);
+  MB_CUDA(cudaGetLastError());
+  count_launch(2);
+  return MIMIR_B200_OK;
+}
+
+}  // namespace mb

@@ -141,11 +141,13 @@ int linear_exec(const LinearExec& e, cudaStream_t st) {
 
 // Attention = QKV projection (GEMM) -> flash core -> output projection (GEMM).
 // Workspace: split(x) | qkv fp32 | attended fp32 | split(attended)
-size_t attention_ws_bytes(int rows, int embed, int precision) {
+size_t attention_ws_bytes(int batch, int seq, int embed, int heads, int precision) {
   int ap, wp;
   precision_planes(precision, &ap, &wp);
-  return align256(split_bytes(rows, embed, ap)) + align256(static_cast<size_t>(rows) * 3 * embed * 4) +
-         align256(static_cast<size_t>(rows) * embed * 4);
+  const size_t rows = static_cast<size_t>(batch) * seq;
+  size_t b = align256(split_bytes(static_cast<int64_t>(rows), embed, ap)) + align256(rows * 3 * embed * 4) + align256(rows * embed * 4);
+  if (attention_tc_supported(seq, embed, heads)) b += align256(attention_tc_ws_bytes(batch, seq, embed));
+  return b;
 }
 
 int attention_exec(const AttentionExec& e, cudaStream_t st) {
@@ -156,12 +158,16 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(ws);
   float* qkv = reinterpret_cast<float*>(ws + align256(split_bytes(rows, e.embed, ap)));
   float* att = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(qkv) + align256(static_cast<size_t>(rows) * 3 * e.embed * 4));
+  uint8_t* tc_ws = reinterpret_cast<uint8_t*>(att) + align256(static_cast<size_t>(rows) * e.embed * 4);
   MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
   GemmArgs g;
   g.a = xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
   g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
   MB_TRY(launch_gemm(g, st));
-  MB_TRY(launch_attention_core(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, st));
+  if (attention_tc_supported(e.seq, e.embed, e.heads))
+    MB_TRY(launch_attention_core_tc(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, tc_ws, st));
+  else
+    MB_TRY(launch_attention_core(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, st));
   MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));  // the x planes are dead by now
   GemmArgs o;
   o.a = xs; o.w = e.wout_split; o.a_planes = ap; o.w_planes = wp;
@@ -432,7 +438,7 @@ int mimir_b200_attention(const float* x, const float* wqkv_wout, float* y, int b
   MB_TRY(launch_split_transposed(w + 3 * E * E, static_cast<__nv_bfloat16*>(wo), embed, embed, 2, nullptr));
   e.wqkv_split = static_cast<const __nv_bfloat16*>(wq);
   e.wout_split = static_cast<const __nv_bfloat16*>(wo);
-  MB_TRY(t.alloc(&e.ws, attention_ws_bytes(static_cast<int>(rows), embed, e.precision), "attn.ws"));
+  MB_TRY(t.alloc(&e.ws, attention_ws_bytes(batch, seq, embed, heads, e.precision), "attn.ws"));
   MB_TRY(attention_exec(e, nullptr));
   return finish_download(y, e.y, rows * E);
 }

@@ -129,6 +129,11 @@ int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softm
 // qkv fp32 [batch*seq, 3E] (Q | K | V thirds) -> attended fp32 [batch*seq, E]
 int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
                           cudaStream_t st);
+// attention_tc.cu: the same core on tcgen05 (head_dim 64); `ws` holds the bf16 operand planes
+bool attention_tc_supported(int seq, int embed, int heads);
+size_t attention_tc_ws_bytes(int batch, int seq, int embed);
+int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, void* ws,
+                             cudaStream_t st);
 
 // conv2d.cu ------------------------------------------------------------------------------------
 // im2col of NCHW fp32 into split planes [planes][batch*oh*ow][kp], k = ic*ks*ks ordered (ic, kh, kw)

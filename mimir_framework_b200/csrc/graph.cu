@@ -546,7 +546,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
           break;
         case LT::Attention: {
           const int64_t r = static_cast<int64_t>(batch) * L.seq;
-          L.ws_bytes = attention_ws_bytes(static_cast<int>(r), L.embed, m->precision);
+          L.ws_bytes = attention_ws_bytes(batch, L.seq, L.embed, L.heads, m->precision);
           const uint64_t core = 4ull * batch * L.seq * L.seq * L.embed;
           flops += 2ull * r * L.embed * 4 * L.embed + (L.d.causal ? core / 2 : core);
           break;

@@ -41,7 +41,7 @@ struct AttentionExec {
   float* y = nullptr;
   void* ws = nullptr;
 };
-size_t attention_ws_bytes(int rows, int embed, int precision);
+size_t attention_ws_bytes(int batch, int seq, int embed, int heads, int precision);
 int attention_exec(const AttentionExec& e, cudaStream_t st);
 
 struct ConvExec {

@@ -92,6 +92,10 @@ def test_matmul_reference_known_answer(backend):
     (1, 96, 128, 4, 1),                       # head_dim 32
     (1, 70, 256, 2, 0),                       # head_dim 128
     (1, 64, 512, 1, 0),                       # single head, head_dim 512 (UNet mid-block shape class)
+    (3, 129, 192, 3, 1),                      # tensor-core core (head_dim 64): one row past a query tile
+    (1, 1, 64, 1, 0),                         # tensor-core core: a single token
+    (2, 63, 128, 2, 0),                       # tensor-core core: ragged key tile
+    (1, 1024, 128, 2, 1),                     # tensor-core core: decoder sequence length, causal
 ])
 def test_attention(backend, batch, seq, E, heads, causal):
     r = rng(seq + E + heads + causal)
