@@ -14,9 +14,9 @@
 //   warp 0      : TMA producer  — cp.async.bulk.tensor (no multicast) into a ring of smem stages
 //   warp 1      : MMA issuer    — one thread issues tcgen05.mma, operands from smem descriptors,
 //                                 accumulators in TMEM (2 x 256 columns, double buffered)
-//   warps 2..9  : epilogue      — tcgen05.ld TMEM -> registers -> 32x33 shared-memory transpose, bias /
-//                                 activation / residual, coalesced stores of fp32 rows and/or the bf16
-//                                 hi/lo planes of the next layer (or channel-major NCHW for convs)
+//   warps 2..9  : epilogue      — tcgen05.ld TMEM -> registers, bias / activation / residual, 256-bit
+//                                 stores of fp32 rows and/or the bf16 hi/lo planes of the next layer
+//                                 (or channel-major NCHW for convs)
 // Every mbarrier wait is bounded: after ~2 s it sets the device error word and the CTA drains.
 #include "common.h"
 #include "sm100_ptx.cuh"
@@ -32,7 +32,6 @@ constexpr int NUM_ACC = 2;     // TMEM accumulator buffers
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 320;  // 10 warps: TMA, MMA, 8 epilogue
 constexpr int EPI_WARPS = 8;
-constexpr int EPI_PATCH_BYTES = EPI_WARPS * 32 * 33 * 4;
 
 // GELU in the reference's tanh form (LayerOps.hpp:556-568); the constant is
 // sqrt(2.0f / 3.14159265359f) evaluated in fp32.
@@ -105,7 +104,6 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   uint64_t* acc_empty = acc_full + NUM_ACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* epi_patch = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -212,15 +210,12 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else {
     // ------------------------------ epilogue (warps 2..9) ---------------------------------
-    // Two warps per TMEM lane quadrant, each owning half of the tile's columns.  Row-major outputs are
-    // transposed through a 32 x 33 shared-memory patch so that a warp instruction writes one full
-    // 128-byte row segment (lane <-> column); bias, activation and residual are applied on that side,
-    // where their loads are coalesced too.  Channel-major (NCHW) outputs are already coalesced with
-    // lane <-> pixel and skip the patch.
+    // Two warps per TMEM lane quadrant, each owning half of the tile's columns.  A lane holds 32 consecutive
+    // columns of its row: row-major outputs leave as whole 128-byte lines through 256-bit stores;
+    // channel-major (NCHW) outputs are coalesced across lanes (lane <-> pixel).
     const int ew = warp - 2;
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
     const int half = ew >> 2;    // which half of the columns
-    float* patch = epi_patch + ew * (32 * 33);
     const bool chan_major = (p.ohw > 0 || p.conv_ks > 0);
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -265,42 +260,100 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (col0 >= col_limit) break;  // warp-uniform
         float v[32];
         tmem_ld_32x32(taddr0 + c0, v);
-        const int col = col0 + lane;  // this lane's column on the transposed side
-        const float bias_l = (p.bias != nullptr && col < p.n) ? __ldg(p.bias + col) : 0.0f;
-        if (chan_major) {
+        const bool full_cols = (col0 + 32 <= p.n);
+        // bias: the same 32 values for every lane (broadcast loads)
+        if (p.bias != nullptr) {
+          if (full_cols && ((reinterpret_cast<uintptr_t>(p.bias + col0) & 15) == 0)) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float b = __shfl_sync(0xffffffffu, bias_l, j);
-            if (cm_ok && col0 + j < p.n) {
-              const long long oi = cm_o0 + static_cast<long long>(col0 + j) * cm_stride;
-              float r = apply_act(v[j] + b, p.activation);
-              if (p.residual != nullptr) r += __ldg(p.residual + oi);
-              p.out_f32[oi] = r;
+            for (int j = 0; j < 32; j += 4) {
+              const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + j));
+              v[j] += b4.x; v[j + 1] += b4.y; v[j + 2] += b4.z; v[j + 3] += b4.w;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.n) v[j] += __ldg(p.bias + col0 + j);
+          }
+        }
+        switch (p.activation) {  // hoisted out of the element loop
+          case MIMIR_B200_ELT_GELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_ref(v[j]);
+            break;
+          case -1:
+            break;
+          default:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.activation);
+            break;
+        }
+        if (chan_major) {
+          if (cm_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (full_cols || col0 + j < p.n) {
+                const long long oi = cm_o0 + static_cast<long long>(col0 + j) * cm_stride;
+                float r = v[j];
+                if (p.residual != nullptr) r += __ldg(p.residual + oi);
+                p.out_f32[oi] = r;
+              }
             }
           }
         } else {
+          // row-major: this lane owns 32 consecutive columns of its row = one 128-byte line, moved with
+          // 256-bit loads / stores (full 32-byte sectors, no transposition needed)
+          const int row = row0 + lane;
+          if (row < p.m) {
+            const long long ro = static_cast<long long>(row) * p.ldo + col0;
+            if (p.residual != nullptr) {
+              const float* rr = p.residual + ro;
+              if (full_cols && ((reinterpret_cast<uintptr_t>(rr) & 31) == 0)) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) patch[lane * 33 + j] = v[j];
-          __syncwarp();
-          const bool col_ok = col < p.n;
-          const int rows_here = min(32, p.m - row0);
-#pragma unroll 4
-          for (int i = 0; i < rows_here; ++i) {
-            float r = apply_act(patch[i * 33 + lane] + bias_l, p.activation);
-            const long long row = row0 + i;
-            if (p.residual != nullptr && col_ok) r += __ldg(p.residual + row * p.ldo + col);
-            if (p.out_f32 != nullptr && col_ok) p.out_f32[row * p.ldo + col] = r;
+                for (int j = 0; j < 32; j += 8) {
+                  float q[8];
+                  ld_global_v8(rr + j, q);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[j + e] += q[e];
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.n) v[j] += __ldg(rr + j);
+              }
+            }
+            if (p.out_f32 != nullptr) {
+              float* o = p.out_f32 + ro;
+              if (full_cols && ((reinterpret_cast<uintptr_t>(o) & 31) == 0)) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) st_global_v8(o + j, &v[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.n) o[j] = v[j];
+              }
+            }
             if (p.out_split != nullptr) {
               // hi/lo planes for the next GEMM; columns n..np-1 are written as zero so that the padded
-              // K of the consumer stays zero
-              const float x = col_ok ? r : 0.0f;
-              const __nv_bfloat16 hi = __float2bfloat16_rn(x);
-              __nv_bfloat16* oh = p.out_split + row * p.np + col;
-              oh[0] = hi;
-              oh[static_cast<long long>(p.m) * p.np] = __float2bfloat16_rn(x - __bfloat162float(hi));
+              // K of the consumer stays zero (np is a multiple of 64, so the chunk is always whole)
+              uint32_t hi[16], lo[16];
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const float x0 = (full_cols || col0 + j < p.n) ? v[j] : 0.0f;
+                const float x1 = (full_cols || col0 + j + 1 < p.n) ? v[j + 1] : 0.0f;
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
+                const float2 hf = __bfloat1622float2(h2);
+                const __nv_bfloat162 l2 = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
+                hi[j >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+                lo[j >> 1] = *reinterpret_cast<const uint32_t*>(&l2);
+              }
+              __nv_bfloat16* oh = p.out_split + static_cast<long long>(row) * p.np + col0;
+              __nv_bfloat16* ol = oh + static_cast<long long>(p.m) * p.np;
+              st_global_v8_b32(oh, &hi[0]);
+              st_global_v8_b32(oh + 16, &hi[8]);
+              st_global_v8_b32(ol, &lo[0]);
+              st_global_v8_b32(ol + 16, &lo[8]);
             }
           }
-          __syncwarp();
         }
       }
       tcgen05_fence_before();
@@ -457,7 +510,7 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.ohw = g.out_nchw_hw;
   p.err_word = ctx().dev_error_word;
   constexpr int STAGE_BYTES = 2 * BM * BK * 2 + 2 * BN * BK * 2;
-  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_PATCH_BYTES;
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ ;
   static_assert(SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   auto kern = gemm_tn_bf16split_kernel<BK, STAGES>;
   static bool attr_set = false;
