@@ -207,45 +207,55 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       while (!mbar_try_wait(s_full, ph)) {}
       tcgen05_fence_after();
       const int key0 = j * AT_BK;
-      // pass 1: row maximum of the valid scores
+      // the whole tile of scores for this row, read once
+      uint32_t sa[32], sb[32];
+      tmem_ld_32x32_nowait(tmem_s + lane_base, sa);
+      tmem_ld_32x32_nowait(tmem_s + lane_base + 32, sb);
+      tmem_wait_ld();
+      // Tiles left of the diagonal and inside the sequence need no masking (warp-uniform test on the
+      // warp's first row, which is the most restrictive one for the causal bound).
+      const int row_first = q0 + quad * 32;
+      const bool full_tile = (key0 + AT_BK <= p.seq) && (!p.causal || key0 + AT_BK - 1 <= row_first);
+      const float c2 = p.scale * 1.4426950408889634f;  // scores are kept in the exp2 domain: s * scale * log2(e)
       float mx = -1e30f;
-      float v[32];
+      if (full_tile) {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tmem_ld_32x32(tmem_s + lane_base + half * 32, v);
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
+      } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int key = key0 + half * 32 + i;
-          const bool valid = key < p.seq && (!p.causal || key <= row);
-          if (valid) mx = fmaxf(mx, v[i] * p.scale);
+          const int ka = key0 + i, kb = key0 + 32 + i;
+          if (!(ka < p.seq && (!p.causal || ka <= row))) sa[i] = 0xff800000u;  // -inf: contributes exp2(-inf) = 0
+          if (!(kb < p.seq && (!p.causal || kb <= row))) sb[i] = 0xff800000u;
+          mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
         }
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float corr = __expf(m_run - m_new);
+      // running maximum in score units (the reference's -1e30 start: LayerOps.hpp:1052)
+      const float m_new = fmaxf(m_run, (mx > -1e30f) ? mx * p.scale : -1e30f);
+      const float corr = exp2f((m_run - m_new) * 1.4426950408889634f);
+      const float m2 = m_new * 1.4426950408889634f;
       float rs = 0.0f;
-      // pass 2: probabilities, written as bf16 hi / lo in the layout the PV MMA reads
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        tmem_ld_32x32(tmem_s + lane_base + half * 32, v);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = key0 + half * 32 + i;
-          const bool valid = key < p.seq && (!p.causal || key <= row);
-          v[i] = valid ? __expf(v[i] * p.scale - m_new) : 0.0f;
-          rs += v[i];
-        }
+        for (int c8 = 0; c8 < 4; ++c8) {  // 16-byte chunks of 8 keys
+          uint32_t hi[4], lo[4];
 #pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {  // four 16-byte chunks of 8 keys per 32 keys
-          __align__(16) __nv_bfloat16 hi[8];
-          __align__(16) __nv_bfloat16 lo[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            hi[e] = __float2bfloat16_rn(v[c8 * 8 + e]);
-            lo[e] = __float2bfloat16_rn(v[c8 * 8 + e] - __bfloat162float(hi[e]));
+          for (int e = 0; e < 8; e += 2) {
+            const uint32_t u0 = half ? sb[c8 * 8 + e] : sa[c8 * 8 + e];
+            const uint32_t u1 = half ? sb[c8 * 8 + e + 1] : sa[c8 * 8 + e + 1];
+            const float p0 = exp2f(fmaf(__uint_as_float(u0), c2, -m2));
+            const float p1 = exp2f(fmaf(__uint_as_float(u1), c2, -m2));
+            rs += p0 + p1;
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+            const float2 hf = __bfloat1622float2(h2);
+            const __nv_bfloat162 l2 = __floats2bfloat162_rn(p0 - hf.x, p1 - hf.y);
+            hi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+            lo[e >> 1] = *reinterpret_cast<const uint32_t*>(&l2);
           }
           const int chunk = (half * 4 + c8) ^ sw;
-          *reinterpret_cast<uint4*>(p_row_hi + chunk * 16) = *reinterpret_cast<const uint4*>(hi);
-          *reinterpret_cast<uint4*>(p_row_lo + chunk * 16) = *reinterpret_cast<const uint4*>(lo);
+          *reinterpret_cast<uint4*>(p_row_hi + chunk * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          *reinterpret_cast<uint4*>(p_row_lo + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
       }
       l_run = l_run * corr + rs;
@@ -264,11 +274,13 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (!ok) { alive = false; break; }
       while (!mbar_try_wait(o_full, ph)) {}
       tcgen05_fence_after();
+      tmem_ld_32x32_nowait(tmem_o + lane_base, sa);
+      tmem_ld_32x32_nowait(tmem_o + lane_base + 32, sb);
+      tmem_wait_ld();
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        tmem_ld_32x32(tmem_o + lane_base + half * 32, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[half * 32 + i] = fmaf(o_acc[half * 32 + i], corr, v[i]);
+      for (int i = 0; i < 32; ++i) {
+        o_acc[i] = fmaf(o_acc[i], corr, __uint_as_float(sa[i]));
+        o_acc[32 + i] = fmaf(o_acc[32 + i], corr, __uint_as_float(sb[i]));
       }
       tcgen05_fence_before();
       __syncwarp();
