@@ -289,15 +289,19 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
         if (chan_major) {
           if (cm_ok) {
+            const long long o0 = cm_o0 + static_cast<long long>(col0) * cm_stride;
+            if (p.residual != nullptr) {
+              // all loads first: the output may alias nothing here, but the compiler cannot know, and
+              // load -> store -> load chains would serialise on memory latency
+              float q[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (full_cols || col0 + j < p.n) {
-                const long long oi = cm_o0 + static_cast<long long>(col0 + j) * cm_stride;
-                float r = v[j];
-                if (p.residual != nullptr) r += __ldg(p.residual + oi);
-                p.out_f32[oi] = r;
-              }
+              for (int j = 0; j < 32; ++j) q[j] = (full_cols || col0 + j < p.n) ? __ldg(p.residual + o0 + j * cm_stride) : 0.0f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += q[j];
             }
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full_cols || col0 + j < p.n) p.out_f32[o0 + j * cm_stride] = v[j];
           }
         } else {
           // row-major: this lane owns 32 consecutive columns of its row = one 128-byte line, moved with

@@ -83,6 +83,7 @@ struct LayerRT {
   bool emit_split = false;            // GEMM writes hi/lo planes for the consuming Linear
   bool emit_f32 = true;
   bool read_split = false;            // Linear reads the producer's planes
+  int res_v = -1;                     // residual tensor folded in from a following Add
   size_t ws_off = 0, ws_bytes = 0;
   // resolved shapes (per sample)
   int rows_ps = 1, in_f = 0, out_f = 0;       // Linear
@@ -423,7 +424,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     LayerRT& L = m->layers[li];
     L.in_v.clear();
     L.out_v = -1;
-    L.skip = false; L.fused_act = -1; L.emit_split = false; L.emit_f32 = true; L.read_split = false;
+    L.skip = false; L.fused_act = -1; L.emit_split = false; L.emit_f32 = true; L.read_split = false; L.res_v = -1;
     L.ws_off = 0; L.ws_bytes = 0;
     std::vector<std::string> names = L.inputs;
     if (names.empty()) names.push_back("x");
@@ -479,6 +480,37 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     pt.producer = -2;  // dead
     A.skip = true;
   }
+  // ---- fusion 1b: a residual Add into the epilogue of the layer that produces one of its operands -------
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& A = m->layers[li];
+    if (A.lt != LT::Add || A.skip || A.in_v.size() != 2) continue;
+    if (m->tensors[A.in_v[0]].n != m->tensors[A.in_v[1]].n) continue;  // broadcast adds stay separate
+    for (int side = 0; side < 2; ++side) {
+      const int uv = A.in_v[side], ov = A.in_v[1 - side];
+      TensorV& ut = m->tensors[uv];
+      if (ut.alias_of >= 0 || ut.producer < 0 || uv == out_root || uv == ov || total_consumers(uv) != 1) continue;
+      LayerRT& P = m->layers[ut.producer];
+      if (P.out_v != uv || P.res_v >= 0 || P.skip) continue;
+      const bool gemm_like = (P.lt == LT::Linear && !linear_uses_skinny(P.rows_ps * batch, m->precision)) ||
+                             P.lt == LT::Attention || P.lt == LT::Conv2d;
+      if (!gemm_like && P.lt != LT::GroupNorm) continue;
+      // the other operand must already exist when P runs
+      const int orr = root_of(m->tensors, ov);
+      const TensorV& ot = m->tensors[orr];
+      if (ot.producer >= ut.producer || ot.producer == -2 || !ot.want_f32) continue;
+      P.res_v = ov;
+      P.out_v = A.out_v;
+      m->tensors[A.out_v].producer = ut.producer;
+      // ov is now read by P instead of A
+      for (int& c : m->tensors[ov].consumers)
+        if (c == li) c = ut.producer;
+      ut.consumers.clear();
+      ut.want_f32 = false;
+      ut.producer = -2;  // dead
+      A.skip = true;
+      break;
+    }
+  }
   // ---- fusion 2: hi/lo planes straight from one GEMM epilogue into the next Linear -------------
   for (int li = 0; li < nl; ++li) {
     LayerRT& C = m->layers[li];
@@ -488,7 +520,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     TensorV& t = m->tensors[v];
     if (t.alias_of >= 0 || t.producer < 0 || v == out_root || total_consumers(v) != 1) continue;
     LayerRT& P = m->layers[t.producer];
-    if (P.lt != LT::Linear || P.out_v != v || P.out_f != C.in_f || P.rows_ps != C.rows_ps) continue;
+    if (P.lt != LT::Linear || P.out_v != v || P.out_f != C.in_f || P.rows_ps != C.rows_ps || P.res_v >= 0) continue;
     if (linear_uses_skinny(P.rows_ps * batch, m->precision)) continue;
     P.emit_split = true;
     P.emit_f32 = false;
@@ -633,6 +665,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.w_split = L.w_split;
         e.bias = d.use_bias ? L.w_f32 + static_cast<size_t>(L.in_f) * L.out_f : nullptr;
         e.activation = L.fused_act;
+        if (L.res_v >= 0) e.residual = f32p(L.res_v);
         if (L.emit_f32) e.y_f32 = f32p(L.out_v);
         if (L.emit_split) e.y_split = splitp(L.out_v);
         e.ws = ws; e.ws_bytes = L.ws_bytes;
@@ -644,6 +677,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.batch = batch; e.seq = L.seq; e.embed = L.embed; e.heads = L.heads; e.causal = d.causal;
         e.precision = m->precision;
         e.x = f32p(L.in_v[0]); e.wqkv_split = L.w_split; e.wout_split = L.w_split2; e.y = f32p(L.out_v); e.ws = ws;
+        if (L.res_v >= 0) e.residual = f32p(L.res_v);
         s = attention_exec(e, st);
         break;
       }
@@ -653,6 +687,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.stride = d.stride; e.pad = d.padding; e.precision = m->precision;
         e.activation = d.activation ? MIMIR_B200_ELT_RELU : L.fused_act;
         e.x = f32p(L.in_v[0]); e.w_split = L.w_split; e.y = f32p(L.out_v); e.ws = ws;
+        if (L.res_v >= 0) e.residual = f32p(L.res_v);
         s = conv_exec(e, st);
         break;
       }
@@ -673,7 +708,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         const float* g = d.affine ? L.w_f32 : nullptr;
         const float* b = (d.affine && d.use_bias) ? L.w_f32 + L.ch : nullptr;
         s = launch_groupnorm(f32p(L.in_v[0]), g, b, f32p(L.out_v), batch, L.ch, L.h * L.w, d.num_groups, d.eps, L.fused_act,
-                             nullptr, st);
+                             L.res_v >= 0 ? f32p(L.res_v) : nullptr, st);
         break;
       }
       case LT::Softmax:
