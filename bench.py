@@ -130,7 +130,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"Linear+bias+GELU x3, K=N={K}, CPU sample of {rows} rows per step (rows are independent)"},
+        "config": {"workload": f"Linear+bias+GELU x3, K=N={K}, M={args.rows} fp32 rows per GPU", "rows_per_gpu": args.rows,
+                   "sample": f"each step times {rows} of the rows on the host cores (rows are independent)"},
         "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": "reference",
                          "sample": f"{rows} rows per step, median of {args.steps} steps, reference CPU code, OpenMP threads = {cores}"},
         "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -289,7 +290,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=65536, help="rows per GPU")
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--pipeline", type=int, default=8, help="micro-batches of the end-to-end (host pointer) arm")
+    ap.add_argument("--pipeline", type=int, default=16, help="micro-batches of the end-to-end (host pointer) arm")
     ap.add_argument("--cpu-rows", type=int, default=2048, help="rows of the CPU-baseline sample")
     ap.add_argument("--ref-rows", type=int, default=1024, help="rows per step of --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -173,52 +173,73 @@ constexpr int SEQ_PER_THREAD = 32;  // CHUNK / 256 threads
 
 __global__ void __launch_bounds__(256) rms_seq_err_kernel(const float* __restrict__ x, const float* __restrict__ part,
                                                           double* __restrict__ seq_err, long long len, int chunks, int chunk_len) {
-  __shared__ float sx[CHUNK + CHUNK / 32];  // padded: thread t reads sx[t * 33 + j]
-  __shared__ double sscan[256];
+  __shared__ float wsum[8];
+  __shared__ double werr[8];
   const long long row = blockIdx.y;
   const int c = blockIdx.x;
   const long long off = static_cast<long long>(c) * chunk_len;
   const int n = static_cast<int>(min(static_cast<long long>(chunk_len), len - off));
   const float* g = x + row * len + off;
-  for (int i = threadIdx.x; i < chunk_len; i += blockDim.x) sx[i + i / SEQ_PER_THREAD] = (i < n) ? __ldg(g + i) : 0.0f;
-  double prefix = 0.0;  // exact sum of the squares before this chunk
-  for (int j = 0; j < c; ++j) prefix += static_cast<double>(part[row * chunks + j]);
-  __syncthreads();
-  const float* mine = sx + threadIdx.x * (SEQ_PER_THREAD + 1);
-  double local = 0.0;
-#pragma unroll
-  for (int j = 0; j < SEQ_PER_THREAD; ++j) local += static_cast<double>(mine[j]) * static_cast<double>(mine[j]);
-  // exclusive scan of the per-thread sums (Hillis-Steele over 256 entries)
-  sscan[threadIdx.x] = local;
-  __syncthreads();
-  for (int d = 1; d < 256; d <<= 1) {
-    const double v = (threadIdx.x >= d) ? sscan[threadIdx.x - d] : 0.0;
-    __syncthreads();
-    sscan[threadIdx.x] += v;
-    __syncthreads();
-  }
-  const double before = prefix + sscan[threadIdx.x] - local;
-  float sf = static_cast<float>(before);  // on the chain's grid: same binade as the true running sum
-  double err = 0.0;
+  // this thread's 32 consecutive elements (one 128-byte line), straight into registers
+  float mine[SEQ_PER_THREAD];
   const int first = threadIdx.x * SEQ_PER_THREAD;
-#pragma unroll 8
+  if (first + SEQ_PER_THREAD <= n && ((reinterpret_cast<uintptr_t>(g + first) & 15) == 0)) {
+#pragma unroll
+    for (int j = 0; j < SEQ_PER_THREAD; j += 4) {
+      const float4 v4 = __ldg(reinterpret_cast<const float4*>(g + first + j));
+      mine[j] = v4.x; mine[j + 1] = v4.y; mine[j + 2] = v4.z; mine[j + 3] = v4.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < SEQ_PER_THREAD; ++j) mine[j] = (first + j < n) ? __ldg(g + first + j) : 0.0f;
+  }
+  // sum of the squares before this chunk; only its binade matters, fp32 chunk sums added in double are ample
+  double prefix = 0.0;
+  for (int j = 0; j < c; ++j) prefix += static_cast<double>(part[row * chunks + j]);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  float local = 0.0f;
+#pragma unroll
+  for (int j = 0; j < SEQ_PER_THREAD; ++j) local = fmaf(mine[j], mine[j], local);
+  // exclusive prefix of the per-thread sums: warp scan, then the eight warp totals
+  float scan = local;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, scan, d);
+    if (lane >= d) scan += t;
+  }
+  if (lane == 31) wsum[w] = scan;
+  __syncthreads();
+  float wbase = 0.0f;
+  for (int k = 0; k < w; ++k) wbase += wsum[k];
+  float sf = static_cast<float>(prefix + static_cast<double>(wbase + (scan - local)));  // on the chain's grid
+  // replay this thread's stretch of the chain; every step's rounding error is recovered exactly with
+  // error-free transformations: T = sf + v*v exactly equals s1 + e2 + e1, and nf = round(T)
+  float err = 0.0f;
+#pragma unroll
   for (int j = 0; j < SEQ_PER_THREAD; ++j) {
     if (first + j < n) {
       const float v = mine[j];
-      const float nf = fmaf(v, v, sf);
-      err += static_cast<double>(nf) - (static_cast<double>(sf) + static_cast<double>(v) * static_cast<double>(v));
+      const float nf = fmaf(v, v, sf);          // what the reference computes
+      // (__fmul_rn / __fadd_rn are never contracted into an FMA, which would defeat the transformations)
+      const float pr = __fmul_rn(v, v);
+      const float e1 = fmaf(v, v, -pr);         // product error
+      const float s1 = __fadd_rn(sf, pr);
+      const float bb = __fadd_rn(s1, -sf);
+      const float e2 = __fadd_rn(__fadd_rn(sf, -__fadd_rn(s1, -bb)), __fadd_rn(pr, -bb));  // TwoSum error
+      err += __fadd_rn(__fadd_rn(__fadd_rn(nf, -s1), -e2), -e1);
       sf = nf;
     }
   }
-  // block sum of the errors
+  double e = static_cast<double>(err);
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) e += __shfl_xor_sync(0xffffffffu, e, d);
+  if (lane == 0) werr[w] = e;
   __syncthreads();
-  sscan[threadIdx.x] = err;
-  __syncthreads();
-  for (int d = 128; d > 0; d >>= 1) {
-    if (threadIdx.x < d) sscan[threadIdx.x] += sscan[threadIdx.x + d];
-    __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int k = 0; k < 8; ++k) t += werr[k];
+    seq_err[row * chunks + c] = t;
   }
-  if (threadIdx.x == 0) seq_err[row * chunks + c] = sscan[0];
 }
 
 __global__ void rms_chunk_apply_kernel(const float* __restrict__ x, const float* __restrict__ gamma, long long n_gamma,
