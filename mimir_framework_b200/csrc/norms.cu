@@ -346,16 +346,33 @@ struct RowParams {
 
 __device__ __forceinline__ float silu_fast(float v) { return v * __fdividef(1.0f, 1.0f + __expf(-v)); }
 
+// Visits the 128-bit vectors of a row in this thread's grid-stride order with four loads in flight
+// before the first use (the rows are streamed from HBM / L2: memory-level parallelism is what counts).
+template <bool STREAMING, class F>
+__device__ __forceinline__ void for_each_vec4(const float4* __restrict__ g4, int n4, F body) {
+  const int step = blockDim.x;
+  int i = threadIdx.x;
+  for (; i + 3 * step < n4; i += 4 * step) {
+    float4 a, b, c, d;
+    if (STREAMING) {
+      a = __ldcs(g4 + i); b = __ldcs(g4 + i + step); c = __ldcs(g4 + i + 2 * step); d = __ldcs(g4 + i + 3 * step);
+    } else {
+      a = __ldg(g4 + i); b = __ldg(g4 + i + step); c = __ldg(g4 + i + 2 * step); d = __ldg(g4 + i + 3 * step);
+    }
+    body(i, a);
+    body(i + step, b);
+    body(i + 2 * step, c);
+    body(i + 3 * step, d);
+  }
+  for (; i < n4; i += step) body(i, STREAMING ? __ldcs(g4 + i) : __ldg(g4 + i));
+}
+
 template <class F>
 __device__ __forceinline__ void sweep_read(const float* __restrict__ g, long long n, bool vec, F f) {
   if (vec) {
-    const float4* g4 = reinterpret_cast<const float4*>(g);
-    const int n4 = static_cast<int>(n >> 2);
-#pragma unroll 4
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-      const float4 v = __ldg(g4 + i);
+    for_each_vec4<false>(reinterpret_cast<const float4*>(g), static_cast<int>(n >> 2), [&](int, const float4& v) {
       f(v.x); f(v.y); f(v.z); f(v.w);
-    }
+    });
   } else {
     for (long long i = threadIdx.x; i < n; i += blockDim.x) f(__ldg(g + i));
   }
@@ -364,17 +381,13 @@ __device__ __forceinline__ void sweep_read(const float* __restrict__ g, long lon
 template <class F>
 __device__ __forceinline__ void sweep_write(const float* __restrict__ g, float* __restrict__ o, long long n, bool vec, F f) {
   if (vec) {
-    const float4* g4 = reinterpret_cast<const float4*>(g);
     float4* o4 = reinterpret_cast<float4*>(o);
-    const int n4 = static_cast<int>(n >> 2);
-#pragma unroll 4
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-      const float4 v = __ldcs(g4 + i);
+    for_each_vec4<true>(reinterpret_cast<const float4*>(g), static_cast<int>(n >> 2), [&](int i, const float4& v) {
       const long long e = static_cast<long long>(i) << 2;
       float4 r;
       r.x = f(v.x, e); r.y = f(v.y, e + 1); r.z = f(v.z, e + 2); r.w = f(v.w, e + 3);
       __stcs(o4 + i, r);
-    }
+    });
   } else {
     for (long long i = threadIdx.x; i < n; i += blockDim.x) o[i] = f(__ldg(g + i), i);
   }
@@ -391,12 +404,8 @@ __device__ __forceinline__ void meanvar_write_row(const float* __restrict__ g, f
   const bool silu_on = a.act == MIMIR_B200_ELT_SILU;
   if (vec && !a.per_channel && (gam == nullptr || ((reinterpret_cast<uintptr_t>(gam) & 15) == 0 &&
                                                    (bet == nullptr || (reinterpret_cast<uintptr_t>(bet) & 15) == 0)))) {
-    const float4* g4 = reinterpret_cast<const float4*>(g);
     float4* o4 = reinterpret_cast<float4*>(o);
-    const int n4 = static_cast<int>(n >> 2);
-#pragma unroll 4
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-      const float4 v = __ldcs(g4 + i);
+    for_each_vec4<true>(reinterpret_cast<const float4*>(g), static_cast<int>(n >> 2), [&](int i, const float4& v) {
       float4 r = make_float4((v.x - mean) * inv, (v.y - mean) * inv, (v.z - mean) * inv, (v.w - mean) * inv);
       if (gam != nullptr) {
         const float4 w = __ldg(reinterpret_cast<const float4*>(gam) + i);
@@ -412,20 +421,16 @@ __device__ __forceinline__ void meanvar_write_row(const float* __restrict__ g, f
         r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w;
       }
       __stcs(o4 + i, r);
-    }
+    });
     return;
   }
   if (vec && a.per_channel && (a.hw & 3) == 0) {
     // the four elements of a vector share a channel; the channel advances incrementally
-    const float4* g4 = reinterpret_cast<const float4*>(g);
     float4* o4 = reinterpret_cast<float4*>(o);
-    const int n4 = static_cast<int>(n >> 2);
     const unsigned hw = static_cast<unsigned>(a.hw), estep = blockDim.x * 4u;
     unsigned c = static_cast<unsigned>((off + threadIdx.x * 4u) / hw), rem = static_cast<unsigned>((off + threadIdx.x * 4u) % hw);
     const int c0 = static_cast<int>(row % a.groups) * a.cpg;
-#pragma unroll 4
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-      const float4 v = __ldcs(g4 + i);
+    for_each_vec4<true>(reinterpret_cast<const float4*>(g), static_cast<int>(n >> 2), [&](int i, const float4& v) {
       float sc = inv, sh = -mean * inv;
       if (gam != nullptr) {
         const float w = __ldg(gam + c0 + c);
@@ -442,7 +447,7 @@ __device__ __forceinline__ void meanvar_write_row(const float* __restrict__ g, f
       __stcs(o4 + i, r);
       rem += estep;
       while (rem >= hw) { rem -= hw; ++c; }
-    }
+    });
     return;
   }
   for (long long i = threadIdx.x; i < n; i += blockDim.x) o[i] = finish((__ldg(g + i) - mean) * inv, off + i, row, base, a);
@@ -490,12 +495,23 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 512) ? 2 : 1) sweep_row_k
                (n < (1LL << 31));
     if (FAM == FAM_MEANVAR) {
       if (p.aff.residual != nullptr && (reinterpret_cast<uintptr_t>(p.aff.residual + base) & 15) != 0) vec = false;
-      float s = 0.0f;
-      sweep_read(g, n, vec, [&](float v) { s += v; });
-      const float mean = block_sum(s, red) / static_cast<float>(n);
-      float q = 0.0f;
-      sweep_read(g, n, vec, [&](float v) { const float d = v - mean; q = fmaf(d, d, q); });
-      const float inv = 1.0f / sqrtf(block_sum(q, red) / static_cast<float>(n) + p.eps);
+      // One statistics sweep: sums of (x - K) and (x - K)^2 with K = the row's first element, which
+      // is exact algebra for mean and variance and loses nothing as long as K is within a few standard
+      // deviations of the mean.  When the shift turns out to be poor (the correction term eats more than
+      // 3/4 of the second moment) the variance is recomputed centred on the mean, as the reference does.
+      const float shift = __ldg(g);
+      float s = 0.0f, q = 0.0f;
+      sweep_read(g, n, vec, [&](float v) { const float d = v - shift; s += d; q = fmaf(d, d, q); });
+      const float s1 = block_sum(s, red), s2 = block_sum(q, red);
+      const float fn = static_cast<float>(n);
+      const float mean = shift + s1 / fn;
+      float m2 = s2 - s1 * (s1 / fn);
+      if (s1 * (s1 / fn) > 0.75f * s2) {  // block-uniform
+        float qc = 0.0f;
+        sweep_read(g, n, vec, [&](float v) { const float d = v - mean; qc = fmaf(d, d, qc); });
+        m2 = block_sum(qc, red);
+      }
+      const float inv = 1.0f / sqrtf(fmaxf(m2, 0.0f) / fn + p.eps);
       meanvar_write_row(g, o, n, vec, mean, inv, row, base, p.aff);
     } else if (FAM == FAM_RMS) {
       float q = 0.0f;
@@ -504,19 +520,16 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 512) ? 2 : 1) sweep_row_k
       const float* gam = p.gamma;
       const long long ng = p.n_gamma;
       if (vec && (gam == nullptr || (ng >= n && (reinterpret_cast<uintptr_t>(gam) & 15) == 0))) {
-        const float4* g4 = reinterpret_cast<const float4*>(g);
         float4* o4 = reinterpret_cast<float4*>(o);
-        const int n4 = static_cast<int>(n >> 2);
-#pragma unroll 4
-        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-          float4 v = __ldcs(g4 + i);
+        for_each_vec4<true>(reinterpret_cast<const float4*>(g), static_cast<int>(n >> 2), [&](int i, const float4& vin) {
+          float4 v = vin;
           v.x *= rinv; v.y *= rinv; v.z *= rinv; v.w *= rinv;
           if (gam != nullptr) {
             const float4 w = __ldg(reinterpret_cast<const float4*>(gam) + i);
             v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
           }
           __stcs(o4 + i, v);
-        }
+        });
       } else {
         sweep_write(g, o, n, false, [&](float v, long long e) {
           float r = v * rinv;
@@ -530,15 +543,11 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 512) ? 2 : 1) sweep_row_k
       // elements keep the transcendental unit below the memory time
       float m = -3.0e38f, sum = 0.0f;
       if (vec) {
-        const float4* g4 = reinterpret_cast<const float4*>(g);
-        const int n4 = static_cast<int>(n >> 2);
-#pragma unroll 4
-        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-          const float4 v = __ldg(g4 + i);
+        for_each_vec4<false>(reinterpret_cast<const float4*>(g), static_cast<int>(n >> 2), [&](int, const float4& v) {
           const float mn = fmaxf(fmaxf(m, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
           sum = sum * __expf(m - mn) + ((__expf(v.x - mn) + __expf(v.y - mn)) + (__expf(v.z - mn) + __expf(v.w - mn)));
           m = mn;
-        }
+        });
       } else {
         sweep_read(g, n, false, [&](float v) {
           const float mn = fmaxf(m, v);

@@ -241,7 +241,7 @@ def bench_decoder(no_cpu):
 def bench_conv_stack(no_cpu):
     descs = configs.conv_stack()
     weights = configs.conv_stack_weights(descs)
-    batch = 64
+    batch = int(os.environ.get("OPBENCH_BATCH", "64"))
     x = np.random.default_rng(0).random((batch, 3 * 224 * 224), dtype=np.float32)
     bench_graph_config("4 conv vision stack, stem 7x7 s2 + 4 x [conv3x3, GroupNorm(32), SiLU, residual], 64..256 ch @112^2", descs,
                        weights, x, batch, 256 * 112 * 112, configs.conv_flops(descs), abi.PREC_BF16X2, no_cpu,

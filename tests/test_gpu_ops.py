@@ -250,3 +250,24 @@ def test_pools(backend):
     assert_close(backend.token_mean_pool(x, 2, 7, 12), want, "token mean pool", abs_tol=1e-6, rel_tol=1e-6)
     want = np.concatenate([port.global_avgpool(x[i * 84:(i + 1) * 84], 3, 4, 7) for i in range(2)])
     assert_close(backend.global_avgpool(x, 2, 3, 4, 7), want, "global avgpool", abs_tol=1e-6, rel_tol=1e-5)
+
+
+def test_norm_statistics_are_robust_to_offsets_and_outliers(backend):
+    """The streaming norm kernels take mean and variance from one sweep of sums shifted by the row's first
+    element; rows with a large common offset and rows whose first element is an outlier (worst case for
+    the shift) must still match the two-pass reference."""
+    r = rng(77)
+    rows, n = 200, 5000  # >= one row per SM: the CTA-per-row sweep path
+    x = (300.0 + r.standard_normal((rows, n))).astype(np.float32)
+    x[::2, 0] = 1e4
+    x[1::4, 0] = -3e3
+    g, b = r.standard_normal(n).astype(np.float32), r.standard_normal(n).astype(np.float32)
+    assert_close(backend.layernorm(x.ravel(), g, b, rows, n), port.layernorm(x.ravel(), g, b, rows, n, 1e-5), "layernorm offset/outlier rows")
+    # GroupNorm slabs with the same treatment
+    batch, ch, h, w, groups = 8, 64, 20, 20, 32
+    per = ch * h * w
+    xg = (50.0 + r.standard_normal(batch * per) * 0.5).astype(np.float32)
+    xg[::per // groups] = 7e3  # first element of every group slab
+    gg, bg = r.standard_normal(ch).astype(np.float32), r.standard_normal(ch).astype(np.float32)
+    want = np.concatenate([port.groupnorm(xg[i * per:(i + 1) * per], gg, bg, ch, h, w, groups, 1e-5) for i in range(batch)])
+    assert_close(backend.groupnorm(xg, gg, bg, batch, ch, h, w, groups, 1e-5, -1), want, "groupnorm offset/outlier slabs")
