@@ -150,9 +150,16 @@ __global__ void rms_chunk_stats_kernel(const float* __restrict__ x, float* __res
   const float* g = x + row * len + off;
   float acc = 0.0f;
   if ((reinterpret_cast<uintptr_t>(g) & 15) == 0 && (n & 3) == 0) {
-#pragma unroll 8
-    for (long long i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(g) + i);
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    const int n4 = static_cast<int>(n >> 2), step = blockDim.x;
+    int i = threadIdx.x;
+    for (; i + 3 * step < n4; i += 4 * step) {  // four loads in flight
+      const float4 a = __ldg(g4 + i), b = __ldg(g4 + i + step), c = __ldg(g4 + i + 2 * step), d = __ldg(g4 + i + 3 * step);
+      acc += ((a.x * a.x + a.y * a.y) + (a.z * a.z + a.w * a.w)) + ((b.x * b.x + b.y * b.y) + (b.z * b.z + b.w * b.w)) +
+             ((c.x * c.x + c.y * c.y) + (c.z * c.z + c.w * c.w)) + ((d.x * d.x + d.y * d.y) + (d.z * d.z + d.w * d.w));
+    }
+    for (; i < n4; i += step) {
+      const float4 v = __ldg(g4 + i);
       acc += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
     }
   } else {
@@ -263,15 +270,24 @@ __global__ void rms_chunk_apply_kernel(const float* __restrict__ x, const float*
   float* o = y + row * len + off;
   if (((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(o)) & 15) == 0 && (cn & 3) == 0 &&
       (gamma == nullptr || ((reinterpret_cast<uintptr_t>(gamma + off) & 15) == 0 && off + cn <= n_gamma))) {
-    for (long long i = threadIdx.x; i < (cn >> 2); i += blockDim.x) {
-      float4 v = __ldg(reinterpret_cast<const float4*>(g) + i);
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    const float4* w4 = gamma ? reinterpret_cast<const float4*>(gamma + off) : nullptr;
+    float4* o4 = reinterpret_cast<float4*>(o);
+    const int n4 = static_cast<int>(cn >> 2), step = blockDim.x;
+    auto one = [&](int i, float4 v, float4 w) {
       v.x /= rms; v.y /= rms; v.z /= rms; v.w /= rms;
-      if (gamma != nullptr) {
-        const float4 w = __ldg(reinterpret_cast<const float4*>(gamma + off) + i);
-        v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w;
-      }
-      reinterpret_cast<float4*>(o)[i] = v;
+      if (w4 != nullptr) { v.x *= w.x; v.y *= w.y; v.z *= w.z; v.w *= w.w; }
+      __stcs(o4 + i, v);
+    };
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    int i = threadIdx.x;
+    for (; i + 3 * step < n4; i += 4 * step) {  // eight loads in flight
+      const float4 a = __ldcs(g4 + i), b = __ldcs(g4 + i + step), c = __ldcs(g4 + i + 2 * step), d = __ldcs(g4 + i + 3 * step);
+      const float4 wa = w4 ? __ldg(w4 + i) : z, wb = w4 ? __ldg(w4 + i + step) : z, wc = w4 ? __ldg(w4 + i + 2 * step) : z,
+                   wd = w4 ? __ldg(w4 + i + 3 * step) : z;
+      one(i, a, wa); one(i + step, b, wb); one(i + 2 * step, c, wc); one(i + 3 * step, d, wd);
     }
+    for (; i < n4; i += step) one(i, __ldcs(g4 + i), w4 ? __ldg(w4 + i) : z);
   } else {
     for (long long i = threadIdx.x; i < cn; i += blockDim.x) {
       float v = __ldg(g + i) / rms;
@@ -685,7 +701,7 @@ int norm_scratch(float** out) {
 
 // Rows longer than a cluster can hold go through the two-pass chunk kernels in groups of rows whose
 // footprint stays inside L2 (so the second pass reads x from L2, not from HBM).
-constexpr long long L2_GROUP_BYTES = 64ll << 20;
+constexpr long long L2_GROUP_BYTES = 104ll << 20;
 
 int meanvar_dispatch(const float* x, float* y, long long rows, long long len, float eps, const Affine& a, cudaStream_t st) {
   if (rows <= 0 || len <= 0) return fail(MIMIR_B200_E_INVALID, "norm: empty input");
