@@ -251,7 +251,7 @@ def bench_conv_stack(no_cpu):
 def bench_unet(no_cpu):
     descs = configs.unet_mid_up()
     weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
-    batch = 16
+    batch = int(os.environ.get("OPBENCH_BATCH", "16"))
     x = np.random.default_rng(0).standard_normal((batch, 4 * 64 * 64), dtype=np.float32)
     bench_graph_config("5 UNet mid+up, latent 4x64x64 -> 3x256x256, channels 512/256/128, bf16-exact weights", descs, weights, x, batch,
                        3 * 256 * 256, configs.conv_flops(descs), abi.PREC_BF16W, no_cpu, "one sample through the reference CPU path")
