@@ -36,6 +36,11 @@ UNIT = "samples/s (1 sample = 1 row through Linear+bias+GELU x3, K=N=4096)"
 K = configs.LINEAR_STACK_K
 
 
+# DRAM bytes (read + write) of one GEMM launch of this workload at M = 8192 rows, from the ncu capture
+# summarised in profiles/gemm_tn_bf16split_linear_stack.md
+NCU_TRAFFIC_BYTES_AT_8192_ROWS = 627.6e6
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -241,7 +246,10 @@ def run_ours(args):
     achieved = per_launch_flops / (gemm_avg_ms * 1e-3) / 1e12 if gemm_launches else None
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s",
-        "frac": (achieved / peaks["bf16_sustained"]) if achieved else None, "traffic": None,
+        "frac": (achieved / peaks["bf16_sustained"]) if achieved else None,
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch at M = 8192 rows (510.7 MB + 116.9 MB, ncu --set full),
+        # scaled by the rows of this launch: the traffic is per row tile, so it grows in proportion
+        "traffic": NCU_TRAFFIC_BYTES_AT_8192_ROWS * M / 8192, "traffic_unit": "bytes per launch (ncu at M=8192, scaled by rows)",
         "kernel": "gemm_tn_bf16split_kernel", "launches_timed": gemm_launches, "avg_launch_ms": gemm_avg_ms,
         "peak_source": f"{peaks['source']} (cuBLAS bf16 8192^3 sustained)",
         "issued_tflops": (3 * achieved) if achieved else None,

@@ -27,9 +27,10 @@
 extern "C" {
 #endif
 
-#define MIMIR_B200_ABI_VERSION 1
+#define MIMIR_B200_ABI_VERSION 2
 #define MIMIR_B200_MAX_INPUTS 8
 #define MIMIR_B200_MAX_DIMS 8
+#define MIMIR_B200_MAX_SPLITS 16
 
 typedef enum MimirB200Status {
   MIMIR_B200_OK = 0,
@@ -61,7 +62,14 @@ typedef enum MimirB200Eltwise {
   MIMIR_B200_ELT_SILU = 3,
   MIMIR_B200_ELT_RELU = 4,
   MIMIR_B200_ELT_TANH = 5,
-  MIMIR_B200_ELT_SIGMOID = 6
+  MIMIR_B200_ELT_SIGMOID = 6,
+  MIMIR_B200_ELT_LEAKY_RELU = 7,   /* x > 0 ? x : alpha x (LayerOpsExt.hpp:29-39) */
+  MIMIR_B200_ELT_SOFTPLUS = 8,     /* x > 20 ? x : log(1 + exp x) (LayerOpsExt.hpp:59-68) */
+  MIMIR_B200_ELT_MISH = 9,         /* x tanh(softplus x) (LayerOpsExt.hpp:44-54) */
+  MIMIR_B200_ELT_HARD_SIGMOID = 10,/* clamp((x + 3) / 6, 0, 1) (LayerOpsExt.hpp:73-82) */
+  MIMIR_B200_ELT_HARD_SWISH = 11,  /* x hard_sigmoid(x) (LayerOpsExt.hpp:87-99) */
+  MIMIR_B200_ELT_SUBTRACT = 12,    /* equal sizes (LayerOpsExt.hpp:105-122) */
+  MIMIR_B200_ELT_DIVIDE = 13       /* equal sizes, |divisor| < 1e-8 replaced by +-1e-8 (LayerOpsExt.hpp:127-148) */
 } MimirB200Eltwise;
 
 /* ---------------------------------------------------------------------------------------------
@@ -132,6 +140,9 @@ int mimir_b200_softmax(const float* x, float* y, int batch, long long n, int log
  * (nb == n, 1, or a divisor of n).  Replaces LayerOps.hpp:142-230, 556-623. */
 int mimir_b200_eltwise(int op, const float* a, const float* b, float* y, int batch, long long n,
                        long long nb);
+/* Same with the slope of LeakyReLU (ignored by the other ops). */
+int mimir_b200_eltwise_alpha(int op, const float* a, const float* b, float* y, int batch, long long n,
+                             long long nb, float alpha);
 /* Row gather; ids given as floats are rounded like llround; id == padding_idx (when >= 0) or out
  * of range gives a zero row.  Replaces the Embedding case (Model.cpp:5301-5334; int ids:
  * Model.cpp:1152-1205).  Exactly one of ids_f32 / ids_i32 is non-NULL. */
@@ -149,6 +160,47 @@ int mimir_b200_permute(const float* x, float* y, int batch, int ndim, const int*
  * (LayerOps.hpp:459-482). */
 int mimir_b200_token_mean_pool(const float* x, float* y, int batch, int seq, int dim);
 int mimir_b200_global_avgpool(const float* x, float* y, int batch, int channels, int h, int w);
+
+/* ---- the remaining cases of the layer switch ("next" rows: cross attention and the long tail) ---- */
+
+/* Cross attention on `batch` pairs of query [q_len, embed] and key/value [kv_len, embed] inputs.
+ * Weight block = Wq[E][E], Wkv[E][2E] (K | V halves), Wout[E][E], input-major, no biases.  Replaces
+ * LayerOps::cross_attention_forward (LayerOps.hpp:1116-1216) as dispatched at Model.cpp:5935-5996. */
+int mimir_b200_cross_attention(const float* query, const float* key_value, const float* wq_wkv_wout,
+                               float* y, int batch, int q_len, int kv_len, int embed, int heads,
+                               int causal);
+/* One filter per channel, weights [C][k][k] then bias[C] when `bias` is non-NULL.  Replaces
+ * LayerOpsExt::depthwise_conv2d_forward (LayerOpsExt.hpp:442-497). */
+int mimir_b200_depthwise_conv2d(const float* x, const float* w, const float* bias, float* y, int batch,
+                                int channels, int h, int wd, int k, int stride, int pad);
+/* x [ic][len], weights [oc][ic][k] (+ bias[oc]).  Replaces LayerOpsExt::conv1d_forward
+ * (LayerOpsExt.hpp:388-437). */
+int mimir_b200_conv1d(const float* x, const float* w, const float* bias, float* y, int batch, int ic,
+                      int oc, int len, int k, int stride, int pad);
+/* The ConvTranspose2d branch of the Conv2d case (Model.cpp:4946-4953, 5047-5079): output size
+ * (h-1)*stride - 2*pad + k, taps gathered with the forward-convolution formula, no bias. */
+int mimir_b200_conv_transpose2d(const float* x, const float* w, float* y, int batch, int ic, int oc,
+                                int h, int wd, int k, int stride, int pad, int relu);
+/* is_max != 0: MaxPool2d (Model.cpp:5508-5559); else AvgPool2d over the in-bounds taps
+ * (LayerOps.hpp:404-453). */
+int mimir_b200_pool2d(int is_max, const float* x, float* y, int batch, int channels, int h, int wd,
+                      int kh, int kw, int stride_h, int stride_w, int pad_h, int pad_w);
+/* mode 0 zero, 1 reflection, 2 replication (LayerOpsExt.hpp:582-690). */
+int mimir_b200_pad2d(int mode, const float* x, float* y, int batch, int channels, int h, int wd,
+                     int pad_h, int pad_w);
+/* [C r^2, H, W] -> [C, H r, W r] (LayerOpsExt.hpp:749-795). */
+int mimir_b200_pixel_shuffle(const float* x, float* y, int batch, int in_channels, int h, int wd, int r);
+/* 2x bilinear upsample; half_pixel = 0: LayerOps::upsample_bilinear_forward (LayerOps.hpp:833-874),
+ * 1: the variant dispatched for UpsampleBicubic (LayerOpsExt.hpp:695-744). */
+int mimir_b200_upsample_bilinear(const float* x, float* y, int batch, int channels, int h, int wd,
+                                 int out_h, int out_w, int half_pixel);
+/* C[b] = A[b] (M x K) . B[b] (K x N) for nb matrices.  Replaces the BatchMatMul / MatMul cases
+ * (Model.cpp:5847-5898). */
+int mimir_b200_batch_matmul(const float* A, const float* B, float* C, long long nb, int M, int K, int N);
+/* Inference BatchNorm of the reference: statistics over each sample's WHOLE vector, then
+ * y[i] *= w[i] for i < n_w; no shift (Model.cpp:5387-5421). */
+int mimir_b200_batchnorm_inference(const float* x, const float* w, long long n_w, float* y, int batch,
+                                   long long n, float eps);
 
 /* ---------------------------------------------------------------------------------------------
  * 3. Whole-graph entry points (activations stay on the device between layers)
@@ -177,6 +229,16 @@ typedef struct MimirLayerDesc {
   int32_t n_dims;
   int32_t shape[MIMIR_B200_MAX_DIMS];        /* Permute */
   int32_t permute_dims[MIMIR_B200_MAX_DIMS];
+  /* --- ABI version 2: fields read by the remaining switch cases ------------------------------ */
+  int32_t head_dim;                          /* CrossAttention: embed_dim <= 0 => head_dim * num_heads (Model.cpp:5954-5957) */
+  float leaky_relu_alpha;                    /* LeakyReLU: <= 0 => 0.01 (Model.cpp:5453) */
+  int32_t kernel_w, stride_w, padding_w;     /* resolved get_kernel_w / get_stride_w / get_pad_w (AvgPool2d, LayerOps.hpp:408-413) */
+  int32_t raw_kernel_h, raw_stride_h, raw_pad_h, raw_pad_w; /* the RAW Layer fields kernel_h / stride_h / pad_h / pad_w:
+                                                DepthwiseConv2d, Conv1d and the pads read these, not the get_* helpers
+                                                (LayerOpsExt.hpp:449-451, 395-398, 589-592) */
+  int32_t n_splits;                          /* Split: number of entries of split_sizes (Model.cpp:5802-5815) */
+  int32_t split_sizes[MIMIR_B200_MAX_SPLITS];
+  int32_t num_chunks;                        /* Chunk (Model.cpp:5817-5832) */
 } MimirLayerDesc;
 
 typedef struct MimirNamedInput {

@@ -65,6 +65,23 @@ inline MimirLayerDesc describe(const Layer& L) {
       d.permute_dims[i] = L.permute_dims[i];
     }
   }
+  d.head_dim = L.head_dim;
+  d.leaky_relu_alpha = L.leaky_relu_alpha;
+  d.kernel_w = L.get_kernel_w();
+  d.stride_w = L.get_stride_w();
+  d.padding_w = L.get_pad_w();
+  d.raw_kernel_h = L.kernel_h;
+  d.raw_stride_h = L.stride_h;
+  d.raw_pad_h = L.pad_h;
+  d.raw_pad_w = L.pad_w;
+  d.n_splits = 0;
+  if (L.split_sizes.size() <= MIMIR_B200_MAX_SPLITS) {
+    d.n_splits = static_cast<int32_t>(L.split_sizes.size());
+    for (size_t i = 0; i < L.split_sizes.size(); ++i) d.split_sizes[i] = L.split_sizes[i];
+  } else {
+    d.n_splits = -1;  // more pieces than the descriptor carries: model_create refuses the layer
+  }
+  d.num_chunks = L.num_chunks;
   return d;
 }
 
@@ -116,6 +133,16 @@ inline void apply(const MimirLayerDesc& d, Layer& L) {
   L.activation = d.activation ? ActivationType::RELU : ActivationType::NONE;
   L.shape.assign(d.shape, d.shape + d.n_dims);
   L.permute_dims.assign(d.permute_dims, d.permute_dims + d.n_dims);
+  L.head_dim = d.head_dim;
+  L.leaky_relu_alpha = d.leaky_relu_alpha;
+  L.kernel_h = d.raw_kernel_h;
+  L.stride_h = d.raw_stride_h > 0 ? d.raw_stride_h : 1;
+  L.pad_h = d.raw_pad_h;
+  L.pad_w = d.raw_pad_w;
+  L.kernel_w = (d.kernel_w > 0 && d.kernel_w != d.kernel) ? d.kernel_w : d.raw_kernel_h;
+  if (d.stride_w > 0 && d.stride_w != d.stride) L.stride_w = d.stride_w;
+  if (d.n_splits > 0) L.split_sizes.assign(d.split_sizes, d.split_sizes + d.n_splits);
+  L.num_chunks = d.num_chunks;
 }
 
 }  // namespace mimir_b200

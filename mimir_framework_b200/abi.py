@@ -11,12 +11,14 @@ import os
 
 MAX_INPUTS = 8
 MAX_DIMS = 8
+MAX_SPLITS = 16
 
 OK, E_INVALID, E_UNSUPPORTED, E_OOM_BUDGET, E_CUDA, E_TIMEOUT, E_NOT_INIT = range(7)
 STATUS_NAMES = ["OK", "E_INVALID", "E_UNSUPPORTED", "E_OOM_BUDGET", "E_CUDA", "E_TIMEOUT", "E_NOT_INIT"]
 
 PREC_BF16X2, PREC_BF16W, PREC_BF16 = 0, 1, 2
 ELT_ADD, ELT_MULTIPLY, ELT_GELU, ELT_SILU, ELT_RELU, ELT_TANH, ELT_SIGMOID = range(7)
+ELT_LEAKY_RELU, ELT_SOFTPLUS, ELT_MISH, ELT_HARD_SIGMOID, ELT_HARD_SWISH, ELT_SUBTRACT, ELT_DIVIDE = range(7, 14)
 
 
 class MimirLayerDesc(C.Structure):
@@ -54,6 +56,18 @@ class MimirLayerDesc(C.Structure):
         ("n_dims", C.c_int32),
         ("shape", C.c_int32 * MAX_DIMS),
         ("permute_dims", C.c_int32 * MAX_DIMS),
+        ("head_dim", C.c_int32),
+        ("leaky_relu_alpha", C.c_float),
+        ("kernel_w", C.c_int32),
+        ("stride_w", C.c_int32),
+        ("padding_w", C.c_int32),
+        ("raw_kernel_h", C.c_int32),
+        ("raw_stride_h", C.c_int32),
+        ("raw_pad_h", C.c_int32),
+        ("raw_pad_w", C.c_int32),
+        ("n_splits", C.c_int32),
+        ("split_sizes", C.c_int32 * MAX_SPLITS),
+        ("num_chunks", C.c_int32),
     ]
 
 
@@ -84,10 +98,13 @@ LAYER_DEFAULTS = dict(
     input_height=0, input_width=0, kernel=3, stride=1, padding=0, eps=1e-5, num_groups=1,
     affine=1, use_bias=1, vocab_size=0, embed_dim=0, padding_idx=-1, num_heads=8, seq_len=0,
     causal=0, out_h=0, out_w=0, scale_h=2, scale_w=2, activation=0,
+    head_dim=64, leaky_relu_alpha=0.01, kernel_w=None, stride_w=None, padding_w=None,
+    raw_kernel_h=0, raw_stride_h=1, raw_pad_h=0, raw_pad_w=0, num_chunks=2,
 )
+_FLOAT_FIELDS = ("eps", "leaky_relu_alpha")
 
 
-def make_desc(name: str, type: str, inputs=(), output: str = "x", shape=(), permute_dims=(), **kw) -> MimirLayerDesc:
+def make_desc(name: str, type: str, inputs=(), output: str = "x", shape=(), permute_dims=(), split_sizes=(), **kw) -> MimirLayerDesc:
     """Builds one descriptor with the reference's Layer defaults for everything not given."""
     d = MimirLayerDesc()
     d.name = name.encode()
@@ -104,8 +121,17 @@ def make_desc(name: str, type: str, inputs=(), output: str = "x", shape=(), perm
         if k not in vals:
             raise KeyError(f"unknown layer field {k!r}")
         vals[k] = v
+    # the *_w accessors fall back to the square setting (Layers.hpp:251-257)
+    for wk, hk in (("kernel_w", "kernel"), ("stride_w", "stride"), ("padding_w", "padding")):
+        if vals[wk] is None:
+            vals[wk] = vals[hk]
     for k, v in vals.items():
         setattr(d, k, v)
+    if len(split_sizes) > MAX_SPLITS:
+        raise ValueError("too many split sizes")
+    d.n_splits = len(split_sizes)
+    for i, v in enumerate(split_sizes):
+        d.split_sizes[i] = int(v)
     if len(shape) != len(permute_dims) or len(shape) > MAX_DIMS:
         raise ValueError("shape / permute_dims mismatch")
     d.n_dims = len(shape)
@@ -146,21 +172,22 @@ def load() -> C.CDLL:
     return _lib
 
 
-_SCALAR_FIELDS = [n for n, _ in MimirLayerDesc._fields_ if n not in ("name", "type", "inputs", "n_inputs", "output", "n_dims", "shape", "permute_dims")]
+_SCALAR_FIELDS = [n for n, _ in MimirLayerDesc._fields_ if n not in ("name", "type", "inputs", "n_inputs", "output", "n_dims", "shape", "permute_dims", "n_splits", "split_sizes")]
 
 
 def desc_to_dict(d: MimirLayerDesc) -> dict:
     """JSON-friendly form of a descriptor (used by the golden fixtures)."""
     out = {"name": (d.name or b"").decode(), "type": (d.type or b"").decode(),
            "inputs": [d.inputs[i].decode() for i in range(d.n_inputs)], "output": (d.output or b"x").decode() or "x",
-           "shape": [int(d.shape[i]) for i in range(d.n_dims)], "permute_dims": [int(d.permute_dims[i]) for i in range(d.n_dims)]}
+           "shape": [int(d.shape[i]) for i in range(d.n_dims)], "permute_dims": [int(d.permute_dims[i]) for i in range(d.n_dims)],
+           "split_sizes": [int(d.split_sizes[i]) for i in range(d.n_splits)]}
     for f in _SCALAR_FIELDS:
         v = getattr(d, f)
-        out[f] = float(v) if f == "eps" else int(v)
+        out[f] = float(v) if f in _FLOAT_FIELDS else int(v)
     return out
 
 
 def desc_from_dict(j: dict) -> MimirLayerDesc:
     kw = {f: j[f] for f in _SCALAR_FIELDS if f in j}
     return make_desc(j["name"], j["type"], inputs=j.get("inputs", []), output=j.get("output", "x"), shape=j.get("shape", []),
-                     permute_dims=j.get("permute_dims", []), **kw)
+                     permute_dims=j.get("permute_dims", []), split_sizes=j.get("split_sizes", []), **kw)

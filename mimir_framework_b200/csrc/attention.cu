@@ -17,8 +17,7 @@ constexpr int BQ = 64, BKV = 64, LDT = 68;  // LDT: padded leading dimension of 
 
 template <int HD>
 __global__ void __launch_bounds__(256)
-flash_attn_fp32_kernel(const float* __restrict__ qkv, float* __restrict__ out, int seq, int embed, int heads, int causal,
-                       float scale) {
+flash_attn_fp32_kernel(const AttnView a, float* __restrict__ out, int embed, int heads, int causal, float scale) {
   constexpr int CPT = HD / 16;  // output columns per thread
   extern __shared__ __align__(16) float sm[];
   float* Qt = sm;                 // [HD][LDT]   Qt[d][row]
@@ -29,14 +28,17 @@ flash_attn_fp32_kernel(const float* __restrict__ qkv, float* __restrict__ out, i
   const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int q0 = qt * BQ;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
-  const long long ld = 3LL * embed;
-  const float* base = qkv + static_cast<long long>(b) * seq * ld + h * HD;
+  const int seq = a.q_len, kvn = a.kv_len;
+  const long long ldq = a.ldq, ldk = a.ldkv;
+  const float* qb = a.q + static_cast<long long>(b) * seq * ldq + h * HD;
+  const float* kb = a.k + static_cast<long long>(b) * kvn * ldk + h * HD;
+  const float* vb = a.v + static_cast<long long>(b) * kvn * ldk + h * HD;
 
-  // Q tile, transposed into Qt (rows past seq are zero)
+  // Q tile, transposed into Qt (rows past q_len are zero)
   for (int i = tid; i < BQ * (HD / 4); i += 256) {
     const int r = i / (HD / 4), c4 = (i - r * (HD / 4)) * 4;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (q0 + r < seq) v = __ldg(reinterpret_cast<const float4*>(base + (q0 + r) * ld + c4));
+    if (q0 + r < seq) v = __ldg(reinterpret_cast<const float4*>(qb + (q0 + r) * ldq + c4));
     Qt[(c4 + 0) * LDT + r] = v.x; Qt[(c4 + 1) * LDT + r] = v.y; Qt[(c4 + 2) * LDT + r] = v.z; Qt[(c4 + 3) * LDT + r] = v.w;
   }
 
@@ -49,15 +51,15 @@ flash_attn_fp32_kernel(const float* __restrict__ qkv, float* __restrict__ out, i
     for (int c = 0; c < CPT; ++c) o_acc[i][c] = 0.0f;
   }
 
-  const int kv_end = causal ? min(seq, q0 + BQ) : seq;
+  const int kv_end = causal ? min(kvn, q0 + BQ) : kvn;
   for (int k0 = 0; k0 < kv_end; k0 += BKV) {
     __syncthreads();  // previous tile fully consumed (also orders the Qt writes before first use)
     for (int i = tid; i < BKV * (HD / 4); i += 256) {
       const int r = i / (HD / 4), c4 = (i - r * (HD / 4)) * 4;
       float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
-      if (k0 + r < seq) {
-        kv = __ldg(reinterpret_cast<const float4*>(base + (k0 + r) * ld + embed + c4));
-        vv = __ldg(reinterpret_cast<const float4*>(base + (k0 + r) * ld + 2 * embed + c4));
+      if (k0 + r < kvn) {
+        kv = __ldg(reinterpret_cast<const float4*>(kb + (k0 + r) * ldk + c4));
+        vv = __ldg(reinterpret_cast<const float4*>(vb + (k0 + r) * ldk + c4));
       }
       Kt[(c4 + 0) * LDT + r] = kv.x; Kt[(c4 + 1) * LDT + r] = kv.y; Kt[(c4 + 2) * LDT + r] = kv.z; Kt[(c4 + 3) * LDT + r] = kv.w;
       *reinterpret_cast<float4*>(Vs + r * HD + c4) = vv;
@@ -89,7 +91,7 @@ flash_attn_fp32_kernel(const float* __restrict__ qkv, float* __restrict__ out, i
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kj = k0 + tx * 4 + j;
-        const bool valid = (kj < seq) && (!causal || kj <= qi);
+        const bool valid = (kj < kvn) && (!causal || kj <= qi);
         s[i][j] = valid ? s[i][j] * scale : -INFINITY;
         if (valid) mx = fmaxf(mx, s[i][j]);
       }
@@ -148,22 +150,24 @@ flash_attn_fp32_kernel(const float* __restrict__ qkv, float* __restrict__ out, i
 }
 
 // Any head dimension: one CTA per (sample, head, query row); the score row lives in shared memory.
-__global__ void attn_row_kernel(const float* __restrict__ qkv, float* __restrict__ out, int seq, int embed, int heads, int hd,
-                                int causal, float scale) {
+__global__ void attn_row_kernel(const AttnView a, float* __restrict__ out, int embed, int heads, int hd, int causal, float scale) {
   extern __shared__ __align__(16) float sm[];
   float* q = sm;         // [hd]
-  float* p = sm + hd;    // [seq]
+  float* p = sm + hd;    // [kv_len]
   __shared__ float red[33];
   const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const long long ld = 3LL * embed;
-  const float* base = qkv + static_cast<long long>(b) * seq * ld + h * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) q[d] = base[i * ld + d];
+  const int seq = a.q_len, kvn = a.kv_len;
+  const long long ld = a.ldkv;
+  const float* qrow = a.q + (static_cast<long long>(b) * seq + i) * a.ldq + h * hd;
+  const float* kb = a.k + static_cast<long long>(b) * kvn * ld + h * hd;
+  const float* vb = a.v + static_cast<long long>(b) * kvn * ld + h * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) q[d] = qrow[d];
   __syncthreads();
-  const int n_keys = causal ? (i + 1) : seq;
+  const int n_keys = causal ? min(i + 1, kvn) : kvn;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
   float mx = -1e30f;
   for (int j = w; j < n_keys; j += nw) {  // one warp per key: coalesced reads of the K row
-    const float* kr = base + j * ld + embed;
+    const float* kr = kb + j * ld;
     float dot = 0.0f;
     for (int d = lane; d < hd; d += 32) dot += q[d] * __ldg(kr + d);
 #pragma unroll
@@ -204,7 +208,7 @@ __global__ void attn_row_kernel(const float* __restrict__ qkv, float* __restrict
   __syncthreads();
   const float inv = 1.0f / (red[32] + 1e-9f);
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    const float* vr = base + 2 * embed + d;
+    const float* vr = vb + d;
     float o = 0.0f;
     for (int j = 0; j < n_keys; ++j) o += p[j] * __ldg(vr + j * ld);
     out[(static_cast<long long>(b) * seq + i) * embed + h * hd + d] = o * inv;
@@ -212,16 +216,15 @@ __global__ void attn_row_kernel(const float* __restrict__ qkv, float* __restrict
 }
 
 template <int HD>
-int launch_flash(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, float scale,
-                 cudaStream_t st) {
+int launch_flash(const AttnView& a, float* out, int batch, int embed, int heads, int causal, float scale, cudaStream_t st) {
   constexpr int SMEM = (2 * HD * LDT + BKV * HD + BKV * LDT) * 4;
   static bool attr = false;
   if (!attr) {
     MB_CUDA(cudaFuncSetAttribute(flash_attn_fp32_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr = true;
   }
-  dim3 grid((seq + BQ - 1) / BQ, heads, batch);
-  flash_attn_fp32_kernel<HD><<<grid, 256, SMEM, st>>>(qkv, out, seq, embed, heads, causal, scale);
+  dim3 grid((a.q_len + BQ - 1) / BQ, heads, batch);
+  flash_attn_fp32_kernel<HD><<<grid, 256, SMEM, st>>>(a, out, embed, heads, causal, scale);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
@@ -229,29 +232,40 @@ int launch_flash(const float* qkv, float* out, int batch, int seq, int embed, in
 
 }  // namespace
 
-int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
-                          cudaStream_t st) {
-  if (batch <= 0 || seq <= 0 || embed <= 0 || heads <= 0 || embed % heads != 0)
-    return fail(MIMIR_B200_E_INVALID, "SelfAttention: embed_dim must be divisible by num_heads");
+int launch_attention_core_view(const AttnView& a, float* out, int batch, int embed, int heads, int causal, cudaStream_t st) {
+  if (batch <= 0 || a.q_len <= 0 || a.kv_len <= 0 || embed <= 0 || heads <= 0 || embed % heads != 0)
+    return fail(MIMIR_B200_E_INVALID, "Attention: embed_dim must be divisible by num_heads");
   const int hd = embed / heads;
   const float scale = 1.0f / sqrtf(static_cast<float>(hd));
-  const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) & 15) == 0) && (embed % 4 == 0);
-  if (aligned && hd == 32) return launch_flash<32>(qkv, out, batch, seq, embed, heads, causal, scale, st);
-  if (aligned && hd == 64) return launch_flash<64>(qkv, out, batch, seq, embed, heads, causal, scale, st);
-  if (aligned && hd == 128) return launch_flash<128>(qkv, out, batch, seq, embed, heads, causal, scale, st);
-  const size_t smem = static_cast<size_t>(hd + seq) * 4;
+  const bool aligned = (((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) == 0) &&
+                       (embed % 4 == 0) && (a.ldq % 4 == 0) && (a.ldkv % 4 == 0) && batch <= 65535 && heads <= 65535;
+  if (aligned && hd == 32) return launch_flash<32>(a, out, batch, embed, heads, causal, scale, st);
+  if (aligned && hd == 64) return launch_flash<64>(a, out, batch, embed, heads, causal, scale, st);
+  if (aligned && hd == 128) return launch_flash<128>(a, out, batch, embed, heads, causal, scale, st);
+  const size_t smem = static_cast<size_t>(hd + a.kv_len) * 4;
   if (smem > 200 * 1024 || batch > 65535 || heads > 65535)
-    return fail(MIMIR_B200_E_UNSUPPORTED, "attention: seq %d with head_dim %d exceeds the row kernel's shared memory", seq, hd);
+    return fail(MIMIR_B200_E_UNSUPPORTED, "attention: %d keys with head_dim %d exceed the row kernel's shared memory", a.kv_len, hd);
   static size_t attr_bytes = 0;
   if (smem > 48 * 1024 && smem > attr_bytes) {
     MB_CUDA(cudaFuncSetAttribute(attn_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     attr_bytes = smem;
   }
-  dim3 grid(seq, heads, batch);
-  attn_row_kernel<<<grid, 256, smem, st>>>(qkv, out, seq, embed, heads, hd, causal, scale);
+  dim3 grid(a.q_len, heads, batch);
+  attn_row_kernel<<<grid, 256, smem, st>>>(a, out, embed, heads, hd, causal, scale);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
+}
+
+int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
+                          cudaStream_t st) {
+  if (batch <= 0 || seq <= 0 || embed <= 0 || heads <= 0 || embed % heads != 0)
+    return fail(MIMIR_B200_E_INVALID, "SelfAttention: embed_dim must be divisible by num_heads");
+  AttnView a;
+  a.q = qkv; a.k = qkv + embed; a.v = qkv + 2 * embed;
+  a.ldq = a.ldkv = 3LL * embed;
+  a.q_len = a.kv_len = seq;
+  return launch_attention_core_view(a, out, batch, embed, heads, causal, st);
 }
 
 }  // namespace mb

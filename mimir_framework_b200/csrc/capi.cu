@@ -3,6 +3,7 @@
 // VulkanCompute.hpp:209-210), and their device-pointer forms.  The whole-graph entry points live
 // in graph.cu.  No function here throws; none falls back to the CPU.
 #include "ops.h"
+#include "host_call.h"
 
 #include <cstdlib>
 #include <cstring>
@@ -92,7 +93,6 @@ size_t split_bytes(int64_t rows, int k, int planes) {
   return static_cast<size_t>(planes) * static_cast<size_t>(plane_elems(rows, k)) * sizeof(__nv_bfloat16);
 }
 
-static size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 bool linear_uses_skinny(int rows, int precision) { return rows <= 16 && precision == MIMIR_B200_PREC_BF16X2; }
 
@@ -257,41 +257,6 @@ namespace {
 using namespace mb;
 
 std::mutex g_init_mu;
-
-// Device buffers of one host-pointer call; everything is released when the call returns.
-struct Temps {
-  std::vector<std::pair<void*, size_t>> bufs;
-  ~Temps() {
-    for (auto& b : bufs) dev_free(b.first, b.second);
-  }
-  int alloc(void** p, size_t bytes, const char* tag) {
-    MB_TRY(dev_alloc(p, bytes ? bytes : 4, tag));
-    bufs.emplace_back(*p, bytes ? bytes : 4);
-    return MIMIR_B200_OK;
-  }
-  int upload(const float** dev, const float* host, size_t n, const char* tag) {
-    void* p;
-    MB_TRY(alloc(&p, n * sizeof(float), tag));
-    MB_CUDA(cudaMemcpy(p, host, n * sizeof(float), cudaMemcpyHostToDevice));
-    *dev = static_cast<const float*>(p);
-    return MIMIR_B200_OK;
-  }
-  int out(float** dev, size_t n, const char* tag) {
-    void* p;
-    MB_TRY(alloc(&p, n * sizeof(float), tag));
-    *dev = static_cast<float*>(p);
-    return MIMIR_B200_OK;
-  }
-};
-
-int finish_download(float* host, const float* dev, size_t n) {
-  MB_TRY(check_device_error_word(nullptr));
-  MB_CUDA(cudaMemcpy(host, dev, n * sizeof(float), cudaMemcpyDeviceToHost));
-  return MIMIR_B200_OK;
-}
-
-#define MB_REQUIRE_INIT() \
-  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called")
 
 }  // namespace
 

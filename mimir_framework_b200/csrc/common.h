@@ -101,7 +101,7 @@ size_t skinny_scratch_bytes(int m, int k, int n);
 
 // pointwise.cu ---------------------------------------------------------------------------------
 int launch_eltwise(int op, const float* a, const float* b, float* y, int batch, int64_t n, int64_t nb,
-                   cudaStream_t st);
+                   cudaStream_t st, float alpha = 0.0f);
 int launch_embedding(const float* ids_f32, const int32_t* ids_i32, const float* table, float* y, int64_t n_ids,
                      int vocab, int dim, int padding_idx, cudaStream_t st);
 int launch_upsample_nearest(const float* x, float* y, int batch, int ch, int in_h, int in_w, int sh, int sw,
@@ -112,8 +112,9 @@ int launch_global_avgpool(const float* x, float* y, int batch, int ch, int hw, c
 int launch_argmax_rows(const float* x, int32_t* ids, int64_t rows, int n, cudaStream_t st);
 // copies `n` floats per sample from src (per-sample stride n) into dst at offset `off` of a
 // per-sample vector of `total` floats (Concat)
+// (Concat); with `src_stride` > 0 the source is a slice of a larger per-sample vector (Split / Chunk)
 int launch_copy_strided(const float* src, float* dst, int batch, int64_t n, int64_t total, int64_t off,
-                        cudaStream_t st);
+                        cudaStream_t st, int64_t src_stride = 0);
 int launch_broadcast_rows(const float* src, float* dst, int batch, int64_t n, cudaStream_t st);
 
 // norms.cu -------------------------------------------------------------------------------------
@@ -126,9 +127,20 @@ int launch_groupnorm(const float* x, const float* gamma, const float* beta, floa
 int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softmax, cudaStream_t st);
 
 // attention.cu ---------------------------------------------------------------------------------
+// Where the projected queries, keys and values of one attention call live: row-major fp32, sample b at
+// q + b*q_len*ldq and k/v + b*kv_len*ldkv.
+struct AttnView {
+  const float* q = nullptr;
+  const float* k = nullptr;
+  const float* v = nullptr;
+  long long ldq = 0, ldkv = 0;
+  int q_len = 0, kv_len = 0;
+};
 // qkv fp32 [batch*seq, 3E] (Q | K | V thirds) -> attended fp32 [batch*seq, E]
 int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
                           cudaStream_t st);
+// general form (cross attention: queries and keys/values from different projections and lengths)
+int launch_attention_core_view(const AttnView& a, float* out, int batch, int embed, int heads, int causal, cudaStream_t st);
 // attention_tc.cu: the same core on tcgen05 (head_dim 64); `ws` holds the bf16 operand planes
 bool attention_tc_supported(int seq, int embed, int heads);
 size_t attention_tc_ws_bytes(int batch, int seq, int embed);
@@ -144,4 +156,20 @@ int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int bat
                                      cudaStream_t st);
 // OIHW fp32 -> planes [planes][oc][round_up(ks*ks*ic, 64)] with K ordered (kh, kw, ic)
 int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st);
+
+// spatial.cu -----------------------------------------------------------------------------------
+int launch_depthwise_conv2d(const float* x, const float* w, const float* bias, float* y, int batch, int ch, int h, int wd, int k,
+                            int stride, int pad, int64_t w_count, cudaStream_t st);
+int launch_conv1d(const float* x, const float* w, const float* bias, float* y, int batch, int ic, int oc, int len, int k, int stride,
+                  int pad, int64_t w_count, cudaStream_t st);
+int launch_conv_gather(const float* x, const float* w, float* y, int batch, int ic, int oc, int h, int wd, int oh, int ow, int k,
+                       int stride, int pad, int relu, cudaStream_t st);
+int launch_pool2d(int is_max, const float* x, float* y, int batch, int ch, int h, int wd, int kh, int kw, int sh, int sw, int ph, int pw,
+                  cudaStream_t st);
+int launch_pad2d(int mode, const float* x, float* y, int batch, int ch, int h, int wd, int ph, int pw, cudaStream_t st);
+int launch_pixel_shuffle(const float* x, float* y, int batch, int ic, int h, int wd, int r, cudaStream_t st);
+int launch_upsample_bilinear(const float* x, float* y, int batch, int ch, int h, int wd, int oh, int ow, int half_pixel,
+                             cudaStream_t st);
+int launch_batch_matmul(const float* a, const float* b, float* c, int64_t nb, int m, int k, int n, cudaStream_t st);
+int launch_scale_prefix(float* y, const float* g, int batch, int64_t n, int64_t cnt, cudaStream_t st);
 }  // namespace mb

@@ -26,7 +26,11 @@ namespace {
 
 enum class LT {
   Linear, Attention, Conv2d, LayerNorm, RMSNorm, GroupNorm, Softmax, LogSoftmax, Act, Add, Multiply, Embedding,
-  UpsampleNearest, Permute, Concat, Alias, TokenMeanPool, GlobalAvgPool, Unsupported
+  UpsampleNearest, Permute, Concat, Alias, TokenMeanPool, GlobalAvgPool,
+  // the remaining switch cases
+  CrossAttention, Split, DepthwiseConv2d, Conv1d, ConvTranspose2d, Pool2d, Pad2d, PixelShuffle, UpsampleBilinear, MatMul,
+  BatchMatMul, BatchNorm, InstanceNorm, Binary2, Transpose,
+  Unsupported
 };
 
 struct TypeInfo { LT lt; int act; };
@@ -55,6 +59,36 @@ TypeInfo classify(const std::string& t) {
   if (t == "Identity" || t == "Reshape" || t == "Flatten" || t == "View" || t == "Dropout" || t == "Dropout2d" ||
       t == "AlphaDropout")
     return {LT::Alias, -1};
+  // Squeeze / Unsqueeze only edit a shape vector that nobody reads (LayerOpsExt.hpp:160-208); Reparameterize
+  // at inference copies mu, its first input (Model.cpp:5767-5770)
+  if (t == "Squeeze" || t == "Unsqueeze" || t == "Reparameterize") return {LT::Alias, -1};
+  if (t == "LeakyReLU") return {LT::Act, MIMIR_B200_ELT_LEAKY_RELU};
+  if (t == "Softplus") return {LT::Act, MIMIR_B200_ELT_SOFTPLUS};
+  if (t == "Mish") return {LT::Act, MIMIR_B200_ELT_MISH};
+  if (t == "HardSigmoid") return {LT::Act, MIMIR_B200_ELT_HARD_SIGMOID};
+  if (t == "HardSwish") return {LT::Act, MIMIR_B200_ELT_HARD_SWISH};
+  if (t == "Subtract") return {LT::Binary2, MIMIR_B200_ELT_SUBTRACT};
+  if (t == "Divide") return {LT::Binary2, MIMIR_B200_ELT_DIVIDE};
+  if (t == "CrossAttention") return {LT::CrossAttention, -1};
+  if (t == "Split") return {LT::Split, 0};
+  if (t == "Chunk") return {LT::Split, 1};
+  if (t == "Stack") return {LT::Concat, -1};  // flat append of equal-sized inputs (LayerOpsExt.hpp:245-272)
+  if (t == "DepthwiseConv2d") return {LT::DepthwiseConv2d, -1};
+  if (t == "Conv1d") return {LT::Conv1d, -1};
+  if (t == "ConvTranspose2d") return {LT::ConvTranspose2d, -1};
+  if (t == "MaxPool2d") return {LT::Pool2d, 1};
+  if (t == "AvgPool2d") return {LT::Pool2d, 0};
+  if (t == "ZeroPad2d") return {LT::Pad2d, 0};
+  if (t == "ReflectionPad2d") return {LT::Pad2d, 1};
+  if (t == "ReplicationPad2d") return {LT::Pad2d, 2};
+  if (t == "PixelShuffle") return {LT::PixelShuffle, -1};
+  if (t == "UpsampleBilinear") return {LT::UpsampleBilinear, 0};
+  if (t == "UpsampleBicubic") return {LT::UpsampleBilinear, 1};  // bilinear with half-pixel centres (LayerOpsExt.hpp:695-744)
+  if (t == "MatMul") return {LT::MatMul, -1};
+  if (t == "BatchMatMul") return {LT::BatchMatMul, -1};
+  if (t == "BatchNorm2d" || t == "BatchNorm1d") return {LT::BatchNorm, -1};
+  if (t == "InstanceNorm2d") return {LT::InstanceNorm, -1};
+  if (t == "Transpose") return {LT::Transpose, -1};
   if (t == "TokenMeanPool") return {LT::TokenMeanPool, -1};
   if (t == "GlobalAvgPool2d" || t == "AdaptiveAvgPool2d") return {LT::GlobalAvgPool, -1};
   return {LT::Unsupported, -1};
@@ -74,10 +108,14 @@ struct LayerRT {
   size_t w_split_bytes = 0;
   __nv_bfloat16* w_split2 = nullptr;  // Wout^T for attention
   size_t w_split2_bytes = 0;
+  __nv_bfloat16* w_split3 = nullptr;  // Wout^T for cross attention (w_split = Wq^T, w_split2 = Wkv^T)
+  size_t w_split3_bytes = 0;
   int w_split_k = -1;                 // K the planes were built for (Linear in_features may be implicit)
   // plan
   std::vector<int> in_v;              // tensor versions read
   int out_v = -1;
+  std::vector<int> piece_v;           // Split / Chunk: the tensors "<output>_i"
+  std::vector<int64_t> piece_n;
   bool skip = false;                  // activation folded into its producer
   int fused_act = -1;                 // activation folded into this layer
   bool emit_split = false;            // GEMM writes hi/lo planes for the consuming Linear
@@ -87,7 +125,10 @@ struct LayerRT {
   size_t ws_off = 0, ws_bytes = 0;
   // resolved shapes (per sample)
   int rows_ps = 1, in_f = 0, out_f = 0;       // Linear
-  int seq = 0, embed = 0, heads = 1;          // Attention
+  int seq = 0, embed = 0, heads = 1;          // Attention (cross attention: seq = query length)
+  int kv_len = 0;                             // CrossAttention
+  int kk = 0, kw = 0, st = 1, sw = 1, pd = 0, pw = 0;  // resolved kernel / stride / pad of the spatial ops
+  int mm_b = 1, mm_m = 0, mm_k = 0, mm_n = 0; // MatMul / BatchMatMul
   int h = 0, w = 0, oh = 0, ow = 0;           // Conv2d / GroupNorm / Upsample
   int ch = 0;
   int64_t norm_n = 0;                         // LayerNorm group size
@@ -196,6 +237,7 @@ void free_layer_weights(LayerRT& L, MimirB200Model* m) {
   if (L.w_f32) { dev_free(L.w_f32, L.w_count * 4); m->weight_bytes -= L.w_count * 4; L.w_f32 = nullptr; }
   if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
   if (L.w_split2) { dev_free(L.w_split2, L.w_split2_bytes); m->weight_bytes -= L.w_split2_bytes; L.w_split2 = nullptr; }
+  if (L.w_split3) { dev_free(L.w_split3, L.w_split3_bytes); m->weight_bytes -= L.w_split3_bytes; L.w_split3 = nullptr; }
   L.w_split_k = -1;
 }
 
@@ -236,6 +278,27 @@ int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
     m->weight_bytes += L.w_split2_bytes;
     MB_TRY(launch_split_transposed(L.w_f32, L.w_split, E, 3 * E, wp, st));
     MB_TRY(launch_split_transposed(L.w_f32 + static_cast<size_t>(3) * E * E, L.w_split2, E, E, wp, st));
+    L.w_split_k = E;
+  } else if (L.lt == LT::CrossAttention) {
+    // block = Wq[E][E] | Wkv[E][2E] | Wout[E][E], input-major (Model.cpp:5975-5982)
+    const int E = L.embed;
+    if (L.w_split && L.w_split_k == E) return MIMIR_B200_OK;
+    if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
+    if (L.w_split2) { dev_free(L.w_split2, L.w_split2_bytes); m->weight_bytes -= L.w_split2_bytes; L.w_split2 = nullptr; }
+    if (L.w_split3) { dev_free(L.w_split3, L.w_split3_bytes); m->weight_bytes -= L.w_split3_bytes; L.w_split3 = nullptr; }
+    L.w_split_bytes = split_bytes(E, E, wp);
+    L.w_split2_bytes = split_bytes(2 * E, E, wp);
+    L.w_split3_bytes = split_bytes(E, E, wp);
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split), L.w_split_bytes, "xattn.wq_planes"));
+    m->weight_bytes += L.w_split_bytes;
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split2), L.w_split2_bytes, "xattn.wkv_planes"));
+    m->weight_bytes += L.w_split2_bytes;
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split3), L.w_split3_bytes, "xattn.wout_planes"));
+    m->weight_bytes += L.w_split3_bytes;
+    const size_t EE = static_cast<size_t>(E) * E;
+    MB_TRY(launch_split_transposed(L.w_f32, L.w_split, E, E, wp, st));
+    MB_TRY(launch_split_transposed(L.w_f32 + EE, L.w_split2, E, 2 * E, wp, st));
+    MB_TRY(launch_split_transposed(L.w_f32 + 3 * EE, L.w_split3, E, E, wp, st));
     L.w_split_k = E;
   }
   return MIMIR_B200_OK;
@@ -381,6 +444,185 @@ int infer_layer(LayerRT& L, const std::vector<int64_t>& in_n, int64_t* out_n) {
       *out_n = L.ch;
       return MIMIR_B200_OK;
     }
+    case LT::Binary2: {
+      if (in_n.size() < 2) return fail(MIMIR_B200_E_INVALID, "%s layer requires 2 inputs, got %zu", L.type.c_str(), in_n.size());
+      if (in_n[0] != in_n[1] || n0 <= 0)
+        return fail(MIMIR_B200_E_INVALID, "%s: size mismatch: %lld vs %lld", L.type.c_str(), static_cast<long long>(in_n[0]),
+                    static_cast<long long>(in_n[1]));
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::CrossAttention: {
+      if (in_n.size() < 2) return fail(MIMIR_B200_E_INVALID, "CrossAttention requires 2 inputs (query, key_value), got %zu", in_n.size());
+      L.heads = d.num_heads > 0 ? d.num_heads : 1;
+      L.embed = d.embed_dim;
+      if (L.embed <= 0 && d.head_dim > 0) L.embed = d.head_dim * L.heads;
+      if (L.embed <= 0) return fail(MIMIR_B200_E_INVALID, "CrossAttention: embed_dim must be configured (set layer.embed_dim or head_dim*num_heads)");
+      if (in_n[0] % L.embed != 0) return fail(MIMIR_B200_E_INVALID, "CrossAttention: query input size must be divisible by embed_dim");
+      if (in_n[1] % L.embed != 0) return fail(MIMIR_B200_E_INVALID, "CrossAttention: key/value input size must be divisible by embed_dim");
+      L.seq = static_cast<int>(in_n[0] / L.embed);
+      L.kv_len = static_cast<int>(in_n[1] / L.embed);
+      if (L.seq <= 0 || L.kv_len <= 0) return fail(MIMIR_B200_E_INVALID, "CrossAttention: invalid sequence lengths");
+      if (L.embed % L.heads != 0) return fail(MIMIR_B200_E_INVALID, "CrossAttention: embed_dim must be divisible by num_heads");
+      if (L.w_count < static_cast<size_t>(4) * L.embed * L.embed)
+        return fail(MIMIR_B200_E_INVALID, "CrossAttention: weights not initialized. Call allocateParams() first.");
+      *out_n = in_n[0];
+      return MIMIR_B200_OK;
+    }
+    case LT::Split: {
+      L.piece_n.clear();
+      if (L.act_of_type == 0) {  // Split (Model.cpp:5802-5815, LayerOps.hpp:759-795)
+        if (d.n_splits < 0) return fail(MIMIR_B200_E_UNSUPPORTED, "Split (%s): more than %d pieces", L.name.c_str(), MIMIR_B200_MAX_SPLITS);
+        if (d.n_splits == 0) return fail(MIMIR_B200_E_INVALID, "Split: split_sizes must be configured");
+        int64_t tot = 0;
+        for (int i = 0; i < d.n_splits; ++i) {
+          if (d.split_sizes[i] <= 0) return fail(MIMIR_B200_E_INVALID, "Split: all split_sizes must be positive");
+          L.piece_n.push_back(d.split_sizes[i]);
+          tot += d.split_sizes[i];
+        }
+        if (tot != n0)
+          return fail(MIMIR_B200_E_INVALID, "Split: sum of split_sizes (%lld) != input size (%lld)", static_cast<long long>(tot),
+                      static_cast<long long>(n0));
+      } else {  // Chunk (Model.cpp:5817-5832, LayerOpsExt.hpp:215-240): the first `remainder` chunks get one more
+        if (d.num_chunks <= 0) return fail(MIMIR_B200_E_INVALID, "Chunk: num_chunks must be set");
+        const int64_t base = n0 / d.num_chunks, rem = n0 % d.num_chunks;
+        if (base == 0) return fail(MIMIR_B200_E_UNSUPPORTED, "Chunk (%s): more chunks than elements", L.name.c_str());
+        for (int i = 0; i < d.num_chunks; ++i) L.piece_n.push_back(base + (i < rem ? 1 : 0));
+      }
+      *out_n = L.piece_n[0];
+      return MIMIR_B200_OK;
+    }
+    case LT::DepthwiseConv2d: {  // LayerOpsExt.hpp:446-455: raw kernel_h / stride_h / pad_h
+      L.ch = d.in_channels > 0 ? d.in_channels : 3;
+      L.h = d.input_height > 0 ? d.input_height : 32;
+      L.w = d.input_width > 0 ? d.input_width : 32;
+      L.kk = d.raw_kernel_h > 0 ? d.raw_kernel_h : 3;
+      L.st = d.raw_stride_h > 0 ? d.raw_stride_h : 1;
+      L.pd = d.raw_pad_h >= 0 ? d.raw_pad_h : 0;
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "DepthwiseConv2d (%s): input size mismatch", L.name.c_str());
+      L.oh = (L.h + 2 * L.pd - L.kk) / L.st + 1;
+      L.ow = (L.w + 2 * L.pd - L.kk) / L.st + 1;
+      if (L.oh <= 0 || L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "DepthwiseConv2d (%s): empty output", L.name.c_str());
+      if (L.w_count < static_cast<size_t>(L.ch) * L.kk * L.kk + (d.use_bias ? L.ch : 0))
+        return fail(MIMIR_B200_E_INVALID, "DepthwiseConv2d (%s): weights not uploaded or too small", L.name.c_str());
+      *out_n = static_cast<int64_t>(L.ch) * L.oh * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::Conv1d: {  // LayerOpsExt.hpp:392-399
+      L.ch = d.in_channels > 0 ? d.in_channels : 1;
+      const int oc = d.out_channels > 0 ? d.out_channels : 1;
+      L.kk = d.raw_kernel_h > 0 ? d.raw_kernel_h : 3;
+      L.st = d.raw_stride_h > 0 ? d.raw_stride_h : 1;
+      L.pd = d.raw_pad_h >= 0 ? d.raw_pad_h : 0;
+      if (n0 % L.ch != 0) return fail(MIMIR_B200_E_INVALID, "Conv1d (%s): input size is not a multiple of in_channels", L.name.c_str());
+      L.w = static_cast<int>(n0 / L.ch);
+      L.ow = (L.w + 2 * L.pd - L.kk) / L.st + 1;
+      if (L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "Conv1d (%s): empty output", L.name.c_str());
+      if (L.w_count < static_cast<size_t>(oc) * L.ch * L.kk + (d.use_bias ? oc : 0))
+        return fail(MIMIR_B200_E_INVALID, "Conv1d (%s): weights not uploaded or too small", L.name.c_str());
+      L.out_f = oc;
+      *out_n = static_cast<int64_t>(oc) * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::ConvTranspose2d: {  // Model.cpp:4908-4953
+      if (d.in_channels <= 0 || d.out_channels <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: in_channels and out_channels must be set");
+      if (d.kernel <= 0 || d.stride <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: kernel_size must be set");
+      L.h = d.input_height > 0 ? d.input_height : 64;
+      L.w = d.input_width > 0 ? d.input_width : 64;
+      L.ch = d.in_channels;
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "ConvTranspose2d (%s): input size mismatch", L.name.c_str());
+      L.oh = (L.h - 1) * d.stride - 2 * d.padding + d.kernel;
+      L.ow = (L.w - 1) * d.stride - 2 * d.padding + d.kernel;
+      if (L.oh <= 0 || L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "ConvTranspose2d (%s): empty output", L.name.c_str());
+      if (L.w_count < static_cast<size_t>(d.out_channels) * d.in_channels * d.kernel * d.kernel)
+        return fail(MIMIR_B200_E_INVALID, "Conv2d: weights invalid");
+      *out_n = static_cast<int64_t>(d.out_channels) * L.oh * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::Pool2d: {
+      const bool is_max = L.act_of_type == 1;
+      L.ch = d.in_channels > 0 ? d.in_channels : 64;
+      L.h = d.input_height > 0 ? d.input_height : (is_max ? 64 : 32);  // Model.cpp:5511-5512 vs LayerOps.hpp:416-417
+      L.w = d.input_width > 0 ? d.input_width : (is_max ? 64 : 32);
+      L.kk = d.kernel; L.st = d.stride; L.pd = d.padding;
+      L.kw = is_max ? d.kernel : (d.kernel_w > 0 ? d.kernel_w : d.kernel);
+      L.sw = is_max ? d.stride : (d.stride_w > 0 ? d.stride_w : d.stride);
+      L.pw = is_max ? d.padding : d.padding_w;
+      if (L.kk <= 0 || L.kw <= 0) return fail(MIMIR_B200_E_INVALID, "MaxPool2d: kernel_size must be > 0");
+      if (L.st <= 0 || L.sw <= 0) return fail(MIMIR_B200_E_INVALID, "MaxPool2d: stride must be > 0");
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "%s (%s): input size mismatch", L.type.c_str(), L.name.c_str());
+      L.oh = (L.h + 2 * L.pd - L.kk) / L.st + 1;
+      L.ow = (L.w + 2 * L.pw - L.kw) / L.sw + 1;
+      if (L.oh <= 0 || L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "MaxPool2d: output dimensions must be > 0");
+      *out_n = static_cast<int64_t>(L.ch) * L.oh * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::Pad2d: {  // LayerOpsExt.hpp:586-595, 618-624
+      L.ch = d.in_channels > 0 ? d.in_channels : 3;
+      L.h = d.input_height > 0 ? d.input_height : 32;
+      L.w = d.input_width > 0 ? d.input_width : 32;
+      L.pd = d.raw_pad_h >= 0 ? d.raw_pad_h : 1;
+      L.pw = (L.act_of_type == 0) ? (d.raw_pad_w >= 0 ? d.raw_pad_w : 1) : L.pd;  // reflection / replication pad both axes by pad_h
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "%s (%s): input size mismatch", L.type.c_str(), L.name.c_str());
+      L.oh = L.h + 2 * L.pd; L.ow = L.w + 2 * L.pw;
+      *out_n = static_cast<int64_t>(L.ch) * L.oh * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::PixelShuffle: {  // LayerOpsExt.hpp:753-768
+      L.kk = d.scale_h > 0 ? d.scale_h : 2;
+      L.ch = d.in_channels > 0 ? d.in_channels : 12;
+      L.h = d.input_height > 0 ? d.input_height : 32;
+      L.w = d.input_width > 0 ? d.input_width : 32;
+      if (L.ch % (L.kk * L.kk) != 0)
+        return fail(MIMIR_B200_E_INVALID, "PixelShuffle: in_channels (%d) must be divisible by upscale_factor^2 (%d)", L.ch, L.kk * L.kk);
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "PixelShuffle (%s): input size mismatch", L.name.c_str());
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::UpsampleBilinear: {  // Model.cpp:6020-6054: out_h / out_w are the INPUT size, the factor is always 2
+      if (d.out_h <= 0 || d.out_w <= 0 || (L.act_of_type == 0 && d.in_channels <= 0))
+        return fail(MIMIR_B200_E_INVALID, "%s: dimensions must be set", L.type.c_str());
+      L.h = d.out_h; L.w = d.out_w;
+      L.ch = d.in_channels > 0 ? d.in_channels : 3;
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0) return fail(MIMIR_B200_E_INVALID, "%s (%s): input size mismatch", L.type.c_str(), L.name.c_str());
+      L.oh = 2 * L.h; L.ow = 2 * L.w;
+      *out_n = static_cast<int64_t>(L.ch) * L.oh * L.ow;
+      return MIMIR_B200_OK;
+    }
+    case LT::MatMul:
+    case LT::BatchMatMul: {  // Model.cpp:5847-5898: M = in_features, K = out_features, N = embed_dim, batch = seq_len
+      if (in_n.size() < 2) return fail(MIMIR_B200_E_INVALID, "%s requires 2 inputs", L.type.c_str());
+      const bool bmm = L.lt == LT::BatchMatMul;
+      if (d.in_features <= 0 || d.out_features <= 0 || d.embed_dim <= 0 || (bmm && d.seq_len <= 0))
+        return fail(MIMIR_B200_E_INVALID, "%s: dimensions (in_features, out_features, embed_dim) must be configured", L.type.c_str());
+      L.mm_b = bmm ? d.seq_len : 1; L.mm_m = d.in_features; L.mm_k = d.out_features; L.mm_n = d.embed_dim;
+      if (in_n[0] != static_cast<int64_t>(L.mm_b) * L.mm_m * L.mm_k) return fail(MIMIR_B200_E_INVALID, "%s: A size mismatch", L.type.c_str());
+      if (in_n[1] != static_cast<int64_t>(L.mm_b) * L.mm_k * L.mm_n) return fail(MIMIR_B200_E_INVALID, "%s: B size mismatch", L.type.c_str());
+      *out_n = static_cast<int64_t>(L.mm_b) * L.mm_m * L.mm_n;
+      return MIMIR_B200_OK;
+    }
+    case LT::BatchNorm:
+      if (n0 <= 0) return fail(MIMIR_B200_E_INVALID, "%s: empty input", L.type.c_str());
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    case LT::InstanceNorm: {  // LayerOpsExt.hpp:282-294
+      L.ch = d.in_channels > 0 ? d.in_channels : 3;
+      L.h = d.input_height > 0 ? d.input_height : 32;
+      L.w = d.input_width > 0 ? d.input_width : 32;
+      if (static_cast<int64_t>(L.ch) * L.h * L.w != n0)
+        return fail(MIMIR_B200_E_INVALID, "InstanceNorm2d: input size mismatch. Expected %lld, got %lld",
+                    static_cast<long long>(L.ch) * L.h * L.w, static_cast<long long>(n0));
+      if (d.affine && L.w_count > 0 && L.w_count < static_cast<size_t>(2) * L.ch)
+        return fail(MIMIR_B200_E_INVALID, "InstanceNorm2d (%s): weights too small", L.name.c_str());
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::Transpose: {  // Model.cpp:5649-5659: rows = in_features, cols = out_features
+      if (d.in_features <= 0 || d.out_features <= 0) return fail(MIMIR_B200_E_INVALID, "Transpose: in_features and out_features must be set");
+      if (n0 != static_cast<int64_t>(d.in_features) * d.out_features) return fail(MIMIR_B200_E_INVALID, "Transpose: input size mismatch");
+      *out_n = n0;
+      return MIMIR_B200_OK;
+    }
     default:
       return fail(MIMIR_B200_E_UNSUPPORTED, "layer type '%s' (%s) is not supported by the B200 backend", L.type.c_str(), L.name.c_str());
   }
@@ -437,11 +679,26 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     }
     int64_t out_n = 0;
     MB_TRY(infer_layer(L, in_n, &out_n));
+    L.piece_v.clear();
+    if (L.lt == LT::Split) {
+      // the pieces are stored as "<output>_<i>" and the layer's own output is piece 0 (Model.cpp:5808-5813)
+      const std::string base = L.output.empty() ? "x" : L.output;
+      for (size_t pi = 0; pi < L.piece_n.size(); ++pi) {
+        TensorV pt;
+        pt.name = base + "_" + std::to_string(pi);
+        pt.n = L.piece_n[pi];
+        pt.producer = li;
+        m->tensors.push_back(pt);
+        L.piece_v.push_back(static_cast<int>(m->tensors.size()) - 1);
+        cur[pt.name] = L.piece_v.back();
+      }
+    }
     TensorV t;
     t.name = L.output.empty() ? "x" : L.output;
     t.n = out_n;
     t.producer = li;
     if (L.lt == LT::Alias) t.alias_of = root_of(m->tensors, L.in_v[0]);
+    if (L.lt == LT::Split) t.alias_of = L.piece_v[0];
     m->tensors.push_back(t);
     L.out_v = static_cast<int>(m->tensors.size()) - 1;
     for (int v : L.in_v) m->tensors[v].consumers.push_back(li);
@@ -463,7 +720,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
   // ---- fusion 1: activation into the producing GEMM / GroupNorm ---------------------------------
   for (int li = 0; li < nl; ++li) {
     LayerRT& A = m->layers[li];
-    if (A.lt != LT::Act) continue;
+    if (A.lt != LT::Act || A.act_of_type > MIMIR_B200_ELT_SIGMOID) continue;  // the epilogues know GELU..Sigmoid
     const int pv = A.in_v[0];
     TensorV& pt = m->tensors[pv];
     if (pt.alias_of >= 0 || pt.producer < 0 || pv == out_root || total_consumers(pv) != 1) continue;
@@ -492,7 +749,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
       LayerRT& P = m->layers[ut.producer];
       if (P.out_v != uv || P.res_v >= 0 || P.skip) continue;
       const bool gemm_like = (P.lt == LT::Linear && !linear_uses_skinny(P.rows_ps * batch, m->precision)) ||
-                             P.lt == LT::Attention || P.lt == LT::Conv2d;
+                             P.lt == LT::Attention || P.lt == LT::CrossAttention || P.lt == LT::Conv2d;
       if (!gemm_like && P.lt != LT::GroupNorm) continue;
       // the other operand must already exist when P runs
       const int orr = root_of(m->tensors, ov);
@@ -570,6 +827,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     LayerRT& L = m->layers[li];
     if (!L.skip && L.lt != LT::Alias) {
       place(L.out_v);
+      for (int pv : L.piece_v) place(pv);
       const int64_t rows = static_cast<int64_t>(batch) * L.rows_ps;
       switch (L.lt) {
         case LT::Linear:
@@ -581,6 +839,12 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
           L.ws_bytes = attention_ws_bytes(batch, L.seq, L.embed, L.heads, m->precision);
           const uint64_t core = 4ull * batch * L.seq * L.seq * L.embed;
           flops += 2ull * r * L.embed * 4 * L.embed + (L.d.causal ? core / 2 : core);
+          break;
+        }
+        case LT::CrossAttention: {
+          L.ws_bytes = cross_attention_ws_bytes(batch, L.seq, L.kv_len, L.embed, m->precision);
+          const uint64_t E = static_cast<uint64_t>(L.embed);
+          flops += 2ull * batch * L.seq * E * E * 2 + 2ull * batch * L.kv_len * E * 2 * E + 4ull * batch * L.seq * L.kv_len * E;
           break;
         }
         case LT::Conv2d: {
@@ -716,7 +980,8 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         s = launch_softmax(f32p(L.in_v[0]), f32p(L.out_v), batch, m->tensors[L.in_v[0]].n, L.lt == LT::LogSoftmax, st);
         break;
       case LT::Act:
-        s = launch_eltwise(L.act_of_type, f32p(L.in_v[0]), nullptr, f32p(L.out_v), batch, m->tensors[L.in_v[0]].n, 0, st);
+        s = launch_eltwise(L.act_of_type, f32p(L.in_v[0]), nullptr, f32p(L.out_v), batch, m->tensors[L.in_v[0]].n, 0, st,
+                           d.leaky_relu_alpha > 0.0f ? d.leaky_relu_alpha : 0.01f);
         break;
       case LT::Add:
       case LT::Multiply: {
@@ -744,6 +1009,79 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
           if (s != MIMIR_B200_OK) break;
           off += m->tensors[v].n;
         }
+        break;
+      }
+      case LT::CrossAttention: {
+        CrossAttentionExec e;
+        e.batch = batch; e.q_len = L.seq; e.kv_len = L.kv_len; e.embed = L.embed; e.heads = L.heads; e.causal = d.causal;
+        e.precision = m->precision;
+        e.q_in = f32p(L.in_v[0]); e.kv_in = f32p(L.in_v[1]);
+        e.wq_split = L.w_split; e.wkv_split = L.w_split2; e.wout_split = L.w_split3;
+        e.y = f32p(L.out_v); e.ws = ws;
+        if (L.res_v >= 0) e.residual = f32p(L.res_v);
+        s = cross_attention_exec(e, st);
+        break;
+      }
+      case LT::Binary2:
+        s = launch_eltwise(L.act_of_type, f32p(L.in_v[0]), f32p(L.in_v[1]), f32p(L.out_v), batch, m->tensors[L.in_v[0]].n,
+                           m->tensors[L.in_v[1]].n, st);
+        break;
+      case LT::Split: {
+        const int64_t total = m->tensors[L.in_v[0]].n;
+        int64_t off = 0;
+        for (size_t pi = 0; pi < L.piece_v.size(); ++pi) {
+          s = launch_copy_strided(f32p(L.in_v[0]) + off, f32p(L.piece_v[pi]), batch, L.piece_n[pi], L.piece_n[pi], 0, st, total);
+          if (s != MIMIR_B200_OK) break;
+          off += L.piece_n[pi];
+        }
+        break;
+      }
+      case LT::DepthwiseConv2d:
+        s = launch_depthwise_conv2d(f32p(L.in_v[0]), L.w_f32, d.use_bias ? L.w_f32 + static_cast<size_t>(L.ch) * L.kk * L.kk : nullptr,
+                                    f32p(L.out_v), batch, L.ch, L.h, L.w, L.kk, L.st, L.pd, static_cast<int64_t>(L.w_count), st);
+        break;
+      case LT::Conv1d:
+        s = launch_conv1d(f32p(L.in_v[0]), L.w_f32, d.use_bias ? L.w_f32 + static_cast<size_t>(L.out_f) * L.ch * L.kk : nullptr,
+                          f32p(L.out_v), batch, L.ch, L.out_f, L.w, L.kk, L.st, L.pd, static_cast<int64_t>(L.w_count), st);
+        break;
+      case LT::ConvTranspose2d:
+        s = launch_conv_gather(f32p(L.in_v[0]), L.w_f32, f32p(L.out_v), batch, d.in_channels, d.out_channels, L.h, L.w, L.oh, L.ow,
+                               d.kernel, d.stride, d.padding, d.activation != 0, st);
+        break;
+      case LT::Pool2d:
+        s = launch_pool2d(L.act_of_type, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.kk, L.kw, L.st, L.sw, L.pd, L.pw, st);
+        break;
+      case LT::Pad2d:
+        s = launch_pad2d(L.act_of_type, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.pd, L.pw, st);
+        break;
+      case LT::PixelShuffle:
+        s = launch_pixel_shuffle(f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.kk, st);
+        break;
+      case LT::UpsampleBilinear:
+        s = launch_upsample_bilinear(f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.oh, L.ow, L.act_of_type, st);
+        break;
+      case LT::MatMul:
+      case LT::BatchMatMul:
+        s = launch_batch_matmul(f32p(L.in_v[0]), f32p(L.in_v[1]), f32p(L.out_v), static_cast<int64_t>(batch) * L.mm_b, L.mm_m, L.mm_k,
+                                L.mm_n, st);
+        break;
+      case LT::BatchNorm: {
+        // statistics over the whole sample, then y[i] *= w[i] for i < weight count; no shift (Model.cpp:5396-5416)
+        const int64_t n = m->tensors[L.in_v[0]].n;
+        s = launch_layernorm(f32p(L.in_v[0]), nullptr, nullptr, f32p(L.out_v), batch, n, d.eps, st);
+        if (s == MIMIR_B200_OK && d.affine && L.w_f32 && L.w_count > 0)
+          s = launch_scale_prefix(f32p(L.out_v), L.w_f32, batch, n, static_cast<int64_t>(L.w_count), st);
+        break;
+      }
+      case LT::InstanceNorm: {
+        const bool aff = d.affine && L.w_f32 && L.w_count >= static_cast<size_t>(2) * L.ch;
+        s = launch_groupnorm(f32p(L.in_v[0]), aff ? L.w_f32 : nullptr, aff ? L.w_f32 + L.ch : nullptr, f32p(L.out_v), batch, L.ch,
+                             L.h * L.w, L.ch, d.eps, -1, nullptr, st);
+        break;
+      }
+      case LT::Transpose: {
+        const int shape[2] = {d.in_features, d.out_features}, dims[2] = {1, 0};
+        s = launch_permute(f32p(L.in_v[0]), f32p(L.out_v), batch, 2, shape, dims, st);
         break;
       }
       case LT::TokenMeanPool:
@@ -852,6 +1190,7 @@ int mimir_b200_model_set_precision(MimirB200ModelHandle m, int precision) {
     for (auto& L : m->layers) {
       if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
       if (L.w_split2) { dev_free(L.w_split2, L.w_split2_bytes); m->weight_bytes -= L.w_split2_bytes; L.w_split2 = nullptr; }
+      if (L.w_split3) { dev_free(L.w_split3, L.w_split3_bytes); m->weight_bytes -= L.w_split3_bytes; L.w_split3 = nullptr; }
       L.w_split_k = -1;
     }
     m->planned_batch = 0;

@@ -7,6 +7,7 @@
 
 namespace mb {
 
+inline size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 void precision_planes(int precision, int* a_planes, int* w_planes);
 size_t split_bytes(int64_t rows, int k, int planes);
 int check_device_error_word(cudaStream_t st);
@@ -43,6 +44,22 @@ struct AttentionExec {
 };
 size_t attention_ws_bytes(int batch, int seq, int embed, int heads, int precision);
 int attention_exec(const AttentionExec& e, cudaStream_t st);
+
+// CrossAttention (LayerOps.hpp:1116-1216): Q = query . Wq, K | V = key_value . Wkv, softmax core, . Wout
+struct CrossAttentionExec {
+  int batch = 0, q_len = 0, kv_len = 0, embed = 0, heads = 1, causal = 0;
+  int precision = MIMIR_B200_PREC_BF16X2;
+  const float* q_in = nullptr;                 // fp32 [batch*q_len, embed]
+  const float* kv_in = nullptr;                // fp32 [batch*kv_len, embed]
+  const __nv_bfloat16* wq_split = nullptr;     // planes of Wq^T:   [E][round_up(E,64)]
+  const __nv_bfloat16* wkv_split = nullptr;    // planes of Wkv^T:  [2E][round_up(E,64)]
+  const __nv_bfloat16* wout_split = nullptr;   // planes of Wout^T: [E][round_up(E,64)]
+  const float* residual = nullptr;
+  float* y = nullptr;
+  void* ws = nullptr;
+};
+size_t cross_attention_ws_bytes(int batch, int q_len, int kv_len, int embed, int precision);
+int cross_attention_exec(const CrossAttentionExec& e, cudaStream_t st);
 
 struct ConvExec {
   int batch = 0, ic = 0, oc = 0, h = 0, w = 0, ks = 3, stride = 1, pad = 0;

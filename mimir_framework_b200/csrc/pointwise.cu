@@ -11,8 +11,14 @@
 namespace mb {
 namespace {
 
-__device__ __forceinline__ float act_apply(int op, float v) {
+__device__ __forceinline__ float act_apply(int op, float v, float alpha = 0.0f) {
   switch (op) {
+    // LayerOpsExt.hpp:29-99
+    case MIMIR_B200_ELT_LEAKY_RELU: return v > 0.0f ? v : alpha * v;
+    case MIMIR_B200_ELT_SOFTPLUS: return v > 20.0f ? v : logf(1.0f + expf(v));
+    case MIMIR_B200_ELT_MISH: return v * tanhf(v > 20.0f ? v : logf(1.0f + expf(v)));
+    case MIMIR_B200_ELT_HARD_SIGMOID: return fmaxf(0.0f, fminf(1.0f, (v + 3.0f) / 6.0f));
+    case MIMIR_B200_ELT_HARD_SWISH: return v * fmaxf(0.0f, fminf(1.0f, (v + 3.0f) / 6.0f));
     case MIMIR_B200_ELT_GELU: {
       const float c = 0.7978845608f;  // sqrt(2.0f / 3.14159265359f) in fp32
       return v * (0.5f * (1.0f + tanhf(c * (v + 0.044715f * v * v * v))));
@@ -26,7 +32,7 @@ __device__ __forceinline__ float act_apply(int op, float v) {
 }
 
 template <int OP>
-__global__ void unary_kernel(const float* __restrict__ a, float* __restrict__ y, long long total) {
+__global__ void unary_kernel(const float* __restrict__ a, float* __restrict__ y, long long total, float alpha) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   const bool vec = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
@@ -34,17 +40,28 @@ __global__ void unary_kernel(const float* __restrict__ a, float* __restrict__ y,
     const long long n4 = total >> 2;
     for (long long i = tid; i < n4; i += stride) {
       float4 v = __ldg(reinterpret_cast<const float4*>(a) + i);
-      v.x = act_apply(OP, v.x); v.y = act_apply(OP, v.y); v.z = act_apply(OP, v.z); v.w = act_apply(OP, v.w);
+      v.x = act_apply(OP, v.x, alpha); v.y = act_apply(OP, v.y, alpha); v.z = act_apply(OP, v.z, alpha); v.w = act_apply(OP, v.w, alpha);
       reinterpret_cast<float4*>(y)[i] = v;
     }
-    for (long long i = (n4 << 2) + tid; i < total; i += stride) y[i] = act_apply(OP, a[i]);
+    for (long long i = (n4 << 2) + tid; i < total; i += stride) y[i] = act_apply(OP, a[i], alpha);
   } else {
-    for (long long i = tid; i < total; i += stride) y[i] = act_apply(OP, a[i]);
+    for (long long i = tid; i < total; i += stride) y[i] = act_apply(OP, a[i], alpha);
   }
 }
 
-// y[s, i] = a[s, i] (+|*) b[s, i % nb]; nb == n is the plain case
-template <bool MUL>
+// BOP: 0 add, 1 multiply, 2 subtract (LayerOpsExt.hpp:105-122), 3 divide (LayerOpsExt.hpp:127-148: a divisor
+// closer to zero than 1e-8 is replaced by +-1e-8, +1e-8 for +-0)
+template <int BOP>
+__device__ __forceinline__ float bin_apply(float u, float w) {
+  if (BOP == 0) return u + w;
+  if (BOP == 1) return u * w;
+  if (BOP == 2) return u - w;
+  if (fabsf(w) < 1e-8f) w = (w >= 0.0f) ? 1e-8f : -1e-8f;
+  return u / w;
+}
+
+// y[s, i] = a[s, i] op b[s, i % nb]; nb == n is the plain case
+template <int BOP>
 __global__ void binary_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ y,
                               long long batch, long long n, long long nb) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -58,16 +75,15 @@ __global__ void binary_kernel(const float* __restrict__ a, const float* __restri
       const float4 u = __ldg(reinterpret_cast<const float4*>(a) + i);
       const float4 w = __ldg(reinterpret_cast<const float4*>(b) + i);
       float4 r;
-      if (MUL) { r.x = u.x * w.x; r.y = u.y * w.y; r.z = u.z * w.z; r.w = u.w * w.w; }
-      else     { r.x = u.x + w.x; r.y = u.y + w.y; r.z = u.z + w.z; r.w = u.w + w.w; }
+      r.x = bin_apply<BOP>(u.x, w.x); r.y = bin_apply<BOP>(u.y, w.y); r.z = bin_apply<BOP>(u.z, w.z); r.w = bin_apply<BOP>(u.w, w.w);
       reinterpret_cast<float4*>(y)[i] = r;
     }
-    for (long long i = (n4 << 2) + tid; i < total; i += stride) y[i] = MUL ? a[i] * b[i] : a[i] + b[i];
+    for (long long i = (n4 << 2) + tid; i < total; i += stride) y[i] = bin_apply<BOP>(a[i], b[i]);
   } else {
     for (long long i = tid; i < total; i += stride) {
       const long long s = i / n, j = i - s * n;
       const float w = b[s * nb + (j % nb)];
-      y[i] = MUL ? a[i] * w : a[i] + w;
+      y[i] = bin_apply<BOP>(a[i], w);
     }
   }
 }
@@ -204,7 +220,8 @@ int grid_for(long long work_items, int threads) {
 
 }  // namespace
 
-int launch_eltwise(int op, const float* a, const float* b, float* y, int batch, int64_t n, int64_t nb, cudaStream_t st) {
+int launch_eltwise(int op, const float* a, const float* b, float* y, int batch, int64_t n, int64_t nb, cudaStream_t st,
+                   float alpha) {
   if (batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "eltwise: inputs must be non-empty");
   const long long total = static_cast<long long>(batch) * n;
   const int threads = 256;
@@ -216,14 +233,27 @@ int launch_eltwise(int op, const float* a, const float* b, float* y, int batch, 
       if (op == MIMIR_B200_ELT_MULTIPLY && nb != n) return fail(MIMIR_B200_E_INVALID, "Multiply: input sizes must match");
       if (nb != n && nb != 1 && (n % nb) != 0)
         return fail(MIMIR_B200_E_INVALID, "Add: input sizes must match or be broadcastable");
-      if (op == MIMIR_B200_ELT_ADD) binary_kernel<false><<<grid, threads, 0, st>>>(a, b, y, batch, n, nb);
-      else binary_kernel<true><<<grid, threads, 0, st>>>(a, b, y, batch, n, nb);
+      if (op == MIMIR_B200_ELT_ADD) binary_kernel<0><<<grid, threads, 0, st>>>(a, b, y, batch, n, nb);
+      else binary_kernel<1><<<grid, threads, 0, st>>>(a, b, y, batch, n, nb);
       break;
-    case MIMIR_B200_ELT_GELU: unary_kernel<MIMIR_B200_ELT_GELU><<<grid, threads, 0, st>>>(a, y, total); break;
-    case MIMIR_B200_ELT_SILU: unary_kernel<MIMIR_B200_ELT_SILU><<<grid, threads, 0, st>>>(a, y, total); break;
-    case MIMIR_B200_ELT_RELU: unary_kernel<MIMIR_B200_ELT_RELU><<<grid, threads, 0, st>>>(a, y, total); break;
-    case MIMIR_B200_ELT_TANH: unary_kernel<MIMIR_B200_ELT_TANH><<<grid, threads, 0, st>>>(a, y, total); break;
-    case MIMIR_B200_ELT_SIGMOID: unary_kernel<MIMIR_B200_ELT_SIGMOID><<<grid, threads, 0, st>>>(a, y, total); break;
+    case MIMIR_B200_ELT_SUBTRACT:
+    case MIMIR_B200_ELT_DIVIDE:
+      if (!b || nb != n)
+        return fail(MIMIR_B200_E_INVALID, "%s: size mismatch: %lld vs %lld", op == MIMIR_B200_ELT_SUBTRACT ? "Subtract" : "Divide",
+                    static_cast<long long>(n), static_cast<long long>(nb));
+      if (op == MIMIR_B200_ELT_SUBTRACT) binary_kernel<2><<<grid, threads, 0, st>>>(a, b, y, batch, n, nb);
+      else binary_kernel<3><<<grid, threads, 0, st>>>(a, b, y, batch, n, nb);
+      break;
+    case MIMIR_B200_ELT_GELU: unary_kernel<MIMIR_B200_ELT_GELU><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_SILU: unary_kernel<MIMIR_B200_ELT_SILU><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_RELU: unary_kernel<MIMIR_B200_ELT_RELU><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_TANH: unary_kernel<MIMIR_B200_ELT_TANH><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_SIGMOID: unary_kernel<MIMIR_B200_ELT_SIGMOID><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_LEAKY_RELU: unary_kernel<MIMIR_B200_ELT_LEAKY_RELU><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_SOFTPLUS: unary_kernel<MIMIR_B200_ELT_SOFTPLUS><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_MISH: unary_kernel<MIMIR_B200_ELT_MISH><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_HARD_SIGMOID: unary_kernel<MIMIR_B200_ELT_HARD_SIGMOID><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_HARD_SWISH: unary_kernel<MIMIR_B200_ELT_HARD_SWISH><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
     default: return fail(MIMIR_B200_E_INVALID, "eltwise: unknown op %d", op);
   }
   MB_CUDA(cudaGetLastError());
@@ -300,9 +330,11 @@ int launch_argmax_rows(const float* x, int32_t* ids, int64_t rows, int n, cudaSt
   return MIMIR_B200_OK;
 }
 
-int launch_copy_strided(const float* src, float* dst, int batch, int64_t n, int64_t total, int64_t off, cudaStream_t st) {
+int launch_copy_strided(const float* src, float* dst, int batch, int64_t n, int64_t total, int64_t off, cudaStream_t st,
+                        int64_t src_stride) {
   if (batch <= 0 || n <= 0) return MIMIR_B200_OK;
-  copy_strided_kernel<<<grid_for(static_cast<long long>(batch) * n, 256), 256, 0, st>>>(src, dst, batch, n, total, off, n);
+  copy_strided_kernel<<<grid_for(static_cast<long long>(batch) * n, 256), 256, 0, st>>>(src, dst, batch, n, total, off,
+                                                                                        src_stride > 0 ? src_stride : n);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;

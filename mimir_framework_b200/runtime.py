@@ -44,6 +44,17 @@ _SIGS = {
     "mimir_b200_permute": [_P, _P, C.c_int, C.c_int, _P, _P],
     "mimir_b200_token_mean_pool": [_P, _P, C.c_int, C.c_int, C.c_int],
     "mimir_b200_global_avgpool": [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_eltwise_alpha": [C.c_int, _P, _P, _P, C.c_int, C.c_longlong, C.c_longlong, C.c_float],
+    "mimir_b200_cross_attention": [_P, _P, _P, _P] + [C.c_int] * 6,
+    "mimir_b200_depthwise_conv2d": [_P, _P, _P, _P] + [C.c_int] * 7,
+    "mimir_b200_conv1d": [_P, _P, _P, _P] + [C.c_int] * 7,
+    "mimir_b200_conv_transpose2d": [_P, _P, _P] + [C.c_int] * 9,
+    "mimir_b200_pool2d": [C.c_int, _P, _P] + [C.c_int] * 10,
+    "mimir_b200_pad2d": [C.c_int, _P, _P] + [C.c_int] * 6,
+    "mimir_b200_pixel_shuffle": [_P, _P] + [C.c_int] * 5,
+    "mimir_b200_upsample_bilinear": [_P, _P] + [C.c_int] * 7,
+    "mimir_b200_batch_matmul": [_P, _P, _P, C.c_longlong, C.c_int, C.c_int, C.c_int],
+    "mimir_b200_batchnorm_inference": [_P, _P, C.c_longlong, _P, C.c_int, C.c_longlong, C.c_float],
     "mimir_b200_model_create": [_P, C.c_int, _P],
     "mimir_b200_model_destroy": [_P],
     "mimir_b200_model_set_precision": [_P, C.c_int],
@@ -236,6 +247,88 @@ def global_avgpool(x, batch, ch, h, w):
     x = _f(x)
     y = np.empty(batch * ch, np.float32)
     check(lib().mimir_b200_global_avgpool(_p(x), _p(y), batch, ch, h, w))
+    return y
+
+
+def eltwise_alpha(op, a, alpha, b=None, batch=1):
+    a, b = _f(a), _f(b)
+    n = a.size // batch
+    nb = 0 if b is None else b.size // batch
+    y = np.empty(a.size, np.float32)
+    check(lib().mimir_b200_eltwise_alpha(op, _p(a), _p(b), _p(y), batch, n, nb, alpha))
+    return y
+
+
+def cross_attention(q, kv, w, batch, q_len, kv_len, embed, heads, causal):
+    q, kv, w = _f(q), _f(kv), _f(w)
+    y = np.empty(batch * q_len * embed, np.float32)
+    check(lib().mimir_b200_cross_attention(_p(q), _p(kv), _p(w), _p(y), batch, q_len, kv_len, embed, heads, int(causal)))
+    return y
+
+
+def depthwise_conv2d(x, w, bias, batch, ch, h, wd, k, stride, pad):
+    x, w, bias = _f(x), _f(w), _f(bias)
+    oh, ow = (h + 2 * pad - k) // stride + 1, (wd + 2 * pad - k) // stride + 1
+    y = np.empty(batch * ch * oh * ow, np.float32)
+    check(lib().mimir_b200_depthwise_conv2d(_p(x), _p(w), _p(bias), _p(y), batch, ch, h, wd, k, stride, pad))
+    return y
+
+
+def conv1d(x, w, bias, batch, ic, oc, length, k, stride, pad):
+    x, w, bias = _f(x), _f(w), _f(bias)
+    y = np.empty(batch * oc * ((length + 2 * pad - k) // stride + 1), np.float32)
+    check(lib().mimir_b200_conv1d(_p(x), _p(w), _p(bias), _p(y), batch, ic, oc, length, k, stride, pad))
+    return y
+
+
+def conv_transpose2d(x, w, batch, ic, oc, h, wd, k, stride, pad, relu=False):
+    x, w = _f(x), _f(w)
+    oh, ow = (h - 1) * stride - 2 * pad + k, (wd - 1) * stride - 2 * pad + k
+    y = np.empty(batch * oc * oh * ow, np.float32)
+    check(lib().mimir_b200_conv_transpose2d(_p(x), _p(w), _p(y), batch, ic, oc, h, wd, k, stride, pad, int(relu)))
+    return y
+
+
+def pool2d(is_max, x, batch, ch, h, wd, kh, kw, sh, sw, ph, pw):
+    x = _f(x)
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (wd + 2 * pw - kw) // sw + 1
+    y = np.empty(batch * ch * oh * ow, np.float32)
+    check(lib().mimir_b200_pool2d(int(is_max), _p(x), _p(y), batch, ch, h, wd, kh, kw, sh, sw, ph, pw))
+    return y
+
+
+def pad2d(mode, x, batch, ch, h, wd, ph, pw):
+    x = _f(x)
+    y = np.empty(batch * ch * (h + 2 * ph) * (wd + 2 * pw), np.float32)
+    check(lib().mimir_b200_pad2d(mode, _p(x), _p(y), batch, ch, h, wd, ph, pw))
+    return y
+
+
+def pixel_shuffle(x, batch, ic, h, wd, r):
+    x = _f(x)
+    y = np.empty_like(x)
+    check(lib().mimir_b200_pixel_shuffle(_p(x), _p(y), batch, ic, h, wd, r))
+    return y
+
+
+def upsample_bilinear(x, batch, ch, h, wd, oh, ow, half_pixel=False):
+    x = _f(x)
+    y = np.empty(batch * ch * oh * ow, np.float32)
+    check(lib().mimir_b200_upsample_bilinear(_p(x), _p(y), batch, ch, h, wd, oh, ow, int(half_pixel)))
+    return y
+
+
+def batch_matmul(a, b, nb, M, K, N):
+    a, b = _f(a), _f(b)
+    y = np.empty(nb * M * N, np.float32)
+    check(lib().mimir_b200_batch_matmul(_p(a), _p(b), _p(y), nb, M, K, N))
+    return y
+
+
+def batchnorm_inference(x, w, batch, n, eps=1e-5):
+    x, w = _f(x), _f(w)
+    y = np.empty(batch * n, np.float32)
+    check(lib().mimir_b200_batchnorm_inference(_p(x), _p(w), 0 if w is None else w.size, _p(y), batch, n, eps))
     return y
 
 

@@ -291,8 +291,41 @@ int mo_eltwise(int op, const float* a, const float* b, float* y, long n, long nb
     case 6:
       for (long i = 0; i < n; ++i) y[i] = 1.0f / (1.0f + expf(-a[i]));
       return 0;
+    /* LayerOpsExt.hpp:44-99 (the LeakyReLU slope travels through mo_leaky_relu) */
+    case 8: /* softplus */
+      for (long i = 0; i < n; ++i) y[i] = a[i] > 20.0f ? a[i] : logf(1.0f + expf(a[i]));
+      return 0;
+    case 9: /* mish */
+      for (long i = 0; i < n; ++i) {
+        const float sp = a[i] > 20.0f ? a[i] : logf(1.0f + expf(a[i]));
+        y[i] = a[i] * tanhf(sp);
+      }
+      return 0;
+    case 10: /* hard sigmoid */
+      for (long i = 0; i < n; ++i) y[i] = fmaxf(0.0f, fminf(1.0f, (a[i] + 3.0f) / 6.0f));
+      return 0;
+    case 11: /* hard swish */
+      for (long i = 0; i < n; ++i) y[i] = a[i] * fmaxf(0.0f, fminf(1.0f, (a[i] + 3.0f) / 6.0f));
+      return 0;
+    case 12: /* subtract, LayerOpsExt.hpp:105-122 */
+      if (nb != n) return 1;
+      for (long i = 0; i < n; ++i) y[i] = a[i] - b[i];
+      return 0;
+    case 13: /* divide, LayerOpsExt.hpp:127-148 */
+      if (nb != n) return 1;
+      for (long i = 0; i < n; ++i) {
+        float dv = b[i];
+        if (fabsf(dv) < 1e-8f) dv = dv >= 0 ? 1e-8f : -1e-8f;
+        y[i] = a[i] / dv;
+      }
+      return 0;
   }
   return 1;
+}
+
+/* LayerOpsExt::leaky_relu_forward, LayerOpsExt.hpp:29-39 */
+void mo_leaky_relu(const float* a, float* y, long n, float alpha) {
+  for (long i = 0; i < n; ++i) y[i] = a[i] > 0.0f ? a[i] : alpha * a[i];
 }
 
 /* Embedding case, Model.cpp:5301-5334: id = llround(x); id == padding_idx (when >= 0) or out of
@@ -353,5 +386,232 @@ void mo_global_avgpool(const float* x, float* y, int ch, int h, int w) {
     float s = 0.0f;
     for (long i = 0; i < (long)h * w; ++i) s += x[(size_t)c * h * w + i];
     y[c] = s / area;
+  }
+}
+
+/* ---- the remaining cases of the layer switch -------------------------------------------------- */
+
+/* LayerOps::cross_attention_forward, LayerOps.hpp:1116-1216: Q = query.Wq, KV = kv.Wkv (K | V halves),
+ * per head and query row the same softmax as self attention (masked scores are -1e9 and stay out of
+ * the max), then . Wout.  Weights are input-major; no biases. */
+void mo_cross_attention(const float* q_in, const float* kv_in, const float* wq, const float* wkv, const float* wout, float* y,
+                        int q_len, int kv_len, int E, int heads, int causal) {
+  const int hd = E / heads;
+  float* Q = (float*)malloc(sizeof(float) * (size_t)q_len * E);
+  float* KV = (float*)malloc(sizeof(float) * (size_t)kv_len * 2 * E);
+  float* att = (float*)calloc((size_t)q_len * E, sizeof(float));
+  float* row = (float*)malloc(sizeof(float) * (size_t)kv_len);
+  mo_matmul(q_in, wq, Q, q_len, E, E);
+  mo_matmul(kv_in, wkv, KV, kv_len, E, 2 * E);
+  const float scale = 1.0f / sqrtf((float)hd);
+  for (int h = 0; h < heads; ++h) {
+    const int ho = h * hd;
+    for (int i = 0; i < q_len; ++i) {
+      float mx = -1e30f;
+      for (int j = 0; j < kv_len; ++j) {
+        if (causal && j > i) { row[j] = -1e9f; continue; }
+        float dot = 0.0f;
+        for (int k = 0; k < hd; ++k) dot += Q[(size_t)i * E + ho + k] * KV[(size_t)j * 2 * E + ho + k];
+        const float s = dot * scale;
+        row[j] = s;
+        if (s > mx) mx = s;
+      }
+      float sum = 0.0f;
+      for (int j = 0; j < kv_len; ++j) { row[j] = expf(row[j] - mx); sum += row[j]; }
+      const float inv = 1.0f / (sum + 1e-9f);
+      for (int j = 0; j < kv_len; ++j) row[j] *= inv;
+      for (int k = 0; k < hd; ++k) {
+        float acc = 0.0f;
+        for (int j = 0; j < kv_len; ++j) acc += row[j] * KV[(size_t)j * 2 * E + E + ho + k];
+        att[(size_t)i * E + ho + k] = acc;
+      }
+    }
+  }
+  mo_matmul(att, wout, y, q_len, E, E);
+  free(Q); free(KV); free(att); free(row);
+}
+
+/* LayerOpsExt::depthwise_conv2d_forward, LayerOpsExt.hpp:442-497 */
+void mo_depthwise_conv2d(const float* x, const float* w, const float* bias, float* y, int ch, int h, int wd, int k, int stride,
+                         int pad) {
+  const int oh = (h + 2 * pad - k) / stride + 1, ow = (wd + 2 * pad - k) / stride + 1;
+  for (int c = 0; c < ch; ++c)
+    for (int r = 0; r < oh; ++r)
+      for (int q = 0; q < ow; ++q) {
+        float sum = 0.0f;
+        for (int kh = 0; kh < k; ++kh)
+          for (int kw = 0; kw < k; ++kw) {
+            const int ih = r * stride + kh - pad, iw = q * stride + kw - pad;
+            if (ih >= 0 && ih < h && iw >= 0 && iw < wd) sum += x[(size_t)c * h * wd + ih * wd + iw] * w[c * k * k + kh * k + kw];
+          }
+        if (bias) sum += bias[c];
+        y[((size_t)c * oh + r) * ow + q] = sum;
+      }
+}
+
+/* LayerOpsExt::conv1d_forward, LayerOpsExt.hpp:388-437 */
+void mo_conv1d(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int len, int k, int stride, int pad) {
+  const int olen = (len + 2 * pad - k) / stride + 1;
+  for (int o = 0; o < oc; ++o)
+    for (int ol = 0; ol < olen; ++ol) {
+      float sum = 0.0f;
+      for (int c = 0; c < ic; ++c)
+        for (int kk = 0; kk < k; ++kk) {
+          const int il = ol * stride + kk - pad;
+          if (il >= 0 && il < len) sum += x[c * len + il] * w[(o * ic + c) * k + kk];
+        }
+      if (bias) sum += bias[o];
+      y[o * olen + ol] = sum;
+    }
+}
+
+/* ConvTranspose2d branch of the Conv2d case, Model.cpp:4946-4953 (output size) and :5047-5079 (the
+ * naive loop, which gathers like a FORWARD convolution), optional ReLU :5081-5086 */
+void mo_conv_transpose2d(const float* x, const float* w, float* y, int ic, int oc, int h, int wd, int k, int stride, int pad,
+                         int relu) {
+  const int oh = (h - 1) * stride - 2 * pad + k, ow = (wd - 1) * stride - 2 * pad + k;
+  for (int o = 0; o < oc; ++o)
+    for (int r = 0; r < oh; ++r)
+      for (int q = 0; q < ow; ++q) {
+        float sum = 0.0f;
+        for (int c = 0; c < ic; ++c)
+          for (int kh = 0; kh < k; ++kh)
+            for (int kw = 0; kw < k; ++kw) {
+              const int ih = r * stride + kh - pad, iw = q * stride + kw - pad;
+              if (ih >= 0 && ih < h && iw >= 0 && iw < wd)
+                sum += x[((size_t)c * h + ih) * wd + iw] * w[(((size_t)o * ic + c) * k + kh) * k + kw];
+            }
+        y[((size_t)o * oh + r) * ow + q] = relu ? (sum > 0.0f ? sum : 0.0f) : sum;
+      }
+}
+
+/* MaxPool2d, Model.cpp:5508-5559; AvgPool2d, LayerOps.hpp:404-453 (mean over the in-bounds taps) */
+void mo_pool2d(int is_max, const float* x, float* y, int ch, int h, int wd, int kh_n, int kw_n, int sh, int sw, int ph, int pw) {
+  const int oh = (h + 2 * ph - kh_n) / sh + 1, ow = (wd + 2 * pw - kw_n) / sw + 1;
+  for (int c = 0; c < ch; ++c)
+    for (int r = 0; r < oh; ++r)
+      for (int q = 0; q < ow; ++q) {
+        float acc = is_max ? -INFINITY : 0.0f;
+        int count = 0;
+        for (int kh = 0; kh < kh_n; ++kh)
+          for (int kw = 0; kw < kw_n; ++kw) {
+            const int ih = r * sh + kh - ph, iw = q * sw + kw - pw;
+            if (ih >= 0 && ih < h && iw >= 0 && iw < wd) {
+              const float v = x[((size_t)c * h + ih) * wd + iw];
+              if (is_max) acc = v > acc ? v : acc; else acc += v;
+              ++count;
+            }
+          }
+        y[((size_t)c * oh + r) * ow + q] = is_max ? acc : (count > 0 ? acc / count : 0.0f);
+      }
+}
+
+/* zero / reflection / replication pad, LayerOpsExt.hpp:582-690 (mode 0 / 1 / 2) */
+void mo_pad2d(int mode, const float* x, float* y, int ch, int h, int wd, int ph, int pw) {
+  const int oh = h + 2 * ph, ow = wd + 2 * pw;
+  for (int c = 0; c < ch; ++c)
+    for (int r = 0; r < oh; ++r)
+      for (int q = 0; q < ow; ++q) {
+        int ih = r - ph, iw = q - pw;
+        float v = 0.0f;
+        if (mode == 0) {
+          if (ih >= 0 && ih < h && iw >= 0 && iw < wd) v = x[((size_t)c * h + ih) * wd + iw];
+        } else {
+          if (mode == 1) {
+            if (ih < 0) ih = -ih;
+            if (ih >= h) ih = 2 * h - ih - 2;
+            if (iw < 0) iw = -iw;
+            if (iw >= wd) iw = 2 * wd - iw - 2;
+          }
+          ih = ih < 0 ? 0 : (ih > h - 1 ? h - 1 : ih);
+          iw = iw < 0 ? 0 : (iw > wd - 1 ? wd - 1 : iw);
+          v = x[((size_t)c * h + ih) * wd + iw];
+        }
+        y[((size_t)c * oh + r) * ow + q] = v;
+      }
+}
+
+/* LayerOpsExt::pixel_shuffle_forward, LayerOpsExt.hpp:749-795 */
+void mo_pixel_shuffle(const float* x, float* y, int ic, int h, int wd, int r) {
+  const int oc = ic / (r * r), oh = h * r, ow = wd * r;
+  for (int o = 0; o < oc; ++o)
+    for (int p = 0; p < oh; ++p)
+      for (int q = 0; q < ow; ++q) {
+        const int ih = p / r, iw = q / r;
+        const int c = o * r * r + (p - ih * r) * r + (q - iw * r);
+        y[((size_t)o * oh + p) * ow + q] = x[((size_t)c * h + ih) * wd + iw];
+      }
+}
+
+/* half_pixel 0: LayerOps::upsample_bilinear_forward, LayerOps.hpp:833-874; 1: the function dispatched
+ * for UpsampleBicubic, LayerOpsExt.hpp:695-744 (bilinear weights around a half-pixel source index) */
+void mo_upsample_bilinear(const float* x, float* y, int ch, int h, int wd, int oh, int ow, int half_pixel) {
+  const float sch = (float)h / oh, scw = (float)wd / ow;
+  for (int c = 0; c < ch; ++c)
+    for (int r = 0; r < oh; ++r)
+      for (int q = 0; q < ow; ++q) {
+        float fh, fw;
+        if (half_pixel) {
+          fh = (r + 0.5f) * sch - 0.5f;
+          fw = (q + 0.5f) * scw - 0.5f;
+          fh = fmaxf(0.0f, fminf(fh, h - 1.0f));
+          fw = fmaxf(0.0f, fminf(fw, wd - 1.0f));
+        } else {
+          fh = r * sch;
+          fw = q * scw;
+        }
+        const int h0 = (int)floorf(fh), w0 = (int)floorf(fw);
+        const int h1 = h0 + 1 < h - 1 ? h0 + 1 : h - 1, w1 = w0 + 1 < wd - 1 ? w0 + 1 : wd - 1;
+        const float dh = fh - h0, dw = fw - w0;
+        const float* xp = x + (size_t)c * h * wd;
+        y[((size_t)c * oh + r) * ow + q] = xp[h0 * wd + w0] * (1 - dh) * (1 - dw) + xp[h0 * wd + w1] * (1 - dh) * dw +
+                                           xp[h1 * wd + w0] * dh * (1 - dw) + xp[h1 * wd + w1] * dh * dw;
+      }
+}
+
+/* BatchMatMul case, Model.cpp:5865-5898 (MatMul is nb = 1): k-sequential per output */
+void mo_batch_matmul(const float* A, const float* B, float* C, long nb, int M, int K, int N) {
+  for (long b = 0; b < nb; ++b)
+    for (int i = 0; i < M; ++i)
+      for (int j = 0; j < N; ++j) {
+        float sum = 0.0f;
+        for (int k = 0; k < K; ++k) sum += A[((size_t)b * M + i) * K + k] * B[((size_t)b * K + k) * N + j];
+        C[((size_t)b * M + i) * N + j] = sum;
+      }
+}
+
+/* BatchNorm1d/2d at inference, Model.cpp:5387-5421: sequential mean and biased variance over the whole
+ * input, y = (x - mean) / sqrt(var + eps), then y[i] *= w[i] for i < n_w; no shift */
+void mo_batchnorm_inference(const float* x, const float* w, long n_w, float* y, long n, float eps) {
+  float mean = 0.0f;
+  for (long i = 0; i < n; ++i) mean += x[i];
+  mean /= n;
+  float var = 0.0f;
+  for (long i = 0; i < n; ++i) { const float d = x[i] - mean; var += d * d; }
+  var /= n;
+  const float sd = sqrtf(var + eps);
+  for (long i = 0; i < n; ++i) {
+    y[i] = (x[i] - mean) / sd;
+    if (w && i < n_w) y[i] *= w[i];
+  }
+}
+
+/* LayerOpsExt::instance_norm2d_forward, LayerOpsExt.hpp:278-339: per channel, then gamma[c], beta[C + c] */
+void mo_instance_norm2d(const float* x, const float* w, float* y, int ch, int h, int wd, float eps) {
+  const int hw = h * wd;
+  for (int c = 0; c < ch; ++c) {
+    const float* p = x + (size_t)c * hw;
+    float mean = 0.0f;
+    for (int i = 0; i < hw; ++i) mean += p[i];
+    mean /= hw;
+    float var = 0.0f;
+    for (int i = 0; i < hw; ++i) { const float d = p[i] - mean; var += d * d; }
+    var /= hw;
+    const float sd = sqrtf(var + eps);
+    for (int i = 0; i < hw; ++i) {
+      float v = (p[i] - mean) / sd;
+      if (w) v = w[c] * v + w[ch + c];
+      y[(size_t)c * hw + i] = v;
+    }
   }
 }

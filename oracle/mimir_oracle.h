@@ -19,6 +19,21 @@ void mo_upsample_nearest(const float* x, float* y, int ch, int in_h, int in_w, i
 void mo_permute(const float* x, float* y, int nd, const int* shape, const int* dims);
 void mo_token_mean_pool(const float* x, float* y, int seq, int dim);
 void mo_global_avgpool(const float* x, float* y, int ch, int h, int w);
+void mo_leaky_relu(const float* a, float* y, long n, float alpha);
+void mo_cross_attention(const float* q_in, const float* kv_in, const float* wq, const float* wkv, const float* wout, float* y,
+                        int q_len, int kv_len, int E, int heads, int causal);
+void mo_depthwise_conv2d(const float* x, const float* w, const float* bias, float* y, int ch, int h, int wd, int k, int stride,
+                         int pad);
+void mo_conv1d(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int len, int k, int stride, int pad);
+void mo_conv_transpose2d(const float* x, const float* w, float* y, int ic, int oc, int h, int wd, int k, int stride, int pad,
+                         int relu);
+void mo_pool2d(int is_max, const float* x, float* y, int ch, int h, int wd, int kh_n, int kw_n, int sh, int sw, int ph, int pw);
+void mo_pad2d(int mode, const float* x, float* y, int ch, int h, int wd, int ph, int pw);
+void mo_pixel_shuffle(const float* x, float* y, int ic, int h, int wd, int r);
+void mo_upsample_bilinear(const float* x, float* y, int ch, int h, int wd, int oh, int ow, int half_pixel);
+void mo_batch_matmul(const float* A, const float* B, float* C, long nb, int M, int K, int N);
+void mo_batchnorm_inference(const float* x, const float* w, long n_w, float* y, long n, float eps);
+void mo_instance_norm2d(const float* x, const float* w, float* y, int ch, int h, int wd, float eps);
 #ifdef __cplusplus
 }
 #endif

@@ -19,7 +19,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libmimir_oracle.so")
 _lib = None
 
-ELT = {"Add": 0, "Multiply": 1, "GELU": 2, "SiLU": 3, "ReLU": 4, "Tanh": 5, "Sigmoid": 6}
+ELT = {"Add": 0, "Multiply": 1, "GELU": 2, "SiLU": 3, "ReLU": 4, "Tanh": 5, "Sigmoid": 6, "Softplus": 8, "Mish": 9,
+       "HardSigmoid": 10, "HardSwish": 11, "Subtract": 12, "Divide": 13}
 
 
 def build():
@@ -157,6 +158,119 @@ def global_avgpool(x, ch, h, w):
     return y
 
 
+def _ci(*v):
+    return [C.c_int(int(i)) for i in v]
+
+
+def leaky_relu(x, alpha):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().mo_leaky_relu(_p(x), _p(y), C.c_long(x.size), C.c_float(alpha))
+    return y
+
+
+def cross_attention(q_in, kv_in, w, q_len, kv_len, E, heads, causal):
+    q_in, kv_in, w = _f(q_in), _f(kv_in), _f(w)
+    wq, wkv, wout = w[: E * E], w[E * E : 3 * E * E], w[3 * E * E : 4 * E * E]
+    y = np.empty(q_len * E, np.float32)
+    lib().mo_cross_attention(_p(q_in), _p(kv_in), _p(_f(wq)), _p(_f(wkv)), _p(_f(wout)), _p(y), *_ci(q_len, kv_len, E, heads, causal))
+    return y
+
+
+def depthwise_conv2d(x, w, bias, ch, h, wd, k, stride, pad):
+    x, w = _f(x), _f(w)
+    bias = _f(bias) if bias is not None else None
+    oh, ow = (h + 2 * pad - k) // stride + 1, (wd + 2 * pad - k) // stride + 1
+    y = np.empty(ch * oh * ow, np.float32)
+    lib().mo_depthwise_conv2d(_p(x), _p(w), _p(bias), _p(y), *_ci(ch, h, wd, k, stride, pad))
+    return y
+
+
+def conv1d(x, w, bias, ic, oc, length, k, stride, pad):
+    x, w = _f(x), _f(w)
+    bias = _f(bias) if bias is not None else None
+    y = np.empty(oc * ((length + 2 * pad - k) // stride + 1), np.float32)
+    lib().mo_conv1d(_p(x), _p(w), _p(bias), _p(y), *_ci(ic, oc, length, k, stride, pad))
+    return y
+
+
+def conv_transpose2d(x, w, ic, oc, h, wd, k, stride, pad, relu):
+    x, w = _f(x), _f(w)
+    oh, ow = (h - 1) * stride - 2 * pad + k, (wd - 1) * stride - 2 * pad + k
+    y = np.empty(oc * oh * ow, np.float32)
+    lib().mo_conv_transpose2d(_p(x), _p(w), _p(y), *_ci(ic, oc, h, wd, k, stride, pad, relu))
+    return y
+
+
+def pool2d(is_max, x, ch, h, wd, kh, kw, sh, sw, ph, pw):
+    x = _f(x)
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (wd + 2 * pw - kw) // sw + 1
+    y = np.empty(ch * oh * ow, np.float32)
+    lib().mo_pool2d(C.c_int(int(is_max)), _p(x), _p(y), *_ci(ch, h, wd, kh, kw, sh, sw, ph, pw))
+    return y
+
+
+def pad2d(mode, x, ch, h, wd, ph, pw):
+    x = _f(x)
+    y = np.empty(ch * (h + 2 * ph) * (wd + 2 * pw), np.float32)
+    lib().mo_pad2d(C.c_int(mode), _p(x), _p(y), *_ci(ch, h, wd, ph, pw))
+    return y
+
+
+def pixel_shuffle(x, ic, h, wd, r):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().mo_pixel_shuffle(_p(x), _p(y), *_ci(ic, h, wd, r))
+    return y
+
+
+def upsample_bilinear(x, ch, h, wd, oh, ow, half_pixel):
+    x = _f(x)
+    y = np.empty(ch * oh * ow, np.float32)
+    lib().mo_upsample_bilinear(_p(x), _p(y), *_ci(ch, h, wd, oh, ow, half_pixel))
+    return y
+
+
+def batch_matmul(a, b, nb, M, K, N):
+    a, b = _f(a), _f(b)
+    y = np.empty(nb * M * N, np.float32)
+    lib().mo_batch_matmul(_p(a), _p(b), _p(y), C.c_long(nb), *_ci(M, K, N))
+    return y
+
+
+def batchnorm_inference(x, w, eps):
+    x = _f(x)
+    w = _f(w) if w is not None else None
+    y = np.empty_like(x)
+    lib().mo_batchnorm_inference(_p(x), _p(w), C.c_long(0 if w is None else w.size), _p(y), C.c_long(x.size), C.c_float(eps))
+    return y
+
+
+def instance_norm2d(x, w, ch, h, wd, eps):
+    x = _f(x)
+    w = _f(w) if w is not None else None
+    y = np.empty_like(x)
+    lib().mo_instance_norm2d(_p(x), _p(w), _p(y), *_ci(ch, h, wd), C.c_float(eps))
+    return y
+
+
+def split_pieces(d, n):
+    """Sizes of the tensors a Split / Chunk layer stores (Model.cpp:5802-5832)."""
+    if d.type.decode() == "Split":
+        sizes = [int(d.split_sizes[i]) for i in range(d.n_splits)]
+        if not sizes:
+            raise RuntimeError("Split: split_sizes must be configured")
+        if sum(sizes) != n:
+            raise RuntimeError("Split: sum of split_sizes != input size")
+        return sizes
+    base, rem = divmod(n, d.num_chunks)
+    return [base + (1 if i < rem else 0) for i in range(d.num_chunks)]
+
+
+def _dflt(v, default):
+    return v if v > 0 else default
+
+
 def run_layer(d, ins, w):
     """One layer of the switch in Model::forwardPassView (Model.cpp:4891-6291) on one sample."""
     t = d.type.decode()
@@ -204,9 +318,11 @@ def run_layer(d, ins, w):
         return groupnorm(x, gamma, beta, ch, h, wd, d.num_groups, d.eps)
     if t in ("Softmax", "LogSoftmax"):
         return softmax(x, t == "LogSoftmax")
-    if t in ("GELU", "SiLU", "ReLU", "Tanh", "Sigmoid"):
+    if t in ("GELU", "SiLU", "ReLU", "Tanh", "Sigmoid", "Softplus", "Mish", "HardSigmoid", "HardSwish"):
         return eltwise(ELT[t], x)
-    if t in ("Add", "Multiply"):
+    if t == "LeakyReLU":
+        return leaky_relu(x, d.leaky_relu_alpha if d.leaky_relu_alpha > 0 else 0.01)
+    if t in ("Add", "Multiply", "Subtract", "Divide"):
         if len(ins) < 2:
             raise RuntimeError(f"{t} layer requires 2 inputs")
         return eltwise(ELT[t], ins[0], ins[1])
@@ -218,10 +334,55 @@ def run_layer(d, ins, w):
         return upsample_nearest(x, d.in_channels, d.out_h, d.out_w, sh, sw)
     if t == "Permute":
         return permute(x, list(d.shape[: d.n_dims]), list(d.permute_dims[: d.n_dims]))
-    if t == "Concat":
+    if t in ("Concat", "Stack"):
         return np.concatenate([_f(i) for i in ins])
-    if t in ("Identity", "Reshape", "Flatten", "View", "Dropout", "Dropout2d"):
-        return _f(x).copy()
+    if t in ("Identity", "Reshape", "Flatten", "View", "Dropout", "Dropout2d", "AlphaDropout", "Squeeze", "Unsqueeze", "Reparameterize"):
+        return _f(x).copy()  # Reparameterize at inference returns mu, its first input (Model.cpp:5767-5770)
+    if t == "CrossAttention":
+        heads = _dflt(d.num_heads, 1)
+        E = d.embed_dim if d.embed_dim > 0 else d.head_dim * heads
+        return cross_attention(ins[0], ins[1], w, ins[0].size // E, ins[1].size // E, E, heads, d.causal)
+    if t == "DepthwiseConv2d":
+        ch, h, wd = _dflt(d.in_channels, 3), _dflt(d.input_height, 32), _dflt(d.input_width, 32)
+        k, st = _dflt(d.raw_kernel_h, 3), _dflt(d.raw_stride_h, 1)
+        pad = d.raw_pad_h if d.raw_pad_h >= 0 else 0
+        return depthwise_conv2d(x, w[: ch * k * k], w[ch * k * k : ch * k * k + ch] if d.use_bias else None, ch, h, wd, k, st, pad)
+    if t == "Conv1d":
+        ic, oc = _dflt(d.in_channels, 1), _dflt(d.out_channels, 1)
+        k, st = _dflt(d.raw_kernel_h, 3), _dflt(d.raw_stride_h, 1)
+        pad = d.raw_pad_h if d.raw_pad_h >= 0 else 0
+        nw = oc * ic * k
+        return conv1d(x, w[:nw], w[nw : nw + oc] if d.use_bias else None, ic, oc, x.size // ic, k, st, pad)
+    if t == "ConvTranspose2d":
+        return conv_transpose2d(x, w, d.in_channels, d.out_channels, _dflt(d.input_height, 64), _dflt(d.input_width, 64), d.kernel,
+                                d.stride, d.padding, d.activation != 0)
+    if t == "MaxPool2d":
+        return pool2d(1, x, _dflt(d.in_channels, 64), _dflt(d.input_height, 64), _dflt(d.input_width, 64), d.kernel, d.kernel,
+                      d.stride, d.stride, d.padding, d.padding)
+    if t == "AvgPool2d":
+        return pool2d(0, x, _dflt(d.in_channels, 64), _dflt(d.input_height, 32), _dflt(d.input_width, 32), d.kernel,
+                      _dflt(d.kernel_w, d.kernel), d.stride, _dflt(d.stride_w, d.stride), d.padding, d.padding_w)
+    if t in ("ZeroPad2d", "ReflectionPad2d", "ReplicationPad2d"):
+        mode = ("ZeroPad2d", "ReflectionPad2d", "ReplicationPad2d").index(t)
+        ph = d.raw_pad_h if d.raw_pad_h >= 0 else 1
+        pw = (d.raw_pad_w if d.raw_pad_w >= 0 else 1) if mode == 0 else ph
+        return pad2d(mode, x, _dflt(d.in_channels, 3), _dflt(d.input_height, 32), _dflt(d.input_width, 32), ph, pw)
+    if t == "PixelShuffle":
+        return pixel_shuffle(x, _dflt(d.in_channels, 12), _dflt(d.input_height, 32), _dflt(d.input_width, 32), _dflt(d.scale_h, 2))
+    if t in ("UpsampleBilinear", "UpsampleBicubic"):
+        return upsample_bilinear(x, _dflt(d.in_channels, 3), d.out_h, d.out_w, 2 * d.out_h, 2 * d.out_w, t == "UpsampleBicubic")
+    if t == "MatMul":
+        return batch_matmul(ins[0], ins[1], 1, d.in_features, d.out_features, d.embed_dim)
+    if t == "BatchMatMul":
+        return batch_matmul(ins[0], ins[1], d.seq_len, d.in_features, d.out_features, d.embed_dim)
+    if t in ("BatchNorm2d", "BatchNorm1d"):
+        return batchnorm_inference(x, w if (d.affine and w is not None and w.size) else None, d.eps)
+    if t == "InstanceNorm2d":
+        ch = _dflt(d.in_channels, 3)
+        return instance_norm2d(x, w if (d.affine and w is not None and w.size >= 2 * ch) else None, ch, _dflt(d.input_height, 32),
+                               _dflt(d.input_width, 32), d.eps)
+    if t == "Transpose":
+        return permute(x, [d.in_features, d.out_features], [1, 0])
     if t == "TokenMeanPool":
         return token_mean_pool(x, d.seq_len, d.embed_dim)
     if t in ("GlobalAvgPool2d", "AdaptiveAvgPool2d"):
@@ -245,6 +406,15 @@ def run_graph(descs, weights, inputs):
         for n in names:
             if n not in store:
                 raise RuntimeError("Missing input tensor: " + n)
-        out = run_layer(d, [store[n] for n in names], None if w is None else _f(w))
-        store[(d.output or b"x").decode() or "x"] = out
+        out_name = (d.output or b"x").decode() or "x"
+        if d.type.decode() in ("Split", "Chunk"):
+            src = store[names[0]]
+            off = 0
+            for i, sz in enumerate(split_pieces(d, src.size)):
+                store[f"{out_name}_{i}"] = src[off : off + sz].copy()
+                off += sz
+            out = store[out_name + "_0"].copy()
+        else:
+            out = run_layer(d, [store[n] for n in names], None if w is None else _f(w))
+        store[out_name] = out
     return store["x"]

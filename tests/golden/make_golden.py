@@ -63,6 +63,48 @@ def cases():
     add("global_avgpool", [make_desc("g", "GlobalAvgPool2d", in_channels=3, input_height=4, input_width=7)], [None], {"x": f(84)})
     d = configs.linear_gelu_stack(16, 64)
     add("linear_gelu_stack_16x64", d, configs.linear_gelu_stack_weights(64), {"x": configs.linear_gelu_stack_input(16, 64).ravel()})
+    # ---- the remaining switch cases (appended: the generator above must keep its random stream) ----
+    E, ql, kl = 32, 10, 17
+    wx = f(4 * E * E, scale=0.15)
+    for causal in (0, 1):
+        add(f"cross_attention_causal{causal}", [make_desc("a", "CrossAttention", inputs=["x", "ctx"], embed_dim=E, num_heads=4, causal=causal, params_count=wx.size)],
+            [wx], {"x": f(ql * E), "ctx": f(kl * E)})
+    add("cross_attention_head_dim", [make_desc("a", "CrossAttention", inputs=["x", "ctx"], embed_dim=0, head_dim=8, num_heads=4, params_count=wx.size)],
+        [wx], {"x": f(kl * E), "ctx": f(ql * E)})
+    add("split_concat", [make_desc("s", "Split", output="s", split_sizes=[20, 13, 7]), make_desc("c", "Concat", inputs=["s_2", "s", "s_1"])],
+        [None, None], {"x": f(40)})
+    add("chunk_concat", [make_desc("s", "Chunk", output="c", num_chunks=3), make_desc("c", "Concat", inputs=["c_1", "c_2", "c_0", "c"])],
+        [None, None], {"x": f(10)})
+    add("depthwise_conv_s2_bias", [make_desc("d", "DepthwiseConv2d", in_channels=6, input_height=9, input_width=11, raw_kernel_h=3, raw_stride_h=2, raw_pad_h=1,
+                                             use_bias=1, params_count=6 * 9 + 6)], [f(60, scale=0.3)], {"x": f(6 * 99)})
+    add("conv1d_s2_bias", [make_desc("c", "Conv1d", in_channels=3, out_channels=5, raw_kernel_h=3, raw_stride_h=2, raw_pad_h=1, use_bias=1, params_count=45 + 5)],
+        [f(50, scale=0.3)], {"x": f(60)})
+    add("conv_transpose2d_relu", [make_desc("c", "ConvTranspose2d", in_channels=3, out_channels=4, input_height=5, input_width=6, kernel=4, stride=2, padding=1,
+                                            activation=1, params_count=4 * 3 * 16)], [f(192, scale=0.2)], {"x": f(90)})
+    add("maxpool_k3s2p1", [make_desc("p", "MaxPool2d", in_channels=3, input_height=7, input_width=9, kernel=3, stride=2, padding=1)], [None], {"x": f(189)})
+    add("avgpool_k3s1p1", [make_desc("p", "AvgPool2d", in_channels=3, input_height=7, input_width=9, kernel=3, stride=1, padding=1)], [None], {"x": f(189)})
+    add("avgpool_k2s2", [make_desc("p", "AvgPool2d", in_channels=2, input_height=6, input_width=8, kernel=2, stride=2, padding=0)], [None], {"x": f(96)})
+    for t, kw in (("ZeroPad2d", dict(raw_pad_h=1, raw_pad_w=2)), ("ReflectionPad2d", dict(raw_pad_h=2)), ("ReplicationPad2d", dict(raw_pad_h=2))):
+        add(t.lower(), [make_desc("p", t, in_channels=2, input_height=4, input_width=5, **kw)], [None], {"x": f(40)})
+    add("pixel_shuffle_r2", [make_desc("p", "PixelShuffle", in_channels=8, input_height=3, input_width=5, scale_h=2)], [None], {"x": f(120)})
+    for t in ("UpsampleBilinear", "UpsampleBicubic"):
+        add(t.lower(), [make_desc("u", t, in_channels=3, out_h=5, out_w=7)], [None], {"x": f(105)})
+    add("matmul", [make_desc("m", "MatMul", inputs=["x", "b"], in_features=5, out_features=37, embed_dim=9)], [None], {"x": f(5 * 37), "b": f(37 * 9)})
+    add("batch_matmul", [make_desc("m", "BatchMatMul", inputs=["x", "b"], seq_len=3, in_features=33, out_features=40, embed_dim=35)], [None],
+        {"x": f(3 * 33 * 40), "b": f(3 * 40 * 35)})
+    add("batchnorm_partial_weights", [make_desc("n", "BatchNorm2d", params_count=24)], [f(24) + 1.0], {"x": f(96, scale=2.0) + 0.7})
+    add("instance_norm_affine", [make_desc("n", "InstanceNorm2d", in_channels=4, input_height=5, input_width=6, params_count=8)], [f(8) + 1.0], {"x": f(120, scale=1.5)})
+    add("leaky_relu_02", [make_desc("n", "LeakyReLU", leaky_relu_alpha=0.2)], [None], {"x": f(257, scale=3.0)})
+    for t in ("Softplus", "Mish", "HardSigmoid", "HardSwish"):
+        add(t.lower(), [make_desc("n", t)], [None], {"x": f(257, scale=8.0)})
+    add("subtract", [make_desc("n", "Subtract", inputs=["x", "b"])], [None], {"x": f(33), "b": f(33)})
+    dv = f(33)
+    dv[[0, 5, 9]] = [0.0, -0.0, 1e-9]
+    add("divide_small_divisors", [make_desc("n", "Divide", inputs=["x", "b"])], [None], {"x": f(33), "b": dv})
+    add("transpose_2d", [make_desc("t", "Transpose", in_features=6, out_features=11)], [None], {"x": f(66)})
+    add("reparameterize_inference", [make_desc("r", "Reparameterize", inputs=["x", "lv"])], [None], {"x": f(20), "lv": f(20)})
+    add("squeeze_unsqueeze", [make_desc("a", "Squeeze"), make_desc("b", "Unsqueeze")], [None, None], {"x": f(12)})
+    add("stack2", [make_desc("s", "Stack", inputs=["x", "y"])], [None], {"x": f(7), "y": f(7)})
     return out
 
 

@@ -72,6 +72,30 @@ def reference_kats():
     # named routing a+b -> sum, sum*c -> x, test_layers_named_routing.cpp:14-40
     k.append(("routing", [make_desc("add", "Add", inputs=["a", "b"], output="sum"), make_desc("mul", "Multiply", inputs=["sum", "c"], output="x")],
               [None, None], {"a": f(1, 2, 3), "b": f(10, 20, 30), "c": f(2, 2, 2)}, f(22, 44, 66), 1e-6))
+    # DepthwiseConv2d k=1 -> scale by 3, test_layers_all_types.cpp:135-169
+    k.append(("depthwise_k1", [make_desc("t0", "DepthwiseConv2d", in_channels=1, input_height=2, input_width=2, raw_kernel_h=1, raw_stride_h=1,
+                                         raw_pad_h=0, use_bias=0, params_count=1)], [f(3)], {"x": f(1, 2, 3, 4)}, f(3, 6, 9, 12), 1e-6))
+    # Conv1d k=1 -> scale by 4, :171-200
+    k.append(("conv1d_k1", [make_desc("t0", "Conv1d", in_channels=1, out_channels=1, raw_kernel_h=1, raw_stride_h=1, raw_pad_h=0, use_bias=0,
+                                      params_count=1)], [f(4)], {"x": f(1, 2, 3)}, f(4, 8, 12), 1e-6))
+    # MaxPool2d / AvgPool2d 2x2 stride 2 on [1,2,3,4], :345-363
+    pool = dict(in_channels=1, input_height=2, input_width=2, kernel=2, stride=2, padding=0)
+    k.append(("maxpool", [make_desc("t0", "MaxPool2d", **pool)], [None], {"x": f(1, 2, 3, 4)}, f(4), 1e-6))
+    k.append(("avgpool", [make_desc("t0", "AvgPool2d", **pool)], [None], {"x": f(1, 2, 3, 4)}, f(2.5), 1e-5))
+    # Subtract / Divide, :405-421
+    k.append(("subtract", [make_desc("t0", "Subtract", inputs=["x", "y"])], [None], {"x": f(1, 2, 3), "y": f(4, 5, 6)}, f(-3, -3, -3), 1e-6))
+    k.append(("divide", [make_desc("t0", "Divide", inputs=["x", "y"])], [None], {"x": f(1, 2, 3), "y": f(4, 5, 6)}, f(0.25, 0.4, 0.5), 1e-6))
+    # Split [2,2] then Concat gives the input back, :442-466
+    k.append(("split_concat", [make_desc("split", "Split", inputs=["x"], output="s", split_sizes=[2, 2]),
+                               make_desc("cat", "Concat", inputs=["s_0", "s_1"], output="x")], [None, None], {"x": f(1, 2, 3, 4)}, f(1, 2, 3, 4), 1e-6))
+    # MatMul 2x3 . 3x2, :470-506
+    k.append(("matmul", [make_desc("mm", "MatMul", inputs=["a", "b"], in_features=2, out_features=3, embed_dim=2)], [None],
+              {"a": f(1, 2, 3, 4, 5, 6), "b": f(7, 8, 9, 10, 11, 12)}, f(58, 64, 139, 154), 1e-6))
+    # PixelShuffle r=2 of 4 channels 1x1, :560-577; ZeroPad2d 1x1 pad 1, :579-592
+    k.append(("pixel_shuffle", [make_desc("t0", "PixelShuffle", in_channels=4, input_height=1, input_width=1, scale_h=2)], [None],
+              {"x": f(10, 11, 12, 13)}, f(10, 11, 12, 13), 1e-6))
+    k.append(("zero_pad", [make_desc("t0", "ZeroPad2d", in_channels=1, input_height=1, input_width=1, raw_pad_h=1, raw_pad_w=1)], [None],
+              {"x": f(5)}, f(0, 0, 0, 0, 5, 0, 0, 0, 0), 1e-6))
     return k
 
 

@@ -38,9 +38,10 @@ def test_struct_layout_matches_header(tmp_path):
 #include <stddef.h>
 #include "mimir_b200.h"
 int main(void) {
-  printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(MimirLayerDesc), sizeof(MimirNamedInput), sizeof(MimirB200Stats),
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(MimirLayerDesc), sizeof(MimirNamedInput), sizeof(MimirB200Stats),
          offsetof(MimirLayerDesc, params_count), offsetof(MimirLayerDesc, eps), offsetof(MimirLayerDesc, shape),
-         offsetof(MimirNamedInput, broadcast));
+         offsetof(MimirNamedInput, broadcast), offsetof(MimirLayerDesc, head_dim), offsetof(MimirLayerDesc, raw_pad_w),
+         offsetof(MimirLayerDesc, split_sizes), offsetof(MimirLayerDesc, num_chunks));
   return 0;
 }
 """)
@@ -49,12 +50,13 @@ int main(void) {
     got = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     want = [ctypes.sizeof(abi.MimirLayerDesc), ctypes.sizeof(abi.MimirNamedInput), ctypes.sizeof(abi.MimirB200Stats),
             abi.MimirLayerDesc.params_count.offset, abi.MimirLayerDesc.eps.offset, abi.MimirLayerDesc.shape.offset,
-            abi.MimirNamedInput.broadcast.offset]
+            abi.MimirNamedInput.broadcast.offset, abi.MimirLayerDesc.head_dim.offset, abi.MimirLayerDesc.raw_pad_w.offset,
+            abi.MimirLayerDesc.split_sizes.offset, abi.MimirLayerDesc.num_chunks.offset]
     assert got == want
 
 
 def test_abi_version():
-    assert runtime.lib().mimir_b200_abi_version() == 1
+    assert runtime.lib().mimir_b200_abi_version() == 2
 
 
 def _has_gpu():

@@ -43,3 +43,32 @@ def test_backend_layernorm_mean_variance_property(backend):
     descs, weights, inputs = layernorm_property_case()
     out = run(backend, descs, weights, inputs, 4)
     assert abs(out.mean()) < 1e-5 and abs(out.var() - 1.0) < 1e-4
+
+
+# The remaining switch cases with a batch: every sample is an independent reference forward.
+BATCHED = ["cross_attention_causal0", "cross_attention_causal1", "split_concat", "chunk_concat", "depthwise_conv_s2_bias", "conv1d_s2_bias",
+           "conv_transpose2d_relu", "maxpool_k3s2p1", "avgpool_k3s1p1", "zeropad2d", "reflectionpad2d", "replicationpad2d",
+           "pixel_shuffle_r2", "upsamplebilinear", "upsamplebicubic", "matmul", "batch_matmul", "batchnorm_partial_weights",
+           "instance_norm_affine", "leaky_relu_02", "mish", "divide_small_divisors", "transpose_2d"]
+
+
+@pytest.mark.parametrize("name", BATCHED)
+def test_backend_batched_matches_port(backend, name):
+    from oracle import port
+    _, descs, weights, inputs, want = next(g for g in GOLDEN if g[0] == name)
+    batch = 3
+    rng = np.random.default_rng(7)
+    samples = [{k: (v if s == 0 else rng.standard_normal(v.size).astype(np.float32)) for k, v in inputs.items()} for s in range(batch)]
+    m = backend.GraphModel(descs)
+    for i, w in enumerate(weights):
+        m.upload_weights(i, w)
+    m.plan({k: (v.size, False) for k, v in inputs.items()}, batch)
+    stacked = {k: (np.concatenate([s[k] for s in samples]), False) for k in inputs}
+    got = m.forward(stacked, batch, want.size).reshape(batch, -1)
+    m.close()
+    for s in range(batch):
+        ref_out = port.run_graph(descs, weights, samples[s])
+        if name in BITEXACT:
+            assert np.array_equal(got[s], ref_out), f"{name} sample {s}"
+        else:
+            assert_close(got[s], ref_out, f"{name} sample {s}")

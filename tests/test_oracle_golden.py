@@ -12,7 +12,9 @@ from oracle import port, ref
 GOLDEN = load_golden()
 KATS = reference_kats()
 # integer / index / pure data-movement cases must be bit-exact
-BITEXACT = {"embedding_pad_oob_round", "upsample_nearest", "permute_201", "concat3", "relu", "add_broadcast", "add_scalar", "multiply"}
+BITEXACT = {"embedding_pad_oob_round", "upsample_nearest", "permute_201", "concat3", "relu", "add_broadcast", "add_scalar", "multiply",
+            "split_concat", "chunk_concat", "maxpool_k3s2p1", "zeropad2d", "reflectionpad2d", "replicationpad2d", "pixel_shuffle_r2",
+            "leaky_relu_02", "subtract", "transpose_2d", "reparameterize_inference", "squeeze_unsqueeze", "stack2"}
 
 
 @pytest.mark.parametrize("case", KATS, ids=[k[0] for k in KATS])
