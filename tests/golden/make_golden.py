@@ -126,7 +126,54 @@ def transformer_case():
     return "transformer_registry_tiny", ours, weights, {"x": ids, "mag": mag, "mod": mod}, y
 
 
+def _compact(j):
+    """Drops descriptor fields that hold the Layer defaults (desc_from_dict restores them)."""
+    from mimir_framework_b200.abi import LAYER_DEFAULTS
+    out = {}
+    for k, v in j.items():
+        if k in LAYER_DEFAULTS and LAYER_DEFAULTS[k] is not None and (abs(v - LAYER_DEFAULTS[k]) < 1e-9):
+            continue
+        if k in ("kernel_w", "stride_w", "padding_w") and v == j[{"kernel_w": "kernel", "stride_w": "stride", "padding_w": "padding"}[k]]:
+            continue
+        if k in ("shape", "permute_dims", "split_sizes") and not v:
+            continue
+        out[k] = v
+    return out
+
+
+def registry_graphs():
+    """Every architecture of the reference's registry at a small width: the layer list comes from the
+    reference's own builder, the weights from a seeded generator, the expected output from the
+    compiled reference's forward."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import registry_cases as rc
+    graphs, arrays = {}, {}
+    for arch, cfg in rc.CFG.items():
+        m = ref.RefModel(registry=arch, cfg_json=json.dumps(cfg))
+        descs = m.layer_descs()
+        weights = rc.make_weights(descs)
+        for i, w in enumerate(weights):
+            if w is not None:
+                m.set_weights(i, w)
+        inputs = rc.make_inputs(arch)
+        if arch == "transformer":
+            inputs["mag"], inputs["mod"] = m.mag_mod()
+        y = m.forward(inputs)
+        assert np.all(np.isfinite(y)) and y.size > 0, arch
+        graphs[arch] = [_compact(desc_to_dict(d)) for d in descs]
+        for k, v in inputs.items():
+            arrays[f"{arch}/in/{k}"] = v
+        arrays[f"{arch}/out"] = y
+        print(f"{arch:20s} layers {len(descs):3d} out {y.size:6d} |y| mean {np.abs(y).mean():.3e}")
+        m.close()
+    np.savez_compressed(os.path.join(HERE, "registry_graphs.npz"), **arrays)
+    with open(os.path.join(HERE, "registry_graphs.json"), "w") as fh:
+        json.dump({"generator": "tests/golden/make_golden.py", "source": "ModelArchitectures::create + forwardPassNamed(training=false) of the compiled reference",
+                   "configs": rc.CFG, "graphs": graphs}, fh)
+
+
 def main():
+    registry_graphs()
     index = []
     arrays = {}
     for name, descs, weights, inputs in cases():
