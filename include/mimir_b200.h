@@ -275,6 +275,21 @@ int mimir_b200_model_set_pipeline(MimirB200ModelHandle m, int micro_batches);
  * the weights change. */
 int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, const float* host,
                                     uint64_t n);
+/* Allocates (or re-allocates) the device block of one layer's `n` weights and returns its device
+ * pointer for the caller to fill (weights that already live on the GPU, or a loader that streams them
+ * in).  upload_weights is this plus one host-to-device copy. */
+int mimir_b200_model_weights_device(MimirB200ModelHandle m, int layer_index, uint64_t n, float** dev);
+int mimir_b200_model_num_layers(MimirB200ModelHandle m, int* n_layers);
+int mimir_b200_model_layer_info(MimirB200ModelHandle m, int layer_index, const char** name,
+                                uint64_t* params_count);
+/* Streams the tensors "<layer name>/weights" (F32, or BF16 widened on the device) of a safetensors
+ * checkpoint straight into the device weight blocks, through pinned staging buffers, without a host
+ * copy of the model.  Replaces the layer-weights part of SafeTensorsReader::load
+ * (Serialization/SafeTensorsReader.cpp:276-325): same tensor naming, same size check ("Size mismatch
+ * for ..."), `strict` != 0 fails on a missing tensor ("Missing tensor in strict mode: ...") like
+ * LoadOptions::strict_mode.  Other tensors in the file (tokenizer, encoder, optimizer) are ignored. */
+int mimir_b200_model_load_safetensors(MimirB200ModelHandle m, const char* path, int strict,
+                                      int* layers_loaded, unsigned long long* bytes_loaded);
 /* Declares the per-sample size of a named graph input, then plans the activation arena for
  * `batch` samples: liveness over the layer list, offsets reused after the last consumer, peak
  * checked against the budget BEFORE anything is launched (E_OOM_BUDGET).  Mirrors

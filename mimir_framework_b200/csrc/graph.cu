@@ -1199,7 +1199,7 @@ int mimir_b200_model_set_precision(MimirB200ModelHandle m, int precision) {
   return MIMIR_B200_OK;
 }
 
-int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, const float* host, uint64_t n) {
+int mimir_b200_model_weights_device(MimirB200ModelHandle m, int layer_index, uint64_t n, float** dev) {
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (layer_index < 0 || layer_index >= static_cast<int>(m->layers.size())) return fail(MIMIR_B200_E_INVALID, "upload_weights: layer index out of range");
   LayerRT& L = m->layers[static_cast<size_t>(layer_index)];
@@ -1208,13 +1208,36 @@ int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, con
   cudaDeviceSynchronize();
   free_layer_weights(L, m);
   L.w_count = 0;
+  if (dev) *dev = nullptr;
   if (n == 0) return MIMIR_B200_OK;
-  if (!host) return fail(MIMIR_B200_E_INVALID, "upload_weights: null host pointer");
   MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_f32), n * 4, "layer weights"));
   L.w_count = n;
   m->weight_bytes += n * 4;
-  MB_CUDA(cudaMemcpy(L.w_f32, host, n * 4, cudaMemcpyHostToDevice));
   m->planned_batch = 0;  // planes are rebuilt by the next plan
+  if (dev) *dev = L.w_f32;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, const float* host, uint64_t n) {
+  if (n != 0 && !host) return fail(MIMIR_B200_E_INVALID, "upload_weights: null host pointer");
+  float* dev = nullptr;
+  MB_TRY(mimir_b200_model_weights_device(m, layer_index, n, &dev));
+  if (n) MB_CUDA(cudaMemcpy(dev, host, n * 4, cudaMemcpyHostToDevice));
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_layer_info(MimirB200ModelHandle m, int layer_index, const char** name, uint64_t* params_count) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (layer_index < 0 || layer_index >= static_cast<int>(m->layers.size())) return fail(MIMIR_B200_E_INVALID, "layer index out of range");
+  const LayerRT& L = m->layers[static_cast<size_t>(layer_index)];
+  if (name) *name = L.name.c_str();
+  if (params_count) *params_count = L.d.params_count;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_num_layers(MimirB200ModelHandle m, int* n) {
+  if (!m || !n) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  *n = static_cast<int>(m->layers.size());
   return MIMIR_B200_OK;
 }
 

@@ -6,6 +6,7 @@ numpy arrays, device-pointer calls take raw addresses (e.g. ``torch.Tensor.data_
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -60,6 +61,10 @@ _SIGS = {
     "mimir_b200_model_set_precision": [_P, C.c_int],
     "mimir_b200_model_set_pipeline": [_P, C.c_int],
     "mimir_b200_model_upload_weights": [_P, C.c_int, _P, C.c_uint64],
+    "mimir_b200_model_weights_device": [_P, C.c_int, C.c_uint64, _P],
+    "mimir_b200_model_num_layers": [_P, _P],
+    "mimir_b200_model_layer_info": [_P, C.c_int, _P, _P],
+    "mimir_b200_model_load_safetensors": [_P, C.c_char_p, C.c_int, _P, _P],
     "mimir_b200_model_plan": [_P, _P, C.c_int, C.c_int, _P],
     "mimir_b200_model_forward": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P],
     "mimir_b200_model_forward_device": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P, _P],
@@ -363,6 +368,12 @@ class GraphModel:
             return
         w = _f(w)
         check(lib().mimir_b200_model_upload_weights(self._h, i, _p(w), w.size))
+
+    def load_safetensors(self, path: str, strict: bool = True):
+        """Streams "<layer>/weights" tensors of a safetensors checkpoint into the device blocks."""
+        n, b = C.c_int(0), C.c_ulonglong(0)
+        check(lib().mimir_b200_model_load_safetensors(self._h, os.fsencode(path), int(strict), C.byref(n), C.byref(b)))
+        return n.value, b.value
 
     @staticmethod
     def _inputs(spec):

@@ -90,6 +90,10 @@ class RefModel:
         _check(lib().mimir_ref_model_get_weights(self._h, C.c_int(i), w.ctypes.data_as(C.c_void_p), C.c_ulonglong(n)))
         return w
 
+    def save_safetensors(self, path: str):
+        """Checkpoint written by the reference's own SafeTensorsWriter."""
+        _check(lib().mimir_ref_model_save_safetensors(self._h, os.fsencode(path)))
+
     def mag_mod(self, cap: int = 65536):
         mag = np.zeros(cap, dtype=np.float32)
         mod = np.zeros(cap, dtype=np.float32)

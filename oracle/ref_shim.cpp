@@ -24,6 +24,7 @@
 #include "Model.hpp"
 #include "MemoryGuard.hpp"
 #include "Models/Registry/ModelArchitectures.hpp"
+#include "Serialization/SafeTensorsWriter.hpp"
 #include "mimir_b200_layer_shim.hpp"
 
 namespace {
@@ -166,6 +167,19 @@ int mimir_ref_model_get_mag_mod(void* h, float* mag, float* mod, int cap, int* n
     if (static_cast<int>(a.size()) > cap) throw std::runtime_error("mag/mod capacity too small");
     std::memcpy(mag, a.data(), a.size() * sizeof(float));
     std::memcpy(mod, b.data(), b.size() * sizeof(float));
+  });
+}
+
+// Writes the model with the reference's own SafeTensorsWriter (tensors "<layer>/weights" plus its
+// tokenizer / encoder blobs), so that the device loader can be tested against a real checkpoint.
+int mimir_ref_model_save_safetensors(void* h, const char* path) {
+  return guarded([&] {
+    auto* rm = static_cast<RefModel*>(h);
+    Mimir::Serialization::SaveOptions opt;
+    opt.include_git_info = false;
+    Mimir::Serialization::SafeTensorsWriter w;
+    std::string err;
+    if (!w.save(*rm->model, path, opt, &err)) throw std::runtime_error("SafeTensorsWriter::save failed: " + err);
   });
 }
 
