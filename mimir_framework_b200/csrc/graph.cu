@@ -219,6 +219,17 @@ struct MimirB200Model {
   uint8_t* arena2 = nullptr;
   cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_d2h = nullptr;
   std::vector<cudaEvent_t> ev_h2d, ev_comp, ev_d2h;
+  // The layer loop of one (batch, arena, bound pointers) combination, captured into a CUDA graph the second
+  // time it is seen and replayed afterwards: one launch instead of one per layer.
+  struct CachedGraph {
+    std::vector<const void*> key;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches = 0;  // kernels inside, for the launch counter
+    int seen = 0;
+    bool unusable = false;  // capture failed once: keep launching layer by layer
+  };
+  std::vector<CachedGraph> graphs;
+  cudaStream_t s_capture = nullptr;
 };
 
 namespace mb {
@@ -227,6 +238,12 @@ namespace {
 std::mutex g_models_mu;
 std::set<MimirB200Model*> g_models;
 MimirB200Stats g_stats{};
+
+void drop_graphs(MimirB200Model* m) {
+  for (auto& g : m->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+  m->graphs.clear();
+}
 
 int root_of(const std::vector<TensorV>& ts, int v) {
   while (ts[v].alias_of >= 0) v = ts[v].alias_of;
@@ -644,6 +661,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
   const int full_batch = batch;
   batch = batch / m->pipeline;  // everything below is sized for one micro-batch
   const int nl = static_cast<int>(m->layers.size());
+  drop_graphs(m);  // offsets, fusion decisions and operand planes may all change
   m->tensors.clear();
   m->input_v.clear();
   m->planned_batch = 0;
@@ -1098,6 +1116,74 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
   return MIMIR_B200_OK;
 }
 
+bool graphs_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("MIMIR_B200_GRAPH");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+// run_layers through the graph cache.  The first call with a given set of pointers runs layer by layer (it also
+// performs every one-time host-side setup the launch helpers do); the second is captured on a private stream;
+// from then on the instantiated graph is launched into the caller's stream.
+int run_layers_cached(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, uint8_t* arena) {
+  if (!graphs_enabled() || ctx().prof_gemm) return run_layers(m, batch, bnd, st, arena);
+  std::vector<const void*> key;
+  key.reserve(bnd.in_ptr.size() + 3);
+  key.push_back(reinterpret_cast<const void*>(static_cast<uintptr_t>(batch)));
+  key.push_back(arena);
+  key.push_back(bnd.out_ptr);
+  for (const float* p : bnd.in_ptr) key.push_back(p);
+  MimirB200Model::CachedGraph* g = nullptr;
+  for (auto& c : m->graphs)
+    if (c.key == key) { g = &c; break; }
+  if (!g) {
+    if (m->graphs.size() >= 64) drop_graphs(m);  // callers that move their buffers every call never hit the cache
+    m->graphs.emplace_back();
+    g = &m->graphs.back();
+    g->key = key;
+  }
+  if (g->exec) {
+    MB_CUDA(cudaGraphLaunch(g->exec, st));
+    count_launch(static_cast<int>(g->launches));
+    return MIMIR_B200_OK;
+  }
+  if (g->unusable || g->seen++ == 0) return run_layers(m, batch, bnd, st, arena);
+  if (!m->s_capture) MB_CUDA(cudaStreamCreateWithFlags(&m->s_capture, cudaStreamNonBlocking));
+  const uint64_t before = ctx().launches.load();
+  if (cudaStreamBeginCapture(m->s_capture, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+    cudaGetLastError();
+    g->unusable = true;
+    return run_layers(m, batch, bnd, st, arena);
+  }
+  const int s = run_layers(m, batch, bnd, m->s_capture, arena);
+  cudaGraph_t graph = nullptr;
+  const cudaError_t ce = cudaStreamEndCapture(m->s_capture, &graph);
+  const uint64_t inside = ctx().launches.load() - before;
+  ctx().launches.fetch_sub(inside);  // nothing ran yet
+  if (s != MIMIR_B200_OK || ce != cudaSuccess || !graph) {
+    if (graph) cudaGraphDestroy(graph);
+    cudaGetLastError();
+    g->unusable = true;
+    if (s != MIMIR_B200_OK) return s;
+    return run_layers(m, batch, bnd, st, arena);
+  }
+  cudaGraphExec_t exec = nullptr;
+  const cudaError_t ie = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (ie != cudaSuccess || !exec) {
+    cudaGetLastError();
+    g->unusable = true;
+    return run_layers(m, batch, bnd, st, arena);
+  }
+  g->exec = exec;
+  g->launches = inside;
+  MB_CUDA(cudaGraphLaunch(g->exec, st));
+  count_launch(static_cast<int>(g->launches));
+  return MIMIR_B200_OK;
+}
+
 int check_inputs(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, int batch, std::vector<int>* vs) {
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (m->planned_batch != batch) return fail(MIMIR_B200_E_INVALID, "forward: model is planned for batch %d, not %d", m->planned_batch, batch);
@@ -1157,6 +1243,8 @@ int mimir_b200_model_create(const MimirLayerDesc* layers, int n_layers, MimirB20
 }
 
 static void destroy_model(MimirB200Model* m) {
+  drop_graphs(m);
+  if (m->s_capture) cudaStreamDestroy(m->s_capture);
   for (auto& L : m->layers) free_layer_weights(L, m);
   if (m->arena) dev_free(m->arena, m->arena_bytes);
   if (m->arena2) dev_free(m->arena2, m->arena_bytes);
@@ -1277,7 +1365,7 @@ int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInpu
     }
     float* out_c = out_dev + static_cast<size_t>(c) * micro * ot.n;
     if (ot.producer >= 0) b.out_ptr = out_c;
-    MB_TRY(run_layers(m, micro, b, st, m->arena));
+    MB_TRY(run_layers_cached(m, micro, b, st, m->arena));
     if (ot.producer < 0) {  // the graph returns one of its inputs
       const float* src = b.in_ptr[out_root] ? b.in_ptr[out_root] : reinterpret_cast<float*>(m->arena + ot.off_f32);
       MB_CUDA(cudaMemcpyAsync(out_c, src, static_cast<size_t>(ot.n) * micro * 4, cudaMemcpyDeviceToDevice, st));
@@ -1342,7 +1430,7 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
     MB_CUDA(cudaStreamWaitEvent(m->s_comp, m->ev_h2d[c], 0));
     if (c >= 2) MB_CUDA(cudaStreamWaitEvent(m->s_comp, m->ev_d2h[c - 2], 0));
     Bound b;
-    MB_TRY(run_layers(m, micro, b, m->s_comp, arena));
+    MB_TRY(run_layers_cached(m, micro, b, m->s_comp, arena));
     MB_CUDA(cudaEventRecord(m->ev_comp[c], m->s_comp));
     MB_CUDA(cudaStreamWaitEvent(m->s_d2h, m->ev_comp[c], 0));
     MB_CUDA(cudaMemcpyAsync(out_host + static_cast<size_t>(c) * micro * ot.n, arena + ot.off_f32, static_cast<size_t>(ot.n) * micro * 4,

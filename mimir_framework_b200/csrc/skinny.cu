@@ -6,19 +6,29 @@
 // back), so with batch 8 each layer reads a 134 MB weight matrix for 8 rows: tensor cores have
 // nothing to do; the job is to read W exactly once at full HBM rate.
 //
-// Layout of the work: grid = (out tiles of 64) x (K slices of 1024).  A CTA stages its x slice
-// [m][1024] in shared memory once.  Each warp owns 8 output rows of W; 4 lanes share one W row and
-// read 64 contiguous bytes of it per step (128-bit loads), x comes from shared memory as broadcast
-// reads.  Partial sums over K slices go to a small global scratch and are reduced in a fixed order
-// by a second kernel (deterministic, no atomics).
+// Layout of the work: an item is (tile of 8 x WR output rows) x (K slice of 512); one persistent CTA per SM
+// takes items round-robin, so every SM streams the same number of bytes whatever the shape.  A warp owns WR
+// rows of W; per step its 32 lanes cover 128 consecutive k (16 bytes per lane and row, 512 contiguous bytes
+// per row and warp).  W never passes through registers on its way in: every warp runs its own ring of
+// SK_STAGES shared-memory stages filled with asynchronous 16-byte copies (cp.async, zero-filled past the
+// end of a row or of W) that run three steps ahead, across item boundaries, so ~96 KB per SM are in
+// flight all the time; the x slice of the next item rides in the same copy groups into a double buffer.
+// Each x vector read from shared memory is reused for all WR rows.  Every lane keeps WR x m partial sums; a
+// recursive-halving exchange (N/2 + N/4 + ... shuffles instead of 5 N) leaves each lane with the finished
+// sums of N / 32 outputs.  Partial sums over K slices go to a small global scratch and are reduced in a
+// fixed order by a second kernel (deterministic, no atomics).  Unaligned operands or K % 4 != 0 take a
+// plain-load kernel with the same arithmetic.
+#include <cstdlib>
+
 #include "common.h"
 
 namespace mb {
 namespace {
 
-constexpr int SK_TILE_N = 64;
-constexpr int SK_SLICE = 1024;
 constexpr int SK_THREADS = 256;
+constexpr int SK_WARPS = SK_THREADS / 32;
+constexpr int SK_STEP = 128;   // k covered by one warp step
+constexpr int SK_SLICE = 512;  // k covered by one CTA
 
 __device__ __forceinline__ float sk_act(float v, int act) {
   switch (act) {
@@ -34,61 +44,211 @@ __device__ __forceinline__ float sk_act(float v, int act) {
   }
 }
 
-template <int MT>
-__global__ void __launch_bounds__(SK_THREADS)
-skinny_partial_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ part, int m, int k,
-                      int n, int kslices) {
-  extern __shared__ __align__(16) float xs_raw[];
-  float (*xs)[SK_SLICE] = reinterpret_cast<float (*)[SK_SLICE]>(xs_raw);
-  const int o_tile = blockIdx.x * SK_TILE_N;
+template <int MT, int WR>
+__device__ __forceinline__ void sk_fma_step(float (&acc)[MT * WR], const float4 (&wv)[WR], const float* __restrict__ xs, int c) {
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    const float4 xv = *reinterpret_cast<const float4*>(xs + r * SK_SLICE + c);
+#pragma unroll
+    for (int j = 0; j < WR; ++j) {
+      float a = acc[j * MT + r];
+      a = fmaf(wv[j].x, xv.x, a);
+      a = fmaf(wv[j].y, xv.y, a);
+      a = fmaf(wv[j].z, xv.z, a);
+      a = fmaf(wv[j].w, xv.w, a);
+      acc[j * MT + r] = a;
+    }
+  }
+}
+
+// MT = rows of x held (m <= MT), WR = rows of W per warp.
+template <int MT, int WR>
+__global__ void __launch_bounds__(SK_THREADS, 2)
+skinny_partial_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ part, int m, int k, int n) {
+  constexpr int N = MT * WR;   // partial sums per lane
+  constexpr int PER = N / 32;  // finished sums per lane after the exchange
+  static_assert(N % 32 == 0 && PER >= 1, "WR x MT must be a multiple of the warp size");
+  extern __shared__ __align__(16) float xs[];  // [MT][SK_SLICE]
   const int ks = blockIdx.y;
   const int k0 = ks * SK_SLICE;
   const int klen = min(SK_SLICE, k - k0);
-  for (int i = threadIdx.x; i < MT * SK_SLICE; i += SK_THREADS) {
-    const int r = i / SK_SLICE, c = i - r * SK_SLICE;
-    xs[r][c] = (r < m && c < klen) ? __ldg(x + static_cast<long long>(r) * k + k0 + c) : 0.0f;
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 && (k & 3) == 0;
+  // stage x (zero past m and past the end of K so that the main loop needs no row masks)
+  for (int i = threadIdx.x; i < MT * (SK_SLICE / 4); i += SK_THREADS) {
+    const int r = i / (SK_SLICE / 4), c = (i - r * (SK_SLICE / 4)) << 2;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < m) {
+      const float* src = x + static_cast<long long>(r) * k + k0 + c;
+      if (vec && c + 3 < klen) v = __ldg(reinterpret_cast<const float4*>(src));
+      else {
+        if (c + 0 < klen) v.x = __ldg(src + 0);
+        if (c + 1 < klen) v.y = __ldg(src + 1);
+        if (c + 2 < klen) v.z = __ldg(src + 2);
+        if (c + 3 < klen) v.w = __ldg(src + 3);
+      }
+    }
+    *reinterpret_cast<float4*>(xs + r * SK_SLICE + c) = v;
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q = lane & 3;                      // position of this lane inside its group of 4
-  const int o = o_tile + warp * 8 + (lane >> 2);
-  float acc[MT];
+  const int o0 = (blockIdx.x * SK_WARPS + warp) * WR;
+  float acc[N];
 #pragma unroll
-  for (int r = 0; r < MT; ++r) acc[r] = 0.0f;
-  if (o < n) {
-    const float* wrow = w + static_cast<long long>(o) * k + k0;
-    const bool vec = ((reinterpret_cast<uintptr_t>(wrow) & 15) == 0) && ((klen & 15) == 0);
-    if (vec) {
-#pragma unroll 4
-      for (int c = q * 4; c < klen; c += 16) {
-        const float4 wv = __ldg(reinterpret_cast<const float4*>(wrow + c));
+  for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+  const float* wbase = w + static_cast<long long>(o0) * k + k0 + lane * 4;
+  if (vec && klen == SK_SLICE && o0 + WR <= n) {
+    // full tile: no masks, all loads of the four steps are independent of the arithmetic
 #pragma unroll
-        for (int r = 0; r < MT; ++r) {
-          const float4 xv = *reinterpret_cast<const float4*>(&xs[r][c]);
-          acc[r] = fmaf(wv.x, xv.x, acc[r]);
-          acc[r] = fmaf(wv.y, xv.y, acc[r]);
-          acc[r] = fmaf(wv.z, xv.z, acc[r]);
-          acc[r] = fmaf(wv.w, xv.w, acc[r]);
+    for (int st = 0; st < SK_SLICE / SK_STEP; ++st) {
+      float4 wv[WR];
+#pragma unroll
+      for (int j = 0; j < WR; ++j)
+        wv[j] = __ldcs(reinterpret_cast<const float4*>(wbase + static_cast<long long>(j) * k + st * SK_STEP));  // read once
+      sk_fma_step<MT, WR>(acc, wv, xs, st * SK_STEP + lane * 4);
+    }
+  } else {
+    for (int c = lane * 4; c < klen; c += SK_STEP) {
+      float4 wv[WR];
+#pragma unroll
+      for (int j = 0; j < WR; ++j) {
+        wv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (o0 + j < n) {
+          const float* src = wbase + static_cast<long long>(j) * k + (c - lane * 4);
+          if (vec && c + 3 < klen) wv[j] = __ldcs(reinterpret_cast<const float4*>(src));
+          else {
+            if (c + 0 < klen) wv[j].x = __ldg(src + 0);
+            if (c + 1 < klen) wv[j].y = __ldg(src + 1);
+            if (c + 2 < klen) wv[j].z = __ldg(src + 2);
+            if (c + 3 < klen) wv[j].w = __ldg(src + 3);
+          }
         }
       }
-    } else {
-      for (int c = q; c < klen; c += 4) {
-        const float wv = __ldg(wrow + c);
+      sk_fma_step<MT, WR>(acc, wv, xs, c);
+    }
+  }
+  // recursive halving: after the round with partner distance `mask` a lane keeps the half of its
+  // values selected by that lane bit; it ends with acc[0..PER) = sums of indices lane * PER + t
 #pragma unroll
-        for (int r = 0; r < MT; ++r) acc[r] = fmaf(wv, xs[r][c], acc[r]);
-      }
+  for (int half = N / 2, mask = 16; mask >= 1; half >>= 1, mask >>= 1) {
+    const bool upper = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float send = upper ? acc[i] : acc[i + half];
+      const float keep = upper ? acc[i + half] : acc[i];
+      acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
     }
   }
 #pragma unroll
-  for (int r = 0; r < MT; ++r) {
-    acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 1);
-    acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 2);
+  for (int t = 0; t < PER; ++t) {
+    const int idx = lane * PER + t, j = idx / MT, r = idx - j * MT;
+    if (r < m && o0 + j < n) part[(static_cast<long long>(ks) * m + r) * n + o0 + j] = acc[t];
   }
-  if (q == 0 && o < n) {
+}
+
+constexpr int SK_STAGES = 4;
+constexpr int SK_STEPS = SK_SLICE / SK_STEP;  // steps per item
+
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  const int bytes = valid ? 16 : 0;  // src-size 0: the 16 destination bytes are zero-filled, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// Persistent form for 16-byte aligned operands with k % 4 == 0.  Shared memory: x double buffer
+// [2][MT][SK_SLICE], then the rings [warp][SK_STAGES][WR][SK_STEP].
+template <int MT, int WR>
+__global__ void __launch_bounds__(SK_THREADS, 1)
+skinny_stream_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ part, int m, int k, int n,
+                     int kslices, int items) {
+  constexpr int N = MT * WR;
+  constexpr int PER = N / 32;
+  static_assert(N % 32 == 0 && PER >= 1, "WR x MT must be a multiple of the warp size");
+  extern __shared__ __align__(16) float sk_smem[];
+  float* xs = sk_smem;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float* ring = sk_smem + 2 * MT * SK_SLICE + warp * (SK_STAGES * WR * SK_STEP);
+  const int my_items = (items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int total_steps = my_items * SK_STEPS;
+
+  // copy group of global step g (= this CTA's item g / SK_STEPS, step g % SK_STEPS): this warp's WR rows, and with
+  // the first step of an item every thread's share of that item's x slice
+  auto issue = [&](int g) {
+    if (g < total_steps) {
+      const int j = g / SK_STEPS, st = g - j * SK_STEPS;
+      const int item = blockIdx.x + j * gridDim.x;
+      const int tile = item / kslices, ks = item - tile * kslices;
+      const int c = ks * SK_SLICE + st * SK_STEP + lane * 4;
+      const long long o0 = (static_cast<long long>(tile) * SK_WARPS + warp) * WR;
+      float* dst = ring + (g % SK_STAGES) * (WR * SK_STEP) + lane * 4;
 #pragma unroll
-    for (int r = 0; r < MT; ++r)
-      if (r < m) part[(static_cast<long long>(ks) * m + r) * n + o] = acc[r];
+      for (int jj = 0; jj < WR; ++jj) {
+        const bool ok = (o0 + jj < n) && (c < k);
+        cp_async16_zfill(dst + jj * SK_STEP, ok ? (w + (o0 + jj) * k + c) : w, ok);
+      }
+      if (st == 0) {
+        float* xd = xs + (j & 1) * (MT * SK_SLICE);
+        for (int i = threadIdx.x; i < MT * (SK_SLICE / 4); i += SK_THREADS) {
+          const int r = i / (SK_SLICE / 4), cc = (i - r * (SK_SLICE / 4)) << 2;
+          const int kc = ks * SK_SLICE + cc;
+          const bool ok = (r < m) && (kc < k);
+          cp_async16_zfill(xd + r * SK_SLICE + cc, ok ? (x + static_cast<long long>(r) * k + kc) : x, ok);
+        }
+      }
+    }
+    cp_async_commit();  // one group per step, empty past the end, so that the wait count stays fixed
+  };
+#pragma unroll
+  for (int i = 0; i < SK_STAGES - 1; ++i) issue(i);
+
+  float acc[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+  for (int j = 0; j < my_items; ++j) {
+    const int item = blockIdx.x + j * gridDim.x;
+    const int tile = item / kslices, ks = item - tile * kslices;
+    const float* xj = xs + (j & 1) * (MT * SK_SLICE);
+#pragma unroll
+    for (int st = 0; st < SK_STEPS; ++st) {
+      const int g = j * SK_STEPS + st;
+      if (st == 1) issue(g + SK_STAGES - 1);  // (after the item's barrier: it may overwrite the x buffer of item j - 1)
+      else if (st != 0) issue(g + SK_STAGES - 1);
+      if (st == 0) {
+        // the group of step g carries this item's x slice: wait for it, then let every thread's share become visible
+        cp_async_wait<SK_STAGES - 2>();
+        __syncthreads();
+        issue(g + SK_STAGES - 1);
+      } else {
+        cp_async_wait<SK_STAGES - 1>();
+      }
+      const float* src = ring + (g % SK_STAGES) * (WR * SK_STEP) + lane * 4;
+      float4 wv[WR];
+#pragma unroll
+      for (int jj = 0; jj < WR; ++jj) wv[jj] = *reinterpret_cast<const float4*>(src + jj * SK_STEP);
+      sk_fma_step<MT, WR>(acc, wv, xj, st * SK_STEP + lane * 4);
+    }
+#pragma unroll
+    for (int half = N / 2, mask = 16; mask >= 1; half >>= 1, mask >>= 1) {
+      const bool upper = (lane & mask) != 0;
+#pragma unroll
+      for (int i = 0; i < half; ++i) {
+        const float send = upper ? acc[i] : acc[i + half];
+        const float keep = upper ? acc[i + half] : acc[i];
+        acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+      }
+    }
+    const long long o0 = (static_cast<long long>(tile) * SK_WARPS + warp) * WR;
+#pragma unroll
+    for (int t = 0; t < PER; ++t) {
+      const int idx = lane * PER + t, jj = idx / MT, r = idx - jj * MT;
+      if (r < m && o0 + jj < n) part[(static_cast<long long>(ks) * m + r) * n + o0 + jj] = acc[t];
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) acc[i] = 0.0f;
   }
+  cp_async_wait<0>();
 }
 
 __global__ void skinny_finish_kernel(const float* __restrict__ part, const float* __restrict__ bias, float* __restrict__ y,
@@ -104,6 +264,30 @@ __global__ void skinny_finish_kernel(const float* __restrict__ part, const float
   }
 }
 
+template <int MT, int WR>
+int launch_partial(const float* x, const float* w, float* scratch, int m, int k, int n, cudaStream_t st) {
+  const int tiles = (n + SK_WARPS * WR - 1) / (SK_WARPS * WR), kslices = (k + SK_SLICE - 1) / SK_SLICE;
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 && (k & 3) == 0;
+  const char* plain = getenv("MIMIR_B200_SKINNY_PLAIN");
+  if (vec && !(plain && plain[0] == '1') && static_cast<long long>(tiles) * kslices < (1LL << 30)) {
+    constexpr int SMEM = (2 * MT * SK_SLICE + SK_WARPS * SK_STAGES * WR * SK_STEP) * 4;
+    static bool attr = false;
+    if (!attr) {
+      MB_CUDA(cudaFuncSetAttribute(skinny_stream_kernel<MT, WR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+      attr = true;
+    }
+    const int items = tiles * kslices;
+    const int grid = items < ctx().sm_count ? items : ctx().sm_count;
+    skinny_stream_kernel<MT, WR><<<grid, SK_THREADS, SMEM, st>>>(x, w, scratch, m, k, n, kslices, items);
+  } else {
+    constexpr int SMEM = MT * SK_SLICE * 4;
+    dim3 grid(tiles, kslices);
+    skinny_partial_kernel<MT, WR><<<grid, SK_THREADS, SMEM, st>>>(x, w, scratch, m, k, n);
+  }
+  MB_CUDA(cudaGetLastError());
+  return MIMIR_B200_OK;
+}
+
 }  // namespace
 
 size_t skinny_scratch_bytes(int m, int k, int n) {
@@ -116,23 +300,14 @@ int launch_skinny_linear(const float* x, const float* w, const float* bias, floa
   if (m <= 0 || m > 16 || k <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "skinny linear: m must be in 1..16");
   if (scratch == nullptr || scratch_bytes < skinny_scratch_bytes(m, k, n))
     return fail(MIMIR_B200_E_INVALID, "skinny linear: scratch too small");
-  const int kslices = (k + SK_SLICE - 1) / SK_SLICE;
-  dim3 grid((n + SK_TILE_N - 1) / SK_TILE_N, kslices);
-  if (m <= 4) skinny_partial_kernel<4><<<grid, SK_THREADS, 4 * SK_SLICE * 4, st>>>(x, w, scratch, m, k, n, kslices);
-  else if (m <= 8) skinny_partial_kernel<8><<<grid, SK_THREADS, 8 * SK_SLICE * 4, st>>>(x, w, scratch, m, k, n, kslices);
-  else {
-    static bool attr = false;
-    if (!attr) {
-      MB_CUDA(cudaFuncSetAttribute(skinny_partial_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * SK_SLICE * 4));
-      attr = true;
-    }
-    skinny_partial_kernel<16><<<grid, SK_THREADS, 16 * SK_SLICE * 4, st>>>(x, w, scratch, m, k, n, kslices);
-  }
-  MB_CUDA(cudaGetLastError());
+  if ((k + SK_SLICE - 1) / SK_SLICE > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "skinny linear: in_features %d too large", k);
+  if (m <= 4) MB_TRY((launch_partial<4, 8>(x, w, scratch, m, k, n, st)));
+  else if (m <= 8) MB_TRY((launch_partial<8, 8>(x, w, scratch, m, k, n, st)));
+  else MB_TRY((launch_partial<16, 4>(x, w, scratch, m, k, n, st)));
   const long long total = static_cast<long long>(m) * n;
   int fb = static_cast<int>((total + 255) / 256);
   if (fb > ctx().sm_count * 8) fb = ctx().sm_count * 8;
-  skinny_finish_kernel<<<fb, 256, 0, st>>>(scratch, bias, y, m, n, kslices, activation);
+  skinny_finish_kernel<<<fb, 256, 0, st>>>(scratch, bias, y, m, n, (k + SK_SLICE - 1) / SK_SLICE, activation);
   MB_CUDA(cudaGetLastError());
   count_launch(2);
   return MIMIR_B200_OK;

@@ -282,3 +282,39 @@ def test_unet_mid_up_reduced(backend):
     inputs = {"x": (x.ravel(), False)}
     want = oracle_batch(descs, weights, inputs, batch)
     assert_close(gpu_batch(backend, descs, weights, inputs, batch, 3 * 64 * 64, precision=abi.PREC_BF16W), want, "unet mid+up")
+
+
+def test_repeated_forwards_replay_a_cuda_graph_with_identical_results(backend):
+    """The third forward with the same buffers replays a captured CUDA graph of the layer loop: results stay
+    bit-identical, the launch counter keeps counting the kernels inside, and a re-plan drops the graph."""
+    cfg = dict(seq_len=16, d_model=32, vocab_size=64, num_layers=1, num_heads=2, mlp_hidden=48, output_dim=8, causal=False)
+    descs = configs.transformer_encoder(**cfg)
+    weights = configs.seeded_weights(descs, seed=3, std=0.1)
+    r = np.random.default_rng(0)
+    batch = 4
+    ids = r.integers(1, 64, (batch, 16)).astype(np.float32)
+    mag, mod = r.standard_normal(32).astype(np.float32), r.standard_normal(32).astype(np.float32)
+    inputs = {"x": (ids, False), "mag": (mag, True), "mod": (mod, True)}
+    m = backend.GraphModel(descs)
+    for i, w in enumerate(weights):
+        m.upload_weights(i, w)
+    m.plan({"x": (16, False), "mag": (32, True), "mod": (32, True)}, batch)
+    outs, per_call = [], []
+    for _ in range(5):
+        before = backend.stats()["kernels_launched"]
+        outs.append(m.forward(inputs, batch, 8).copy())
+        per_call.append(backend.stats()["kernels_launched"] - before)
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    assert len(set(per_call)) == 1 and per_call[0] > 10, per_call
+    assert_close(outs[0], oracle_batch(descs, weights, inputs, batch), "transformer, replayed")
+    # other inputs through the same graph, then a new plan (different batch)
+    ids2 = r.integers(1, 64, (batch, 16)).astype(np.float32)
+    inputs2 = {"x": (ids2, False), "mag": (mag, True), "mod": (mod, True)}
+    assert_close(m.forward(inputs2, batch, 8), oracle_batch(descs, weights, inputs2, batch), "transformer, replayed, new ids")
+    m.plan({"x": (16, False), "mag": (32, True), "mod": (32, True)}, 2)
+    half = {"x": (ids[:2], False), "mag": (mag, True), "mod": (mod, True)}
+    for _ in range(3):
+        got = m.forward(half, 2, 8)
+    assert_close(got, oracle_batch(descs, weights, half, 2), "transformer, re-planned")
+    m.close()

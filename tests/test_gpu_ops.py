@@ -23,6 +23,9 @@ def rng(seed):
     (37, 50, 29, True),       # ragged everything, skinny path excluded (rows > 16)
     (8, 300, 70, True),       # skinny (weight-streaming) path
     (16, 4096, 130, False),   # skinny path, several K slices
+    (3, 77, 5, True),         # skinny path, K not a multiple of 4 (scalar loads), fewer outputs than a row group
+    (8, 33000, 24, True),     # skinny path, one row group spread over many warps
+    (5, 130, 1000, False),    # skinny path, warps that span several row groups
     (128, 64, 256, True),     # exactly one tile
     (129, 65, 257, True),     # one past a tile in every dimension
     (300, 1000, 515, True),
