@@ -75,35 +75,56 @@ int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, i
 namespace mb {
 namespace {
 
-// One CTA per (sample, padded row yp, 32-channel block): 32x32 tiles through shared memory turn the
-// W-contiguous NCHW row into C-contiguous NHWC pixels; border pixels are written as zeros.
+// One CTA per (sample, padded row yp, 64-channel block): 64 x 64 tiles through shared memory turn the
+// W-contiguous NCHW rows into C-contiguous NHWC pixels; border pixels are written as zeros.  Sixteen
+// coalesced loads are in flight per thread; on the way out a lane owns a channel pair, so a warp writes
+// 128 contiguous bytes per pixel and plane as packed bf16x2.
+constexpr int TP_C = 64, TP_X = 64;
+
 __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
                                                                   int c, int h, int w, int pad, int planes, long long plane_stride) {
-  __shared__ float tile[32][33];
+  __shared__ float tile[TP_C][TP_X + 1];
   const int hp = h + 2 * pad, wp = w + 2 * pad;
-  const int cb = blockIdx.x * 32;
+  const int cb = blockIdx.x * TP_C;
   const int yp = blockIdx.y;
   const int n = blockIdx.z;
   const int y = yp - pad;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool row_in = y >= 0 && y < h;
-  for (int x0 = 0; x0 < wp; x0 += 32) {
-    // load tile[cc][xx] = x[n, cb + cc, y, x0 + xx - pad]
-    for (int cc = ty; cc < 32; cc += 8) {
-      const int xs = x0 + tx - pad;
-      float v = 0.0f;
-      if (row_in && xs >= 0 && xs < w && cb + cc < c) v = __ldg(x + ((static_cast<long long>(n) * c + cb + cc) * h + y) * w + xs);
-      tile[cc][tx] = v;
+  const float* src = x + ((static_cast<long long>(n) * c + cb) * h + (row_in ? y : 0)) * w;
+  const long long ch_stride = static_cast<long long>(h) * w;
+  for (int x0 = 0; x0 < wp; x0 += TP_X) {
+    // tile[cc][xx] = x[n, cb + cc, y, x0 + xx - pad]; a warp reads 32 consecutive pixels of one channel
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = threadIdx.x + 256 * i;
+      const int cc = idx >> 6, xx = idx & 63;
+      const int xs = x0 + xx - pad;
+      v[i] = (row_in && xs >= 0 && xs < w && cb + cc < c) ? __ldg(src + cc * ch_stride + xs) : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int idx = threadIdx.x + 256 * i;
+      tile[idx >> 6][idx & 63] = v[i];
     }
     __syncthreads();
-    for (int xx = ty; xx < 32; xx += 8) {
-      const int xp = x0 + xx;
-      if (xp < wp && cb + tx < c) {
-        const float v = tile[tx][xx];
-        const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-        const long long o = ((static_cast<long long>(n) * hp + yp) * wp + xp) * c + cb + tx;
-        dst[o] = hi;
-        if (planes == 2) dst[o + plane_stride] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    const int c0 = cb + 2 * lane;
+    if (c0 < c) {  // c is even (a multiple of 32)
+#pragma unroll
+      for (int i = 0; i < TP_X / 8; ++i) {
+        const int xx = warp + 8 * i;
+        const int xp = x0 + xx;
+        if (xp < wp) {
+          const float a = tile[2 * lane][xx], b = tile[2 * lane + 1][xx];
+          const __nv_bfloat162 hi = __floats2bfloat162_rn(a, b);
+          const long long o = ((static_cast<long long>(n) * hp + yp) * wp + xp) * c + c0;
+          *reinterpret_cast<__nv_bfloat162*>(dst + o) = hi;
+          if (planes == 2) {
+            const float2 hf = __bfloat1622float2(hi);
+            *reinterpret_cast<__nv_bfloat162*>(dst + o + plane_stride) = __floats2bfloat162_rn(a - hf.x, b - hf.y);
+          }
+        }
       }
     }
     __syncthreads();
@@ -136,7 +157,7 @@ int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int bat
   if (batch <= 0 || c <= 0 || h <= 0 || w <= 0 || pad < 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad activation shape");
   const int hp = h + 2 * pad, wp = w + 2 * pad;
   if (hp > 65535 || batch > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: image too tall for the layout kernel");
-  dim3 grid((c + 31) / 32, hp, batch);
+  dim3 grid((c + TP_C - 1) / TP_C, hp, batch);
   nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, static_cast<long long>(batch) * hp * wp * c);
   MB_CUDA(cudaGetLastError());
   count_launch();

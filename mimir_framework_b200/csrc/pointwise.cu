@@ -126,6 +126,23 @@ __global__ void upsample_nearest_kernel(const float* __restrict__ x, float* __re
   }
 }
 
+// 2 x 2 nearest upsample of rows with an even width: a thread reads two neighbouring input pixels (64 bits)
+// and writes the same four values (128 bits) into two output rows; all index math in 32 bits per plane row.
+__global__ void upsample_nearest_2x2_kernel(const float* __restrict__ x, float* __restrict__ y, long long plane_rows, int in_w) {
+  const int half_w = in_w >> 1;
+  const long long total = plane_rows * half_w;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
+    const long long row = i / half_w;            // (plane, input row)
+    const int q = static_cast<int>(i - row * half_w);
+    const float2 v = __ldcs(reinterpret_cast<const float2*>(x + row * in_w) + q);
+    const float4 o = make_float4(v.x, v.x, v.y, v.y);
+    float* out = y + row * 4 * in_w + 4 * q;     // output row 2*r of the same plane: (plane*in_h + r) * 2 * (2*in_w)
+    __stcs(reinterpret_cast<float4*>(out), o);
+    __stcs(reinterpret_cast<float4*>(out + 2 * in_w), o);
+  }
+}
+
 struct PermuteDesc {
   int nd;
   long long out_shape[MIMIR_B200_MAX_DIMS];
@@ -277,6 +294,13 @@ int launch_upsample_nearest(const float* x, float* y, int batch, int ch, int in_
     return fail(MIMIR_B200_E_INVALID, "UpsampleNearest: dimensions (out_h, out_w, in_channels) must be set");
   const long long planes = static_cast<long long>(batch) * ch;
   const long long total = planes * in_h * sh * in_w * sw;
+  if (sh == 2 && sw == 2 && (in_w & 1) == 0 && ((reinterpret_cast<uintptr_t>(x) & 7) | (reinterpret_cast<uintptr_t>(y) & 15)) == 0) {
+    const long long items = planes * in_h * (in_w >> 1);
+    upsample_nearest_2x2_kernel<<<grid_for(items, 256), 256, 0, st>>>(x, y, planes * in_h, in_w);
+    MB_CUDA(cudaGetLastError());
+    count_launch();
+    return MIMIR_B200_OK;
+  }
   upsample_nearest_kernel<<<grid_for(total, 256), 256, 0, st>>>(x, y, planes, in_h, in_w, sh, sw);
   MB_CUDA(cudaGetLastError());
   count_launch();

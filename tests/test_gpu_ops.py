@@ -239,6 +239,9 @@ def test_data_movement_bitexact(backend):
     x = r.standard_normal(2 * 3 * 4 * 5).astype(np.float32)
     want = np.concatenate([port.upsample_nearest(x[i * 60:(i + 1) * 60], 3, 4, 5, 2, 3) for i in range(2)])
     assert np.array_equal(backend.upsample_nearest(x, 2, 3, 4, 5, 2, 3), want)
+    x2 = r.standard_normal(2 * 3 * 5 * 6).astype(np.float32)  # 2 x 2 with an even width: the vectorised kernel
+    want = np.concatenate([port.upsample_nearest(x2[i * 90:(i + 1) * 90], 3, 5, 6, 2, 2) for i in range(2)])
+    assert np.array_equal(backend.upsample_nearest(x2, 2, 3, 5, 6, 2, 2), want)
     for dims in ([2, 0, 1], [0, 2, 1], [1, 0, 2]):
         want = np.concatenate([port.permute(x[i * 60:(i + 1) * 60], [3, 4, 5], dims) for i in range(2)])
         assert np.array_equal(backend.permute(x, [3, 4, 5], dims, batch=2), want)
