@@ -8,13 +8,19 @@
 //   * one CTA owns 128 query rows of one (sample, head) and walks the keys in tiles of 64:
 //       warp 0    TMA producer (Q once, then K_j, V_j; single-buffered, refilled as soon as the MMA
 //                 that read them has completed)
-//       warp 1    MMA issuer: S_j = Q K_j^T (hi*hi + lo*hi + hi*lo) into TMEM, later
-//                 PV_j = P_j V_j (same three products) into a second TMEM tile
-//       warps 2-5 one thread per query row: tcgen05.ld S_j, running max / sum, P_j written to shared
-//                 memory as bf16 hi/lo in the 128-byte-swizzled K-major layout the MMA reads, then
-//                 O = O * exp(m_old - m_new) + PV_j in registers (no TMEM read-modify-write)
-//   * 96 KB of shared memory and 128 TMEM columns per CTA, so two CTAs share an SM and one's softmax
-//     overlaps the other's MMAs.
+//       warp 1    MMA issuer, one tile ahead on the scores: S_{j+1} = Q K_{j+1}^T (hi*hi + lo*hi + hi*lo)
+//                 goes into the second of two TMEM score tiles while the softmax of tile j runs, then
+//                 O += P_j V_j (same three products) accumulates in a third TMEM tile
+//       warps 2-5 one thread per query row: tcgen05.ld S_j (the score tile is released as soon as it is
+//                 in registers), running max / sum, P_j written to shared memory as bf16 hi/lo in the
+//                 128-byte-swizzled K-major layout the MMA reads
+//   * O stays in TMEM for the whole key loop.  The running maximum of a row is only raised when it grew
+//     by more than 2^8 (decided per warp): then the warp waits for the last P V product, multiplies its
+//     32 rows of O by exp(m_old - m_new) in place (tcgen05.ld / tcgen05.st) and carries on.  Otherwise
+//     the stale maximum is kept - probabilities up to 2^8 are harmless in fp32 / split bf16 and the final
+//     division by the row sum taken with the same maximum cancels it.  So there is no per-tile
+//     read-modify-write of O and the softmax of tile j+1 overlaps P_j V_j.
+//   * 96 KB of shared memory and 256 TMEM columns per CTA, so two CTAs share an SM.
 // Every mbarrier wait is bounded; on expiry the CTA raises its abort flag, sets the device error word,
 // leaves all loops and frees its TMEM.
 #include "common.h"
@@ -27,7 +33,7 @@ constexpr int AT_HD = 64;     // head dimension this kernel is written for
 constexpr int AT_BQ = 128;    // query rows per CTA (TMEM lanes)
 constexpr int AT_BK = 64;     // keys per tile
 constexpr int AT_THREADS = 192;
-constexpr int AT_TMEM_COLS = 128;  // S tile (64) + PV tile (64)
+constexpr int AT_TMEM_COLS = 256;  // two S tiles (64 each) + the O tile (64); a power of two
 
 constexpr int AT_Q_BYTES = AT_BQ * AT_HD * 2;   // one plane
 constexpr int AT_K_BYTES = AT_BK * AT_HD * 2;
@@ -94,8 +100,8 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   uint8_t* sP = sV + 2 * AT_V_BYTES;        // [2][128][64 keys]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * AT_P_BYTES);
   uint64_t *q_full = bars, *k_full = bars + 1, *k_empty = bars + 2, *v_full = bars + 3, *v_empty = bars + 4,
-           *s_full = bars + 5, *s_empty = bars + 6, *p_full = bars + 7, *o_full = bars + 8, *o_empty = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+           *s_full = bars + 5 /* [2] */, *s_empty = bars + 7 /* [2] */, *p_full = bars + 9, *pv_done = bars + 10;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,10 +117,11 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
+    mbar_init(s_full + 1, 1);
     mbar_init(s_empty, 4);
+    mbar_init(s_empty + 1, 4);
     mbar_init(p_full, 4);
-    mbar_init(o_full, 1);
-    mbar_init(o_empty, 4);
+    mbar_init(pv_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -127,7 +134,7 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + AT_BK;
+  const uint32_t tmem_o = tmem_base + 2 * AT_BK;  // score tile b lives at tmem_base + b * 64
 
   if (warp == 0) {
     if (lane == 0) {
@@ -151,11 +158,14 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       constexpr uint32_t idesc = make_idesc(AT_BQ, AT_BK);  // M = 128, N = 64 for both products
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err_word, 13);
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const uint32_t ph = j & 1;
-        if (!mbar_wait(k_full, ph, abort_flag, p.err_word, 14)) break;
-        if (!mbar_wait(s_empty, ph ^ 1, abort_flag, p.err_word, 15)) break;
+      // S_t = Q K_t^T into score tile t & 1 (the tile's u-th use, u = t >> 1)
+      auto issue_scores = [&](int t) -> bool {
+        const int b = t & 1;
+        const uint32_t u = static_cast<uint32_t>(t >> 1) & 1;
+        if (!mbar_wait(k_full, t & 1, abort_flag, p.err_word, 14)) return false;
+        if (!mbar_wait(s_empty + b, u ^ 1, abort_flag, p.err_word, 15)) return false;
         tcgen05_fence_after();
+        const uint32_t tmem_s = tmem_base + b * AT_BK;
 #pragma unroll
         for (int k = 0; k < AT_HD / 16; ++k) {
           const uint32_t ko = k * 32;
@@ -165,58 +175,70 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           umma_bf16(tmem_s, ql, kh, idesc, 1u);
           umma_bf16(tmem_s, qh, kl, idesc, 1u);
         }
-        umma_commit(s_full);
+        umma_commit(s_full + b);
         umma_commit(k_empty);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_scores(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t ph = j & 1;
+        if (j + 1 < n_tiles && !issue_scores(j + 1)) break;
         if (!mbar_wait(p_full, ph, abort_flag, p.err_word, 16)) break;
         if (!mbar_wait(v_full, ph, abort_flag, p.err_word, 17)) break;
-        if (!mbar_wait(o_empty, ph ^ 1, abort_flag, p.err_word, 18)) break;
         tcgen05_fence_after();
 #pragma unroll
         for (int k = 0; k < AT_BK / 16; ++k) {
           const uint32_t ko = k * 32;
           const uint64_t ph_ = make_smem_desc(aP + ko, 128), pl = make_smem_desc(aP + AT_P_BYTES + ko, 128);
           const uint64_t vh = make_smem_desc(aV + ko, 128), vl = make_smem_desc(aV + AT_V_BYTES + ko, 128);
-          umma_bf16(tmem_o, ph_, vh, idesc, k != 0 ? 1u : 0u);
+          umma_bf16(tmem_o, ph_, vh, idesc, (j != 0 || k != 0) ? 1u : 0u);
           umma_bf16(tmem_o, pl, vh, idesc, 1u);
           umma_bf16(tmem_o, ph_, vl, idesc, 1u);
         }
-        umma_commit(o_full);
+        umma_commit(pv_done);
         umma_commit(v_empty);
       }
     }
   } else {
-    // ------------------------------ softmax / accumulate: one thread per query row ----------------
+    // ------------------------------ softmax: one thread per query row ------------------------------
     const int quad = warp & 3;
     const int r_local = quad * 32 + lane;
     const int row = q0 + r_local;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    constexpr float LOG2E = 1.4426950408889634f;
     float m_run = -1e30f, l_run = 0.0f;  // the reference's initial max (LayerOps.hpp:1052)
-    float o_acc[AT_HD];
-#pragma unroll
-    for (int c = 0; c < AT_HD; ++c) o_acc[c] = 0.0f;
     uint8_t* p_row_hi = sP + r_local * 128;
     uint8_t* p_row_lo = p_row_hi + AT_P_BYTES;
     const int sw = r_local & 7;  // 128-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ (r % 8)
     bool alive = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const uint32_t ph = j & 1;
+    // whole-warp wait: lane 0 runs the bounded wait, the others then see the completed phase at once
+    auto warp_wait = [&](uint64_t* bar, uint32_t parity, int where) -> bool {
       int ok = 1;
-      if (lane == 0) ok = mbar_wait(s_full, ph, abort_flag, p.err_word, 19) ? 1 : 0;
+      if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, p.err_word, where) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) { alive = false; break; }
-      while (!mbar_try_wait(s_full, ph)) {}
+      if (!ok) return false;
+      while (!mbar_try_wait(bar, parity)) {}
+      return true;
+    };
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = j & 1;
+      if (!warp_wait(s_full + b, static_cast<uint32_t>(j >> 1) & 1, 19)) { alive = false; break; }
       tcgen05_fence_after();
       const int key0 = j * AT_BK;
-      // the whole tile of scores for this row, read once
+      // the whole tile of scores for this row, read once; the TMEM tile is free for S_{j+2} right away
       uint32_t sa[32], sb[32];
+      const uint32_t tmem_s = tmem_base + b * AT_BK;
       tmem_ld_32x32_nowait(tmem_s + lane_base, sa);
       tmem_ld_32x32_nowait(tmem_s + lane_base + 32, sb);
       tmem_wait_ld();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty + b);
       // Tiles left of the diagonal and inside the sequence need no masking (warp-uniform test on the
       // warp's first row, which is the most restrictive one for the causal bound).
       const int row_first = q0 + quad * 32;
       const bool full_tile = (key0 + AT_BK <= p.seq) && (!p.causal || key0 + AT_BK - 1 <= row_first);
-      const float c2 = p.scale * 1.4426950408889634f;  // scores are kept in the exp2 domain: s * scale * log2(e)
+      const float c2 = p.scale * LOG2E;  // scores are kept in the exp2 domain: s * scale * log2(e)
       float mx = -1e30f;
       if (full_tile) {
 #pragma unroll
@@ -230,10 +252,38 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           mx = fmaxf(mx, fmaxf(__uint_as_float(sa[i]), __uint_as_float(sb[i])));
         }
       }
-      // running maximum in score units (the reference's -1e30 start: LayerOps.hpp:1052)
+      // candidate maximum in score units (the reference's -1e30 start: LayerOps.hpp:1052)
       const float m_new = fmaxf(m_run, (mx > -1e30f) ? mx * p.scale : -1e30f);
-      const float corr = exp2f((m_run - m_new) * 1.4426950408889634f);
-      const float m2 = m_new * 1.4426950408889634f;
+      bool waited_pv = false;
+      if (j == 0) {
+        m_run = m_new;  // O is still empty: nothing to rescale
+      } else {
+        // raise the maximum only when some row of this warp outgrew it by more than 2^8
+        const bool grow = (m_new - m_run) * LOG2E > 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+          if (!warp_wait(pv_done, static_cast<uint32_t>(j - 1) & 1, 20)) { alive = false; break; }
+          waited_pv = true;
+          tcgen05_fence_after();
+          const float corr = exp2f((m_run - m_new) * LOG2E);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t o[32];
+            tmem_ld_32x32_nowait(tmem_o + lane_base + half * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+            tmem_st_32x32(tmem_o + lane_base + half * 32, o);
+          }
+          tmem_wait_st();
+          l_run *= corr;
+          m_run = m_new;
+        }
+      }
+      const float m2 = m_run * LOG2E;
+      // P_{j-1} V_{j-1} must have finished reading the P buffer before it is overwritten
+      if (j > 0 && !waited_pv) {
+        if (!warp_wait(pv_done, static_cast<uint32_t>(j - 1) & 1, 21)) { alive = false; break; }
+      }
       float rs = 0.0f;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -258,41 +308,32 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           *reinterpret_cast<uint4*>(p_row_lo + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
       }
-      l_run = l_run * corr + rs;
-      m_run = m_new;
-      // S has been read twice and P is in shared memory: publish both
+      l_run += rs;
+      // P is in shared memory and any rescaled O is back in TMEM: let the MMA warp issue P_j V_j
       tcgen05_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty);
-        mbar_arrive(p_full);
-      }
-      // PV_j -> registers
-      if (lane == 0) ok = mbar_wait(o_full, ph, abort_flag, p.err_word, 20) ? 1 : 0;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) { alive = false; break; }
-      while (!mbar_try_wait(o_full, ph)) {}
-      tcgen05_fence_after();
-      tmem_ld_32x32_nowait(tmem_o + lane_base, sa);
-      tmem_ld_32x32_nowait(tmem_o + lane_base + 32, sb);
-      tmem_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        o_acc[i] = fmaf(o_acc[i], corr, __uint_as_float(sa[i]));
-        o_acc[32 + i] = fmaf(o_acc[32 + i], corr, __uint_as_float(sb[i]));
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_empty);
+      if (lane == 0) mbar_arrive(p_full);
     }
-    if (alive && row < p.seq) {
+    if (alive && n_tiles > 0) alive = warp_wait(pv_done, static_cast<uint32_t>(n_tiles - 1) & 1, 22);
+    if (alive) {
+      tcgen05_fence_after();
       const float inv = 1.0f / (l_run + 1e-9f);  // LayerOps.hpp:1076
-      const int b = bhi / p.heads, h = bhi - b * p.heads;
-      float* o = p.out + (static_cast<long long>(b) * p.seq + row) * p.embed + h * AT_HD;
+      const int bb = bhi / p.heads, h = bhi - bb * p.heads;
+      float* o = p.out + (static_cast<long long>(bb) * p.seq + row) * p.embed + h * AT_HD;
 #pragma unroll
-      for (int c = 0; c < AT_HD; c += 4)
-        *reinterpret_cast<float4*>(o + c) = make_float4(o_acc[c] * inv, o_acc[c + 1] * inv, o_acc[c + 2] * inv, o_acc[c + 3] * inv);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[32];
+        tmem_ld_32x32_nowait(tmem_o + lane_base + half * 32, v);  // every lane of the warp takes part in the load
+        tmem_wait_ld();
+        if (row < p.seq) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<float4*>(o + half * 32 + c) =
+                make_float4(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv, __uint_as_float(v[c + 2]) * inv,
+                            __uint_as_float(v[c + 3]) * inv);
+        }
+      }
     }
   }
 

@@ -109,6 +109,25 @@ def test_attention(backend, batch, seq, E, heads, causal):
     assert_close(got, want, f"attention b{batch} s{seq} E{E} h{heads} c{causal}")
 
 
+@pytest.mark.parametrize("causal", [0, 1])
+def test_attention_running_maximum_grows_across_key_tiles(backend, causal):
+    """Scores whose row maximum grows by 2^8 .. 2^16 from one 64-key tile to the next (later keys are
+    "louder"): the tensor-core kernel keeps a stale maximum below 2^8 of growth and rescales the output
+    it holds in TMEM above it, so both branches run.  Scores reach |s| = 24 here, which amplifies the
+    rounding differences of the QKV projection by e^(24 * 1e-5): the gate is widened accordingly (the
+    fp32 CUDA-core attention shows the same spread); a wrong rescale would be off by factors."""
+    batch, seq, E, heads = 2, 320, 128, 2
+    r = rng(77)
+    x = r.standard_normal((batch, seq, E)).astype(np.float32)
+    x *= (1.0 + 5.0 * np.arange(seq, dtype=np.float32) / seq)[None, :, None]
+    w = (r.standard_normal(4 * E * E) / np.sqrt(E)).astype(np.float32)
+    w[: 3 * E * E].reshape(E, 3 * E)[:, : 2 * E] *= 0.45
+    x = x.ravel()
+    want = np.concatenate([port.attention(x[i * seq * E:(i + 1) * seq * E], w, seq, E, heads, causal) for i in range(batch)])
+    got = backend.attention(x, w, batch, seq, E, heads, causal)
+    assert_close(got, want, f"attention with growing maximum, causal={causal}", abs_tol=1e-3, rel_tol=5e-3)
+
+
 def test_attention_identity_weights(backend):
     # hand-checkable: Wq=Wk=0 makes every score 0 -> uniform attention -> each output row is the mean
     # of V rows (all rows for non-causal); Wv = Wout = I.
