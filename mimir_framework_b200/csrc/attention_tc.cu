@@ -105,7 +105,9 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = blockIdx.x, bhi = blockIdx.y;
+  // causal: the query tiles with the most key tiles are scheduled first, so the last wave is made of short ones
+  const int qt = p.causal ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int bhi = blockIdx.y;
   const int q0 = qt * AT_BQ;
   int n_tiles = (p.seq + AT_BK - 1) / AT_BK;
   if (p.causal) n_tiles = min(n_tiles, (min(p.seq, q0 + AT_BQ) + AT_BK - 1) / AT_BK);
@@ -284,7 +286,7 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (j > 0 && !waited_pv) {
         if (!warp_wait(pv_done, static_cast<uint32_t>(j - 1) & 1, 21)) { alive = false; break; }
       }
-      float rs = 0.0f;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
 #pragma unroll
@@ -296,7 +298,7 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const uint32_t u1 = half ? sb[c8 * 8 + e + 1] : sa[c8 * 8 + e + 1];
             const float p0 = exp2f(fmaf(__uint_as_float(u0), c2, -m2));
             const float p1 = exp2f(fmaf(__uint_as_float(u1), c2, -m2));
-            rs += p0 + p1;
+            rs4[c8] += p0 + p1;
             const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
             const float2 hf = __bfloat1622float2(h2);
             const __nv_bfloat162 l2 = __floats2bfloat162_rn(p0 - hf.x, p1 - hf.y);
@@ -308,7 +310,7 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           *reinterpret_cast<uint4*>(p_row_lo + chunk * 16) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
         }
       }
-      l_run += rs;
+      l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
       // P is in shared memory and any rescaled O is back in TMEM: let the MMA warp issue P_j V_j
       tcgen05_fence_before();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
