@@ -66,6 +66,11 @@ struct GemmParams {
   // [samples * hp * wp, C]; k-block kb belongs to tap t = kb / conv_cblocks and reads A rows shifted by
   // (kh - pad) * wp + (kw - pad); output rows live on the padded grid, border rows are dropped.
   int conv_ks, conv_cblocks, conv_pad, conv_hp, conv_wp, conv_h, conv_w;
+  // swap != 0 (channel-major outputs with at most 128 output channels): the weights are the M side of the
+  // MMA (TMEM lane = output channel) and 256 activation rows are its N side.  A tcgen05.mma with M = 128 costs
+  // the same whatever its N, so a narrow layer computed the usual way (N = its few channels, padded to the
+  // tile) pays for 256 columns it does not have; swapped, every instruction does full work.
+  int swap;
   int* err_word;
 };
 
@@ -131,7 +136,9 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const uint32_t tx_bytes = static_cast<uint32_t>(p.a_planes * A_TILE + p.w_planes * W_TILE);
+  // planes on the M side (128-row tiles) and on the N side (256-row tiles) of the MMA
+  const int m_planes = p.swap ? p.w_planes : p.a_planes, n_planes = p.swap ? p.a_planes : p.w_planes;
+  const uint32_t tx_bytes = static_cast<uint32_t>(m_planes * A_TILE + n_planes * W_TILE);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
@@ -153,10 +160,19 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             a_row += (kh - p.conv_pad) * p.conv_wp + (kw - p.conv_pad);  // may be negative: TMA zero-fills
             a_col = cb * BK;
           }
-          for (int pl = 0; pl < p.a_planes; ++pl)
-            tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
-          for (int pl = 0; pl < p.w_planes; ++pl)
-            tma_load_3d(sbase + 2 * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * BN, pl);
+          if (!p.swap) {
+            for (int pl = 0; pl < p.a_planes; ++pl)
+              tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
+            for (int pl = 0; pl < p.w_planes; ++pl)
+              tma_load_3d(sbase + 2 * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * BN, pl);
+          } else {
+            // 128 weight rows into the M-side tiles, 256 activation rows (tile tn) into the N-side tiles
+            a_row += tn * BN - tm * BM;
+            for (int pl = 0; pl < p.w_planes; ++pl)
+              tma_load_3d(sbase + pl * A_TILE, &map_w, &full_bar[stage], kb * BK, tm * BM, pl);
+            for (int pl = 0; pl < p.a_planes; ++pl)
+              tma_load_3d(sbase + 2 * A_TILE + pl * W_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -191,11 +207,11 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint64_t a_hi = make_smem_desc(sa + koff, SWZ);
             const uint64_t w_hi = make_smem_desc(sw + koff, SWZ);
             umma_bf16(d_tmem, a_hi, w_hi, idesc, (kb | k) != 0 ? 1u : 0u);
-            if (p.a_planes == 2) {
+            if (m_planes == 2) {
               const uint64_t a_lo = make_smem_desc(sa + A_TILE + koff, SWZ);
               umma_bf16(d_tmem, a_lo, w_hi, idesc, 1u);
             }
-            if (p.w_planes == 2) {
+            if (n_planes == 2) {
               const uint64_t w_lo = make_smem_desc(sw + W_TILE + koff, SWZ);
               umma_bf16(d_tmem, a_hi, w_lo, idesc, 1u);
             }
@@ -232,6 +248,62 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tcgen05_fence_after();
       const int row0 = tm * BM + quad * 32;
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      if (p.swap) {
+        // TMEM lane = output channel, column = activation row (pixel).  Lane j works out where pixel j of the chunk
+        // lives in the NCHW output; every lane then writes its channel's value for the 32 pixels (consecutive
+        // addresses per lane, so each lane fills whole lines over the loop).
+        const int oc = row0 + lane;
+        const long long hw = (p.conv_ks > 0) ? static_cast<long long>(p.conv_h) * p.conv_w : static_cast<long long>(p.ohw);
+#pragma unroll 1
+        for (int ci = 0; ci < (BN / 32) / 2; ++ci) {
+          const int c0 = (half * (BN / 64) + ci) * 32;
+          const int r0 = tn * BN + c0;
+          if (r0 >= p.m) break;  // warp-uniform
+          float v[32];
+          tmem_ld_32x32(taddr0 + c0, v);
+          const int prow = r0 + lane;
+          bool pv = prow < p.m;
+          long long pbase = 0;
+          if (p.conv_ks > 0) {
+            const int per = p.conv_hp * p.conv_wp;
+            const int smp = prow / per, rem = prow - smp * per;
+            const int yq = rem / p.conv_wp;
+            const int yy = yq - p.conv_pad, xx = rem - yq * p.conv_wp - p.conv_pad;
+            pv = pv && yy >= 0 && yy < p.conv_h && xx >= 0 && xx < p.conv_w;
+            pbase = static_cast<long long>(smp) * p.n * hw + static_cast<long long>(yy) * p.conv_w + xx;
+          } else {
+            const long long smp = prow / p.ohw;
+            pbase = smp * p.n * hw + (prow - smp * p.ohw);
+          }
+          if (p.activation != -1) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.activation);
+          }
+          const unsigned valid_mask = __ballot_sync(0xffffffffu, pv);
+          const long long mine = static_cast<long long>(oc) * hw;
+          const bool oc_ok = oc < p.n;
+          if (p.residual != nullptr) {
+            float q[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const long long o = __shfl_sync(0xffffffffu, pbase, j) + mine;
+              q[j] = (oc_ok && ((valid_mask >> j) & 1u)) ? __ldg(p.residual + o) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += q[j];
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const long long o = __shfl_sync(0xffffffffu, pbase, j) + mine;
+            if (oc_ok && ((valid_mask >> j) & 1u)) p.out_f32[o] = v[j];
+          }
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
+        continue;
+      }
       const int col_limit = (p.out_split != nullptr) ? static_cast<int>(p.np) : p.n;
       // channel-major addressing of this lane's row
       bool cm_ok = false;
@@ -484,9 +556,19 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   const bool conv = g.conv_ks > 0;
   CUtensorMap map_a, map_w;
   // conv: A rows are `conv_c` channels long and K = taps * conv_c runs over (tap, channel)
-  MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, conv ? g.conv_c : kp, BK, BM));
-  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, BN));
+  // narrow channel-major layers run with the operands swapped (see GemmParams::swap); short K keeps the usual
+  // form, whose epilogue writes NCHW with coalesced stores
+  const char* noswap = getenv("MIMIR_B200_GEMM_NOSWAP");
+  const int kblocks_all = conv ? g.conv_ks * g.conv_ks * (g.conv_c / BK) : kp / BK;
+  // (the swapped epilogue stores one channel per lane, 4 bytes per sector and instruction: it hides behind a long
+  // main loop or when only a few channels exist; measured on 128 -> 128 channels, K = 1152, it loses)
+  const bool swap = (conv || g.out_nchw_hw > 0) && g.bias == nullptr && g.out_split == nullptr && g.out_f32 != nullptr &&
+                    g.m >= 4 * BN && (g.n <= 32 ? kblocks_all * BK >= 256 : (g.n <= BM && kblocks_all * BK >= 2048)) &&
+                    !(noswap && noswap[0] == '1');
+  MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, conv ? g.conv_c : kp, BK, swap ? BN : BM));
+  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : BN));
   GemmParams p;
+  p.swap = swap ? 1 : 0;
   p.m = g.m;
   p.n = g.n;
   p.kblocks = conv ? g.conv_ks * g.conv_ks * (g.conv_c / BK) : kp / BK;
@@ -499,8 +581,8 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.conv_w = g.conv_w;
   p.a_planes = g.a_planes;
   p.w_planes = g.w_planes;
-  p.tiles_m = (g.m + BM - 1) / BM;
-  p.tiles_n = (g.n + BN - 1) / BN;
+  p.tiles_m = swap ? (g.n + BM - 1) / BM : (g.m + BM - 1) / BM;
+  p.tiles_n = swap ? (g.m + BN - 1) / BN : (g.n + BN - 1) / BN;
   p.group_n = env_int("MIMIR_B200_GEMM_GROUP_N", 8);
   if (p.group_n < 1) p.group_n = 1;
   if (p.group_n > p.tiles_n) p.group_n = p.tiles_n;

@@ -153,6 +153,9 @@ def test_attention_identity_weights(backend):
     (2, 64, 24, 7, 11, 5, 1, 2, 0),   # shifted-GEMM path, 5x5 taps
     (1, 256, 300, 20, 20, 3, 1, 1, 0),  # shifted-GEMM path, two column tiles
     (2, 32, 16, 12, 12, 3, 2, 1, 0),  # stride 2 stays on the im2col path
+    (2, 64, 3, 40, 40, 3, 1, 1, 0),   # few output channels: operands swapped (channels on the TMEM lanes)
+    (2, 256, 128, 24, 24, 3, 1, 1, 1),  # 128 channels with a long K: swapped too, ReLU
+    (3, 32, 20, 30, 26, 5, 1, 2, 0),  # swapped, 5x5 taps, ragged pixel tiles
 ])
 def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
     r = rng(ic * oc + h)
