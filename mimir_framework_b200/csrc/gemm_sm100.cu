@@ -249,18 +249,25 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const int row0 = tm * BM + quad * 32;
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
       if (p.swap) {
-        // TMEM lane = output channel, column = activation row (pixel).  Lane j works out where pixel j of the chunk
-        // lives in the NCHW output; every lane then writes its channel's value for the 32 pixels (consecutive
-        // addresses per lane, so each lane fills whole lines over the loop).
-        const int oc = row0 + lane;
+        // TMEM lane = output channel, column = activation row (pixel).  Each 32 x 32 chunk is turned around
+        // through a padded shared-memory tile so that a lane owns a pixel again and the NCHW stores (and
+        // residual loads) of a warp are 128 contiguous bytes per channel, as in the unswapped form.
+        float* tbuf = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + ew * (32 * 33);
+        const int oc0 = row0;  // first output channel of this warp's 32 lanes
         const long long hw = (p.conv_ks > 0) ? static_cast<long long>(p.conv_h) * p.conv_w : static_cast<long long>(p.ohw);
 #pragma unroll 1
         for (int ci = 0; ci < (BN / 32) / 2; ++ci) {
           const int c0 = (half * (BN / 64) + ci) * 32;
           const int r0 = tn * BN + c0;
-          if (r0 >= p.m) break;  // warp-uniform
+          if (r0 >= p.m || oc0 >= p.n) break;  // warp-uniform
           float v[32];
           tmem_ld_32x32(taddr0 + c0, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tbuf[j * 33 + lane] = v[j];  // [pixel][channel]
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = tbuf[lane * 33 + j];  // lane = pixel r0 + lane, j = channel oc0 + j
+          __syncwarp();
           const int prow = r0 + lane;
           bool pv = prow < p.m;
           long long pbase = 0;
@@ -279,23 +286,19 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.activation);
           }
-          const unsigned valid_mask = __ballot_sync(0xffffffffu, pv);
-          const long long mine = static_cast<long long>(oc) * hw;
-          const bool oc_ok = oc < p.n;
-          if (p.residual != nullptr) {
-            float q[32];
+          if (pv) {
+            const long long o0 = pbase + static_cast<long long>(oc0) * hw;
+            const bool full = oc0 + 32 <= p.n;
+            if (p.residual != nullptr) {
+              float q[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const long long o = __shfl_sync(0xffffffffu, pbase, j) + mine;
-              q[j] = (oc_ok && ((valid_mask >> j) & 1u)) ? __ldg(p.residual + o) : 0.0f;
+              for (int j = 0; j < 32; ++j) q[j] = (full || oc0 + j < p.n) ? __ldg(p.residual + o0 + j * hw) : 0.0f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += q[j];
             }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += q[j];
-          }
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const long long o = __shfl_sync(0xffffffffu, pbase, j) + mine;
-            if (oc_ok && ((valid_mask >> j) & 1u)) p.out_f32[o] = v[j];
+            for (int j = 0; j < 32; ++j)
+              if (full || oc0 + j < p.n) p.out_f32[o0 + j * hw] = v[j];
           }
         }
         tcgen05_fence_before();
@@ -560,11 +563,8 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   // form, whose epilogue writes NCHW with coalesced stores
   const char* noswap = getenv("MIMIR_B200_GEMM_NOSWAP");
   const int kblocks_all = conv ? g.conv_ks * g.conv_ks * (g.conv_c / BK) : kp / BK;
-  // (the swapped epilogue stores one channel per lane, 4 bytes per sector and instruction: it hides behind a long
-  // main loop or when only a few channels exist; measured on 128 -> 128 channels, K = 1152, it loses)
-  const bool swap = (conv || g.out_nchw_hw > 0) && g.bias == nullptr && g.out_split == nullptr && g.out_f32 != nullptr &&
-                    g.m >= 4 * BN && (g.n <= 32 ? kblocks_all * BK >= 256 : (g.n <= BM && kblocks_all * BK >= 2048)) &&
-                    !(noswap && noswap[0] == '1');
+  const bool swap = (conv || g.out_nchw_hw > 0) && g.n <= BM && g.bias == nullptr && g.out_split == nullptr && g.out_f32 != nullptr &&
+                    g.m >= 4 * BN && kblocks_all * BK >= 256 && !(noswap && noswap[0] == '1');
   MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, conv ? g.conv_c : kp, BK, swap ? BN : BM));
   MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : BN));
   GemmParams p;
@@ -596,7 +596,7 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.ohw = g.out_nchw_hw;
   p.err_word = ctx().dev_error_word;
   constexpr int STAGE_BYTES = 2 * BM * BK * 2 + 2 * BN * BK * 2;
-  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ ;
+  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_WARPS * 32 * 33 * 4 /*swapped-epilogue tiles*/;
   static_assert(SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   auto kern = gemm_tn_bf16split_kernel<BK, STAGES>;
   static bool attr_set = false;
