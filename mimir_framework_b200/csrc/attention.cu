@@ -149,69 +149,106 @@ flash_attn_fp32_kernel(const AttnView a, float* __restrict__ out, int embed, int
   }
 }
 
-// Any head dimension: one CTA per (sample, head, query row); the score row lives in shared memory.
+// Any head dimension: one CTA per (sample, head, group of AR query rows); the score rows live in shared memory.
+// Every K and V row is read once per group (a warp per key computes the AR dot products; a thread per output
+// column accumulates the AR weighted sums), which cuts the L2 traffic of the one-row form by AR.
+constexpr int AR = 8;
+
 __global__ void attn_row_kernel(const AttnView a, float* __restrict__ out, int embed, int heads, int hd, int causal, float scale) {
   extern __shared__ __align__(16) float sm[];
-  float* q = sm;         // [hd]
-  float* p = sm + hd;    // [kv_len]
-  __shared__ float red[33];
-  const int i = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  float* q = sm;               // [AR][hd]
+  float* p = sm + AR * hd;     // [AR][kv_len]
+  __shared__ float red[AR][33];
+  const int i0 = blockIdx.x * AR, h = blockIdx.y, b = blockIdx.z;
   const int seq = a.q_len, kvn = a.kv_len;
+  const int nr = min(AR, seq - i0);  // query rows of this group
   const long long ld = a.ldkv;
-  const float* qrow = a.q + (static_cast<long long>(b) * seq + i) * a.ldq + h * hd;
   const float* kb = a.k + static_cast<long long>(b) * kvn * ld + h * hd;
   const float* vb = a.v + static_cast<long long>(b) * kvn * ld + h * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) q[d] = qrow[d];
+  for (int t = threadIdx.x; t < AR * hd; t += blockDim.x) {
+    const int r = t / hd, d = t - r * hd;
+    q[t] = (r < nr) ? a.q[(static_cast<long long>(b) * seq + i0 + r) * a.ldq + h * hd + d] : 0.0f;
+  }
   __syncthreads();
-  const int n_keys = causal ? min(i + 1, kvn) : kvn;
+  // keys this group can see: row i0 + r sees min(i0 + r + 1, kvn) of them under the causal mask
+  const int n_keys = causal ? min(i0 + nr, kvn) : kvn;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  float mx = -1e30f;
+  float mx[AR];
+#pragma unroll
+  for (int r = 0; r < AR; ++r) mx[r] = -1e30f;
   for (int j = w; j < n_keys; j += nw) {  // one warp per key: coalesced reads of the K row
     const float* kr = kb + j * ld;
-    float dot = 0.0f;
-    for (int d = lane; d < hd; d += 32) dot += q[d] * __ldg(kr + d);
+    float dot[AR];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float s = dot * scale;
-    if (lane == 0) p[j] = s;
-    mx = fmaxf(mx, s);
+    for (int r = 0; r < AR; ++r) dot[r] = 0.0f;
+    for (int d = lane; d < hd; d += 32) {
+      const float kv = __ldg(kr + d);
+#pragma unroll
+      for (int r = 0; r < AR; ++r) dot[r] += q[r * hd + d] * kv;
+    }
+#pragma unroll
+    for (int r = 0; r < AR; ++r) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], o);
+      const bool visible = !causal || j <= i0 + r;
+      const float s = dot[r] * scale;
+      if (lane == 0) p[r * kvn + j] = visible ? s : -INFINITY;  // exp(-inf - max) = 0, like the reference's -1e9
+      if (visible) mx[r] = fmaxf(mx[r], s);
+    }
   }
-  // block max
+  // block max per row
   __syncthreads();
-  if (lane == 0) red[w] = mx;
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < AR; ++r) red[r][w] = mx[r];
+  }
   __syncthreads();
-  if (w == 0) {
-    float t = (lane < nw) ? red[lane] : -1e30f;
+  if (w < AR) {
+    float t = (lane < nw) ? red[w][lane] : -1e30f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
-    if (lane == 0) red[32] = t;
+    if (lane == 0) red[w][32] = t;
   }
   __syncthreads();
-  mx = red[32];
-  float acc = 0.0f;
-  for (int j = threadIdx.x; j < n_keys; j += blockDim.x) {
-    const float e = expf(p[j] - mx);
-    p[j] = e;
-    acc += e;
-  }
+  float acc[AR];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  for (int r = 0; r < AR; ++r) {
+    acc[r] = 0.0f;
+    const float m = red[r][32];
+    for (int j = threadIdx.x; j < n_keys; j += blockDim.x) {
+      const float e = expf(p[r * kvn + j] - m);
+      p[r * kvn + j] = e;
+      acc[r] += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+  }
   __syncthreads();
-  if (lane == 0) red[w] = acc;
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < AR; ++r) red[r][w] = acc[r];
+  }
   __syncthreads();
-  if (w == 0) {
-    float t = (lane < nw) ? red[lane] : 0.0f;
+  if (w < AR) {
+    float t = (lane < nw) ? red[w][lane] : 0.0f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (lane == 0) red[32] = t;
+    if (lane == 0) red[w][32] = t;
   }
   __syncthreads();
-  const float inv = 1.0f / (red[32] + 1e-9f);
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     const float* vr = vb + d;
-    float o = 0.0f;
-    for (int j = 0; j < n_keys; ++j) o += p[j] * __ldg(vr + j * ld);
-    out[(static_cast<long long>(b) * seq + i) * embed + h * hd + d] = o * inv;
+    float o[AR];
+#pragma unroll
+    for (int r = 0; r < AR; ++r) o[r] = 0.0f;
+    for (int j = 0; j < n_keys; ++j) {
+      const float v = __ldg(vr + j * ld);
+#pragma unroll
+      for (int r = 0; r < AR; ++r) o[r] += p[r * kvn + j] * v;
+    }
+#pragma unroll
+    for (int r = 0; r < AR; ++r)
+      if (r < nr) out[(static_cast<long long>(b) * seq + i0 + r) * embed + h * hd + d] = o[r] * (1.0f / (red[r][32] + 1e-9f));
   }
 }
 
@@ -242,7 +279,7 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
   if (aligned && hd == 32) return launch_flash<32>(a, out, batch, embed, heads, causal, scale, st);
   if (aligned && hd == 64) return launch_flash<64>(a, out, batch, embed, heads, causal, scale, st);
   if (aligned && hd == 128) return launch_flash<128>(a, out, batch, embed, heads, causal, scale, st);
-  const size_t smem = static_cast<size_t>(hd + a.kv_len) * 4;
+  const size_t smem = static_cast<size_t>(AR) * (hd + a.kv_len) * 4;
   if (smem > 200 * 1024 || batch > 65535 || heads > 65535)
     return fail(MIMIR_B200_E_UNSUPPORTED, "attention: %d keys with head_dim %d exceed the row kernel's shared memory", a.kv_len, hd);
   static size_t attr_bytes = 0;
@@ -250,7 +287,7 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
     MB_CUDA(cudaFuncSetAttribute(attn_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     attr_bytes = smem;
   }
-  dim3 grid(a.q_len, heads, batch);
+  dim3 grid((a.q_len + AR - 1) / AR, heads, batch);
   attn_row_kernel<<<grid, 256, smem, st>>>(a, out, embed, heads, hd, causal, scale);
   MB_CUDA(cudaGetLastError());
   count_launch();
