@@ -604,8 +604,10 @@ int launch_sweep_rows(const RowParams& p, cudaStream_t st) {
   return MIMIR_B200_OK;
 }
 
-// The sweeps pay off when every SM has rows of its own and the rows in flight (re-read from L2)
-// stay well inside L2; otherwise the chunk path (L2-sized row groups) is used.
+// The sweeps pay off when every SM has rows of its own.  They are at their best when the rows in flight
+// stay inside L2 (the second sweep then never touches HBM), but measured on 1 MB rows (GroupNorm over
+// 4 x 256 x 256 slabs, 148 MB in flight) they still beat the chunk path's many short launches, so only
+// very long rows go to the chunk path (L2-sized row groups).
 // MIMIR_B200_NORM_PATH=sweep|chunk overrides the choice (measurement aid).
 inline bool use_sweeps(long long rows, long long len) {
   const char* v = getenv("MIMIR_B200_NORM_PATH");
@@ -613,7 +615,7 @@ inline bool use_sweeps(long long rows, long long len) {
   if (v && v[0] == 'c') return false;
   const long long sms = ctx().sm_count;
   const long long in_flight = (rows < sms ? rows : sms) * len * 4;
-  return rows >= sms && in_flight <= (72ll << 20);
+  return rows >= sms && in_flight <= (1024ll << 20);
 }
 
 // ---- warp-per-row LayerNorm for short rows (token-wise norms): no block barrier at all --------
