@@ -193,6 +193,8 @@ bool conv_uses_shifted(int ic, int ks, int stride, int pad) {
   return stride == 1 && (ks & 1) == 1 && pad == ks / 2 && ic % 32 == 0 && ks <= 7;
 }
 
+size_t conv_prenorm_bytes(int batch, int groups) { return align256(static_cast<size_t>(batch) * groups * 2 * sizeof(float)); }
+
 size_t conv_ws_bytes(int batch, int ic, int h, int w, int ks, int stride, int pad, int precision) {
   int ap, wp;
   precision_planes(precision, &ap, &wp);
@@ -214,7 +216,14 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
     // NCHW fp32 -> zero-padded NHWC planes, then one GEMM that walks the taps as shifted row offsets
     const long long rows = static_cast<long long>(e.batch) * (e.h + 2 * e.pad) * (e.w + 2 * e.pad);
     if (rows > 0x7fffffffLL) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: batch too large for one launch");
-    MB_TRY(launch_nchw_to_padded_nhwc_split(e.x, static_cast<__nv_bfloat16*>(e.ws), e.batch, e.ic, e.h, e.w, e.pad, ap, st));
+    PreNorm pre;
+    if (e.pre_groups > 0) {
+      // statistics live behind the operand planes in the workspace
+      float* stats = reinterpret_cast<float*>(static_cast<uint8_t*>(e.ws) + align256(static_cast<size_t>(ap) * rows * e.ic * sizeof(__nv_bfloat16)));
+      MB_TRY(launch_groupnorm_stats(e.x, stats, e.batch, e.ic, e.h * e.w, e.pre_groups, e.pre_eps, st));
+      pre.stats = stats; pre.gamma = e.pre_gamma; pre.beta = e.pre_gamma ? e.pre_beta : nullptr; pre.groups = e.pre_groups; pre.act = e.pre_act;
+    }
+    MB_TRY(launch_nchw_to_padded_nhwc_split(e.x, static_cast<__nv_bfloat16*>(e.ws), e.batch, e.ic, e.h, e.w, e.pad, ap, st, pre));
     GemmArgs g;
     g.a = static_cast<const __nv_bfloat16*>(e.ws);
     g.w = e.w_split;

@@ -125,6 +125,8 @@ int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y
 int launch_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int batch, int ch, int hw,
                      int groups, float eps, int act, const float* residual, cudaStream_t st);
 int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softmax, cudaStream_t st);
+// stats[(sample * groups + g) * 2 + {0, 1}] = mean, 1 / sqrt(var + eps) of each GroupNorm slab
+int launch_groupnorm_stats(const float* x, float* stats, int batch, int ch, int hw, int groups, float eps, cudaStream_t st);
 
 // attention.cu ---------------------------------------------------------------------------------
 // Where the projected queries, keys and values of one attention call live: row-major fp32, sample b at
@@ -152,8 +154,17 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
 int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, int h, int w, int ks, int stride,
                         int pad, int oh, int ow, int planes, cudaStream_t st);
 // NCHW fp32 -> zero-padded NHWC planes [planes][batch*(h+2p)*(w+2p)][c] (borders written as zero)
+// A GroupNorm (+ SiLU) whose only consumer is the convolution can be applied on the way: `pre` carries its
+// statistics and affine parameters.
+struct PreNorm {
+  const float* stats = nullptr;  // [batch][groups][2] from launch_groupnorm_stats; null = no normalisation
+  const float* gamma = nullptr;
+  const float* beta = nullptr;
+  int groups = 1;
+  int act = -1;                  // -1 or MIMIR_B200_ELT_SILU
+};
 int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int batch, int c, int h, int w, int pad, int planes,
-                                     cudaStream_t st);
+                                     cudaStream_t st, const PreNorm& pre = PreNorm());
 // OIHW fp32 -> planes [planes][oc][round_up(ks*ks*ic, 64)] with K ordered (kh, kw, ic)
 int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st);
 

@@ -82,7 +82,8 @@ namespace {
 constexpr int TP_C = 64, TP_X = 64;
 
 __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
-                                                                  int c, int h, int w, int pad, int planes, long long plane_stride) {
+                                                                  int c, int h, int w, int pad, int planes, long long plane_stride,
+                                                                  const PreNorm pre) {
   __shared__ float tile[TP_C][TP_X + 1];
   const int hp = h + 2 * pad, wp = w + 2 * pad;
   const int cb = blockIdx.x * TP_C;
@@ -93,6 +94,24 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* _
   const bool row_in = y >= 0 && y < h;
   const float* src = x + ((static_cast<long long>(n) * c + cb) * h + (row_in ? y : 0)) * w;
   const long long ch_stride = static_cast<long long>(h) * w;
+  // this thread's 16 elements of a tile belong to 16 fixed channels: their scale / shift once per CTA
+  float sc[16], sh[16];
+  if (pre.stats != nullptr) {
+    const int cpg = c / pre.groups;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int ch = cb + ((threadIdx.x + 256 * i) >> 6);
+      sc[i] = 0.0f; sh[i] = 0.0f;
+      if (ch < c) {
+        const float* st = pre.stats + (static_cast<long long>(n) * pre.groups + ch / cpg) * 2;
+        const float mean = __ldg(st), inv = __ldg(st + 1);
+        const float g = pre.gamma != nullptr ? __ldg(pre.gamma + ch) : 1.0f;
+        const float b = (pre.gamma != nullptr && pre.beta != nullptr) ? __ldg(pre.beta + ch) : 0.0f;
+        sc[i] = inv * g;
+        sh[i] = b - mean * inv * g;
+      }
+    }
+  }
   for (int x0 = 0; x0 < wp; x0 += TP_X) {
     // tile[cc][xx] = x[n, cb + cc, y, x0 + xx - pad]; a warp reads 32 consecutive pixels of one channel
     float v[16];
@@ -102,6 +121,18 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* _
       const int cc = idx >> 6, xx = idx & 63;
       const int xs = x0 + xx - pad;
       v[i] = (row_in && xs >= 0 && xs < w && cb + cc < c) ? __ldg(src + cc * ch_stride + xs) : 0.0f;
+    }
+    if (pre.stats != nullptr) {
+      // GroupNorm (+ SiLU) of the producer applied here; the zero padding ring stays zero
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int xs = x0 + ((threadIdx.x + 256 * i) & 63) - pad;
+        if (row_in && xs >= 0 && xs < w) {  // (channels past c are never stored)
+          float r = fmaf(v[i], sc[i], sh[i]);
+          if (pre.act == MIMIR_B200_ELT_SILU) r = r * __fdividef(1.0f, 1.0f + __expf(-r));
+          v[i] = r;
+        }
+      }
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -153,12 +184,13 @@ __global__ void conv_weight_planes_kernel(const float* __restrict__ w, __nv_bflo
 }  // namespace
 
 int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int batch, int c, int h, int w, int pad, int planes,
-                                     cudaStream_t st) {
+                                     cudaStream_t st, const PreNorm& pre) {
   if (batch <= 0 || c <= 0 || h <= 0 || w <= 0 || pad < 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad activation shape");
   const int hp = h + 2 * pad, wp = w + 2 * pad;
   if (hp > 65535 || batch > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: image too tall for the layout kernel");
   dim3 grid((c + TP_C - 1) / TP_C, hp, batch);
-  nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, static_cast<long long>(batch) * hp * wp * c);
+  if (pre.stats != nullptr && (pre.groups <= 0 || c % pre.groups != 0)) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad fused GroupNorm");
+  nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, static_cast<long long>(batch) * hp * wp * c, pre);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;

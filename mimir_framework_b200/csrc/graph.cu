@@ -78,6 +78,7 @@ TypeInfo classify(const std::string& t) {
   if (t == "ConvTranspose2d") return {LT::ConvTranspose2d, -1};
   if (t == "MaxPool2d") return {LT::Pool2d, 1};
   if (t == "AvgPool2d") return {LT::Pool2d, 0};
+  if (t == "AvgPool1d") return {LT::Pool2d, 2};  // one row per channel (LayerOpsExt.hpp:540-575)
   if (t == "ZeroPad2d") return {LT::Pad2d, 0};
   if (t == "ReflectionPad2d") return {LT::Pad2d, 1};
   if (t == "ReplicationPad2d") return {LT::Pad2d, 2};
@@ -122,6 +123,7 @@ struct LayerRT {
   bool emit_f32 = true;
   bool read_split = false;            // Linear reads the producer's planes
   int res_v = -1;                     // residual tensor folded in from a following Add
+  int pre_norm = -1;                  // Conv2d: index of the GroupNorm layer applied while its operand planes are laid out
   size_t ws_off = 0, ws_bytes = 0;
   // resolved shapes (per sample)
   int rows_ps = 1, in_f = 0, out_f = 0;       // Linear
@@ -557,6 +559,18 @@ int infer_layer(LayerRT& L, const std::vector<int64_t>& in_n, int64_t* out_n) {
       return MIMIR_B200_OK;
     }
     case LT::Pool2d: {
+      if (L.act_of_type == 2) {  // AvgPool1d: raw kernel_h (default 2), raw stride_h (default = kernel), raw pad_h
+        L.ch = d.in_channels > 0 ? d.in_channels : 1;
+        if (n0 % L.ch != 0) return fail(MIMIR_B200_E_INVALID, "AvgPool1d (%s): input size is not a multiple of in_channels", L.name.c_str());
+        L.h = 1; L.w = static_cast<int>(n0 / L.ch);
+        L.kk = 1; L.kw = d.raw_kernel_h > 0 ? d.raw_kernel_h : 2;
+        L.st = 1; L.sw = d.raw_stride_h > 0 ? d.raw_stride_h : L.kw;
+        L.pd = 0; L.pw = d.raw_pad_h >= 0 ? d.raw_pad_h : 0;
+        L.oh = 1; L.ow = (L.w + 2 * L.pw - L.kw) / L.sw + 1;
+        if (L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "AvgPool1d (%s): empty output", L.name.c_str());
+        *out_n = static_cast<int64_t>(L.ch) * L.ow;
+        return MIMIR_B200_OK;
+      }
       const bool is_max = L.act_of_type == 1;
       L.ch = d.in_channels > 0 ? d.in_channels : 64;
       L.h = d.input_height > 0 ? d.input_height : (is_max ? 64 : 32);  // Model.cpp:5511-5512 vs LayerOps.hpp:416-417
@@ -684,7 +698,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     LayerRT& L = m->layers[li];
     L.in_v.clear();
     L.out_v = -1;
-    L.skip = false; L.fused_act = -1; L.emit_split = false; L.emit_f32 = true; L.read_split = false; L.res_v = -1;
+    L.skip = false; L.fused_act = -1; L.emit_split = false; L.emit_f32 = true; L.read_split = false; L.res_v = -1; L.pre_norm = -1;
     L.ws_off = 0; L.ws_bytes = 0;
     std::vector<std::string> names = L.inputs;
     if (names.empty()) names.push_back("x");
@@ -786,6 +800,34 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
       break;
     }
   }
+  // ---- fusion 1c: GroupNorm (+ SiLU) whose only consumer is a shifted-GEMM convolution: the convolution's layout
+  //      kernel normalises on the fly from per-slab statistics, the normalised tensor never exists in memory ----
+  // (off unless MIMIR_B200_FUSE_GN_CONV=1: it removes a full write + read of the normalised tensor, but measured on
+  // the UNet configuration the layout kernel with the normalisation inside costs more than the streaming
+  // GroupNorm sweep it replaces - 8.6 vs 8.2 ms per step - so it waits for a faster layout kernel)
+  const char* fuse_gn_env = getenv("MIMIR_B200_FUSE_GN_CONV");
+  const bool fuse_gn = fuse_gn_env && fuse_gn_env[0] == '1';
+  for (int li = 0; li < nl && fuse_gn; ++li) {
+    LayerRT& P = m->layers[li];
+    if (P.lt != LT::GroupNorm || P.skip || P.res_v >= 0) continue;
+    if (P.fused_act >= 0 && P.fused_act != MIMIR_B200_ELT_SILU) continue;
+    const int pv = P.out_v;
+    TensorV& pt = m->tensors[pv];
+    if (pt.alias_of >= 0 || pv == out_root || total_consumers(pv) != 1 || pt.consumers.size() != 1) continue;
+    LayerRT& C = m->layers[pt.consumers[0]];
+    if (C.lt != LT::Conv2d || C.skip || C.pre_norm >= 0 || C.in_v[0] != pv) continue;
+    if (!conv_uses_shifted(C.d.in_channels, C.d.kernel, C.d.stride, C.d.padding)) continue;
+    if (C.d.in_channels != P.ch || C.h != P.h || C.w != P.w) continue;
+    const int xin = P.in_v[0];
+    C.pre_norm = li;
+    C.in_v[0] = xin;
+    for (int& c : m->tensors[xin].consumers)
+      if (c == li) c = pt.consumers[0];
+    pt.consumers.clear();
+    pt.want_f32 = false;
+    pt.producer = -2;  // dead
+    P.skip = true;
+  }
   // ---- fusion 2: hi/lo planes straight from one GEMM epilogue into the next Linear -------------
   for (int li = 0; li < nl; ++li) {
     LayerRT& C = m->layers[li];
@@ -868,6 +910,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
         case LT::Conv2d: {
           const int k = L.d.in_channels * L.d.kernel * L.d.kernel;
           L.ws_bytes = conv_ws_bytes(batch, L.d.in_channels, L.h, L.w, L.d.kernel, L.d.stride, L.d.padding, m->precision);
+          if (L.pre_norm >= 0) L.ws_bytes += conv_prenorm_bytes(batch, m->layers[L.pre_norm].d.num_groups);
           flops += 2ull * batch * L.oh * L.ow * k * L.d.out_channels;
           break;
         }
@@ -970,6 +1013,14 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.activation = d.activation ? MIMIR_B200_ELT_RELU : L.fused_act;
         e.x = f32p(L.in_v[0]); e.w_split = L.w_split; e.y = f32p(L.out_v); e.ws = ws;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
+        if (L.pre_norm >= 0) {
+          const LayerRT& G = m->layers[L.pre_norm];
+          e.pre_groups = G.d.num_groups;
+          e.pre_gamma = G.d.affine ? G.w_f32 : nullptr;
+          e.pre_beta = (G.d.affine && G.d.use_bias) ? G.w_f32 + G.ch : nullptr;
+          e.pre_eps = G.d.eps;
+          e.pre_act = G.fused_act;
+        }
         s = conv_exec(e, st);
         break;
       }
@@ -1067,7 +1118,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
                                d.kernel, d.stride, d.padding, d.activation != 0, st);
         break;
       case LT::Pool2d:
-        s = launch_pool2d(L.act_of_type, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.kk, L.kw, L.st, L.sw, L.pd, L.pw, st);
+        s = launch_pool2d(L.act_of_type == 1 ? 1 : 0, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.kk, L.kw, L.st, L.sw, L.pd, L.pw, st);
         break;
       case LT::Pad2d:
         s = launch_pad2d(L.act_of_type, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.pd, L.pw, st);

@@ -358,6 +358,7 @@ struct RowParams {
   const float* gamma;    // FAM_RMS
   long long n_gamma;     // FAM_RMS
   int log_softmax;       // FAM_SOFTMAX
+  float* stats_out;      // FAM_MEANVAR: when set, only (mean, 1/std) of every row is written, no output sweep
 };
 
 __device__ __forceinline__ float silu_fast(float v) { return v * __fdividef(1.0f, 1.0f + __expf(-v)); }
@@ -528,6 +529,13 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 512) ? 2 : 1) sweep_row_k
         m2 = block_sum(qc, red);
       }
       const float inv = 1.0f / sqrtf(fmaxf(m2, 0.0f) / fn + p.eps);
+      if (p.stats_out != nullptr) {
+        if (threadIdx.x == 0) {
+          p.stats_out[2 * row] = mean;
+          p.stats_out[2 * row + 1] = inv;
+        }
+        continue;
+      }
       meanvar_write_row(g, o, n, vec, mean, inv, row, base, p.aff);
     } else if (FAM == FAM_RMS) {
       float q = 0.0f;
@@ -759,6 +767,20 @@ int launch_groupnorm(const float* x, const float* gamma, const float* beta, floa
   const int cpg = ch / groups;
   Affine a{gamma, gamma ? beta : nullptr, 1, groups, cpg, hw, act, residual};
   return meanvar_dispatch(x, y, static_cast<long long>(batch) * groups, static_cast<long long>(cpg) * hw, eps, a, st);
+}
+
+// (mean, 1 / sqrt(var + eps)) of every (sample, group) slab, for consumers that normalise on the fly
+int launch_groupnorm_stats(const float* x, float* stats, int batch, int ch, int hw, int groups, float eps, cudaStream_t st) {
+  if (groups <= 0 || ch % groups != 0) return fail(MIMIR_B200_E_INVALID, "GroupNorm: channels must be divisible by num_groups");
+  RowParams p{};
+  p.x = x;
+  p.y = const_cast<float*>(x);  // never written on this path
+  p.rows = static_cast<long long>(batch) * groups;
+  p.len = static_cast<long long>(ch / groups) * hw;
+  p.eps = eps;
+  p.aff = Affine{nullptr, nullptr, 1, groups, ch / groups, hw, -1, nullptr};
+  p.stats_out = stats;
+  return launch_sweep_rows<FAM_MEANVAR>(p, st);
 }
 
 int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y, int batch, int64_t n, float eps,

@@ -70,7 +70,15 @@ struct ConvExec {
   const float* residual = nullptr;             // NCHW, same shape as y
   float* y = nullptr;
   void* ws = nullptr;
+  // GroupNorm (+ SiLU) of the producing layer, applied while the operand planes are laid out (shifted path only):
+  // x is then the GroupNorm's INPUT
+  int pre_groups = 0;                          // > 0 switches it on
+  const float* pre_gamma = nullptr;
+  const float* pre_beta = nullptr;
+  float pre_eps = 1e-5f;
+  int pre_act = -1;
 };
+size_t conv_prenorm_bytes(int batch, int groups);
 // stride-1 "same" convolutions with a channel count that is a multiple of 32 run as shifted GEMMs over the
 // padded NHWC activation; everything else goes through im2col planes.  The two paths want different
 // weight-plane orders ((kh, kw, ic) vs (ic, kh, kw)).

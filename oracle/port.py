@@ -362,6 +362,12 @@ def run_layer(d, ins, w):
     if t == "AvgPool2d":
         return pool2d(0, x, _dflt(d.in_channels, 64), _dflt(d.input_height, 32), _dflt(d.input_width, 32), d.kernel,
                       _dflt(d.kernel_w, d.kernel), d.stride, _dflt(d.stride_w, d.stride), d.padding, d.padding_w)
+    if t == "AvgPool1d":  # LayerOpsExt.hpp:540-575: per channel over the length, mean of the in-bounds taps
+        ch = _dflt(d.in_channels, 1)
+        k = _dflt(d.raw_kernel_h, 2)
+        st = d.raw_stride_h if d.raw_stride_h > 0 else k
+        pad = d.raw_pad_h if d.raw_pad_h >= 0 else 0
+        return pool2d(0, x, ch, 1, x.size // ch, 1, k, 1, st, 0, pad)
     if t in ("ZeroPad2d", "ReflectionPad2d", "ReplicationPad2d"):
         mode = ("ZeroPad2d", "ReflectionPad2d", "ReplicationPad2d").index(t)
         ph = d.raw_pad_h if d.raw_pad_h >= 0 else 1

@@ -105,6 +105,7 @@ def cases():
     add("reparameterize_inference", [make_desc("r", "Reparameterize", inputs=["x", "lv"])], [None], {"x": f(20), "lv": f(20)})
     add("squeeze_unsqueeze", [make_desc("a", "Squeeze"), make_desc("b", "Unsqueeze")], [None, None], {"x": f(12)})
     add("stack2", [make_desc("s", "Stack", inputs=["x", "y"])], [None], {"x": f(7), "y": f(7)})
+    add("avgpool1d_k3s2p1", [make_desc("p", "AvgPool1d", in_channels=3, raw_kernel_h=3, raw_stride_h=2, raw_pad_h=1)], [None], {"x": f(3 * 17)})
     return out
 
 

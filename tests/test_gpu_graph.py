@@ -318,3 +318,32 @@ def test_repeated_forwards_replay_a_cuda_graph_with_identical_results(backend):
         got = m.forward(half, 2, 8)
     assert_close(got, oracle_batch(descs, weights, half, 2), "transformer, re-planned")
     m.close()
+
+
+@pytest.mark.parametrize("shared_output,fuse", [(False, "0"), (False, "1"), (True, "1")])
+def test_groupnorm_silu_applied_inside_the_convolution(backend, monkeypatch, shared_output, fuse):
+    """UNet-style ResBlock: GroupNorm -> SiLU -> Conv3x3 -> GroupNorm -> SiLU -> Conv3x3 + skip.  With
+    MIMIR_B200_FUSE_GN_CONV=1 a GroupNorm whose output feeds nothing but the convolution is folded into the
+    convolution's layout kernel (statistics pass + normalise on the fly); with a second consumer of the normalised
+    tensor it must stay a layer of its own."""
+    monkeypatch.setenv("MIMIR_B200_FUSE_GN_CONV", fuse)
+    ch, hw, batch, groups = 64, 10, 3, 8
+    gn = dict(in_channels=ch, input_height=hw, input_width=hw, num_groups=groups, params_count=2 * ch)
+    cv = dict(in_channels=ch, out_channels=ch, input_height=hw, input_width=hw, kernel=3, stride=1, padding=1, params_count=ch * ch * 9)
+    descs = [
+        make_desc("gn1", "GroupNorm", inputs=["x"], output="n1", **gn),
+        make_desc("act1", "SiLU", inputs=["n1"], output="a1"),
+        make_desc("conv1", "Conv2d", inputs=["a1"], output="c1", **cv),
+        make_desc("gn2", "GroupNorm", inputs=["c1"], output="n2", **gn),
+        make_desc("act2", "SiLU", inputs=["n2"], output="a2"),
+        make_desc("conv2", "Conv2d", inputs=["a2"], output="c2", **cv),
+        make_desc("add", "Add", inputs=["c2", "a1" if shared_output else "__input__"], output="x"),
+    ]
+    r = np.random.default_rng(12)
+    gw = lambda: np.concatenate([1 + 0.2 * r.standard_normal(ch), 0.1 * r.standard_normal(ch)]).astype(np.float32)  # noqa: E731
+    cw = lambda: (r.standard_normal(ch * ch * 9) * np.sqrt(2 / (ch * 9))).astype(np.float32)  # noqa: E731
+    weights = [gw(), None, cw(), gw(), None, cw(), None]
+    x = (r.standard_normal((batch, ch * hw * hw)) * 1.5 + 0.3).astype(np.float32)
+    inputs = {"x": (x.ravel(), False)}
+    assert_close(gpu_batch(backend, descs, weights, inputs, batch, ch * hw * hw), oracle_batch(descs, weights, inputs, batch),
+                 f"resblock, shared={shared_output}")
