@@ -150,7 +150,8 @@ def desc_array(descs) -> C.Array:
 
 
 def library_path() -> str:
-    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmimir_b200.so")
+    """The in-tree build; MIMIR_B200_LIB points at another build of the same library (A/B measurements)."""
+    return os.environ.get("MIMIR_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "libmimir_b200.so")
 
 
 _lib = None
