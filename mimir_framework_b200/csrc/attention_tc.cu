@@ -42,7 +42,10 @@ constexpr int AT_P_BYTES = AT_BQ * AT_BK * 2;
 constexpr int AT_SMEM = 2 * AT_Q_BYTES + 2 * AT_K_BYTES + 2 * AT_V_BYTES + 2 * AT_P_BYTES + 256 + 1024;
 
 struct AttnParams {
-  float* out;        // fp32 [batch*seq][embed]
+  float* out;        // fp32 [batch*seq][embed], or nullptr
+  __nv_bfloat16* out_split;  // or: bf16 hi (+ lo) operand planes [planes][batch*seq][embed] for the output projection
+  long long plane_stride;
+  int planes;
   int seq, embed, heads, causal;
   int bh;            // batch * heads
   float scale;
@@ -322,18 +325,39 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tcgen05_fence_after();
       const float inv = 1.0f / (l_run + 1e-9f);  // LayerOps.hpp:1076
       const int bb = bhi / p.heads, h = bhi - bb * p.heads;
-      float* o = p.out + (static_cast<long long>(bb) * p.seq + row) * p.embed + h * AT_HD;
+      const long long o_off = (static_cast<long long>(bb) * p.seq + row) * p.embed + h * AT_HD;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t v[32];
         tmem_ld_32x32_nowait(tmem_o + lane_base + half * 32, v);  // every lane of the warp takes part in the load
         tmem_wait_ld();
         if (row < p.seq) {
+          if (p.out != nullptr) {
+            float* o = p.out + o_off;
 #pragma unroll
-          for (int c = 0; c < 32; c += 4)
-            *reinterpret_cast<float4*>(o + half * 32 + c) =
-                make_float4(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv, __uint_as_float(v[c + 2]) * inv,
-                            __uint_as_float(v[c + 3]) * inv);
+            for (int c = 0; c < 32; c += 4)
+              *reinterpret_cast<float4*>(o + half * 32 + c) =
+                  make_float4(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv, __uint_as_float(v[c + 2]) * inv,
+                              __uint_as_float(v[c + 3]) * inv);
+          }
+          if (p.out_split != nullptr) {
+            __nv_bfloat16* oh = p.out_split + o_off + half * 32;
+#pragma unroll
+            for (int c = 0; c < 32; c += 8) {
+              uint32_t hi[4], lo[4];
+#pragma unroll
+              for (int e = 0; e < 8; e += 2) {
+                const float f0 = __uint_as_float(v[c + e]) * inv, f1 = __uint_as_float(v[c + e + 1]) * inv;
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(f0, f1);
+                const float2 hf = __bfloat1622float2(h2);
+                const __nv_bfloat162 l2 = __floats2bfloat162_rn(f0 - hf.x, f1 - hf.y);
+                hi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
+                lo[e >> 1] = *reinterpret_cast<const uint32_t*>(&l2);
+              }
+              *reinterpret_cast<uint4*>(oh + c) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+              if (p.planes == 2) *reinterpret_cast<uint4*>(oh + p.plane_stride + c) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            }
+          }
         }
       }
     }
@@ -387,7 +411,7 @@ size_t attention_tc_ws_bytes(int batch, int seq, int embed) {
 }
 
 int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, void* ws,
-                             cudaStream_t st) {
+                             cudaStream_t st, __nv_bfloat16* out_split, int planes) {
   if (!attention_tc_supported(seq, embed, heads)) return fail(MIMIR_B200_E_UNSUPPORTED, "attention: tensor-core core needs head_dim 64");
   const int bh = batch * heads;
   const int seqp = round_up(seq, 64);
@@ -411,6 +435,9 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   }
   AttnParams p;
   p.out = out;
+  p.out_split = out_split;  // embed = heads * 64, so the planes' padded row length equals embed
+  p.plane_stride = static_cast<long long>(batch) * seq * embed;
+  p.planes = planes;
   p.seq = seq; p.embed = embed; p.heads = heads; p.causal = causal; p.bh = bh;
   p.scale = 1.0f / sqrtf(static_cast<float>(AT_HD));
   p.err_word = ctx().dev_error_word;

@@ -159,16 +159,18 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   float* qkv = reinterpret_cast<float*>(ws + align256(split_bytes(rows, e.embed, ap)));
   float* att = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(qkv) + align256(static_cast<size_t>(rows) * 3 * e.embed * 4));
   uint8_t* tc_ws = reinterpret_cast<uint8_t*>(att) + align256(static_cast<size_t>(rows) * e.embed * 4);
-  MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
+  if (!e.x_split) MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
   GemmArgs g;
-  g.a = xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
+  g.a = e.x_split ? e.x_split : xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
   g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
   MB_TRY(launch_gemm(g, st));
-  if (attention_tc_supported(e.seq, e.embed, e.heads))
-    MB_TRY(launch_attention_core_tc(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, tc_ws, st));
-  else
+  // the attended rows go to the output projection as operand planes (the x planes are dead by now)
+  if (attention_tc_supported(e.seq, e.embed, e.heads)) {
+    MB_TRY(launch_attention_core_tc(qkv, nullptr, e.batch, e.seq, e.embed, e.heads, e.causal, tc_ws, st, xs, ap));
+  } else {
     MB_TRY(launch_attention_core(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, st));
-  MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));  // the x planes are dead by now
+    MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));
+  }
   GemmArgs o;
   o.a = xs; o.w = e.wout_split; o.a_planes = ap; o.w_planes = wp;
   o.m = rows; o.n = e.embed; o.k = e.embed; o.out_f32 = e.y; o.ldo = e.embed; o.residual = e.residual;

@@ -120,8 +120,11 @@ int launch_broadcast_rows(const float* src, float* dst, int batch, int64_t n, cu
 // norms.cu -------------------------------------------------------------------------------------
 int launch_layernorm(const float* x, const float* gamma, const float* beta, float* y, int64_t rows, int64_t n,
                      float eps, cudaStream_t st);
+// y_split (optional): the result as bf16 hi (+ lo) operand planes, `plane_stride` elements apart, written by the
+// one-pass kernel; only where rmsnorm_onepass_ok() holds.  y may then be nullptr.
 int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y, int batch, int64_t n, float eps,
-                   cudaStream_t st);
+                   cudaStream_t st, __nv_bfloat16* y_split = nullptr, int planes = 0, int64_t plane_stride = 0);
+bool rmsnorm_onepass_ok(int batch, int64_t n);
 int launch_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int batch, int ch, int hw,
                      int groups, float eps, int act, const float* residual, cudaStream_t st);
 int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softmax, cudaStream_t st);
@@ -147,7 +150,7 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
 bool attention_tc_supported(int seq, int embed, int heads);
 size_t attention_tc_ws_bytes(int batch, int seq, int embed);
 int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, void* ws,
-                             cudaStream_t st);
+                             cudaStream_t st, __nv_bfloat16* out_split = nullptr, int planes = 0);
 
 // conv2d.cu ------------------------------------------------------------------------------------
 // im2col of NCHW fp32 into split planes [planes][batch*oh*ow][kp], k = ic*ks*ks ordered (ic, kh, kw)

@@ -848,6 +848,36 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     t.split_k = P.out_f;
   }
 
+  // ---- fusion 2b: a whole-sample RMSNorm whose only consumer is a tensor-core Linear / attention block writes
+  //      that consumer's operand planes itself (the one-pass kernel holds the values in registers anyway) ----
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& P = m->layers[li];
+    if (P.lt != LT::RMSNorm || P.skip) continue;
+    const int v = P.out_v;
+    TensorV& t = m->tensors[v];
+    if (t.alias_of >= 0 || v == out_root || total_consumers(v) != 1 || t.consumers.size() != 1) continue;
+    if (!rmsnorm_onepass_ok(batch, t.n)) continue;
+    LayerRT& C = m->layers[t.consumers[0]];
+    if (C.skip || C.in_v[0] != v) continue;
+    int k = 0;
+    int64_t rows_ps = 0;
+    if (C.lt == LT::Linear && !linear_uses_skinny(C.rows_ps * batch, m->precision)) {
+      k = C.in_f; rows_ps = C.rows_ps;
+    } else if (C.lt == LT::Attention) {
+      k = C.embed; rows_ps = C.seq;
+    } else {
+      continue;
+    }
+    if (k <= 0 || k % 64 != 0 || rows_ps * k != t.n) continue;
+    P.emit_split = true;
+    P.emit_f32 = false;
+    C.read_split = true;
+    t.want_f32 = false;
+    t.want_split = true;
+    t.split_rows_ps = rows_ps;
+    t.split_k = k;
+  }
+
   // ---- liveness ------------------------------------------------------------------------------------
   const int nt = static_cast<int>(m->tensors.size());
   for (int v = 0; v < nt; ++v) {
@@ -1001,7 +1031,8 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         AttentionExec e;
         e.batch = batch; e.seq = L.seq; e.embed = L.embed; e.heads = L.heads; e.causal = d.causal;
         e.precision = m->precision;
-        e.x = f32p(L.in_v[0]); e.wqkv_split = L.w_split; e.wout_split = L.w_split2; e.y = f32p(L.out_v); e.ws = ws;
+        if (L.read_split) e.x_split = splitp(L.in_v[0]); else e.x = f32p(L.in_v[0]);
+        e.wqkv_split = L.w_split; e.wout_split = L.w_split2; e.y = f32p(L.out_v); e.ws = ws;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
         s = attention_exec(e, st);
         break;
@@ -1033,8 +1064,12 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
       }
       case LT::RMSNorm: {
         const bool aff = d.affine && L.w_f32 && L.w_count > 0;
-        s = launch_rmsnorm(f32p(L.in_v[0]), aff ? L.w_f32 : nullptr, aff ? static_cast<int64_t>(L.w_count) : 0, f32p(L.out_v),
-                           batch, m->tensors[L.in_v[0]].n, d.eps, st);
+        const int64_t n = m->tensors[L.in_v[0]].n;
+        int ap, wp;
+        precision_planes(m->precision, &ap, &wp);
+        s = launch_rmsnorm(f32p(L.in_v[0]), aff ? L.w_f32 : nullptr, aff ? static_cast<int64_t>(L.w_count) : 0,
+                           L.emit_f32 ? f32p(L.out_v) : nullptr, batch, n, d.eps, st, L.emit_split ? splitp(L.out_v) : nullptr, ap,
+                           static_cast<int64_t>(batch) * n);
         break;
       }
       case LT::GroupNorm: {

@@ -12,6 +12,7 @@
 //     partial statistics in a small global scratch, pass 2 combines the partials of its row and
 //     writes the result; rows are processed in groups that fit in L2 so that pass 2 reads from L2.
 #include "common.h"
+#include "sm100_ptx.cuh"
 
 
 namespace mb {
@@ -293,6 +294,233 @@ __global__ void rms_chunk_apply_kernel(const float* __restrict__ x, const float*
       float v = __ldg(g + i) / rms;
       if (gamma != nullptr && off + i < n_gamma) v *= __ldg(gamma + off + i);
       o[i] = v;
+    }
+  }
+}
+
+// ---- RMSNorm over a long sample in ONE pass over HBM ---------------------------------------------
+// One CTA per 8192-element chunk keeps its chunk in registers from the load to the store.  Between
+// the two it needs (1) the sum of squares of the chunks before it in the sample (for the binade of
+// the reference's running sum, see rms_seq_err_kernel) and (2) the sample's total.  Both travel
+// through 64-bit slots {tag, fp32 value} in global memory.  CTAs take their chunk from a ticket
+// counter, so a CTA only ever waits for chunks whose CTAs started before it or belong to its own
+// sample; the launcher only uses this kernel when a whole sample's CTAs are resident at once.
+// Every wait is bounded: after ~2 s (or when another CTA gave up) the CTA reports through the
+// device error word and leaves.
+constexpr int OP_VEC = CHUNK / (256 * 4);  // float4 per thread
+
+struct RmsOnePass {
+  const float* x;
+  const float* gamma;
+  long long n_gamma;
+  float* y;                 // fp32 output, or nullptr
+  __nv_bfloat16* y_split;   // bf16 hi (and lo) planes, or nullptr
+  long long plane_stride;   // elements between the hi and the lo plane
+  int planes;
+  unsigned* ticket;         // [0] ticket counter, [1] abort flag
+  unsigned long long* sum_slots;
+  unsigned long long* err_slots;
+  long long len;
+  int chunks;
+  float eps;
+  int* err_word;
+};
+
+__device__ __forceinline__ unsigned long long slot_pack(float v) {
+  return (1ull << 32) | static_cast<unsigned long long>(__float_as_uint(v));
+}
+// Polls one slot until its tag is set.  Returns false when the wait gave up.
+__device__ __forceinline__ bool slot_wait(const unsigned long long* slot, volatile unsigned* abort_flag, int* err_word, int site,
+                                          float* out) {
+  const volatile unsigned long long* p = slot;
+  unsigned long long v = *p;
+  if ((v >> 32) == 0) {
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    unsigned spins = 0;
+    while (((v = *p) >> 32) == 0) {
+      __nanosleep(64);
+      if ((++spins & 0xFF) == 0) {
+        if (*abort_flag) return false;
+        uint64_t t1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 2000000000ull) {
+          *abort_flag = 1u;
+          atomicExch(err_word, site);
+          return false;
+        }
+      }
+    }
+  }
+  *out = __uint_as_float(static_cast<unsigned>(v & 0xffffffffull));
+  return true;
+}
+__device__ __forceinline__ double block_sum_f64(double v, double* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  double t = 0.0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) t += red[k];
+  return t;
+}
+
+__global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p) {
+  extern __shared__ __align__(128) float sx[];  // the chunk, zero beyond its end
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ unsigned s_id;
+  __shared__ int s_abort;
+  __shared__ float wtab[OP_VEC][8];
+  __shared__ double red[8];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  if (tid == 0) {
+    s_id = atomicAdd(p.ticket, 1u);
+    s_abort = 0;
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const long long row = s_id / static_cast<unsigned>(p.chunks);
+  const int c = static_cast<int>(s_id % static_cast<unsigned>(p.chunks));
+  const long long off = static_cast<long long>(c) * CHUNK;
+  const int n = static_cast<int>(min(static_cast<long long>(CHUNK), p.len - off));
+  const float* g = p.x + row * p.len + off;
+  volatile unsigned* abort_flag = p.ticket + 1;
+
+  // ---- the chunk into shared memory: bulk copies when source and size allow, plain loads otherwise ----
+  const bool bulk = (reinterpret_cast<uintptr_t>(g) & 15) == 0 && (n & 3) == 0;
+  bool ok = true;
+  if (bulk) {
+    if (tid == 0) {
+      mbar_expect_tx(&bar, static_cast<uint32_t>(n) * 4u);
+      for (int b0 = 0; b0 < n; b0 += 2048) bulk_load_1d(sx + b0, g + b0, static_cast<uint32_t>(min(2048, n - b0)) * 4u, &bar);
+    }
+    for (int i = n + tid; i < CHUNK; i += 256) sx[i] = 0.0f;
+    if (!mbar_wait(&bar, 0, &s_abort, p.err_word, 20)) ok = false;
+  } else {
+    for (int i = tid; i < CHUNK; i += 256) sx[i] = (i < n) ? __ldg(g + i) : 0.0f;
+  }
+  __syncthreads();
+  const float4* s4 = reinterpret_cast<const float4*>(sx);
+  // ---- sums of squares: per float4 (number i*256 + tid of the chunk), scanned over the chunk in element order ----
+  float ex[OP_VEC];
+#pragma unroll
+  for (int i = 0; i < OP_VEC; ++i) {
+    const float4 v = s4[i * 256 + tid];
+    const float q = (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+    float sc = q;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, sc, d);
+      if (lane >= d) sc += t;
+    }
+    if (lane == 31) wtab[i][w] = sc;
+    ex[i] = sc - q;  // exclusive inside the warp
+  }
+  __syncthreads();
+  float run = 0.0f;
+#pragma unroll
+  for (int i = 0; i < OP_VEC; ++i) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (k == w) ex[i] += run;
+      run += wtab[i][k];
+    }
+  }
+  const long long slot0 = row * p.chunks;
+  if (tid == 0) atomicExch(p.sum_slots + slot0 + c, slot_pack(run));
+
+  // ---- sum of the chunks before this one (only its binade matters) ----
+  double before = 0.0;
+  for (int j = tid; j < c; j += 256) {
+    float t = 0.0f;
+    ok = ok && slot_wait(p.sum_slots + slot0 + j, abort_flag, p.err_word, 21, &t);
+    before += static_cast<double>(t);
+  }
+  const double prefix = block_sum_f64(before, red);
+
+  // ---- replay the reference's chain s = fma(x, x, s) over this thread's elements and collect the
+  //      rounding error of every step with error-free transformations (see rms_seq_err_kernel) ----
+  float err = 0.0f;
+#pragma unroll
+  for (int i = 0; i < OP_VEC; ++i) {
+    float sf = static_cast<float>(prefix + static_cast<double>(ex[i]));
+    const float4 v = s4[i * 256 + tid];
+    const float e4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {  // the zero tail adds nothing and rounds nothing
+      const float a = e4[j];
+      const float nf = fmaf(a, a, sf);
+      const float pr = __fmul_rn(a, a);
+      const float e1 = fmaf(a, a, -pr);
+      const float s1 = __fadd_rn(sf, pr);
+      const float bb = __fadd_rn(s1, -sf);
+      const float e2 = __fadd_rn(__fadd_rn(sf, -__fadd_rn(s1, -bb)), __fadd_rn(pr, -bb));
+      err += __fadd_rn(__fadd_rn(__fadd_rn(nf, -s1), -e2), -e1);
+      sf = nf;
+    }
+  }
+  const double chunk_err = block_sum_f64(static_cast<double>(err), red);
+  if (tid == 0) atomicExch(p.err_slots + slot0 + c, slot_pack(static_cast<float>(chunk_err)));
+
+  // ---- the sample's total: every chunk's sum and chain error ----
+  double mine = 0.0;
+  for (int j = tid; j < p.chunks; j += 256) {
+    float e = 0.0f, s = 0.0f;
+    ok = ok && slot_wait(p.err_slots + slot0 + j, abort_flag, p.err_word, 22, &e);
+    ok = ok && slot_wait(p.sum_slots + slot0 + j, abort_flag, p.err_word, 23, &s);
+    mine += static_cast<double>(s) + static_cast<double>(e);
+  }
+  const double sd = block_sum_f64(mine, red);
+  if (__syncthreads_or(!ok)) {  // a wait gave up: the error word is set, nothing is written
+    if (tid == 0) *abort_flag = 1u;
+    return;
+  }
+  const float rms = sqrtf(static_cast<float>(sd) / static_cast<float>(p.len) + p.eps);
+
+  // ---- apply and store ----
+  const long long base = row * p.len + off;
+  const bool vec_out = (n & 3) == 0 && (p.y == nullptr || (reinterpret_cast<uintptr_t>(p.y + base) & 15) == 0) &&
+                       (p.y_split == nullptr || ((reinterpret_cast<uintptr_t>(p.y_split + base) & 7) == 0 && (p.plane_stride & 3) == 0));
+  const bool vec_gamma = p.gamma != nullptr && (reinterpret_cast<uintptr_t>(p.gamma + off) & 15) == 0 && off + n <= p.n_gamma;
+#pragma unroll 2
+  for (int i = 0; i < OP_VEC; ++i) {
+    const int e0 = (i * 256 + tid) * 4;
+    if (e0 >= n) break;
+    const float4 v = s4[i * 256 + tid];
+    float o[4] = {v.x / rms, v.y / rms, v.z / rms, v.w / rms};
+    if (vec_gamma) {
+      const float4 gm = __ldg(reinterpret_cast<const float4*>(p.gamma + off + e0));
+      o[0] *= gm.x; o[1] *= gm.y; o[2] *= gm.z; o[3] *= gm.w;
+    } else if (p.gamma != nullptr) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (off + e0 + j < p.n_gamma) o[j] *= __ldg(p.gamma + off + e0 + j);
+    }
+    if (vec_out) {
+      if (p.y != nullptr) __stcs(reinterpret_cast<float4*>(p.y + base + e0), make_float4(o[0], o[1], o[2], o[3]));
+      if (p.y_split != nullptr) {
+        const __nv_bfloat162 h01 = __floats2bfloat162_rn(o[0], o[1]), h23 = __floats2bfloat162_rn(o[2], o[3]);
+        const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
+        const __nv_bfloat162 l01 = __floats2bfloat162_rn(o[0] - f01.x, o[1] - f01.y), l23 = __floats2bfloat162_rn(o[2] - f23.x, o[3] - f23.y);
+        *reinterpret_cast<uint2*>(p.y_split + base + e0) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+        if (p.planes == 2)
+          *reinterpret_cast<uint2*>(p.y_split + p.plane_stride + base + e0) =
+              make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+      }
+    } else {
+      for (int j = 0; j < 4 && e0 + j < n; ++j) {
+        if (p.y != nullptr) p.y[base + e0 + j] = o[j];
+        if (p.y_split != nullptr) {
+          const __nv_bfloat16 h = __float2bfloat16_rn(o[j]);
+          p.y_split[base + e0 + j] = h;
+          if (p.planes == 2) p.y_split[p.plane_stride + base + e0 + j] = __float2bfloat16_rn(o[j] - __bfloat162float(h));
+        }
+      }
     }
   }
 }
@@ -783,9 +1011,45 @@ int launch_groupnorm_stats(const float* x, float* stats, int batch, int ch, int 
   return launch_sweep_rows<FAM_MEANVAR>(p, st);
 }
 
+// The one-pass kernel needs every CTA of a sample resident at once and a slot pair per chunk.
+bool rmsnorm_onepass_ok(int batch, int64_t n) {
+  static const bool off = [] { const char* e = getenv("MIMIR_B200_RMS_ONEPASS"); return e && e[0] == '0'; }();
+  if (off || n <= 16384) return false;
+  static int per_sm = -1;
+  if (per_sm < 0) {
+    int v = 0;
+    cudaFuncSetAttribute(rms_onepass_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, rms_onepass_kernel, 256, CHUNK * sizeof(float)) != cudaSuccess) v = 0;
+    per_sm = v;
+  }
+  const int64_t chunks = (n + CHUNK - 1) / CHUNK;
+  if (chunks > static_cast<int64_t>(per_sm) * ctx().sm_count) return false;
+  return static_cast<uint64_t>(batch) * chunks * 16 + 256 <= NORM_SCRATCH_BYTES && static_cast<uint64_t>(batch) * chunks < 0x7fffffffull;
+}
+
 int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y, int batch, int64_t n, float eps,
-                   cudaStream_t st) {
+                   cudaStream_t st, __nv_bfloat16* y_split, int planes, int64_t plane_stride) {
   if (batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "RMSNorm: empty input");
+  if (rmsnorm_onepass_ok(batch, n)) {
+    float* scratch;
+    MB_TRY(norm_scratch(&scratch));
+    const int chunks = static_cast<int>((n + CHUNK - 1) / CHUNK);
+    const size_t slots = static_cast<size_t>(batch) * chunks;
+    MB_CUDA(cudaMemsetAsync(scratch, 0, 256 + slots * 16, st));
+    RmsOnePass p{};
+    p.x = x; p.gamma = gamma; p.n_gamma = gamma ? n_gamma : 0; p.y = y; p.y_split = y_split; p.plane_stride = plane_stride;
+    p.planes = planes;
+    p.ticket = reinterpret_cast<unsigned*>(scratch);
+    p.sum_slots = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(scratch) + 256);
+    p.err_slots = p.sum_slots + slots;
+    p.len = n; p.chunks = chunks; p.eps = eps; p.err_word = ctx().dev_error_word;
+    rms_onepass_kernel<<<static_cast<unsigned>(slots), 256, CHUNK * sizeof(float), st>>>(p);
+    MB_CUDA(cudaGetLastError());
+    count_launch();
+    return MIMIR_B200_OK;
+  }
+  if (y == nullptr || y_split != nullptr)
+    return fail(MIMIR_B200_E_UNSUPPORTED, "RMSNorm: operand planes were requested for a shape the one-pass kernel does not take");
   // Below this length the sequential chain's rounding loss is < 1e-6 of the sum and any summation order
   // agrees with the reference; above it the chain is reproduced (rms_seq_err_kernel).
   constexpr long long FAITHFUL_FROM = 16384;

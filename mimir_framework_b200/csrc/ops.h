@@ -36,6 +36,7 @@ struct AttentionExec {
   int batch = 0, seq = 0, embed = 0, heads = 1, causal = 0;
   int precision = MIMIR_B200_PREC_BF16X2;
   const float* x = nullptr;                    // fp32 [batch*seq, embed]
+  const __nv_bfloat16* x_split = nullptr;      // or: its operand planes, written by the producing layer
   const __nv_bfloat16* wqkv_split = nullptr;   // planes of Wqkv^T: [3E][round_up(E,64)]
   const __nv_bfloat16* wout_split = nullptr;   // planes of Wout^T: [E][round_up(E,64)]
   const float* residual = nullptr;

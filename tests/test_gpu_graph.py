@@ -180,10 +180,12 @@ def test_conv_groupnorm_silu_residual_block(backend):
     assert_close(gpu_batch(backend, descs, weights, inputs, batch, oc * hw * hw), oracle_batch(descs, weights, inputs, batch), "conv block")
 
 
-def test_decoder_block_bf16_weights(backend):
+@pytest.mark.parametrize("S,E,H,F", [(64, 128, 2, 256), (96, 512, 8, 320)])
+def test_decoder_block_bf16_weights(backend, S, E, H, F):
     """One block of configuration 3 at reduced size: RMSNorm (whole-tensor) -> causal attention ->
-    Add -> RMSNorm -> Linear -> GELU -> Linear -> Add, weights pre-rounded to bf16, BF16W precision."""
-    S, E, H, F = 64, 128, 2, 256
+    Add -> RMSNorm -> Linear -> GELU -> Linear -> Add, weights pre-rounded to bf16, BF16W precision.
+    The second size has samples above 16384 elements: there the norms run as the single-pass kernel and hand
+    operand planes straight to the attention block and to fc1."""
     descs = [
         make_desc("n1", "RMSNorm", inputs=["x"], output="h1", params_count=S * E),
         make_desc("attn", "MultiHeadAttention", inputs=["h1"], output="a", seq_len=S, embed_dim=E, num_heads=H, causal=1, params_count=4 * E * E),

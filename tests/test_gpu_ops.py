@@ -181,13 +181,28 @@ def test_layernorm(backend, rows, n):
     assert_close(backend.layernorm(x, None, None, rows, n), port.layernorm(x, None, None, rows, n, 1e-5), "layernorm no affine")
 
 
-@pytest.mark.parametrize("batch,n,ng", [(2, 1200, 700), (1, 16384, 16384), (3, 50000, 50000), (2, 786432, 786432)])
+@pytest.mark.parametrize("batch,n,ng", [(2, 1200, 700), (1, 16384, 16384), (3, 50000, 50000), (2, 786432, 786432),
+                                        (3, 33333, 20001), (5, 16385, 0)])
 def test_rmsnorm(backend, batch, n, ng):
     r = rng(n)
     x = r.standard_normal(batch * n).astype(np.float32)
-    g = r.standard_normal(ng).astype(np.float32)
+    g = r.standard_normal(ng).astype(np.float32) if ng else None
     want = np.concatenate([port.rmsnorm(x[i * n:(i + 1) * n], g, 1e-5) for i in range(batch)])
     assert_close(backend.rmsnorm(x, g, batch, n), want, f"rmsnorm {batch}x{n}")
+
+
+def test_rmsnorm_long_sample_follows_the_sequential_sum(backend):
+    """The reference adds the squares of a whole sample in one fp32 chain (LayerOpsExt.hpp:353-356); over 786 432
+    elements that chain loses ~4e-4 of the sum.  The single-pass kernel replays the chain's rounding, so it must sit
+    far closer to the reference than that loss (half of which would show in every output)."""
+    n = 786432
+    x = rng(5).standard_normal(2 * n).astype(np.float32)
+    want = np.concatenate([port.rmsnorm(x[i * n:(i + 1) * n], None, 1e-5) for i in range(2)])
+    got = backend.rmsnorm(x, None, 2, n)
+    rel = np.abs(got - want) / np.maximum(np.abs(want), 1e-3)
+    assert rel.max() < 5e-6, f"max relative deviation {rel.max():.3e}"
+    exact = x.reshape(2, n) / np.sqrt((x.reshape(2, n).astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)
+    assert np.abs(want - exact.ravel()).max() > 2e-5, "the case no longer exercises the chain's rounding loss"
 
 
 def test_rmsnorm_reference_known_answer(backend):
