@@ -299,14 +299,16 @@ __global__ void rms_chunk_apply_kernel(const float* __restrict__ x, const float*
 }
 
 // ---- RMSNorm over a long sample in ONE pass over HBM ---------------------------------------------
-// One CTA per 8192-element chunk keeps its chunk in registers from the load to the store.  Between
-// the two it needs (1) the sum of squares of the chunks before it in the sample (for the binade of
-// the reference's running sum, see rms_seq_err_kernel) and (2) the sample's total.  Both travel
-// through 64-bit slots {tag, fp32 value} in global memory.  CTAs take their chunk from a ticket
-// counter, so a CTA only ever waits for chunks whose CTAs started before it or belong to its own
-// sample; the launcher only uses this kernel when a whole sample's CTAs are resident at once.
-// Every wait is bounded: after ~2 s (or when another CTA gave up) the CTA reports through the
-// device error word and leaves.
+// One CTA per 8192-element chunk keeps its chunk in shared memory from the load to the store (six
+// CTAs per SM: 192 KB of the sample in flight per SM).  Between the two it needs (1) the sum of
+// squares of the chunks before it in the sample - for the binade of the reference's running sum,
+// see rms_seq_err_kernel; inside the chunk the running sum is interpolated - and (2) the sample's
+// total.  Both travel through 64-bit slots {tag, fp32 value} in global memory, published with an
+// atomic exchange (a plain store takes measurably longer to become visible to the pollers).  CTAs
+// take their chunk from a ticket counter, so a CTA only ever waits for chunks whose CTAs started
+// before it or belong to its own sample; the launcher only uses this kernel when a whole sample's
+// CTAs are resident at once.  Every wait is bounded: after ~2 s (or when another CTA gave up) the
+// CTA reports through the device error word and leaves without writing.
 constexpr int OP_VEC = CHUNK / (256 * 4);  // float4 per thread
 
 struct RmsOnePass {
@@ -373,9 +375,9 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
   __shared__ __align__(8) uint64_t bar;
   __shared__ unsigned s_id;
   __shared__ int s_abort;
-  __shared__ float wtab[OP_VEC][8];
+  __shared__ float redf[33];
   __shared__ double red[8];
-  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+  const int tid = threadIdx.x;
   if (tid == 0) {
     s_id = atomicAdd(p.ticket, 1u);
     s_abort = 0;
@@ -405,31 +407,14 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
   }
   __syncthreads();
   const float4* s4 = reinterpret_cast<const float4*>(sx);
-  // ---- sums of squares: per float4 (number i*256 + tid of the chunk), scanned over the chunk in element order ----
-  float ex[OP_VEC];
+  // ---- the chunk's sum of squares ----
+  float acc = 0.0f;
 #pragma unroll
   for (int i = 0; i < OP_VEC; ++i) {
     const float4 v = s4[i * 256 + tid];
-    const float q = (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
-    float sc = q;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const float t = __shfl_up_sync(0xffffffffu, sc, d);
-      if (lane >= d) sc += t;
-    }
-    if (lane == 31) wtab[i][w] = sc;
-    ex[i] = sc - q;  // exclusive inside the warp
+    acc += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
   }
-  __syncthreads();
-  float run = 0.0f;
-#pragma unroll
-  for (int i = 0; i < OP_VEC; ++i) {
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      if (k == w) ex[i] += run;
-      run += wtab[i][k];
-    }
-  }
+  const float run = block_sum(acc, redf);
   const long long slot0 = row * p.chunks;
   if (tid == 0) atomicExch(p.sum_slots + slot0 + c, slot_pack(run));
 
@@ -447,7 +432,9 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
   float err = 0.0f;
 #pragma unroll
   for (int i = 0; i < OP_VEC; ++i) {
-    float sf = static_cast<float>(prefix + static_cast<double>(ex[i]));
+    // Where the chain stood before this float4: only the binade of that value enters the rounding of a step,
+    // so inside the chunk (1 % of a long sample) the running sum is taken as growing evenly.
+    float sf = static_cast<float>(prefix) + run * (static_cast<float>((i * 256 + tid) * 4) * (1.0f / CHUNK));
     const float4 v = s4[i * 256 + tid];
     const float e4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -457,8 +444,8 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
       const float pr = __fmul_rn(a, a);
       const float e1 = fmaf(a, a, -pr);
       const float s1 = __fadd_rn(sf, pr);
-      const float bb = __fadd_rn(s1, -sf);
-      const float e2 = __fadd_rn(__fadd_rn(sf, -__fadd_rn(s1, -bb)), __fadd_rn(pr, -bb));
+      const float big = fmaxf(sf, pr), small = fminf(sf, pr);  // both are >= 0: the larger one first makes the short form exact
+      const float e2 = __fadd_rn(small, -__fadd_rn(s1, -big));
       err += __fadd_rn(__fadd_rn(__fadd_rn(nf, -s1), -e2), -e1);
       sf = nf;
     }
@@ -480,6 +467,7 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
     return;
   }
   const float rms = sqrtf(static_cast<float>(sd) / static_cast<float>(p.len) + p.eps);
+  const float inv_rms = 1.0f / rms;
 
   // ---- apply and store ----
   const long long base = row * p.len + off;
@@ -491,7 +479,14 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
     const int e0 = (i * 256 + tid) * 4;
     if (e0 >= n) break;
     const float4 v = s4[i * 256 + tid];
-    float o[4] = {v.x / rms, v.y / rms, v.z / rms, v.w / rms};
+    // x / rms as one multiply by the reciprocal plus one correction step (what the division routine itself does,
+    // minus its special-case handling: the quotient of two normal numbers comes out correctly rounded)
+    float o[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float q0 = o[j] * inv_rms;
+      o[j] = fmaf(fmaf(-q0, rms, o[j]), inv_rms, q0);
+    }
     if (vec_gamma) {
       const float4 gm = __ldg(reinterpret_cast<const float4*>(p.gamma + off + e0));
       o[0] *= gm.x; o[1] *= gm.y; o[2] *= gm.z; o[3] *= gm.w;
