@@ -201,6 +201,17 @@ int mimir_b200_batch_matmul(const float* A, const float* B, float* C, long long 
  * y[i] *= w[i] for i < n_w; no shift (Model.cpp:5387-5421). */
 int mimir_b200_batchnorm_inference(const float* x, const float* w, long long n_w, float* y, int batch,
                                    long long n, float eps);
+/* BatchNorm with running statistics, the inference branch of Model::computeBatchNorm / Normalization::batch_norm
+ * (Model.cpp:4066-4148, Layers.hpp:932-970): x is [batch][channels][spatial];
+ * y = (x - mean[c]) * (1 / sqrt(var[c] + eps)) * gamma[c] + beta[c]. */
+int mimir_b200_batchnorm_running(const float* x, const float* gamma, const float* beta, const float* running_mean,
+                                 const float* running_var, float* y, int batch, int channels, long long spatial,
+                                 float eps);
+/* Attention core on separate, already projected Q / K / V, each [batch*seq][d_model] with the heads side by side
+ * (Model::computeAttention, scalar branch, Model.cpp:4223-4289): softmax(Q_h K_h^T / sqrt(head_dim)) V_h per head,
+ * no mask, no projections. */
+int mimir_b200_attention_qkv(const float* q, const float* k, const float* v, float* y, int batch, int seq,
+                             int d_model, int num_heads);
 
 /* ---------------------------------------------------------------------------------------------
  * 3. Whole-graph entry points (activations stay on the device between layers)

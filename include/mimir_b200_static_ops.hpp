@@ -10,13 +10,14 @@
 // reference reports shape errors (RuntimeAllocator.hpp:344-358).  mimir_b200_init must have been called.
 //
 // Covered: computeLinear, computeMaxPool2D, computeAvgPool2D, computeActivation (relu, leaky_relu, tanh,
-// sigmoid, gelu, softmax), computeLayerNorm.  Not covered, because their arithmetic differs from the layer
-// ops this backend implements: computeConv2D / computeConvTranspose2D (Conv::conv2d adds a bias and takes
-// a dilation; Conv::conv_transpose2d is the scatter form, Layers.hpp:611-830), computeBatchNorm (running
-// statistics, Model.cpp:4066-4148), computeAttention (separate Q / K / V without projections,
-// Model.cpp:4223-4289), activation "elu".  Calling those here throws.
+// sigmoid, gelu, softmax), computeLayerNorm, computeBatchNorm (inference), computeAttention.  Not covered,
+// because their arithmetic differs from the layer ops this backend implements: computeConv2D /
+// computeConvTranspose2D (Conv::conv2d adds a bias and takes a dilation; Conv::conv_transpose2d is the
+// scatter form, Layers.hpp:611-830), computeBatchNorm with training = true, activation "elu".  Calling
+// those here throws.
 #pragma once
 
+#include <algorithm>
 #include <stdexcept>
 #include <string>
 #include <vector>
@@ -128,13 +129,35 @@ inline void computeConvTranspose2D(const std::vector<float>&, std::vector<float>
                                    bool = true) {
   not_available("computeConvTranspose2D");
 }
-inline void computeBatchNorm(std::vector<float>&, const std::vector<float>&, const std::vector<float>&, const std::vector<float>&,
-                             const std::vector<float>&, int, int, int, float = 1e-5f, bool = false, bool = true) {
-  not_available("computeBatchNorm");
+
+// Model::computeBatchNorm (Model.cpp:4066-4148), in place, data [batch][channels][spatial].  Inference only: with
+// training = true the reference recomputes the statistics from the batch, which is outside the forward path.
+inline void computeBatchNorm(std::vector<float>& data, const std::vector<float>& gamma, const std::vector<float>& beta,
+                             const std::vector<float>& running_mean, const std::vector<float>& running_var, int batch_size,
+                             int channels, int spatial_size, float eps = 1e-5f, bool training = false, bool /*use_hardware*/ = true) {
+  if (training) not_available("computeBatchNorm(training = true)");
+  const size_t n = static_cast<size_t>(batch_size) * channels * spatial_size;
+  const size_t c = static_cast<size_t>(channels);
+  if (batch_size <= 0 || channels <= 0 || spatial_size <= 0 || data.size() < n || gamma.size() < c || beta.size() < c ||
+      running_mean.size() < c || running_var.size() < c)
+    throw std::runtime_error("computeBatchNorm: data or parameters smaller than batch x channels x spatial");
+  std::vector<float> out(data.size());
+  check(mimir_b200_batchnorm_running(data.data(), gamma.data(), beta.data(), running_mean.data(), running_var.data(), out.data(),
+                                     batch_size, channels, spatial_size, eps));
+  std::copy(out.begin(), out.begin() + static_cast<std::ptrdiff_t>(n), data.begin());
 }
-inline void computeAttention(const std::vector<float>&, const std::vector<float>&, const std::vector<float>&, std::vector<float>&, int,
-                             int, int, bool = true) {
-  not_available("computeAttention");
+
+// Model::computeAttention (Model.cpp:4223-4289): separate, already projected Q / K / V of one sequence, [seq_len][d_model]
+// with the heads side by side; no mask.  Follows the reference's scalar branch; its AVX2 branch reads every head as a
+// dense [seq_len][head_dim] block, which only coincides with this layout for num_heads = 1.
+inline void computeAttention(const std::vector<float>& query, const std::vector<float>& key, const std::vector<float>& value,
+                             std::vector<float>& output, int seq_len, int d_model, int num_heads, bool /*use_hardware*/ = true) {
+  const size_t n = static_cast<size_t>(seq_len) * d_model;
+  if (seq_len <= 0 || d_model <= 0 || num_heads <= 0 || d_model % num_heads != 0 || query.size() < n || key.size() < n ||
+      value.size() < n)
+    throw std::runtime_error("computeAttention: Q / K / V smaller than seq_len x d_model, or d_model not a multiple of num_heads");
+  output.assign(n, 0.0f);
+  check(mimir_b200_attention_qkv(query.data(), key.data(), value.data(), output.data(), 1, seq_len, d_model, num_heads));
 }
 
 }  // namespace static_ops

@@ -243,4 +243,42 @@ int mimir_b200_batchnorm_inference(const float* x, const float* w, long long n_w
   return finish_download(y, dy, static_cast<size_t>(batch) * n);
 }
 
+int mimir_b200_batchnorm_running(const float* x, const float* gamma, const float* beta, const float* running_mean,
+                                 const float* running_var, float* y, int batch, int channels, long long spatial, float eps) {
+  MB_REQUIRE_INIT();
+  if (!x || !y || !gamma || !beta || !running_mean || !running_var) return fail(MIMIR_B200_E_INVALID, "BatchNorm: null argument");
+  if (batch <= 0 || channels <= 0 || spatial <= 0) return fail(MIMIR_B200_E_INVALID, "BatchNorm: empty input");
+  Temps t;
+  const size_t n = static_cast<size_t>(batch) * channels * spatial;
+  const float *dx, *dg, *db, *dm, *dv;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, n, "bn.x"));
+  MB_TRY(t.upload(&dg, gamma, channels, "bn.gamma"));
+  MB_TRY(t.upload(&db, beta, channels, "bn.beta"));
+  MB_TRY(t.upload(&dm, running_mean, channels, "bn.mean"));
+  MB_TRY(t.upload(&dv, running_var, channels, "bn.var"));
+  MB_TRY(t.out(&dy, n, "bn.y"));
+  MB_TRY(launch_batchnorm_running(dx, dg, db, dm, dv, dy, batch, channels, spatial, eps, nullptr));
+  return finish_download(y, dy, n);
+}
+
+int mimir_b200_attention_qkv(const float* q, const float* k, const float* v, float* y, int batch, int seq, int d_model,
+                             int num_heads) {
+  MB_REQUIRE_INIT();
+  if (!q || !k || !v || !y) return fail(MIMIR_B200_E_INVALID, "attention: null argument");
+  if (batch <= 0 || seq <= 0 || d_model <= 0 || num_heads <= 0 || d_model % num_heads != 0)
+    return fail(MIMIR_B200_E_INVALID, "attention: d_model must be a positive multiple of num_heads");
+  Temps t;
+  const size_t n = static_cast<size_t>(batch) * seq * d_model;
+  AttnView a;
+  float* dy;
+  MB_TRY(t.upload(&a.q, q, n, "attn.q"));
+  MB_TRY(t.upload(&a.k, k, n, "attn.k"));
+  MB_TRY(t.upload(&a.v, v, n, "attn.v"));
+  MB_TRY(t.out(&dy, n, "attn.y"));
+  a.ldq = d_model; a.ldkv = d_model; a.q_len = seq; a.kv_len = seq;
+  MB_TRY(launch_attention_core_view(a, dy, batch, d_model, num_heads, 0, nullptr));
+  return finish_download(y, dy, n);
+}
+
 }  // extern "C"

@@ -185,5 +185,7 @@ int launch_pixel_shuffle(const float* x, float* y, int batch, int ic, int h, int
 int launch_upsample_bilinear(const float* x, float* y, int batch, int ch, int h, int wd, int oh, int ow, int half_pixel,
                              cudaStream_t st);
 int launch_batch_matmul(const float* a, const float* b, float* c, int64_t nb, int m, int k, int n, cudaStream_t st);
+int launch_batchnorm_running(const float* x, const float* gamma, const float* beta, const float* mean, const float* var, float* y,
+                             int batch, int channels, int64_t spatial, float eps, cudaStream_t st);
 int launch_scale_prefix(float* y, const float* g, int batch, int64_t n, int64_t cnt, cudaStream_t st);
 }  // namespace mb

@@ -439,14 +439,15 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
     const float e4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {  // the zero tail adds nothing and rounds nothing
+      // One step of the chain, nf = RN(sf + a*a), and its rounding error nf - (sf + a*a), from three exact pieces:
+      // a*a = pr + e1 (product and its error), d = nf - sf (exact while nf <= 2 sf, i.e. once the running sum
+      // exceeds a single square) and d - pr (exact when a*a is not far below the sum's ulp; otherwise its own
+      // rounding is 2^-24 of a rounding error).
       const float a = e4[j];
       const float nf = fmaf(a, a, sf);
       const float pr = __fmul_rn(a, a);
       const float e1 = fmaf(a, a, -pr);
-      const float s1 = __fadd_rn(sf, pr);
-      const float big = fmaxf(sf, pr), small = fminf(sf, pr);  // both are >= 0: the larger one first makes the short form exact
-      const float e2 = __fadd_rn(small, -__fadd_rn(s1, -big));
-      err += __fadd_rn(__fadd_rn(__fadd_rn(nf, -s1), -e2), -e1);
+      err += __fadd_rn(__fadd_rn(__fadd_rn(nf, -sf), -pr), -e1);
       sf = nf;
     }
   }

@@ -244,6 +244,18 @@ __global__ void __launch_bounds__(256) batch_matmul_kernel(const float* __restri
   }
 }
 
+// (x - mean[c]) * inv_std[c] * gamma[c] + beta[c], in the reference's order of operations (Layers.hpp:961-966)
+__global__ void batchnorm_running_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                         const float* __restrict__ mean, const float* __restrict__ var, float* __restrict__ y,
+                                         long long total, int channels, long long spatial, float eps) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>((i / spatial) % channels);
+    const float inv_std = 1.0f / sqrtf(__ldg(var + c) + eps);
+    y[i] = __fadd_rn(__fmul_rn(__fmul_rn(__ldg(x + i) - __ldg(mean + c), inv_std), __ldg(gamma + c)), __ldg(beta + c));
+  }
+}
+
 __global__ void scale_prefix_kernel(float* __restrict__ y, const float* __restrict__ g, long long batch, long long n, long long cnt) {
   const long long total = batch * cnt;
   MB_GRID_STRIDE(i, total) {
@@ -336,6 +348,16 @@ int launch_batch_matmul(const float* a, const float* b, float* c, int64_t nb, in
   dim3 grid((n + 31) / 32, (m + 31) / 32, static_cast<unsigned>(nb));
   batch_matmul_kernel<<<grid, 256, 0, st>>>(a, b, c, m, k, n);
   MB_LAUNCHED();
+}
+
+int launch_batchnorm_running(const float* x, const float* gamma, const float* beta, const float* mean, const float* var, float* y,
+                             int batch, int channels, int64_t spatial, float eps, cudaStream_t st) {
+  const long long total = static_cast<long long>(batch) * channels * spatial;
+  if (total <= 0) return MIMIR_B200_OK;
+  batchnorm_running_kernel<<<grid_of(total, 256), 256, 0, st>>>(x, gamma, beta, mean, var, y, total, channels, spatial, eps);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
 }
 
 int launch_scale_prefix(float* y, const float* g, int batch, int64_t n, int64_t cnt, cudaStream_t st) {

@@ -56,6 +56,8 @@ _SIGS = {
     "mimir_b200_upsample_bilinear": [_P, _P] + [C.c_int] * 7,
     "mimir_b200_batch_matmul": [_P, _P, _P, C.c_longlong, C.c_int, C.c_int, C.c_int],
     "mimir_b200_batchnorm_inference": [_P, _P, C.c_longlong, _P, C.c_int, C.c_longlong, C.c_float],
+    "mimir_b200_batchnorm_running": [_P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_longlong, C.c_float],
+    "mimir_b200_attention_qkv": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int],
     "mimir_b200_model_create": [_P, C.c_int, _P],
     "mimir_b200_model_destroy": [_P],
     "mimir_b200_model_set_precision": [_P, C.c_int],
@@ -334,6 +336,20 @@ def batchnorm_inference(x, w, batch, n, eps=1e-5):
     x, w = _f(x), _f(w)
     y = np.empty(batch * n, np.float32)
     check(lib().mimir_b200_batchnorm_inference(_p(x), _p(w), 0 if w is None else w.size, _p(y), batch, n, eps))
+    return y
+
+
+def batchnorm_running(x, gamma, beta, mean, var, batch, channels, spatial, eps=1e-5):
+    x, gamma, beta, mean, var = (_f(a) for a in (x, gamma, beta, mean, var))
+    y = np.empty(batch * channels * spatial, np.float32)
+    check(lib().mimir_b200_batchnorm_running(_p(x), _p(gamma), _p(beta), _p(mean), _p(var), _p(y), batch, channels, spatial, eps))
+    return y
+
+
+def attention_qkv(q, k, v, batch, seq, d_model, heads):
+    q, k, v = _f(q), _f(k), _f(v)
+    y = np.empty(batch * seq * d_model, np.float32)
+    check(lib().mimir_b200_attention_qkv(_p(q), _p(k), _p(v), _p(y), batch, seq, d_model, heads))
     return y
 
 

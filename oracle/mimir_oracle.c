@@ -596,6 +596,48 @@ void mo_batchnorm_inference(const float* x, const float* w, long n_w, float* y, 
   }
 }
 
+/* Normalization::batch_norm with training = false (Layers.hpp:932-970; Model::computeBatchNorm's software branch,
+ * Model.cpp:4144-4147): data is [batch][channels][spatial], statistics are the running ones */
+void mo_batchnorm_running(const float* x, const float* gamma, const float* beta, const float* mean, const float* var,
+                          float* y, int batch, int channels, long spatial, float eps) {
+  for (int c = 0; c < channels; ++c) {
+    const float inv_std = 1.0f / sqrtf(var[c] + eps);
+    for (int b = 0; b < batch; ++b)
+      for (long s = 0; s < spatial; ++s) {
+        const size_t i = ((size_t)b * channels + c) * spatial + s;
+        y[i] = (x[i] - mean[c]) * inv_std * gamma[c] + beta[c];
+      }
+  }
+}
+
+/* Model::computeAttention, scalar branch (Model.cpp:4223-4289) with Model::softmax_inplace (Model.hpp:522-535):
+ * Q, K, V are [seq][d_model], heads side by side; per head scores = Q_h K_h^T * (1 / sqrt(head_dim)), row softmax
+ * (max, exp, divide by the plain sum), output = P V_h */
+void mo_attention_qkv(const float* q, const float* k, const float* v, float* y, int seq, int d_model, int heads) {
+  const int hd = d_model / heads;
+  const float scale = 1.0f / sqrtf((float)hd);
+  float* row = (float*)malloc((size_t)seq * sizeof(float));
+  for (int h = 0; h < heads; ++h)
+    for (int i = 0; i < seq; ++i) {
+      for (int j = 0; j < seq; ++j) {
+        float sum = 0.0f;
+        for (int d = 0; d < hd; ++d) sum += q[(size_t)i * d_model + h * hd + d] * k[(size_t)j * d_model + h * hd + d];
+        row[j] = sum * scale;
+      }
+      float m = row[0];
+      for (int j = 1; j < seq; ++j) m = row[j] > m ? row[j] : m;
+      float s = 0.0f;
+      for (int j = 0; j < seq; ++j) { row[j] = expf(row[j] - m); s += row[j]; }
+      for (int j = 0; j < seq; ++j) row[j] /= s;
+      for (int d = 0; d < hd; ++d) {
+        float sum = 0.0f;
+        for (int j = 0; j < seq; ++j) sum += row[j] * v[(size_t)j * d_model + h * hd + d];
+        y[(size_t)i * d_model + h * hd + d] = sum;
+      }
+    }
+  free(row);
+}
+
 /* LayerOpsExt::instance_norm2d_forward, LayerOpsExt.hpp:278-339: per channel, then gamma[c], beta[C + c] */
 void mo_instance_norm2d(const float* x, const float* w, float* y, int ch, int h, int wd, float eps) {
   const int hw = h * wd;

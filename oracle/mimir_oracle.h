@@ -33,6 +33,9 @@ void mo_pixel_shuffle(const float* x, float* y, int ic, int h, int wd, int r);
 void mo_upsample_bilinear(const float* x, float* y, int ch, int h, int wd, int oh, int ow, int half_pixel);
 void mo_batch_matmul(const float* A, const float* B, float* C, long nb, int M, int K, int N);
 void mo_batchnorm_inference(const float* x, const float* w, long n_w, float* y, long n, float eps);
+void mo_batchnorm_running(const float* x, const float* gamma, const float* beta, const float* mean, const float* var,
+                          float* y, int batch, int channels, long spatial, float eps);
+void mo_attention_qkv(const float* q, const float* k, const float* v, float* y, int seq, int d_model, int heads);
 void mo_instance_norm2d(const float* x, const float* w, float* y, int ch, int h, int wd, float eps);
 #ifdef __cplusplus
 }

@@ -246,6 +246,20 @@ def batchnorm_inference(x, w, eps):
     return y
 
 
+def batchnorm_running(x, gamma, beta, mean, var, batch, channels, spatial, eps=1e-5):
+    x, gamma, beta, mean, var = (_f(a) for a in (x, gamma, beta, mean, var))
+    y = np.empty_like(x)
+    lib().mo_batchnorm_running(_p(x), _p(gamma), _p(beta), _p(mean), _p(var), _p(y), *_ci(batch, channels), C.c_long(spatial), C.c_float(eps))
+    return y
+
+
+def attention_qkv(q, k, v, seq, d_model, heads):
+    q, k, v = _f(q), _f(k), _f(v)
+    y = np.empty_like(q)
+    lib().mo_attention_qkv(_p(q), _p(k), _p(v), _p(y), *_ci(seq, d_model, heads))
+    return y
+
+
 def instance_norm2d(x, w, ch, h, wd, eps):
     x = _f(x)
     w = _f(w) if w is not None else None

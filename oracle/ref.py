@@ -122,3 +122,23 @@ class RefModel:
         _check(lib().mimir_ref_model_forward(self._h, arr, C.c_int(len(inputs)), out.ctypes.data_as(C.c_void_p), C.c_ulonglong(out_cap), C.byref(n), C.byref(secs)))
         out = out[: n.value]
         return (out, secs.value) if return_seconds else out
+
+
+def compute_attention(q, k, v, seq: int, d_model: int, heads: int) -> np.ndarray:
+    """Model::computeAttention, software branch, one sample."""
+    q, k, v = (np.ascontiguousarray(a, np.float32).ravel() for a in (q, k, v))
+    out = np.empty(seq * d_model, np.float32)
+    fp = C.POINTER(C.c_float)
+    _check(lib().mimir_ref_compute_attention(q.ctypes.data_as(fp), k.ctypes.data_as(fp), v.ctypes.data_as(fp), out.ctypes.data_as(fp),
+                                             C.c_int(seq), C.c_int(d_model), C.c_int(heads)))
+    return out
+
+
+def compute_batchnorm(x, gamma, beta, mean, var, batch: int, channels: int, spatial: int, eps: float = 1e-5) -> np.ndarray:
+    """Model::computeBatchNorm, software branch, training = false."""
+    d = np.array(x, np.float32).ravel().copy()
+    g, b, m, v = (np.ascontiguousarray(a, np.float32).ravel() for a in (gamma, beta, mean, var))
+    fp = C.POINTER(C.c_float)
+    _check(lib().mimir_ref_compute_batchnorm(d.ctypes.data_as(fp), g.ctypes.data_as(fp), b.ctypes.data_as(fp), m.ctypes.data_as(fp),
+                                             v.ctypes.data_as(fp), C.c_int(batch), C.c_int(channels), C.c_int(spatial), C.c_float(eps)))
+    return d

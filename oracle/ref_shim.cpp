@@ -183,6 +183,27 @@ int mimir_ref_model_save_safetensors(void* h, const char* path) {
   });
 }
 
+// The legacy static API, software branch (use_hardware = false): Model::computeAttention on separate Q / K / V and
+// Model::computeBatchNorm with running statistics (Model.hpp:409-429).
+int mimir_ref_compute_attention(const float* q, const float* k, const float* v, float* out, int seq, int d_model, int heads) {
+  return guarded([&] {
+    const size_t n = static_cast<size_t>(seq) * d_model;
+    std::vector<float> Q(q, q + n), K(k, k + n), V(v, v + n), O;
+    Model::computeAttention(Q, K, V, O, seq, d_model, heads, false);
+    std::memcpy(out, O.data(), n * sizeof(float));
+  });
+}
+int mimir_ref_compute_batchnorm(float* data, const float* gamma, const float* beta, const float* mean, const float* var,
+                                int batch, int channels, int spatial, float eps) {
+  return guarded([&] {
+    const size_t n = static_cast<size_t>(batch) * channels * spatial;
+    std::vector<float> d(data, data + n), g(gamma, gamma + channels), b(beta, beta + channels), m(mean, mean + channels),
+        vv(var, var + channels);
+    Model::computeBatchNorm(d, g, b, m, vv, batch, channels, spatial, eps, false, false);
+    std::memcpy(data, d.data(), n * sizeof(float));
+  });
+}
+
 // One sample through Model::forwardPassNamed(training=false).  Returns seconds in *seconds.
 int mimir_ref_model_forward(void* h, const MimirNamedInput* inputs, int n_inputs, float* out,
                             unsigned long long cap, unsigned long long* out_len, double* seconds) {

@@ -314,3 +314,25 @@ def test_norm_statistics_are_robust_to_offsets_and_outliers(backend):
     gg, bg = r.standard_normal(ch).astype(np.float32), r.standard_normal(ch).astype(np.float32)
     want = np.concatenate([port.groupnorm(xg[i * per:(i + 1) * per], gg, bg, ch, h, w, groups, 1e-5) for i in range(batch)])
     assert_close(backend.groupnorm(xg, gg, bg, batch, ch, h, w, groups, 1e-5, -1), want, "groupnorm offset/outlier slabs")
+
+
+@pytest.mark.parametrize("batch,seq,d_model,heads", [(1, 5, 8, 2), (2, 77, 128, 2), (3, 130, 96, 3), (1, 300, 40, 1)])
+def test_attention_on_separate_qkv(backend, batch, seq, d_model, heads):
+    """Model::computeAttention (Model.cpp:4223-4289): projected Q / K / V in, no mask, heads side by side."""
+    r = rng(seq * d_model)
+    q, k, v = (r.standard_normal(batch * seq * d_model).astype(np.float32) for _ in range(3))
+    n = seq * d_model
+    want = np.concatenate([port.attention_qkv(q[b * n:(b + 1) * n], k[b * n:(b + 1) * n], v[b * n:(b + 1) * n], seq, d_model, heads)
+                           for b in range(batch)])
+    assert_close(backend.attention_qkv(q, k, v, batch, seq, d_model, heads), want, f"attention_qkv {batch}x{seq}x{d_model}/{heads}")
+
+
+@pytest.mark.parametrize("batch,ch,spatial", [(1, 1, 1), (2, 3, 50), (4, 64, 49), (1, 7, 1000)])
+def test_batchnorm_with_running_statistics(backend, batch, ch, spatial):
+    """Model::computeBatchNorm at inference (Layers.hpp:932-970)."""
+    r = rng(ch * spatial)
+    x = (r.standard_normal(batch * ch * spatial) * 3 + 1).astype(np.float32)
+    g, b, m = (r.standard_normal(ch).astype(np.float32) for _ in range(3))
+    var = (r.random(ch) + 0.1).astype(np.float32)
+    want = port.batchnorm_running(x, g, b, m, var, batch, ch, spatial, 1e-5)
+    assert_close(backend.batchnorm_running(x, g, b, m, var, batch, ch, spatial), want, f"batchnorm_running {batch}x{ch}x{spatial}")

@@ -71,3 +71,19 @@ def test_compiled_reference_passes_its_own_known_answers():
             if w is not None:
                 m.set_weights(i, w)
         np.testing.assert_allclose(m.forward(inputs), want, atol=max(atol, 1e-7), rtol=0, err_msg=name)
+
+
+@pytest.mark.skipif(not ref.available(), reason="compiled reference (oracle/_ref) not built here")
+def test_port_of_the_legacy_static_ops_matches_the_compiled_reference():
+    """Model::computeAttention and Model::computeBatchNorm (software branch) against their plain-C restatements."""
+    r = np.random.default_rng(3)
+    for seq, d_model, heads in [(5, 8, 2), (33, 48, 3), (64, 64, 1)]:
+        q, k, v = (r.standard_normal(seq * d_model).astype(np.float32) for _ in range(3))
+        np.testing.assert_allclose(port.attention_qkv(q, k, v, seq, d_model, heads), ref.compute_attention(q, k, v, seq, d_model, heads),
+                                   atol=2e-6, rtol=1e-5)
+    for batch, ch, spatial in [(1, 1, 1), (3, 5, 17), (2, 16, 64)]:
+        x = (r.standard_normal(batch * ch * spatial) * 2).astype(np.float32)
+        g, b, m = (r.standard_normal(ch).astype(np.float32) for _ in range(3))
+        var = (r.random(ch) + 0.05).astype(np.float32)
+        np.testing.assert_allclose(port.batchnorm_running(x, g, b, m, var, batch, ch, spatial, 1e-5),
+                                   ref.compute_batchnorm(x, g, b, m, var, batch, ch, spatial, 1e-5), atol=1e-6, rtol=1e-6)

@@ -54,8 +54,14 @@ int main() {
   computeLayerNorm(a, g, b, 8, 1e-5f);
   dump("layernorm", a);
   try { computeActivation(a, "elu", 1.0f); std::printf("elu no-throw\n"); } catch (const std::exception& e) { std::printf("elu throws\n"); }
-  try { std::vector<float> o; computeAttention(x, x, x, o, 5, 8, 2); std::printf("attention no-throw\n"); }
-  catch (const std::exception& e) { std::printf("attention throws\n"); }
+  { std::vector<float> o, kk(x.rbegin(), x.rend()); computeAttention(x, kk, x, o, 5, 8, 2); dump("attention", o); }
+  {
+    std::vector<float> d = x, gm{1.5f, -0.5f}, bt{0.1f, 0.2f}, mu{0.25f, -0.75f}, vr{0.5f, 2.0f};
+    computeBatchNorm(d, gm, bt, mu, vr, 4, 2, 5, 1e-5f);
+    dump("batchnorm", d);
+    try { computeBatchNorm(d, gm, bt, mu, vr, 4, 2, 5, 1e-5f, true); std::printf("bn_training no-throw\n"); }
+    catch (const std::exception& e) { std::printf("bn_training throws\n"); }
+  }
   mimir_b200_shutdown();
   return 0;
 }
@@ -83,7 +89,7 @@ def test_static_ops_against_the_oracle(tmp_path):
     got = {}
     for line in out.splitlines():
         name, *vals = line.split()
-        got[name] = np.array([float(v) for v in vals], np.float32) if vals and name not in ("elu", "attention") else " ".join(vals)
+        got[name] = np.array([float(v) for v in vals], np.float32) if vals and name not in ("elu", "bn_training") else " ".join(vals)
     x = np.array([0.25 * ((i * 7) % 11) - 1.0 for i in range(40)], np.float32)
     w = np.array([0.01 * ((i * 13) % 17) - 0.05 for i in range(240)], np.float32)
     b = np.array([0.1 * i for i in range(6)], np.float32)
@@ -97,4 +103,7 @@ def test_static_ops_against_the_oracle(tmp_path):
     g = np.array([1.0 + 0.1 * i for i in range(8)], np.float32)
     be = np.array([-0.05 * i for i in range(8)], np.float32)
     np.testing.assert_allclose(got["layernorm"], port.layernorm(x, g, be, 5, 8, 1e-5), atol=1e-5, rtol=1e-4)
-    assert got["elu"] == "throws" and got["attention"] == "throws"
+    np.testing.assert_allclose(got["attention"], port.attention_qkv(x, x[::-1].copy(), x, 5, 8, 2), atol=1e-5, rtol=1e-4)
+    np.testing.assert_allclose(got["batchnorm"], port.batchnorm_running(x, [1.5, -0.5], [0.1, 0.2], [0.25, -0.75], [0.5, 2.0], 4, 2, 5, 1e-5),
+                               atol=1e-6, rtol=1e-6)
+    assert got["elu"] == "throws" and got["bn_training"] == "throws"
