@@ -11,6 +11,8 @@
 //   * "chunk" kernels when there are only a few (long) rows: pass 1 reduces 8192-element chunks to
 //     partial statistics in a small global scratch, pass 2 combines the partials of its row and
 //     writes the result; rows are processed in groups that fit in L2 so that pass 2 reads from L2.
+#include <cooperative_groups.h>
+
 #include "common.h"
 #include "sm100_ptx.cuh"
 
@@ -724,6 +726,76 @@ __global__ void meanvar_chunk_apply_kernel(const float* __restrict__ x, float* _
   meanvar_write_row(g, o, cn, vec, mean, inv, row + row0, base, al, off);
 }
 
+// ---- a few rows of up to ~100 000 elements: one thread-block cluster per row -----------------------
+// Each CTA of the cluster keeps a slice of the row in shared memory; the partial sums meet through
+// distributed shared memory (every CTA reads all partials in the same order, so all agree bit for bit):
+// first the sum for the mean, then the centred second moment, as the reference's two loops do
+// (LayerOps.hpp:287-300).  One launch, one read and one write of the row, no global scratch.
+constexpr int CLUSTER_SLICE_MAX = 12288;  // floats of shared memory per CTA (48 KB)
+
+__global__ void __launch_bounds__(256) meanvar_cluster_kernel(const float* __restrict__ x, float* __restrict__ y, long long len,
+                                                              int slice, float eps, Affine a) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cl = cg::this_cluster();
+  extern __shared__ __align__(16) float sx[];
+  __shared__ float red[33];
+  __shared__ float part[2];
+  const unsigned ncl = cl.num_blocks(), rank = cl.block_rank();
+  const long long row = blockIdx.x / ncl;
+  const long long off = static_cast<long long>(rank) * slice;
+  const int n = static_cast<int>(max(0ll, min(static_cast<long long>(slice), len - off)));
+  const long long base = row * len;
+  const float acc = stage_and_sum(x + base + off, sx, n);
+  const float s = block_sum(acc, red);
+  if (threadIdx.x == 0) part[0] = s;
+  cl.sync();
+  float total = 0.0f;
+  for (unsigned k = 0; k < ncl; ++k) total += *cl.map_shared_rank(&part[0], k);
+  const float mean = total / static_cast<float>(len);
+  float q = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float d = sx[i] - mean;
+    q = fmaf(d, d, q);
+  }
+  const float m2 = block_sum(q, red);
+  if (threadIdx.x == 0) part[1] = m2;
+  cl.sync();
+  float var = 0.0f;
+  for (unsigned k = 0; k < ncl; ++k) var += *cl.map_shared_rank(&part[1], k);
+  const float inv = 1.0f / sqrtf(var / static_cast<float>(len) + eps);
+  float* o = y + base + off;
+  const bool vec = !a.per_channel && a.act < 0 && (n & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0 &&
+                   (a.gamma == nullptr || (reinterpret_cast<uintptr_t>(a.gamma + off) & 15) == 0) &&
+                   (a.beta == nullptr || (reinterpret_cast<uintptr_t>(a.beta + off) & 15) == 0) &&
+                   (a.residual == nullptr || (reinterpret_cast<uintptr_t>(a.residual + base + off) & 15) == 0);
+  if (vec) {
+    const float4* s4 = reinterpret_cast<const float4*>(sx);
+    const float4* g4 = a.gamma ? reinterpret_cast<const float4*>(a.gamma + off) : nullptr;
+    const float4* b4 = a.beta ? reinterpret_cast<const float4*>(a.beta + off) : nullptr;
+    const float4* r4 = a.residual ? reinterpret_cast<const float4*>(a.residual + base + off) : nullptr;
+    for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+      const float4 v = s4[i];
+      float4 r = make_float4((v.x - mean) * inv, (v.y - mean) * inv, (v.z - mean) * inv, (v.w - mean) * inv);
+      if (g4 != nullptr) {
+        const float4 w = __ldg(g4 + i);
+        r.x *= w.x; r.y *= w.y; r.z *= w.z; r.w *= w.w;
+        if (b4 != nullptr) {
+          const float4 b = __ldg(b4 + i);
+          r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
+        }
+      }
+      if (r4 != nullptr) {
+        const float4 t = __ldg(r4 + i);
+        r.x += t.x; r.y += t.y; r.z += t.z; r.w += t.w;
+      }
+      __stcs(reinterpret_cast<float4*>(o) + i, r);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = finish((sx[i] - mean) * inv, off + i, row, base, a);
+  }
+  cl.sync();  // nobody leaves while a neighbour may still read its partial sums
+}
+
 template <int FAM, int THREADS>
 __global__ void __launch_bounds__(THREADS, (THREADS <= 512) ? 2 : 1) sweep_row_kernel(RowParams p) {
   __shared__ float red[33];
@@ -953,6 +1025,32 @@ int meanvar_dispatch(const float* x, float* y, long long rows, long long len, fl
     RowParams p{};
     p.x = x; p.y = y; p.rows = rows; p.len = len; p.eps = eps; p.aff = a;
     return launch_sweep_rows<FAM_MEANVAR>(p, st);
+  }
+  static const bool no_cluster = [] { const char* e = getenv("MIMIR_B200_NORM_CLUSTER"); return e && e[0] == '0'; }();
+  if (!no_cluster && len <= 8ll * CLUSTER_SLICE_MAX && rows * 8 < 0x7fffffffLL) {
+    int ncl = 1;
+    while (ncl < 8 && (len + ncl - 1) / ncl > 4096) ncl *= 2;  // ~16 KB per CTA, at most the portable cluster size
+    const int slice = static_cast<int>(((len + ncl - 1) / ncl + 3) & ~3ll);
+    static bool attr_set = false;
+    if (!attr_set) {  // static + dynamic shared memory of the largest slice is just above the 48 KB default
+      MB_CUDA(cudaFuncSetAttribute(meanvar_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CLUSTER_SLICE_MAX * 4));
+      attr_set = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(rows * ncl));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = static_cast<size_t>(slice) * sizeof(float);
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = static_cast<unsigned>(ncl);
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, meanvar_cluster_kernel, x, y, len, slice, eps, a));
+    count_launch();
+    return MIMIR_B200_OK;
   }
   const int chunks = static_cast<int>((len + CHUNK - 1) / CHUNK);
   float* part;

@@ -172,7 +172,7 @@ def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
         np.testing.assert_allclose(got, [2, 4, 6, 8], atol=1e-6)
 
 
-@pytest.mark.parametrize("rows,n", [(4, 300), (3, 768), (2, 32768), (1, 40000), (9, 5)])
+@pytest.mark.parametrize("rows,n", [(4, 300), (3, 768), (2, 32768), (1, 40000), (9, 5), (3, 98304), (5, 98301), (2, 200000), (150, 5000)])
 def test_layernorm(backend, rows, n):
     r = rng(n)
     x = (r.standard_normal(rows * n) * 2 + 0.5).astype(np.float32)
