@@ -315,6 +315,25 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
 int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInput* inputs,
                                     int n_inputs, int batch, float* out_dev, uint64_t out_capacity,
                                     uint64_t* out_len, void* stream);
+/* Incremental decoding with a key / value cache.  The reference has none (its user guide says so,
+ * docs/02-User-Guide/12-Transformer-GPT.md:34-37): generating token by token there re-runs the whole prefix
+ * through Model::forwardPass.  For graphs whose layers all act per token (Embedding, Linear with seq_len,
+ * LayerNorm with in_features, activations, element-wise layers, CAUSAL self-attention) row t of that full
+ * forward depends on tokens 0..t only, so it can be produced from token t alone plus cached keys and values.
+ *   decode_begin: on a planned model (pipeline 1); `inputs` declares the PER-TOKEN input sizes (data unused).
+ *                 Builds a one-token plan that shares the model's weights and allocates caches of `max_seq`
+ *                 positions per attention layer (2 * batch * max_seq * embed floats each; total in *cache_bytes).
+ *                 E_UNSUPPORTED names the first layer that does not act per token (e.g. a whole-sample RMSNorm).
+ *   prefill:      after decode_begin every mimir_b200_model_forward / _forward_device of the model itself (same
+ *                 batch, seq_len <= max_seq) also stores its keys and values at positions 0 .. seq_len-1.
+ *   decode_step:  one token per sample at position `pos` (0-based; the caches must hold positions 0 .. pos-1 of the
+ *                 same sequences); returns what row `pos` of the full causal forward would be.
+ *   decode_end:   frees the caches.  A new plan or upload_weights invalidates the decode state: call decode_begin again. */
+int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs,
+                                  int batch, int max_seq, uint64_t* cache_bytes);
+int mimir_b200_model_decode_step(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs,
+                                 int batch, int pos, float* out_host, uint64_t out_capacity, uint64_t* out_len);
+int mimir_b200_model_decode_end(MimirB200ModelHandle m);
 /* Per-position argmax over rows of `n` (first maximum wins), for token ids.  No counterpart layer
  * in the reference (harness step of the decoder config). */
 int mimir_b200_argmax_rows_device(const float* x_dev, int32_t* ids_dev, long long rows, int n,

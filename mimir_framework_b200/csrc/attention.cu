@@ -30,9 +30,10 @@ flash_attn_fp32_kernel(const AttnView a, float* __restrict__ out, int embed, int
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   const int seq = a.q_len, kvn = a.kv_len;
   const long long ldq = a.ldq, ldk = a.ldkv;
-  const float* qb = a.q + static_cast<long long>(b) * seq * ldq + h * HD;
-  const float* kb = a.k + static_cast<long long>(b) * kvn * ldk + h * HD;
-  const float* vb = a.v + static_cast<long long>(b) * kvn * ldk + h * HD;
+  const long long qbs = a.q_bstride ? a.q_bstride : seq * ldq, kbs = a.kv_bstride ? a.kv_bstride : kvn * ldk;
+  const float* qb = a.q + b * qbs + h * HD;
+  const float* kb = a.k + b * kbs + h * HD;
+  const float* vb = a.v + b * kbs + h * HD;
 
   // Q tile, transposed into Qt (rows past q_len are zero)
   for (int i = tid; i < BQ * (HD / 4); i += 256) {
@@ -163,11 +164,12 @@ __global__ void attn_row_kernel(const AttnView a, float* __restrict__ out, int e
   const int seq = a.q_len, kvn = a.kv_len;
   const int nr = min(AR, seq - i0);  // query rows of this group
   const long long ld = a.ldkv;
-  const float* kb = a.k + static_cast<long long>(b) * kvn * ld + h * hd;
-  const float* vb = a.v + static_cast<long long>(b) * kvn * ld + h * hd;
+  const long long qbs = a.q_bstride ? a.q_bstride : seq * a.ldq, kbs = a.kv_bstride ? a.kv_bstride : kvn * ld;
+  const float* kb = a.k + b * kbs + h * hd;
+  const float* vb = a.v + b * kbs + h * hd;
   for (int t = threadIdx.x; t < AR * hd; t += blockDim.x) {
     const int r = t / hd, d = t - r * hd;
-    q[t] = (r < nr) ? a.q[(static_cast<long long>(b) * seq + i0 + r) * a.ldq + h * hd + d] : 0.0f;
+    q[t] = (r < nr) ? a.q[b * qbs + (i0 + r) * a.ldq + h * hd + d] : 0.0f;
   }
   __syncthreads();
   // keys this group can see: row i0 + r sees min(i0 + r + 1, kvn) of them under the causal mask
@@ -276,9 +278,13 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
   const float scale = 1.0f / sqrtf(static_cast<float>(hd));
   const bool aligned = (((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) == 0) &&
                        (embed % 4 == 0) && (a.ldq % 4 == 0) && (a.ldkv % 4 == 0) && batch <= 65535 && heads <= 65535;
-  if (aligned && hd == 32) return launch_flash<32>(a, out, batch, embed, heads, causal, scale, st);
-  if (aligned && hd == 64) return launch_flash<64>(a, out, batch, embed, heads, causal, scale, st);
-  if (aligned && hd == 128) return launch_flash<128>(a, out, batch, embed, heads, causal, scale, st);
+  // a query tile of 64 rows would be almost empty for a decode step: the row kernel reads K and V once, a warp per key
+  const bool few_rows = a.q_len <= 2 && static_cast<size_t>(AR) * (hd + a.kv_len) * 4 <= 200 * 1024;
+  if (!few_rows) {
+    if (aligned && hd == 32) return launch_flash<32>(a, out, batch, embed, heads, causal, scale, st);
+    if (aligned && hd == 64) return launch_flash<64>(a, out, batch, embed, heads, causal, scale, st);
+    if (aligned && hd == 128) return launch_flash<128>(a, out, batch, embed, heads, causal, scale, st);
+  }
   const size_t smem = static_cast<size_t>(AR) * (hd + a.kv_len) * 4;
   if (smem > 200 * 1024 || batch > 65535 || heads > 65535)
     return fail(MIMIR_B200_E_UNSUPPORTED, "attention: %d keys with head_dim %d exceed the row kernel's shared memory", a.kv_len, hd);
@@ -289,6 +295,33 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
   }
   dim3 grid((a.q_len + AR - 1) / AR, heads, batch);
   attn_row_kernel<<<grid, 256, smem, st>>>(a, out, embed, heads, hd, causal, scale);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+namespace {
+__global__ void kv_cache_write_kernel(const float* __restrict__ qkv, float* __restrict__ kcache, float* __restrict__ vcache, long long total,
+                                      int seq, int embed, int max_seq, int pos0) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int d = static_cast<int>(i % embed);
+    const long long row = i / embed;  // b * seq + s
+    const long long b = row / seq, s = row - b * seq;
+    const long long dst = (b * max_seq + pos0 + s) * embed + d;
+    kcache[dst] = __ldg(qkv + row * 3 * embed + embed + d);
+    vcache[dst] = __ldg(qkv + row * 3 * embed + 2 * embed + d);
+  }
+}
+}  // namespace
+
+int launch_kv_cache_write(const float* qkv, float* kcache, float* vcache, int batch, int seq, int embed, int max_seq, int pos0,
+                          cudaStream_t st) {
+  if (pos0 < 0 || pos0 + seq > max_seq) return fail(MIMIR_B200_E_INVALID, "KV cache: positions %d..%d exceed the cache of %d", pos0, pos0 + seq - 1, max_seq);
+  const long long total = static_cast<long long>(batch) * seq * embed;
+  long long blocks = (total + 255) / 256;
+  if (blocks > ctx().sm_count * 16LL) blocks = ctx().sm_count * 16LL;
+  kv_cache_write_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(qkv, kcache, vcache, total, seq, embed, max_seq, pos0);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;

@@ -164,6 +164,17 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   g.a = e.x_split ? e.x_split : xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
   g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
   MB_TRY(launch_gemm(g, st));
+  if (e.kcache) MB_TRY(launch_kv_cache_write(qkv, e.kcache, e.vcache, e.batch, e.seq, e.embed, e.max_seq, e.decode_pos < 0 ? 0 : e.decode_pos, st));
+  if (e.decode_pos >= 0) {
+    // one new token per sample against the cached keys and values (all of them are in its past)
+    if (!e.kcache || e.seq != 1) return fail(MIMIR_B200_E_INVALID, "attention: a decode step needs a cache and one token per sample");
+    AttnView a;
+    a.q = qkv; a.ldq = 3LL * e.embed; a.q_len = 1;
+    a.k = e.kcache; a.v = e.vcache; a.ldkv = e.embed; a.kv_len = e.decode_pos + 1;
+    a.kv_bstride = static_cast<long long>(e.max_seq) * e.embed;
+    MB_TRY(launch_attention_core_view(a, att, e.batch, e.embed, e.heads, 0, st));
+    MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));
+  } else
   // the attended rows go to the output projection as operand planes (the x planes are dead by now)
   if (attention_tc_supported(e.seq, e.embed, e.heads)) {
     MB_TRY(launch_attention_core_tc(qkv, nullptr, e.batch, e.seq, e.embed, e.heads, e.causal, tc_ws, st, xs, ap));

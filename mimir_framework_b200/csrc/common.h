@@ -140,7 +140,11 @@ struct AttnView {
   const float* v = nullptr;
   long long ldq = 0, ldkv = 0;
   int q_len = 0, kv_len = 0;
+  long long q_bstride = 0, kv_bstride = 0;  // elements between samples; 0 = q_len * ldq / kv_len * ldkv
 };
+// K and V thirds of qkv [batch*seq][3E] -> cache[b][pos0 + s][E] of caches holding max_seq positions per sample
+int launch_kv_cache_write(const float* qkv, float* kcache, float* vcache, int batch, int seq, int embed, int max_seq, int pos0,
+                          cudaStream_t st);
 // qkv fp32 [batch*seq, 3E] (Q | K | V thirds) -> attended fp32 [batch*seq, E]
 int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
                           cudaStream_t st);

@@ -124,6 +124,11 @@ struct LayerRT {
   bool read_split = false;            // Linear reads the producer's planes
   int res_v = -1;                     // residual tensor folded in from a following Add
   int pre_norm = -1;                  // Conv2d: index of the GroupNorm layer applied while its operand planes are laid out
+  // decode twin (see mimir_b200_model_decode_begin): weights borrowed from the main model, key / value caches owned
+  bool borrowed_f32 = false, borrowed_planes = false;
+  float* kcache = nullptr;
+  float* vcache = nullptr;
+  size_t cache_bytes = 0;
   size_t ws_off = 0, ws_bytes = 0;
   // resolved shapes (per sample)
   int rows_ps = 1, in_f = 0, out_f = 0;       // Linear
@@ -232,6 +237,12 @@ struct MimirB200Model {
   };
   std::vector<CachedGraph> graphs;
   cudaStream_t s_capture = nullptr;
+  // Incremental decoding: a second plan of the same layers for ONE token per sample, sharing this model's weights,
+  // whose attention layers keep their keys and values in caches of max_seq positions.
+  MimirB200Model* decode = nullptr;
+  bool is_twin = false;
+  int decode_pos = 0, max_seq = 0;
+  uint64_t plan_epoch = 0, twin_epoch = 0;
 };
 
 namespace mb {
@@ -253,6 +264,8 @@ int root_of(const std::vector<TensorV>& ts, int v) {
 }
 
 void free_layer_weights(LayerRT& L, MimirB200Model* m) {
+  if (L.borrowed_f32) L.w_f32 = nullptr;
+  if (L.borrowed_planes) L.w_split = L.w_split2 = L.w_split3 = nullptr;
   if (L.w_f32) { dev_free(L.w_f32, L.w_count * 4); m->weight_bytes -= L.w_count * 4; L.w_f32 = nullptr; }
   if (L.w_split) { dev_free(L.w_split, L.w_split_bytes); m->weight_bytes -= L.w_split_bytes; L.w_split = nullptr; }
   if (L.w_split2) { dev_free(L.w_split2, L.w_split2_bytes); m->weight_bytes -= L.w_split2_bytes; L.w_split2 = nullptr; }
@@ -676,6 +689,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
   batch = batch / m->pipeline;  // everything below is sized for one micro-batch
   const int nl = static_cast<int>(m->layers.size());
   drop_graphs(m);  // offsets, fusion decisions and operand planes may all change
+  if (!m->is_twin) ++m->plan_epoch;  // a decode twin made before this plan is stale
   m->tensors.clear();
   m->input_v.clear();
   m->planned_batch = 0;
@@ -1034,6 +1048,13 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         if (L.read_split) e.x_split = splitp(L.in_v[0]); else e.x = f32p(L.in_v[0]);
         e.wqkv_split = L.w_split; e.wout_split = L.w_split2; e.y = f32p(L.out_v); e.ws = ws;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
+        if (m->is_twin) {
+          e.kcache = L.kcache; e.vcache = L.vcache; e.max_seq = m->max_seq; e.decode_pos = m->decode_pos;
+        } else if (m->decode && m->decode->twin_epoch == m->plan_epoch && batch == m->decode->planned_batch && L.seq <= m->decode->max_seq) {
+          // a full forward of the main model doubles as the prefill: its keys and values land in the caches
+          const LayerRT& T = m->decode->layers[static_cast<size_t>(li)];
+          e.kcache = T.kcache; e.vcache = T.vcache; e.max_seq = m->decode->max_seq;
+        }
         s = attention_exec(e, st);
         break;
       }
@@ -1214,7 +1235,7 @@ bool graphs_enabled() {
 // performs every one-time host-side setup the launch helpers do); the second is captured on a private stream;
 // from then on the instantiated graph is launched into the caller's stream.
 int run_layers_cached(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, uint8_t* arena) {
-  if (!graphs_enabled() || ctx().prof_gemm) return run_layers(m, batch, bnd, st, arena);
+  if (!graphs_enabled() || ctx().prof_gemm || m->is_twin) return run_layers(m, batch, bnd, st, arena);  // (a twin's position changes per call)
   std::vector<const void*> key;
   key.reserve(bnd.in_ptr.size() + 3);
   key.push_back(reinterpret_cast<const void*>(static_cast<uintptr_t>(batch)));
@@ -1329,6 +1350,15 @@ int mimir_b200_model_create(const MimirLayerDesc* layers, int n_layers, MimirB20
 }
 
 static void destroy_model(MimirB200Model* m) {
+  if (m->decode) {
+    destroy_model(m->decode);
+    m->decode = nullptr;
+  }
+  for (auto& L : m->layers) {
+    if (L.kcache) dev_free(L.kcache, L.cache_bytes);
+    if (L.vcache) dev_free(L.vcache, L.cache_bytes);
+    L.kcache = L.vcache = nullptr;
+  }
   drop_graphs(m);
   if (m->s_capture) cudaStreamDestroy(m->s_capture);
   for (auto& L : m->layers) free_layer_weights(L, m);
@@ -1532,6 +1562,93 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
   g_stats.flops_last_forward = m->flops * P;
   g_stats.bytes_last_forward = m->hbm_bytes * P;
   return MIMIR_B200_OK;
+}
+
+// ---- incremental decoding ---------------------------------------------------------------------------
+// The reference has no key / value cache (its documentation names the absence); a caller that generates token by
+// token re-runs the whole prefix.  For graphs whose layers all act per token - Embedding, Linear with seq_len, LayerNorm
+// with in_features, activations, element-wise layers, causal self-attention - row t of the full causal forward depends
+// only on tokens 0..t, so one token per step against cached keys and values gives the same row.
+static int token_wise(const LayerRT& L) {
+  switch (L.lt) {
+    case LT::Alias: case LT::Act: case LT::Add: case LT::Multiply: case LT::Binary2: case LT::Embedding:
+      return MIMIR_B200_OK;
+    case LT::Linear:
+      if (L.d.seq_len > 0) return MIMIR_B200_OK;
+      return fail(MIMIR_B200_E_UNSUPPORTED, "decode: Linear '%s' runs over the flattened sequence (seq_len = 0), not per token", L.name.c_str());
+    case LT::LayerNorm:
+      if (L.d.in_features > 0) return MIMIR_B200_OK;
+      return fail(MIMIR_B200_E_UNSUPPORTED, "decode: LayerNorm '%s' normalises the whole sample (in_features = 0), not one token", L.name.c_str());
+    case LT::Attention:
+      if (L.d.causal) return MIMIR_B200_OK;
+      return fail(MIMIR_B200_E_UNSUPPORTED, "decode: attention '%s' is not causal: every row depends on later tokens", L.name.c_str());
+    default:
+      return fail(MIMIR_B200_E_UNSUPPORTED, "decode: layer '%s' of type '%s' does not act per token", L.name.c_str(), L.type.c_str());
+  }
+}
+
+int mimir_b200_model_decode_end(MimirB200ModelHandle m) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (m->decode) {
+    cudaDeviceSynchronize();
+    destroy_model(m->decode);
+    m->decode = nullptr;
+    drop_graphs(m);  // captured forwards may write into the caches that just went away
+  }
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, int max_seq,
+                                  uint64_t* cache_bytes) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (m->is_twin) return fail(MIMIR_B200_E_INVALID, "decode_begin: not a model handle");
+  if (m->planned_batch <= 0) return fail(MIMIR_B200_E_INVALID, "decode_begin: plan the model first (its operand planes are shared)");
+  if (m->pipeline != 1) return fail(MIMIR_B200_E_UNSUPPORTED, "decode_begin: set_pipeline(1) first");
+  if (!inputs || n_inputs <= 0 || batch <= 0 || max_seq <= 0) return fail(MIMIR_B200_E_INVALID, "decode_begin: bad arguments");
+  MB_TRY(mimir_b200_model_decode_end(m));
+  for (const auto& L : m->layers) MB_TRY(token_wise(L));
+  auto t = std::make_unique<MimirB200Model>();
+  t->is_twin = true;
+  t->precision = m->precision;
+  t->max_seq = max_seq;
+  t->layers = m->layers;  // descriptors, classification and weight pointers
+  uint64_t bytes = 0;
+  int status = MIMIR_B200_OK;
+  for (auto& L : t->layers) {
+    L.borrowed_f32 = true;
+    L.borrowed_planes = (L.w_split != nullptr);
+    L.kcache = L.vcache = nullptr;
+    if (L.d.seq_len > 0) L.d.seq_len = 1;  // one token per sample and step
+  }
+  status = plan_model(t.get(), inputs, n_inputs, batch);
+  for (auto& L : t->layers) {
+    if (status != MIMIR_B200_OK) break;
+    if (L.lt != LT::Attention) continue;
+    L.cache_bytes = static_cast<size_t>(batch) * max_seq * L.embed * sizeof(float);
+    status = dev_alloc(reinterpret_cast<void**>(&L.kcache), L.cache_bytes, "key cache");
+    if (status == MIMIR_B200_OK) status = dev_alloc(reinterpret_cast<void**>(&L.vcache), L.cache_bytes, "value cache");
+    bytes += 2 * L.cache_bytes;
+  }
+  if (status != MIMIR_B200_OK) {
+    destroy_model(t.release());
+    return status;
+  }
+  t->twin_epoch = m->plan_epoch;
+  m->decode = t.release();
+  drop_graphs(m);  // forwards captured so far do not fill the caches
+  if (cache_bytes) *cache_bytes = bytes;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_decode_step(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, int pos,
+                                 float* out_host, uint64_t out_capacity, uint64_t* out_len) {
+  if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
+  if (!m->decode) return fail(MIMIR_B200_E_INVALID, "decode_step: decode_begin has not been called");
+  if (m->decode->twin_epoch != m->plan_epoch || m->planned_batch <= 0)
+    return fail(MIMIR_B200_E_INVALID, "decode_step: the model was planned or its weights changed since decode_begin; call decode_begin again");
+  if (pos < 0 || pos >= m->decode->max_seq) return fail(MIMIR_B200_E_INVALID, "decode_step: position %d outside the cache of %d", pos, m->decode->max_seq);
+  m->decode->decode_pos = pos;
+  return mimir_b200_model_forward(m->decode, inputs, n_inputs, batch, out_host, out_capacity, out_len);
 }
 
 // Cuts the batch of the host-pointer forward into `micro_batches` pieces that overlap their

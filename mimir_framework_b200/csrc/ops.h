@@ -42,6 +42,13 @@ struct AttentionExec {
   const float* residual = nullptr;
   float* y = nullptr;
   void* ws = nullptr;
+  // Key / value cache [batch][max_seq][embed] (optional).  decode_pos < 0: a normal forward that also stores its K and V
+  // rows at positions 0 .. seq-1.  decode_pos >= 0: seq must be 1; the new token's K and V go to that position and
+  // the query attends to positions 0 .. decode_pos.
+  float* kcache = nullptr;
+  float* vcache = nullptr;
+  int max_seq = 0;
+  int decode_pos = -1;
 };
 size_t attention_ws_bytes(int batch, int seq, int embed, int heads, int precision);
 int attention_exec(const AttentionExec& e, cudaStream_t st);

@@ -70,6 +70,9 @@ _SIGS = {
     "mimir_b200_model_plan": [_P, _P, C.c_int, C.c_int, _P],
     "mimir_b200_model_forward": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P],
     "mimir_b200_model_forward_device": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P, _P],
+    "mimir_b200_model_decode_begin": [_P, _P, C.c_int, C.c_int, C.c_int, _P],
+    "mimir_b200_model_decode_step": [_P, _P, C.c_int, C.c_int, C.c_int, _P, C.c_uint64, _P],
+    "mimir_b200_model_decode_end": [_P],
     "mimir_b200_argmax_rows_device": [_P, _P, C.c_longlong, C.c_int, _P],
     "mimir_b200_get_stats": [_P],
     "mimir_b200_check_device": [_P],
@@ -428,6 +431,28 @@ class GraphModel:
         n = C.c_uint64(0)
         check(lib().mimir_b200_model_forward(self._h, C.addressof(arr), len(spec), batch, _p(out), out.size, C.byref(n)))
         return out.reshape(batch, n.value) if n.value * batch == out.size else out
+
+    def decode_begin(self, spec: dict, batch: int, max_seq: int) -> int:
+        """spec: name -> (per-TOKEN size, broadcast).  Returns the bytes of the key / value caches."""
+        arr = self._inputs({k: (0, per, bc) for k, (per, bc) in spec.items()})
+        nbytes = C.c_uint64(0)
+        check(lib().mimir_b200_model_decode_begin(self._h, C.addressof(arr), len(spec), batch, max_seq, C.byref(nbytes)))
+        return nbytes.value
+
+    def decode_step(self, inputs: dict, batch: int, pos: int, out_per_sample: int) -> np.ndarray:
+        """inputs: name -> (numpy array holding ONE token per sample, broadcast flag)."""
+        spec = {}
+        for k, (a, bc) in inputs.items():
+            a = _f(a)
+            spec[k] = (a, a.size if bc else a.size // batch, bc)
+        arr = self._inputs(spec)
+        out = np.empty(batch * out_per_sample, np.float32)
+        n = C.c_uint64(0)
+        check(lib().mimir_b200_model_decode_step(self._h, C.addressof(arr), len(spec), batch, pos, _p(out), out.size, C.byref(n)))
+        return out.reshape(batch, n.value) if n.value * batch == out.size else out
+
+    def decode_end(self):
+        check(lib().mimir_b200_model_decode_end(self._h))
 
     def forward_host_ptrs(self, spec: dict, batch: int, out_ptr: int, out_capacity: int) -> int:
         """spec: name -> (host address, per_sample, broadcast).  For pinned buffers."""
