@@ -134,23 +134,30 @@ def round_to_bf16(a: np.ndarray) -> np.ndarray:
 DECODER_CFG = dict(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=1024)
 
 
-def gpt_decoder(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=1024):
+def gpt_decoder(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=1024, norm="rms"):
     """Embedding -> layers x [RMSNorm -> MultiHeadAttention(causal) -> Add -> RMSNorm -> Linear -> GELU ->
     Linear -> Add] -> RMSNorm -> Linear (LM head), token-wise layers (`seq_len` set) like the
     reference's ViT / SD3.5 builders.  RMSNorm is the reference's whole-tensor form with one gamma per
     element (`params_count = seq * d_model`)."""
     E, S = d_model, seq
+
+    def norm_desc(name, src, dst):
+        # "layer": token-wise LayerNorm (in_features = E), the form under which every row depends on its own past only
+        if norm == "layer":
+            return make_desc(name, "LayerNorm", inputs=[src], output=dst, in_features=E, affine=1, use_bias=1, params_count=2 * E)
+        return make_desc(name, "RMSNorm", inputs=[src], output=dst, params_count=S * E)
+
     d = [make_desc("dec/tok_embed", "Embedding", inputs=["__input__"], output="dec/h0", vocab_size=vocab, embed_dim=E,
                    padding_idx=-1, params_count=vocab * E)]
     x = "dec/h0"
     for i in range(layers):
         b = f"dec/block{i}"
         d += [
-            make_desc(f"{b}/norm1", "RMSNorm", inputs=[x], output=f"{b}/n1", params_count=S * E),
+            norm_desc(f"{b}/norm1", x, f"{b}/n1"),
             make_desc(f"{b}/attn", "MultiHeadAttention", inputs=[f"{b}/n1"], output=f"{b}/a", seq_len=S, embed_dim=E,
                       num_heads=heads, causal=1, params_count=4 * E * E),
             make_desc(f"{b}/add1", "Add", inputs=[x, f"{b}/a"], output=f"{b}/r1"),
-            make_desc(f"{b}/norm2", "RMSNorm", inputs=[f"{b}/r1"], output=f"{b}/n2", params_count=S * E),
+            norm_desc(f"{b}/norm2", f"{b}/r1", f"{b}/n2"),
             make_desc(f"{b}/fc1", "Linear", inputs=[f"{b}/n2"], output=f"{b}/f1", in_features=E, out_features=ffn, seq_len=S,
                       use_bias=1, params_count=E * ffn + ffn),
             make_desc(f"{b}/gelu", "GELU", inputs=[f"{b}/f1"], output=f"{b}/f1a"),
@@ -159,7 +166,7 @@ def gpt_decoder(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=102
             make_desc(f"{b}/add2", "Add", inputs=[f"{b}/r1", f"{b}/f2"], output=f"{b}/r2"),
         ]
         x = f"{b}/r2"
-    d += [make_desc("dec/norm_f", "RMSNorm", inputs=[x], output="dec/nf", params_count=S * E),
+    d += [norm_desc("dec/norm_f", x, "dec/nf"),
           make_desc("dec/lm_head", "Linear", inputs=["dec/nf"], output="x", in_features=E, out_features=vocab, seq_len=S,
                     use_bias=0, params_count=E * vocab)]
     return d

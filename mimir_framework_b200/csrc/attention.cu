@@ -178,24 +178,38 @@ __global__ void attn_row_kernel(const AttnView a, float* __restrict__ out, int e
   float mx[AR];
 #pragma unroll
   for (int r = 0; r < AR; ++r) mx[r] = -1e30f;
-  for (int j = w; j < n_keys; j += nw) {  // one warp per key: coalesced reads of the K row
-    const float* kr = kb + j * ld;
-    float dot[AR];
+  constexpr int KU = 4;  // keys per warp and pass: their K rows are loaded together, so four loads are in flight per lane
+  for (int j0 = w * KU; j0 < n_keys; j0 += nw * KU) {  // a warp per key: coalesced reads of the K rows
+    float dot[KU][AR];
 #pragma unroll
-    for (int r = 0; r < AR; ++r) dot[r] = 0.0f;
+    for (int u = 0; u < KU; ++u)
+#pragma unroll
+      for (int r = 0; r < AR; ++r) dot[u][r] = 0.0f;
     for (int d = lane; d < hd; d += 32) {
-      const float kv = __ldg(kr + d);
+      float kv[KU];
 #pragma unroll
-      for (int r = 0; r < AR; ++r) dot[r] += q[r * hd + d] * kv;
+      for (int u = 0; u < KU; ++u) kv[u] = (j0 + u < n_keys) ? __ldg(kb + static_cast<long long>(j0 + u) * ld + d) : 0.0f;
+#pragma unroll
+      for (int r = 0; r < AR; ++r) {
+        const float qv = q[r * hd + d];
+#pragma unroll
+        for (int u = 0; u < KU; ++u) dot[u][r] += qv * kv[u];
+      }
     }
 #pragma unroll
-    for (int r = 0; r < AR; ++r) {
+    for (int u = 0; u < KU; ++u) {
+      const int j = j0 + u;
+      if (j >= n_keys) break;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], o);
-      const bool visible = !causal || j <= i0 + r;
-      const float s = dot[r] * scale;
-      if (lane == 0) p[r * kvn + j] = visible ? s : -INFINITY;  // exp(-inf - max) = 0, like the reference's -1e9
-      if (visible) mx[r] = fmaxf(mx[r], s);
+      for (int r = 0; r < AR; ++r) {
+        float dv = dot[u][r];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dv += __shfl_xor_sync(0xffffffffu, dv, o);
+        const bool visible = !causal || j <= i0 + r;
+        const float sc = dv * scale;
+        if (lane == 0) p[r * kvn + j] = visible ? sc : -INFINITY;  // exp(-inf - max) = 0, like the reference's -1e9
+        if (visible) mx[r] = fmaxf(mx[r], sc);
+      }
     }
   }
   // block max per row
@@ -238,19 +252,58 @@ __global__ void attn_row_kernel(const AttnView a, float* __restrict__ out, int e
     if (lane == 0) red[w][32] = t;
   }
   __syncthreads();
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    const float* vr = vb + d;
+  // O = P V.  A thread owns one output column; when the head is narrower than the CTA the keys are dealt to
+  // G = blockDim / hd groups of threads whose partial sums meet in shared memory (the Q rows there are dead by
+  // now) in group order, so the result does not depend on timing.  Four V loads are in flight per thread.
+  const int G = (hd < static_cast<int>(blockDim.x)) ? static_cast<int>(blockDim.x) / hd : 1;
+  const int g = static_cast<int>(threadIdx.x) / hd;
+  float* accs = q;  // [AR][hd]
+  for (int d0 = 0; d0 < hd; d0 += blockDim.x) {
+    const int d = (G > 1) ? static_cast<int>(threadIdx.x) - g * hd : d0 + static_cast<int>(threadIdx.x);
+    const bool active = (G > 1) ? (g < G) : (d < hd);
     float o[AR];
 #pragma unroll
     for (int r = 0; r < AR; ++r) o[r] = 0.0f;
-    for (int j = 0; j < n_keys; ++j) {
-      const float v = __ldg(vr + j * ld);
+    if (active) {
+      const float* vr = vb + d;
+      int j = g;
+      for (; j + 3 * G < n_keys; j += 4 * G) {
+        const float v0 = __ldg(vr + static_cast<long long>(j) * ld), v1 = __ldg(vr + static_cast<long long>(j + G) * ld),
+                    v2 = __ldg(vr + static_cast<long long>(j + 2 * G) * ld), v3 = __ldg(vr + static_cast<long long>(j + 3 * G) * ld);
 #pragma unroll
-      for (int r = 0; r < AR; ++r) o[r] += p[r * kvn + j] * v;
+        for (int r = 0; r < AR; ++r) {
+          const float* pr = p + r * kvn + j;
+          o[r] += pr[0] * v0;
+          o[r] += pr[G] * v1;
+          o[r] += pr[2 * G] * v2;
+          o[r] += pr[3 * G] * v3;
+        }
+      }
+      for (; j < n_keys; j += G) {
+        const float v = __ldg(vr + static_cast<long long>(j) * ld);
+#pragma unroll
+        for (int r = 0; r < AR; ++r) o[r] += p[r * kvn + j] * v;
+      }
     }
+    if (G > 1) {
+      for (int gg = 0; gg < G; ++gg) {
+        __syncthreads();
+        if (active && g == gg) {
 #pragma unroll
-    for (int r = 0; r < AR; ++r)
-      if (r < nr) out[(static_cast<long long>(b) * seq + i0 + r) * embed + h * hd + d] = o[r] * (1.0f / (red[r][32] + 1e-9f));
+          for (int r = 0; r < AR; ++r) accs[r * hd + d] = (gg == 0) ? o[r] : accs[r * hd + d] + o[r];
+        }
+      }
+      __syncthreads();
+      if (active && g == 0) {
+#pragma unroll
+        for (int r = 0; r < AR; ++r) o[r] = accs[r * hd + d];
+      }
+    }
+    if (active && (G == 1 || g == 0)) {
+#pragma unroll
+      for (int r = 0; r < AR; ++r)
+        if (r < nr) out[(static_cast<long long>(b) * seq + i0 + r) * embed + h * hd + d] = o[r] * (1.0f / (red[r][32] + 1e-9f));
+    }
   }
 }
 
@@ -314,6 +367,160 @@ __global__ void kv_cache_write_kernel(const float* __restrict__ qkv, float* __re
   }
 }
 }  // namespace
+
+// ---- one query row per (sample, head) against a long key / value cache: the decode step ---------------
+// The keys are cut into chunks of 128; a CTA of 128 threads takes one chunk of one (sample, head): a thread per key
+// computes the score with 128-bit loads along its own K row (every load independent: hd / 4 in flight per
+// thread), the chunk's softmax terms go through shared memory, then the threads regroup as (quad of output
+// columns, key group) to accumulate P V with coalesced 128-bit loads of the V rows.  Each chunk leaves
+// (max, sum, unnormalised O) in a scratch; a second kernel merges the chunks in chunk order.
+namespace {
+constexpr int DEC_CHUNK = 128;
+
+__global__ void __launch_bounds__(DEC_CHUNK) attn_decode_chunk_kernel(const AttnView a, float* __restrict__ scratch, int heads, int hd,
+                                                                     float scale) {
+  extern __shared__ __align__(16) float dsm[];
+  float* q = dsm;                  // [hd]
+  float* pj = dsm + hd;            // [DEC_CHUNK]
+  float* part = pj + DEC_CHUNK;    // [groups][hd]
+  __shared__ float red[33];
+  const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
+  const int kvn = a.kv_len, k0 = chunk * DEC_CHUNK;
+  const int nk = min(DEC_CHUNK, kvn - k0);
+  const long long ld = a.ldkv;
+  const long long qbs = a.q_bstride ? a.q_bstride : a.q_len * a.ldq, kbs = a.kv_bstride ? a.kv_bstride : static_cast<long long>(kvn) * ld;
+  const float* kb = a.k + b * kbs + h * hd + static_cast<long long>(k0) * ld;
+  const float* vb = a.v + b * kbs + h * hd + static_cast<long long>(k0) * ld;
+  for (int d = t; d < hd; d += DEC_CHUNK) q[d] = a.q[b * qbs + h * hd + d];
+  __syncthreads();
+  const int nq = hd >> 2;
+  float sc = -1e30f;
+  if (t < nk) {
+    const float4* kr = reinterpret_cast<const float4*>(kb + static_cast<long long>(t) * ld);
+    float dot = 0.0f;
+    for (int c0 = 0; c0 < nq; c0 += 8) {  // eight loads ahead of their use; d ascending like the reference's dot product
+      float4 kv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) kv[u] = (c0 + u < nq) ? __ldg(kr + c0 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (c0 + u < nq) {
+          const float4 qv = *reinterpret_cast<const float4*>(q + 4 * (c0 + u));
+          dot += qv.x * kv[u].x; dot += qv.y * kv[u].y; dot += qv.z * kv[u].z; dot += qv.w * kv[u].w;
+        }
+      }
+    }
+    sc = dot * scale;
+  }
+  // chunk maximum and sum (128 threads = 4 warps)
+  float mx = sc;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((t & 31) == 0) red[t >> 5] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  const float pv = (t < nk) ? expf(sc - mx) : 0.0f;
+  pj[t] = pv;
+  float sum = pv;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncthreads();  // red[] read by everybody, pj[] written
+  if ((t & 31) == 0) red[8 + (t >> 5)] = sum;
+  __syncthreads();
+  sum = (red[8] + red[9]) + (red[10] + red[11]);
+  // P V: thread = (column quad c, key group g)
+  const int groups = (nq <= DEC_CHUNK) ? DEC_CHUNK / nq : 1;
+  for (int c0 = 0; c0 < nq; c0 += DEC_CHUNK) {
+    const int g = (groups > 1) ? t / nq : 0;
+    const int c = (groups > 1) ? t - g * nq : c0 + t;
+    const bool active = (groups > 1) ? (g < groups) : (c < nq);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (active) {
+      const float4* vr = reinterpret_cast<const float4*>(vb) + c;
+      const long long ld4 = ld >> 2;
+      int j = g;
+      for (; j + 7 * groups < nk; j += 8 * groups) {
+        float4 vv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) vv[u] = __ldg(vr + static_cast<long long>(j + u * groups) * ld4);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float w = pj[j + u * groups];
+          acc.x += w * vv[u].x; acc.y += w * vv[u].y; acc.z += w * vv[u].z; acc.w += w * vv[u].w;
+        }
+      }
+      for (; j < nk; j += groups) {
+        const float4 v4 = __ldg(vr + static_cast<long long>(j) * ld4);
+        const float w = pj[j];
+        acc.x += w * v4.x; acc.y += w * v4.y; acc.z += w * v4.z; acc.w += w * v4.w;
+      }
+      if (groups > 1) *reinterpret_cast<float4*>(part + g * hd + 4 * c) = acc;
+    }
+    float* dst = scratch + (((static_cast<long long>(b) * heads + h) * gridDim.x + chunk) * (hd + 2));
+    if (groups > 1) {
+      __syncthreads();
+      if (t < nq) {
+        float4 o = *reinterpret_cast<const float4*>(part + 4 * t);
+        for (int gg = 1; gg < groups; ++gg) {
+          const float4 x = *reinterpret_cast<const float4*>(part + gg * hd + 4 * t);
+          o.x += x.x; o.y += x.y; o.z += x.z; o.w += x.w;
+        }
+        dst[2 + 4 * t] = o.x; dst[3 + 4 * t] = o.y; dst[4 + 4 * t] = o.z; dst[5 + 4 * t] = o.w;
+      }
+    } else if (active) {
+      dst[2 + 4 * c] = acc.x; dst[3 + 4 * c] = acc.y; dst[4 + 4 * c] = acc.z; dst[5 + 4 * c] = acc.w;
+    }
+    if (t == 0 && c0 == 0) { dst[0] = mx; dst[1] = sum; }
+  }
+}
+
+__global__ void attn_decode_merge_kernel(const float* __restrict__ scratch, float* __restrict__ out, int chunks, int heads, int hd,
+                                         int embed) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float* src = scratch + (static_cast<long long>(b) * heads + h) * chunks * (hd + 2);
+  float m = -1e30f;  // the reference's initial maximum (LayerOps.hpp:1052)
+  for (int c = 0; c < chunks; ++c) m = fmaxf(m, src[static_cast<long long>(c) * (hd + 2)]);
+  float l = 0.0f;
+  for (int c = 0; c < chunks; ++c) l += src[static_cast<long long>(c) * (hd + 2) + 1] * expf(src[static_cast<long long>(c) * (hd + 2)] - m);
+  const float inv = 1.0f / (l + 1e-9f);  // LayerOps.hpp:1076
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float o = 0.0f;
+    for (int c = 0; c < chunks; ++c) o += src[static_cast<long long>(c) * (hd + 2) + 2 + d] * expf(src[static_cast<long long>(c) * (hd + 2)] - m);
+    out[static_cast<long long>(b) * embed + h * hd + d] = o * inv;
+  }
+}
+}  // namespace
+
+size_t attention_decode_scratch_bytes(int batch, int heads, int embed, int max_seq) {
+  const size_t chunks = static_cast<size_t>((max_seq + DEC_CHUNK - 1) / DEC_CHUNK);
+  return static_cast<size_t>(batch) * heads * chunks * (static_cast<size_t>(embed / (heads > 0 ? heads : 1)) + 2) * sizeof(float);
+}
+
+bool attention_decode_supported(const AttnView& a, int embed, int heads) {
+  if (heads <= 0 || embed % heads != 0) return false;
+  const int hd = embed / heads;
+  return a.q_len == 1 && hd % 4 == 0 && hd <= 512 && a.ldkv % 4 == 0 && a.kv_bstride % 4 == 0 &&
+         ((reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) == 0;
+}
+
+// out [batch][embed]; `scratch` holds attention_decode_scratch_bytes(batch, heads, embed, kv_len)
+int launch_attention_decode(const AttnView& a, float* out, float* scratch, int batch, int embed, int heads, cudaStream_t st) {
+  if (!attention_decode_supported(a, embed, heads) || !scratch) return fail(MIMIR_B200_E_INVALID, "attention decode: unsupported layout");
+  const int hd = embed / heads;
+  const int chunks = (a.kv_len + DEC_CHUNK - 1) / DEC_CHUNK;
+  if (chunks > 65535 || heads > 65535 || batch > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "attention decode: too many chunks / heads / samples for one launch");
+  const int nq = hd / 4;
+  const int groups = (nq <= DEC_CHUNK) ? DEC_CHUNK / nq : 1;
+  const size_t smem = (static_cast<size_t>(hd) + DEC_CHUNK + static_cast<size_t>(groups) * hd) * sizeof(float);
+  dim3 grid(chunks, heads, batch);
+  attn_decode_chunk_kernel<<<grid, DEC_CHUNK, smem, st>>>(a, scratch, heads, hd, 1.0f / sqrtf(static_cast<float>(hd)));
+  MB_CUDA(cudaGetLastError());
+  dim3 mgrid(heads, batch);
+  attn_decode_merge_kernel<<<mgrid, 128, 0, st>>>(scratch, out, chunks, heads, hd, embed);
+  MB_CUDA(cudaGetLastError());
+  count_launch(2);
+  return MIMIR_B200_OK;
+}
 
 int launch_kv_cache_write(const float* qkv, float* kcache, float* vcache, int batch, int seq, int embed, int max_seq, int pos0,
                           cudaStream_t st) {

@@ -94,7 +94,12 @@ size_t split_bytes(int64_t rows, int k, int planes) {
 }
 
 
-bool linear_uses_skinny(int rows, int precision) { return rows <= 16 && precision == MIMIR_B200_PREC_BF16X2; }
+// A handful of rows stream the fp32 weights once through every SM (exact fp32 arithmetic, so it serves every
+// precision mode); a 128-row GEMM tile would keep one SM per 256 output columns busy with mostly empty rows.
+bool linear_uses_skinny(int rows, int precision) {
+  (void)precision;
+  return rows <= 16;
+}
 
 size_t linear_ws_bytes(int rows, int in_f, int out_f, int precision, bool a_presplit) {
   if (linear_uses_skinny(rows, precision)) return align256(skinny_scratch_bytes(rows, in_f, out_f));
@@ -159,11 +164,18 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   float* qkv = reinterpret_cast<float*>(ws + align256(split_bytes(rows, e.embed, ap)));
   float* att = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(qkv) + align256(static_cast<size_t>(rows) * 3 * e.embed * 4));
   uint8_t* tc_ws = reinterpret_cast<uint8_t*>(att) + align256(static_cast<size_t>(rows) * e.embed * 4);
-  if (!e.x_split) MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
-  GemmArgs g;
-  g.a = e.x_split ? e.x_split : xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
-  g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
-  MB_TRY(launch_gemm(g, st));
+  // a decode step of a few samples: both projections stream fp32 weights (transposed copies, W[out][in]) instead of
+  // running 128-row GEMM tiles that are almost empty
+  const bool stream_w = e.decode_pos >= 0 && e.wqkv_t_f32 && e.wout_t_f32 && e.x && rows <= 16 && e.skinny_scratch;
+  if (stream_w) {
+    MB_TRY(launch_skinny_linear(e.x, e.wqkv_t_f32, nullptr, qkv, rows, e.embed, 3 * e.embed, -1, e.skinny_scratch, e.skinny_scratch_bytes, st));
+  } else {
+    if (!e.x_split) MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
+    GemmArgs g;
+    g.a = e.x_split ? e.x_split : xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
+    g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
+    MB_TRY(launch_gemm(g, st));
+  }
   if (e.kcache) MB_TRY(launch_kv_cache_write(qkv, e.kcache, e.vcache, e.batch, e.seq, e.embed, e.max_seq, e.decode_pos < 0 ? 0 : e.decode_pos, st));
   if (e.decode_pos >= 0) {
     // one new token per sample against the cached keys and values (all of them are in its past)
@@ -172,7 +184,17 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
     a.q = qkv; a.ldq = 3LL * e.embed; a.q_len = 1;
     a.k = e.kcache; a.v = e.vcache; a.ldkv = e.embed; a.kv_len = e.decode_pos + 1;
     a.kv_bstride = static_cast<long long>(e.max_seq) * e.embed;
-    MB_TRY(launch_attention_core_view(a, att, e.batch, e.embed, e.heads, 0, st));
+    if (e.decode_scratch && attention_decode_supported(a, e.embed, e.heads))
+      MB_TRY(launch_attention_decode(a, att, e.decode_scratch, e.batch, e.embed, e.heads, st));
+    else
+      MB_TRY(launch_attention_core_view(a, att, e.batch, e.embed, e.heads, 0, st));
+    if (stream_w) {
+      MB_TRY(launch_skinny_linear(att, e.wout_t_f32, nullptr, e.y, rows, e.embed, e.embed, -1, e.skinny_scratch, e.skinny_scratch_bytes, st));
+      if (e.residual)
+        MB_TRY(launch_eltwise(MIMIR_B200_ELT_ADD, e.y, e.residual, e.y, 1, static_cast<int64_t>(rows) * e.embed,
+                              static_cast<int64_t>(rows) * e.embed, st));
+      return MIMIR_B200_OK;
+    }
     MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));
   } else
   // the attended rows go to the output projection as operand planes (the x planes are dead by now)

@@ -129,6 +129,8 @@ struct LayerRT {
   float* kcache = nullptr;
   float* vcache = nullptr;
   size_t cache_bytes = 0;
+  float* w_t_f32 = nullptr;           // attention of a twin with <= 16 samples: Wqkv^T [3E][E] then Wout^T [E][E], fp32
+  size_t w_t_bytes = 0;
   size_t ws_off = 0, ws_bytes = 0;
   // resolved shapes (per sample)
   int rows_ps = 1, in_f = 0, out_f = 0;       // Linear
@@ -243,6 +245,10 @@ struct MimirB200Model {
   bool is_twin = false;
   int decode_pos = 0, max_seq = 0;
   uint64_t plan_epoch = 0, twin_epoch = 0;
+  float* decode_scratch = nullptr;  // partial softmax results of the decode attention, shared by the twin's layers
+  size_t decode_scratch_bytes = 0;
+  float* skinny_scratch = nullptr;  // K-slice partial sums of the weight-streaming projections of a twin's attention
+  size_t skinny_scratch_bytes = 0;
 };
 
 namespace mb {
@@ -1050,6 +1056,13 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
         if (m->is_twin) {
           e.kcache = L.kcache; e.vcache = L.vcache; e.max_seq = m->max_seq; e.decode_pos = m->decode_pos;
+          e.decode_scratch = m->decode_scratch;
+          if (L.w_t_f32) {
+            e.wqkv_t_f32 = L.w_t_f32;
+            e.wout_t_f32 = L.w_t_f32 + static_cast<size_t>(3) * L.embed * L.embed;
+            e.skinny_scratch = m->skinny_scratch;
+            e.skinny_scratch_bytes = m->skinny_scratch_bytes;
+          }
         } else if (m->decode && m->decode->twin_epoch == m->plan_epoch && batch == m->decode->planned_batch && L.seq <= m->decode->max_seq) {
           // a full forward of the main model doubles as the prefill: its keys and values land in the caches
           const LayerRT& T = m->decode->layers[static_cast<size_t>(li)];
@@ -1357,8 +1370,12 @@ static void destroy_model(MimirB200Model* m) {
   for (auto& L : m->layers) {
     if (L.kcache) dev_free(L.kcache, L.cache_bytes);
     if (L.vcache) dev_free(L.vcache, L.cache_bytes);
-    L.kcache = L.vcache = nullptr;
+    if (L.w_t_f32) dev_free(L.w_t_f32, L.w_t_bytes);
+    L.kcache = L.vcache = L.w_t_f32 = nullptr;
   }
+  if (m->decode_scratch) dev_free(m->decode_scratch, m->decode_scratch_bytes);
+  if (m->skinny_scratch) dev_free(m->skinny_scratch, m->skinny_scratch_bytes);
+  m->decode_scratch = m->skinny_scratch = nullptr;
   drop_graphs(m);
   if (m->s_capture) cudaStreamDestroy(m->s_capture);
   for (auto& L : m->layers) free_layer_weights(L, m);
@@ -1628,7 +1645,23 @@ int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput*
     status = dev_alloc(reinterpret_cast<void**>(&L.kcache), L.cache_bytes, "key cache");
     if (status == MIMIR_B200_OK) status = dev_alloc(reinterpret_cast<void**>(&L.vcache), L.cache_bytes, "value cache");
     bytes += 2 * L.cache_bytes;
+    t->decode_scratch_bytes = std::max(t->decode_scratch_bytes, attention_decode_scratch_bytes(batch, L.heads, L.embed, max_seq));
+    if (status == MIMIR_B200_OK && batch <= 16 && L.w_f32 && L.w_count >= static_cast<size_t>(4) * L.embed * L.embed) {
+      // Wqkv [E][3E] and Wout [E][E] are stored input-major; the weight-streaming kernel reads W[out][in]
+      const int E = L.embed;
+      L.w_t_bytes = static_cast<size_t>(4) * E * E * sizeof(float);
+      status = dev_alloc(reinterpret_cast<void**>(&L.w_t_f32), L.w_t_bytes, "attention weights, output-major");
+      const int s1[2] = {E, 3 * E}, s2[2] = {E, E}, dims[2] = {1, 0};
+      if (status == MIMIR_B200_OK) status = launch_permute(L.w_f32, L.w_t_f32, 1, 2, s1, dims, nullptr);
+      if (status == MIMIR_B200_OK)
+        status = launch_permute(L.w_f32 + static_cast<size_t>(3) * E * E, L.w_t_f32 + static_cast<size_t>(3) * E * E, 1, 2, s2, dims, nullptr);
+      t->skinny_scratch_bytes = std::max(t->skinny_scratch_bytes, skinny_scratch_bytes(batch, E, 3 * E));
+    }
   }
+  if (status == MIMIR_B200_OK && t->skinny_scratch_bytes)
+    status = dev_alloc(reinterpret_cast<void**>(&t->skinny_scratch), t->skinny_scratch_bytes, "decode projection scratch");
+  if (status == MIMIR_B200_OK && t->decode_scratch_bytes)
+    status = dev_alloc(reinterpret_cast<void**>(&t->decode_scratch), t->decode_scratch_bytes, "decode attention scratch");
   if (status != MIMIR_B200_OK) {
     destroy_model(t.release());
     return status;

@@ -49,6 +49,12 @@ struct AttentionExec {
   float* vcache = nullptr;
   int max_seq = 0;
   int decode_pos = -1;
+  float* decode_scratch = nullptr;  // attention_decode_scratch_bytes(batch, heads, embed, max_seq), for decode steps
+  // decode steps of <= 16 samples: fp32 copies of the projections as W[out][in] and the weight-streaming kernel's scratch
+  const float* wqkv_t_f32 = nullptr;
+  const float* wout_t_f32 = nullptr;
+  float* skinny_scratch = nullptr;
+  size_t skinny_scratch_bytes = 0;
 };
 size_t attention_ws_bytes(int batch, int seq, int embed, int heads, int precision);
 int attention_exec(const AttentionExec& e, cudaStream_t st);

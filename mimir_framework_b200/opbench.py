@@ -257,9 +257,50 @@ def bench_unet(no_cpu):
                        3 * 256 * 256, configs.conv_flops(descs), abi.PREC_BF16W, no_cpu, "one sample through the reference CPU path")
 
 
+def bench_decode_steps():
+    """Token-by-token generation on the decoder configuration's shape with token-wise LayerNorm (the reference's
+    whole-sample RMSNorm makes every row depend on later tokens, so that graph cannot be decoded incrementally):
+    prefill of 1023 tokens through the ordinary forward, then steps at positions 1023 .. through the host-pointer
+    entry point.  A step streams every weight once: bytes = fp32 Linear weights (rows <= 16 take the
+    weight-streaming kernel) + bf16 attention planes + the key / value cache read."""
+    batch, S = int(os.environ.get("OPBENCH_BATCH", "16")), 1024
+    P = S - 1 - 32
+    E, V, L = 768, 32000, 12
+    descs = configs.gpt_decoder(seq=P, norm="layer")
+    weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
+    model = rt.GraphModel(descs, abi.PREC_BF16W)
+    for i, w in enumerate(weights):
+        model.upload_weights(i, w)
+    model.plan({"x": (P, False)}, batch)
+    cache = model.decode_begin({"x": (1, False)}, batch, S)
+    ids = np.random.default_rng(0).integers(0, V, (batch, S)).astype(np.float32)
+    model.forward({"x": (ids[:, :P].copy().ravel(), False)}, batch, P * V)
+    import time
+    for t in range(P, P + 4):  # warm-up steps
+        model.decode_step({"x": (ids[:, t].copy(), False)}, batch, t, V)
+    ts = []
+    for t in range(P + 4, P + 32):
+        tok = ids[:, t].copy()
+        t0 = time.perf_counter()
+        model.decode_step({"x": (tok, False)}, batch, t, V)
+        ts.append(time.perf_counter() - t0)
+    ms = 1e3 * float(np.median(ts))
+    dev_ms = rt.stats()["ms_last_forward"]
+    lin_bytes = 4 * (L * 2 * E * 3072 + E * V)
+    attn_bytes = 2 * L * 4 * E * E
+    kv_bytes = 4 * 2 * L * batch * (P + 18) * E
+    total = lin_bytes + attn_bytes + kv_bytes
+    peak, src = hbm_peak()
+    print(json.dumps({"config": "GPT decoder d768 h12 ffn3072 vocab32000, token-wise LayerNorm: decode steps at positions ~1000", "batch": batch,
+                      "ms_per_step_host": ms, "ms_per_step_device": dev_ms, "tokens_per_s": batch / (ms * 1e-3), "cache_bytes": cache,
+                      "bytes_per_step": total, "achieved_gbs_device": total / (dev_ms * 1e-3) / 1e9, "peak_gbs": peak,
+                      "frac_device": total / (dev_ms * 1e-3) / 1e9 / peak, "peak_source": src}), flush=True)
+    model.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="all", choices=["all", "norms", "configs", "c1", "c3", "c4", "c5"])
+    ap.add_argument("--only", default="all", choices=["all", "norms", "configs", "c1", "c3", "c4", "c5", "decode"])
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     rt.init(0, 0)
@@ -273,6 +314,8 @@ def main():
         bench_conv_stack(args.no_cpu)
     if args.only in ("all", "configs", "c5"):
         bench_unet(args.no_cpu)
+    if args.only in ("all", "decode"):
+        bench_decode_steps()
     rt.shutdown()
 
 

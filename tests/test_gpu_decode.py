@@ -42,9 +42,10 @@ def close(got, want, what):
     assert np.all(err <= 1e-4 + 1e-3 * np.abs(want)), f"{what}: max abs error {err.max():.3e}"
 
 
-@pytest.mark.parametrize("batch", [2, 20])  # 20 rows per step leave the weight-streaming path for the tensor-core GEMM
-def test_decode_steps_reproduce_the_rows_of_the_full_causal_forward(backend, batch):
-    S, P = 12, 7
+# 20 rows per step leave the weight-streaming path for the tensor-core GEMM; 300 positions span three key chunks of
+# the decode attention kernel
+@pytest.mark.parametrize("batch,S,P", [(2, 12, 7), (20, 12, 7), (3, 300, 292)])
+def test_decode_steps_reproduce_the_rows_of_the_full_causal_forward(backend, batch, S, P):
     full = gpt(S)
     weights = configs.seeded_weights(full, seed=3, std=0.08)
     ids = np.random.default_rng(batch).integers(0, V, (batch, S)).astype(np.float32)
@@ -58,7 +59,8 @@ def test_decode_steps_reproduce_the_rows_of_the_full_causal_forward(backend, bat
     assert m.decode_begin({"x": (1, False)}, batch, S) == 2 * 2 * batch * S * E * 4
     for t in range(S):
         got = m.decode_step({"x": (ids[:, t].copy(), False)}, batch, t, V)
-        close(got, want[:, t, :], f"decode from scratch, position {t}")
+        if S <= 16 or t % 37 == 0 or t >= S - 3:
+            close(got, want[:, t, :], f"decode from scratch, position {t}")
     m.decode_end()
     m.close()
 
