@@ -355,7 +355,8 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
 
 namespace {
 __global__ void kv_cache_write_kernel(const float* __restrict__ qkv, float* __restrict__ kcache, float* __restrict__ vcache, long long total,
-                                      int seq, int embed, int max_seq, int pos0) {
+                                      int seq, int embed, int max_seq, int pos0, const int* __restrict__ pos_dev) {
+  if (pos_dev) pos0 = *pos_dev;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int d = static_cast<int>(i % embed);
@@ -385,10 +386,11 @@ __global__ void __launch_bounds__(DEC_CHUNK) attn_decode_chunk_kernel(const Attn
   float* part = pj + DEC_CHUNK;    // [groups][hd]
   __shared__ float red[33];
   const int chunk = blockIdx.x, h = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
-  const int kvn = a.kv_len, k0 = chunk * DEC_CHUNK;
+  const int kvn = a.pos_dev ? (*a.pos_dev + 1) : a.kv_len, k0 = chunk * DEC_CHUNK;
+  if (k0 >= kvn) return;  // (the launch is sized for the whole cache when the position comes from device memory)
   const int nk = min(DEC_CHUNK, kvn - k0);
   const long long ld = a.ldkv;
-  const long long qbs = a.q_bstride ? a.q_bstride : a.q_len * a.ldq, kbs = a.kv_bstride ? a.kv_bstride : static_cast<long long>(kvn) * ld;
+  const long long qbs = a.q_bstride ? a.q_bstride : a.q_len * a.ldq, kbs = a.kv_bstride ? a.kv_bstride : static_cast<long long>(a.kv_len) * ld;
   const float* kb = a.k + b * kbs + h * hd + static_cast<long long>(k0) * ld;
   const float* vb = a.v + b * kbs + h * hd + static_cast<long long>(k0) * ld;
   for (int d = t; d < hd; d += DEC_CHUNK) q[d] = a.q[b * qbs + h * hd + d];
@@ -474,10 +476,11 @@ __global__ void __launch_bounds__(DEC_CHUNK) attn_decode_chunk_kernel(const Attn
   }
 }
 
-__global__ void attn_decode_merge_kernel(const float* __restrict__ scratch, float* __restrict__ out, int chunks, int heads, int hd,
-                                         int embed) {
+__global__ void attn_decode_merge_kernel(const float* __restrict__ scratch, float* __restrict__ out, int chunks_launched, int heads, int hd,
+                                         int embed, const int* __restrict__ pos_dev) {
   const int h = blockIdx.x, b = blockIdx.y;
-  const float* src = scratch + (static_cast<long long>(b) * heads + h) * chunks * (hd + 2);
+  const float* src = scratch + (static_cast<long long>(b) * heads + h) * chunks_launched * (hd + 2);
+  const int chunks = pos_dev ? (*pos_dev + DEC_CHUNK) / DEC_CHUNK : chunks_launched;
   float m = -1e30f;  // the reference's initial maximum (LayerOps.hpp:1052)
   for (int c = 0; c < chunks; ++c) m = fmaxf(m, src[static_cast<long long>(c) * (hd + 2)]);
   float l = 0.0f;
@@ -516,19 +519,19 @@ int launch_attention_decode(const AttnView& a, float* out, float* scratch, int b
   attn_decode_chunk_kernel<<<grid, DEC_CHUNK, smem, st>>>(a, scratch, heads, hd, 1.0f / sqrtf(static_cast<float>(hd)));
   MB_CUDA(cudaGetLastError());
   dim3 mgrid(heads, batch);
-  attn_decode_merge_kernel<<<mgrid, 128, 0, st>>>(scratch, out, chunks, heads, hd, embed);
+  attn_decode_merge_kernel<<<mgrid, 128, 0, st>>>(scratch, out, chunks, heads, hd, embed, a.pos_dev);
   MB_CUDA(cudaGetLastError());
   count_launch(2);
   return MIMIR_B200_OK;
 }
 
 int launch_kv_cache_write(const float* qkv, float* kcache, float* vcache, int batch, int seq, int embed, int max_seq, int pos0,
-                          cudaStream_t st) {
+                          cudaStream_t st, const int* pos_dev) {
   if (pos0 < 0 || pos0 + seq > max_seq) return fail(MIMIR_B200_E_INVALID, "KV cache: positions %d..%d exceed the cache of %d", pos0, pos0 + seq - 1, max_seq);
   const long long total = static_cast<long long>(batch) * seq * embed;
   long long blocks = (total + 255) / 256;
   if (blocks > ctx().sm_count * 16LL) blocks = ctx().sm_count * 16LL;
-  kv_cache_write_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(qkv, kcache, vcache, total, seq, embed, max_seq, pos0);
+  kv_cache_write_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(qkv, kcache, vcache, total, seq, embed, max_seq, pos0, pos_dev);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;

@@ -176,7 +176,9 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
     g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
     MB_TRY(launch_gemm(g, st));
   }
-  if (e.kcache) MB_TRY(launch_kv_cache_write(qkv, e.kcache, e.vcache, e.batch, e.seq, e.embed, e.max_seq, e.decode_pos < 0 ? 0 : e.decode_pos, st));
+  if (e.kcache)
+    MB_TRY(launch_kv_cache_write(qkv, e.kcache, e.vcache, e.batch, e.seq, e.embed, e.max_seq, e.decode_pos < 0 ? 0 : e.decode_pos, st,
+                                 e.decode_pos >= 0 ? e.pos_dev : nullptr));
   if (e.decode_pos >= 0) {
     // one new token per sample against the cached keys and values (all of them are in its past)
     if (!e.kcache || e.seq != 1) return fail(MIMIR_B200_E_INVALID, "attention: a decode step needs a cache and one token per sample");
@@ -184,9 +186,15 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
     a.q = qkv; a.ldq = 3LL * e.embed; a.q_len = 1;
     a.k = e.kcache; a.v = e.vcache; a.ldkv = e.embed; a.kv_len = e.decode_pos + 1;
     a.kv_bstride = static_cast<long long>(e.max_seq) * e.embed;
-    if (e.decode_scratch && attention_decode_supported(a, e.embed, e.heads))
+    if (e.decode_scratch && attention_decode_supported(a, e.embed, e.heads)) {
+      if (e.pos_dev) {  // sized for the whole cache; the kernels read the position themselves
+        a.kv_len = e.max_seq;
+        a.pos_dev = e.pos_dev;
+      }
       MB_TRY(launch_attention_decode(a, att, e.decode_scratch, e.batch, e.embed, e.heads, st));
-    else
+    } else if (e.pos_dev) {
+      return fail(MIMIR_B200_E_UNSUPPORTED, "attention: this head layout cannot take its position from device memory");
+    } else
       MB_TRY(launch_attention_core_view(a, att, e.batch, e.embed, e.heads, 0, st));
     if (stream_w) {
       MB_TRY(launch_skinny_linear(att, e.wout_t_f32, nullptr, e.y, rows, e.embed, e.embed, -1, e.skinny_scratch, e.skinny_scratch_bytes, st));

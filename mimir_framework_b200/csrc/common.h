@@ -141,6 +141,9 @@ struct AttnView {
   long long ldq = 0, ldkv = 0;
   int q_len = 0, kv_len = 0;
   long long q_bstride = 0, kv_bstride = 0;  // elements between samples; 0 = q_len * ldq / kv_len * ldkv
+  // decode steps replayed from a CUDA graph: the position lives in device memory (kv_len = *pos_dev + 1) and
+  // kv_len above is the cache capacity the launch is sized for
+  const int* pos_dev = nullptr;
 };
 // One query row per (sample, head) against kv_len cached keys / values (a decode step), keys cut into chunks
 size_t attention_decode_scratch_bytes(int batch, int heads, int embed, int max_seq);
@@ -148,7 +151,7 @@ bool attention_decode_supported(const AttnView& a, int embed, int heads);
 int launch_attention_decode(const AttnView& a, float* out, float* scratch, int batch, int embed, int heads, cudaStream_t st);
 // K and V thirds of qkv [batch*seq][3E] -> cache[b][pos0 + s][E] of caches holding max_seq positions per sample
 int launch_kv_cache_write(const float* qkv, float* kcache, float* vcache, int batch, int seq, int embed, int max_seq, int pos0,
-                          cudaStream_t st);
+                          cudaStream_t st, const int* pos_dev = nullptr);
 // qkv fp32 [batch*seq, 3E] (Q | K | V thirds) -> attended fp32 [batch*seq, E]
 int launch_attention_core(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal,
                           cudaStream_t st);

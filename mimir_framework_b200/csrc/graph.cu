@@ -247,6 +247,8 @@ struct MimirB200Model {
   uint64_t plan_epoch = 0, twin_epoch = 0;
   float* decode_scratch = nullptr;  // partial softmax results of the decode attention, shared by the twin's layers
   size_t decode_scratch_bytes = 0;
+  int* pos_dev = nullptr;           // set when every attention layer of the twin can read its position on the device:
+                                    // the step is then a fixed launch sequence and is replayed as a CUDA graph
   float* skinny_scratch = nullptr;  // K-slice partial sums of the weight-streaming projections of a twin's attention
   size_t skinny_scratch_bytes = 0;
 };
@@ -1057,6 +1059,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         if (m->is_twin) {
           e.kcache = L.kcache; e.vcache = L.vcache; e.max_seq = m->max_seq; e.decode_pos = m->decode_pos;
           e.decode_scratch = m->decode_scratch;
+          e.pos_dev = m->pos_dev;
           if (L.w_t_f32) {
             e.wqkv_t_f32 = L.w_t_f32;
             e.wout_t_f32 = L.w_t_f32 + static_cast<size_t>(3) * L.embed * L.embed;
@@ -1248,7 +1251,8 @@ bool graphs_enabled() {
 // performs every one-time host-side setup the launch helpers do); the second is captured on a private stream;
 // from then on the instantiated graph is launched into the caller's stream.
 int run_layers_cached(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, uint8_t* arena) {
-  if (!graphs_enabled() || ctx().prof_gemm || m->is_twin) return run_layers(m, batch, bnd, st, arena);  // (a twin's position changes per call)
+  // (a twin whose position is a launch argument changes from call to call)
+  if (!graphs_enabled() || ctx().prof_gemm || (m->is_twin && !m->pos_dev)) return run_layers(m, batch, bnd, st, arena);
   std::vector<const void*> key;
   key.reserve(bnd.in_ptr.size() + 3);
   key.push_back(reinterpret_cast<const void*>(static_cast<uintptr_t>(batch)));
@@ -1375,6 +1379,8 @@ static void destroy_model(MimirB200Model* m) {
   }
   if (m->decode_scratch) dev_free(m->decode_scratch, m->decode_scratch_bytes);
   if (m->skinny_scratch) dev_free(m->skinny_scratch, m->skinny_scratch_bytes);
+  if (m->pos_dev) dev_free(m->pos_dev, 256);
+  m->pos_dev = nullptr;
   m->decode_scratch = m->skinny_scratch = nullptr;
   drop_graphs(m);
   if (m->s_capture) cudaStreamDestroy(m->s_capture);
@@ -1658,6 +1664,13 @@ int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput*
       t->skinny_scratch_bytes = std::max(t->skinny_scratch_bytes, skinny_scratch_bytes(batch, E, 3 * E));
     }
   }
+  bool pos_on_device = (status == MIMIR_B200_OK);
+  for (const auto& L : t->layers)
+    if (L.lt == LT::Attention) {
+      const int hd = L.heads > 0 ? L.embed / L.heads : 0;
+      pos_on_device = pos_on_device && hd > 0 && hd % 4 == 0 && hd <= 512 && L.embed % 4 == 0;
+    }
+  if (pos_on_device) status = dev_alloc(reinterpret_cast<void**>(&t->pos_dev), 256, "decode position");
   if (status == MIMIR_B200_OK && t->skinny_scratch_bytes)
     status = dev_alloc(reinterpret_cast<void**>(&t->skinny_scratch), t->skinny_scratch_bytes, "decode projection scratch");
   if (status == MIMIR_B200_OK && t->decode_scratch_bytes)
@@ -1680,8 +1693,14 @@ int mimir_b200_model_decode_step(MimirB200ModelHandle m, const MimirNamedInput* 
   if (m->decode->twin_epoch != m->plan_epoch || m->planned_batch <= 0)
     return fail(MIMIR_B200_E_INVALID, "decode_step: the model was planned or its weights changed since decode_begin; call decode_begin again");
   if (pos < 0 || pos >= m->decode->max_seq) return fail(MIMIR_B200_E_INVALID, "decode_step: position %d outside the cache of %d", pos, m->decode->max_seq);
-  m->decode->decode_pos = pos;
-  return mimir_b200_model_forward(m->decode, inputs, n_inputs, batch, out_host, out_capacity, out_len);
+  MimirB200Model* t = m->decode;
+  t->decode_pos = pos;
+  if (t->pos_dev) {
+    // the previous step has fully drained (forward synchronises), so the word can be rewritten before this one starts
+    MB_TRY(ensure_pipeline_objects(t));
+    MB_CUDA(cudaMemcpyAsync(t->pos_dev, &t->decode_pos, sizeof(int), cudaMemcpyHostToDevice, t->s_comp));
+  }
+  return mimir_b200_model_forward(t, inputs, n_inputs, batch, out_host, out_capacity, out_len);
 }
 
 // Cuts the batch of the host-pointer forward into `micro_batches` pieces that overlap their

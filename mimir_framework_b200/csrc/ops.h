@@ -49,6 +49,7 @@ struct AttentionExec {
   float* vcache = nullptr;
   int max_seq = 0;
   int decode_pos = -1;
+  const int* pos_dev = nullptr;     // decode steps replayed from a CUDA graph read the position here instead of decode_pos
   float* decode_scratch = nullptr;  // attention_decode_scratch_bytes(batch, heads, embed, max_seq), for decode steps
   // decode steps of <= 16 samples: fp32 copies of the projections as W[out][in] and the weight-streaming kernel's scratch
   const float* wqkv_t_f32 = nullptr;
