@@ -71,6 +71,7 @@ struct GemmParams {
   // the same whatever its N, so a narrow layer computed the usual way (N = its few channels, padded to the
   // tile) pays for 256 columns it does not have; swapped, every instruction does full work.
   int swap;
+  int tma_store;  // fp32 row-major output leaves through TMA stores (map_o) instead of per-lane stores
   int* err_word;
 };
 
@@ -95,7 +96,7 @@ struct SmemLayout {
 template <int BK, int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                         const GemmParams p) {
+                         const __grid_constant__ CUtensorMap map_o, const GemmParams p) {
   constexpr int SWZ = BK * 2;                      // bytes per smem row = swizzle span
   constexpr int A_TILE = BM * BK * 2;
   constexpr int W_TILE = BN * BK * 2;
@@ -103,7 +104,10 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // behind the stages: one staging tile per epilogue warp (32 x 33 floats for the swapped form's transposition, or a
+  // dense 128-byte-swizzled 32 x 32 tile, 1024-byte aligned, as the source of a TMA store), then the barriers
+  uint8_t* epi_tiles = smem + STAGES * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_tiles + EPI_WARPS * 32 * 33 * 4);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;
   uint64_t* acc_empty = acc_full + NUM_ACC;
@@ -252,7 +256,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         // TMEM lane = output channel, column = activation row (pixel).  Each 32 x 32 chunk is turned around
         // through a padded shared-memory tile so that a lane owns a pixel again and the NCHW stores (and
         // residual loads) of a warp are 128 contiguous bytes per channel, as in the unswapped form.
-        float* tbuf = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + ew * (32 * 33);
+        float* tbuf = reinterpret_cast<float*>(epi_tiles) + ew * (32 * 33);
         const int oc0 = row0;  // first output channel of this warp's 32 lanes
         const long long hw = (p.conv_ks > 0) ? static_cast<long long>(p.conv_h) * p.conv_w : static_cast<long long>(p.ohw);
 #pragma unroll 1
@@ -400,7 +404,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                   if (col0 + j < p.n) v[j] += __ldg(rr + j);
               }
             }
-            if (p.out_f32 != nullptr) {
+            if (p.out_f32 != nullptr && !p.tma_store) {
               float* o = p.out_f32 + ro;
               if (full_cols && ((reinterpret_cast<uintptr_t>(o) & 31) == 0)) {
 #pragma unroll
@@ -433,6 +437,22 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               st_global_v8_b32(ol + 16, &lo[8]);
             }
           }
+          if (p.tma_store) {
+            // fp32 rows through a TMA store: staged in shared memory (128-byte swizzle, conflict-free 128-bit writes)
+            // the 32 x 32 chunk is one copy, clipped at the edges of the output by the tensor map.
+            float* tile = reinterpret_cast<float*>(epi_tiles + ew * 4096);
+            if (lane == 0) bulk_wait_read0();  // the previous chunk's copy has read the tile
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<float4*>(tile + lane * 32 + ((c ^ (lane & 7)) << 2)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&map_o, tile, col0, row0);
+              bulk_commit();
+            }
+          }
         }
       }
       tcgen05_fence_before();
@@ -440,6 +460,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
     }
+    if (lane == 0) bulk_wait_read0();  // no copy may still be reading shared memory when the CTA exits
   }
 
   tcgen05_fence_before();
@@ -548,6 +569,21 @@ int make_plane_map(CUtensorMap* map, const void* base, int planes, long long row
   return MIMIR_B200_OK;
 }
 
+// 2-D map over the fp32 row-major output [rows][ld]; box = 32 x 32, 128-byte swizzle (the epilogue's staging tile)
+int make_out_map(CUtensorMap* map, const float* base, long long rows, int cols, long long ld) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled (output) failed (%d)", static_cast<int>(r));
+  return MIMIR_B200_OK;
+}
+
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
   return (v && *v) ? atoi(v) : dflt;
@@ -567,7 +603,17 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
                     g.m >= 4 * BN && kblocks_all * BK >= 256 && !(noswap && noswap[0] == '1');
   MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, conv ? g.conv_c : kp, BK, swap ? BN : BM));
   MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : BN));
+  // Optional (MIMIR_B200_GEMM_TMA_STORE=1): row-major fp32 outputs leave through TMA stores.  Measured neutral on the
+  // decoder's K = 768 layers (1 078 vs 1 100 TFLOP/s issued): what slows those layers is not the shape of the stores but
+  // their bytes - the operand loads alone run at ~62 B per cycle and SM, next to what an SM can take from L2, and the
+  // same kernel without any output store reaches 1 315.
+  static const bool use_tma_store = [] { const char* e = getenv("MIMIR_B200_GEMM_TMA_STORE"); return e && e[0] == '1'; }();
+  const bool tma_store = use_tma_store && !swap && !conv && g.out_nchw_hw <= 0 && g.out_f32 != nullptr && g.ldo % 4 == 0 &&
+                         (reinterpret_cast<uintptr_t>(g.out_f32) & 15) == 0;
+  CUtensorMap map_o = map_a;  // (a valid map when unused)
+  if (tma_store) MB_TRY(make_out_map(&map_o, g.out_f32, g.m, g.n, g.ldo));
   GemmParams p;
+  p.tma_store = tma_store ? 1 : 0;
   p.swap = swap ? 1 : 0;
   p.m = g.m;
   p.n = g.n;
@@ -612,7 +658,7 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
     MB_CUDA(cudaEventCreate(&e1));
     MB_CUDA(cudaEventRecord(e0, st));
   }
-  kern<<<grid, NUM_THREADS, SMEM, st>>>(map_a, map_w, p);
+  kern<<<grid, NUM_THREADS, SMEM, st>>>(map_a, map_w, map_o, p);
   MB_CUDA(cudaGetLastError());
   if (e0) {
     MB_CUDA(cudaEventRecord(e1, st));

@@ -336,3 +336,20 @@ def test_batchnorm_with_running_statistics(backend, batch, ch, spatial):
     var = (r.random(ch) + 0.1).astype(np.float32)
     want = port.batchnorm_running(x, g, b, m, var, batch, ch, spatial, 1e-5)
     assert_close(backend.batchnorm_running(x, g, b, m, var, batch, ch, spatial), want, f"batchnorm_running {batch}x{ch}x{spatial}")
+
+
+def test_gemm_output_through_tma_stores():
+    """MIMIR_B200_GEMM_TMA_STORE=1 routes row-major fp32 GEMM outputs through shared-memory staging and TMA stores
+    (off by default: measured neutral).  The switch is read once per process, so the Linear, MatMul and attention
+    cases - ragged row and column counts included - run again in a child interpreter with it set."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, MIMIR_B200_GEMM_TMA_STORE="1")
+    here = os.path.abspath(__file__)
+    r = subprocess.run([sys.executable, "-m", "pytest", here, "-q", "-m", "gpu", "-x", "-k",
+                        "test_linear or test_matmul or test_attention and not tma_stores"], env=env, capture_output=True, text=True,
+                       cwd=os.path.dirname(os.path.dirname(here)))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
