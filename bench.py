@@ -52,17 +52,50 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock, power and throttle reasons while the timed region runs: NVML read-only queries every 5 ms
+    from a thread (the timed region of the default run lasts ~150 ms), nvidia-smi at its fastest cadence as fallback."""
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index = index
-        self.rows = []
+        self.rows = []   # (time, sm MHz, max MHz, W, [reason names])
         self.proc = None
+        self.stop_flag = False
+        self.t = None
+
+    def _nvml_loop(self, nv, h, sm_max):
+        masks = [("hw_slowdown", nv.nvmlClocksThrottleReasonHwSlowdown), ("hw_thermal_slowdown", nv.nvmlClocksThrottleReasonHwThermalSlowdown),
+                 ("sw_thermal_slowdown", nv.nvmlClocksThrottleReasonSwThermalSlowdown), ("sw_power_cap", nv.nvmlClocksThrottleReasonSwPowerCap)]
+        while not self.stop_flag:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                w = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.rows.append((time.time(), float(sm), float(sm_max), w, [n for n, m in masks if bits & m]))
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def start(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            # the physical index behind CUDA_VISIBLE_DEVICES, by UUID when torch can tell
+            h = None
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                h = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            sm_max = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self.t = threading.Thread(target=self._nvml_loop, args=(nv, h, sm_max), daemon=True)
+            self.t.start()
+            return
+        except Exception:
+            self.t = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
@@ -73,28 +106,33 @@ class ClockSampler:
             self.proc = None
 
     def _read(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.proc.stdout:
-            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+            c = [x.strip() for x in line.split(",")]
+            if len(c) >= 7:
+                try:
+                    self.rows.append((time.time(), float(c[0]), float(c[1]), float(c[2]),
+                                      [n for i, n in enumerate(names) if c[3 + i].lower().startswith("active")]))
+                except ValueError:
+                    pass
 
     def stop(self, t0: float, t1: float):
-        if not self.proc:
-            return None
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        rows = [r for (t, r) in self.rows if t0 <= t <= t1 + 0.2 and len(r) >= 7] or [r for (_, r) in self.rows if len(r) >= 7]
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        self.stop_flag = True
+        if self.t is not None and not self.proc:
+            self.t.join(timeout=1)
+        rows = [r for r in self.rows if t0 <= r[0] <= t1] or [r for r in self.rows if t0 <= r[0] <= t1 + 0.2] or self.rows
         if not rows:
             return None
-        sm = [float(r[0]) for r in rows]
-        reasons = []
-        for i, name in enumerate(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]):
-            if any(r[3 + i].lower().startswith("active") for r in rows):
-                reasons.append(name)
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][1]), "reasons": reasons, "samples": len(rows),
-                "power_w_max": max(float(r[2]) for r in rows)}
+        reasons = sorted({n for r in rows for n in r[4]})
+        return {"sm_mhz": statistics.median(r[1] for r in rows), "sm_max_mhz": rows[0][2], "reasons": reasons, "samples": len(rows),
+                "power_w_max": max(r[3] for r in rows), "source": "nvml" if not self.proc else "nvidia-smi"}
 
 
 def cpu_reference_rate(sample_rows: int, repeats: int, warmup: int):
