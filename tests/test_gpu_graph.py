@@ -349,3 +349,28 @@ def test_groupnorm_silu_applied_inside_the_convolution(backend, monkeypatch, sha
     inputs = {"x": (x.ravel(), False)}
     assert_close(gpu_batch(backend, descs, weights, inputs, batch, ch * hw * hw), oracle_batch(descs, weights, inputs, batch),
                  f"resblock, shared={shared_output}")
+
+
+def test_replayed_graph_with_one_pass_rmsnorm_and_cluster_layernorm(backend):
+    """The captured layer loop holds a memset node + the ticketed single-pass RMSNorm, and a cluster-launched
+    LayerNorm: five forwards (run, capture, three replays) must agree bit for bit and with the oracle."""
+    S, E = 96, 512
+    descs = [
+        make_desc("n1", "RMSNorm", inputs=["x"], output="h1", params_count=S * E),
+        make_desc("fc", "Linear", inputs=["h1"], output="h2", in_features=E, out_features=E, seq_len=S, params_count=E * E + E),
+        make_desc("ln", "LayerNorm", inputs=["h2"], output="h3", affine=1, use_bias=1, params_count=2 * S * E),  # whole sample: 49152 elements
+        make_desc("add", "Add", inputs=["h3", "__input__"], output="x"),
+    ]
+    weights = configs.seeded_weights(descs, seed=2, std=0.05)
+    batch = 3
+    x = np.random.default_rng(1).standard_normal((batch, S * E)).astype(np.float32)
+    inputs = {"x": (x.ravel(), False)}
+    m = backend.GraphModel(descs)
+    for i, w in enumerate(weights):
+        m.upload_weights(i, w)
+    m.plan({"x": (S * E, False)}, batch)
+    outs = [m.forward(inputs, batch, S * E).copy() for _ in range(5)]
+    m.close()
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    assert_close(outs[0], oracle_batch(descs, weights, inputs, batch), "rmsnorm -> linear -> layernorm, replayed")
