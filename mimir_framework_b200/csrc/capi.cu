@@ -112,11 +112,8 @@ size_t linear_ws_bytes(int rows, int in_f, int out_f, int precision, bool a_pres
 int linear_exec(const LinearExec& e, cudaStream_t st) {
   if (linear_uses_skinny(e.rows, e.precision)) {
     if (!e.x_f32 || !e.w_f32 || !e.y_f32) return fail(MIMIR_B200_E_INVALID, "linear: skinny path needs fp32 operands");
-    MB_TRY(launch_skinny_linear(e.x_f32, e.w_f32, e.bias, e.y_f32, e.rows, e.in_f, e.out_f, e.activation,
-                                static_cast<float*>(e.ws), e.ws_bytes, st));
-    if (e.residual) MB_TRY(launch_eltwise(MIMIR_B200_ELT_ADD, e.y_f32, e.residual, e.y_f32, 1,
-                                          static_cast<int64_t>(e.rows) * e.out_f, static_cast<int64_t>(e.rows) * e.out_f, st));
-    return MIMIR_B200_OK;
+    return launch_skinny_linear(e.x_f32, e.w_f32, e.bias, e.y_f32, e.rows, e.in_f, e.out_f, e.activation, static_cast<float*>(e.ws),
+                                e.ws_bytes, st, e.residual);
   }
   int ap, wp;
   precision_planes(e.precision, &ap, &wp);
@@ -197,11 +194,8 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
     } else
       MB_TRY(launch_attention_core_view(a, att, e.batch, e.embed, e.heads, 0, st));
     if (stream_w) {
-      MB_TRY(launch_skinny_linear(att, e.wout_t_f32, nullptr, e.y, rows, e.embed, e.embed, -1, e.skinny_scratch, e.skinny_scratch_bytes, st));
-      if (e.residual)
-        MB_TRY(launch_eltwise(MIMIR_B200_ELT_ADD, e.y, e.residual, e.y, 1, static_cast<int64_t>(rows) * e.embed,
-                              static_cast<int64_t>(rows) * e.embed, st));
-      return MIMIR_B200_OK;
+      return launch_skinny_linear(att, e.wout_t_f32, nullptr, e.y, rows, e.embed, e.embed, -1, e.skinny_scratch, e.skinny_scratch_bytes, st,
+                                  e.residual);
     }
     MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));
   } else

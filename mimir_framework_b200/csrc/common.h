@@ -96,7 +96,7 @@ struct GemmArgs {
 int launch_gemm(const GemmArgs& g, cudaStream_t st);
 // fp32 weight-streaming kernel for very small m (<= 16 rows): y[m,n] = x[m,k] · w[n,k]ᵀ + bias.
 int launch_skinny_linear(const float* x, const float* w, const float* bias, float* y, int m, int k, int n,
-                         int activation, float* scratch, size_t scratch_bytes, cudaStream_t st);
+                         int activation, float* scratch, size_t scratch_bytes, cudaStream_t st, const float* residual = nullptr);
 size_t skinny_scratch_bytes(int m, int k, int n);
 
 // pointwise.cu ---------------------------------------------------------------------------------

@@ -16,7 +16,9 @@
 // Each x vector read from shared memory is reused for all WR rows.  Every lane keeps WR x m partial sums; a
 // recursive-halving exchange (N/2 + N/4 + ... shuffles instead of 5 N) leaves each lane with the finished
 // sums of N / 32 outputs.  Partial sums over K slices go to a small global scratch and are reduced in a
-// fixed order by a second kernel (deterministic, no atomics).  Unaligned operands or K % 4 != 0 take a
+// fixed order by a second kernel (deterministic, no atomics), which also adds bias, activation and a folded residual.
+// (Letting the CTA that delivers a tile's last slice do that sum was measured and dropped: the fence it needs after
+// every item drains the asynchronous copies, 0.34 -> 0.52 ms on the registry transformer.)  Unaligned operands or K % 4 != 0 take a
 // plain-load kernel with the same arithmetic.
 #include <cstdlib>
 
@@ -251,8 +253,8 @@ skinny_stream_kernel(const float* __restrict__ x, const float* __restrict__ w, f
   cp_async_wait<0>();
 }
 
-__global__ void skinny_finish_kernel(const float* __restrict__ part, const float* __restrict__ bias, float* __restrict__ y,
-                                     int m, int n, int kslices, int act) {
+__global__ void skinny_finish_kernel(const float* __restrict__ part, const float* __restrict__ bias, const float* __restrict__ residual,
+                                     float* __restrict__ y, int m, int n, int kslices, int act) {
   const long long total = static_cast<long long>(m) * n;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -260,7 +262,9 @@ __global__ void skinny_finish_kernel(const float* __restrict__ part, const float
     float s = 0.0f;
     for (int ks = 0; ks < kslices; ++ks) s += part[static_cast<long long>(ks) * total + i];
     if (bias != nullptr) s += __ldg(bias + o);
-    y[i] = sk_act(s, act);
+    s = sk_act(s, act);
+    if (residual != nullptr) s += __ldg(residual + i);  // a residual Add folded into this layer
+    y[i] = s;
   }
 }
 
@@ -296,7 +300,7 @@ size_t skinny_scratch_bytes(int m, int k, int n) {
 }
 
 int launch_skinny_linear(const float* x, const float* w, const float* bias, float* y, int m, int k, int n, int activation,
-                         float* scratch, size_t scratch_bytes, cudaStream_t st) {
+                         float* scratch, size_t scratch_bytes, cudaStream_t st, const float* residual) {
   if (m <= 0 || m > 16 || k <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "skinny linear: m must be in 1..16");
   if (scratch == nullptr || scratch_bytes < skinny_scratch_bytes(m, k, n))
     return fail(MIMIR_B200_E_INVALID, "skinny linear: scratch too small");
@@ -307,7 +311,7 @@ int launch_skinny_linear(const float* x, const float* w, const float* bias, floa
   const long long total = static_cast<long long>(m) * n;
   int fb = static_cast<int>((total + 255) / 256);
   if (fb > ctx().sm_count * 8) fb = ctx().sm_count * 8;
-  skinny_finish_kernel<<<fb, 256, 0, st>>>(scratch, bias, y, m, n, (k + SK_SLICE - 1) / SK_SLICE, activation);
+  skinny_finish_kernel<<<fb, 256, 0, st>>>(scratch, bias, residual, y, m, n, (k + SK_SLICE - 1) / SK_SLICE, activation);
   MB_CUDA(cudaGetLastError());
   count_launch(2);
   return MIMIR_B200_OK;
