@@ -68,12 +68,24 @@ class ClockSampler:
     def _nvml_loop(self, nv, h, sm_max):
         masks = [("hw_slowdown", nv.nvmlClocksThrottleReasonHwSlowdown), ("hw_thermal_slowdown", nv.nvmlClocksThrottleReasonHwThermalSlowdown),
                  ("sw_thermal_slowdown", nv.nvmlClocksThrottleReasonSwThermalSlowdown), ("sw_power_cap", nv.nvmlClocksThrottleReasonSwPowerCap)]
+        # every other reason the driver reports is recorded too, so that a clock below maximum is never left unexplained
+        for name, attr in (("gpu_idle", "nvmlClocksThrottleReasonGpuIdle"), ("applications_clocks_setting", "nvmlClocksThrottleReasonApplicationsClocksSetting"),
+                           ("sync_boost", "nvmlClocksThrottleReasonSyncBoost"), ("hw_power_brake_slowdown", "nvmlClocksThrottleReasonHwPowerBrakeSlowdown"),
+                           ("display_clock_setting", "nvmlClocksThrottleReasonDisplayClockSetting")):
+            if hasattr(nv, attr):
+                masks.append((name, getattr(nv, attr)))
+        known = 0
+        for _, m in masks:
+            known |= m
         while not self.stop_flag:
             try:
                 sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
                 w = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
                 bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                self.rows.append((time.time(), float(sm), float(sm_max), w, [n for n, m in masks if bits & m]))
+                names = [n for n, m in masks if bits & m]
+                if bits & ~known:
+                    names.append("other_0x%x" % (bits & ~known))
+                self.rows.append((time.time(), float(sm), float(sm_max), w, names))
             except Exception:
                 pass
             time.sleep(0.005)
