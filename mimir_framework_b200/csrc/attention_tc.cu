@@ -49,6 +49,7 @@ struct AttnParams {
   int seq, embed, heads, causal;
   int bh;            // batch * heads
   float scale;
+  int qk_from_planes;  // Q and K tiles come straight from the QKV GEMM's output planes [2][batch*seq][3E] (5-D maps)
   int* err_word;
 };
 
@@ -88,6 +89,33 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
       const __nv_bfloat16 vh = __float2bfloat16_rn(v);
       vt[o] = vh;
       vt[o + v_plane] = __float2bfloat16_rn(v - __bfloat162float(vh));
+    }
+  }
+}
+
+// V third of the QKV planes [2][batch*seq][3E] -> V^T planes [2][bh][64][seqp] (keys contiguous), zero past seq
+__global__ void __launch_bounds__(256) attn_vt_kernel(const __nv_bfloat16* __restrict__ planes, __nv_bfloat16* __restrict__ vt, int seq,
+                                                      int seqp, int embed, int heads, int bh, long long rows) {
+  __shared__ __nv_bfloat16 tile[2][64][66];
+  const int s0 = blockIdx.x * 64;
+  const int b = blockIdx.y / heads, h = blockIdx.y - b * heads;
+  const long long ld = 3LL * embed;
+  const long long in_plane = rows * ld, v_plane = static_cast<long long>(bh) * AT_HD * seqp;
+  const __nv_bfloat16* base = planes + (static_cast<long long>(b) * seq) * ld + 2 * embed + h * AT_HD;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+  for (int r = ty; r < 64; r += 4) {
+    const int sidx = s0 + r;
+    tile[0][r][tx] = (sidx < seq) ? base[sidx * ld + tx] : zero;
+    tile[1][r][tx] = (sidx < seq) ? base[in_plane + sidx * ld + tx] : zero;
+  }
+  __syncthreads();
+  for (int d = ty; d < 64; d += 4) {
+    const int sidx = s0 + tx;
+    if (sidx < seqp) {
+      const long long o = (static_cast<long long>(blockIdx.y) * AT_HD + d) * seqp + sidx;
+      vt[o] = tile[0][tx][d];
+      vt[o + v_plane] = tile[1][tx][d];
     }
   }
 }
@@ -143,15 +171,26 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
   if (warp == 0) {
     if (lane == 0) {
+      const int smp = bhi / p.heads, hd_slot = bhi - smp * p.heads;  // coordinates in the 5-D maps: (d, s, sample, head slot, plane)
       mbar_expect_tx(q_full, 2 * AT_Q_BYTES);
-      tma_load_3d(sQ, &map_q, q_full, 0, q0, bhi);
-      tma_load_3d(sQ + AT_Q_BYTES, &map_q, q_full, 0, q0, p.bh + bhi);
+      if (p.qk_from_planes) {
+        tma_load_5d(sQ, &map_q, q_full, 0, q0, smp, hd_slot, 0);
+        tma_load_5d(sQ + AT_Q_BYTES, &map_q, q_full, 0, q0, smp, hd_slot, 1);
+      } else {
+        tma_load_3d(sQ, &map_q, q_full, 0, q0, bhi);
+        tma_load_3d(sQ + AT_Q_BYTES, &map_q, q_full, 0, q0, p.bh + bhi);
+      }
       for (int j = 0; j < n_tiles; ++j) {
         const uint32_t ph = j & 1;
         if (!mbar_wait(k_empty, ph ^ 1, abort_flag, p.err_word, 11)) break;
         mbar_expect_tx(k_full, 2 * AT_K_BYTES);
-        tma_load_3d(sK, &map_k, k_full, 0, j * AT_BK, bhi);
-        tma_load_3d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, p.bh + bhi);
+        if (p.qk_from_planes) {
+          tma_load_5d(sK, &map_k, k_full, 0, j * AT_BK, smp, p.heads + hd_slot, 0);
+          tma_load_5d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, smp, p.heads + hd_slot, 1);
+        } else {
+          tma_load_3d(sK, &map_k, k_full, 0, j * AT_BK, bhi);
+          tma_load_3d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, p.bh + bhi);
+        }
         if (!mbar_wait(v_empty, ph ^ 1, abort_flag, p.err_word, 12)) break;
         mbar_expect_tx(v_full, 2 * AT_V_BYTES);
         tma_load_3d(sV, &map_v, v_full, j * AT_BK, 0, bhi);
@@ -410,8 +449,33 @@ size_t attention_tc_ws_bytes(int batch, int seq, int embed) {
   return ((2 * qk + 255) & ~size_t(255)) + ((v + 255) & ~size_t(255)) + 512;
 }
 
+namespace {
+// 5-D map over the QKV planes [2][batch*seq][3E]: (d in head, position, sample, head slot of Q|K|V, plane)
+int make_map_qkv5(CUtensorMap* map, const void* base, int batch, int seq, int embed, uint32_t box_rows) {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  if (!fn) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const uint64_t ld = 3ull * embed;
+  cuuint64_t dims[5] = {AT_HD, static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(batch), ld / AT_HD, 2};
+  cuuint64_t strides[4] = {ld * 2, static_cast<cuuint64_t>(seq) * ld * 2, AT_HD * 2, static_cast<cuuint64_t>(batch) * seq * ld * 2};
+  cuuint32_t box[5] = {AT_HD, box_rows, 1, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MIMIR_B200_E_CUDA, "cuTensorMapEncodeTiled (QKV planes) failed (%d)", static_cast<int>(r));
+  return MIMIR_B200_OK;
+}
+
+}  // namespace
+
 int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, void* ws,
-                             cudaStream_t st, __nv_bfloat16* out_split, int planes) {
+                             cudaStream_t st, __nv_bfloat16* out_split, int planes, const __nv_bfloat16* qkv_planes) {
   if (!attention_tc_supported(seq, embed, heads)) return fail(MIMIR_B200_E_UNSUPPORTED, "attention: tensor-core core needs head_dim 64");
   const int bh = batch * heads;
   const int seqp = round_up(seq, 64);
@@ -422,11 +486,19 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   __nv_bfloat16* kp = reinterpret_cast<__nv_bfloat16*>(w + qk_bytes);
   __nv_bfloat16* vt = reinterpret_cast<__nv_bfloat16*>(w + ((2 * qk_bytes + 255) & ~size_t(255)));
   dim3 pgrid(seqp / 64, bh);
-  attn_prep_kernel<<<pgrid, 256, 0, st>>>(qkv, qp, kp, vt, seq, seqp, embed, heads, bh);
-  MB_CUDA(cudaGetLastError());
   CUtensorMap mq, mk, mv;
-  MB_TRY(make_map3(&mq, qp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BQ));
-  MB_TRY(make_map3(&mk, kp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BK));
+  if (qkv_planes != nullptr) {
+    // Q and K are read where the projection GEMM left them; only V needs turning around
+    attn_vt_kernel<<<pgrid, 256, 0, st>>>(qkv_planes, vt, seq, seqp, embed, heads, bh, static_cast<long long>(batch) * seq);
+    MB_CUDA(cudaGetLastError());
+    MB_TRY(make_map_qkv5(&mq, qkv_planes, batch, seq, embed, AT_BQ));
+    MB_TRY(make_map_qkv5(&mk, qkv_planes, batch, seq, embed, AT_BK));
+  } else {
+    attn_prep_kernel<<<pgrid, 256, 0, st>>>(qkv, qp, kp, vt, seq, seqp, embed, heads, bh);
+    MB_CUDA(cudaGetLastError());
+    MB_TRY(make_map3(&mq, qp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BQ));
+    MB_TRY(make_map3(&mk, kp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BK));
+  }
   MB_TRY(make_map3(&mv, vt, static_cast<uint64_t>(seqp), AT_HD, 2ull * bh, AT_BK, AT_HD));
   static bool attr = false;
   if (!attr) {
@@ -438,6 +510,7 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   p.out_split = out_split;  // embed = heads * 64, so the planes' padded row length equals embed
   p.plane_stride = static_cast<long long>(batch) * seq * embed;
   p.planes = planes;
+  p.qk_from_planes = qkv_planes != nullptr ? 1 : 0;
   p.seq = seq; p.embed = embed; p.heads = heads; p.causal = causal; p.bh = bh;
   p.scale = 1.0f / sqrtf(static_cast<float>(AT_HD));
   p.err_word = ctx().dev_error_word;

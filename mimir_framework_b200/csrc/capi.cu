@@ -152,6 +152,11 @@ size_t attention_ws_bytes(int batch, int seq, int embed, int heads, int precisio
   return b;
 }
 
+static bool no_qkv_planes() {
+  static const bool off = [] { const char* v = getenv("MIMIR_B200_ATTN_QKV_PLANES"); return v && v[0] == '0'; }();
+  return off;
+}
+
 int attention_exec(const AttentionExec& e, cudaStream_t st) {
   int ap, wp;
   precision_planes(e.precision, &ap, &wp);
@@ -163,6 +168,7 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   uint8_t* tc_ws = reinterpret_cast<uint8_t*>(att) + align256(static_cast<size_t>(rows) * e.embed * 4);
   // a decode step of a few samples: both projections stream fp32 weights (transposed copies, W[out][in]) instead of
   // running 128-row GEMM tiles that are almost empty
+  bool qkv_as_planes = false;
   const bool stream_w = e.decode_pos >= 0 && e.wqkv_t_f32 && e.wout_t_f32 && e.x && rows <= 16 && e.skinny_scratch;
   if (stream_w) {
     MB_TRY(launch_skinny_linear(e.x, e.wqkv_t_f32, nullptr, qkv, rows, e.embed, 3 * e.embed, -1, e.skinny_scratch, e.skinny_scratch_bytes, st));
@@ -170,7 +176,12 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
     if (!e.x_split) MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
     GemmArgs g;
     g.a = e.x_split ? e.x_split : xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
-    g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.out_f32 = qkv; g.ldo = 3 * e.embed;
+    g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.ldo = 3 * e.embed;
+    // the tensor-core attention core takes Q and K straight from hi/lo planes written by this GEMM's epilogue (they
+    // occupy the fp32 buffer's place: 2 planes x 2 bytes); a cache fill or decode step needs the fp32 rows
+    qkv_as_planes = attention_tc_supported(e.seq, e.embed, e.heads) && !e.kcache && e.decode_pos < 0 && !no_qkv_planes();
+    if (qkv_as_planes) g.out_split = reinterpret_cast<__nv_bfloat16*>(qkv);
+    else g.out_f32 = qkv;
     MB_TRY(launch_gemm(g, st));
   }
   if (e.kcache)
@@ -201,7 +212,8 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   } else
   // the attended rows go to the output projection as operand planes (the x planes are dead by now)
   if (attention_tc_supported(e.seq, e.embed, e.heads)) {
-    MB_TRY(launch_attention_core_tc(qkv, nullptr, e.batch, e.seq, e.embed, e.heads, e.causal, tc_ws, st, xs, ap));
+    MB_TRY(launch_attention_core_tc(qkv, nullptr, e.batch, e.seq, e.embed, e.heads, e.causal, tc_ws, st, xs, ap,
+                                    qkv_as_planes ? reinterpret_cast<const __nv_bfloat16*>(qkv) : nullptr));
   } else {
     MB_TRY(launch_attention_core(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, st));
     MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));

@@ -161,7 +161,8 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
 bool attention_tc_supported(int seq, int embed, int heads);
 size_t attention_tc_ws_bytes(int batch, int seq, int embed);
 int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, void* ws,
-                             cudaStream_t st, __nv_bfloat16* out_split = nullptr, int planes = 0);
+                             cudaStream_t st, __nv_bfloat16* out_split = nullptr, int planes = 0,
+                             const __nv_bfloat16* qkv_planes = nullptr);  // hi/lo planes [2][batch*seq][3E] instead of fp32 qkv
 
 // conv2d.cu ------------------------------------------------------------------------------------
 // im2col of NCHW fp32 into split planes [planes][batch*oh*ow][kp], k = ic*ks*ks ordered (ic, kh, kw)
