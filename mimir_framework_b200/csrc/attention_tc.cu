@@ -3,8 +3,11 @@
 // s = (Q.K) / sqrt(hd), causal rows skip j > i, p = exp(s - max), p *= 1 / (sum p + 1e-9), O = P V.
 //
 // Flash-style with QK^T and PV on tcgen05 and the online softmax in registers:
-//   * a pre-pass turns the fp32 QKV matrix into bf16 hi/lo planes laid out per (sample, head):
-//     Q and K as [seq][64] (K-major for Q K^T) and V transposed as [64][seq] (K-major for P V);
+//   * the operands are bf16 hi/lo planes.  Normally they are the planes [2][batch*seq][3E] that the QKV projection
+//     GEMM writes from its epilogue, read in place through 5-D tensor maps (d, position, sample, head slot, plane):
+//     Q and K tiles as [rows][64] (K-major for Q K^T), V tiles as [keys][64] rows used as an MN-major B operand of
+//     P V - no pre-pass at all.  (From an fp32 QKV matrix, e.g. when a key / value cache is being filled, a pre-pass
+//     lays the planes out per (sample, head), with V transposed to [64][seq] for a K-major P V.);
 //   * one CTA owns 128 query rows of one (sample, head) and walks the keys in tiles of 64:
 //       warp 0    TMA producer (Q once, then K_j, V_j; single-buffered, refilled as soon as the MMA
 //                 that read them has completed)
@@ -50,6 +53,7 @@ struct AttnParams {
   int bh;            // batch * heads
   float scale;
   int qk_from_planes;  // Q and K tiles come straight from the QKV GEMM's output planes [2][batch*seq][3E] (5-D maps)
+  int v_mn_major;      // ... and so do the V tiles, as [key][d] rows read by the MMA as an MN-major B operand
   int* err_word;
 };
 
@@ -193,8 +197,13 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         if (!mbar_wait(v_empty, ph ^ 1, abort_flag, p.err_word, 12)) break;
         mbar_expect_tx(v_full, 2 * AT_V_BYTES);
-        tma_load_3d(sV, &map_v, v_full, j * AT_BK, 0, bhi);
-        tma_load_3d(sV + AT_V_BYTES, &map_v, v_full, j * AT_BK, 0, p.bh + bhi);
+        if (p.v_mn_major) {
+          tma_load_5d(sV, &map_v, v_full, 0, j * AT_BK, smp, 2 * p.heads + hd_slot, 0);
+          tma_load_5d(sV + AT_V_BYTES, &map_v, v_full, 0, j * AT_BK, smp, 2 * p.heads + hd_slot, 1);
+        } else {
+          tma_load_3d(sV, &map_v, v_full, j * AT_BK, 0, bhi);
+          tma_load_3d(sV + AT_V_BYTES, &map_v, v_full, j * AT_BK, 0, p.bh + bhi);
+        }
       }
     }
   } else if (warp == 1) {
@@ -234,10 +243,14 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int k = 0; k < AT_BK / 16; ++k) {
           const uint32_t ko = k * 32;
           const uint64_t ph_ = make_smem_desc(aP + ko, 128), pl = make_smem_desc(aP + AT_P_BYTES + ko, 128);
-          const uint64_t vh = make_smem_desc(aV + ko, 128), vl = make_smem_desc(aV + AT_V_BYTES + ko, 128);
-          umma_bf16(tmem_o, ph_, vh, idesc, (j != 0 || k != 0) ? 1u : 0u);
-          umma_bf16(tmem_o, pl, vh, idesc, 1u);
-          umma_bf16(tmem_o, ph_, vl, idesc, 1u);
+          // V^T tile [d][keys]: K-major, 32 bytes along the row per 16 keys.  V tile [keys][d]: MN-major (bit 16 of the
+          // instruction descriptor), one 128-byte row per key, so 16 keys are two 1024-byte groups of eight rows
+          const uint32_t vo = p.v_mn_major ? k * 2048u : ko;
+          const uint32_t id_pv = p.v_mn_major ? (idesc | (1u << 16)) : idesc;
+          const uint64_t vh = make_smem_desc(aV + vo, 128), vl = make_smem_desc(aV + AT_V_BYTES + vo, 128);
+          umma_bf16(tmem_o, ph_, vh, id_pv, (j != 0 || k != 0) ? 1u : 0u);
+          umma_bf16(tmem_o, pl, vh, id_pv, 1u);
+          umma_bf16(tmem_o, ph_, vl, id_pv, 1u);
         }
         umma_commit(pv_done);
         umma_commit(v_empty);
@@ -487,10 +500,15 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   __nv_bfloat16* vt = reinterpret_cast<__nv_bfloat16*>(w + ((2 * qk_bytes + 255) & ~size_t(255)));
   dim3 pgrid(seqp / 64, bh);
   CUtensorMap mq, mk, mv;
+  // (MIMIR_B200_ATTN_V_MN=0 goes back to the transposed V^T planes: decoder configuration 22.0 instead of 21.0 ms)
+  static const bool v_mn_env = [] { const char* e = getenv("MIMIR_B200_ATTN_V_MN"); return !(e && e[0] == '0'); }();
+  const bool v_mn = v_mn_env && qkv_planes != nullptr;
   if (qkv_planes != nullptr) {
     // Q and K are read where the projection GEMM left them; only V needs turning around
-    attn_vt_kernel<<<pgrid, 256, 0, st>>>(qkv_planes, vt, seq, seqp, embed, heads, bh, static_cast<long long>(batch) * seq);
-    MB_CUDA(cudaGetLastError());
+    if (!v_mn) {
+      attn_vt_kernel<<<pgrid, 256, 0, st>>>(qkv_planes, vt, seq, seqp, embed, heads, bh, static_cast<long long>(batch) * seq);
+      MB_CUDA(cudaGetLastError());
+    }
     MB_TRY(make_map_qkv5(&mq, qkv_planes, batch, seq, embed, AT_BQ));
     MB_TRY(make_map_qkv5(&mk, qkv_planes, batch, seq, embed, AT_BK));
   } else {
@@ -499,7 +517,8 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
     MB_TRY(make_map3(&mq, qp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BQ));
     MB_TRY(make_map3(&mk, kp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BK));
   }
-  MB_TRY(make_map3(&mv, vt, static_cast<uint64_t>(seqp), AT_HD, 2ull * bh, AT_BK, AT_HD));
+  if (v_mn) MB_TRY(make_map_qkv5(&mv, qkv_planes, batch, seq, embed, AT_BK));
+  else MB_TRY(make_map3(&mv, vt, static_cast<uint64_t>(seqp), AT_HD, 2ull * bh, AT_BK, AT_HD));
   static bool attr = false;
   if (!attr) {
     MB_CUDA(cudaFuncSetAttribute(flash_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
@@ -511,6 +530,7 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   p.plane_stride = static_cast<long long>(batch) * seq * embed;
   p.planes = planes;
   p.qk_from_planes = qkv_planes != nullptr ? 1 : 0;
+  p.v_mn_major = v_mn ? 1 : 0;
   p.seq = seq; p.embed = embed; p.heads = heads; p.causal = causal; p.bh = bh;
   p.scale = 1.0f / sqrtf(static_cast<float>(AT_HD));
   p.err_word = ctx().dev_error_word;
