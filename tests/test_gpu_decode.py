@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 V, E, H, F = 50, 64, 2, 96
 
 
-def gpt(S):
+def gpt(S, E=E, H=H):
     """Token-wise decoder: Embedding -> 2 x [LayerNorm -> causal attention -> Add -> LayerNorm -> Linear -> GELU ->
     Linear -> Add] -> LayerNorm -> Linear to the vocabulary."""
     d = [make_desc("emb", "Embedding", inputs=["x"], output="h", vocab_size=V, embed_dim=E, padding_idx=-1, seq_len=S, params_count=V * E)]
@@ -44,9 +44,11 @@ def close(got, want, what):
 
 # 20 rows per step leave the weight-streaming path for the tensor-core GEMM; 300 positions span three key chunks of
 # the decode attention kernel
-@pytest.mark.parametrize("batch,S,P", [(2, 12, 7), (20, 12, 7), (3, 300, 292)])
-def test_decode_steps_reproduce_the_rows_of_the_full_causal_forward(backend, batch, S, P):
-    full = gpt(S)
+# head_dim 64 (E = 128) puts the prefill on the tensor-core attention core, whose cache-filling form lays fp32 QKV rows
+# out per head instead of reading the projection's planes in place
+@pytest.mark.parametrize("batch,S,P,E", [(2, 12, 7, 64), (20, 12, 7, 64), (3, 300, 292, 64), (2, 150, 140, 128)])
+def test_decode_steps_reproduce_the_rows_of_the_full_causal_forward(backend, batch, S, P, E):
+    full = gpt(S, E)
     weights = configs.seeded_weights(full, seed=3, std=0.08)
     ids = np.random.default_rng(batch).integers(0, V, (batch, S)).astype(np.float32)
     want = np.stack([port.run_graph(full, weights, {"x": ids[b]}).reshape(S, V) for b in range(batch)])  # [batch][S][V]
@@ -65,7 +67,7 @@ def test_decode_steps_reproduce_the_rows_of_the_full_causal_forward(backend, bat
     m.close()
 
     # (2) prefill of the first P tokens through the ordinary forward of a model built for P tokens, then steps
-    pre = gpt(P)
+    pre = gpt(P, E)
     m = backend.GraphModel(pre)
     for i, w in enumerate(weights):
         m.upload_weights(i, w)
