@@ -259,8 +259,18 @@ __global__ void skinny_finish_kernel(const float* __restrict__ part, const float
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int o = static_cast<int>(i % n);
+    // slices are added in slice order; eight loads are issued before the first add so that a long K (64 slices for
+    // in_features = 32768) does not pay the memory latency once per slice
     float s = 0.0f;
-    for (int ks = 0; ks < kslices; ++ks) s += part[static_cast<long long>(ks) * total + i];
+    int ks = 0;
+    for (; ks + 8 <= kslices; ks += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcs(part + static_cast<long long>(ks + u) * total + i);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s += v[u];
+    }
+    for (; ks < kslices; ++ks) s += __ldcs(part + static_cast<long long>(ks) * total + i);
     if (bias != nullptr) s += __ldg(bias + o);
     s = sk_act(s, act);
     if (residual != nullptr) s += __ldg(residual + i);  // a residual Add folded into this layer
