@@ -39,10 +39,11 @@ constexpr int AT_THREADS = 192;
 constexpr int AT_TMEM_COLS = 256;  // two S tiles (64 each) + the O tile (64); a power of two
 
 constexpr int AT_Q_BYTES = AT_BQ * AT_HD * 2;   // one plane
-constexpr int AT_K_BYTES = AT_BK * AT_HD * 2;
+constexpr int AT_K_BYTES = 2 * AT_BK * AT_HD * 2;  // one plane of a PAIR of key tiles: Q K^T is issued for 128 keys at a time
 constexpr int AT_V_BYTES = AT_HD * AT_BK * 2;
 constexpr int AT_P_BYTES = AT_BQ * AT_BK * 2;
-constexpr int AT_SMEM = 2 * AT_Q_BYTES + 2 * AT_K_BYTES + 2 * AT_V_BYTES + 2 * AT_P_BYTES + 256 + 1024;
+// no slack for aligning the base: two CTAs per SM leave none (the kernel checks the 1024-byte alignment it needs)
+constexpr int AT_SMEM = 2 * AT_Q_BYTES + 2 * AT_K_BYTES + 2 * AT_V_BYTES + 2 * AT_P_BYTES + 256;
 
 struct AttnParams {
   float* out;        // fp32 [batch*seq][embed], or nullptr
@@ -128,9 +129,13 @@ __global__ void __launch_bounds__(AT_THREADS, 2)
 flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need it; never seen, but a wrong answer must not be silent
+    if (threadIdx.x == 0) atomicExch(p.err_word, 29);
+    return;
+  }
   uint8_t* sQ = smem;                       // [2 planes][128][64] bf16, 128B-swizzled rows
-  uint8_t* sK = sQ + 2 * AT_Q_BYTES;        // [2][64 keys][64]
+  uint8_t* sK = sQ + 2 * AT_Q_BYTES;        // [2][128 keys][64]: two consecutive key tiles
   uint8_t* sV = sK + 2 * AT_K_BYTES;        // [2][64 d][64 keys]
   uint8_t* sP = sV + 2 * AT_V_BYTES;        // [2][128][64 keys]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * AT_P_BYTES);
@@ -186,14 +191,17 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
       for (int j = 0; j < n_tiles; ++j) {
         const uint32_t ph = j & 1;
-        if (!mbar_wait(k_empty, ph ^ 1, abort_flag, p.err_word, 11)) break;
-        mbar_expect_tx(k_full, 2 * AT_K_BYTES);
-        if (p.qk_from_planes) {
-          tma_load_5d(sK, &map_k, k_full, 0, j * AT_BK, smp, p.heads + hd_slot, 0);
-          tma_load_5d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, smp, p.heads + hd_slot, 1);
-        } else {
-          tma_load_3d(sK, &map_k, k_full, 0, j * AT_BK, bhi);
-          tma_load_3d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, p.bh + bhi);
+        if ((j & 1) == 0) {  // keys of tiles j and j + 1 in one 128-row box per plane
+          const uint32_t pp = static_cast<uint32_t>(j >> 1) & 1;
+          if (!mbar_wait(k_empty, pp ^ 1, abort_flag, p.err_word, 11)) break;
+          mbar_expect_tx(k_full, 2 * AT_K_BYTES);
+          if (p.qk_from_planes) {
+            tma_load_5d(sK, &map_k, k_full, 0, j * AT_BK, smp, p.heads + hd_slot, 0);
+            tma_load_5d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, smp, p.heads + hd_slot, 1);
+          } else {
+            tma_load_3d(sK, &map_k, k_full, 0, j * AT_BK, bhi);
+            tma_load_3d(sK + AT_K_BYTES, &map_k, k_full, 0, j * AT_BK, p.bh + bhi);
+          }
         }
         if (!mbar_wait(v_empty, ph ^ 1, abort_flag, p.err_word, 12)) break;
         mbar_expect_tx(v_full, 2 * AT_V_BYTES);
@@ -211,31 +219,34 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       constexpr uint32_t idesc = make_idesc(AT_BQ, AT_BK);  // M = 128, N = 64 for both products
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err_word, 13);
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
-      // S_t = Q K_t^T into score tile t & 1 (the tile's u-th use, u = t >> 1)
-      auto issue_scores = [&](int t) -> bool {
-        const int b = t & 1;
-        const uint32_t u = static_cast<uint32_t>(t >> 1) & 1;
-        if (!mbar_wait(k_full, t & 1, abort_flag, p.err_word, 14)) return false;
-        if (!mbar_wait(s_empty + b, u ^ 1, abort_flag, p.err_word, 15)) return false;
+      // S for the key tiles 2 pr and 2 pr + 1 in one go: the two TMEM score tiles are adjacent, so Q [K_2pr ; K_2pr+1]^T is
+      // a single N = 128 accumulator - twelve instructions for 128 keys instead of twenty-four (an instruction costs the
+      // same tensor-pipe time at N = 64 and N = 128)
+      constexpr uint32_t idesc_s = make_idesc(AT_BQ, 2 * AT_BK);
+      auto issue_scores = [&](int pr) -> bool {
+        const uint32_t u = static_cast<uint32_t>(pr) & 1;
+        if (!mbar_wait(k_full, u, abort_flag, p.err_word, 14)) return false;
+        if (!mbar_wait(s_empty, u ^ 1, abort_flag, p.err_word, 15)) return false;
+        if (!mbar_wait(s_empty + 1, u ^ 1, abort_flag, p.err_word, 15)) return false;
         tcgen05_fence_after();
-        const uint32_t tmem_s = tmem_base + b * AT_BK;
 #pragma unroll
         for (int k = 0; k < AT_HD / 16; ++k) {
           const uint32_t ko = k * 32;
           const uint64_t qh = make_smem_desc(aQ + ko, 128), ql = make_smem_desc(aQ + AT_Q_BYTES + ko, 128);
           const uint64_t kh = make_smem_desc(aK + ko, 128), kl = make_smem_desc(aK + AT_K_BYTES + ko, 128);
-          umma_bf16(tmem_s, qh, kh, idesc, k != 0 ? 1u : 0u);
-          umma_bf16(tmem_s, ql, kh, idesc, 1u);
-          umma_bf16(tmem_s, qh, kl, idesc, 1u);
+          umma_bf16(tmem_base, qh, kh, idesc_s, k != 0 ? 1u : 0u);
+          umma_bf16(tmem_base, ql, kh, idesc_s, 1u);
+          umma_bf16(tmem_base, qh, kl, idesc_s, 1u);
         }
-        umma_commit(s_full + b);
+        umma_commit(s_full);
+        umma_commit(s_full + 1);
         umma_commit(k_empty);
         return true;
       };
       if (ok && n_tiles > 0) ok = issue_scores(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const uint32_t ph = j & 1;
-        if (j + 1 < n_tiles && !issue_scores(j + 1)) break;
+        if ((j & 1) == 1 && j + 1 < n_tiles && !issue_scores((j + 1) >> 1)) break;  // the next pair, once both score tiles are read
         if (!mbar_wait(p_full, ph, abort_flag, p.err_word, 16)) break;
         if (!mbar_wait(v_full, ph, abort_flag, p.err_word, 17)) break;
         tcgen05_fence_after();
@@ -510,12 +521,12 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
       MB_CUDA(cudaGetLastError());
     }
     MB_TRY(make_map_qkv5(&mq, qkv_planes, batch, seq, embed, AT_BQ));
-    MB_TRY(make_map_qkv5(&mk, qkv_planes, batch, seq, embed, AT_BK));
+    MB_TRY(make_map_qkv5(&mk, qkv_planes, batch, seq, embed, 2 * AT_BK));
   } else {
     attn_prep_kernel<<<pgrid, 256, 0, st>>>(qkv, qp, kp, vt, seq, seqp, embed, heads, bh);
     MB_CUDA(cudaGetLastError());
     MB_TRY(make_map3(&mq, qp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BQ));
-    MB_TRY(make_map3(&mk, kp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BK));
+    MB_TRY(make_map3(&mk, kp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, 2 * AT_BK));
   }
   if (v_mn) MB_TRY(make_map_qkv5(&mv, qkv_planes, batch, seq, embed, AT_BK));
   else MB_TRY(make_map3(&mv, vt, static_cast<uint64_t>(seqp), AT_HD, 2ull * bh, AT_BK, AT_HD));
