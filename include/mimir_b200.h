@@ -76,13 +76,18 @@ typedef enum MimirB200Eltwise {
  * 1. Life cycle and budget
  * ------------------------------------------------------------------------------------------ */
 
-/* Binds the calling process to CUDA device `device` and sets the HBM budget that arena plans and
- * weight uploads are checked against (0 = 90 % of the device's total memory).  Idempotent and
- * thread-safe.  Replaces the engine construction in Model::Model() (Model.cpp:690-698, 753-878)
- * and MemoryGuard::setLimit (MemoryGuard.hpp:47-60). */
+/* Brings up the context of CUDA device `device` (one context per device, kept in a table) and makes that
+ * device current on the calling thread: the per-op calls and model_create of this thread then run on it.
+ * Sets the HBM budget that arena plans and weight uploads are checked against (0 = keep a limit set earlier
+ * through guard_set_limit, else 90 % of the device's total memory).  Idempotent and thread-safe; a process may
+ * initialise several devices (one host thread per device, or mimir_b200_replicas_*).  Model handles remember
+ * their device and switch to it themselves.  Replaces the engine construction in Model::Model()
+ * (Model.cpp:690-698, 753-878) and MemoryGuard::setLimit (MemoryGuard.hpp:47-60). */
 int mimir_b200_init(int device, size_t hbm_budget_bytes);
-/* Releases every model handle, the arena and the per-op cache.  Replaces the engine teardown in
- * Model::~Model() (Model.cpp:726-741). */
+/* The device the calling thread's per-op calls run on. */
+int mimir_b200_current_device(int* device);
+/* Releases every model handle on every device.  Replaces the engine teardown in Model::~Model()
+ * (Model.cpp:726-741). */
 int mimir_b200_shutdown(void);
 const char* mimir_b200_last_error(void);
 int mimir_b200_abi_version(void);
@@ -93,6 +98,16 @@ int mimir_b200_guard_set_limit(size_t bytes);
 int mimir_b200_guard_request(size_t bytes, const char* tag); /* OK or E_OOM_BUDGET */
 int mimir_b200_guard_release(size_t bytes);
 int mimir_b200_guard_stats(size_t* limit, size_t* current, size_t* peak);
+/* MemoryGuard::blockAllocations / freezeAllocations (MemoryGuard.hpp:37-72): while set, every request - the
+ * explicit guard_request and the library's own arena, weight and workspace allocations - is refused with
+ * E_OOM_BUDGET (blocked is checked before frozen, frozen before the limit, MemoryGuard.hpp:75-112); releases
+ * stay possible.  guard_reset is MemoryGuard::reset (MemoryGuard.hpp:181-186): usage and peak back to zero.
+ * guard_state reads both switches and the refused-attempt counters.  All guard verbs act on the calling
+ * thread's current device and work before mimir_b200_init (host logic only). */
+int mimir_b200_guard_block(int block);
+int mimir_b200_guard_freeze(int freeze);
+int mimir_b200_guard_reset(void);
+int mimir_b200_guard_state(int* blocked, int* frozen, size_t* blocked_attempts, size_t* frozen_attempts);
 
 /* ---------------------------------------------------------------------------------------------
  * 2. Per-op entry points, HOST pointers, synchronous (copy in, run, copy out).
@@ -291,8 +306,17 @@ int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, con
  * in).  upload_weights is this plus one host-to-device copy. */
 int mimir_b200_model_weights_device(MimirB200ModelHandle m, int layer_index, uint64_t n, float** dev);
 int mimir_b200_model_num_layers(MimirB200ModelHandle m, int* n_layers);
+/* Elements per sample of the graph's output tensor "x" in the current plan. */
+int mimir_b200_model_output_len(MimirB200ModelHandle m, uint64_t* per_sample);
 int mimir_b200_model_layer_info(MimirB200ModelHandle m, int layer_index, const char** name,
                                 uint64_t* params_count);
+/* Where the planner put a tensor inside one arena buffer: the graph input `input_name`, or the graph output when
+ * `input_name` is NULL.  Byte offset and byte size for one (micro-)batch.  Input slots are handed on to later
+ * tensors after their last consumer, so an output may share bytes with an input; the pipelined forward orders
+ * its copies accordingly.  Diagnostic view of the plan (the reference's counterpart is
+ * RuntimeAllocator::get_scratchpad's tag -> buffer map, RuntimeAllocator.hpp:240-280). */
+int mimir_b200_model_tensor_slot(MimirB200ModelHandle m, const char* input_name, uint64_t* offset,
+                                 uint64_t* bytes);
 /* Streams the tensors "<layer name>/weights" (F32, or BF16 widened on the device) of a safetensors
  * checkpoint straight into the device weight blocks, through pinned staging buffers, without a host
  * copy of the model.  Replaces the layer-weights part of SafeTensorsReader::load
@@ -334,6 +358,37 @@ int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput*
 int mimir_b200_model_decode_step(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs,
                                  int batch, int pos, float* out_host, uint64_t out_capacity, uint64_t* out_len);
 int mimir_b200_model_decode_end(MimirB200ModelHandle m);
+/* ---- one process, several GPUs -------------------------------------------------------------------------
+ * A full replica of the graph on each listed device; a batch is cut into contiguous slices (shard_range), one
+ * host thread per device runs its slice through mimir_b200_model_forward, and every slice's result is copied
+ * straight into its place in the caller's output buffer (pin it for full copy speed); then the threads are
+ * joined.  No device talks to another.  The reference is a single process whose forward loops over samples on
+ * the host (Model.cpp:4621-6824 called per sample; LuaScripting.cpp:625-683 holds the one context), so this is
+ * the call such a process makes to use all GPUs of a box.  A rank that fails does not stop the others; the
+ * status is the first failing rank's and the message names every failed rank ("replica 1 (device 1): ...").
+ *   shard_range:        slice [begin, end) of `total` units for `rank` of `world`; the first total % world ranks
+ *                       take one extra unit.  Pure host arithmetic.
+ *   replicas_create:    mimir_b200_init(device, hbm_budget_bytes) + model_create + set_precision per device.
+ *   upload_weights / set_pipeline / plan / forward: the model calls, fanned out; plan takes the TOTAL batch.
+ *   inject_failure:     test hook - the next forward fails on that rank on the host, before anything is launched.
+ *   selftest_join:      the fan-out / join with a stand-in job that touches no device (CPU-only check of the
+ *                       failure reporting). */
+typedef struct MimirB200Replicas* MimirB200ReplicasHandle;
+int mimir_b200_shard_range(long long total, int world, int rank, long long* begin, long long* end);
+int mimir_b200_replicas_create(const int* devices, int n_devices, size_t hbm_budget_bytes,
+                               const MimirLayerDesc* layers, int n_layers, int precision,
+                               MimirB200ReplicasHandle* out);
+int mimir_b200_replicas_destroy(MimirB200ReplicasHandle h);
+int mimir_b200_replicas_count(MimirB200ReplicasHandle h, int* n_devices);
+int mimir_b200_replicas_upload_weights(MimirB200ReplicasHandle h, int layer_index, const float* host, uint64_t n);
+int mimir_b200_replicas_set_pipeline(MimirB200ReplicasHandle h, int micro_batches);
+int mimir_b200_replicas_plan(MimirB200ReplicasHandle h, const MimirNamedInput* inputs, int n_inputs,
+                             int batch_total, uint64_t* arena_peak_bytes);
+int mimir_b200_replicas_forward(MimirB200ReplicasHandle h, const MimirNamedInput* inputs, int n_inputs,
+                                int batch_total, float* out_host, uint64_t out_capacity, uint64_t* out_len);
+int mimir_b200_replicas_inject_failure(MimirB200ReplicasHandle h, int rank);
+int mimir_b200_replicas_selftest_join(int n_ranks, int fail_rank);
+
 /* Per-position argmax over rows of `n` (first maximum wins), for token ids.  No counterpart layer
  * in the reference (harness step of the decoder config). */
 int mimir_b200_argmax_rows_device(const float* x_dev, int32_t* ids_dev, long long rows, int n,
@@ -360,8 +415,11 @@ int mimir_b200_dev_rmsnorm(const float* x, const float* gamma, long long n_gamma
  * a step of a latency-critical serving loop (an allocation synchronises the device), a process
  * that has given all free device memory to its own pool, a plugin whose host forbids allocation.
  * This entry point has no counterpart in the reference.  Same arithmetic as
- * mimir_b200_dev_rmsnorm's long-row path (per-chunk sums of squares, then normalise), but the
- * partial sums live in a fixed 64 KB array inside the library (held on every GPU that loads it).
+ * mimir_b200_dev_rmsnorm's chunked path (per-chunk sums of squares; for samples above 16 384
+ * elements also the rounding errors of the reference's one sequential fp32 sum, so the result
+ * agrees with the CPU path like the regular entry point's does; then normalise), but the partial
+ * sums and error terms live in a fixed 192 KB array inside the library (held on every GPU that
+ * loads it).
  * Limit: batch * ceil(n / 8192) <= 16384 and batch <= 65535, else E_INVALID.  It neither needs nor
  * calls mimir_b200_init.  The first call on each device looks up the array's device address, so
  * make that first call outside any stream capture.  All calls share the array: calls that may

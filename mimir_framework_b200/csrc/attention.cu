@@ -310,11 +310,11 @@ __global__ void attn_row_kernel(const AttnView a, float* __restrict__ out, int e
 template <int HD>
 int launch_flash(const AttnView& a, float* out, int batch, int embed, int heads, int causal, float scale, cudaStream_t st) {
   constexpr int SMEM = (2 * HD * LDT + BKV * HD + BKV * LDT) * 4;
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceOnce attr_once;
+  MB_TRY(attr_once.run([&]() -> int {
     MB_CUDA(cudaFuncSetAttribute(flash_attn_fp32_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    attr = true;
-  }
+    return MIMIR_B200_OK;
+  }));
   dim3 grid((a.q_len + BQ - 1) / BQ, heads, batch);
   flash_attn_fp32_kernel<HD><<<grid, 256, SMEM, st>>>(a, out, embed, heads, causal, scale);
   MB_CUDA(cudaGetLastError());
@@ -341,11 +341,11 @@ int launch_attention_core_view(const AttnView& a, float* out, int batch, int emb
   const size_t smem = static_cast<size_t>(AR) * (hd + a.kv_len) * 4;
   if (smem > 200 * 1024 || batch > 65535 || heads > 65535)
     return fail(MIMIR_B200_E_UNSUPPORTED, "attention: %d keys with head_dim %d exceed the row kernel's shared memory", a.kv_len, hd);
-  static size_t attr_bytes = 0;
-  if (smem > 48 * 1024 && smem > attr_bytes) {
-    MB_CUDA(cudaFuncSetAttribute(attn_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    attr_bytes = smem;
-  }
+  static PerDeviceOnce attr_once;  // the largest size the launcher admits, once per device
+  MB_TRY(attr_once.run([&]() -> int {
+    MB_CUDA(cudaFuncSetAttribute(attn_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    return MIMIR_B200_OK;
+  }));
   dim3 grid((a.q_len + AR - 1) / AR, heads, batch);
   attn_row_kernel<<<grid, 256, smem, st>>>(a, out, embed, heads, hd, causal, scale);
   MB_CUDA(cudaGetLastError());

@@ -27,6 +27,7 @@
 // Every mbarrier wait is bounded; on expiry the CTA raises its abort flag, sets the device error word,
 // leaves all loops and frees its TMEM.
 #include "common.h"
+#include "planes.cuh"
 #include "sm100_ptx.cuh"
 
 namespace mb {
@@ -55,13 +56,15 @@ struct AttnParams {
   float scale;
   int qk_from_planes;  // Q and K tiles come straight from the QKV GEMM's output planes [2][batch*seq][3E] (5-D maps)
   int v_mn_major;      // ... and so do the V tiles, as [key][d] rows read by the MMA as an MN-major B operand
+  int f16;             // operand planes hold IEEE half instead of bfloat16
+  float acc_comp;      // relative loss of the truncating fp32 accumulation per MMA (0 = no compensation)
   int* err_word;
 };
 
 // fp32 QKV [batch*seq][3E] -> bf16 planes: Q, K as [plane][bh][seq][64]; V^T as [plane][bh][64][seqp]
 __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ qp,
                                                         __nv_bfloat16* __restrict__ kp, __nv_bfloat16* __restrict__ vt, int seq,
-                                                        int seqp, int embed, int heads, int bh) {
+                                                        int seqp, int embed, int heads, int bh, int f16) {
   __shared__ float tile[64][65];
   const int s0 = blockIdx.x * 64;       // 64 sequence positions
   const int b = blockIdx.y / heads, h = blockIdx.y - b * heads;
@@ -76,11 +79,13 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
     if (sidx < seq) {
       const float q = __ldg(base + sidx * ld + tx), k = __ldg(base + sidx * ld + embed + tx);
       const long long o = (static_cast<long long>(blockIdx.y) * seq + sidx) * AT_HD + tx;
-      const __nv_bfloat16 qh = __float2bfloat16_rn(q), kh = __float2bfloat16_rn(k);
-      qp[o] = qh;
-      qp[o + qk_plane] = __float2bfloat16_rn(q - __bfloat162float(qh));
-      kp[o] = kh;
-      kp[o + qk_plane] = __float2bfloat16_rn(k - __bfloat162float(kh));
+      uint16_t qh, ql, kh, kl;
+      split_one(q, f16, qh, ql);
+      split_one(k, f16, kh, kl);
+      reinterpret_cast<uint16_t*>(qp)[o] = qh;
+      reinterpret_cast<uint16_t*>(qp)[o + qk_plane] = ql;
+      reinterpret_cast<uint16_t*>(kp)[o] = kh;
+      reinterpret_cast<uint16_t*>(kp)[o + qk_plane] = kl;
     }
     tile[r][tx] = (sidx < seq) ? __ldg(base + sidx * ld + 2 * embed + tx) : 0.0f;
   }
@@ -91,9 +96,10 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const float* __restrict_
     if (sidx < seqp) {
       const float v = tile[tx][d];
       const long long o = (static_cast<long long>(blockIdx.y) * AT_HD + d) * seqp + sidx;
-      const __nv_bfloat16 vh = __float2bfloat16_rn(v);
-      vt[o] = vh;
-      vt[o + v_plane] = __float2bfloat16_rn(v - __bfloat162float(vh));
+      uint16_t vh, vl;
+      split_one(v, f16, vh, vl);
+      reinterpret_cast<uint16_t*>(vt)[o] = vh;
+      reinterpret_cast<uint16_t*>(vt)[o + v_plane] = vl;
     }
   }
 }
@@ -108,7 +114,7 @@ __global__ void __launch_bounds__(256) attn_vt_kernel(const __nv_bfloat16* __res
   const long long in_plane = rows * ld, v_plane = static_cast<long long>(bh) * AT_HD * seqp;
   const __nv_bfloat16* base = planes + (static_cast<long long>(b) * seq) * ld + 2 * embed + h * AT_HD;
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-  const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);
+  const __nv_bfloat16 zero = __float2bfloat16_rn(0.0f);  // all-zero bits in either plane format
   for (int r = ty; r < 64; r += 4) {
     const int sidx = s0 + r;
     tile[0][r][tx] = (sidx < seq) ? base[sidx * ld + tx] : zero;
@@ -216,13 +222,13 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(AT_BQ, AT_BK);  // M = 128, N = 64 for both products
+      const uint32_t idesc = make_idesc(AT_BQ, AT_BK, p.f16);  // M = 128, N = 64 for both products
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err_word, 13);
       const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
       // S for the key tiles 2 pr and 2 pr + 1 in one go: the two TMEM score tiles are adjacent, so Q [K_2pr ; K_2pr+1]^T is
       // a single N = 128 accumulator - twelve instructions for 128 keys instead of twenty-four (an instruction costs the
       // same tensor-pipe time at N = 64 and N = 128)
-      constexpr uint32_t idesc_s = make_idesc(AT_BQ, 2 * AT_BK);
+      const uint32_t idesc_s = make_idesc(AT_BQ, 2 * AT_BK, p.f16);
       auto issue_scores = [&](int pr) -> bool {
         const uint32_t u = static_cast<uint32_t>(pr) & 1;
         if (!mbar_wait(k_full, u, abort_flag, p.err_word, 14)) return false;
@@ -365,11 +371,7 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const float p0 = exp2f(fmaf(__uint_as_float(u0), c2, -m2));
             const float p1 = exp2f(fmaf(__uint_as_float(u1), c2, -m2));
             rs4[c8] += p0 + p1;
-            const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-            const float2 hf = __bfloat1622float2(h2);
-            const __nv_bfloat162 l2 = __floats2bfloat162_rn(p0 - hf.x, p1 - hf.y);
-            hi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
-            lo[e >> 1] = *reinterpret_cast<const uint32_t*>(&l2);
+            split_pair(p0, p1, p.f16, hi[e >> 1], lo[e >> 1]);
           }
           const int chunk = (half * 4 + c8) ^ sw;
           *reinterpret_cast<uint4*>(p_row_hi + chunk * 16) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
@@ -386,7 +388,12 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (alive && n_tiles > 0) alive = warp_wait(pv_done, static_cast<uint32_t>(n_tiles - 1) & 1, 22);
     if (alive) {
       tcgen05_fence_after();
-      const float inv = 1.0f / (l_run + 1e-9f);  // LayerOps.hpp:1076
+      // 1 / (sum p + 1e-9) (LayerOps.hpp:1076), times the compensation for the truncating accumulation of P V: every
+      // tcgen05.mma that added non-zero products into this row of O (three per 16 visible keys) lost about 1.5e-8 of
+      // the running value (measured; the same constant as in the GEMM kernel).  Keys behind the causal mask add exact
+      // zeros and lose nothing.
+      const int keys_seen = p.causal ? min(p.seq, row + 1) : p.seq;
+      const float inv = (1.0f + p.acc_comp * static_cast<float>(3 * ((keys_seen + 15) / 16))) / (l_run + 1e-9f);
       const int bb = bhi / p.heads, h = bhi - bb * p.heads;
       const long long o_off = (static_cast<long long>(bb) * p.seq + row) * p.embed + h * AT_HD;
 #pragma unroll
@@ -411,11 +418,7 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
               for (int e = 0; e < 8; e += 2) {
                 const float f0 = __uint_as_float(v[c + e]) * inv, f1 = __uint_as_float(v[c + e + 1]) * inv;
-                const __nv_bfloat162 h2 = __floats2bfloat162_rn(f0, f1);
-                const float2 hf = __bfloat1622float2(h2);
-                const __nv_bfloat162 l2 = __floats2bfloat162_rn(f0 - hf.x, f1 - hf.y);
-                hi[e >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
-                lo[e >> 1] = *reinterpret_cast<const uint32_t*>(&l2);
+                split_pair(f0, f1, p.f16, hi[e >> 1], lo[e >> 1]);
               }
               *reinterpret_cast<uint4*>(oh + c) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
               if (p.planes == 2) *reinterpret_cast<uint4*>(oh + p.plane_stride + c) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -523,18 +526,18 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
     MB_TRY(make_map_qkv5(&mq, qkv_planes, batch, seq, embed, AT_BQ));
     MB_TRY(make_map_qkv5(&mk, qkv_planes, batch, seq, embed, 2 * AT_BK));
   } else {
-    attn_prep_kernel<<<pgrid, 256, 0, st>>>(qkv, qp, kp, vt, seq, seqp, embed, heads, bh);
+    attn_prep_kernel<<<pgrid, 256, 0, st>>>(qkv, qp, kp, vt, seq, seqp, embed, heads, bh, plane_format() == PLANES_F16);
     MB_CUDA(cudaGetLastError());
     MB_TRY(make_map3(&mq, qp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, AT_BQ));
     MB_TRY(make_map3(&mk, kp, AT_HD, static_cast<uint64_t>(seq), 2ull * bh, AT_HD, 2 * AT_BK));
   }
   if (v_mn) MB_TRY(make_map_qkv5(&mv, qkv_planes, batch, seq, embed, AT_BK));
   else MB_TRY(make_map3(&mv, vt, static_cast<uint64_t>(seqp), AT_HD, 2ull * bh, AT_BK, AT_HD));
-  static bool attr = false;
-  if (!attr) {
+  static PerDeviceOnce attr_once;
+  MB_TRY(attr_once.run([&]() -> int {
     MB_CUDA(cudaFuncSetAttribute(flash_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM));
-    attr = true;
-  }
+    return MIMIR_B200_OK;
+  }));
   AttnParams p;
   p.out = out;
   p.out_split = out_split;  // embed = heads * 64, so the planes' padded row length equals embed
@@ -545,6 +548,9 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   p.seq = seq; p.embed = embed; p.heads = heads; p.causal = causal; p.bh = bh;
   p.scale = 1.0f / sqrtf(static_cast<float>(AT_HD));
   p.err_word = ctx().dev_error_word;
+  static const bool comp = [] { const char* e = getenv("MIMIR_B200_ACC_COMP"); return !(e && e[0] == '0'); }();
+  p.acc_comp = comp ? 1.5e-8f : 0.0f;
+  p.f16 = plane_format() == PLANES_F16 ? 1 : 0;
   dim3 grid((seq + AT_BQ - 1) / AT_BQ, bh);
   flash_attn_tc_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(mq, mk, mv, p);
   MB_CUDA(cudaGetLastError());

@@ -29,17 +29,32 @@ int fail(int status, const char* fmt, ...) {
   return status;
 }
 
+static Context g_ctx[MAX_DEVICES];
+
+Context& ctx_of(int device) { return g_ctx[(device >= 0 && device < MAX_DEVICES) ? device : 0]; }
+
 Context& ctx() {
-  static Context c;
-  return c;
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess) {
+    cudaGetLastError();  // no driver / no device: not an error of the caller's
+    d = 0;
+  }
+  return ctx_of(d);
 }
 
-bool Guard::request(size_t bytes) {
+int Guard::request_why(size_t bytes) {
   std::lock_guard<std::mutex> lk(mu);
-  if (limit != 0 && current + bytes > limit) return false;
+  if (blocked) { ++blocked_attempts; return 2; }
+  if (frozen) { ++frozen_attempts; return 3; }
+  if (limit != 0 && current + bytes > limit) return 1;
   current += bytes;
   if (current > peak) peak = current;
-  return true;
+  return 0;
+}
+void Guard::reset() {
+  std::lock_guard<std::mutex> lk(mu);
+  current = 0;
+  peak = 0;
 }
 void Guard::release(size_t bytes) {
   std::lock_guard<std::mutex> lk(mu);
@@ -50,9 +65,10 @@ int dev_alloc(void** p, size_t bytes, const char* tag) {
   *p = nullptr;
   if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
   if (bytes == 0) return MIMIR_B200_OK;
-  if (!ctx().guard.request(bytes))
-    return fail(MIMIR_B200_E_OOM_BUDGET, "HBM budget refused %zu bytes for %s (limit %zu, in use %zu)", bytes, tag,
-                ctx().guard.limit, ctx().guard.current);
+  if (const int why = ctx().guard.request_why(bytes))
+    return fail(MIMIR_B200_E_OOM_BUDGET, "HBM budget refused %zu bytes for %s (%s; limit %zu, in use %zu)", bytes, tag,
+                why == 2 ? "allocations are blocked" : why == 3 ? "allocations are frozen" : "over the limit", ctx().guard.limit,
+                ctx().guard.current);
   cudaError_t e = cudaMalloc(p, bytes);
   if (e != cudaSuccess) {
     ctx().guard.release(bytes);
@@ -128,6 +144,7 @@ int linear_exec(const LinearExec& e, cudaStream_t st) {
   g.w = e.w_split;
   g.a_planes = ap;
   g.w_planes = wp;
+  g.w_scale = e.w_scale;
   g.m = e.rows;
   g.n = e.out_f;
   g.k = e.in_f;
@@ -175,7 +192,7 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   } else {
     if (!e.x_split) MB_TRY(launch_split(e.x, xs, rows, e.embed, ap, st));
     GemmArgs g;
-    g.a = e.x_split ? e.x_split : xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp;
+    g.a = e.x_split ? e.x_split : xs; g.w = e.wqkv_split; g.a_planes = ap; g.w_planes = wp; g.w_scale = e.w_scale;
     g.m = rows; g.n = 3 * e.embed; g.k = e.embed; g.ldo = 3 * e.embed;
     // the tensor-core attention core takes Q and K straight from hi/lo planes written by this GEMM's epilogue (they
     // occupy the fp32 buffer's place: 2 planes x 2 bytes); a cache fill or decode step needs the fp32 rows
@@ -219,7 +236,7 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
     MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));
   }
   GemmArgs o;
-  o.a = xs; o.w = e.wout_split; o.a_planes = ap; o.w_planes = wp;
+  o.a = xs; o.w = e.wout_split; o.a_planes = ap; o.w_planes = wp; o.w_scale = e.w_scale;
   o.m = rows; o.n = e.embed; o.k = e.embed; o.out_f32 = e.y; o.ldo = e.embed; o.residual = e.residual;
   return launch_gemm(o, st);
 }
@@ -276,7 +293,7 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
     GemmArgs g;
     g.a = static_cast<const __nv_bfloat16*>(e.ws);
     g.w = e.w_split;
-    g.a_planes = ap; g.w_planes = wp;
+    g.a_planes = ap; g.w_planes = wp; g.w_scale = e.w_scale;
     g.m = static_cast<int>(rows); g.n = e.oc; g.k = k;
     g.activation = e.activation;
     g.out_f32 = e.y;
@@ -293,7 +310,7 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
     GemmArgs g;
     g.a = static_cast<const __nv_bfloat16*>(e.ws);
     g.w = e.w_split;
-    g.a_planes = ap; g.w_planes = wp;
+    g.a_planes = ap; g.w_planes = wp; g.w_scale = e.w_scale;
     g.m = bc * ohw; g.n = e.oc; g.k = k;
     g.activation = e.activation;
     g.out_f32 = e.y + static_cast<size_t>(b0) * e.oc * ohw;
@@ -325,18 +342,19 @@ const char* mimir_b200_last_error(void) { return mb::last_error().c_str(); }
 
 int mimir_b200_init(int device, size_t hbm_budget_bytes) {
   std::lock_guard<std::mutex> lk(g_init_mu);
-  Context& c = ctx();
-  if (c.initialised) {
-    if (device != c.device) return fail(MIMIR_B200_E_INVALID, "already initialised on device %d", c.device);
-    if (hbm_budget_bytes) c.guard.limit = hbm_budget_bytes;
-    return MIMIR_B200_OK;
-  }
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
   if (e != cudaSuccess || count <= 0)
     return fail(MIMIR_B200_E_CUDA, "no CUDA device: %s (this backend has no CPU fallback)", cudaGetErrorString(e));
-  if (device < 0 || device >= count) return fail(MIMIR_B200_E_INVALID, "device %d out of range (0..%d)", device, count - 1);
+  if (device < 0 || device >= count || device >= MAX_DEVICES)
+    return fail(MIMIR_B200_E_INVALID, "device %d out of range (0..%d)", device, (count < MAX_DEVICES ? count : MAX_DEVICES) - 1);
+  // the device becomes current on the calling thread: per-op calls and model_create of this thread run on it
   MB_CUDA(cudaSetDevice(device));
+  Context& c = ctx_of(device);
+  if (c.initialised) {
+    if (hbm_budget_bytes) c.guard.limit = hbm_budget_bytes;
+    return MIMIR_B200_OK;
+  }
   cudaDeviceProp prop;
   MB_CUDA(cudaGetDeviceProperties(&prop, device));
   if (prop.major != 10)
@@ -346,9 +364,12 @@ int mimir_b200_init(int device, size_t hbm_budget_bytes) {
   c.sm_count = prop.multiProcessorCount;
   size_t free_b = 0, total_b = 0;
   MB_CUDA(cudaMemGetInfo(&free_b, &total_b));
-  c.guard.limit = hbm_budget_bytes ? hbm_budget_bytes : static_cast<size_t>(total_b * 0.9);
-  c.guard.current = 0;
-  c.guard.peak = 0;
+  {
+    std::lock_guard<std::mutex> gl(c.guard.mu);
+    // a limit set through guard_set_limit before init (selection by environment) is kept
+    if (hbm_budget_bytes) c.guard.limit = hbm_budget_bytes;
+    else if (c.guard.limit == 0) c.guard.limit = static_cast<size_t>(total_b * 0.9);
+  }
   c.initialised = true;
   void* w = nullptr;
   int s = dev_alloc(&w, 256, "error_word");
@@ -361,29 +382,57 @@ int mimir_b200_init(int device, size_t hbm_budget_bytes) {
   return MIMIR_B200_OK;
 }
 
-int mimir_b200_guard_set_limit(size_t bytes) {
+int mimir_b200_current_device(int* device) {
+  if (!device) return fail(MIMIR_B200_E_INVALID, "current_device: null argument");
   MB_REQUIRE_INIT();
+  *device = ctx().device;
+  return MIMIR_B200_OK;
+}
+
+/* The guard verbs are host logic: they work before mimir_b200_init (on the calling thread's current device, device 0
+ * on a machine without one), so a limit can be in place before the first allocation. */
+int mimir_b200_guard_set_limit(size_t bytes) {
   std::lock_guard<std::mutex> lk(ctx().guard.mu);
   ctx().guard.limit = bytes;
   return MIMIR_B200_OK;
 }
 int mimir_b200_guard_request(size_t bytes, const char* tag) {
-  MB_REQUIRE_INIT();
-  if (!ctx().guard.request(bytes))
-    return fail(MIMIR_B200_E_OOM_BUDGET, "HBM budget refused %zu bytes for %s", bytes, tag ? tag : "?");
+  if (const int why = ctx().guard.request_why(bytes))
+    return fail(MIMIR_B200_E_OOM_BUDGET, "HBM budget refused %zu bytes for %s (%s)", bytes, tag ? tag : "?",
+                why == 2 ? "allocations are blocked" : why == 3 ? "allocations are frozen" : "over the limit");
   return MIMIR_B200_OK;
 }
 int mimir_b200_guard_release(size_t bytes) {
-  MB_REQUIRE_INIT();
   ctx().guard.release(bytes);
   return MIMIR_B200_OK;
 }
 int mimir_b200_guard_stats(size_t* limit, size_t* current, size_t* peak) {
-  MB_REQUIRE_INIT();
   std::lock_guard<std::mutex> lk(ctx().guard.mu);
   if (limit) *limit = ctx().guard.limit;
   if (current) *current = ctx().guard.current;
   if (peak) *peak = ctx().guard.peak;
+  return MIMIR_B200_OK;
+}
+int mimir_b200_guard_block(int block) {
+  std::lock_guard<std::mutex> lk(ctx().guard.mu);
+  ctx().guard.blocked = block != 0;
+  return MIMIR_B200_OK;
+}
+int mimir_b200_guard_freeze(int freeze) {
+  std::lock_guard<std::mutex> lk(ctx().guard.mu);
+  ctx().guard.frozen = freeze != 0;
+  return MIMIR_B200_OK;
+}
+int mimir_b200_guard_reset(void) {
+  ctx().guard.reset();
+  return MIMIR_B200_OK;
+}
+int mimir_b200_guard_state(int* blocked, int* frozen, size_t* blocked_attempts, size_t* frozen_attempts) {
+  std::lock_guard<std::mutex> lk(ctx().guard.mu);
+  if (blocked) *blocked = ctx().guard.blocked ? 1 : 0;
+  if (frozen) *frozen = ctx().guard.frozen ? 1 : 0;
+  if (blocked_attempts) *blocked_attempts = ctx().guard.blocked_attempts;
+  if (frozen_attempts) *frozen_attempts = ctx().guard.frozen_attempts;
   return MIMIR_B200_OK;
 }
 
@@ -406,7 +455,8 @@ int mimir_b200_linear_forward_ex(const float* input, const float* weights, const
     precision_planes(precision, &ap, &wp);
     void* wsplit;
     MB_TRY(t.alloc(&wsplit, split_bytes(out_f, in_f, wp), "linear.wsplit"));
-    MB_TRY(launch_split(e.w_f32, static_cast<__nv_bfloat16*>(wsplit), out_f, in_f, wp, nullptr));
+    MB_TRY(weight_plane_scale(e.w_f32, static_cast<size_t>(out_f) * in_f, nullptr, &e.w_scale));
+    MB_TRY(launch_split(e.w_f32, static_cast<__nv_bfloat16*>(wsplit), out_f, in_f, wp, nullptr, e.w_scale));
     e.w_split = static_cast<const __nv_bfloat16*>(wsplit);
   }
   MB_TRY(linear_exec(e, nullptr));
@@ -431,8 +481,9 @@ int mimir_b200_matmul(const float* A, const float* B, float* C, int M, int K, in
   MB_TRY(t.alloc(&as, split_bytes(M, K, 2), "matmul.as"));
   MB_TRY(t.alloc(&bs, split_bytes(N, K, 2), "matmul.bs"));
   MB_TRY(launch_split(a, static_cast<__nv_bfloat16*>(as), M, K, 2, nullptr));
-  MB_TRY(launch_split_transposed(b, static_cast<__nv_bfloat16*>(bs), K, N, 2, nullptr));
   GemmArgs g;
+  MB_TRY(weight_plane_scale(b, static_cast<size_t>(K) * N, nullptr, &g.w_scale));
+  MB_TRY(launch_split_transposed(b, static_cast<__nv_bfloat16*>(bs), K, N, 2, nullptr, g.w_scale));
   g.a = static_cast<const __nv_bfloat16*>(as);
   g.w = static_cast<const __nv_bfloat16*>(bs);
   g.m = M; g.n = N; g.k = K; g.out_f32 = c; g.ldo = N;
@@ -457,8 +508,9 @@ int mimir_b200_attention(const float* x, const float* wqkv_wout, float* y, int b
   void *wq, *wo;
   MB_TRY(t.alloc(&wq, split_bytes(3 * embed, embed, 2), "attn.wqkv"));
   MB_TRY(t.alloc(&wo, split_bytes(embed, embed, 2), "attn.wout"));
-  MB_TRY(launch_split_transposed(w, static_cast<__nv_bfloat16*>(wq), embed, 3 * embed, 2, nullptr));
-  MB_TRY(launch_split_transposed(w + 3 * E * E, static_cast<__nv_bfloat16*>(wo), embed, embed, 2, nullptr));
+  MB_TRY(weight_plane_scale(w, 4 * E * E, nullptr, &e.w_scale));
+  MB_TRY(launch_split_transposed(w, static_cast<__nv_bfloat16*>(wq), embed, 3 * embed, 2, nullptr, e.w_scale));
+  MB_TRY(launch_split_transposed(w + 3 * E * E, static_cast<__nv_bfloat16*>(wo), embed, embed, 2, nullptr, e.w_scale));
   e.wqkv_split = static_cast<const __nv_bfloat16*>(wq);
   e.wout_split = static_cast<const __nv_bfloat16*>(wo);
   MB_TRY(t.alloc(&e.ws, attention_ws_bytes(batch, seq, embed, heads, e.precision), "attn.ws"));
@@ -484,8 +536,9 @@ int mimir_b200_conv2d(const float* x, const float* w, float* y, int batch, int i
   MB_TRY(t.out(&e.y, static_cast<size_t>(batch) * oc * oh * ow, "conv.y"));
   void* ws;
   MB_TRY(t.alloc(&ws, split_bytes(oc, ic * k * k, 2), "conv.wsplit"));
-  if (conv_uses_shifted(ic, k, stride, pad)) MB_TRY(launch_conv_weight_planes(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic, k, 2, nullptr));
-  else MB_TRY(launch_split(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic * k * k, 2, nullptr));
+  MB_TRY(weight_plane_scale(wdv, static_cast<size_t>(oc) * ic * k * k, nullptr, &e.w_scale));
+  if (conv_uses_shifted(ic, k, stride, pad)) MB_TRY(launch_conv_weight_planes(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic, k, 2, nullptr, e.w_scale));
+  else MB_TRY(launch_split(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic * k * k, 2, nullptr, e.w_scale));
   e.w_split = static_cast<const __nv_bfloat16*>(ws);
   MB_TRY(t.alloc(&e.ws, conv_ws_bytes(batch, ic, h, wd, k, stride, pad, e.precision), "conv.ws"));
   MB_TRY(conv_exec(e, nullptr));

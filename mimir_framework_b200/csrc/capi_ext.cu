@@ -30,11 +30,11 @@ int cross_attention_exec(const CrossAttentionExec& e, cudaStream_t st) {
   MB_TRY(launch_split(e.q_in, qs, qr, E, ap, st));
   MB_TRY(launch_split(e.kv_in, ks, kr, E, ap, st));
   GemmArgs g;
-  g.a = qs; g.w = e.wq_split; g.a_planes = ap; g.w_planes = wp;
+  g.a = qs; g.w = e.wq_split; g.a_planes = ap; g.w_planes = wp; g.w_scale = e.w_scale;
   g.m = qr; g.n = E; g.k = E; g.out_f32 = q; g.ldo = E;
   MB_TRY(launch_gemm(g, st));
   GemmArgs h;
-  h.a = ks; h.w = e.wkv_split; h.a_planes = ap; h.w_planes = wp;
+  h.a = ks; h.w = e.wkv_split; h.a_planes = ap; h.w_planes = wp; h.w_scale = e.w_scale;
   h.m = kr; h.n = 2 * E; h.k = E; h.out_f32 = kv; h.ldo = 2 * E;
   MB_TRY(launch_gemm(h, st));
   AttnView v;
@@ -44,7 +44,7 @@ int cross_attention_exec(const CrossAttentionExec& e, cudaStream_t st) {
   MB_TRY(launch_attention_core_view(v, att, e.batch, E, e.heads, e.causal, st));
   MB_TRY(launch_split(att, qs, qr, E, ap, st));  // the query planes are dead by now
   GemmArgs o;
-  o.a = qs; o.w = e.wout_split; o.a_planes = ap; o.w_planes = wp;
+  o.a = qs; o.w = e.wout_split; o.a_planes = ap; o.w_planes = wp; o.w_scale = e.w_scale;
   o.m = qr; o.n = E; o.k = E; o.out_f32 = e.y; o.ldo = E; o.residual = e.residual;
   return launch_gemm(o, st);
 }
@@ -74,9 +74,10 @@ int mimir_b200_cross_attention(const float* query, const float* key_value, const
   MB_TRY(t.alloc(&wq, split_bytes(embed, embed, 2), "xattn.wq"));
   MB_TRY(t.alloc(&wkv, split_bytes(2 * embed, embed, 2), "xattn.wkv"));
   MB_TRY(t.alloc(&wo, split_bytes(embed, embed, 2), "xattn.wout"));
-  MB_TRY(launch_split_transposed(dw, static_cast<__nv_bfloat16*>(wq), embed, embed, 2, nullptr));
-  MB_TRY(launch_split_transposed(dw + E * E, static_cast<__nv_bfloat16*>(wkv), embed, 2 * embed, 2, nullptr));
-  MB_TRY(launch_split_transposed(dw + 3 * E * E, static_cast<__nv_bfloat16*>(wo), embed, embed, 2, nullptr));
+  MB_TRY(weight_plane_scale(dw, 4 * E * E, nullptr, &e.w_scale));
+  MB_TRY(launch_split_transposed(dw, static_cast<__nv_bfloat16*>(wq), embed, embed, 2, nullptr, e.w_scale));
+  MB_TRY(launch_split_transposed(dw + E * E, static_cast<__nv_bfloat16*>(wkv), embed, 2 * embed, 2, nullptr, e.w_scale));
+  MB_TRY(launch_split_transposed(dw + 3 * E * E, static_cast<__nv_bfloat16*>(wo), embed, embed, 2, nullptr, e.w_scale));
   e.wq_split = static_cast<const __nv_bfloat16*>(wq);
   e.wkv_split = static_cast<const __nv_bfloat16*>(wkv);
   e.wout_split = static_cast<const __nv_bfloat16*>(wo);

@@ -39,8 +39,13 @@ int fail(int status, const char* fmt, ...);
 struct Guard {
   std::mutex mu;
   size_t limit = 0, current = 0, peak = 0;
-  bool request(size_t bytes);
+  bool blocked = false, frozen = false;       // MemoryGuard::blockAllocations / freezeAllocations (MemoryGuard.hpp:37-72)
+  size_t blocked_attempts = 0, frozen_attempts = 0;
+  // 0 = granted, 1 = over the limit, 2 = blocked, 3 = frozen (the order of the checks in MemoryGuard::requestAllocation)
+  int request_why(size_t bytes);
+  bool request(size_t bytes) { return request_why(bytes) == 0; }
   void release(size_t bytes);
+  void reset();                                // MemoryGuard::reset (MemoryGuard.hpp:181-186): usage and peak to zero
 };
 
 struct Context {
@@ -55,8 +60,41 @@ struct Context {
   // stream around every GEMM launch while enabled (read back by mimir_b200_profile_read).
   bool prof_gemm = false;
   std::vector<cudaEvent_t> prof_events;
+  MimirB200Stats stats{};
 };
+// One context per CUDA device, selected by the calling thread's current device (cudaGetDevice); slot 0 when no
+// device is reachable, so that the host-only verbs (the budget guard) work on a machine without a GPU.
+constexpr int MAX_DEVICES = 64;
 Context& ctx();
+Context& ctx_of(int device);
+
+// Function attributes (opt-in shared memory sizes) belong to a device: set them once per device, not once per process.
+struct PerDeviceOnce {
+  std::mutex mu;
+  uint64_t done = 0;
+  template <class F>
+  int run(F&& fn) {
+    const int dev = ctx().device;
+    std::lock_guard<std::mutex> lk(mu);
+    if (done & (1ull << dev)) return MIMIR_B200_OK;
+    const int s = fn();
+    if (s == MIMIR_B200_OK) done |= (1ull << dev);
+    return s;
+  }
+};
+
+// Makes `device` current on the calling thread for the lifetime of the object (model handles carry their device).
+struct DeviceScope {
+  int prev = -1;
+  explicit DeviceScope(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != device) cudaSetDevice(device); else prev = -1;
+  }
+  ~DeviceScope() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+// The device a model handle lives on (the calling thread's current device for a null handle); graph.cu.
+int model_device(MimirB200ModelHandle m);
 
 // Budgeted device allocation: every cudaMalloc of the backend goes through these.
 int dev_alloc(void** p, size_t bytes, const char* tag);
@@ -71,15 +109,22 @@ inline void count_launch(int n = 1) { ctx().launches.fetch_add(static_cast<uint6
 // Split planes: bf16 [planes][rows][kp] with kp = round_up(k, 64), zero padded.
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 inline int64_t plane_elems(int64_t rows, int k) { return rows * static_cast<int64_t>(round_up(k, 64)); }
-// fp32 [rows, k] -> planes (hi, and lo when planes == 2)
-int launch_split(const float* src, __nv_bfloat16* dst, int64_t rows, int k, int planes, cudaStream_t st);
-// fp32 [k, n] (row-major, "input-major") -> planes of its transpose [n, kp]
-int launch_split_transposed(const float* src, __nv_bfloat16* dst, int k, int n, int planes, cudaStream_t st);
+// The planes are 16-bit containers declared as __nv_bfloat16 throughout; what the 16 bits hold (bfloat16 or IEEE
+// half) is a process-wide choice, see planes.cuh.  MIMIR_B200_PLANES=bf16 selects bfloat16 planes; half is the default.
+int plane_format();
+// Power of two that the weights of one layer are multiplied by before they become half planes (1 for bfloat16
+// planes): brings the largest magnitude near 2^14 so that small weights keep their bits.  Synchronises `st`.
+int weight_plane_scale(const float* w_dev, size_t n, cudaStream_t st, float* scale);
+// fp32 [rows, k] -> planes (hi, and lo when planes == 2) of src * scale
+int launch_split(const float* src, __nv_bfloat16* dst, int64_t rows, int k, int planes, cudaStream_t st, float scale = 1.0f);
+// fp32 [k, n] (row-major, "input-major") -> planes of its transpose [n, kp], times scale
+int launch_split_transposed(const float* src, __nv_bfloat16* dst, int k, int n, int planes, cudaStream_t st, float scale = 1.0f);
 
 struct GemmArgs {
   const __nv_bfloat16* a = nullptr;  // [a_planes][m][kp]
   const __nv_bfloat16* w = nullptr;  // [w_planes][n][kp]
   int a_planes = 2, w_planes = 2;
+  float w_scale = 1.0f;              // the weight planes hold w * w_scale (weight_plane_scale); divided out in the epilogue
   int m = 0, n = 0, k = 0;           // logical sizes; kp = round_up(k, 64)
   const float* bias = nullptr;       // [n] or null
   const float* residual = nullptr;   // fp32 [m, n] added after the activation, or null
@@ -125,6 +170,11 @@ int launch_layernorm(const float* x, const float* gamma, const float* beta, floa
 int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y, int batch, int64_t n, float eps,
                    cudaStream_t st, __nv_bfloat16* y_split = nullptr, int planes = 0, int64_t plane_stride = 0);
 bool rmsnorm_onepass_ok(int batch, int64_t n);
+// The chunked norm / softmax paths keep partial results in a scratch buffer per (device, stream), allocated at first use.
+// A stream that is about to be captured into a CUDA graph must have its buffer beforehand (no allocation while
+// capturing) and keeps it, at a fixed address, until norm_scratch_release: call on the stream's device.
+int norm_scratch_reserve(cudaStream_t st);
+void norm_scratch_release(cudaStream_t st);
 int launch_groupnorm(const float* x, const float* gamma, const float* beta, float* y, int batch, int ch, int hw,
                      int groups, float eps, int act, const float* residual, cudaStream_t st);
 int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softmax, cudaStream_t st);
@@ -181,7 +231,7 @@ struct PreNorm {
 int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int batch, int c, int h, int w, int pad, int planes,
                                      cudaStream_t st, const PreNorm& pre = PreNorm());
 // OIHW fp32 -> planes [planes][oc][round_up(ks*ks*ic, 64)] with K ordered (kh, kw, ic)
-int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st);
+int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st, float scale = 1.0f);
 
 // spatial.cu -----------------------------------------------------------------------------------
 int launch_depthwise_conv2d(const float* x, const float* w, const float* bias, float* y, int batch, int ch, int h, int wd, int k,

@@ -5,13 +5,14 @@
 // bf16 hi/lo planes the GEMM consumes (one pass over the input, no fp32 column matrix), the OIHW
 // weight block already is the K-major [oc][ic*k*k] operand, and the GEMM epilogue writes NCHW.
 #include "common.h"
+#include "planes.cuh"
 
 namespace mb {
 namespace {
 
 // One thread produces 8 consecutive K entries of one output pixel.
 __global__ void im2col_split_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst, long long rows, int ic, int h,
-                                    int w, int ks, int stride, int pad, int oh, int ow, int k, int kp, int planes) {
+                                    int w, int ks, int stride, int pad, int oh, int ow, int k, int kp, int planes, int f16) {
   const int chunks = kp >> 3;
   const long long total = rows * chunks;
   const long long plane_stride = rows * static_cast<long long>(kp);
@@ -26,8 +27,8 @@ __global__ void im2col_split_kernel(const float* __restrict__ x, __nv_bfloat16* 
     const int pix = static_cast<int>(r - smp * ohw);
     const int oy = pix / ow, ox = pix - oy * ow;
     const float* xs = x + smp * ic * h * w;
-    __align__(16) __nv_bfloat16 hi[8];
-    __align__(16) __nv_bfloat16 lo[8];
+    __align__(16) uint16_t hi[8];
+    __align__(16) uint16_t lo[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int kidx = c * 8 + j;
@@ -38,8 +39,7 @@ __global__ void im2col_split_kernel(const float* __restrict__ x, __nv_bfloat16* 
         const int iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
         if (iy >= 0 && iy < h && ix >= 0 && ix < w) v = __ldg(xs + (static_cast<long long>(ci) * h + iy) * w + ix);
       }
-      hi[j] = __float2bfloat16_rn(v);
-      lo[j] = __float2bfloat16_rn(v - __bfloat162float(hi[j]));
+      split_one(v, f16, hi[j], lo[j]);
     }
     __nv_bfloat16* d = dst + r * kp + c * 8;
     *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(hi);
@@ -59,7 +59,7 @@ int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, i
   long long blocks = (total + 255) / 256;
   const long long cap = static_cast<long long>(ctx().sm_count) * 32;
   if (blocks > cap) blocks = cap;
-  im2col_split_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(x, dst, rows, ic, h, w, ks, stride, pad, oh, ow, k, kp, planes);
+  im2col_split_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(x, dst, rows, ic, h, w, ks, stride, pad, oh, ow, k, kp, planes, plane_format() == PLANES_F16);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
@@ -83,7 +83,7 @@ constexpr int TP_C = 64, TP_X = 64;
 
 __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
                                                                   int c, int h, int w, int pad, int planes, long long plane_stride,
-                                                                  const PreNorm pre) {
+                                                                  const PreNorm pre, int f16) {
   __shared__ float tile[TP_C][TP_X + 1];
   const int hp = h + 2 * pad, wp = w + 2 * pad;
   const int cb = blockIdx.x * TP_C;
@@ -148,13 +148,11 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* _
         const int xp = x0 + xx;
         if (xp < wp) {
           const float a = tile[2 * lane][xx], b = tile[2 * lane + 1][xx];
-          const __nv_bfloat162 hi = __floats2bfloat162_rn(a, b);
+          uint32_t hi, lo;
+          split_pair(a, b, f16, hi, lo);
           const long long o = ((static_cast<long long>(n) * hp + yp) * wp + xp) * c + c0;
-          *reinterpret_cast<__nv_bfloat162*>(dst + o) = hi;
-          if (planes == 2) {
-            const float2 hf = __bfloat1622float2(hi);
-            *reinterpret_cast<__nv_bfloat162*>(dst + o + plane_stride) = __floats2bfloat162_rn(a - hf.x, b - hf.y);
-          }
+          *reinterpret_cast<uint32_t*>(dst + o) = hi;
+          if (planes == 2) *reinterpret_cast<uint32_t*>(dst + o + plane_stride) = lo;
         }
       }
     }
@@ -164,7 +162,7 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* _
 
 // dst[pl][o][(kh*ks + kw)*ic + i] = split(w[o][i][kh][kw]); the padded tail of K is zero
 __global__ void conv_weight_planes_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ dst, int oc, int ic, int ks,
-                                          int kp, int planes) {
+                                          int kp, int planes, int f16, float scale) {
   const int k = ks * ks * ic;
   const long long total = static_cast<long long>(oc) * kp;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
@@ -175,9 +173,11 @@ __global__ void conv_weight_planes_kernel(const float* __restrict__ w, __nv_bflo
       const int t = kk / ic, ci = kk - t * ic;
       v = __ldg(w + (static_cast<long long>(o) * ic + ci) * ks * ks + t);
     }
-    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-    dst[i] = hi;
-    if (planes == 2) dst[i + total] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    uint16_t hi, lo;
+    split_one(v * scale, f16, hi, lo);
+    uint16_t* d16 = reinterpret_cast<uint16_t*>(dst);
+    d16[i] = hi;
+    if (planes == 2) d16[i + total] = lo;
   }
 }
 
@@ -190,18 +190,18 @@ int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int bat
   if (hp > 65535 || batch > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: image too tall for the layout kernel");
   dim3 grid((c + TP_C - 1) / TP_C, hp, batch);
   if (pre.stats != nullptr && (pre.groups <= 0 || c % pre.groups != 0)) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad fused GroupNorm");
-  nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, static_cast<long long>(batch) * hp * wp * c, pre);
+  nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, static_cast<long long>(batch) * hp * wp * c, pre, plane_format() == PLANES_F16);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
 }
 
-int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st) {
+int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st, float scale) {
   const int kp = round_up(ks * ks * ic, 64);
   const long long total = static_cast<long long>(oc) * kp;
   long long blocks = (total + 255) / 256;
   if (blocks > ctx().sm_count * 16) blocks = ctx().sm_count * 16;
-  conv_weight_planes_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(w, dst, oc, ic, ks, kp, planes);
+  conv_weight_planes_kernel<<<static_cast<int>(blocks), 256, 0, st>>>(w, dst, oc, ic, ks, kp, planes, plane_format() == PLANES_F16, scale);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;

@@ -19,7 +19,11 @@
 //                                 (or channel-major NCHW for convs)
 // Every mbarrier wait is bounded: after ~2 s it sets the device error word and the CTA drains.
 #include "common.h"
+#include "planes.cuh"
 #include "sm100_ptx.cuh"
+
+#include <cmath>
+#include <cstring>
 
 namespace mb {
 
@@ -32,6 +36,7 @@ constexpr int NUM_ACC = 2;     // TMEM accumulator buffers
 constexpr int TMEM_COLS = 512;
 constexpr int NUM_THREADS = 320;  // 10 warps: TMA, MMA, 8 epilogue
 constexpr int EPI_WARPS = 8;
+constexpr float ACC_TRUNC_PER_MMA = 1.5e-8f;  // mean relative loss of the fp32 accumulator per tcgen05.mma (truncating adds)
 
 // GELU in the reference's tanh form (LayerOps.hpp:556-568); the constant is
 // sqrt(2.0f / 3.14159265359f) evaluated in fp32.
@@ -72,6 +77,11 @@ struct GemmParams {
   // tile) pays for 256 columns it does not have; swapped, every instruction does full work.
   int swap;
   int tma_store;  // fp32 row-major output leaves through TMA stores (map_o) instead of per-lane stores
+  // Every accumulator is multiplied by this before bias / activation: 1 + ACC_TRUNC_PER_MMA * (MMAs per output).
+  // The tensor core adds each MMA's products to the fp32 accumulator with truncation, not round-to-nearest, which
+  // shrinks every result by a little less than 2^-26 of its value per instruction (see launch_gemm_t).
+  float acc_scale;
+  int f16;        // operand planes (and out_split) hold IEEE half instead of bfloat16
   int* err_word;
 };
 
@@ -190,7 +200,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
+      const uint32_t idesc = make_idesc(BM, BN, p.f16);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -267,7 +277,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           float v[32];
           tmem_ld_32x32(taddr0 + c0, v);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) tbuf[j * 33 + lane] = v[j];  // [pixel][channel]
+          for (int j = 0; j < 32; ++j) tbuf[j * 33 + lane] = v[j] * p.acc_scale;  // [pixel][channel]
           __syncwarp();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = tbuf[lane * 33 + j];  // lane = pixel r0 + lane, j = channel oc0 + j
@@ -339,6 +349,8 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         if (col0 >= col_limit) break;  // warp-uniform
         float v[32];
         tmem_ld_32x32(taddr0 + c0, v);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] *= p.acc_scale;
         const bool full_cols = (col0 + 32 <= p.n);
         // bias: the same 32 values for every lane (broadcast loads)
         if (p.bias != nullptr) {
@@ -423,11 +435,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
               for (int j = 0; j < 32; j += 2) {
                 const float x0 = (full_cols || col0 + j < p.n) ? v[j] : 0.0f;
                 const float x1 = (full_cols || col0 + j + 1 < p.n) ? v[j + 1] : 0.0f;
-                const __nv_bfloat162 h2 = __floats2bfloat162_rn(x0, x1);
-                const float2 hf = __bfloat1622float2(h2);
-                const __nv_bfloat162 l2 = __floats2bfloat162_rn(x0 - hf.x, x1 - hf.y);
-                hi[j >> 1] = *reinterpret_cast<const uint32_t*>(&h2);
-                lo[j >> 1] = *reinterpret_cast<const uint32_t*>(&l2);
+                split_pair(x0, x1, p.f16, hi[j >> 1], lo[j >> 1]);
               }
               __nv_bfloat16* oh = p.out_split + static_cast<long long>(row) * p.np + col0;
               __nv_bfloat16* ol = oh + static_cast<long long>(p.m) * p.np;
@@ -478,14 +486,9 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // ------------------------------------------------------------------------------------------
 namespace {
 
-__device__ __forceinline__ void split1(float x, __nv_bfloat16& h, __nv_bfloat16& l) {
-  h = __float2bfloat16_rn(x);
-  l = __float2bfloat16_rn(x - __bfloat162float(h));
-}
-
 // One thread per 8 consecutive K elements of one row; the padded tail kp > k is written as zero.
 __global__ void split_rows_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long rows, int k,
-                                  int kp, int planes) {
+                                  int kp, int planes, int f16, float scale) {
   const int chunks = kp >> 3;
   const long long total = rows * chunks;
   const long long plane_stride = rows * static_cast<long long>(kp);
@@ -504,19 +507,18 @@ __global__ void split_rows_kernel(const float* __restrict__ src, __nv_bfloat16* 
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[j] = (c + j < k) ? __ldg(s + j) : 0.0f;
     }
-    __align__(16) __nv_bfloat16 h[8];
-    __align__(16) __nv_bfloat16 l[8];
+    uint32_t h[4], l[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) split1(v[j], h[j], l[j]);
+    for (int j = 0; j < 8; j += 2) split_pair(v[j] * scale, v[j + 1] * scale, f16, h[j >> 1], l[j >> 1]);
     __nv_bfloat16* d = dst + r * kp + c;
-    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(h);
-    if (planes == 2) *reinterpret_cast<uint4*>(d + plane_stride) = *reinterpret_cast<const uint4*>(l);
+    *reinterpret_cast<uint4*>(d) = make_uint4(h[0], h[1], h[2], h[3]);
+    if (planes == 2) *reinterpret_cast<uint4*>(d + plane_stride) = make_uint4(l[0], l[1], l[2], l[3]);
   }
 }
 
 // src fp32 [k, n] row-major -> planes of the transpose [n, kp].  32x32 tiles through shared memory.
 __global__ void split_transposed_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int k, int n,
-                                        int kp, int planes) {
+                                        int kp, int planes, int f16, float scale) {
   __shared__ float tile[32][33];
   const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -528,10 +530,11 @@ __global__ void split_transposed_kernel(const float* __restrict__ src, __nv_bflo
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
     const int nn = n0 + i, kk = k0 + threadIdx.x;
     if (nn < n && kk < kp) {
-      __nv_bfloat16 h, l;
-      split1(tile[threadIdx.x][i], h, l);
-      dst[static_cast<long long>(nn) * kp + kk] = h;
-      if (planes == 2) dst[plane_stride + static_cast<long long>(nn) * kp + kk] = l;
+      uint16_t h, l;
+      split_one(tile[threadIdx.x][i] * scale, f16, h, l);
+      uint16_t* d16 = reinterpret_cast<uint16_t*>(dst);
+      d16[static_cast<long long>(nn) * kp + kk] = h;
+      if (planes == 2) d16[plane_stride + static_cast<long long>(nn) * kp + kk] = l;
     }
   }
 }
@@ -641,15 +644,27 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.np = round_up(g.n, 64);
   p.ohw = g.out_nchw_hw;
   p.err_word = ctx().dev_error_word;
+  {
+    // Measured on B200 against fp64 products of the same operand planes (random normal operands, K = 256 ... 4096,
+    // two and three MMAs per 16-wide K step): the accumulated result is low by 1.47e-8 ... 1.58e-8 of its value per
+    // MMA instruction that added into it; all-positive operands lose 2.1e-8 ... 3.6e-8.  Zero-padded K adds exact
+    // zeros and loses nothing, so only the real K counts.  Undoing the mean loss halves the accumulation error.
+    const long long ksteps = conv ? static_cast<long long>(g.conv_ks) * g.conv_ks * ((g.conv_c + UMMA_K - 1) / UMMA_K)
+                                  : (g.k + UMMA_K - 1) / UMMA_K;
+    const int products = 1 + (g.a_planes == 2 ? 1 : 0) + (g.w_planes == 2 ? 1 : 0);
+    static const bool comp = [] { const char* e = getenv("MIMIR_B200_ACC_COMP"); return !(e && e[0] == '0'); }();
+    p.acc_scale = (comp ? 1.0f + ACC_TRUNC_PER_MMA * static_cast<float>(ksteps * products) : 1.0f) / g.w_scale;
+  }
+  p.f16 = plane_format() == PLANES_F16 ? 1 : 0;
   constexpr int STAGE_BYTES = 2 * BM * BK * 2 + 2 * BN * BK * 2;
   constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_WARPS * 32 * 33 * 4 /*swapped-epilogue tiles*/;
   static_assert(SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   auto kern = gemm_tn_bf16split_kernel<BK, STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static PerDeviceOnce attr_once;
+  MB_TRY(attr_once.run([&]() -> int {
     MB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    attr_set = true;
-  }
+    return MIMIR_B200_OK;
+  }));
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -671,7 +686,56 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
 
 }  // namespace
 
-int launch_split(const float* src, __nv_bfloat16* dst, int64_t rows, int k, int planes, cudaStream_t st) {
+int plane_format() {
+  static const int fmt = [] {
+    const char* e = getenv("MIMIR_B200_PLANES");
+    return (e && (e[0] == 'b' || e[0] == 'B')) ? PLANES_BF16 : PLANES_F16;
+  }();
+  return fmt;
+}
+
+namespace {
+// largest finite |w| as its bit pattern (non-negative floats order like unsigned integers)
+__global__ void absmax_kernel(const float* __restrict__ w, size_t n, unsigned* __restrict__ out) {
+  unsigned m = 0;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const unsigned u = __float_as_uint(__ldg(w + i)) & 0x7fffffffu;
+    if (u < 0x7f800000u && u > m) m = u;
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
+  if ((threadIdx.x & 31) == 0 && m != 0) atomicMax(out, m);
+}
+}  // namespace
+
+int weight_plane_scale(const float* w_dev, size_t n, cudaStream_t st, float* scale) {
+  *scale = 1.0f;
+  if (plane_format() != PLANES_F16 || n == 0 || w_dev == nullptr) return MIMIR_B200_OK;
+  static std::mutex mu;  // one spare device word is shared by every caller
+  std::lock_guard<std::mutex> lk(mu);
+  unsigned* word = reinterpret_cast<unsigned*>(ctx().dev_error_word) + 8;  // a spare word of the 256-byte error block
+  MB_CUDA(cudaMemsetAsync(word, 0, sizeof(unsigned), st));
+  const size_t want = (n + 255) / 256;
+  const int blocks = static_cast<int>(want < static_cast<size_t>(ctx().sm_count) * 8 ? want : static_cast<size_t>(ctx().sm_count) * 8);
+  absmax_kernel<<<blocks, 256, 0, st>>>(w_dev, n, word);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  unsigned bits = 0;
+  MB_CUDA(cudaMemcpyAsync(&bits, word, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+  MB_CUDA(cudaStreamSynchronize(st));
+  float amax;
+  memcpy(&amax, &bits, sizeof(float));
+  if (!(amax > 0.0f)) return MIMIR_B200_OK;
+  int e = 0;
+  frexpf(amax, &e);            // amax = f * 2^e with f in [0.5, 1)
+  int s = 14 - e;              // amax * 2^s in [2^13, 2^14)
+  if (s > 60) s = 60;
+  if (s < -60) s = -60;
+  *scale = ldexpf(1.0f, s);
+  return MIMIR_B200_OK;
+}
+
+int launch_split(const float* src, __nv_bfloat16* dst, int64_t rows, int k, int planes, cudaStream_t st, float scale) {
   if (rows <= 0 || k <= 0) return MIMIR_B200_OK;
   const int kp = round_up(k, 64);
   const long long total = rows * (kp >> 3);
@@ -679,17 +743,17 @@ int launch_split(const float* src, __nv_bfloat16* dst, int64_t rows, int k, int 
   long long blocks = (total + threads - 1) / threads;
   const long long cap = static_cast<long long>(ctx().sm_count) * 16;
   if (blocks > cap) blocks = cap;
-  split_rows_kernel<<<static_cast<int>(blocks), threads, 0, st>>>(src, dst, rows, k, kp, planes);
+  split_rows_kernel<<<static_cast<int>(blocks), threads, 0, st>>>(src, dst, rows, k, kp, planes, plane_format() == PLANES_F16, scale);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
 }
 
-int launch_split_transposed(const float* src, __nv_bfloat16* dst, int k, int n, int planes, cudaStream_t st) {
+int launch_split_transposed(const float* src, __nv_bfloat16* dst, int k, int n, int planes, cudaStream_t st, float scale) {
   if (n <= 0 || k <= 0) return MIMIR_B200_OK;
   const int kp = round_up(k, 64);
   dim3 grid((n + 31) / 32, kp / 32), block(32, 8);
-  split_transposed_kernel<<<grid, block, 0, st>>>(src, dst, k, n, kp, planes);
+  split_transposed_kernel<<<grid, block, 0, st>>>(src, dst, k, n, kp, planes, plane_format() == PLANES_F16, scale);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;

@@ -106,6 +106,7 @@ struct LayerRT {
   float* w_f32 = nullptr;
   size_t w_count = 0;
   __nv_bfloat16* w_split = nullptr;   // Linear / Conv2d operand, or Wqkv^T for attention
+  float w_scale = 1.0f;               // every plane set of the layer holds its weights times this power of two
   size_t w_split_bytes = 0;
   __nv_bfloat16* w_split2 = nullptr;  // Wout^T for attention
   size_t w_split2_bytes = 0;
@@ -213,6 +214,7 @@ struct MimirB200Model {
   std::vector<mb::TensorV> tensors;
   std::map<std::string, int> input_v;  // graph input name -> tensor version
   int precision = MIMIR_B200_PREC_BF16X2;
+  int device = 0;  // the CUDA device the model lives on: the creating thread's current device
   int planned_batch = 0;
   int out_v = -1;
   uint8_t* arena = nullptr;
@@ -258,7 +260,6 @@ namespace {
 
 std::mutex g_models_mu;
 std::set<MimirB200Model*> g_models;
-MimirB200Stats g_stats{};
 
 void drop_graphs(MimirB200Model* m) {
   for (auto& g : m->graphs)
@@ -292,7 +293,8 @@ int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
     L.w_split_bytes = split_bytes(L.out_f, L.in_f, wp);
     MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split), L.w_split_bytes, "linear.w_planes"));
     m->weight_bytes += L.w_split_bytes;
-    MB_TRY(launch_split(L.w_f32, L.w_split, L.out_f, L.in_f, wp, st));
+    MB_TRY(weight_plane_scale(L.w_f32, static_cast<size_t>(L.out_f) * L.in_f, st, &L.w_scale));
+    MB_TRY(launch_split(L.w_f32, L.w_split, L.out_f, L.in_f, wp, st, L.w_scale));
     L.w_split_k = L.in_f;
   } else if (L.lt == LT::Conv2d) {
     const int k = L.d.in_channels * L.d.kernel * L.d.kernel;
@@ -300,10 +302,11 @@ int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
     L.w_split_bytes = split_bytes(L.d.out_channels, k, wp);
     MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split), L.w_split_bytes, "conv.w_planes"));
     m->weight_bytes += L.w_split_bytes;
+    MB_TRY(weight_plane_scale(L.w_f32, static_cast<size_t>(L.d.out_channels) * k, st, &L.w_scale));
     if (conv_uses_shifted(L.d.in_channels, L.d.kernel, L.d.stride, L.d.padding))
-      MB_TRY(launch_conv_weight_planes(L.w_f32, L.w_split, L.d.out_channels, L.d.in_channels, L.d.kernel, wp, st));
+      MB_TRY(launch_conv_weight_planes(L.w_f32, L.w_split, L.d.out_channels, L.d.in_channels, L.d.kernel, wp, st, L.w_scale));
     else
-      MB_TRY(launch_split(L.w_f32, L.w_split, L.d.out_channels, k, wp, st));
+      MB_TRY(launch_split(L.w_f32, L.w_split, L.d.out_channels, k, wp, st, L.w_scale));
     L.w_split_k = k;
   } else if (L.lt == LT::Attention) {
     const int E = L.embed;
@@ -316,8 +319,9 @@ int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
     m->weight_bytes += L.w_split_bytes;
     MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split2), L.w_split2_bytes, "attn.wout_planes"));
     m->weight_bytes += L.w_split2_bytes;
-    MB_TRY(launch_split_transposed(L.w_f32, L.w_split, E, 3 * E, wp, st));
-    MB_TRY(launch_split_transposed(L.w_f32 + static_cast<size_t>(3) * E * E, L.w_split2, E, E, wp, st));
+    MB_TRY(weight_plane_scale(L.w_f32, static_cast<size_t>(4) * E * E, st, &L.w_scale));
+    MB_TRY(launch_split_transposed(L.w_f32, L.w_split, E, 3 * E, wp, st, L.w_scale));
+    MB_TRY(launch_split_transposed(L.w_f32 + static_cast<size_t>(3) * E * E, L.w_split2, E, E, wp, st, L.w_scale));
     L.w_split_k = E;
   } else if (L.lt == LT::CrossAttention) {
     // block = Wq[E][E] | Wkv[E][2E] | Wout[E][E], input-major (Model.cpp:5975-5982)
@@ -336,9 +340,10 @@ int prepare_weight_planes(MimirB200Model* m, LayerRT& L, cudaStream_t st) {
     MB_TRY(dev_alloc(reinterpret_cast<void**>(&L.w_split3), L.w_split3_bytes, "xattn.wout_planes"));
     m->weight_bytes += L.w_split3_bytes;
     const size_t EE = static_cast<size_t>(E) * E;
-    MB_TRY(launch_split_transposed(L.w_f32, L.w_split, E, E, wp, st));
-    MB_TRY(launch_split_transposed(L.w_f32 + EE, L.w_split2, E, 2 * E, wp, st));
-    MB_TRY(launch_split_transposed(L.w_f32 + 3 * EE, L.w_split3, E, E, wp, st));
+    MB_TRY(weight_plane_scale(L.w_f32, 4 * EE, st, &L.w_scale));
+    MB_TRY(launch_split_transposed(L.w_f32, L.w_split, E, E, wp, st, L.w_scale));
+    MB_TRY(launch_split_transposed(L.w_f32 + EE, L.w_split2, E, 2 * E, wp, st, L.w_scale));
+    MB_TRY(launch_split_transposed(L.w_f32 + 3 * EE, L.w_split3, E, E, wp, st, L.w_scale));
     L.w_split_k = E;
   }
   return MIMIR_B200_OK;
@@ -1009,7 +1014,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
   m->planned_micro = batch;
   for (auto& L : m->layers) MB_TRY(prepare_weight_planes(m, L, nullptr));
   MB_CUDA(cudaStreamSynchronize(nullptr));
-  g_stats.arena_peak_bytes = need * (m->pipeline > 1 ? 2 : 1);
+  ctx().stats.arena_peak_bytes = need * (m->pipeline > 1 ? 2 : 1);
   return MIMIR_B200_OK;
 }
 
@@ -1040,6 +1045,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         if (L.read_split) e.x_split = splitp(L.in_v[0]); else e.x_f32 = f32p(L.in_v[0]);
         e.w_f32 = L.w_f32;
         e.w_split = L.w_split;
+        e.w_scale = L.w_scale;
         e.bias = d.use_bias ? L.w_f32 + static_cast<size_t>(L.in_f) * L.out_f : nullptr;
         e.activation = L.fused_act;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
@@ -1054,7 +1060,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.batch = batch; e.seq = L.seq; e.embed = L.embed; e.heads = L.heads; e.causal = d.causal;
         e.precision = m->precision;
         if (L.read_split) e.x_split = splitp(L.in_v[0]); else e.x = f32p(L.in_v[0]);
-        e.wqkv_split = L.w_split; e.wout_split = L.w_split2; e.y = f32p(L.out_v); e.ws = ws;
+        e.wqkv_split = L.w_split; e.wout_split = L.w_split2; e.w_scale = L.w_scale; e.y = f32p(L.out_v); e.ws = ws;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
         if (m->is_twin) {
           e.kcache = L.kcache; e.vcache = L.vcache; e.max_seq = m->max_seq; e.decode_pos = m->decode_pos;
@@ -1079,7 +1085,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.batch = batch; e.ic = d.in_channels; e.oc = d.out_channels; e.h = L.h; e.w = L.w; e.ks = d.kernel;
         e.stride = d.stride; e.pad = d.padding; e.precision = m->precision;
         e.activation = d.activation ? MIMIR_B200_ELT_RELU : L.fused_act;
-        e.x = f32p(L.in_v[0]); e.w_split = L.w_split; e.y = f32p(L.out_v); e.ws = ws;
+        e.x = f32p(L.in_v[0]); e.w_split = L.w_split; e.w_scale = L.w_scale; e.y = f32p(L.out_v); e.ws = ws;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
         if (L.pre_norm >= 0) {
           const LayerRT& G = m->layers[L.pre_norm];
@@ -1157,7 +1163,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.batch = batch; e.q_len = L.seq; e.kv_len = L.kv_len; e.embed = L.embed; e.heads = L.heads; e.causal = d.causal;
         e.precision = m->precision;
         e.q_in = f32p(L.in_v[0]); e.kv_in = f32p(L.in_v[1]);
-        e.wq_split = L.w_split; e.wkv_split = L.w_split2; e.wout_split = L.w_split3;
+        e.wq_split = L.w_split; e.wkv_split = L.w_split2; e.wout_split = L.w_split3; e.w_scale = L.w_scale;
         e.y = f32p(L.out_v); e.ws = ws;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
         s = cross_attention_exec(e, st);
@@ -1274,7 +1280,10 @@ int run_layers_cached(MimirB200Model* m, int batch, const Bound& bnd, cudaStream
     return MIMIR_B200_OK;
   }
   if (g->unusable || g->seen++ == 0) return run_layers(m, batch, bnd, st, arena);
-  if (!m->s_capture) MB_CUDA(cudaStreamCreateWithFlags(&m->s_capture, cudaStreamNonBlocking));
+  if (!m->s_capture) {
+    MB_CUDA(cudaStreamCreateWithFlags(&m->s_capture, cudaStreamNonBlocking));
+    MB_TRY(norm_scratch_reserve(m->s_capture));
+  }
   const uint64_t before = ctx().launches.load();
   if (cudaStreamBeginCapture(m->s_capture, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
     cudaGetLastError();
@@ -1329,6 +1338,10 @@ int check_inputs(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs,
 }  // namespace
 }  // namespace mb
 
+namespace mb {
+int model_device(MimirB200ModelHandle m) { return m ? m->device : ctx().device; }
+}  // namespace mb
+
 extern "C" {
 
 using namespace mb;
@@ -1337,6 +1350,7 @@ int mimir_b200_model_create(const MimirLayerDesc* layers, int n_layers, MimirB20
   if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
   if (!layers || n_layers <= 0 || !out) return fail(MIMIR_B200_E_INVALID, "model_create: no layers defined");
   auto m = std::make_unique<MimirB200Model>();
+  m->device = ctx().device;
   m->layers.resize(static_cast<size_t>(n_layers));
   for (int i = 0; i < n_layers; ++i) {
     const MimirLayerDesc& d = layers[i];
@@ -1383,7 +1397,10 @@ static void destroy_model(MimirB200Model* m) {
   m->pos_dev = nullptr;
   m->decode_scratch = m->skinny_scratch = nullptr;
   drop_graphs(m);
-  if (m->s_capture) cudaStreamDestroy(m->s_capture);
+  if (m->s_capture) {
+    norm_scratch_release(m->s_capture);
+    cudaStreamDestroy(m->s_capture);
+  }
   for (auto& L : m->layers) free_layer_weights(L, m);
   if (m->arena) dev_free(m->arena, m->arena_bytes);
   if (m->arena2) dev_free(m->arena2, m->arena_bytes);
@@ -1399,6 +1416,7 @@ static void destroy_model(MimirB200Model* m) {
 }
 
 int mimir_b200_model_destroy(MimirB200ModelHandle m) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return MIMIR_B200_OK;
   {
     std::lock_guard<std::mutex> lk(g_models_mu);
@@ -1410,6 +1428,7 @@ int mimir_b200_model_destroy(MimirB200ModelHandle m) {
 }
 
 int mimir_b200_model_set_precision(MimirB200ModelHandle m, int precision) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (precision < MIMIR_B200_PREC_BF16X2 || precision > MIMIR_B200_PREC_BF16) return fail(MIMIR_B200_E_INVALID, "unknown precision %d", precision);
   if (precision != m->precision) {
@@ -1427,6 +1446,7 @@ int mimir_b200_model_set_precision(MimirB200ModelHandle m, int precision) {
 }
 
 int mimir_b200_model_weights_device(MimirB200ModelHandle m, int layer_index, uint64_t n, float** dev) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (layer_index < 0 || layer_index >= static_cast<int>(m->layers.size())) return fail(MIMIR_B200_E_INVALID, "upload_weights: layer index out of range");
   LayerRT& L = m->layers[static_cast<size_t>(layer_index)];
@@ -1446,6 +1466,7 @@ int mimir_b200_model_weights_device(MimirB200ModelHandle m, int layer_index, uin
 }
 
 int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, const float* host, uint64_t n) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (n != 0 && !host) return fail(MIMIR_B200_E_INVALID, "upload_weights: null host pointer");
   float* dev = nullptr;
   MB_TRY(mimir_b200_model_weights_device(m, layer_index, n, &dev));
@@ -1454,6 +1475,7 @@ int mimir_b200_model_upload_weights(MimirB200ModelHandle m, int layer_index, con
 }
 
 int mimir_b200_model_layer_info(MimirB200ModelHandle m, int layer_index, const char** name, uint64_t* params_count) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (layer_index < 0 || layer_index >= static_cast<int>(m->layers.size())) return fail(MIMIR_B200_E_INVALID, "layer index out of range");
   const LayerRT& L = m->layers[static_cast<size_t>(layer_index)];
@@ -1462,23 +1484,49 @@ int mimir_b200_model_layer_info(MimirB200ModelHandle m, int layer_index, const c
   return MIMIR_B200_OK;
 }
 
+int mimir_b200_model_tensor_slot(MimirB200ModelHandle m, const char* input_name, uint64_t* offset, uint64_t* bytes) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
+  if (!m || !offset || !bytes) return fail(MIMIR_B200_E_INVALID, "tensor_slot: null argument");
+  if (m->planned_batch <= 0) return fail(MIMIR_B200_E_INVALID, "tensor_slot: plan the model first");
+  int v = m->out_v;
+  if (input_name) {
+    auto it = m->input_v.find(input_name);
+    if (it == m->input_v.end()) return fail(MIMIR_B200_E_INVALID, "tensor_slot: '%s' is not a graph input", input_name);
+    v = it->second;
+  }
+  const TensorV& t = m->tensors[root_of(m->tensors, v)];
+  *offset = t.off_f32;
+  *bytes = static_cast<uint64_t>(t.n) * (t.broadcast_input ? 1 : m->planned_micro) * 4;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_model_output_len(MimirB200ModelHandle m, uint64_t* per_sample) {
+  if (!m || !per_sample) return fail(MIMIR_B200_E_INVALID, "output_len: null argument");
+  if (m->planned_batch <= 0) return fail(MIMIR_B200_E_INVALID, "output_len: plan the model first");
+  *per_sample = static_cast<uint64_t>(m->tensors[root_of(m->tensors, m->out_v)].n);
+  return MIMIR_B200_OK;
+}
+
 int mimir_b200_model_num_layers(MimirB200ModelHandle m, int* n) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m || !n) return fail(MIMIR_B200_E_INVALID, "null model handle");
   *n = static_cast<int>(m->layers.size());
   return MIMIR_B200_OK;
 }
 
 int mimir_b200_model_plan(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, uint64_t* arena_peak_bytes) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (!inputs || n_inputs <= 0) return fail(MIMIR_B200_E_INVALID, "plan: no inputs declared");
   MB_TRY(plan_model(m, inputs, n_inputs, batch));
   if (arena_peak_bytes) *arena_peak_bytes = m->arena_bytes * (m->arena2 ? 2 : 1);
-  g_stats.weight_bytes = m->weight_bytes;
+  ctx().stats.weight_bytes = m->weight_bytes;
   return MIMIR_B200_OK;
 }
 
 int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, float* out_dev,
                                     uint64_t out_capacity, uint64_t* out_len, void* stream) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   std::vector<int> vs;
   MB_TRY(check_inputs(m, inputs, n_inputs, batch, &vs));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -1510,8 +1558,8 @@ int mimir_b200_model_forward_device(MimirB200ModelHandle m, const MimirNamedInpu
       MB_CUDA(cudaMemcpyAsync(out_c, src, static_cast<size_t>(ot.n) * micro * 4, cudaMemcpyDeviceToDevice, st));
     }
   }
-  g_stats.flops_last_forward = m->flops * m->pipeline;
-  g_stats.bytes_last_forward = m->hbm_bytes * m->pipeline;
+  ctx().stats.flops_last_forward = m->flops * m->pipeline;
+  ctx().stats.bytes_last_forward = m->hbm_bytes * m->pipeline;
   return MIMIR_B200_OK;
 }
 
@@ -1535,6 +1583,7 @@ static int ensure_pipeline_objects(MimirB200Model* m) {
 
 int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, float* out_host,
                              uint64_t out_capacity, uint64_t* out_len) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   std::vector<int> vs;
   MB_TRY(check_inputs(m, inputs, n_inputs, batch, &vs));
   const TensorV& ot = m->tensors[root_of(m->tensors, m->out_v)];
@@ -1552,7 +1601,12 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
   // micro-batch c + 2 only after its compute (inputs) and its copy-out (output) have finished
   for (int c = 0; c < P; ++c) {
     uint8_t* arena = bufs[c & 1];
-    if (c >= 2) MB_CUDA(cudaStreamWaitEvent(m->s_h2d, m->ev_comp[c - 2], 0));
+    if (c >= 2) {
+      // the planner may hand a graph input's slot to the output tensor once the input's last consumer has run,
+      // so the copy-in of micro-batch c must also wait for the copy-out of micro-batch c - 2 from the same buffer
+      MB_CUDA(cudaStreamWaitEvent(m->s_h2d, m->ev_comp[c - 2], 0));
+      MB_CUDA(cudaStreamWaitEvent(m->s_h2d, m->ev_d2h[c - 2], 0));
+    }
     for (int i = 0; i < n_inputs; ++i) {
       const TensorV& t = m->tensors[vs[i]];
       float* slot = reinterpret_cast<float*>(arena + t.off_f32);
@@ -1581,9 +1635,9 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
   MB_CUDA(cudaStreamSynchronize(m->s_comp));
   MB_TRY(check_device_error_word(m->s_comp));
   cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1);
-  g_stats.ms_last_forward = m->last_ms;
-  g_stats.flops_last_forward = m->flops * P;
-  g_stats.bytes_last_forward = m->hbm_bytes * P;
+  ctx().stats.ms_last_forward = m->last_ms;
+  ctx().stats.flops_last_forward = m->flops * P;
+  ctx().stats.bytes_last_forward = m->hbm_bytes * P;
   return MIMIR_B200_OK;
 }
 
@@ -1611,6 +1665,7 @@ static int token_wise(const LayerRT& L) {
 }
 
 int mimir_b200_model_decode_end(MimirB200ModelHandle m) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (m->decode) {
     cudaDeviceSynchronize();
@@ -1623,6 +1678,7 @@ int mimir_b200_model_decode_end(MimirB200ModelHandle m) {
 
 int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, int max_seq,
                                   uint64_t* cache_bytes) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (m->is_twin) return fail(MIMIR_B200_E_INVALID, "decode_begin: not a model handle");
   if (m->planned_batch <= 0) return fail(MIMIR_B200_E_INVALID, "decode_begin: plan the model first (its operand planes are shared)");
@@ -1632,6 +1688,7 @@ int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput*
   for (const auto& L : m->layers) MB_TRY(token_wise(L));
   auto t = std::make_unique<MimirB200Model>();
   t->is_twin = true;
+  t->device = m->device;
   t->precision = m->precision;
   t->max_seq = max_seq;
   t->layers = m->layers;  // descriptors, classification and weight pointers
@@ -1688,6 +1745,7 @@ int mimir_b200_model_decode_begin(MimirB200ModelHandle m, const MimirNamedInput*
 
 int mimir_b200_model_decode_step(MimirB200ModelHandle m, const MimirNamedInput* inputs, int n_inputs, int batch, int pos,
                                  float* out_host, uint64_t out_capacity, uint64_t* out_len) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (!m->decode) return fail(MIMIR_B200_E_INVALID, "decode_step: decode_begin has not been called");
   if (m->decode->twin_epoch != m->plan_epoch || m->planned_batch <= 0)
@@ -1706,6 +1764,7 @@ int mimir_b200_model_decode_step(MimirB200ModelHandle m, const MimirNamedInput* 
 // Cuts the batch of the host-pointer forward into `micro_batches` pieces that overlap their
 // copy-in, compute and copy-out (takes effect at the next plan; batch must be a multiple).
 int mimir_b200_model_set_pipeline(MimirB200ModelHandle m, int micro_batches) {
+  DeviceScope dev_scope(m ? m->device : ctx().device);
   if (!m) return fail(MIMIR_B200_E_INVALID, "null model handle");
   if (micro_batches < 1 || micro_batches > 1024) return fail(MIMIR_B200_E_INVALID, "set_pipeline: micro_batches must be in 1..1024");
   if (micro_batches != m->pipeline) m->planned_batch = 0;
@@ -1715,7 +1774,7 @@ int mimir_b200_model_set_pipeline(MimirB200ModelHandle m, int micro_batches) {
 
 int mimir_b200_get_stats(MimirB200Stats* out) {
   if (!out) return fail(MIMIR_B200_E_INVALID, "get_stats: null output");
-  *out = g_stats;
+  *out = ctx().stats;
   out->kernels_launched = ctx().launches.load();
   return MIMIR_B200_OK;
 }
@@ -1752,15 +1811,23 @@ int mimir_b200_profile_read(float* total_ms, int* launches) {
 }
 
 int mimir_b200_shutdown(void) {
-  Context& c = ctx();
-  if (!c.initialised) return MIMIR_B200_OK;
-  cudaDeviceSynchronize();
   std::set<MimirB200Model*> models;
   {
     std::lock_guard<std::mutex> lk(g_models_mu);
     models.swap(g_models);
   }
-  for (auto* m : models) destroy_model(m);
+  int prev = 0;
+  const bool have_prev = cudaGetDevice(&prev) == cudaSuccess;
+  for (int d = 0; d < MAX_DEVICES; ++d) {
+    if (!ctx_of(d).initialised) continue;
+    cudaSetDevice(d);
+    cudaDeviceSynchronize();
+  }
+  for (auto* m : models) {
+    cudaSetDevice(m->device);
+    destroy_model(m);
+  }
+  if (have_prev) cudaSetDevice(prev); else cudaGetLastError();
   return MIMIR_B200_OK;
 }
 

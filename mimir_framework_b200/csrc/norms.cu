@@ -13,7 +13,12 @@
 //     writes the result; rows are processed in groups that fit in L2 so that pass 2 reads from L2.
 #include <cooperative_groups.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "common.h"
+#include "planes.cuh"
 #include "sm100_ptx.cuh"
 
 
@@ -321,6 +326,7 @@ struct RmsOnePass {
   __nv_bfloat16* y_split;   // bf16 hi (and lo) planes, or nullptr
   long long plane_stride;   // elements between the hi and the lo plane
   int planes;
+  int f16;                  // the planes hold IEEE half instead of bfloat16
   unsigned* ticket;         // [0] ticket counter, [1] abort flag
   unsigned long long* sum_slots;
   unsigned long long* err_slots;
@@ -501,22 +507,21 @@ __global__ void __launch_bounds__(256, 6) rms_onepass_kernel(const RmsOnePass p)
     if (vec_out) {
       if (p.y != nullptr) __stcs(reinterpret_cast<float4*>(p.y + base + e0), make_float4(o[0], o[1], o[2], o[3]));
       if (p.y_split != nullptr) {
-        const __nv_bfloat162 h01 = __floats2bfloat162_rn(o[0], o[1]), h23 = __floats2bfloat162_rn(o[2], o[3]);
-        const float2 f01 = __bfloat1622float2(h01), f23 = __bfloat1622float2(h23);
-        const __nv_bfloat162 l01 = __floats2bfloat162_rn(o[0] - f01.x, o[1] - f01.y), l23 = __floats2bfloat162_rn(o[2] - f23.x, o[3] - f23.y);
-        *reinterpret_cast<uint2*>(p.y_split + base + e0) =
-            make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
-        if (p.planes == 2)
-          *reinterpret_cast<uint2*>(p.y_split + p.plane_stride + base + e0) =
-              make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+        uint32_t h01, h23, l01, l23;
+        split_pair(o[0], o[1], p.f16, h01, l01);
+        split_pair(o[2], o[3], p.f16, h23, l23);
+        *reinterpret_cast<uint2*>(p.y_split + base + e0) = make_uint2(h01, h23);
+        if (p.planes == 2) *reinterpret_cast<uint2*>(p.y_split + p.plane_stride + base + e0) = make_uint2(l01, l23);
       }
     } else {
       for (int j = 0; j < 4 && e0 + j < n; ++j) {
         if (p.y != nullptr) p.y[base + e0 + j] = o[j];
         if (p.y_split != nullptr) {
-          const __nv_bfloat16 h = __float2bfloat16_rn(o[j]);
-          p.y_split[base + e0 + j] = h;
-          if (p.planes == 2) p.y_split[p.plane_stride + base + e0 + j] = __float2bfloat16_rn(o[j] - __bfloat162float(h));
+          uint16_t h, l;
+          split_one(o[j], p.f16, h, l);
+          uint16_t* y16 = reinterpret_cast<uint16_t*>(p.y_split);
+          y16[base + e0 + j] = h;
+          if (p.planes == 2) y16[p.plane_stride + base + e0 + j] = l;
         }
       }
     }
@@ -996,12 +1001,45 @@ int launch_warp_rows(const float* x, float* y, long long rows, int len, float ep
 }
 
 // ---- scratch for the chunk kernels -------------------------------------------------------------
+// Partial statistics, and the ticket / slot words of the one-pass RMSNorm, live in an 8 MB buffer PER (device,
+// stream): two calls on different streams (two models, two host threads) never share partials or tickets, and
+// calls on one stream are ordered by the stream.  g_norm_mu is held while a call enqueues its launches, so the
+// memset + kernel pairs of two host threads that use the same stream cannot interleave either.
 constexpr size_t NORM_SCRATCH_BYTES = 8u << 20;
-float* g_norm_scratch = nullptr;
+constexpr size_t NORM_SCRATCH_MAX_STREAMS = 32;
+std::mutex g_norm_mu;
+struct NormScratch {
+  float* p = nullptr;
+  bool pinned = false;  // reserved for a capture stream: its address is baked into CUDA graphs, never recycled
+};
+std::map<std::pair<int, cudaStream_t>, NormScratch> g_norm_scratch;
 
-int norm_scratch(float** out) {
-  if (!g_norm_scratch) MB_TRY(dev_alloc(reinterpret_cast<void**>(&g_norm_scratch), NORM_SCRATCH_BYTES, "norm_scratch"));
-  *out = g_norm_scratch;
+// Call with g_norm_mu held.
+int norm_scratch(cudaStream_t st, float** out, bool pin = false) {
+  int dev = 0;
+  MB_CUDA(cudaGetDevice(&dev));
+  const auto key = std::make_pair(dev, st);
+  auto it = g_norm_scratch.find(key);
+  if (it == g_norm_scratch.end()) {
+    size_t loose = 0;
+    for (auto& kv : g_norm_scratch) loose += kv.second.pinned ? 0 : 1;
+    if (loose >= NORM_SCRATCH_MAX_STREAMS) {
+      // streams come and go: once the table is full, wait for everything in flight and drop the unpinned buffers
+      for (auto jt = g_norm_scratch.begin(); jt != g_norm_scratch.end();) {
+        if (jt->second.pinned) { ++jt; continue; }
+        MB_CUDA(cudaSetDevice(jt->first.first));
+        MB_CUDA(cudaDeviceSynchronize());
+        dev_free(jt->second.p, NORM_SCRATCH_BYTES);
+        jt = g_norm_scratch.erase(jt);
+      }
+      MB_CUDA(cudaSetDevice(dev));
+    }
+    NormScratch ns;
+    MB_TRY(dev_alloc(reinterpret_cast<void**>(&ns.p), NORM_SCRATCH_BYTES, "norm_scratch"));
+    it = g_norm_scratch.emplace(key, ns).first;
+  }
+  if (pin) it->second.pinned = true;
+  *out = it->second.p;
   return MIMIR_B200_OK;
 }
 
@@ -1031,11 +1069,11 @@ int meanvar_dispatch(const float* x, float* y, long long rows, long long len, fl
     int ncl = 1;
     while (ncl < 8 && (len + ncl - 1) / ncl > 4096) ncl *= 2;  // ~16 KB per CTA, at most the portable cluster size
     const int slice = static_cast<int>(((len + ncl - 1) / ncl + 3) & ~3ll);
-    static bool attr_set = false;
-    if (!attr_set) {  // static + dynamic shared memory of the largest slice is just above the 48 KB default
+    static PerDeviceOnce attr_once;  // static + dynamic shared memory of the largest slice is just above the 48 KB default
+    MB_TRY(attr_once.run([&]() -> int {
       MB_CUDA(cudaFuncSetAttribute(meanvar_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, CLUSTER_SLICE_MAX * 4));
-      attr_set = true;
-    }
+      return MIMIR_B200_OK;
+    }));
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(rows * ncl));
     cfg.blockDim = dim3(256);
@@ -1053,8 +1091,9 @@ int meanvar_dispatch(const float* x, float* y, long long rows, long long len, fl
     return MIMIR_B200_OK;
   }
   const int chunks = static_cast<int>((len + CHUNK - 1) / CHUNK);
+  std::lock_guard<std::mutex> scratch_lock(g_norm_mu);
   float* part;
-  MB_TRY(norm_scratch(&part));
+  MB_TRY(norm_scratch(st, &part));
   long long group = L2_GROUP_BYTES / (len * 4);
   if (group < 1) group = 1;
   const long long cap_rows = static_cast<long long>(NORM_SCRATCH_BYTES / (sizeof(float) * 3)) / chunks;
@@ -1076,6 +1115,22 @@ int meanvar_dispatch(const float* x, float* y, long long rows, long long len, fl
 }
 
 }  // namespace
+
+int norm_scratch_reserve(cudaStream_t st) {
+  std::lock_guard<std::mutex> lk(g_norm_mu);
+  float* p = nullptr;
+  return norm_scratch(st, &p, true);
+}
+
+void norm_scratch_release(cudaStream_t st) {
+  std::lock_guard<std::mutex> lk(g_norm_mu);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  auto it = g_norm_scratch.find(std::make_pair(dev, st));
+  if (it == g_norm_scratch.end()) return;
+  dev_free(it->second.p, NORM_SCRATCH_BYTES);
+  g_norm_scratch.erase(it);
+}
 
 int launch_layernorm(const float* x, const float* gamma, const float* beta, float* y, int64_t rows, int64_t n, float eps,
                      cudaStream_t st) {
@@ -1109,12 +1164,19 @@ int launch_groupnorm_stats(const float* x, float* stats, int batch, int ch, int 
 bool rmsnorm_onepass_ok(int batch, int64_t n) {
   static const bool off = [] { const char* e = getenv("MIMIR_B200_RMS_ONEPASS"); return e && e[0] == '0'; }();
   if (off || n <= 16384) return false;
-  static int per_sm = -1;
-  if (per_sm < 0) {
-    int v = 0;
-    cudaFuncSetAttribute(rms_onepass_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, rms_onepass_kernel, 256, CHUNK * sizeof(float)) != cudaSuccess) v = 0;
-    per_sm = v;
+  static int per_sm_dev[MAX_DEVICES];  // occupancy of the one-pass kernel, asked once per device (0 = not asked yet)
+  static std::mutex per_sm_mu;
+  int per_sm;
+  {
+    std::lock_guard<std::mutex> lk(per_sm_mu);
+    int& slot = per_sm_dev[ctx().device];
+    if (slot == 0) {
+      int v = 0;
+      cudaFuncSetAttribute(rms_onepass_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, rms_onepass_kernel, 256, CHUNK * sizeof(float)) != cudaSuccess) v = 0;
+      slot = v > 0 ? v : -1;
+    }
+    per_sm = slot > 0 ? slot : 0;
   }
   const int64_t chunks = (n + CHUNK - 1) / CHUNK;
   if (chunks > static_cast<int64_t>(per_sm) * ctx().sm_count) return false;
@@ -1125,14 +1187,16 @@ int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y
                    cudaStream_t st, __nv_bfloat16* y_split, int planes, int64_t plane_stride) {
   if (batch <= 0 || n <= 0) return fail(MIMIR_B200_E_INVALID, "RMSNorm: empty input");
   if (rmsnorm_onepass_ok(batch, n)) {
+    std::lock_guard<std::mutex> scratch_lock(g_norm_mu);
     float* scratch;
-    MB_TRY(norm_scratch(&scratch));
+    MB_TRY(norm_scratch(st, &scratch));
     const int chunks = static_cast<int>((n + CHUNK - 1) / CHUNK);
     const size_t slots = static_cast<size_t>(batch) * chunks;
     MB_CUDA(cudaMemsetAsync(scratch, 0, 256 + slots * 16, st));
     RmsOnePass p{};
     p.x = x; p.gamma = gamma; p.n_gamma = gamma ? n_gamma : 0; p.y = y; p.y_split = y_split; p.plane_stride = plane_stride;
     p.planes = planes;
+    p.f16 = plane_format() == PLANES_F16 ? 1 : 0;
     p.ticket = reinterpret_cast<unsigned*>(scratch);
     p.sum_slots = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(scratch) + 256);
     p.err_slots = p.sum_slots + slots;
@@ -1153,8 +1217,9 @@ int launch_rmsnorm(const float* x, const float* gamma, int64_t n_gamma, float* y
     return launch_sweep_rows<FAM_RMS>(p, st);
   }
   const int chunks = static_cast<int>((n + CHUNK - 1) / CHUNK);
+  std::lock_guard<std::mutex> scratch_lock(g_norm_mu);
   float* part;
-  MB_TRY(norm_scratch(&part));
+  MB_TRY(norm_scratch(st, &part));
   // scratch: [floats: partial sums | doubles: rounding errors], a third and two thirds of the buffer
   constexpr size_t ERR_OFFSET = (NORM_SCRATCH_BYTES / 3) & ~size_t(255);  // doubles start 256-byte aligned
   const long long cap_rows = static_cast<long long>(ERR_OFFSET / sizeof(float)) / chunks;
@@ -1192,8 +1257,9 @@ int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softm
     return launch_sweep_rows<FAM_SOFTMAX>(p, st);
   }
   const int chunks = static_cast<int>((n + CHUNK - 1) / CHUNK);
+  std::lock_guard<std::mutex> scratch_lock(g_norm_mu);
   float* part;
-  MB_TRY(norm_scratch(&part));
+  MB_TRY(norm_scratch(st, &part));
   long long group = L2_GROUP_BYTES / (n * 4);
   if (group < 1) group = 1;
   const long long cap_rows = static_cast<long long>(NORM_SCRATCH_BYTES / (2 * sizeof(float))) / chunks;
@@ -1218,22 +1284,27 @@ int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softm
 // The chunked RMSNorm above keeps its per-chunk partial sums in a buffer obtained from cudaMalloc.
 // Some callers cannot afford that: code running between the launches of a latency-critical
 // serving loop (cudaMalloc synchronises the device), code that has handed all free device memory
-// to its own pool, and plugins whose host forbids them to allocate.  For them the same two kernels
-// run with the partial sums in this fixed array instead.  Every GPU that loads the library carries
-// these 64 KB until the process exits.
+// to its own pool, and plugins whose host forbids them to allocate.  For them the same kernels
+// run with the partial sums (and, for samples above 16 384 elements, the replayed rounding errors
+// of the reference's sequential sum) in this fixed array instead.  Every GPU that loads the library
+// carries these 192 KB until the process exits.
 namespace {
 
-constexpr int NOALLOC_MAX_PARTIALS = 16384;  // floats; batch * ceil(n / 8192) must not exceed it
-static __device__ __align__(256) float g_rms_noalloc_scratch[NOALLOC_MAX_PARTIALS];
+constexpr int NOALLOC_MAX_PARTIALS = 16384;  // batch * ceil(n / 8192) must not exceed it
+struct NoAllocScratch {
+  float part[NOALLOC_MAX_PARTIALS];    // per-chunk sums of squares
+  double err[NOALLOC_MAX_PARTIALS];    // per-chunk rounding errors of the sequential chain
+};
+static __device__ __align__(256) NoAllocScratch g_rms_noalloc_scratch;
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
 std::mutex g_noalloc_mu;
-float* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device
+NoAllocScratch* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {};  // device address of the array, per device
 
 // `g_rms_noalloc_scratch` in host code is only a handle for the runtime, not something a kernel may
 // dereference; the address kernels can use comes from cudaGetSymbolAddress, asked once per device
 // while that device is current.
-int noalloc_scratch_for_current_device(float** out) {
+int noalloc_scratch_for_current_device(NoAllocScratch** out) {
   int dev = -1;
   MB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return fail(MIMIR_B200_E_UNSUPPORTED, "rmsnorm_noalloc: device index %d not supported", dev);
@@ -1243,7 +1314,7 @@ int noalloc_scratch_for_current_device(float** out) {
     cudaError_t e = cudaGetSymbolAddress(&p, g_rms_noalloc_scratch);
     if (e != cudaSuccess || !p)
       return fail(MIMIR_B200_E_CUDA, "rmsnorm_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
-    g_noalloc_addr[dev] = static_cast<float*>(p);
+    g_noalloc_addr[dev] = static_cast<NoAllocScratch*>(p);
   }
   *out = g_noalloc_addr[dev];
   return MIMIR_B200_OK;
@@ -1262,15 +1333,25 @@ extern "C" int mimir_b200_dev_rmsnorm_noalloc(const float* x, const float* gamma
                 "rmsnorm_noalloc: batch %d x %lld elements needs %lld partial sums, the fixed scratch holds %d "
                 "(batch * ceil(n / %d) <= %d, batch <= 65535)",
                 batch, n, chunks * batch, NOALLOC_MAX_PARTIALS, CHUNK, NOALLOC_MAX_PARTIALS);
-  float* part = nullptr;
-  MB_TRY(noalloc_scratch_for_current_device(&part));
+  NoAllocScratch* sc = nullptr;
+  MB_TRY(noalloc_scratch_for_current_device(&sc));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const float* g = (gamma && n_gamma > 0) ? gamma : nullptr;
   dim3 grid(static_cast<unsigned>(chunks), static_cast<unsigned>(batch));
-  // every partial that pass 2 reads is written by pass 1 of the same call: nothing has to be cleared
-  rms_chunk_stats_kernel<<<grid, 256, 0, st>>>(x, part, n, static_cast<int>(chunks), CHUNK);
+  // every partial and error term that a later pass reads is written by an earlier pass of the same call:
+  // nothing has to be cleared
+  rms_chunk_stats_kernel<<<grid, 256, 0, st>>>(x, sc->part, n, static_cast<int>(chunks), CHUNK);
   MB_CUDA(cudaGetLastError());
-  rms_chunk_apply_kernel<<<grid, 256, 0, st>>>(x, g, g ? n_gamma : 0, y, part, n, static_cast<int>(chunks), CHUNK, eps);
+  // above this length the reference's one sequential fp32 sum differs measurably from an exact sum, and the
+  // difference is reproduced like in mimir_b200_dev_rmsnorm (same threshold)
+  const bool faithful = n > 16384;
+  if (faithful) {
+    rms_seq_err_kernel<<<grid, 256, 0, st>>>(x, sc->part, sc->err, n, static_cast<int>(chunks), CHUNK);
+    MB_CUDA(cudaGetLastError());
+    count_launch();
+  }
+  rms_chunk_apply_kernel<<<grid, 256, 0, st>>>(x, g, g ? n_gamma : 0, y, sc->part, n, static_cast<int>(chunks), CHUNK, eps,
+                                               faithful ? sc->err : nullptr);
   MB_CUDA(cudaGetLastError());
   count_launch(2);
   return MIMIR_B200_OK;

@@ -19,6 +19,7 @@ struct LinearExec {
   const __nv_bfloat16* x_split = nullptr;   // planes produced by an upstream GEMM epilogue
   const float* w_f32 = nullptr;             // fp32 [out_f, in_f] (skinny path)
   const __nv_bfloat16* w_split = nullptr;   // planes [w_planes][out_f][kp] (tensor-core path)
+  float w_scale = 1.0f;                     // the planes hold W * w_scale (weight_plane_scale)
   const float* bias = nullptr;
   const float* residual = nullptr;          // same layout as y_f32
   int activation = -1;
@@ -39,6 +40,7 @@ struct AttentionExec {
   const __nv_bfloat16* x_split = nullptr;      // or: its operand planes, written by the producing layer
   const __nv_bfloat16* wqkv_split = nullptr;   // planes of Wqkv^T: [3E][round_up(E,64)]
   const __nv_bfloat16* wout_split = nullptr;   // planes of Wout^T: [E][round_up(E,64)]
+  float w_scale = 1.0f;                        // both plane sets hold their weights times this (weight_plane_scale)
   const float* residual = nullptr;
   float* y = nullptr;
   void* ws = nullptr;
@@ -69,6 +71,7 @@ struct CrossAttentionExec {
   const __nv_bfloat16* wq_split = nullptr;     // planes of Wq^T:   [E][round_up(E,64)]
   const __nv_bfloat16* wkv_split = nullptr;    // planes of Wkv^T:  [2E][round_up(E,64)]
   const __nv_bfloat16* wout_split = nullptr;   // planes of Wout^T: [E][round_up(E,64)]
+  float w_scale = 1.0f;                        // all three plane sets hold their weights times this
   const float* residual = nullptr;
   float* y = nullptr;
   void* ws = nullptr;
@@ -82,6 +85,7 @@ struct ConvExec {
   int activation = -1;                         // MIMIR_B200_ELT_RELU when the layer asks for it
   const float* x = nullptr;                    // NCHW
   const __nv_bfloat16* w_split = nullptr;      // planes [oc][round_up(ic*ks*ks, 64)]
+  float w_scale = 1.0f;                        // the planes hold W * w_scale
   const float* residual = nullptr;             // NCHW, same shape as y
   float* y = nullptr;
   void* ws = nullptr;

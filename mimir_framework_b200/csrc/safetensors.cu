@@ -214,6 +214,7 @@ using namespace mb;
 
 int mimir_b200_model_load_safetensors(MimirB200ModelHandle m, const char* path, int strict, int* layers_loaded,
                                       unsigned long long* bytes_loaded) {
+  DeviceScope dev_scope(model_device(m));
   if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
   if (!m || !path) return fail(MIMIR_B200_E_INVALID, "load_safetensors: null argument");
   if (layers_loaded) *layers_loaded = 0;

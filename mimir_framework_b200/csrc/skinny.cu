@@ -285,11 +285,11 @@ int launch_partial(const float* x, const float* w, float* scratch, int m, int k,
   const char* plain = getenv("MIMIR_B200_SKINNY_PLAIN");
   if (vec && !(plain && plain[0] == '1') && static_cast<long long>(tiles) * kslices < (1LL << 30)) {
     constexpr int SMEM = (2 * MT * SK_SLICE + SK_WARPS * SK_STAGES * WR * SK_STEP) * 4;
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr_once;
+    MB_TRY(attr_once.run([&]() -> int {
       MB_CUDA(cudaFuncSetAttribute(skinny_stream_kernel<MT, WR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-      attr = true;
-    }
+      return MIMIR_B200_OK;
+    }));
     const int items = tiles * kslices;
     const int grid = items < ctx().sm_count ? items : ctx().sm_count;
     skinny_stream_kernel<MT, WR><<<grid, SK_THREADS, SMEM, st>>>(x, w, scratch, m, k, n, kslices, items);

@@ -151,10 +151,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int swizzle_b
   return static_cast<uint64_t>((saddr & 0x3FFFF) >> 4) | (sbo << 32) | (1ull << 46) | (layout << 61);
 }
 
-// Instruction descriptor for kind::f16: D fp32 (bits [4,6) = 1), A and B bf16 (bits [7,10) and
-// [10,13) = 1), both K-major (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in [24,29).
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+// Instruction descriptor for kind::f16: D fp32 (bits [4,6) = 1), A and B formats in bits [7,10) and
+// [10,13) (0 = IEEE half, 1 = bfloat16; both operands always share the format here), both K-major
+// (bits 15, 16 = 0), N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, int f16 = 0) {
+  return (1u << 4) | (f16 ? 0u : ((1u << 7) | (1u << 10))) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // The same load without the wait, so that several loads can be in flight before one tmem_wait_ld().

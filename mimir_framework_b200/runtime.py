@@ -30,6 +30,22 @@ _SIGS = {
     "mimir_b200_guard_request": [C.c_size_t, C.c_char_p],
     "mimir_b200_guard_release": [C.c_size_t],
     "mimir_b200_guard_stats": [_P, _P, _P],
+    "mimir_b200_guard_block": [C.c_int],
+    "mimir_b200_guard_freeze": [C.c_int],
+    "mimir_b200_guard_reset": [],
+    "mimir_b200_guard_state": [_P, _P, _P, _P],
+    "mimir_b200_current_device": [_P],
+    "mimir_b200_shard_range": [C.c_longlong, C.c_int, C.c_int, _P, _P],
+    "mimir_b200_replicas_create": [_P, C.c_int, C.c_size_t, _P, C.c_int, C.c_int, _P],
+    "mimir_b200_replicas_destroy": [_P],
+    "mimir_b200_replicas_count": [_P, _P],
+    "mimir_b200_replicas_upload_weights": [_P, C.c_int, _P, C.c_uint64],
+    "mimir_b200_replicas_set_pipeline": [_P, C.c_int],
+    "mimir_b200_replicas_plan": [_P, _P, C.c_int, C.c_int, _P],
+    "mimir_b200_replicas_forward": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P],
+    "mimir_b200_replicas_inject_failure": [_P, C.c_int],
+    "mimir_b200_replicas_selftest_join": [C.c_int, C.c_int],
+    "mimir_b200_model_output_len": [_P, _P],
     "mimir_b200_linear_forward": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int],
     "mimir_b200_linear_forward_ex": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int],
     "mimir_b200_matmul": [_P, _P, _P, C.c_int, C.c_int, C.c_int],
@@ -66,6 +82,7 @@ _SIGS = {
     "mimir_b200_model_weights_device": [_P, C.c_int, C.c_uint64, _P],
     "mimir_b200_model_num_layers": [_P, _P],
     "mimir_b200_model_layer_info": [_P, C.c_int, _P, _P],
+    "mimir_b200_model_tensor_slot": [_P, C.c_char_p, _P, _P],
     "mimir_b200_model_load_safetensors": [_P, C.c_char_p, C.c_int, _P, _P],
     "mimir_b200_model_plan": [_P, _P, C.c_int, C.c_int, _P],
     "mimir_b200_model_forward": [_P, _P, C.c_int, C.c_int, _P, C.c_uint64, _P],
@@ -420,6 +437,12 @@ class GraphModel:
         self.arena_bytes = peak.value
         return peak.value
 
+    def tensor_slot(self, input_name=None):
+        """(byte offset, byte size) of a graph input's slot, or of the output's (None), in one arena buffer."""
+        off, nb = C.c_uint64(0), C.c_uint64(0)
+        check(lib().mimir_b200_model_tensor_slot(self._h, None if input_name is None else input_name.encode(), C.byref(off), C.byref(nb)))
+        return off.value, nb.value
+
     def forward(self, inputs: dict, batch: int, out_per_sample: int) -> np.ndarray:
         """inputs: name -> (numpy array, broadcast flag).  Host in, host out."""
         spec = {}
@@ -467,4 +490,51 @@ class GraphModel:
         n = C.c_uint64(0)
         check(lib().mimir_b200_model_forward_device(self._h, C.addressof(arr), len(spec), batch, out_ptr, out_capacity,
                                                     C.byref(n), stream))
+        return n.value
+
+
+class Replicas:
+    """One replica of a layer graph per listed device, one host thread per device: ``mimir_b200_replicas_*``."""
+
+    def __init__(self, devices, descs, precision: int = abi.PREC_BF16X2, hbm_budget_bytes: int = 0, pipeline: int = 1):
+        self._descs = list(descs)
+        self._arr = desc_array(self._descs)
+        self._h = C.c_void_p()
+        devs = (C.c_int * len(devices))(*devices)
+        check(lib().mimir_b200_replicas_create(devs, len(devices), hbm_budget_bytes, C.addressof(self._arr), len(self._descs), precision,
+                                               C.byref(self._h)))
+        if pipeline != 1:
+            check(lib().mimir_b200_replicas_set_pipeline(self._h, pipeline))
+
+    def close(self):
+        if self._h:
+            lib().mimir_b200_replicas_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def upload_weights(self, i: int, w):
+        if w is None:
+            return
+        w = _f(w)
+        check(lib().mimir_b200_replicas_upload_weights(self._h, i, _p(w), w.size))
+
+    def plan(self, spec: dict, batch_total: int) -> int:
+        arr = GraphModel._inputs({k: (0, per, bc) for k, (per, bc) in spec.items()})
+        peak = C.c_uint64(0)
+        check(lib().mimir_b200_replicas_plan(self._h, C.addressof(arr), len(spec), batch_total, C.byref(peak)))
+        return peak.value
+
+    def inject_failure(self, rank: int):
+        check(lib().mimir_b200_replicas_inject_failure(self._h, rank))
+
+    def forward_host_ptrs(self, spec: dict, batch_total: int, out_ptr: int, out_capacity: int) -> int:
+        """spec: name -> (host address or array, per_sample, broadcast); the output lands in one host buffer."""
+        arr = GraphModel._inputs(spec)
+        n = C.c_uint64(0)
+        check(lib().mimir_b200_replicas_forward(self._h, C.addressof(arr), len(spec), batch_total, out_ptr, out_capacity, C.byref(n)))
         return n.value

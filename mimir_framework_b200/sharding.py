@@ -13,11 +13,14 @@ import numpy as np
 def shard_range(total: int, world: int, rank: int) -> tuple[int, int]:
     """Contiguous slice [begin, end) of `total` units for `rank`; the first `total % world` ranks
     take one extra unit.  Slices are disjoint and cover everything."""
-    if world <= 0 or not (0 <= rank < world) or total < 0:
+    import ctypes as C
+
+    from . import runtime as rt
+
+    b, e = C.c_longlong(), C.c_longlong()
+    if rt.lib().mimir_b200_shard_range(total, world, rank, C.byref(b), C.byref(e)) != 0:  # the library's own slicing rule
         raise ValueError("bad shard arguments")
-    base, extra = divmod(total, world)
-    begin = rank * base + min(rank, extra)
-    return begin, begin + base + (1 if rank < extra else 0)
+    return b.value, e.value
 
 
 def reduce_max(value: float, device=None) -> float:

@@ -242,6 +242,40 @@ def test_pipelined_forward_equals_single_pass(backend):
     m.close()
 
 
+def test_pipelined_forward_output_in_an_input_slot(backend):
+    """A two-layer Linear graph whose output the planner puts into the (dead) input slot: with 8 micro-batches
+    of 8 MB each, the copy-in of micro-batch c and the copy-out of micro-batch c-2 use the same bytes of the
+    same arena buffer and must be ordered.  The result has to be bit-equal to the un-pipelined forward."""
+    rows, k = 4096, 512   # 8 MB per micro-batch in and out
+    P = 8
+    descs = [make_desc("l0", "Linear", inputs=["x"], output="h", in_features=k, out_features=k, seq_len=rows, use_bias=1, params_count=k * k + k),
+             make_desc("l1", "Linear", inputs=["h"], output="x", in_features=k, out_features=k, seq_len=rows, use_bias=1, params_count=k * k + k)]
+    r = np.random.default_rng(5)
+    weights = [np.concatenate([r.uniform(-1, 1, k * k).astype(np.float32) / np.sqrt(k), r.uniform(-0.1, 0.1, k).astype(np.float32)]) for _ in range(2)]
+    x = r.standard_normal((P, rows * k), dtype=np.float32)
+    m1 = backend.GraphModel(descs)
+    mp = backend.GraphModel(descs, pipeline=P)
+    for m in (m1, mp):
+        for i, w in enumerate(weights):
+            m.upload_weights(i, w)
+    m1.plan({"x": (rows * k, False)}, P)
+    mp.plan({"x": (rows * k, False)}, P)
+    in_off, in_bytes = mp.tensor_slot("x")
+    out_off, out_bytes = mp.tensor_slot(None)
+    assert in_off < out_off + out_bytes and out_off < in_off + in_bytes, "the plan no longer reuses the input slot: pick another graph"
+    want = m1.forward({"x": (x.ravel(), False)}, P, rows * k)
+    for _ in range(3):
+        got = mp.forward({"x": (x.ravel(), False)}, P, rows * k)
+        assert np.array_equal(got, want)
+    sub = np.sort(r.choice(rows, 16, replace=False))
+    ref_rows = port.run_graph([make_desc("l0", "Linear", inputs=["x"], output="h", in_features=k, out_features=k, seq_len=16, use_bias=1, params_count=k * k + k),
+                               make_desc("l1", "Linear", inputs=["h"], output="x", in_features=k, out_features=k, seq_len=16, use_bias=1, params_count=k * k + k)],
+                              weights, {"x": x[P - 1].reshape(rows, k)[sub].ravel()})
+    assert_close(got.reshape(P, rows, k)[P - 1][sub], ref_rows, "pipelined two-layer stack, last micro-batch")
+    m1.close()
+    mp.close()
+
+
 def test_gpt_decoder_reduced(backend):
     """Configuration 3 at reduced size (2 layers, d 128, 4 heads of 32, seq 96, vocab 300), bf16-rounded
     weights, both precision modes; logits within tolerance and argmax ids equal wherever the CPU top-2

@@ -5,8 +5,9 @@ serving loop between latency-critical launches (cudaMalloc synchronises the devi
 own pool already owns all free HBM, a plugin whose host forbids allocation.
 ``mimir_b200_dev_rmsnorm_noalloc`` serves them with a fixed scratch array inside the library.  This
 file checks it against the regular entry point (``mimir_b200_dev_rmsnorm``, which takes its scratch
-from cudaMalloc) on two consecutive calls with different data, and checks the size limit.  It is
-named so that pytest collects it last.
+from cudaMalloc) and against the CPU oracle on two consecutive calls with different data, for samples
+below and above the length from which the reference's sequential fp32 sum is reproduced, and checks
+the size limit.  It is named so that pytest collects it last.
 """
 import numpy as np
 import pytest
@@ -44,6 +45,37 @@ def test_rmsnorm_noalloc_matches_regular_entry_point_twice():
         assert np.all(np.isfinite(got)), f"call {call}: non-finite output"
         err = np.abs(got - ref)
         assert np.all(err <= 1e-4 + 1e-3 * np.abs(ref)), f"call {call}: max err {err.max():.3e}"
+
+
+@pytest.mark.parametrize("n", [12000, 100000, 786432])
+def test_rmsnorm_noalloc_matches_the_cpu_oracle_twice(n):
+    """Short samples (plain sum) and long ones (the reference's sequential chain, LayerOpsExt.hpp:353-356,
+    reproduced from the error terms kept in the same fixed array): both calls inside the parity gate, and
+    for the long ones much closer than the 1.8e-4 relative an exact sum would be off by."""
+    import torch
+
+    from conftest import assert_close
+    from mimir_framework_b200 import runtime as rt
+    from oracle import port
+
+    lib = rt.lib()
+    torch.cuda.set_device(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    batch = 2
+    r = np.random.default_rng(n)
+    gamma = r.standard_normal(n).astype(np.float32)
+    d_gamma = torch.from_numpy(gamma).cuda()
+    for call in range(2):
+        x = (r.standard_normal((batch, n)) * (0.5 + 2.0 * call)).astype(np.float32)
+        d_x = torch.from_numpy(x).cuda()
+        d_y = torch.full((batch, n), float("nan"), device="cuda")
+        rt.check(lib.mimir_b200_dev_rmsnorm_noalloc(d_x.data_ptr(), d_gamma.data_ptr(), n, d_y.data_ptr(), batch, n, 1e-5, stream))
+        torch.cuda.synchronize()
+        got = d_y.cpu().numpy()
+        want = np.stack([port.rmsnorm(x[b], gamma, 1e-5) for b in range(batch)])
+        assert_close(got, want, f"rmsnorm_noalloc n={n} call {call}")
+        rel = np.abs(got - want).max() / np.abs(want).max()
+        assert rel < 2e-5, f"n={n} call {call}: relative error {rel:.2e} - the sequential sum is not reproduced"
 
 
 def test_rmsnorm_noalloc_rejects_sizes_beyond_its_scratch():
