@@ -84,6 +84,16 @@ typedef enum MimirB200Eltwise {
  * their device and switch to it themselves.  Replaces the engine construction in Model::Model()
  * (Model.cpp:690-698, 753-878) and MemoryGuard::setLimit (MemoryGuard.hpp:47-60). */
 int mimir_b200_init(int device, size_t hbm_budget_bytes);
+/* Selection inside Mimir by environment, default off, with the conventions of the reference's accelerator switches
+ * (env_flag_true / env_int, Model.cpp:704-722; MIMIR_VULKAN_LINEAR at Model.cpp:5110-5112):
+ *   MIMIR_B200               any non-empty value other than "0" selects this backend
+ *   MIMIR_B200_DEVICE        CUDA device index (default 0)
+ *   MIMIR_B200_HBM_BUDGET_MB budget of the guard in MiB (unset or 0: 90 % of the device's memory)
+ * env_selection only parses; init_from_env also calls mimir_b200_init when selected (*enabled = 1) and touches nothing
+ * otherwise (*enabled = 0, status OK).  When selected and no usable GPU is there the status is the init error: there is
+ * no silent CPU fallback inside the backend. */
+int mimir_b200_env_selection(int* enabled, int* device, size_t* hbm_budget_bytes);
+int mimir_b200_init_from_env(int* enabled);
 /* The device the calling thread's per-op calls run on. */
 int mimir_b200_current_device(int* device);
 /* Releases every model handle on every device.  Replaces the engine teardown in Model::~Model()
@@ -397,6 +407,11 @@ int mimir_b200_get_stats(MimirB200Stats* out);
 /* Reads (and clears) the device word that bounded in-kernel waits set when they give up:
  * OK, or E_TIMEOUT.  model_forward and the host-pointer calls check it themselves. */
 int mimir_b200_check_device(void* stream);
+/* Runs the give-up path of the kernels' bounded waits on purpose: one thread block waits `limit_ns` (at most 100 ms)
+ * on a barrier that nothing arrives on, then sets the device error word, drains and returns normally.  The next
+ * mimir_b200_check_device returns E_TIMEOUT ("site 90"); calls after that work as usual.  Nothing faults or hangs.
+ * No counterpart in the reference. */
+int mimir_b200_selftest_wait_timeout(unsigned long long limit_ns, void* stream);
 /* Live timing of the contraction (GEMM) kernel: while enabled, every launch is bracketed by CUDA
  * events on the launching stream; profile_read synchronises, returns the summed duration and the
  * number of launches, and clears the record.  No counterpart in the reference. */

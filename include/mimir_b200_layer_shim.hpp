@@ -17,7 +17,19 @@
 #include "Layers.hpp"     // Mímir
 #include "mimir_b200.h"
 
+#include <stdexcept>
+
 namespace mimir_b200 {
+
+// Reads MIMIR_B200 / MIMIR_B200_DEVICE / MIMIR_B200_HBM_BUDGET_MB and brings the backend up when it is selected (default
+// off, like the reference's own accelerator switches, Model.cpp:5110-5112).  Returns whether it is selected; throws
+// std::runtime_error - the reference's error convention (RuntimeAllocator.hpp:344-358) - when it is selected but cannot
+// start: the backend has no CPU fallback of its own, the caller decides what happens then.
+inline bool init_from_env() {
+  int enabled = 0;
+  if (mimir_b200_init_from_env(&enabled) != MIMIR_B200_OK) throw std::runtime_error(std::string("mimir_b200: ") + mimir_b200_last_error());
+  return enabled != 0;
+}
 
 inline MimirLayerDesc describe(const Layer& L) {
   MimirLayerDesc d;

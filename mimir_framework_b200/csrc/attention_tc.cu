@@ -57,6 +57,7 @@ struct AttnParams {
   int qk_from_planes;  // Q and K tiles come straight from the QKV GEMM's output planes [2][batch*seq][3E] (5-D maps)
   int v_mn_major;      // ... and so do the V tiles, as [key][d] rows read by the MMA as an MN-major B operand
   int f16;             // operand planes hold IEEE half instead of bfloat16
+  int head_chunk;      // (sample, head) pairs per scheduling chunk of the second kernel form
   float acc_comp;      // relative loss of the truncating fp32 accumulation per MMA (0 = no compensation)
   int* err_word;
 };
@@ -437,6 +438,335 @@ flash_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Second form of the kernel (the default when Q, K and V come from the projection's planes): the same arithmetic, a
+// deeper pipeline.
+//   * P never goes through shared memory.  The softmax threads write their probabilities back into tensor memory as
+//     packed 16-bit pairs, over the columns of the score tile they were computed from (hi pairs in the first 32 columns
+//     of the tile, lo pairs in the last 32), and P V is issued with its A operand in tensor memory.
+//   * Three score tiles rotate (S_j -> P_j in tile j % 3), so the softmax of tile j + 1 starts as soon as S_{j+1} is
+//     there; it no longer waits for P_j V_j to finish reading a single P buffer.  Q K^T runs two tiles ahead of P V.
+//   * K and V tiles are double-buffered.
+// Shared memory: Q 32 KB + 2 x 16 KB K + 2 x 16 KB V = 96 KB; 256 TMEM columns (3 x 64 scores + 64 for O): two CTAs
+// per SM as before.  A tile's barriers live per score tile / per stage, so that no waiter is ever more than one phase
+// behind the barrier it waits on.
+constexpr int A2_TILE = AT_BK * AT_HD * 2;        // one plane of a 64-key K or V tile
+constexpr int A2_STAGE = 2 * A2_TILE;             // hi and lo plane
+constexpr int A2_THREADS = 320;                    // TMA warp, MMA warp, 8 softmax warps (two threads per query row)
+constexpr int A2_XCHG = 4 * AT_BQ * 4;             // row maxima / sums exchanged between the two threads of a row
+constexpr int A2_SMEM = 2 * AT_Q_BYTES + 2 * A2_STAGE + 2 * A2_STAGE + A2_XCHG + 256;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(A2_THREADS, 2)
+flash_attn_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicExch(p.err_word, 29);
+    return;
+  }
+  uint8_t* sQ = smem;                       // [2 planes][128][64], 128B-swizzled rows
+  uint8_t* sK = sQ + 2 * AT_Q_BYTES;        // [2 stages][2 planes][64 keys][64]
+  uint8_t* sV = sK + 2 * A2_STAGE;          // [2 stages][2 planes][64 keys][64]
+  float* xchg = reinterpret_cast<float*>(sV + 2 * A2_STAGE);  // [tile parity][key half][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * A2_STAGE + A2_XCHG);
+  uint64_t *q_full = bars, *k_full = bars + 1 /*[2]*/, *k_empty = bars + 3 /*[2]*/, *v_full = bars + 5 /*[2]*/, *v_empty = bars + 7 /*[2]*/,
+           *s_full = bars + 9 /*[3]*/, *p_full = bars + 12 /*[3]*/, *pv_done = bars + 15 /*[3]*/;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* xchg_abort = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [4]: a warp of the pair gave up
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // CTA order.  Causal query tiles differ in length (2 ... 2 * q_tiles key tiles); within a chunk of `head_chunk`
+  // (sample, head) pairs - sized so that the chunk's K and V stay in L2 - the longest tiles of all its heads are launched
+  // first and the shortest last, so that the tail of the launch is made of short CTAs whatever the batch.
+  int qt, bhi;
+  {
+    const int q_tiles = (p.seq + AT_BQ - 1) / AT_BQ;
+    const int bid = static_cast<int>(blockIdx.x);
+    const int c = bid / (q_tiles * p.head_chunk);
+    const int rem = bid - c * q_tiles * p.head_chunk;
+    const int hcnt = min(p.head_chunk, p.bh - c * p.head_chunk);
+    const int rank = rem / hcnt;
+    bhi = c * p.head_chunk + (rem - rank * hcnt);
+    qt = p.causal ? q_tiles - 1 - rank : rank;
+  }
+  const int q0 = qt * AT_BQ;
+  int n_tiles = (p.seq + AT_BK - 1) / AT_BK;
+  if (p.causal) n_tiles = min(n_tiles, (min(p.seq, q0 + AT_BQ) + AT_BK - 1) / AT_BK);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(k_full + i, 1);
+      mbar_init(k_empty + i, 1);
+      mbar_init(v_full + i, 1);
+      mbar_init(v_empty + i, 1);
+    }
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(s_full + i, 1);
+      mbar_init(p_full + i, 8);
+      mbar_init(pv_done + i, 1);
+    }
+    *abort_flag = 0;
+    for (int i = 0; i < 4; ++i) xchg_abort[i] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, AT_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 3 * AT_BK;  // score / probability tile b lives at tmem_base + b * 64
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int smp = bhi / p.heads, hd_slot = bhi - smp * p.heads;  // 5-D maps: (d, position, sample, head slot, plane)
+      mbar_expect_tx(q_full, 2 * AT_Q_BYTES);
+      tma_load_5d(sQ, &map_q, q_full, 0, q0, smp, hd_slot, 0);
+      tma_load_5d(sQ + AT_Q_BYTES, &map_q, q_full, 0, q0, smp, hd_slot, 1);
+      bool ok = true;
+      auto load_k = [&](int j) {
+        const int st = j & 1;
+        if (!mbar_wait(k_empty + st, (static_cast<uint32_t>(j >> 1) & 1) ^ 1, abort_flag, p.err_word, 31)) { ok = false; return; }
+        mbar_expect_tx(k_full + st, A2_STAGE);
+        tma_load_5d(sK + st * A2_STAGE, &map_k, k_full + st, 0, j * AT_BK, smp, p.heads + hd_slot, 0);
+        tma_load_5d(sK + st * A2_STAGE + A2_TILE, &map_k, k_full + st, 0, j * AT_BK, smp, p.heads + hd_slot, 1);
+      };
+      auto load_v = [&](int j) {
+        const int st = j & 1;
+        if (!mbar_wait(v_empty + st, (static_cast<uint32_t>(j >> 1) & 1) ^ 1, abort_flag, p.err_word, 32)) { ok = false; return; }
+        mbar_expect_tx(v_full + st, A2_STAGE);
+        tma_load_5d(sV + st * A2_STAGE, &map_v, v_full + st, 0, j * AT_BK, smp, 2 * p.heads + hd_slot, 0);
+        tma_load_5d(sV + st * A2_STAGE + A2_TILE, &map_v, v_full + st, 0, j * AT_BK, smp, 2 * p.heads + hd_slot, 1);
+      };
+      // in the order the MMA warp consumes them: K_0, K_1, then V_j, K_{j+2}
+      if (n_tiles > 0) load_k(0);
+      if (ok && n_tiles > 1) load_k(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        load_v(j);
+        if (ok && j + 2 < n_tiles) load_k(j + 2);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(AT_BQ, AT_BK, p.f16);   // S = Q K^T: M = 128 queries, N = 64 keys
+      const uint32_t idesc_pv = idesc_s | (1u << 16);             // O += P V: N = 64 (d), V rows are keys: MN-major B
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err_word, 33);
+      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      auto issue_scores = [&](int j) -> bool {
+        const uint32_t st = static_cast<uint32_t>(j) & 1, b = static_cast<uint32_t>(j % 3);
+        if (!mbar_wait(k_full + st, static_cast<uint32_t>(j >> 1) & 1, abort_flag, p.err_word, 34)) return false;
+        tcgen05_fence_after();
+        const uint32_t kb = aK + st * A2_STAGE;
+#pragma unroll
+        for (int k = 0; k < AT_HD / 16; ++k) {
+          const uint32_t ko = k * 32;
+          const uint64_t qh = make_smem_desc(aQ + ko, 128), ql = make_smem_desc(aQ + AT_Q_BYTES + ko, 128);
+          const uint64_t kh = make_smem_desc(kb + ko, 128), kl = make_smem_desc(kb + A2_TILE + ko, 128);
+          umma_bf16(tmem_base + b * AT_BK, qh, kh, idesc_s, k != 0 ? 1u : 0u);
+          umma_bf16(tmem_base + b * AT_BK, ql, kh, idesc_s, 1u);
+          umma_bf16(tmem_base + b * AT_BK, qh, kl, idesc_s, 1u);
+        }
+        umma_commit(s_full + b);
+        umma_commit(k_empty + st);
+        return true;
+      };
+      if (ok && n_tiles > 0) ok = issue_scores(0);
+      if (ok && n_tiles > 1) ok = issue_scores(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const uint32_t st = static_cast<uint32_t>(j) & 1, b = static_cast<uint32_t>(j % 3);
+        if (!mbar_wait(p_full + b, static_cast<uint32_t>(j / 3) & 1, abort_flag, p.err_word, 35)) break;
+        if (!mbar_wait(v_full + st, static_cast<uint32_t>(j >> 1) & 1, abort_flag, p.err_word, 36)) break;
+        tcgen05_fence_after();
+        const uint32_t tp = tmem_base + b * AT_BK;  // hi pairs in columns [0, 32), lo pairs in [32, 64) of the tile
+        const uint32_t vb = aV + st * A2_STAGE;
+#pragma unroll
+        for (int k = 0; k < AT_BK / 16; ++k) {
+          // 16 keys: eight packed columns of P, two 1024-byte groups of eight 128-byte V rows
+          const uint64_t vh = make_smem_desc(vb + k * 2048u, 128), vl = make_smem_desc(vb + A2_TILE + k * 2048u, 128);
+          umma_f16_ts(tmem_o, tp + k * 8, vh, idesc_pv, (j != 0 || k != 0) ? 1u : 0u);
+          umma_f16_ts(tmem_o, tp + 32 + k * 8, vh, idesc_pv, 1u);
+          umma_f16_ts(tmem_o, tp + k * 8, vl, idesc_pv, 1u);
+        }
+        umma_commit(pv_done + b);
+        umma_commit(v_empty + st);
+        if (j + 2 < n_tiles) {
+          // S_{j+2} goes into the tile that P_{j-1} V_{j-1} read: that product has long finished (P_j came after it), the
+          // wait only makes the reuse explicit
+          if (j >= 1 && !mbar_wait(pv_done + (j - 1) % 3, static_cast<uint32_t>((j - 1) / 3) & 1, abort_flag, p.err_word, 37)) break;
+          if (!issue_scores(j + 2)) break;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ softmax: two threads per query row ------------------------------
+    // Warps 2-5 take the first 32 keys of every tile, warps 6-9 the last 32; the two warps that share a TMEM lane
+    // quadrant (32 rows) agree on the row maxima through shared memory and a 64-thread named barrier per tile.
+    const int quad = warp & 3;
+    const int grp = (warp - 2) >> 2;  // which half of the tile's keys (and, at the end, of O's columns)
+    const int r_local = quad * 32 + lane;
+    const int row = q0 + r_local;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    constexpr float LOG2E = 1.4426950408889634f;
+    float m_run = -1e30f, l_run = 0.0f;  // the reference's initial max (LayerOps.hpp:1052)
+    bool alive = true;
+    auto warp_wait = [&](uint64_t* bar, uint32_t parity, int where) -> bool {
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, p.err_word, where) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return false;
+      while (!mbar_try_wait(bar, parity)) {}
+      return true;
+    };
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };
+    const float c2 = p.scale * LOG2E;  // scores are kept in the exp2 domain: s * scale * log2(e)
+    for (int j = 0; j < n_tiles; ++j) {
+      const int b = j % 3;
+      // a warp whose wait gave up keeps going round the loop without working, so that it meets its partner at every
+      // pair barrier; the partner learns of it there and does the same (every wait returns at once while the abort flag is up)
+      int ok_tile = 0;
+      if (alive) ok_tile = warp_wait(s_full + b, static_cast<uint32_t>(j / 3) & 1, 38) ? 1 : 0;
+      tcgen05_fence_after();
+      const int key0 = j * AT_BK + grp * 32;
+      uint32_t sc[32];
+      const uint32_t tmem_s = tmem_base + b * AT_BK + lane_base;
+      if (ok_tile) {
+        tmem_ld_32x32_nowait(tmem_s + grp * 32, sc);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sc[i] = 0u;
+      }
+      const int row_first = q0 + quad * 32;
+      const bool full_tile = (key0 + 32 <= p.seq) && (!p.causal || key0 + 31 <= row_first);
+      float mx = -1e30f;
+      if (full_tile) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sc[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int ka = key0 + i;
+          if (!(ka < p.seq && (!p.causal || ka <= row))) sc[i] = 0xff800000u;  // -inf: contributes exp2(-inf) = 0
+          mx = fmaxf(mx, __uint_as_float(sc[i]));
+        }
+      }
+      // the row's maximum over both halves of the tile (two exchange buffers: a thread may be one tile ahead of its partner)
+      xchg[((j & 1) * 2 + grp) * AT_BQ + r_local] = mx;
+      if (!ok_tile) xchg_abort[quad] = 1;
+      pair_sync();
+      if (xchg_abort[quad]) alive = false;
+      if (!alive) continue;
+      mx = fmaxf(mx, xchg[((j & 1) * 2 + (grp ^ 1)) * AT_BQ + r_local]);
+      const float m_new = fmaxf(m_run, (mx > -1e30f) ? mx * p.scale : -1e30f);
+      if (j == 0) {
+        m_run = m_new;  // O is still empty: nothing to rescale
+      } else {
+        // raise the maximum only when some row of this quadrant outgrew it by more than 2^8 (both warps of the pair see
+        // the same maxima, so they decide alike)
+        const bool grow = (m_new - m_run) * LOG2E > 8.0f;
+        if (__any_sync(0xffffffffu, grow)) {
+          // every product issued so far has to be in O before it is rescaled; P_j V_j cannot start before both warps have
+          // handed over their half of P_j, so O's rows are theirs alone until then (each warp its own 32 columns)
+          if (!warp_wait(pv_done + (j - 1) % 3, static_cast<uint32_t>((j - 1) / 3) & 1, 39)) {
+            alive = false;
+            xchg_abort[quad] = 1;  // the partner sees it at the next pair barrier
+            continue;
+          }
+          tcgen05_fence_after();
+          const float corr = fast_exp2((m_run - m_new) * LOG2E);
+          uint32_t o[32];
+          tmem_ld_32x32_nowait(tmem_o + lane_base + grp * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+          tmem_st_32x32(tmem_o + lane_base + grp * 32, o);
+          l_run *= corr;
+          m_run = m_new;
+        }
+      }
+      const float m2 = m_run * LOG2E;
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      // probabilities of keys 2c, 2c + 1 become the packed pair in column c: hi pairs to columns [0, 32) of this score
+      // tile, lo pairs to [32, 64) - the scores they replace are in registers already (this thread's and its partner's:
+      // both loaded before the pair barrier above)
+      uint32_t hi[16], lo[16];
+#pragma unroll
+      for (int e = 0; e < 32; e += 2) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sc[e]), c2, -m2));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sc[e + 1]), c2, -m2));
+        rs4[(e >> 1) & 3] += p0 + p1;
+        split_pair(p0, p1, p.f16, hi[e >> 1], lo[e >> 1]);
+      }
+      tmem_st_32x16(tmem_s + grp * 16, hi);
+      tmem_st_32x16(tmem_s + 32 + grp * 16, lo);
+      l_run += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      // P (and any rescaled O) is in tensor memory: let the MMA warp issue P_j V_j
+      tmem_wait_st();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full + b);
+    }
+    if (alive && n_tiles > 0) alive = warp_wait(pv_done + (n_tiles - 1) % 3, static_cast<uint32_t>((n_tiles - 1) / 3) & 1, 40);
+    // the row sum over both halves (exchange buffer of the parity the last tile did not use)
+    const int last = (n_tiles & 1) * 2;
+    xchg[(last + grp) * AT_BQ + r_local] = l_run;
+    if (!alive) xchg_abort[quad] = 1;
+    pair_sync();
+    if (xchg_abort[quad]) alive = false;
+    if (alive) {
+      l_run += xchg[(last + (grp ^ 1)) * AT_BQ + r_local];
+      tcgen05_fence_after();
+      const int keys_seen = p.causal ? min(p.seq, row + 1) : p.seq;
+      const float inv = (1.0f + p.acc_comp * static_cast<float>(3 * ((keys_seen + 15) / 16))) / (l_run + 1e-9f);  // LayerOps.hpp:1076
+      const int bb = bhi / p.heads, h = bhi - bb * p.heads;
+      const long long o_off = (static_cast<long long>(bb) * p.seq + row) * p.embed + h * AT_HD + grp * 32;
+      uint32_t v[32];
+      tmem_ld_32x32_nowait(tmem_o + lane_base + grp * 32, v);  // every lane of the warp takes part in the load
+      tmem_wait_ld();
+      if (row < p.seq) {
+        if (p.out != nullptr) {
+          float* o = p.out + o_off;
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<float4*>(o + c) = make_float4(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv,
+                                                           __uint_as_float(v[c + 2]) * inv, __uint_as_float(v[c + 3]) * inv);
+        }
+        if (p.out_split != nullptr) {
+          __nv_bfloat16* oh = p.out_split + o_off;
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint32_t h4[4], l4[4];
+#pragma unroll
+            for (int e = 0; e < 8; e += 2)
+              split_pair(__uint_as_float(v[c + e]) * inv, __uint_as_float(v[c + e + 1]) * inv, p.f16, h4[e >> 1], l4[e >> 1]);
+            *reinterpret_cast<uint4*>(oh + c) = make_uint4(h4[0], h4[1], h4[2], h4[3]);
+            if (p.planes == 2) *reinterpret_cast<uint4*>(oh + p.plane_stride + c) = make_uint4(l4[0], l4[1], l4[2], l4[3]);
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, AT_TMEM_COLS);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -517,6 +847,9 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   // (MIMIR_B200_ATTN_V_MN=0 goes back to the transposed V^T planes: decoder configuration 22.0 instead of 21.0 ms)
   static const bool v_mn_env = [] { const char* e = getenv("MIMIR_B200_ATTN_V_MN"); return !(e && e[0] == '0'); }();
   const bool v_mn = v_mn_env && qkv_planes != nullptr;
+  // the deeper-pipelined form (P in tensor memory) takes the all-planes case; MIMIR_B200_ATTN_V2=0 keeps the first form
+  static const bool v2_env = [] { const char* e = getenv("MIMIR_B200_ATTN_V2"); return !(e && e[0] == '0'); }();
+  const bool v2 = v2_env && v_mn;
   if (qkv_planes != nullptr) {
     // Q and K are read where the projection GEMM left them; only V needs turning around
     if (!v_mn) {
@@ -524,7 +857,7 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
       MB_CUDA(cudaGetLastError());
     }
     MB_TRY(make_map_qkv5(&mq, qkv_planes, batch, seq, embed, AT_BQ));
-    MB_TRY(make_map_qkv5(&mk, qkv_planes, batch, seq, embed, 2 * AT_BK));
+    MB_TRY(make_map_qkv5(&mk, qkv_planes, batch, seq, embed, v2 ? AT_BK : 2 * AT_BK));
   } else {
     attn_prep_kernel<<<pgrid, 256, 0, st>>>(qkv, qp, kp, vt, seq, seqp, embed, heads, bh, plane_format() == PLANES_F16);
     MB_CUDA(cudaGetLastError());
@@ -552,6 +885,23 @@ int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, i
   p.acc_comp = comp ? 1.5e-8f : 0.0f;
   p.f16 = plane_format() == PLANES_F16 ? 1 : 0;
   dim3 grid((seq + AT_BQ - 1) / AT_BQ, bh);
+  p.head_chunk = 1;
+  if (v2) {
+    // heads whose K and V planes (seq x 64 x 2 planes x 2 bytes, twice) fill about 48 MB of L2
+    const long long per_head = static_cast<long long>(seq) * AT_HD * 2 * 2 * 2;
+    long long hc = (48ll << 20) / per_head;
+    p.head_chunk = static_cast<int>(hc < 1 ? 1 : (hc > bh ? bh : hc));
+    grid = dim3(static_cast<unsigned>(((seq + AT_BQ - 1) / AT_BQ) * bh));
+    static PerDeviceOnce attr2_once;
+    MB_TRY(attr2_once.run([&]() -> int {
+      MB_CUDA(cudaFuncSetAttribute(flash_attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM));
+      return MIMIR_B200_OK;
+    }));
+    flash_attn_tc2_kernel<<<grid, A2_THREADS, A2_SMEM, st>>>(mq, mk, mv, p);
+    MB_CUDA(cudaGetLastError());
+    count_launch(1);
+    return MIMIR_B200_OK;
+  }
   flash_attn_tc_kernel<<<grid, AT_THREADS, AT_SMEM, st>>>(mq, mk, mv, p);
   MB_CUDA(cudaGetLastError());
   count_launch(2);

@@ -382,6 +382,41 @@ int mimir_b200_init(int device, size_t hbm_budget_bytes) {
   return MIMIR_B200_OK;
 }
 
+/* Selection by environment, with the reference's own conventions for its accelerator switches (Model.cpp:704-722, used at
+ * Model.cpp:5110-5112): a flag is true for any non-empty value other than "0", an integer that does not parse keeps its
+ * default.  Default off. */
+int mimir_b200_env_selection(int* enabled, int* device, size_t* hbm_budget_bytes) {
+  auto flag = [](const char* name) {
+    const char* v = getenv(name);
+    if (!v || v[0] == '\0') return false;
+    return !(v[0] == '0' && v[1] == '\0');
+  };
+  auto integer = [](const char* name, long long dflt) {
+    const char* v = getenv(name);
+    if (!v || v[0] == '\0') return dflt;
+    char* end = nullptr;
+    const long long r = strtoll(v, &end, 10);
+    return (end == v) ? dflt : r;
+  };
+  if (enabled) *enabled = flag("MIMIR_B200") ? 1 : 0;
+  const long long dev = integer("MIMIR_B200_DEVICE", 0);
+  if (device) *device = static_cast<int>(dev < 0 ? 0 : dev);
+  const long long mb = integer("MIMIR_B200_HBM_BUDGET_MB", 0);
+  if (hbm_budget_bytes) *hbm_budget_bytes = mb > 0 ? static_cast<size_t>(mb) << 20 : 0;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_init_from_env(int* enabled) {
+  int on = 0, dev = 0;
+  size_t budget = 0;
+  mimir_b200_env_selection(&on, &dev, &budget);
+  if (enabled) *enabled = 0;
+  if (!on) return MIMIR_B200_OK;  // not selected: nothing is touched, the caller stays on its own path
+  MB_TRY(mimir_b200_init(dev, budget));
+  if (enabled) *enabled = 1;
+  return MIMIR_B200_OK;
+}
+
 int mimir_b200_current_device(int* device) {
   if (!device) return fail(MIMIR_B200_E_INVALID, "current_device: null argument");
   MB_REQUIRE_INIT();

@@ -139,6 +139,9 @@ struct GemmArgs {
 };
 // y = act(a · wᵀ + bias) (+ residual); tcgen05 / TMEM / TMA.
 int launch_gemm(const GemmArgs& g, cudaStream_t st);
+// Runs the bounded-wait give-up path on purpose: one CTA waits `limit_ns` on a barrier nobody arrives on, sets the device
+// error word (site 90) and returns after freeing its tensor memory.
+int launch_wait_timeout_selftest(unsigned long long limit_ns, cudaStream_t st);
 // fp32 weight-streaming kernel for very small m (<= 16 rows): y[m,n] = x[m,k] · w[n,k]ᵀ + bias.
 int launch_skinny_linear(const float* x, const float* w, const float* bias, float* y, int m, int k, int n,
                          int activation, float* scratch, size_t scratch_bytes, cudaStream_t st, const float* residual = nullptr);

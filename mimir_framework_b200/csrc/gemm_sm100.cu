@@ -38,11 +38,18 @@ constexpr int NUM_THREADS = 320;  // 10 warps: TMA, MMA, 8 epilogue
 constexpr int EPI_WARPS = 8;
 constexpr float ACC_TRUNC_PER_MMA = 1.5e-8f;  // mean relative loss of the fp32 accumulator per tcgen05.mma (truncating adds)
 
-// GELU in the reference's tanh form (LayerOps.hpp:556-568); the constant is
-// sqrt(2.0f / 3.14159265359f) evaluated in fp32.
+// GELU in the reference's tanh form (LayerOps.hpp:556-568), x * 0.5 * (1 + tanh(u)) with u = c * (x + 0.044715 x^3) and
+// c = sqrt(2.0f / 3.14159265359f) evaluated in fp32.  0.5 * (1 + tanh(u)) is the logistic function of 2u, so the value is
+// x / (1 + exp(-2u)): one ex2 and one reciprocal on the special-function unit instead of tanhf's ~30 instructions (the
+// epilogue of a K = 768 layer has only ~12 000 cycles per 128 x 256 tile for 32 768 of these), and without the
+// cancellation of 1 + tanh(u) for negative arguments.  Error: a few ulp of the result (ex2.approx 2 ulp, rcp.approx 1 ulp).
 __device__ __forceinline__ float gelu_ref(float x) {
   const float c = 0.7978845608f;
-  return x * (0.5f * (1.0f + tanhf(c * (x + 0.044715f * x * x * x))));
+  const float u = c * (x + 0.044715f * x * x * x);
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(u * -2.885390082f));  // exp(-2u) = 2^(-2u log2 e)
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
 }
 __device__ __forceinline__ float apply_act(float v, int act) {
   switch (act) {
@@ -82,6 +89,10 @@ struct GemmParams {
   // shrinks every result by a little less than 2^-26 of its value per instruction (see launch_gemm_t).
   float acc_scale;
   int f16;        // operand planes (and out_split) hold IEEE half instead of bfloat16
+  // The operand ring: a stage holds only the planes the precision mode uses (32 KB with two activation planes and one
+  // weight plane at BK = 32), so the same shared memory gives six stages instead of four - the K = 768 layers were
+  // starved of operands with four (the MMA thread spent a quarter of every tile waiting on a full barrier).
+  int stages, stage_bytes;
   int* err_word;
 };
 
@@ -103,23 +114,25 @@ struct SmemLayout {
   static constexpr int kWTile = BN * BK * 2;
 };
 
-template <int BK, int STAGES>
+constexpr int MAX_STAGES = 8;
+
+template <int BK, int RING_BYTES>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_o, const GemmParams p) {
   constexpr int SWZ = BK * 2;                      // bytes per smem row = swizzle span
   constexpr int A_TILE = BM * BK * 2;
   constexpr int W_TILE = BN * BK * 2;
-  constexpr int STAGE_BYTES = 2 * A_TILE + 2 * W_TILE;  // room for both planes of both operands
+  const int STAGES = p.stages, STAGE_BYTES = p.stage_bytes;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // behind the stages: one staging tile per epilogue warp (32 x 33 floats for the swapped form's transposition, or a
   // dense 128-byte-swizzled 32 x 32 tile, 1024-byte aligned, as the source of a TMA store), then the barriers
-  uint8_t* epi_tiles = smem + STAGES * STAGE_BYTES;
+  uint8_t* epi_tiles = smem + RING_BYTES;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_tiles + EPI_WARPS * 32 * 33 * 4);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* empty_bar = full_bar + MAX_STAGES;
+  uint64_t* acc_full = empty_bar + MAX_STAGES;
   uint64_t* acc_empty = acc_full + NUM_ACC;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + NUM_ACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -178,14 +191,14 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int pl = 0; pl < p.a_planes; ++pl)
               tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
             for (int pl = 0; pl < p.w_planes; ++pl)
-              tma_load_3d(sbase + 2 * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * BN, pl);
+              tma_load_3d(sbase + m_planes * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * BN, pl);
           } else {
             // 128 weight rows into the M-side tiles, 256 activation rows (tile tn) into the N-side tiles
             a_row += tn * BN - tm * BM;
             for (int pl = 0; pl < p.w_planes; ++pl)
               tma_load_3d(sbase + pl * A_TILE, &map_w, &full_bar[stage], kb * BK, tm * BM, pl);
             for (int pl = 0; pl < p.a_planes; ++pl)
-              tma_load_3d(sbase + 2 * A_TILE + pl * W_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
+              tma_load_3d(sbase + m_planes * A_TILE + pl * W_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -214,7 +227,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.err_word, 4)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sw = sa + 2 * A_TILE;
+          const uint32_t sw = sa + m_planes * A_TILE;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint32_t koff = k * UMMA_K * 2;  // bytes along K inside the swizzled row
@@ -592,7 +605,7 @@ int env_int(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 
-template <int BK, int STAGES>
+template <int BK>
 int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   const int kp = round_up(g.k, 64);
   const bool conv = g.conv_ks > 0;
@@ -656,10 +669,18 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
     p.acc_scale = (comp ? 1.0f + ACC_TRUNC_PER_MMA * static_cast<float>(ksteps * products) : 1.0f) / g.w_scale;
   }
   p.f16 = plane_format() == PLANES_F16 ? 1 : 0;
-  constexpr int STAGE_BYTES = 2 * BM * BK * 2 + 2 * BN * BK * 2;
-  constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_WARPS * 32 * 33 * 4 /*swapped-epilogue tiles*/;
+  constexpr int RING_BYTES = 196608;  // 192 KB of operand stages, cut into as many stages as the planes in use allow
+  constexpr int SMEM = RING_BYTES + 1024 /*align slack*/ + 512 /*barriers*/ + EPI_WARPS * 32 * 33 * 4 /*swapped-epilogue tiles*/;
   static_assert(SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
-  auto kern = gemm_tn_bf16split_kernel<BK, STAGES>;
+  {
+    const int m_pl = swap ? g.w_planes : g.a_planes, n_pl = swap ? g.a_planes : g.w_planes;
+    p.stage_bytes = m_pl * BM * BK * 2 + n_pl * BN * BK * 2;
+    p.stages = RING_BYTES / p.stage_bytes;
+    if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+    const int want = env_int("MIMIR_B200_GEMM_STAGES", 0);
+    if (want >= 2 && want < p.stages) p.stages = want;
+  }
+  auto kern = gemm_tn_bf16split_kernel<BK, RING_BYTES>;
   static PerDeviceOnce attr_once;
   MB_TRY(attr_once.run([&]() -> int {
     MB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
@@ -759,19 +780,71 @@ int launch_split_transposed(const float* src, __nv_bfloat16* dst, int k, int n, 
   return MIMIR_B200_OK;
 }
 
+namespace {
+// One CTA that waits on an mbarrier nobody arrives on, with the kernels' own bounded wait and a caller-given limit:
+// the wait runs out, the error word and the abort flag are set, the roles leave, the TMEM columns are freed and the
+// kernel returns - the give-up path of the tensor-core kernels, run on purpose.
+__global__ void __launch_bounds__(64) wait_timeout_selftest_kernel(unsigned long long limit_ns, int* err_word) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, 32);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (warp == 0) {
+    // the same whole-warp form the epilogue and softmax warps use: lane 0 waits, the verdict is made warp-uniform
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait_limit(&bar, 0, &abort_flag, err_word, 90, limit_ns, 0xF) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    (void)ok;
+  } else if (lane == 0) {
+    // a second role that sees the first one's abort flag and leaves (or runs out itself)
+    mbar_wait_limit(&bar, 0, &abort_flag, err_word, 91, 4 * limit_ns, 0xF);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 32);
+  }
+}
+}  // namespace
+
+int launch_wait_timeout_selftest(unsigned long long limit_ns, cudaStream_t st) {
+  if (limit_ns == 0 || limit_ns > 100000000ull) return fail(MIMIR_B200_E_INVALID, "selftest: the limit must be within (0, 100 ms]");
+  wait_timeout_selftest_kernel<<<1, 64, 0, st>>>(limit_ns, ctx().dev_error_word);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
 int launch_gemm(const GemmArgs& g, cudaStream_t st) {
   if (g.m <= 0 || g.n <= 0 || g.k <= 0) return fail(MIMIR_B200_E_INVALID, "gemm: empty dimension");
   if (!g.a || !g.w) return fail(MIMIR_B200_E_INVALID, "gemm: null operand");
   if (!g.out_f32 && !g.out_split) return fail(MIMIR_B200_E_INVALID, "gemm: no output");
   if (g.residual && !g.out_f32) return fail(MIMIR_B200_E_INVALID, "gemm: residual needs the fp32 output stride");
-  // BK = 32 keeps four 48 KB stages in flight, BK = 64 two 96 KB stages.
+  // K block per stage.  With at most three planes in play (one of the operands single-plane) a 64-wide block still leaves
+  // three 64 KB stages, halves the barrier round trips per MMA and uses 128-byte swizzle rows: measured on the decoder's
+  // K = 768 layers 0.77 -> 0.90 of the sustained cuBLAS rate.  With four planes (both operands split) 64-wide blocks would
+  // leave two 96 KB stages, which measured slower than four 48 KB stages of 32.
   if (g.conv_ks > 0) {
     if (g.conv_c <= 0 || g.conv_c % 32 != 0 || g.k != g.conv_ks * g.conv_ks * g.conv_c || g.out_split || !g.out_f32)
       return fail(MIMIR_B200_E_INVALID, "gemm: bad shifted-convolution arguments");
   }
-  const int bk = env_int("MIMIR_B200_GEMM_BK", 32);
-  if (bk == 64 && (g.conv_ks == 0 || g.conv_c % 64 == 0)) return launch_gemm_t<64, 2>(g, st);
-  return launch_gemm_t<32, 4>(g, st);
+  const int bk = env_int("MIMIR_B200_GEMM_BK", (g.a_planes + g.w_planes <= 3) ? 64 : 32);
+  if (bk == 64 && (g.conv_ks == 0 || g.conv_c % 64 == 0)) return launch_gemm_t<64>(g, st);
+  return launch_gemm_t<32>(g, st);
 }
 
 }  // namespace mb

@@ -227,6 +227,7 @@ struct MimirB200Model {
   // flow through copy-in / compute / copy-out streams over two arena buffers.
   int pipeline = 1;
   int planned_micro = 0;
+  bool out_in_input_slot = false;  // the output tensor shares bytes with a graph input's slot in the current plan
   uint8_t* arena2 = nullptr;
   cudaStream_t s_h2d = nullptr, s_comp = nullptr, s_d2h = nullptr;
   std::vector<cudaEvent_t> ev_h2d, ev_comp, ev_d2h;
@@ -984,7 +985,23 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     }
     for (int v = 0; v < nt; ++v) {
       const TensorV& t = m->tensors[v];
+      // In a pipelined plan the slots of the graph inputs are never handed on: the copy-in of micro-batch c + 2 may then
+      // run while micro-batch c is still being copied out of the same arena buffer (nothing else lives in an input slot).
+      if (m->pipeline > 1 && t.producer == -1) continue;
       if (t.alias_of < 0 && t.producer != -2 && t.last == li) drop(v);
+    }
+  }
+  // Does the output share bytes with a graph input's slot (possible only in un-pipelined plans, or when the graph returns
+  // one of its inputs)?  The pipelined forward then orders copy-in after the copy-out two micro-batches back.
+  m->out_in_input_slot = false;
+  {
+    const TensorV& ot = m->tensors[out_root];
+    const size_t o0 = ot.off_f32, o1 = o0 + static_cast<size_t>(ot.n) * batch * 4;
+    for (int v = 0; v < nt; ++v) {
+      const TensorV& t = m->tensors[v];
+      if (t.producer != -1 || t.alias_of >= 0) continue;
+      const size_t i0 = t.off_f32, i1 = i0 + static_cast<size_t>(t.n) * (t.broadcast_input ? 1 : batch) * 4;
+      if (v == out_root || (i0 < o1 && o0 < i1)) m->out_in_input_slot = true;
     }
   }
   m->flops = flops;
@@ -1602,10 +1619,10 @@ int mimir_b200_model_forward(MimirB200ModelHandle m, const MimirNamedInput* inpu
   for (int c = 0; c < P; ++c) {
     uint8_t* arena = bufs[c & 1];
     if (c >= 2) {
-      // the planner may hand a graph input's slot to the output tensor once the input's last consumer has run,
-      // so the copy-in of micro-batch c must also wait for the copy-out of micro-batch c - 2 from the same buffer
+      // buffer c & 1: its inputs may be overwritten once micro-batch c - 2 has been computed; where the output shares
+      // bytes with an input slot (see plan) the copy-in must also wait for the copy-out of micro-batch c - 2
       MB_CUDA(cudaStreamWaitEvent(m->s_h2d, m->ev_comp[c - 2], 0));
-      MB_CUDA(cudaStreamWaitEvent(m->s_h2d, m->ev_d2h[c - 2], 0));
+      if (m->out_in_input_slot) MB_CUDA(cudaStreamWaitEvent(m->s_h2d, m->ev_d2h[c - 2], 0));
     }
     for (int i = 0; i < n_inputs; ++i) {
       const TensorV& t = m->tensors[vs[i]];
@@ -1786,6 +1803,11 @@ int mimir_b200_check_device(void* stream) {
 }
 
 // Live timing of the contraction kernel with CUDA events on the launching stream.
+int mimir_b200_selftest_wait_timeout(unsigned long long limit_ns, void* stream) {
+  if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
+  return launch_wait_timeout_selftest(limit_ns, static_cast<cudaStream_t>(stream));
+}
+
 int mimir_b200_profile_gemm(int enable) {
   if (!ctx().initialised) return fail(MIMIR_B200_E_NOT_INIT, "mimir_b200_init has not been called");
   ctx().prof_gemm = enable != 0;

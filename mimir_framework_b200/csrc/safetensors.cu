@@ -238,10 +238,11 @@ int mimir_b200_model_load_safetensors(MimirB200ModelHandle m, const char* path, 
 
   int n_layers = 0;
   MB_TRY(mimir_b200_model_num_layers(m, &n_layers));
-  Staging stg;
-  MB_TRY(stg.init());
-  int loaded = 0;
-  unsigned long long total = 0;
+  // Pass 1: check every tensor that will be loaded - dtype, element count without overflow, offsets against the
+  // file size without wrap-around - before any layer's device weights are touched.  The header is untrusted input.
+  struct Job { int layer; uint64_t begin, elems; bool f32; std::string name; };
+  std::vector<Job> jobs;
+  const uint64_t data_bytes = fsize - data0;
   for (int li = 0; li < n_layers; ++li) {
     const char* lname = nullptr;
     uint64_t params = 0;
@@ -256,20 +257,35 @@ int mimir_b200_model_load_safetensors(MimirB200ModelHandle m, const char* path, 
     const StTensor& t = it->second;
     const bool f32 = t.dtype == "F32", bf16 = t.dtype == "BF16";
     if (!f32 && !bf16) return fail(MIMIR_B200_E_UNSUPPORTED, "load_safetensors: %s has dtype %s (F32 or BF16 expected)", tname.c_str(), t.dtype.c_str());
-    const uint64_t elems = t.elements(), esz = f32 ? 4 : 2;
-    if (elems != params)
-      return fail(MIMIR_B200_E_INVALID, "Size mismatch for %s: expected %llu got %llu", tname.c_str(), static_cast<unsigned long long>(elems),
-                  static_cast<unsigned long long>(params));
-    if (t.end - t.begin != elems * esz || data0 + t.end > fsize)
+    uint64_t elems = 1;
+    bool overflow = false;
+    for (uint64_t d : t.shape) {
+      if (d != 0 && elems > (uint64_t(1) << 62) / d) { overflow = true; break; }
+      elems *= d;
+    }
+    const uint64_t esz = f32 ? 4 : 2;
+    if (overflow || elems != params)
+      return fail(MIMIR_B200_E_INVALID, "Size mismatch for %s: expected %llu got %llu", tname.c_str(), static_cast<unsigned long long>(params),
+                  static_cast<unsigned long long>(overflow ? ~0ull : elems));
+    if (t.end < t.begin || t.end > data_bytes || t.end - t.begin != elems * esz)
       return fail(MIMIR_B200_E_INVALID, "load_safetensors: data_offsets of %s do not match its shape or the file size", tname.c_str());
+    jobs.push_back(Job{li, t.begin, elems, f32, tname});
+  }
+  // Pass 2: stream the checked tensors into the layers' device blocks.
+  Staging stg;
+  MB_TRY(stg.init());
+  int loaded = 0;
+  unsigned long long total = 0;
+  for (const Job& jb : jobs) {
+    const uint64_t elems = jb.elems, esz = jb.f32 ? 4 : 2;
     float* dev = nullptr;
-    MB_TRY(mimir_b200_model_weights_device(m, li, params, &dev));
-    if (f32) {
-      MB_TRY(stream_to_device(file.f, data0 + t.begin, elems * 4, dev, stg, tname.c_str()));
+    MB_TRY(mimir_b200_model_weights_device(m, jb.layer, elems, &dev));
+    if (jb.f32) {
+      MB_TRY(stream_to_device(file.f, data0 + jb.begin, elems * 4, dev, stg, jb.name.c_str()));
     } else {
       void* tmp = nullptr;
       MB_TRY(dev_alloc(&tmp, elems * 2, "safetensors.bf16"));
-      int s = stream_to_device(file.f, data0 + t.begin, elems * 2, tmp, stg, tname.c_str());
+      int s = stream_to_device(file.f, data0 + jb.begin, elems * 2, tmp, stg, jb.name.c_str());
       if (s == MIMIR_B200_OK) {
         widen_bf16_kernel<<<static_cast<int>(std::min<uint64_t>((elems + 255) / 256, 148 * 16)), 256, 0, stg.st>>>(
             static_cast<const __nv_bfloat16*>(tmp), dev, static_cast<long long>(elems));

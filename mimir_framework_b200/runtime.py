@@ -35,6 +35,8 @@ _SIGS = {
     "mimir_b200_guard_reset": [],
     "mimir_b200_guard_state": [_P, _P, _P, _P],
     "mimir_b200_current_device": [_P],
+    "mimir_b200_env_selection": [_P, _P, _P],
+    "mimir_b200_init_from_env": [_P],
     "mimir_b200_shard_range": [C.c_longlong, C.c_int, C.c_int, _P, _P],
     "mimir_b200_replicas_create": [_P, C.c_int, C.c_size_t, _P, C.c_int, C.c_int, _P],
     "mimir_b200_replicas_destroy": [_P],
@@ -93,6 +95,7 @@ _SIGS = {
     "mimir_b200_argmax_rows_device": [_P, _P, C.c_longlong, C.c_int, _P],
     "mimir_b200_get_stats": [_P],
     "mimir_b200_check_device": [_P],
+    "mimir_b200_selftest_wait_timeout": [C.c_ulonglong, _P],
     "mimir_b200_profile_gemm": [C.c_int],
     "mimir_b200_profile_read": [_P, _P],
     "mimir_b200_dev_layernorm": [_P, _P, _P, _P, C.c_longlong, C.c_int, C.c_float, _P],

@@ -242,10 +242,12 @@ def test_pipelined_forward_equals_single_pass(backend):
     m.close()
 
 
-def test_pipelined_forward_output_in_an_input_slot(backend):
-    """A two-layer Linear graph whose output the planner puts into the (dead) input slot: with 8 micro-batches
-    of 8 MB each, the copy-in of micro-batch c and the copy-out of micro-batch c-2 use the same bytes of the
-    same arena buffer and must be ordered.  The result has to be bit-equal to the un-pipelined forward."""
+def test_pipelined_forward_keeps_copy_in_and_copy_out_apart(backend):
+    """8 micro-batches of 8 MB over two arena buffers.  (1) A two-layer Linear graph: un-pipelined, the planner puts the
+    output into the dead input slot; pipelined, input slots are never handed on, so that the copy-in of micro-batch c may
+    overlap the copy-out of micro-batch c-2 from the same buffer - results must be bit-equal.  (2) A graph that returns
+    its own input: there the output IS an input slot, the copy-in has to wait for the copy-out, and every micro-batch
+    must come back unchanged."""
     rows, k = 4096, 512   # 8 MB per micro-batch in and out
     P = 8
     descs = [make_desc("l0", "Linear", inputs=["x"], output="h", in_features=k, out_features=k, seq_len=rows, use_bias=1, params_count=k * k + k),
@@ -260,9 +262,12 @@ def test_pipelined_forward_output_in_an_input_slot(backend):
             m.upload_weights(i, w)
     m1.plan({"x": (rows * k, False)}, P)
     mp.plan({"x": (rows * k, False)}, P)
-    in_off, in_bytes = mp.tensor_slot("x")
-    out_off, out_bytes = mp.tensor_slot(None)
-    assert in_off < out_off + out_bytes and out_off < in_off + in_bytes, "the plan no longer reuses the input slot: pick another graph"
+
+    def overlap(m):
+        (i0, ib), (o0, ob) = m.tensor_slot("x"), m.tensor_slot(None)
+        return i0 < o0 + ob and o0 < i0 + ib
+    assert overlap(m1), "un-pipelined: the output was expected in the dead input slot"
+    assert not overlap(mp), "pipelined: input slots must stay the inputs' own"
     want = m1.forward({"x": (x.ravel(), False)}, P, rows * k)
     for _ in range(3):
         got = mp.forward({"x": (x.ravel(), False)}, P, rows * k)
@@ -274,6 +279,14 @@ def test_pipelined_forward_output_in_an_input_slot(backend):
     assert_close(got.reshape(P, rows, k)[P - 1][sub], ref_rows, "pipelined two-layer stack, last micro-batch")
     m1.close()
     mp.close()
+    # (2) the output is the input
+    ident = [make_desc("keep", "Identity", inputs=["x"], output="x")]
+    mi = backend.GraphModel(ident, pipeline=P)
+    mi.plan({"x": (rows * k, False)}, P)
+    assert overlap(mi)
+    for _ in range(3):
+        assert np.array_equal(mi.forward({"x": (x.ravel(), False)}, P, rows * k).ravel(), x.ravel())
+    mi.close()
 
 
 def test_gpt_decoder_reduced(backend):

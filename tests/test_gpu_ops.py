@@ -353,3 +353,22 @@ def test_gemm_output_through_tma_stores():
                        cwd=os.path.dirname(os.path.dirname(here)))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert " passed" in r.stdout
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_device_usable(backend):
+    """The tensor-core kernels bound every mbarrier wait; when one runs out they set a device word, drain, free their
+    tensor memory and return.  Here that path runs on purpose: a one-block kernel waits 1 ms on a barrier that nothing
+    arrives on.  The host then reads E_TIMEOUT with the site of the wait, the word is cleared, and a GEMM straight
+    afterwards is correct - nothing faulted, nothing spun past its limit."""
+    lib = backend.lib()
+    backend.check(lib.mimir_b200_check_device(None))  # clean to start with
+    backend.check(lib.mimir_b200_selftest_wait_timeout(1_000_000, None))
+    status = lib.mimir_b200_check_device(None)
+    assert status == abi.E_TIMEOUT
+    assert "site 90" in lib.mimir_b200_last_error().decode()
+    assert lib.mimir_b200_check_device(None) == abi.OK  # reading it cleared it
+    r = np.random.default_rng(0)
+    x, w = r.standard_normal((200, 96)).astype(np.float32), r.standard_normal((64, 96)).astype(np.float32)
+    assert_close(backend.linear_forward(x.ravel(), w.ravel(), None, 200, 96, 64), port.linear(x.ravel(), w.ravel(), None, 200, 96, 64), "GEMM after a timed-out wait")
+    assert lib.mimir_b200_selftest_wait_timeout(0, None) == abi.E_INVALID
+    assert lib.mimir_b200_selftest_wait_timeout(10**12, None) == abi.E_INVALID

@@ -108,3 +108,47 @@ def test_error_behaviour_follows_the_reference_reader(backend, tmp_path):
     with pytest.raises(backend.MimirB200Error, match="cannot open"):
         m.load_safetensors(str(tmp_path / "nope.safetensors"))
     m.close()
+
+
+def test_untrusted_header_values_are_checked_before_any_weight_is_touched(backend, tmp_path):
+    """Offsets that wrap around, a shape whose product overflows, and a second tensor that is bad: every one is refused,
+    and the model still computes with the weights it had before the failed load (nothing is half-loaded)."""
+    import json as js
+    from mimir_framework_b200.abi import make_desc
+    descs = [make_desc("a", "Linear", inputs=["x"], output="h", in_features=4, out_features=4, use_bias=0, params_count=16),
+             make_desc("b", "Linear", inputs=["h"], output="x", in_features=4, out_features=2, use_bias=0, params_count=8)]
+    r = np.random.default_rng(0)
+    wa, wb = r.standard_normal(16).astype(np.float32), r.standard_normal(8).astype(np.float32)
+    m = backend.GraphModel(descs)
+    m.upload_weights(0, wa)
+    m.upload_weights(1, wb)
+    x = r.standard_normal(4).astype(np.float32)
+    before = forward(backend, m, {"x": x}, 2)
+
+    def write_raw(path, header: dict, payload: bytes):
+        h = js.dumps(header).encode()
+        with open(path, "wb") as fh:
+            fh.write(struct.pack("<Q", len(h)) + h + payload)
+    path = str(tmp_path / "bad.safetensors")
+    big = 2 ** 64 - 128
+    cases = [
+        # begin / end close to 2^64 with the right difference: their sum with the data start wraps
+        ({"a/weights": {"dtype": "F32", "shape": [16], "data_offsets": [big, big + 64]},
+          "b/weights": {"dtype": "F32", "shape": [8], "data_offsets": [0, 32]}}, "data_offsets of a/weights"),
+        # a shape whose element product overflows 64 bits
+        ({"a/weights": {"dtype": "F32", "shape": [2 ** 40, 2 ** 40], "data_offsets": [0, 64]},
+          "b/weights": {"dtype": "F32", "shape": [8], "data_offsets": [64, 96]}}, "Size mismatch for a/weights"),
+        # the first tensor is fine, the second runs past the end of the file
+        ({"a/weights": {"dtype": "F32", "shape": [16], "data_offsets": [0, 64]},
+          "b/weights": {"dtype": "F32", "shape": [8], "data_offsets": [64, 96]}}, "data_offsets of b/weights"),
+    ]
+    for header, msg in cases:
+        write_raw(path, header, np.full(16, 7.0, np.float32).tobytes())  # 64 bytes of payload only
+        with pytest.raises(backend.MimirB200Error, match=msg):
+            m.load_safetensors(path)
+        assert np.array_equal(forward(backend, m, {"x": x}, 2), before), "a failed load changed the model"
+    # "expected" is the layer's parameter count, "got" the tensor's element count
+    write_safetensors(path, {"a/weights": ("F32", np.ones(6, np.float32), [6]), "b/weights": ("F32", np.ones(8, np.float32), [8])})
+    with pytest.raises(backend.MimirB200Error, match="expected 16 got 6"):
+        m.load_safetensors(path)
+    m.close()

@@ -118,3 +118,37 @@ def test_replicas_without_a_gpu_fail_loudly_and_name_the_rank():
     assert "replica 0 (device 0)" in msg and "no CUDA device" in msg
     dup = (C.c_int * 2)(3, 3)
     assert rt.lib().mimir_b200_replicas_create(dup, 2, 0, C.addressof(descs), 1, abi.PREC_BF16X2, C.byref(h)) == abi.E_INVALID
+
+
+def _selection():
+    on, dev, budget = C.c_int(-1), C.c_int(-1), C.c_size_t(1)
+    assert rt.lib().mimir_b200_env_selection(C.byref(on), C.byref(dev), C.byref(budget)) == abi.OK
+    return on.value, dev.value, budget.value
+
+
+def test_selection_by_environment_follows_the_reference_flag_conventions(monkeypatch):
+    """Model.cpp:704-722: a flag is true for any non-empty value other than "0"; an integer that does not parse keeps
+    its default.  Default off."""
+    for k in ("MIMIR_B200", "MIMIR_B200_DEVICE", "MIMIR_B200_HBM_BUDGET_MB"):
+        monkeypatch.delenv(k, raising=False)
+    assert _selection() == (0, 0, 0)
+    for v, want in (("1", 1), ("0", 0), ("", 0), ("yes", 1), ("00", 1)):
+        monkeypatch.setenv("MIMIR_B200", v)
+        assert _selection()[0] == want, v
+    monkeypatch.setenv("MIMIR_B200_DEVICE", "3")
+    monkeypatch.setenv("MIMIR_B200_HBM_BUDGET_MB", "2048")
+    assert _selection() == (1, 3, 2048 << 20)
+    monkeypatch.setenv("MIMIR_B200_DEVICE", "abc")
+    monkeypatch.setenv("MIMIR_B200_HBM_BUDGET_MB", "-5")
+    assert _selection() == (1, 0, 0)
+    # not selected: init_from_env touches nothing and reports "off"
+    monkeypatch.setenv("MIMIR_B200", "0")
+    on = C.c_int(7)
+    assert rt.lib().mimir_b200_init_from_env(C.byref(on)) == abi.OK and on.value == 0
+
+
+@pytest.mark.skipif(_has_gpu(), reason="checks the no-GPU failure mode")
+def test_selected_without_a_gpu_is_an_error_not_a_fallback(monkeypatch):
+    monkeypatch.setenv("MIMIR_B200", "1")
+    on = C.c_int(7)
+    assert rt.lib().mimir_b200_init_from_env(C.byref(on)) == abi.E_CUDA and on.value == 0
