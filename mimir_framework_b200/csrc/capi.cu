@@ -278,6 +278,8 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
   const int ow = (e.w + 2 * e.pad - e.ks) / e.stride + 1;
   if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: empty output");
   const int ohw = oh * ow, k = e.ic * e.ks * e.ks;
+  if (e.w_f32 != nullptr && e.pre_groups == 0 && conv_small_oc_supported(e.oc, e.ks, e.stride, e.pad, e.h, e.w, e.batch, e.activation))
+    return launch_conv_small_oc(e.x, e.w_f32, e.y, e.residual, e.batch, e.ic, e.oc, e.h, e.w, e.ks, e.pad, e.activation, st);
   if (conv_uses_shifted(e.ic, e.ks, e.stride, e.pad)) {
     // NCHW fp32 -> zero-padded NHWC planes, then one GEMM that walks the taps as shifted row offsets
     const long long rows = static_cast<long long>(e.batch) * (e.h + 2 * e.pad) * (e.w + 2 * e.pad);
@@ -571,6 +573,7 @@ int mimir_b200_conv2d(const float* x, const float* w, float* y, int batch, int i
   MB_TRY(t.out(&e.y, static_cast<size_t>(batch) * oc * oh * ow, "conv.y"));
   void* ws;
   MB_TRY(t.alloc(&ws, split_bytes(oc, ic * k * k, 2), "conv.wsplit"));
+  e.w_f32 = wdv;
   MB_TRY(weight_plane_scale(wdv, static_cast<size_t>(oc) * ic * k * k, nullptr, &e.w_scale));
   if (conv_uses_shifted(ic, k, stride, pad)) MB_TRY(launch_conv_weight_planes(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic, k, 2, nullptr, e.w_scale));
   else MB_TRY(launch_split(wdv, static_cast<__nv_bfloat16*>(ws), oc, ic * k * k, 2, nullptr, e.w_scale));

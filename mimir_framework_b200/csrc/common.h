@@ -236,6 +236,11 @@ int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int bat
 // OIHW fp32 -> planes [planes][oc][round_up(ks*ks*ic, 64)] with K ordered (kh, kw, ic)
 int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st, float scale = 1.0f);
 
+// direct fp32 convolution for layers with at most 8 output channels (stride 1, "same" padding): x NCHW, w OIHW, y NCHW
+bool conv_small_oc_supported(int oc, int ks, int stride, int pad, int h, int wd, int batch, int act);
+int launch_conv_small_oc(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int oc, int h, int wd, int ks,
+                         int pad, int act, cudaStream_t st);
+
 // spatial.cu -----------------------------------------------------------------------------------
 int launch_depthwise_conv2d(const float* x, const float* w, const float* bias, float* y, int batch, int ch, int h, int wd, int k,
                             int stride, int pad, int64_t w_count, cudaStream_t st);

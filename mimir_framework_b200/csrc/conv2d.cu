@@ -208,3 +208,165 @@ int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic
 }
 
 }  // namespace mb
+
+// ---------------------------------------------------------------------------------------------
+// Convolutions with very few output channels (an RGB head: 128 -> 3): on the tensor core a 128-row weight tile would be
+// all padding, and the layer is bound by reading its input once.  Direct fp32 convolution instead: a CTA owns a
+// 128 x 8 pixel tile of one sample, stages the input tile (with its halo) for four channels at a time in shared memory,
+// and every thread accumulates all output channels of its four pixels in the reference's order (ic, kh, kw ascending,
+// Model.cpp:5005-5032) with FMAs.  No operand planes, no layout pass.
+// ---------------------------------------------------------------------------------------------
+namespace mb {
+namespace {
+
+constexpr int SO_TX = 32, SO_TY = 8, SO_PX = 4, SO_CC = 4, SO_MAX_OC = 8, SO_MAX_KS = 7;
+
+// A thread owns SO_PX consecutive pixels of one row, so that every weight it reads from shared memory (a broadcast
+// load) feeds SO_PX FMAs and every input row segment is read once for all taps of that row.  The input tile and the
+// weights of the next four channels arrive through cp.async (4-byte copies, zero stores for the padding ring) into the
+// other half of a double buffer while the current four channels are being consumed: one barrier per chunk, no registers
+// spent on staging.
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src)
+               : "memory");
+}
+
+template <int OC, int KS>
+__global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                       float* __restrict__ y, const float* __restrict__ residual, int ic,
+                                                                       int h, int wd, int act) {
+  constexpr int PAD = KS / 2, TW = SO_TX * SO_PX + KS - 1, TH = SO_TY + KS - 1, KK = KS * KS, SEG = SO_PX + KS - 1;
+  // a pad word after every SO_PX pixels: the lanes of a warp then read their segments SO_PX + 1 words apart (no bank conflicts)
+  constexpr int TWP = TW + TW / SO_PX + 1;
+  constexpr int TILE = SO_CC * TH * TWP, WCH = SO_CC * KK * OC;
+  extern __shared__ float so_smem[];  // [2][TILE] input tiles, then [2][WCH] weights as [c][tap][o]
+  const int n = blockIdx.z;
+  const int x0 = blockIdx.x * (SO_TX * SO_PX), y0 = blockIdx.y * SO_TY;
+  const int tx = threadIdx.x & (SO_TX - 1), ty = threadIdx.x / SO_TX;
+  const float* xs = x + static_cast<long long>(n) * ic * h * wd;
+  float acc[OC][SO_PX];
+#pragma unroll
+  for (int o = 0; o < OC; ++o)
+#pragma unroll
+    for (int q = 0; q < SO_PX; ++q) acc[o][q] = 0.0f;
+  auto fetch = [&](int c0, int buf) {
+    const int cc = min(SO_CC, ic - c0);
+    float* tile = so_smem + buf * TILE;
+    for (int i = threadIdx.x; i < SO_CC * TH * TW; i += SO_TX * SO_TY) {
+      const int c = i / (TH * TW), r = i - c * (TH * TW);
+      const int yy = r / TW, xx = r - yy * TW;
+      const int gy = y0 + yy - PAD, gx = x0 + xx - PAD;
+      float* dst = tile + (c * TH + yy) * TWP + xx + xx / SO_PX;
+      if (c < cc && gy >= 0 && gy < h && gx >= 0 && gx < wd) cp_async4(dst, xs + (static_cast<long long>(c0 + c) * h + gy) * wd + gx);
+      else *dst = 0.0f;
+    }
+    float* wch = so_smem + 2 * TILE + buf * WCH;
+    for (int i = threadIdx.x; i < OC * cc * KK; i += SO_TX * SO_TY) {
+      const int o = i / (cc * KK), r = i - o * cc * KK;  // OIHW: (c, kh, kw) of the chunk are contiguous per o
+      cp_async4(wch + (r / KK * KK + r % KK) * OC + o, w + (static_cast<long long>(o) * ic + c0) * KK + r);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(0, 0);
+  int cur = 0;
+  for (int c0 = 0; c0 < ic; c0 += SO_CC, cur ^= 1) {
+    const int cc = min(SO_CC, ic - c0);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // this chunk has landed for every thread, and everyone is done with the other buffer
+    if (c0 + SO_CC < ic) fetch(c0 + SO_CC, cur ^ 1);
+    const float* tile = so_smem + cur * TILE;
+    const float* wch = so_smem + 2 * TILE + cur * WCH;
+    for (int c = 0; c < cc; ++c) {  // (ic, kh, kw) ascending: the reference's accumulation order (Model.cpp:5005-5032)
+#pragma unroll
+      for (int kh = 0; kh < KS; ++kh) {
+        float seg[SEG];
+        const float* row = tile + (c * TH + ty + kh) * TWP + tx * (SO_PX + 1);
+#pragma unroll
+        for (int i = 0; i < SEG; ++i) seg[i] = row[i + i / SO_PX];
+#pragma unroll
+        for (int kw = 0; kw < KS; ++kw) {
+#pragma unroll
+          for (int o = 0; o < OC; ++o) {
+            const float wv = wch[(c * KK + kh * KS + kw) * OC + o];
+#pragma unroll
+            for (int q = 0; q < SO_PX; ++q) acc[o][q] = fmaf(seg[kw + q], wv, acc[o][q]);
+          }
+        }
+      }
+    }
+  }
+  const int gy = y0 + ty;
+  if (gy < h) {
+#pragma unroll
+    for (int o = 0; o < OC; ++o) {
+#pragma unroll
+      for (int q = 0; q < SO_PX; ++q) {
+        const int gx = x0 + tx * SO_PX + q;
+        if (gx < wd) {
+          const long long oi = ((static_cast<long long>(n) * OC + o) * h + gy) * wd + gx;
+          float v = acc[o][q];
+          if (act == MIMIR_B200_ELT_RELU) v = fmaxf(v, 0.0f);
+          else if (act == MIMIR_B200_ELT_SILU) v = v * (1.0f / (1.0f + expf(-v)));
+          if (residual != nullptr) v += __ldg(residual + oi);
+          y[oi] = v;
+        }
+      }
+    }
+  }
+}
+
+template <int OC, int KS>
+int launch_small_oc_k(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int h, int wd, int act,
+                      cudaStream_t st) {
+  constexpr int TW = SO_TX * SO_PX + KS - 1, TH = SO_TY + KS - 1, TWP = TW + TW / SO_PX + 1;
+  constexpr int SMEM = (2 * SO_CC * TH * TWP + 2 * SO_CC * KS * KS * OC) * static_cast<int>(sizeof(float));
+  static PerDeviceOnce attr_once;
+  MB_TRY(attr_once.run([&]() -> int {
+    MB_CUDA(cudaFuncSetAttribute(conv_small_oc_kernel<OC, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    return MIMIR_B200_OK;
+  }));
+  dim3 grid((wd + SO_TX * SO_PX - 1) / (SO_TX * SO_PX), (h + SO_TY - 1) / SO_TY, batch);
+  conv_small_oc_kernel<OC, KS><<<grid, SO_TX * SO_TY, SMEM, st>>>(x, w, y, residual, ic, h, wd, act);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
+}
+
+template <int OC>
+int launch_small_oc_t(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int h, int wd, int ks, int pad,
+                      int act, cudaStream_t st) {
+  (void)pad;
+  switch (ks) {
+    case 1: return launch_small_oc_k<OC, 1>(x, w, y, residual, batch, ic, h, wd, act, st);
+    case 3: return launch_small_oc_k<OC, 3>(x, w, y, residual, batch, ic, h, wd, act, st);
+    case 5: return launch_small_oc_k<OC, 5>(x, w, y, residual, batch, ic, h, wd, act, st);
+    case 7: return launch_small_oc_k<OC, 7>(x, w, y, residual, batch, ic, h, wd, act, st);
+    default: return fail(MIMIR_B200_E_INVALID, "conv_small_oc: kernel size %d", ks);
+  }
+}
+
+}  // namespace
+
+bool conv_small_oc_supported(int oc, int ks, int stride, int pad, int h, int wd, int batch, int act) {
+  static const bool off = [] { const char* e = getenv("MIMIR_B200_CONV_SMALL_OC"); return e && e[0] == '0'; }();
+  return !off && oc >= 1 && oc <= SO_MAX_OC && stride == 1 && ks >= 1 && ks <= SO_MAX_KS && (ks & 1) == 1 && pad == ks / 2 && batch <= 65535 &&
+         (h + SO_TY - 1) / SO_TY <= 65535 && (act == -1 || act == MIMIR_B200_ELT_RELU || act == MIMIR_B200_ELT_SILU) &&
+         static_cast<long long>(h) * wd >= 4096;  // small images keep the tensor-core path (too few tiles to fill the SMs)
+}
+
+int launch_conv_small_oc(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int oc, int h, int wd, int ks,
+                         int pad, int act, cudaStream_t st) {
+  switch (oc) {
+    case 1: return launch_small_oc_t<1>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    case 2: return launch_small_oc_t<2>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    case 3: return launch_small_oc_t<3>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    case 4: return launch_small_oc_t<4>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    case 5: return launch_small_oc_t<5>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    case 6: return launch_small_oc_t<6>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    case 7: return launch_small_oc_t<7>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    case 8: return launch_small_oc_t<8>(x, w, y, residual, batch, ic, h, wd, ks, pad, act, st);
+    default: return fail(MIMIR_B200_E_INVALID, "conv_small_oc: %d output channels", oc);
+  }
+}
+
+}  // namespace mb

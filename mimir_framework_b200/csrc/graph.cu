@@ -1102,7 +1102,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
         e.batch = batch; e.ic = d.in_channels; e.oc = d.out_channels; e.h = L.h; e.w = L.w; e.ks = d.kernel;
         e.stride = d.stride; e.pad = d.padding; e.precision = m->precision;
         e.activation = d.activation ? MIMIR_B200_ELT_RELU : L.fused_act;
-        e.x = f32p(L.in_v[0]); e.w_split = L.w_split; e.w_scale = L.w_scale; e.y = f32p(L.out_v); e.ws = ws;
+        e.x = f32p(L.in_v[0]); e.w_split = L.w_split; e.w_f32 = L.w_f32; e.w_scale = L.w_scale; e.y = f32p(L.out_v); e.ws = ws;
         if (L.res_v >= 0) e.residual = f32p(L.res_v);
         if (L.pre_norm >= 0) {
           const LayerRT& G = m->layers[L.pre_norm];

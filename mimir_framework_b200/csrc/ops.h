@@ -85,6 +85,7 @@ struct ConvExec {
   int activation = -1;                         // MIMIR_B200_ELT_RELU when the layer asks for it
   const float* x = nullptr;                    // NCHW
   const __nv_bfloat16* w_split = nullptr;      // planes [oc][round_up(ic*ks*ks, 64)]
+  const float* w_f32 = nullptr;                // OIHW fp32 (the direct kernel for a handful of output channels)
   float w_scale = 1.0f;                        // the planes hold W * w_scale
   const float* residual = nullptr;             // NCHW, same shape as y
   float* y = nullptr;

@@ -156,6 +156,9 @@ def test_attention_identity_weights(backend):
     (2, 64, 3, 40, 40, 3, 1, 1, 0),   # few output channels: operands swapped (channels on the TMEM lanes)
     (2, 256, 128, 24, 24, 3, 1, 1, 1),  # 128 channels with a long K: swapped too, ReLU
     (3, 32, 20, 30, 26, 5, 1, 2, 0),  # swapped, 5x5 taps, ragged pixel tiles
+    (2, 40, 3, 70, 66, 3, 1, 1, 0),   # an RGB head on a large image: direct fp32 kernel, ragged tiles, channel tail (40 = 5 x 8)
+    (1, 19, 8, 64, 64, 5, 1, 2, 1),   # direct kernel: eight output channels, 5x5, channel count not a multiple of 8, ReLU
+    (2, 12, 1, 96, 50, 1, 1, 0, 0),   # direct kernel: one output channel, 1x1
 ])
 def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
     r = rng(ic * oc + h)
