@@ -219,84 +219,129 @@ int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic
 namespace mb {
 namespace {
 
-constexpr int SO_TX = 32, SO_TY = 8, SO_PX = 4, SO_CC = 4, SO_MAX_OC = 8, SO_MAX_KS = 7;
+constexpr int SO_TX = 32, SO_TY = 8, SO_PX = 4, SO_CC = 2, SO_NBUF = 2, SO_MAX_OC = 8, SO_MAX_KS = 7;
+constexpr int so_rows(int oc) { return oc <= 4 ? 2 : 1; }  // output rows per thread: as many as the accumulators leave registers for
 
-// A thread owns SO_PX consecutive pixels of one row, so that every weight it reads from shared memory (a broadcast
-// load) feeds SO_PX FMAs and every input row segment is read once for all taps of that row.  The input tile and the
-// weights of the next four channels arrive through cp.async (4-byte copies, zero stores for the padding ring) into the
-// other half of a double buffer while the current four channels are being consumed: one barrier per chunk, no registers
-// spent on staging.
+// A thread owns SO_PX consecutive pixels of R consecutive rows.  Every input row segment it reads from shared memory
+// feeds all taps of up to R output rows, and the weights of one (channel, kernel row) come as broadcast 16-byte loads,
+// so the FMA pipe and not the shared-memory pipe sets the pace.  The input tile and the weights of the next SO_CC
+// channels arrive through cp.async (4-byte copies, plain zero stores for the padding ring) into the next slot of a
+// ring of SO_NBUF buffers while the current channels are being consumed: one barrier per chunk, no registers spent on staging.
+// Each output element accumulates over (ic, kh, kw) ascending: the reference's order (Model.cpp:5005-5032).
 __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src)
                : "memory");
 }
 
-template <int OC, int KS>
+template <int KS, int R>
+struct SmallOcGeom {
+  static constexpr int PAD = KS / 2, TW = SO_TX * SO_PX + KS - 1, TH = SO_TY * R + KS - 1, SEG = SO_PX + KS - 1;
+  // a pad word after every SO_PX pixels: the lanes of a warp then read their segments SO_PX + 1 words apart (no bank conflicts)
+  static constexpr int TWP = TW + TW / SO_PX + 1;
+  static constexpr int TILE = SO_CC * TH * TWP, WOFF = (SO_NBUF * TILE + 3) & ~3;
+};
+
+template <int OC, int KS, int R>
 __global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                                        float* __restrict__ y, const float* __restrict__ residual, int ic,
                                                                        int h, int wd, int act) {
-  constexpr int PAD = KS / 2, TW = SO_TX * SO_PX + KS - 1, TH = SO_TY + KS - 1, KK = KS * KS, SEG = SO_PX + KS - 1;
-  // a pad word after every SO_PX pixels: the lanes of a warp then read their segments SO_PX + 1 words apart (no bank conflicts)
-  constexpr int TWP = TW + TW / SO_PX + 1;
-  constexpr int TILE = SO_CC * TH * TWP, WCH = SO_CC * KK * OC;
-  extern __shared__ float so_smem[];  // [2][TILE] input tiles, then [2][WCH] weights as [c][tap][o]
+  using G = SmallOcGeom<KS, R>;
+  constexpr int PAD = G::PAD, TW = G::TW, TH = G::TH, TWP = G::TWP, TILE = G::TILE, SEG = G::SEG, KK = KS * KS;
+  constexpr int WROW = (KS * OC + 3) & ~3;  // the weights of one (channel, kernel row) as [kw][o], padded to whole float4s
+  constexpr int WCH = SO_CC * KS * WROW;
+  extern __shared__ __align__(16) float so_smem[];  // [SO_NBUF][TILE] input tiles, then (16-byte aligned) [SO_NBUF][WCH] weights
   const int n = blockIdx.z;
-  const int x0 = blockIdx.x * (SO_TX * SO_PX), y0 = blockIdx.y * SO_TY;
+  const int x0 = blockIdx.x * (SO_TX * SO_PX), y0 = blockIdx.y * (SO_TY * R);
   const int tx = threadIdx.x & (SO_TX - 1), ty = threadIdx.x / SO_TX;
   const float* xs = x + static_cast<long long>(n) * ic * h * wd;
-  float acc[OC][SO_PX];
+  float acc[OC][R][SO_PX];
 #pragma unroll
   for (int o = 0; o < OC; ++o)
 #pragma unroll
-    for (int q = 0; q < SO_PX; ++q) acc[o][q] = 0.0f;
+    for (int j = 0; j < R; ++j)
+#pragma unroll
+      for (int q = 0; q < SO_PX; ++q) acc[o][j][q] = 0.0f;
+  for (int i = threadIdx.x; i < SO_NBUF * WCH; i += SO_TX * SO_TY) so_smem[G::WOFF + i] = 0.0f;  // the float4 padding is read, never used
+  __syncthreads();
+  // a lane copies the same columns of every tile row: their offsets and bounds once per thread
+  constexpr int NX = (TW + SO_TX - 1) / SO_TX;
+  int xsrc[NX], xdst[NX];  // xsrc < 0: outside the image (or past the tile): a zero is stored, or nothing
+#pragma unroll
+  for (int k = 0; k < NX; ++k) {
+    const int xx = tx + k * SO_TX, gx = x0 - PAD + xx;
+    xdst[k] = xx < TW ? xx + xx / SO_PX : -1;
+    xsrc[k] = (xx < TW && gx >= 0 && gx < wd) ? gx : -1;
+  }
   auto fetch = [&](int c0, int buf) {
     const int cc = min(SO_CC, ic - c0);
     float* tile = so_smem + buf * TILE;
-    for (int i = threadIdx.x; i < SO_CC * TH * TW; i += SO_TX * SO_TY) {
-      const int c = i / (TH * TW), r = i - c * (TH * TW);
-      const int yy = r / TW, xx = r - yy * TW;
-      const int gy = y0 + yy - PAD, gx = x0 + xx - PAD;
-      float* dst = tile + (c * TH + yy) * TWP + xx + xx / SO_PX;
-      if (c < cc && gy >= 0 && gy < h && gx >= 0 && gx < wd) cp_async4(dst, xs + (static_cast<long long>(c0 + c) * h + gy) * wd + gx);
-      else *dst = 0.0f;
+    for (int row = ty; row < SO_CC * TH; row += SO_TY) {  // one warp per tile row
+      const int c = row / TH, yy = row - c * TH, gy = y0 + yy - PAD;
+      const bool row_ok = c < cc && gy >= 0 && gy < h;
+      const float* src = xs + (static_cast<long long>(c0 + c) * h + gy) * wd;
+      float* dst = tile + row * TWP;
+#pragma unroll
+      for (int k = 0; k < NX; ++k) {
+        if (xdst[k] < 0) continue;
+        if (row_ok && xsrc[k] >= 0) cp_async4(dst + xdst[k], src + xsrc[k]);
+        else dst[xdst[k]] = 0.0f;
+      }
     }
-    float* wch = so_smem + 2 * TILE + buf * WCH;
+    float* wch = so_smem + G::WOFF + buf * WCH;
     for (int i = threadIdx.x; i < OC * cc * KK; i += SO_TX * SO_TY) {
       const int o = i / (cc * KK), r = i - o * cc * KK;  // OIHW: (c, kh, kw) of the chunk are contiguous per o
-      cp_async4(wch + (r / KK * KK + r % KK) * OC + o, w + (static_cast<long long>(o) * ic + c0) * KK + r);
+      const int c = r / KK, t = r - c * KK, kh = t / KS, kw = t - kh * KS;
+      cp_async4(wch + (c * KS + kh) * WROW + kw * OC + o, w + (static_cast<long long>(o) * ic + c0) * KK + r);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  fetch(0, 0);
-  int cur = 0;
-  for (int c0 = 0; c0 < ic; c0 += SO_CC, cur ^= 1) {
-    const int cc = min(SO_CC, ic - c0);
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();  // this chunk has landed for every thread, and everyone is done with the other buffer
-    if (c0 + SO_CC < ic) fetch(c0 + SO_CC, cur ^ 1);
-    const float* tile = so_smem + cur * TILE;
-    const float* wch = so_smem + 2 * TILE + cur * WCH;
-    for (int c = 0; c < cc; ++c) {  // (ic, kh, kw) ascending: the reference's accumulation order (Model.cpp:5005-5032)
+  // SO_NBUF - 1 chunks in flight; one commit per iteration (an empty group past the end) keeps the wait count uniform
 #pragma unroll
-      for (int kh = 0; kh < KS; ++kh) {
+  for (int b = 0; b < SO_NBUF - 1; ++b) {
+    if (b * SO_CC < ic) fetch(b * SO_CC, b);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  int cur = 0;
+  for (int c0 = 0; c0 < ic; c0 += SO_CC, cur = cur + 1 == SO_NBUF ? 0 : cur + 1) {
+    const int cc = min(SO_CC, ic - c0);
+    asm volatile("cp.async.wait_group %0;" ::"n"(SO_NBUF - 2) : "memory");
+    __syncthreads();  // this chunk has landed for every thread, and everyone is done with the buffer refilled next
+    if (c0 + (SO_NBUF - 1) * SO_CC < ic) fetch(c0 + (SO_NBUF - 1) * SO_CC, cur == 0 ? SO_NBUF - 1 : cur - 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    const float* tile = so_smem + cur * TILE;
+    const float* wch = so_smem + G::WOFF + cur * WCH;
+    for (int c = 0; c < cc; ++c) {
+#pragma unroll
+      for (int r = 0; r < R + KS - 1; ++r) {  // input rows ascending = kernel rows ascending for every output row
         float seg[SEG];
-        const float* row = tile + (c * TH + ty + kh) * TWP + tx * (SO_PX + 1);
+        const float* row = tile + (c * TH + ty * R + r) * TWP + tx * (SO_PX + 1);
 #pragma unroll
         for (int i = 0; i < SEG; ++i) seg[i] = row[i + i / SO_PX];
 #pragma unroll
-        for (int kw = 0; kw < KS; ++kw) {
+        for (int j = 0; j < R; ++j) {
+          const int kh = r - j;
+          if (kh < 0 || kh >= KS) continue;
+          float wv[WROW];
+          const float4* w4 = reinterpret_cast<const float4*>(wch + (c * KS + kh) * WROW);
 #pragma unroll
-          for (int o = 0; o < OC; ++o) {
-            const float wv = wch[(c * KK + kh * KS + kw) * OC + o];
-#pragma unroll
-            for (int q = 0; q < SO_PX; ++q) acc[o][q] = fmaf(seg[kw + q], wv, acc[o][q]);
+          for (int v = 0; v < WROW / 4; ++v) {
+            const float4 t = w4[v];
+            wv[4 * v] = t.x, wv[4 * v + 1] = t.y, wv[4 * v + 2] = t.z, wv[4 * v + 3] = t.w;
           }
+#pragma unroll
+          for (int kw = 0; kw < KS; ++kw)
+#pragma unroll
+            for (int o = 0; o < OC; ++o)
+#pragma unroll
+              for (int q = 0; q < SO_PX; ++q) acc[o][j][q] = fmaf(seg[kw + q], wv[kw * OC + o], acc[o][j][q]);
         }
       }
     }
   }
-  const int gy = y0 + ty;
-  if (gy < h) {
+#pragma unroll
+  for (int j = 0; j < R; ++j) {
+    const int gy = y0 + ty * R + j;
+    if (gy >= h) continue;
 #pragma unroll
     for (int o = 0; o < OC; ++o) {
 #pragma unroll
@@ -304,7 +349,7 @@ __global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const floa
         const int gx = x0 + tx * SO_PX + q;
         if (gx < wd) {
           const long long oi = ((static_cast<long long>(n) * OC + o) * h + gy) * wd + gx;
-          float v = acc[o][q];
+          float v = acc[o][j][q];
           if (act == MIMIR_B200_ELT_RELU) v = fmaxf(v, 0.0f);
           else if (act == MIMIR_B200_ELT_SILU) v = v * (1.0f / (1.0f + expf(-v)));
           if (residual != nullptr) v += __ldg(residual + oi);
@@ -318,15 +363,16 @@ __global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const floa
 template <int OC, int KS>
 int launch_small_oc_k(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int h, int wd, int act,
                       cudaStream_t st) {
-  constexpr int TW = SO_TX * SO_PX + KS - 1, TH = SO_TY + KS - 1, TWP = TW + TW / SO_PX + 1;
-  constexpr int SMEM = (2 * SO_CC * TH * TWP + 2 * SO_CC * KS * KS * OC) * static_cast<int>(sizeof(float));
+  constexpr int R = so_rows(OC);
+  using G = SmallOcGeom<KS, R>;
+  constexpr int SMEM = (G::WOFF + SO_NBUF * SO_CC * KS * ((KS * OC + 3) & ~3)) * static_cast<int>(sizeof(float));
   static PerDeviceOnce attr_once;
   MB_TRY(attr_once.run([&]() -> int {
-    MB_CUDA(cudaFuncSetAttribute(conv_small_oc_kernel<OC, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(conv_small_oc_kernel<OC, KS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     return MIMIR_B200_OK;
   }));
-  dim3 grid((wd + SO_TX * SO_PX - 1) / (SO_TX * SO_PX), (h + SO_TY - 1) / SO_TY, batch);
-  conv_small_oc_kernel<OC, KS><<<grid, SO_TX * SO_TY, SMEM, st>>>(x, w, y, residual, ic, h, wd, act);
+  dim3 grid((wd + SO_TX * SO_PX - 1) / (SO_TX * SO_PX), (h + SO_TY * R - 1) / (SO_TY * R), batch);
+  conv_small_oc_kernel<OC, KS, R><<<grid, SO_TX * SO_TY, SMEM, st>>>(x, w, y, residual, ic, h, wd, act);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
