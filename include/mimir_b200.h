@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define MIMIR_B200_ABI_VERSION 2
+#define MIMIR_B200_ABI_VERSION 3
 #define MIMIR_B200_MAX_INPUTS 8
 #define MIMIR_B200_MAX_DIMS 8
 #define MIMIR_B200_MAX_SPLITS 16
@@ -69,7 +69,8 @@ typedef enum MimirB200Eltwise {
   MIMIR_B200_ELT_HARD_SIGMOID = 10,/* clamp((x + 3) / 6, 0, 1) (LayerOpsExt.hpp:73-82) */
   MIMIR_B200_ELT_HARD_SWISH = 11,  /* x hard_sigmoid(x) (LayerOpsExt.hpp:87-99) */
   MIMIR_B200_ELT_SUBTRACT = 12,    /* equal sizes (LayerOpsExt.hpp:105-122) */
-  MIMIR_B200_ELT_DIVIDE = 13       /* equal sizes, |divisor| < 1e-8 replaced by +-1e-8 (LayerOpsExt.hpp:127-148) */
+  MIMIR_B200_ELT_DIVIDE = 13,      /* equal sizes, |divisor| < 1e-8 replaced by +-1e-8 (LayerOpsExt.hpp:127-148) */
+  MIMIR_B200_ELT_ELU = 14          /* x >= 0 ? x : alpha (exp x - 1) (Model::elu_inplace, Model.hpp:505-509; static family only) */
 } MimirB200Eltwise;
 
 /* ---------------------------------------------------------------------------------------------
@@ -232,6 +233,22 @@ int mimir_b200_batchnorm_inference(const float* x, const float* w, long long n_w
 int mimir_b200_batchnorm_running(const float* x, const float* gamma, const float* beta, const float* running_mean,
                                  const float* running_var, float* y, int batch, int channels, long long spatial,
                                  float eps);
+/* BatchNorm with batch statistics, the training branch of Model::computeBatchNorm / Normalization::batch_norm
+ * (Layers.hpp:932-970): per channel the mean and the biased variance over the batch and the spatial positions, then
+ * y = (x - mean) * (1 / sqrt(var + eps)) * gamma[c] + beta[c].  The running statistics are neither read nor updated
+ * (the reference does not update them either). */
+int mimir_b200_batchnorm_batchstats(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels,
+                                    long long spatial, float eps);
+/* Conv::conv2d behind Model::computeConv2D (Layers.hpp:611-722, Model.cpp:3880-3888): CHW input, OIHW weights, optional
+ * bias (NULL: none) added after the sum, stride, zero padding and dilation; out = (in + 2p - d (k - 1) - 1) / s + 1.
+ * fp32 FMAs over (ic, kh, kw) ascending. */
+int mimir_b200_conv2d_dilated(const float* x, const float* w, const float* bias, float* y, int batch, int in_c, int out_c,
+                              int in_h, int in_w, int kernel, int stride, int padding, int dilation);
+/* Conv::conv_transpose2d behind Model::computeConvTranspose2D (Layers.hpp:775-818, Model.cpp:4214-4221): the scatter form
+ * y[oc][ih s + kh - p][iw s + kw - p] += x[ic][ih][iw] * w[oc][ic][kh][kw] on top of the bias; out = (in - 1) s - 2p + k.
+ * Computed as a gather that visits the contributions of one output in the reference's order (ic, ih, iw ascending). */
+int mimir_b200_conv_transpose2d_scatter(const float* x, const float* w, const float* bias, float* y, int batch, int in_c,
+                                        int out_c, int in_h, int in_w, int kernel, int stride, int padding);
 /* Attention core on separate, already projected Q / K / V, each [batch*seq][d_model] with the heads side by side
  * (Model::computeAttention, scalar branch, Model.cpp:4223-4289): softmax(Q_h K_h^T / sqrt(head_dim)) V_h per head,
  * no mask, no projections. */
@@ -275,6 +292,11 @@ typedef struct MimirLayerDesc {
   int32_t n_splits;                          /* Split: number of entries of split_sizes (Model.cpp:5802-5815) */
   int32_t split_sizes[MIMIR_B200_MAX_SPLITS];
   int32_t num_chunks;                        /* Chunk (Model.cpp:5817-5832) */
+  /* --- ABI version 3: PatchEmbed and Bilinear ------------------------------------------------- */
+  int32_t seq_text, num_patches, patch_dim;  /* PatchEmbed: text tokens (without the time token), patches, flattened patch size
+                                                (Layers.hpp:181-183, Model.cpp:5203-5243) */
+  int32_t target_dim0;                       /* Bilinear: target_shape[0] (0 when the vector is empty), the output width used
+                                                when embed_dim <= 0 (Model.cpp:5256) */
 } MimirLayerDesc;
 
 typedef struct MimirNamedInput {

@@ -94,6 +94,10 @@ inline MimirLayerDesc describe(const Layer& L) {
     d.n_splits = -1;  // more pieces than the descriptor carries: model_create refuses the layer
   }
   d.num_chunks = L.num_chunks;
+  d.seq_text = L.seq_text;
+  d.num_patches = L.num_patches;
+  d.patch_dim = L.patch_dim;
+  d.target_dim0 = L.target_shape.empty() ? 0 : L.target_shape[0];
   return d;
 }
 
@@ -155,6 +159,10 @@ inline void apply(const MimirLayerDesc& d, Layer& L) {
   if (d.stride_w > 0 && d.stride_w != d.stride) L.stride_w = d.stride_w;
   if (d.n_splits > 0) L.split_sizes.assign(d.split_sizes, d.split_sizes + d.n_splits);
   L.num_chunks = d.num_chunks;
+  L.seq_text = d.seq_text;
+  L.num_patches = d.num_patches;
+  L.patch_dim = d.patch_dim;
+  if (d.target_dim0 > 0) L.target_shape.assign(1, d.target_dim0);
 }
 
 }  // namespace mimir_b200

@@ -9,12 +9,10 @@
 // ignored.  Errors surface as std::runtime_error carrying mimir_b200_last_error(), which is how the
 // reference reports shape errors (RuntimeAllocator.hpp:344-358).  mimir_b200_init must have been called.
 //
-// Covered: computeLinear, computeMaxPool2D, computeAvgPool2D, computeActivation (relu, leaky_relu, tanh,
-// sigmoid, gelu, softmax), computeLayerNorm, computeBatchNorm (inference), computeAttention.  Not covered,
-// because their arithmetic differs from the layer ops this backend implements: computeConv2D /
-// computeConvTranspose2D (Conv::conv2d adds a bias and takes a dilation; Conv::conv_transpose2d is the
-// scatter form, Layers.hpp:611-830), computeBatchNorm with training = true, activation "elu".  Calling
-// those here throws.
+// Covered: computeConv2D (bias, dilation), computeLinear, computeMaxPool2D, computeAvgPool2D, computeActivation
+// (relu, leaky_relu, tanh, sigmoid, gelu, softmax, elu), computeBatchNorm (running or batch statistics),
+// computeLayerNorm, computeConvTranspose2D (the scatter form), computeAttention.  An activation name the reference
+// does not know leaves the data untouched there (Model.cpp:4026-4064) and here.
 #pragma once
 
 #include <algorithm>
@@ -97,7 +95,8 @@ inline void computeActivation(std::vector<float>& data, const std::string& activ
   else if (activation_type == "tanh") op = MIMIR_B200_ELT_TANH;
   else if (activation_type == "sigmoid") op = MIMIR_B200_ELT_SIGMOID;
   else if (activation_type == "gelu") op = MIMIR_B200_ELT_GELU;
-  else throw std::runtime_error("computeActivation: '" + activation_type + "' is not available on the B200 backend");
+  else if (activation_type == "elu") op = MIMIR_B200_ELT_ELU;  // Model::elu_inplace, Model.hpp:505-509
+  else return;  // an unknown name is a no-op in the reference (Model.cpp:4026-4064)
   std::vector<float> out(data.size());
   check(mimir_b200_eltwise_alpha(op, data.data(), nullptr, out.data(), 1, n, 0, param));
   data.swap(out);
@@ -118,32 +117,56 @@ inline void computeLayerNorm(std::vector<float>& data, const std::vector<float>&
   data.swap(out);
 }
 
-[[noreturn]] inline void not_available(const char* what) {
-  throw std::runtime_error(std::string(what) + " has no B200 counterpart: its arithmetic differs from the layer ops "
-                                               "(see the header of mimir_b200_static_ops.hpp)");
-}
-inline void computeConv2D(const std::vector<float>&, std::vector<float>&, const LayerParams&, int, int, int, int, bool = true) {
-  not_available("computeConv2D");
-}
-inline void computeConvTranspose2D(const std::vector<float>&, std::vector<float>&, const LayerParams&, int, int, int, int,
-                                   bool = true) {
-  not_available("computeConvTranspose2D");
+// Model::computeConv2D -> Conv::conv2d (Model.cpp:3880-3888, Layers.hpp:611-722): CHW input, OIHW weights, optional bias,
+// stride, zero padding, dilation.  Follows the scalar branch (Layers.hpp:690-721).  An AVX2 build of the reference adds
+// every tap of the kernel-row remainder (all taps for kernels narrower than eight) to all eight lanes of its accumulator
+// before the horizontal sum (Layers.hpp:658-666, 670-678), so there each such tap counts eight times.
+inline void computeConv2D(const std::vector<float>& input, std::vector<float>& output, const LayerParams& params, int in_h, int in_w,
+                          int in_c, int out_c, bool /*use_hardware*/ = true) {
+  const int k = params.kernel_size, s = params.stride, p = params.padding, d = params.dilation;
+  if (in_h <= 0 || in_w <= 0 || in_c <= 0 || out_c <= 0 || k <= 0 || s <= 0 || d <= 0 ||
+      input.size() < static_cast<size_t>(in_c) * in_h * in_w || params.weights.size() < static_cast<size_t>(out_c) * in_c * k * k ||
+      (!params.bias.empty() && params.bias.size() < static_cast<size_t>(out_c)))
+    throw std::runtime_error("computeConv2D: input, weights or bias smaller than the stated dimensions");
+  const int oh = (in_h + 2 * p - d * (k - 1) - 1) / s + 1, ow = (in_w + 2 * p - d * (k - 1) - 1) / s + 1;
+  if (oh <= 0 || ow <= 0) throw std::runtime_error("computeConv2D: empty output");
+  output.assign(static_cast<size_t>(out_c) * oh * ow, 0.0f);
+  check(mimir_b200_conv2d_dilated(input.data(), params.weights.data(), params.bias.empty() ? nullptr : params.bias.data(), output.data(),
+                                  1, in_c, out_c, in_h, in_w, k, s, p, d));
 }
 
-// Model::computeBatchNorm (Model.cpp:4066-4148), in place, data [batch][channels][spatial].  Inference only: with
-// training = true the reference recomputes the statistics from the batch, which is outside the forward path.
+// Model::computeConvTranspose2D -> Conv::conv_transpose2d (Model.cpp:4214-4221, Layers.hpp:775-818): weights [out_c][in_c][k][k].
+inline void computeConvTranspose2D(const std::vector<float>& input, std::vector<float>& output, const LayerParams& params, int in_h,
+                                   int in_w, int in_c, int out_c, bool /*use_hardware*/ = true) {
+  const int k = params.kernel_size, s = params.stride, p = params.padding;
+  if (in_h <= 0 || in_w <= 0 || in_c <= 0 || out_c <= 0 || k <= 0 || s <= 0 ||
+      input.size() < static_cast<size_t>(in_c) * in_h * in_w || params.weights.size() < static_cast<size_t>(out_c) * in_c * k * k ||
+      (!params.bias.empty() && params.bias.size() < static_cast<size_t>(out_c)))
+    throw std::runtime_error("computeConvTranspose2D: input, weights or bias smaller than the stated dimensions");
+  const int oh = (in_h - 1) * s - 2 * p + k, ow = (in_w - 1) * s - 2 * p + k;
+  if (oh <= 0 || ow <= 0) throw std::runtime_error("computeConvTranspose2D: empty output");
+  output.assign(static_cast<size_t>(out_c) * oh * ow, 0.0f);
+  check(mimir_b200_conv_transpose2d_scatter(input.data(), params.weights.data(), params.bias.empty() ? nullptr : params.bias.data(),
+                                            output.data(), 1, in_c, out_c, in_h, in_w, k, s, p));
+}
+
+// Model::computeBatchNorm (Model.cpp:4066-4148), in place, data [batch][channels][spatial].  training = true takes the
+// mean and the biased variance of each channel from the batch itself (Layers.hpp:940-959); the running statistics are
+// not updated, as in the reference.
 inline void computeBatchNorm(std::vector<float>& data, const std::vector<float>& gamma, const std::vector<float>& beta,
                              const std::vector<float>& running_mean, const std::vector<float>& running_var, int batch_size,
                              int channels, int spatial_size, float eps = 1e-5f, bool training = false, bool /*use_hardware*/ = true) {
-  if (training) not_available("computeBatchNorm(training = true)");
   const size_t n = static_cast<size_t>(batch_size) * channels * spatial_size;
   const size_t c = static_cast<size_t>(channels);
   if (batch_size <= 0 || channels <= 0 || spatial_size <= 0 || data.size() < n || gamma.size() < c || beta.size() < c ||
       running_mean.size() < c || running_var.size() < c)
     throw std::runtime_error("computeBatchNorm: data or parameters smaller than batch x channels x spatial");
   std::vector<float> out(data.size());
-  check(mimir_b200_batchnorm_running(data.data(), gamma.data(), beta.data(), running_mean.data(), running_var.data(), out.data(),
-                                     batch_size, channels, spatial_size, eps));
+  if (training)
+    check(mimir_b200_batchnorm_batchstats(data.data(), gamma.data(), beta.data(), out.data(), batch_size, channels, spatial_size, eps));
+  else
+    check(mimir_b200_batchnorm_running(data.data(), gamma.data(), beta.data(), running_mean.data(), running_var.data(), out.data(),
+                                       batch_size, channels, spatial_size, eps));
   std::copy(out.begin(), out.begin() + static_cast<std::ptrdiff_t>(n), data.begin());
 }
 

@@ -18,7 +18,7 @@ STATUS_NAMES = ["OK", "E_INVALID", "E_UNSUPPORTED", "E_OOM_BUDGET", "E_CUDA", "E
 
 PREC_BF16X2, PREC_BF16W, PREC_BF16 = 0, 1, 2
 ELT_ADD, ELT_MULTIPLY, ELT_GELU, ELT_SILU, ELT_RELU, ELT_TANH, ELT_SIGMOID = range(7)
-ELT_LEAKY_RELU, ELT_SOFTPLUS, ELT_MISH, ELT_HARD_SIGMOID, ELT_HARD_SWISH, ELT_SUBTRACT, ELT_DIVIDE = range(7, 14)
+ELT_LEAKY_RELU, ELT_SOFTPLUS, ELT_MISH, ELT_HARD_SIGMOID, ELT_HARD_SWISH, ELT_SUBTRACT, ELT_DIVIDE, ELT_ELU = range(7, 15)
 
 
 class MimirLayerDesc(C.Structure):
@@ -68,6 +68,10 @@ class MimirLayerDesc(C.Structure):
         ("n_splits", C.c_int32),
         ("split_sizes", C.c_int32 * MAX_SPLITS),
         ("num_chunks", C.c_int32),
+        ("seq_text", C.c_int32),
+        ("num_patches", C.c_int32),
+        ("patch_dim", C.c_int32),
+        ("target_dim0", C.c_int32),
     ]
 
 
@@ -100,6 +104,7 @@ LAYER_DEFAULTS = dict(
     causal=0, out_h=0, out_w=0, scale_h=2, scale_w=2, activation=0,
     head_dim=64, leaky_relu_alpha=0.01, kernel_w=None, stride_w=None, padding_w=None,
     raw_kernel_h=0, raw_stride_h=1, raw_pad_h=0, raw_pad_w=0, num_chunks=2,
+    seq_text=0, num_patches=0, patch_dim=0, target_dim0=0,
 )
 _FLOAT_FIELDS = ("eps", "leaky_relu_alpha")
 

@@ -157,6 +157,63 @@ int mimir_b200_conv_transpose2d(const float* x, const float* w, float* y, int ba
   return finish_download(y, dy, ny);
 }
 
+int mimir_b200_conv2d_dilated(const float* x, const float* w, const float* bias, float* y, int batch, int in_c, int out_c, int in_h,
+                              int in_w, int kernel, int stride, int padding, int dilation) {
+  MB_REQUIRE_INIT();
+  if (!x || !w || !y || batch <= 0 || in_c <= 0 || out_c <= 0 || in_h <= 0 || in_w <= 0 || kernel <= 0 || stride <= 0 || padding < 0 ||
+      dilation <= 0)
+    return fail(MIMIR_B200_E_INVALID, "computeConv2D: bad arguments");
+  const int oh = (in_h + 2 * padding - dilation * (kernel - 1) - 1) / stride + 1;
+  const int ow = (in_w + 2 * padding - dilation * (kernel - 1) - 1) / stride + 1;
+  if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "computeConv2D: empty output");
+  Temps t;
+  const float *dx, *dw, *db = nullptr;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, static_cast<size_t>(batch) * in_c * in_h * in_w, "sconv.x"));
+  MB_TRY(t.upload(&dw, w, static_cast<size_t>(out_c) * in_c * kernel * kernel, "sconv.w"));
+  if (bias) MB_TRY(t.upload(&db, bias, static_cast<size_t>(out_c), "sconv.b"));
+  const size_t ny = static_cast<size_t>(batch) * out_c * oh * ow;
+  MB_TRY(t.out(&dy, ny, "sconv.y"));
+  MB_TRY(launch_conv2d_dilated(dx, dw, db, dy, batch, in_c, out_c, in_h, in_w, kernel, stride, padding, dilation, nullptr));
+  return finish_download(y, dy, ny);
+}
+
+int mimir_b200_conv_transpose2d_scatter(const float* x, const float* w, const float* bias, float* y, int batch, int in_c, int out_c,
+                                        int in_h, int in_w, int kernel, int stride, int padding) {
+  MB_REQUIRE_INIT();
+  if (!x || !w || !y || batch <= 0 || in_c <= 0 || out_c <= 0 || in_h <= 0 || in_w <= 0 || kernel <= 0 || stride <= 0 || padding < 0)
+    return fail(MIMIR_B200_E_INVALID, "computeConvTranspose2D: bad arguments");
+  const int oh = (in_h - 1) * stride - 2 * padding + kernel, ow = (in_w - 1) * stride - 2 * padding + kernel;
+  if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "computeConvTranspose2D: empty output");
+  Temps t;
+  const float *dx, *dw, *db = nullptr;
+  float* dy;
+  MB_TRY(t.upload(&dx, x, static_cast<size_t>(batch) * in_c * in_h * in_w, "sconvt.x"));
+  MB_TRY(t.upload(&dw, w, static_cast<size_t>(out_c) * in_c * kernel * kernel, "sconvt.w"));
+  if (bias) MB_TRY(t.upload(&db, bias, static_cast<size_t>(out_c), "sconvt.b"));
+  const size_t ny = static_cast<size_t>(batch) * out_c * oh * ow;
+  MB_TRY(t.out(&dy, ny, "sconvt.y"));
+  MB_TRY(launch_conv_transpose2d_scatter(dx, dw, db, dy, batch, in_c, out_c, in_h, in_w, kernel, stride, padding, nullptr));
+  return finish_download(y, dy, ny);
+}
+
+int mimir_b200_batchnorm_batchstats(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels,
+                                    long long spatial, float eps) {
+  MB_REQUIRE_INIT();
+  if (!x || !gamma || !beta || !y || batch <= 0 || channels <= 0 || spatial <= 0)
+    return fail(MIMIR_B200_E_INVALID, "computeBatchNorm: bad arguments");
+  Temps t;
+  const float *dx, *dg, *db;
+  float* dy;
+  const size_t n = static_cast<size_t>(batch) * channels * spatial;
+  MB_TRY(t.upload(&dx, x, n, "bnt.x"));
+  MB_TRY(t.upload(&dg, gamma, static_cast<size_t>(channels), "bnt.g"));
+  MB_TRY(t.upload(&db, beta, static_cast<size_t>(channels), "bnt.b"));
+  MB_TRY(t.out(&dy, n, "bnt.y"));
+  MB_TRY(launch_batchnorm_batchstats(dx, dg, db, dy, batch, channels, spatial, eps, nullptr));
+  return finish_download(y, dy, n);
+}
+
 int mimir_b200_pool2d(int is_max, const float* x, float* y, int batch, int channels, int h, int wd, int kh, int kw, int stride_h,
                       int stride_w, int pad_h, int pad_w) {
   MB_REQUIRE_INIT();

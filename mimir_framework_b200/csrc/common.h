@@ -248,6 +248,21 @@ int launch_conv1d(const float* x, const float* w, const float* bias, float* y, i
                   int pad, int64_t w_count, cudaStream_t st);
 int launch_conv_gather(const float* x, const float* w, float* y, int batch, int ic, int oc, int h, int wd, int oh, int ow, int k,
                        int stride, int pad, int relu, cudaStream_t st);
+// EmbeddingBag / PatchEmbed / Bilinear / RNN-GRU-LSTM (sequence.cu); every tensor is [batch][per-sample elements]
+int launch_embedding_bag(const float* ids, int64_t ids_ps, const float* offsets, int64_t off_ps, const float* table, float* y, int batch,
+                         int vocab, int dim, int padding_idx, cudaStream_t st);
+int launch_patch_embed(const float* x, const float* w, float* y, int batch, int d_model, int seq_text, int num_patches, int patch_dim,
+                       cudaStream_t st);
+int launch_bilinear(const float* x1, const float* x2, const float* w, const float* bias, float* y, int64_t rows, int in1, int in2,
+                    int out_f, cudaStream_t st);
+int launch_recurrent(int kind, const float* x, const float* w, float* y, int batch, int T, int I, int H, int use_bias, cudaStream_t st);
+// the static compute family (Model::computeConv2D / computeConvTranspose2D / computeBatchNorm with batch statistics)
+int launch_conv2d_dilated(const float* x, const float* w, const float* bias, float* y, int batch, int ic, int oc, int h, int wd, int k,
+                          int stride, int pad, int dil, cudaStream_t st);
+int launch_conv_transpose2d_scatter(const float* x, const float* w, const float* bias, float* y, int batch, int ic, int oc, int h, int wd,
+                                    int k, int stride, int pad, cudaStream_t st);
+int launch_batchnorm_batchstats(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels, long long spatial,
+                                float eps, cudaStream_t st);
 int launch_pool2d(int is_max, const float* x, float* y, int batch, int ch, int h, int wd, int kh, int kw, int sh, int sw, int ph, int pw,
                   cudaStream_t st);
 int launch_pad2d(int mode, const float* x, float* y, int batch, int ch, int h, int wd, int ph, int pw, cudaStream_t st);

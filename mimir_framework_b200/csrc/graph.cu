@@ -29,7 +29,7 @@ enum class LT {
   UpsampleNearest, Permute, Concat, Alias, TokenMeanPool, GlobalAvgPool,
   // the remaining switch cases
   CrossAttention, Split, DepthwiseConv2d, Conv1d, ConvTranspose2d, Pool2d, Pad2d, PixelShuffle, UpsampleBilinear, MatMul,
-  BatchMatMul, BatchNorm, InstanceNorm, Binary2, Transpose,
+  BatchMatMul, BatchNorm, InstanceNorm, Binary2, Transpose, EmbeddingBag, PatchEmbed, Bilinear, Recurrent,
   Unsupported
 };
 
@@ -79,6 +79,14 @@ TypeInfo classify(const std::string& t) {
   if (t == "MaxPool2d") return {LT::Pool2d, 1};
   if (t == "AvgPool2d") return {LT::Pool2d, 0};
   if (t == "AvgPool1d") return {LT::Pool2d, 2};  // one row per channel (LayerOpsExt.hpp:540-575)
+  // LayerOpsExt::maxpool1d_forward (LayerOpsExt.hpp:504-538); the reference's own switch has no case that calls it
+  if (t == "MaxPool1d") return {LT::Pool2d, 3};
+  if (t == "EmbeddingBag") return {LT::EmbeddingBag, -1};
+  if (t == "PatchEmbed") return {LT::PatchEmbed, -1};
+  if (t == "Bilinear") return {LT::Bilinear, -1};
+  if (t == "RNN") return {LT::Recurrent, 0};
+  if (t == "GRU") return {LT::Recurrent, 1};
+  if (t == "LSTM") return {LT::Recurrent, 2};
   if (t == "ZeroPad2d") return {LT::Pad2d, 0};
   if (t == "ReflectionPad2d") return {LT::Pad2d, 1};
   if (t == "ReplicationPad2d") return {LT::Pad2d, 2};
@@ -586,15 +594,15 @@ int infer_layer(LayerRT& L, const std::vector<int64_t>& in_n, int64_t* out_n) {
       return MIMIR_B200_OK;
     }
     case LT::Pool2d: {
-      if (L.act_of_type == 2) {  // AvgPool1d: raw kernel_h (default 2), raw stride_h (default = kernel), raw pad_h
+      if (L.act_of_type >= 2) {  // AvgPool1d / MaxPool1d: raw kernel_h (default 2), raw stride_h (default = kernel), raw pad_h
         L.ch = d.in_channels > 0 ? d.in_channels : 1;
-        if (n0 % L.ch != 0) return fail(MIMIR_B200_E_INVALID, "AvgPool1d (%s): input size is not a multiple of in_channels", L.name.c_str());
+        if (n0 % L.ch != 0) return fail(MIMIR_B200_E_INVALID, "%s (%s): input size is not a multiple of in_channels", L.type.c_str(), L.name.c_str());
         L.h = 1; L.w = static_cast<int>(n0 / L.ch);
         L.kk = 1; L.kw = d.raw_kernel_h > 0 ? d.raw_kernel_h : 2;
         L.st = 1; L.sw = d.raw_stride_h > 0 ? d.raw_stride_h : L.kw;
         L.pd = 0; L.pw = d.raw_pad_h >= 0 ? d.raw_pad_h : 0;
         L.oh = 1; L.ow = (L.w + 2 * L.pw - L.kw) / L.sw + 1;
-        if (L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "AvgPool1d (%s): empty output", L.name.c_str());
+        if (L.ow <= 0) return fail(MIMIR_B200_E_INVALID, "%s (%s): empty output", L.type.c_str(), L.name.c_str());
         *out_n = static_cast<int64_t>(L.ch) * L.ow;
         return MIMIR_B200_OK;
       }
@@ -673,6 +681,54 @@ int infer_layer(LayerRT& L, const std::vector<int64_t>& in_n, int64_t* out_n) {
       if (d.affine && L.w_count > 0 && L.w_count < static_cast<size_t>(2) * L.ch)
         return fail(MIMIR_B200_E_INVALID, "InstanceNorm2d (%s): weights too small", L.name.c_str());
       *out_n = n0;
+      return MIMIR_B200_OK;
+    }
+    case LT::EmbeddingBag: {  // Model.cpp:5336-5381: ids, optional offsets (num_bags + 1 entries); sum pooling
+      if (L.w_count < static_cast<size_t>(std::max(1, d.vocab_size)) * std::max(1, d.embed_dim))
+        return fail(MIMIR_B200_E_INVALID, "EmbeddingBag: invalid weight size");
+      int64_t bags = 1;
+      if (in_n.size() >= 2 && in_n[1] > 0) {
+        if (in_n[1] < 2) return fail(MIMIR_B200_E_INVALID, "EmbeddingBag: offsets must have at least 2 entries");
+        bags = in_n[1] - 1;
+      }
+      *out_n = bags * std::max(1, d.embed_dim);
+      return MIMIR_B200_OK;
+    }
+    case LT::PatchEmbed: {  // Model.cpp:5203-5243
+      const int d_model = d.embed_dim > 0 ? d.embed_dim : d.out_features;
+      L.mm_b = std::max(1, d.seq_text); L.mm_m = std::max(1, d.num_patches); L.mm_k = std::max(1, d.patch_dim); L.mm_n = d_model;
+      if (d_model <= 0 || n0 != static_cast<int64_t>(L.mm_b + 1) * d_model + static_cast<int64_t>(L.mm_m) * L.mm_k)
+        return fail(MIMIR_B200_E_INVALID, "PatchEmbed: input size mismatch");
+      if (L.w_f32 == nullptr || L.w_count != static_cast<size_t>(L.mm_k) * d_model + d_model)
+        return fail(MIMIR_B200_E_INVALID, "PatchEmbed: weights not initialized or invalid size");
+      *out_n = static_cast<int64_t>(L.mm_b + 1 + L.mm_m) * d_model;
+      return MIMIR_B200_OK;
+    }
+    case LT::Bilinear: {  // Model.cpp:5247-5295: in1 = in_features, in2 = out_features, output width = embed_dim or target_shape[0]
+      if (in_n.size() < 2) return fail(MIMIR_B200_E_INVALID, "Bilinear requires 2 inputs");
+      const int in1 = std::max(1, d.in_features), in2 = std::max(1, d.out_features);
+      const int out_f = d.embed_dim > 0 ? d.embed_dim : d.target_dim0;
+      if (out_f <= 0) return fail(MIMIR_B200_E_INVALID, "Bilinear: set embed_dim (output dim) or target_shape[0]");
+      if (in_n[0] % in1 != 0) return fail(MIMIR_B200_E_INVALID, "Bilinear: input0 size not divisible by in_features");
+      if (in_n[1] % in2 != 0) return fail(MIMIR_B200_E_INVALID, "Bilinear: input1 size not divisible by out_features");
+      if (in_n[0] / in1 != in_n[1] / in2) return fail(MIMIR_B200_E_INVALID, "Bilinear: batch mismatch between inputs");
+      const size_t need = static_cast<size_t>(out_f) * in1 * in2 + (d.use_bias ? out_f : 0);
+      if (L.w_f32 == nullptr || L.w_count < need) return fail(MIMIR_B200_E_INVALID, "Bilinear: weights not initialized/invalid size");
+      L.mm_b = static_cast<int>(in_n[0] / in1); L.mm_m = in1; L.mm_k = in2; L.mm_n = out_f;
+      *out_n = static_cast<int64_t>(L.mm_b) * out_f;
+      return MIMIR_B200_OK;
+    }
+    case LT::Recurrent: {  // Model.cpp:6084-6262: x is [seq_len][in_features], the output [seq_len][out_features]
+      if (d.seq_len <= 0) return fail(MIMIR_B200_E_INVALID, "Recurrent: seq_len must be set");
+      if (d.in_features <= 0 || d.out_features <= 0) return fail(MIMIR_B200_E_INVALID, "Recurrent: in_features/out_features must be set");
+      if (L.w_f32 == nullptr) return fail(MIMIR_B200_E_INVALID, "Recurrent: weights not initialized");
+      if (n0 != static_cast<int64_t>(d.seq_len) * d.in_features)
+        return fail(MIMIR_B200_E_INVALID, "Recurrent: input size mismatch (expected seq_len*in_features)");
+      const size_t g = L.act_of_type == 0 ? 1 : (L.act_of_type == 1 ? 3 : 4), H = d.out_features, I = d.in_features;
+      if (L.w_count < g * H * I + g * H * H + (d.use_bias ? 2 * g * H : 0))
+        return fail(MIMIR_B200_E_INVALID, "%s: invalid weight size", L.type.c_str());
+      L.mm_m = d.seq_len; L.mm_k = d.in_features; L.mm_n = d.out_features;
+      *out_n = static_cast<int64_t>(d.seq_len) * d.out_features;
       return MIMIR_B200_OK;
     }
     case LT::Transpose: {  // Model.cpp:5649-5659: rows = in_features, cols = out_features
@@ -1213,7 +1269,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
                                d.kernel, d.stride, d.padding, d.activation != 0, st);
         break;
       case LT::Pool2d:
-        s = launch_pool2d(L.act_of_type == 1 ? 1 : 0, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.kk, L.kw, L.st, L.sw, L.pd, L.pw, st);
+        s = launch_pool2d((L.act_of_type == 1 || L.act_of_type == 3) ? 1 : 0, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.kk, L.kw, L.st, L.sw, L.pd, L.pw, st);
         break;
       case LT::Pad2d:
         s = launch_pad2d(L.act_of_type, f32p(L.in_v[0]), f32p(L.out_v), batch, L.ch, L.h, L.w, L.pd, L.pw, st);
@@ -1243,6 +1299,25 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
                              L.h * L.w, L.ch, d.eps, -1, nullptr, st);
         break;
       }
+      case LT::EmbeddingBag: {
+        const bool has_off = L.in_v.size() >= 2 && m->tensors[L.in_v[1]].n > 0;
+        s = launch_embedding_bag(f32p(L.in_v[0]), m->tensors[L.in_v[0]].n, has_off ? f32p(L.in_v[1]) : nullptr,
+                                 has_off ? m->tensors[L.in_v[1]].n : 0, L.w_f32, f32p(L.out_v), batch, std::max(1, d.vocab_size),
+                                 std::max(1, d.embed_dim), d.padding_idx, st);
+        break;
+      }
+      case LT::PatchEmbed:
+        s = launch_patch_embed(f32p(L.in_v[0]), L.w_f32, f32p(L.out_v), batch, L.mm_n, L.mm_b, L.mm_m, L.mm_k, st);
+        break;
+      case LT::Bilinear: {
+        const size_t nw = static_cast<size_t>(L.mm_n) * L.mm_m * L.mm_k;
+        s = launch_bilinear(f32p(L.in_v[0]), f32p(L.in_v[1]), L.w_f32, d.use_bias ? L.w_f32 + nw : nullptr, f32p(L.out_v),
+                            static_cast<int64_t>(batch) * L.mm_b, L.mm_m, L.mm_k, L.mm_n, st);
+        break;
+      }
+      case LT::Recurrent:
+        s = launch_recurrent(L.act_of_type, f32p(L.in_v[0]), L.w_f32, f32p(L.out_v), batch, L.mm_m, L.mm_k, L.mm_n, d.use_bias != 0, st);
+        break;
       case LT::Transpose: {
         const int shape[2] = {d.in_features, d.out_features}, dims[2] = {1, 0};
         s = launch_permute(f32p(L.in_v[0]), f32p(L.out_v), batch, 2, shape, dims, st);

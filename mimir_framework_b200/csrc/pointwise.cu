@@ -15,6 +15,7 @@ __device__ __forceinline__ float act_apply(int op, float v, float alpha = 0.0f) 
   switch (op) {
     // LayerOpsExt.hpp:29-99
     case MIMIR_B200_ELT_LEAKY_RELU: return v > 0.0f ? v : alpha * v;
+    case MIMIR_B200_ELT_ELU: return v >= 0.0f ? v : alpha * (expf(v) - 1.0f);  // Model.hpp:505-509
     case MIMIR_B200_ELT_SOFTPLUS: return v > 20.0f ? v : logf(1.0f + expf(v));
     case MIMIR_B200_ELT_MISH: return v * tanhf(v > 20.0f ? v : logf(1.0f + expf(v)));
     case MIMIR_B200_ELT_HARD_SIGMOID: return fmaxf(0.0f, fminf(1.0f, (v + 3.0f) / 6.0f));
@@ -267,6 +268,7 @@ int launch_eltwise(int op, const float* a, const float* b, float* y, int batch, 
     case MIMIR_B200_ELT_TANH: unary_kernel<MIMIR_B200_ELT_TANH><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
     case MIMIR_B200_ELT_SIGMOID: unary_kernel<MIMIR_B200_ELT_SIGMOID><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
     case MIMIR_B200_ELT_LEAKY_RELU: unary_kernel<MIMIR_B200_ELT_LEAKY_RELU><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
+    case MIMIR_B200_ELT_ELU: unary_kernel<MIMIR_B200_ELT_ELU><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
     case MIMIR_B200_ELT_SOFTPLUS: unary_kernel<MIMIR_B200_ELT_SOFTPLUS><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
     case MIMIR_B200_ELT_MISH: unary_kernel<MIMIR_B200_ELT_MISH><<<grid, threads, 0, st>>>(a, y, total, alpha); break;
     case MIMIR_B200_ELT_HARD_SIGMOID: unary_kernel<MIMIR_B200_ELT_HARD_SIGMOID><<<grid, threads, 0, st>>>(a, y, total, alpha); break;

@@ -134,6 +134,112 @@ __global__ void pool2d_kernel(const float* __restrict__ x, float* __restrict__ y
   }
 }
 
+// Conv::conv2d (Layers.hpp:611-722): bias and dilation; one thread per output element, fp32 FMAs over (ic, kh, kw)
+// ascending like the reference's scalar loop.
+__global__ void conv2d_dilated_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                      float* __restrict__ y, int batch, int ic, int oc, int h, int wd, int oh, int ow, int k,
+                                      int stride, int pad, int dil) {
+  const long long total = static_cast<long long>(batch) * oc * oh * ow;
+  MB_GRID_STRIDE(i, total) {
+    const int q = static_cast<int>(i % ow);
+    long long t = i / ow;
+    const int r = static_cast<int>(t % oh);
+    t /= oh;
+    const int o = static_cast<int>(t % oc);
+    const long long n = t / oc;
+    const float* xs = x + n * ic * h * wd;
+    const float* wo = w + static_cast<long long>(o) * ic * k * k;
+    float acc = 0.0f;
+    for (int c = 0; c < ic; ++c)
+      for (int kh = 0; kh < k; ++kh) {
+        const int ih = r * stride - pad + kh * dil;
+        if (ih < 0 || ih >= h) continue;
+        for (int kw = 0; kw < k; ++kw) {
+          const int iw = q * stride - pad + kw * dil;
+          if (iw < 0 || iw >= wd) continue;
+          acc = fmaf(__ldg(xs + (static_cast<long long>(c) * h + ih) * wd + iw), __ldg(wo + (c * k + kh) * k + kw), acc);
+        }
+      }
+    y[i] = bias != nullptr ? acc + __ldg(bias + o) : acc;
+  }
+}
+
+// Conv::conv_transpose2d (Layers.hpp:775-818) as a gather: output (oh, ow) receives x[ic][ih][iw] * w[oc][ic][kh][kw] for every
+// (ih, kh) with ih * stride + kh - pad == oh (and likewise in x).  Walking ic, ih, iw ascending visits them in the order
+// the reference's scatter loop adds them; the sum starts at the bias, as there.
+__global__ void conv_transpose2d_scatter_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                                float* __restrict__ y, int batch, int ic, int oc, int h, int wd, int oh, int ow, int k,
+                                                int stride, int pad) {
+  const long long total = static_cast<long long>(batch) * oc * oh * ow;
+  MB_GRID_STRIDE(i, total) {
+    const int q = static_cast<int>(i % ow);
+    long long t = i / ow;
+    const int r = static_cast<int>(t % oh);
+    t /= oh;
+    const int o = static_cast<int>(t % oc);
+    const long long n = t / oc;
+    const float* xs = x + n * ic * h * wd;
+    float acc = bias != nullptr ? __ldg(bias + o) : 0.0f;
+    // ih * stride + kh - pad = r with 0 <= kh < k  =>  (r + pad - k + 1) / stride <= ih <= (r + pad) / stride
+    const int ih_lo = max(0, (r + pad - k + stride) / stride), ih_hi = min(h - 1, (r + pad) / stride);
+    const int iw_lo = max(0, (q + pad - k + stride) / stride), iw_hi = min(wd - 1, (q + pad) / stride);
+    for (int c = 0; c < ic; ++c) {
+      const float* wc = w + (static_cast<long long>(o) * ic + c) * k * k;
+      for (int ih = ih_lo; ih <= ih_hi; ++ih) {
+        const int kh = r + pad - ih * stride;
+        if (kh < 0 || kh >= k) continue;
+        for (int iw = iw_lo; iw <= iw_hi; ++iw) {
+          const int kw = q + pad - iw * stride;
+          if (kw < 0 || kw >= k) continue;
+          acc = fmaf(__ldg(xs + (static_cast<long long>(c) * h + ih) * wd + iw), __ldg(wc + kh * k + kw), acc);
+        }
+      }
+    }
+    y[i] = acc;
+  }
+}
+
+// Normalization::batch_norm with training = true (Layers.hpp:932-970): one CTA per channel; mean, then the biased
+// variance around it, over the batch and the spatial positions; then the affine map.
+__global__ void __launch_bounds__(256) batchnorm_batchstats_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                                   const float* __restrict__ beta, float* __restrict__ y, int batch,
+                                                                   int channels, long long spatial, float eps) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int c = blockIdx.x;
+  const long long per = static_cast<long long>(batch) * spatial;
+  auto at = [&](long long j) { return (j / spatial) * channels * spatial + static_cast<long long>(c) * spatial + (j % spatial); };
+  auto block_sum = [&](float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();  // the previous broadcast value has been read by everyone
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.0f;
+      for (int i = 0; i < 8; ++i) s += red[i];
+      bc = s;
+    }
+    __syncthreads();
+    return bc;
+  };
+  float s = 0.0f;
+  for (long long j = threadIdx.x; j < per; j += 256) s += x[at(j)];
+  const float mean = block_sum(s) / static_cast<float>(per);
+  float v = 0.0f;
+  for (long long j = threadIdx.x; j < per; j += 256) {
+    const float d = x[at(j)] - mean;
+    v = fmaf(d, d, v);
+  }
+  const float var = block_sum(v) / static_cast<float>(per);
+  const float inv = 1.0f / sqrtf(var + eps);
+  const float g = __ldg(gamma + c), b = __ldg(beta + c);
+  for (long long j = threadIdx.x; j < per; j += 256) {
+    const long long idx = at(j);
+    y[idx] = (x[idx] - mean) * inv * g + b;
+  }
+}
+
 // mode 0 = zero, 1 = reflection, 2 = replication
 __global__ void pad2d_kernel(const float* __restrict__ x, float* __restrict__ y, long long planes, int h, int w, int ph, int pw,
                              int mode) {
@@ -300,6 +406,35 @@ int launch_conv_gather(const float* x, const float* w, float* y, int batch, int 
     return fail(MIMIR_B200_E_INVALID, "ConvTranspose2d: invalid dimensions");
   conv_gather_kernel<<<grid_of(static_cast<long long>(batch) * oc * oh * ow, 256), 256, 0, st>>>(x, w, y, batch, ic, oc, h, wd, oh, ow,
                                                                                                  k, stride, pad, relu);
+  MB_LAUNCHED();
+}
+
+int launch_conv2d_dilated(const float* x, const float* w, const float* bias, float* y, int batch, int ic, int oc, int h, int wd, int k,
+                          int stride, int pad, int dil, cudaStream_t st) {
+  if (batch <= 0 || ic <= 0 || oc <= 0 || h <= 0 || wd <= 0 || k <= 0 || stride <= 0 || pad < 0 || dil <= 0)
+    return fail(MIMIR_B200_E_INVALID, "computeConv2D: invalid dimensions");
+  const int oh = (h + 2 * pad - dil * (k - 1) - 1) / stride + 1, ow = (wd + 2 * pad - dil * (k - 1) - 1) / stride + 1;
+  if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "computeConv2D: empty output");
+  conv2d_dilated_kernel<<<grid_of(static_cast<long long>(batch) * oc * oh * ow, 256), 256, 0, st>>>(x, w, bias, y, batch, ic, oc, h, wd,
+                                                                                                    oh, ow, k, stride, pad, dil);
+  MB_LAUNCHED();
+}
+
+int launch_conv_transpose2d_scatter(const float* x, const float* w, const float* bias, float* y, int batch, int ic, int oc, int h, int wd,
+                                    int k, int stride, int pad, cudaStream_t st) {
+  if (batch <= 0 || ic <= 0 || oc <= 0 || h <= 0 || wd <= 0 || k <= 0 || stride <= 0 || pad < 0)
+    return fail(MIMIR_B200_E_INVALID, "computeConvTranspose2D: invalid dimensions");
+  const int oh = (h - 1) * stride - 2 * pad + k, ow = (wd - 1) * stride - 2 * pad + k;
+  if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "computeConvTranspose2D: empty output");
+  conv_transpose2d_scatter_kernel<<<grid_of(static_cast<long long>(batch) * oc * oh * ow, 256), 256, 0, st>>>(x, w, bias, y, batch, ic, oc,
+                                                                                                              h, wd, oh, ow, k, stride, pad);
+  MB_LAUNCHED();
+}
+
+int launch_batchnorm_batchstats(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels, long long spatial,
+                                float eps, cudaStream_t st) {
+  if (batch <= 0 || channels <= 0 || spatial <= 0) return fail(MIMIR_B200_E_INVALID, "computeBatchNorm: invalid dimensions");
+  batchnorm_batchstats_kernel<<<channels, 256, 0, st>>>(x, gamma, beta, y, batch, channels, spatial, eps);
   MB_LAUNCHED();
 }
 

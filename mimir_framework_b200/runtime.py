@@ -75,6 +75,9 @@ _SIGS = {
     "mimir_b200_batch_matmul": [_P, _P, _P, C.c_longlong, C.c_int, C.c_int, C.c_int],
     "mimir_b200_batchnorm_inference": [_P, _P, C.c_longlong, _P, C.c_int, C.c_longlong, C.c_float],
     "mimir_b200_batchnorm_running": [_P, _P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_longlong, C.c_float],
+    "mimir_b200_batchnorm_batchstats": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_longlong, C.c_float],
+    "mimir_b200_conv2d_dilated": [_P, _P, _P, _P] + [C.c_int] * 9,
+    "mimir_b200_conv_transpose2d_scatter": [_P, _P, _P, _P] + [C.c_int] * 8,
     "mimir_b200_attention_qkv": [_P, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int],
     "mimir_b200_model_create": [_P, C.c_int, _P],
     "mimir_b200_model_destroy": [_P],
@@ -366,6 +369,33 @@ def batchnorm_running(x, gamma, beta, mean, var, batch, channels, spatial, eps=1
     x, gamma, beta, mean, var = (_f(a) for a in (x, gamma, beta, mean, var))
     y = np.empty(batch * channels * spatial, np.float32)
     check(lib().mimir_b200_batchnorm_running(_p(x), _p(gamma), _p(beta), _p(mean), _p(var), _p(y), batch, channels, spatial, eps))
+    return y
+
+
+def batchnorm_batchstats(x, gamma, beta, batch, channels, spatial, eps=1e-5):
+    """Model::computeBatchNorm with training = true: statistics of each channel over the batch and the spatial positions."""
+    x, gamma, beta = (_f(a) for a in (x, gamma, beta))
+    y = np.empty(batch * channels * spatial, np.float32)
+    check(lib().mimir_b200_batchnorm_batchstats(_p(x), _p(gamma), _p(beta), _p(y), batch, channels, spatial, eps))
+    return y
+
+
+def conv2d_dilated(x, w, bias, batch, in_c, out_c, in_h, in_w, k, stride, pad, dil=1):
+    """Model::computeConv2D (Conv::conv2d, scalar branch): bias and dilation."""
+    x, w, bias = _f(x), _f(w), _f(bias)
+    oh = (in_h + 2 * pad - dil * (k - 1) - 1) // stride + 1
+    ow = (in_w + 2 * pad - dil * (k - 1) - 1) // stride + 1
+    y = np.empty(batch * out_c * oh * ow, np.float32)
+    check(lib().mimir_b200_conv2d_dilated(_p(x), _p(w), _p(bias), _p(y), batch, in_c, out_c, in_h, in_w, k, stride, pad, dil))
+    return y
+
+
+def conv_transpose2d_scatter(x, w, bias, batch, in_c, out_c, in_h, in_w, k, stride, pad):
+    """Model::computeConvTranspose2D (Conv::conv_transpose2d): the scatter form on top of the bias."""
+    x, w, bias = _f(x), _f(w), _f(bias)
+    oh, ow = (in_h - 1) * stride - 2 * pad + k, (in_w - 1) * stride - 2 * pad + k
+    y = np.empty(batch * out_c * oh * ow, np.float32)
+    check(lib().mimir_b200_conv_transpose2d_scatter(_p(x), _p(w), _p(bias), _p(y), batch, in_c, out_c, in_h, in_w, k, stride, pad))
     return y
 
 

@@ -657,3 +657,225 @@ void mo_instance_norm2d(const float* x, const float* w, float* y, int ch, int h,
     }
   }
 }
+
+/* EmbeddingBag case, Model.cpp:5336-5381: sum pooling.  offsets (rounded floats, num_bags + 1 entries) may be absent:
+ * then one bag holds every id.  Bag bounds are clamped into [0, n_ids]; ids equal to padding_idx or out of range add
+ * nothing.  Returns the number of bags, or -1 when offsets has a single entry. */
+long mo_embedding_bag(const float* ids, long n_ids, const float* offsets, long n_off, const float* table, float* y, int vocab,
+                      int dim, int padding_idx) {
+  if (offsets != NULL && n_off > 0 && n_off < 2) return -1;
+  const long bags = (offsets != NULL && n_off > 0) ? n_off - 1 : 1;
+  memset(y, 0, sizeof(float) * (size_t)bags * dim);
+  for (long b = 0; b < bags; ++b) {
+    long long s = 0, e = n_ids;
+    if (offsets != NULL && n_off > 0) {
+      s = (int)llround((double)offsets[b]);
+      e = (int)llround((double)offsets[b + 1]);
+    }
+    if (s < 0) s = 0;
+    if (s > n_ids) s = n_ids;
+    if (e < s) e = s;
+    if (e > n_ids) e = n_ids;
+    float* out = y + (size_t)b * dim;
+    for (long long t = s; t < e; ++t) {
+      const long long id = llround((double)ids[t]);
+      if (padding_idx >= 0 && id == padding_idx) continue;
+      if (id < 0 || id >= vocab) continue;
+      for (int d = 0; d < dim; ++d) out[d] += table[(size_t)id * dim + d];
+    }
+  }
+  return bags;
+}
+
+/* PatchEmbed case, Model.cpp:5203-5243: x = [(seq_text + 1) * d_model text floats | num_patches * patch_dim patch floats];
+ * the text part is copied, every patch becomes (x_patch / sqrt(patch_dim)) @ W[patch_dim][d_model] + b.  The scale is
+ * applied to each input element before its product, the bias is the initial value of the sum. */
+void mo_patch_embed(const float* x, const float* w, float* y, int d_model, int seq_text, int num_patches, int patch_dim) {
+  const long text = (long)(seq_text + 1) * d_model;
+  memcpy(y, x, sizeof(float) * (size_t)text);
+  const float* b = w + (size_t)patch_dim * d_model;
+  const float inv = 1.0f / sqrtf((float)patch_dim);
+  for (int p = 0; p < num_patches; ++p)
+    for (int d = 0; d < d_model; ++d) {
+      float sum = b[d];
+      for (int k = 0; k < patch_dim; ++k) sum += (x[text + (long)p * patch_dim + k] * inv) * w[(size_t)k * d_model + d];
+      y[text + (long)p * d_model + d] = sum;
+    }
+}
+
+/* Bilinear case, Model.cpp:5247-5295: y[b][o] = bias[o] + sum_i sum_j x1[b][i] * W[o][i][j] * x2[b][j], the product taken
+ * as (x1 * W) * x2, accumulated over (i, j) ascending. */
+void mo_bilinear(const float* x1, const float* x2, const float* w, const float* bias, float* y, long rows, int in1, int in2,
+                 int out_f) {
+  for (long b = 0; b < rows; ++b)
+    for (int o = 0; o < out_f; ++o) {
+      float sum = bias ? bias[o] : 0.0f;
+      for (int i = 0; i < in1; ++i) {
+        const float ai = x1[b * in1 + i];
+        const float* wr = w + ((size_t)o * in1 + i) * in2;
+        for (int j = 0; j < in2; ++j) sum += ai * wr[j] * x2[b * in2 + j];
+      }
+      y[b * out_f + o] = sum;
+    }
+}
+
+/* LayerOpsExt::maxpool1d_forward, LayerOpsExt.hpp:504-538: per channel over the length; a window with no tap inside
+ * the input stays -inf. */
+void mo_maxpool1d(const float* x, float* y, int ch, long len, int k, int stride, int pad) {
+  const long ol_n = (len + 2 * pad - k) / stride + 1;
+  for (int c = 0; c < ch; ++c)
+    for (long ol = 0; ol < ol_n; ++ol) {
+      float m = -INFINITY;
+      for (int t = 0; t < k; ++t) {
+        const long il = ol * stride + t - pad;
+        if (il >= 0 && il < len && x[c * len + il] > m) m = x[c * len + il];
+      }
+      y[c * ol_n + ol] = m;
+    }
+}
+
+static float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+/* RNN / GRU / LSTM cases, Model.cpp:6084-6262.  kind 0 = RNN (tanh), 1 = GRU (gates r, z, n), 2 = LSTM (gates i, f, g, o).
+ * Weight block: W_ih[G*H][I], W_hh[G*H][H], then b_ih[G*H], b_hh[G*H] when use_bias (G = 1, 3, 4).  The hidden (and cell)
+ * state starts at zero; y is [T][H].  Sums run in the reference's order: for the RNN and the GRU's r and z gates the input
+ * products and the hidden products share one accumulator, then the two biases are added; the GRU's n gate keeps the
+ * hidden sum apart (it is scaled by r); the LSTM adds an input sum and a hidden sum, then the biases. */
+void mo_recurrent(int kind, const float* x, const float* w, float* y, int T, int I, int H, int use_bias) {
+  const int G = kind == 0 ? 1 : (kind == 1 ? 3 : 4);
+  const float* Wih = w;
+  const float* Whh = Wih + (size_t)G * H * I;
+  const float* bih = use_bias ? Whh + (size_t)G * H * H : NULL;
+  const float* bhh = use_bias ? bih + (size_t)G * H : NULL;
+  float* hp = (float*)calloc((size_t)H * 5, sizeof(float));
+  float *cp = hp + H, *r = hp + 2 * H, *z = hp + 3 * H, *nn = hp + 4 * H;
+  for (int t = 0; t < T; ++t) {
+    const float* xt = x + (size_t)t * I;
+    float* ht = y + (size_t)t * H;
+    if (kind == 0) {
+      for (int h = 0; h < H; ++h) {
+        float s = 0.0f;
+        for (int i = 0; i < I; ++i) s += Wih[(size_t)h * I + i] * xt[i];
+        for (int k = 0; k < H; ++k) s += Whh[(size_t)h * H + k] * hp[k];
+        if (bih) s += bih[h];
+        if (bhh) s += bhh[h];
+        ht[h] = tanhf(s);
+      }
+    } else if (kind == 1) {
+      for (int h = 0; h < H; ++h) {
+        float sr = 0.0f, sz = 0.0f;
+        for (int i = 0; i < I; ++i) sr += Wih[(size_t)h * I + i] * xt[i];
+        for (int k = 0; k < H; ++k) sr += Whh[(size_t)h * H + k] * hp[k];
+        if (bih) sr += bih[h];
+        if (bhh) sr += bhh[h];
+        r[h] = sigmoid_f(sr);
+        for (int i = 0; i < I; ++i) sz += Wih[(size_t)(H + h) * I + i] * xt[i];
+        for (int k = 0; k < H; ++k) sz += Whh[(size_t)(H + h) * H + k] * hp[k];
+        if (bih) sz += bih[H + h];
+        if (bhh) sz += bhh[H + h];
+        z[h] = sigmoid_f(sz);
+      }
+      for (int h = 0; h < H; ++h) {
+        float sn = 0.0f, hn = 0.0f;
+        for (int i = 0; i < I; ++i) sn += Wih[(size_t)(2 * H + h) * I + i] * xt[i];
+        for (int k = 0; k < H; ++k) hn += Whh[(size_t)(2 * H + h) * H + k] * hp[k];
+        if (bih) sn += bih[2 * H + h];
+        if (bhh) sn += bhh[2 * H + h];
+        nn[h] = tanhf(sn + r[h] * hn);
+      }
+      for (int h = 0; h < H; ++h) ht[h] = (1.0f - z[h]) * nn[h] + z[h] * hp[h];
+    } else {
+      for (int h = 0; h < H; ++h) {
+        float s[4];
+        for (int g = 0; g < 4; ++g) {
+          float a = 0.0f, b = 0.0f;
+          for (int i = 0; i < I; ++i) a += Wih[(size_t)(g * H + h) * I + i] * xt[i];
+          for (int k = 0; k < H; ++k) b += Whh[(size_t)(g * H + h) * H + k] * hp[k];
+          s[g] = a + b;
+          if (bih) s[g] += bih[g * H + h];
+          if (bhh) s[g] += bhh[g * H + h];
+        }
+        const float c = sigmoid_f(s[1]) * cp[h] + sigmoid_f(s[0]) * tanhf(s[2]);
+        cp[h] = c;
+        ht[h] = sigmoid_f(s[3]) * tanhf(c);
+      }
+    }
+    memcpy(hp, ht, sizeof(float) * (size_t)H);
+  }
+  free(hp);
+}
+
+/* Conv::conv2d behind Model::computeConv2D: bias added after the sum, dilation.  avx2_lanes = 0 restates the scalar branch
+ * (Layers.hpp:690-721).  avx2_lanes = 1 restates what the AVX2 branch (Layers.hpp:622-688) computes: taps are taken eight at
+ * a time into the eight lanes of one accumulator, but every tap of the remainder (all taps when the kernel is narrower than
+ * eight) is added to ALL eight lanes before the horizontal sum, so it counts eight times. */
+void mo_conv2d_dilated(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int h, int wd, int k, int stride,
+                       int pad, int dil, int avx2_lanes) {
+  const int oh = (h + 2 * pad - dil * (k - 1) - 1) / stride + 1, ow = (wd + 2 * pad - dil * (k - 1) - 1) / stride + 1;
+  for (int o = 0; o < oc; ++o)
+    for (int r = 0; r < oh; ++r)
+      for (int q = 0; q < ow; ++q) {
+        float sum = 0.0f;
+        for (int c = 0; c < ic; ++c)
+          for (int kh = 0; kh < k; ++kh) {
+            const int ih = r * stride - pad + kh * dil;
+            if (ih < 0 || ih >= h) continue;
+            for (int kw = 0; kw < k; ++kw) {
+              const int iw = q * stride - pad + kw * dil;
+              if (iw >= 0 && iw < wd) {
+                const float prod = x[((size_t)c * h + ih) * wd + iw] * w[(((size_t)o * ic + c) * k + kh) * k + kw];
+                sum += (avx2_lanes && kw >= (k & ~7)) ? 8.0f * prod : prod;
+              }
+            }
+          }
+        if (bias) sum += bias[o];
+        y[((size_t)o * oh + r) * ow + q] = sum;
+      }
+}
+
+/* Conv::conv_transpose2d (Layers.hpp:775-818) behind Model::computeConvTranspose2D: scatter on top of the bias. */
+void mo_conv_transpose2d_scatter(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int h, int wd, int k,
+                                 int stride, int pad) {
+  const int oh = (h - 1) * stride - 2 * pad + k, ow = (wd - 1) * stride - 2 * pad + k;
+  for (int o = 0; o < oc; ++o)
+    for (long i = 0; i < (long)oh * ow; ++i) y[(size_t)o * oh * ow + i] = bias ? bias[o] : 0.0f;
+  for (int o = 0; o < oc; ++o)
+    for (int c = 0; c < ic; ++c)
+      for (int ih = 0; ih < h; ++ih)
+        for (int iw = 0; iw < wd; ++iw) {
+          const float v = x[((size_t)c * h + ih) * wd + iw];
+          for (int kh = 0; kh < k; ++kh)
+            for (int kw = 0; kw < k; ++kw) {
+              const int r = ih * stride + kh - pad, q = iw * stride + kw - pad;
+              if (r >= 0 && r < oh && q >= 0 && q < ow) y[((size_t)o * oh + r) * ow + q] += v * w[(((size_t)o * ic + c) * k + kh) * k + kw];
+            }
+        }
+}
+
+/* Normalization::batch_norm with training = true (Layers.hpp:932-970): batch mean and biased variance per channel. */
+void mo_batchnorm_batchstats(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels, long spatial,
+                             float eps) {
+  for (int c = 0; c < channels; ++c) {
+    float mean = 0.0f, var = 0.0f;
+    for (int b = 0; b < batch; ++b)
+      for (long s = 0; s < spatial; ++s) mean += x[((size_t)b * channels + c) * spatial + s];
+    mean /= (float)(batch * spatial);
+    for (int b = 0; b < batch; ++b)
+      for (long s = 0; s < spatial; ++s) {
+        const float d = x[((size_t)b * channels + c) * spatial + s] - mean;
+        var += d * d;
+      }
+    var /= (float)(batch * spatial);
+    const float inv = 1.0f / sqrtf(var + eps);
+    for (int b = 0; b < batch; ++b)
+      for (long s = 0; s < spatial; ++s) {
+        const size_t i = ((size_t)b * channels + c) * spatial + s;
+        y[i] = (x[i] - mean) * inv * gamma[c] + beta[c];
+      }
+  }
+}
+
+/* Model::elu_inplace (Model.hpp:505-509). */
+void mo_elu(const float* a, float* y, long n, float alpha) {
+  for (long i = 0; i < n; ++i) y[i] = a[i] >= 0.0f ? a[i] : alpha * (expf(a[i]) - 1.0f);
+}

@@ -37,6 +37,20 @@ void mo_batchnorm_running(const float* x, const float* gamma, const float* beta,
                           float* y, int batch, int channels, long spatial, float eps);
 void mo_attention_qkv(const float* q, const float* k, const float* v, float* y, int seq, int d_model, int heads);
 void mo_instance_norm2d(const float* x, const float* w, float* y, int ch, int h, int wd, float eps);
+long mo_embedding_bag(const float* ids, long n_ids, const float* offsets, long n_off, const float* table, float* y, int vocab,
+                      int dim, int padding_idx);
+void mo_patch_embed(const float* x, const float* w, float* y, int d_model, int seq_text, int num_patches, int patch_dim);
+void mo_bilinear(const float* x1, const float* x2, const float* w, const float* bias, float* y, long rows, int in1, int in2,
+                 int out_f);
+void mo_maxpool1d(const float* x, float* y, int ch, long len, int k, int stride, int pad);
+void mo_conv2d_dilated(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int h, int wd, int k, int stride,
+                       int pad, int dil, int avx2_lanes);
+void mo_conv_transpose2d_scatter(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int h, int wd, int k,
+                                 int stride, int pad);
+void mo_batchnorm_batchstats(const float* x, const float* gamma, const float* beta, float* y, int batch, int channels, long spatial,
+                             float eps);
+void mo_elu(const float* a, float* y, long n, float alpha);
+void mo_recurrent(int kind, const float* x, const float* w, float* y, int T, int I, int H, int use_bias);
 #ifdef __cplusplus
 }
 #endif

@@ -268,6 +268,85 @@ def instance_norm2d(x, w, ch, h, wd, eps):
     return y
 
 
+def embedding_bag(ids, offsets, table, vocab, dim, padding_idx):
+    ids, table = _f(ids), _f(table)
+    off = _f(offsets) if offsets is not None else None
+    n_off = off.size if off is not None else 0
+    bags = max(1, n_off - 1) if n_off else 1
+    y = np.empty(bags * dim, np.float32)
+    fn = lib().mo_embedding_bag
+    fn.restype = C.c_long
+    got = fn(_p(ids), C.c_long(ids.size), _p(off) if n_off else None, C.c_long(n_off), _p(table), _p(y), C.c_int(vocab), C.c_int(dim),
+             C.c_int(padding_idx))
+    if got < 0:
+        raise RuntimeError("EmbeddingBag: offsets must have at least 2 entries")
+    return y
+
+
+def patch_embed(x, w, d_model, seq_text, num_patches, patch_dim):
+    x, w = _f(x), _f(w)
+    y = np.empty((seq_text + 1 + num_patches) * d_model, np.float32)
+    lib().mo_patch_embed(_p(x), _p(w), _p(y), C.c_int(d_model), C.c_int(seq_text), C.c_int(num_patches), C.c_int(patch_dim))
+    return y
+
+
+def bilinear(x1, x2, w, bias, in1, in2, out_f):
+    x1, x2, w = _f(x1), _f(x2), _f(w)
+    rows = x1.size // in1
+    y = np.empty(rows * out_f, np.float32)
+    lib().mo_bilinear(_p(x1), _p(x2), _p(w), _p(_f(bias)) if bias is not None else None, _p(y), C.c_long(rows), C.c_int(in1), C.c_int(in2),
+                      C.c_int(out_f))
+    return y
+
+
+def maxpool1d(x, ch, k, stride, pad):
+    x = _f(x)
+    length = x.size // ch
+    ol = (length + 2 * pad - k) // stride + 1
+    y = np.empty(ch * max(ol, 0), np.float32)
+    lib().mo_maxpool1d(_p(x), _p(y), C.c_int(ch), C.c_long(length), C.c_int(k), C.c_int(stride), C.c_int(pad))
+    return y
+
+
+def recurrent(kind, x, w, T, I, H, use_bias):  # noqa: E741
+    x, w = _f(x), _f(w)
+    y = np.empty(T * H, np.float32)
+    lib().mo_recurrent(C.c_int(kind), _p(x), _p(w), _p(y), C.c_int(T), C.c_int(I), C.c_int(H), C.c_int(1 if use_bias else 0))
+    return y
+
+
+def conv2d_dilated(x, w, bias, ic, oc, h, wd, k, stride, pad, dil, avx2_lanes=False):
+    """Conv::conv2d: the scalar branch, or (avx2_lanes) what an AVX2 build of the reference computes: remainder taps count eight times."""
+    x, w = _f(x), _f(w)
+    oh = (h + 2 * pad - dil * (k - 1) - 1) // stride + 1
+    ow = (wd + 2 * pad - dil * (k - 1) - 1) // stride + 1
+    y = np.empty(oc * oh * ow, np.float32)
+    lib().mo_conv2d_dilated(_p(x), _p(w), _p(_f(bias)) if bias is not None else None, _p(y), *_ci(ic, oc, h, wd, k, stride, pad, dil, 1 if avx2_lanes else 0))
+    return y
+
+
+def conv_transpose2d_scatter(x, w, bias, ic, oc, h, wd, k, stride, pad):
+    x, w = _f(x), _f(w)
+    oh, ow = (h - 1) * stride - 2 * pad + k, (wd - 1) * stride - 2 * pad + k
+    y = np.empty(oc * oh * ow, np.float32)
+    lib().mo_conv_transpose2d_scatter(_p(x), _p(w), _p(_f(bias)) if bias is not None else None, _p(y), *_ci(ic, oc, h, wd, k, stride, pad))
+    return y
+
+
+def batchnorm_batchstats(x, gamma, beta, batch, channels, spatial, eps=1e-5):
+    x, g, b = _f(x), _f(gamma), _f(beta)
+    y = np.empty_like(x)
+    lib().mo_batchnorm_batchstats(_p(x), _p(g), _p(b), _p(y), C.c_int(batch), C.c_int(channels), C.c_long(spatial), C.c_float(eps))
+    return y
+
+
+def elu(x, alpha):
+    x = _f(x)
+    y = np.empty_like(x)
+    lib().mo_elu(_p(x), _p(y), C.c_long(x.size), C.c_float(alpha))
+    return y
+
+
 def split_pieces(d, n):
     """Sizes of the tensors a Split / Chunk layer stores (Model.cpp:5802-5832)."""
     if d.type.decode() == "Split":
@@ -403,6 +482,38 @@ def run_layer(d, ins, w):
                                _dflt(d.input_width, 32), d.eps)
     if t == "Transpose":
         return permute(x, [d.in_features, d.out_features], [1, 0])
+    if t == "EmbeddingBag":
+        return embedding_bag(ins[0], ins[1] if len(ins) >= 2 else None, w, max(1, d.vocab_size), max(1, d.embed_dim), d.padding_idx)
+    if t == "PatchEmbed":
+        dm = d.embed_dim if d.embed_dim > 0 else d.out_features
+        st, npch, pd = max(1, d.seq_text), max(1, d.num_patches), max(1, d.patch_dim)
+        if x.size != (st + 1) * dm + npch * pd:
+            raise RuntimeError("PatchEmbed: input size mismatch")
+        if w is None or w.size != pd * dm + dm:
+            raise RuntimeError("PatchEmbed: weights not initialized or invalid size")
+        return patch_embed(x, w, dm, st, npch, pd)
+    if t == "Bilinear":
+        if len(ins) < 2:
+            raise RuntimeError("Bilinear requires 2 inputs")
+        in1, in2 = max(1, d.in_features), max(1, d.out_features)
+        out_f = d.embed_dim if d.embed_dim > 0 else d.target_dim0
+        if out_f <= 0:
+            raise RuntimeError("Bilinear: set embed_dim (output dim) or target_shape[0]")
+        if ins[0].size % in1 or ins[1].size % in2 or ins[0].size // in1 != ins[1].size // in2:
+            raise RuntimeError("Bilinear: batch mismatch between inputs")
+        nw = out_f * in1 * in2
+        return bilinear(ins[0], ins[1], w[:nw], w[nw : nw + out_f] if d.use_bias else None, in1, in2, out_f)
+    if t == "MaxPool1d":  # LayerOpsExt.hpp:504-538 (the reference's layer switch has no case that calls it)
+        ch = _dflt(d.in_channels, 1)
+        k = _dflt(d.raw_kernel_h, 2)
+        st = d.raw_stride_h if d.raw_stride_h > 0 else k
+        return maxpool1d(x, ch, k, st, d.raw_pad_h if d.raw_pad_h >= 0 else 0)
+    if t in ("RNN", "GRU", "LSTM"):
+        if d.seq_len <= 0 or d.in_features <= 0 or d.out_features <= 0:
+            raise RuntimeError("Recurrent: seq_len / in_features / out_features must be set")
+        if x.size != d.seq_len * d.in_features:
+            raise RuntimeError("Recurrent: input size mismatch (expected seq_len*in_features)")
+        return recurrent(("RNN", "GRU", "LSTM").index(t), x, w, d.seq_len, d.in_features, d.out_features, d.use_bias)
     if t == "TokenMeanPool":
         return token_mean_pool(x, d.seq_len, d.embed_dim)
     if t in ("GlobalAvgPool2d", "AdaptiveAvgPool2d"):

@@ -142,3 +142,45 @@ def compute_batchnorm(x, gamma, beta, mean, var, batch: int, channels: int, spat
     _check(lib().mimir_ref_compute_batchnorm(d.ctypes.data_as(fp), g.ctypes.data_as(fp), b.ctypes.data_as(fp), m.ctypes.data_as(fp),
                                              v.ctypes.data_as(fp), C.c_int(batch), C.c_int(channels), C.c_int(spatial), C.c_float(eps)))
     return d
+
+
+def maxpool1d(x, in_channels: int, kernel_h: int, stride_h: int, pad_h: int) -> np.ndarray:
+    """LayerOpsExt::maxpool1d_forward (LayerOpsExt.hpp:504-538), which the layer switch never dispatches."""
+    x = np.ascontiguousarray(x, np.float32).ravel()
+    out = np.empty(x.size + 16, np.float32)
+    n = C.c_ulonglong(0)
+    fp = C.POINTER(C.c_float)
+    _check(lib().mimir_ref_maxpool1d(x.ctypes.data_as(fp), C.c_ulonglong(x.size), C.c_int(in_channels), C.c_int(kernel_h), C.c_int(stride_h),
+                                     C.c_int(pad_h), out.ctypes.data_as(fp), C.c_ulonglong(out.size), C.byref(n)))
+    return out[: n.value].copy()
+
+
+def compute_conv2d(x, w, bias, in_h: int, in_w: int, in_c: int, out_c: int, k: int, stride: int, pad: int, dil: int = 1, transposed: bool = False) -> np.ndarray:
+    """Model::computeConv2D (Conv::conv2d) or, with transposed, Model::computeConvTranspose2D (Conv::conv_transpose2d)."""
+    x, w = (np.ascontiguousarray(a, np.float32).ravel() for a in (x, w))
+    b = np.ascontiguousarray(bias, np.float32).ravel() if bias is not None else None
+    cap = out_c * ((in_h + 2) * max(stride, 1) + k + 2 * pad) * ((in_w + 2) * max(stride, 1) + k + 2 * pad)
+    out = np.empty(cap, np.float32)
+    n = C.c_ulonglong(0)
+    fp = C.POINTER(C.c_float)
+    _check(lib().mimir_ref_compute_conv2d(C.c_int(1 if transposed else 0), x.ctypes.data_as(fp), w.ctypes.data_as(fp),
+                                          b.ctypes.data_as(fp) if b is not None else None, out.ctypes.data_as(fp), C.c_ulonglong(cap), C.byref(n),
+                                          C.c_int(in_h), C.c_int(in_w), C.c_int(in_c), C.c_int(out_c), C.c_int(k), C.c_int(stride), C.c_int(pad), C.c_int(dil)))
+    return out[: n.value].copy()
+
+
+def compute_batchnorm_training(x, gamma, beta, batch: int, channels: int, spatial: int, eps: float = 1e-5) -> np.ndarray:
+    """Model::computeBatchNorm, software branch, training = true."""
+    d = np.array(x, np.float32).ravel().copy()
+    g, b = (np.ascontiguousarray(a, np.float32).ravel() for a in (gamma, beta))
+    fp = C.POINTER(C.c_float)
+    _check(lib().mimir_ref_compute_batchnorm_training(d.ctypes.data_as(fp), g.ctypes.data_as(fp), b.ctypes.data_as(fp), C.c_int(batch),
+                                                      C.c_int(channels), C.c_int(spatial), C.c_float(eps)))
+    return d
+
+
+def compute_activation(name: str, x, param: float = 0.0) -> np.ndarray:
+    """Model::computeActivation, software branch."""
+    d = np.array(x, np.float32).ravel().copy()
+    _check(lib().mimir_ref_compute_activation(name.encode(), d.ctypes.data_as(C.POINTER(C.c_float)), C.c_ulonglong(d.size), C.c_float(param)))
+    return d

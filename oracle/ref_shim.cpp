@@ -22,6 +22,7 @@
 #include <vector>
 
 #include "Model.hpp"
+#include "LayerOpsExt.hpp"
 #include "MemoryGuard.hpp"
 #include "Models/Registry/ModelArchitectures.hpp"
 #include "Serialization/SafeTensorsWriter.hpp"
@@ -201,6 +202,62 @@ int mimir_ref_compute_batchnorm(float* data, const float* gamma, const float* be
         vv(var, var + channels);
     Model::computeBatchNorm(d, g, b, m, vv, batch, channels, spatial, eps, false, false);
     std::memcpy(data, d.data(), n * sizeof(float));
+  });
+}
+
+// Model::computeConv2D / computeConvTranspose2D (Model.cpp:3880-3888, 4214-4221), Model::computeBatchNorm with training = true
+// (software branch) and Model::computeActivation("elu").  out_len returns the element count the reference produced.
+int mimir_ref_compute_conv2d(int transposed, const float* x, const float* w, const float* bias, float* out, unsigned long long cap,
+                             unsigned long long* out_len, int in_h, int in_w, int in_c, int out_c, int k, int stride, int pad, int dil) {
+  return guarded([&] {
+    Model::LayerParams p;
+    p.weights.assign(w, w + static_cast<size_t>(out_c) * in_c * k * k);
+    if (bias) p.bias.assign(bias, bias + out_c);
+    p.kernel_size = k;
+    p.stride = stride;
+    p.padding = pad;
+    p.dilation = dil;
+    const std::vector<float> in(x, x + static_cast<size_t>(in_c) * in_h * in_w);
+    std::vector<float> y;
+    if (transposed) Model::computeConvTranspose2D(in, y, p, in_h, in_w, in_c, out_c, false);
+    else Model::computeConv2D(in, y, p, in_h, in_w, in_c, out_c, false);
+    if (out_len) *out_len = y.size();
+    if (y.size() > cap) throw std::runtime_error("compute_conv2d: output capacity too small");
+    std::memcpy(out, y.data(), y.size() * sizeof(float));
+  });
+}
+int mimir_ref_compute_batchnorm_training(float* data, const float* gamma, const float* beta, int batch, int channels, int spatial,
+                                         float eps) {
+  return guarded([&] {
+    const size_t n = static_cast<size_t>(batch) * channels * spatial;
+    std::vector<float> d(data, data + n), g(gamma, gamma + channels), b(beta, beta + channels), m(channels, 0.0f), vv(channels, 1.0f);
+    Model::computeBatchNorm(d, g, b, m, vv, batch, channels, spatial, eps, true, false);
+    std::memcpy(data, d.data(), n * sizeof(float));
+  });
+}
+int mimir_ref_compute_activation(const char* name, float* data, unsigned long long n, float param) {
+  return guarded([&] {
+    std::vector<float> d(data, data + n);
+    Model::computeActivation(d, name, param, false);
+    std::memcpy(data, d.data(), n * sizeof(float));
+  });
+}
+
+// LayerOpsExt::maxpool1d_forward (LayerOpsExt.hpp:504-538).  The layer switch of Model::forwardPassView has no case that
+// calls it (a MaxPool1d layer throws there), so it is reached directly.
+int mimir_ref_maxpool1d(const float* x, unsigned long long n, int in_channels, int kernel_h, int stride_h, int pad_h, float* out,
+                        unsigned long long cap, unsigned long long* out_len) {
+  return guarded([&] {
+    Layer L;
+    L.in_channels = in_channels;
+    L.kernel_h = kernel_h;
+    L.stride_h = stride_h;
+    L.pad_h = pad_h;
+    const std::vector<float> in(x, x + n);
+    const std::vector<float> y = LayerOpsExt::maxpool1d_forward(in, L);
+    if (out_len) *out_len = y.size();
+    if (y.size() > cap) throw std::runtime_error("maxpool1d: output capacity too small");
+    std::memcpy(out, y.data(), y.size() * sizeof(float));
   });
 }
 

@@ -105,6 +105,30 @@ def cases():
     add("reparameterize_inference", [make_desc("r", "Reparameterize", inputs=["x", "lv"])], [None], {"x": f(20), "lv": f(20)})
     add("squeeze_unsqueeze", [make_desc("a", "Squeeze"), make_desc("b", "Unsqueeze")], [None, None], {"x": f(12)})
     add("stack2", [make_desc("s", "Stack", inputs=["x", "y"])], [None], {"x": f(7), "y": f(7)})
+    # the layer types whose fields arrived with descriptor version 3, and the recurrent layers
+    tb = f(30 * 6)
+    add("embedding_bag_offsets", [make_desc("e", "EmbeddingBag", inputs=["ids", "offs"], vocab_size=30, embed_dim=6, padding_idx=4, params_count=180)], [tb],
+        {"ids": np.array([1, 4, 29, 30, -2, 7.4, 7.5, 3, 3, 12, 0], np.float32), "offs": np.array([0, 3, 3, 8, 40], np.float32)})
+    add("embedding_bag_unsorted_offsets", [make_desc("e", "EmbeddingBag", inputs=["ids", "offs"], vocab_size=30, embed_dim=6, params_count=180)], [tb],
+        {"ids": np.array([5, 6, 7, 8, 9, 10], np.float32), "offs": np.array([-3, 4, 2, 6], np.float32)})
+    add("embedding_bag_single_bag", [make_desc("e", "EmbeddingBag", inputs=["ids"], vocab_size=30, embed_dim=6, params_count=180)], [tb],
+        {"ids": np.array([2, 2, 19, 11], np.float32)})
+    dm, stx, npch, pdim = 12, 3, 5, 48
+    add("patch_embed", [make_desc("p", "PatchEmbed", embed_dim=dm, seq_text=stx, num_patches=npch, patch_dim=pdim, params_count=pdim * dm + dm)],
+        [f(pdim * dm + dm, scale=0.3)], {"x": f((stx + 1) * dm + npch * pdim)})
+    add("patch_embed_out_features", [make_desc("p", "PatchEmbed", out_features=dm, seq_text=stx, num_patches=2, patch_dim=7, params_count=7 * dm + dm)],
+        [f(7 * dm + dm, scale=0.3)], {"x": f((stx + 1) * dm + 2 * 7)})
+    add("bilinear_bias", [make_desc("b", "Bilinear", inputs=["x", "z"], in_features=9, out_features=14, embed_dim=5, use_bias=1, params_count=5 * 9 * 14 + 5)],
+        [f(5 * 9 * 14 + 5, scale=0.3)], {"x": f(4 * 9), "z": f(4 * 14)})
+    add("bilinear_target_shape_nobias", [make_desc("b", "Bilinear", inputs=["x", "z"], in_features=6, out_features=3, target_dim0=7, use_bias=0, params_count=7 * 18)],
+        [f(7 * 18, scale=0.3)], {"x": f(6), "z": f(3)})
+    T, I, H = 6, 10, 13
+    for kind, g in (("RNN", 1), ("GRU", 3), ("LSTM", 4)):
+        nw = g * H * I + g * H * H
+        add(f"{kind.lower()}_bias", [make_desc("r", kind, seq_len=T, in_features=I, out_features=H, use_bias=1, params_count=nw + 2 * g * H)],
+            [f(nw + 2 * g * H, scale=0.35)], {"x": f(T * I)})
+        add(f"{kind.lower()}_nobias", [make_desc("r", kind, seq_len=3, in_features=4, out_features=5, use_bias=0, params_count=g * 5 * 4 + g * 25)],
+            [f(g * 5 * 4 + g * 25, scale=0.5)], {"x": f(12)})
     add("avgpool1d_k3s2p1", [make_desc("p", "AvgPool1d", in_channels=3, raw_kernel_h=3, raw_stride_h=2, raw_pad_h=1)], [None], {"x": f(3 * 17)})
     return out
 
@@ -125,6 +149,18 @@ def transformer_case():
     ids = np.array([5, 0, 49, 17, 3, 3, 21, 8], np.float32)
     y = m.forward({"x": ids, "mag": mag, "mod": mod})
     return "transformer_registry_tiny", ours, weights, {"x": ids, "mag": mag, "mod": mod}, y
+
+
+def function_cases():
+    """Layer functions of the reference that its layer switch never dispatches, called directly."""
+    r = np.random.default_rng(77)
+    out = []
+    # LayerOpsExt::maxpool1d_forward (LayerOpsExt.hpp:504-538): a MaxPool1d layer throws in Model::forwardPassView
+    for nm, ch, length, k, st, pad in (("maxpool1d_k3s2p1", 3, 17, 3, 2, 1), ("maxpool1d_default_stride", 2, 9, 2, 0, 0), ("maxpool1d_k4s1p3", 1, 6, 4, 1, 3)):
+        x = r.standard_normal(ch * length).astype(np.float32)
+        d = make_desc("p", "MaxPool1d", in_channels=ch, raw_kernel_h=k, raw_stride_h=st, raw_pad_h=pad)
+        out.append((nm, [d], [None], {"x": x}, ref.maxpool1d(x, ch, k, st, pad)))
+    return out
 
 
 def _compact(j):
@@ -187,6 +223,8 @@ def main():
         index.append(_store(arrays, name, descs, weights, inputs, y))
     name, descs, weights, inputs, y = transformer_case()
     index.append(_store(arrays, name, descs, weights, inputs, y))
+    for name, descs, weights, inputs, y in function_cases():
+        index.append(_store(arrays, name, descs, weights, inputs, y))
     np.savez_compressed(os.path.join(HERE, "reference_vectors.npz"), **arrays)
     with open(os.path.join(HERE, "reference_vectors.json"), "w") as fh:
         json.dump({"generator": "tests/golden/make_golden.py", "source": "compiled reference (oracle/_ref), forwardPassNamed(training=false)",

@@ -64,6 +64,14 @@ def reference_kats():
     # Embedding (float ids), :511-535
     k.append(("embedding", [make_desc("t0", "Embedding", inputs=["x"], vocab_size=3, embed_dim=2, padding_idx=-1, params_count=6)],
               [f(0, 0, 1, 10, 2, 20)], {"x": f(1, 2)}, f(1, 10, 2, 20), 1e-6))
+    # EmbeddingBag: ids [1, 2, 1], offsets [0, 2, 3] -> bag0 = tok1 + tok2, bag1 = tok1, :537-554
+    k.append(("embedding_bag", [make_desc("t0", "EmbeddingBag", inputs=["ids", "offs"], vocab_size=3, embed_dim=2, padding_idx=-1, params_count=6)],
+              [f(0, 0, 1, 10, 2, 20)], {"ids": f(1, 2, 1), "offs": f(0, 2, 3)}, f(3, 30, 1, 10), 1e-6))
+    # recurrent layers with zero weights -> zero output, :598-648
+    for kind, g in (("RNN", 1), ("GRU", 3), ("LSTM", 4)):
+        nw = g * 4 * 3 + g * 4 * 4 + 2 * g * 4
+        k.append((f"{kind.lower()}_zero_weights", [make_desc("r", kind, inputs=["x"], seq_len=2, in_features=3, out_features=4, use_bias=1, params_count=nw)],
+                  [np.zeros(nw, np.float32)], {"x": f(1, 2, 3, 4, 5, 6)}, np.zeros(8, np.float32), 1e-6))
     # Embedding with padding_idx = 0 -> zero row, test_runtime_embedding_int_inputs.cpp:44-62 (ids 1, 0, 2)
     table = np.arange(12, dtype=np.float32)
     table[:] = [0, 1, 2, 3, 10, 11, 12, 13, 20, 21, 22, 23]

@@ -56,7 +56,7 @@ int main(void) {
 
 
 def test_abi_version():
-    assert runtime.lib().mimir_b200_abi_version() == 2
+    assert runtime.lib().mimir_b200_abi_version() == 3
 
 
 def _has_gpu():

@@ -49,7 +49,9 @@ def test_backend_layernorm_mean_variance_property(backend):
 BATCHED = ["cross_attention_causal0", "cross_attention_causal1", "split_concat", "chunk_concat", "depthwise_conv_s2_bias", "conv1d_s2_bias",
            "conv_transpose2d_relu", "maxpool_k3s2p1", "avgpool_k3s1p1", "zeropad2d", "reflectionpad2d", "replicationpad2d",
            "pixel_shuffle_r2", "upsamplebilinear", "upsamplebicubic", "matmul", "batch_matmul", "batchnorm_partial_weights",
-           "instance_norm_affine", "leaky_relu_02", "mish", "divide_small_divisors", "transpose_2d"]
+           "instance_norm_affine", "leaky_relu_02", "mish", "divide_small_divisors", "transpose_2d",
+           "embedding_bag_offsets", "embedding_bag_single_bag", "patch_embed", "bilinear_bias", "rnn_bias", "gru_bias", "lstm_bias",
+           "maxpool1d_k3s2p1"]
 
 
 @pytest.mark.parametrize("name", BATCHED)

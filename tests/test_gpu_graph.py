@@ -111,7 +111,7 @@ def test_named_routing_and_missing_input(backend):
 
 def test_unsupported_layer_type_is_an_error_not_a_fallback(backend):
     with pytest.raises(backend.MimirB200Error) as e:
-        backend.GraphModel([make_desc("l", "LSTM")])
+        backend.GraphModel([make_desc("l", "Lambda")])  # throws in the reference's switch too (Model.cpp:5703-5709)
     assert e.value.status == abi.E_UNSUPPORTED
 
 

@@ -341,6 +341,49 @@ def test_batchnorm_with_running_statistics(backend, batch, ch, spatial):
     assert_close(backend.batchnorm_running(x, g, b, m, var, batch, ch, spatial), want, f"batchnorm_running {batch}x{ch}x{spatial}")
 
 
+@pytest.mark.parametrize("batch,ch,spatial", [(1, 1, 2), (3, 5, 17), (4, 64, 49), (2, 7, 3000)])
+def test_batchnorm_with_batch_statistics(backend, batch, ch, spatial):
+    """Model::computeBatchNorm with training = true (Layers.hpp:940-959): statistics from the batch itself."""
+    r = rng(ch * spatial + 1)
+    x = (r.standard_normal(batch * ch * spatial) * 3 + 1).astype(np.float32)
+    g, b = (r.standard_normal(ch).astype(np.float32) for _ in range(2))
+    want = port.batchnorm_batchstats(x, g, b, batch, ch, spatial, 1e-5)
+    np.testing.assert_allclose(backend.batchnorm_batchstats(x, g, b, batch, ch, spatial), want, atol=2e-5, rtol=2e-5)
+
+
+@pytest.mark.parametrize("ic,oc,h,wd,k,st,pad,dil,bias", [(3, 5, 9, 11, 3, 1, 1, 1, True), (2, 4, 12, 10, 3, 2, 2, 2, True), (4, 3, 7, 7, 1, 1, 0, 1, False),
+                                                           (1, 2, 15, 13, 5, 3, 4, 3, True), (2, 2, 20, 20, 9, 1, 4, 1, False), (16, 8, 32, 32, 3, 1, 2, 2, True)])
+def test_static_conv2d_with_bias_and_dilation(backend, ic, oc, h, wd, k, st, pad, dil, bias):
+    """Model::computeConv2D -> Conv::conv2d, scalar branch (Layers.hpp:690-721); two samples at once."""
+    r = rng(ic * h * wd + k)
+    x = r.standard_normal(2 * ic * h * wd).astype(np.float32)
+    w = (r.standard_normal(oc * ic * k * k) * 0.3).astype(np.float32)
+    b = r.standard_normal(oc).astype(np.float32) if bias else None
+    n = ic * h * wd
+    want = np.concatenate([port.conv2d_dilated(x[s * n:(s + 1) * n], w, b, ic, oc, h, wd, k, st, pad, dil) for s in range(2)])
+    np.testing.assert_allclose(backend.conv2d_dilated(x, w, b, 2, ic, oc, h, wd, k, st, pad, dil), want, atol=1e-5, rtol=2e-5)
+
+
+@pytest.mark.parametrize("ic,oc,h,wd,k,st,pad,bias", [(3, 4, 5, 6, 4, 2, 1, True), (2, 3, 7, 5, 3, 1, 0, False), (1, 2, 4, 4, 2, 3, 0, True), (4, 2, 6, 6, 3, 2, 2, True),
+                                                       (8, 8, 16, 16, 5, 3, 1, True)])
+def test_static_conv_transpose2d_scatter_form(backend, ic, oc, h, wd, k, st, pad, bias):
+    """Model::computeConvTranspose2D -> Conv::conv_transpose2d (Layers.hpp:775-818); two samples at once."""
+    r = rng(ic * h * wd + k + 5)
+    x = r.standard_normal(2 * ic * h * wd).astype(np.float32)
+    w = (r.standard_normal(oc * ic * k * k) * 0.3).astype(np.float32)
+    b = r.standard_normal(oc).astype(np.float32) if bias else None
+    n = ic * h * wd
+    want = np.concatenate([port.conv_transpose2d_scatter(x[s * n:(s + 1) * n], w, b, ic, oc, h, wd, k, st, pad) for s in range(2)])
+    np.testing.assert_allclose(backend.conv_transpose2d_scatter(x, w, b, 2, ic, oc, h, wd, k, st, pad), want, atol=1e-5, rtol=2e-5)
+
+
+def test_elu_of_the_static_family(backend):
+    """Model::elu_inplace (Model.hpp:505-509) behind computeActivation("elu")."""
+    x = (rng(3).standard_normal(5000) * 3).astype(np.float32)
+    got = backend.eltwise_alpha(abi.ELT_ELU, x, 1.3)
+    np.testing.assert_allclose(got, port.elu(x, 1.3), atol=1e-6, rtol=1e-6)
+
+
 def test_gemm_output_through_tma_stores():
     """MIMIR_B200_GEMM_TMA_STORE=1 routes row-major fp32 GEMM outputs through shared-memory staging and TMA stores
     (off by default: measured neutral).  The switch is read once per process, so the Linear, MatMul and attention

@@ -14,7 +14,9 @@ KATS = reference_kats()
 # integer / index / pure data-movement cases must be bit-exact
 BITEXACT = {"embedding_pad_oob_round", "upsample_nearest", "permute_201", "concat3", "relu", "add_broadcast", "add_scalar", "multiply",
             "split_concat", "chunk_concat", "maxpool_k3s2p1", "zeropad2d", "reflectionpad2d", "replicationpad2d", "pixel_shuffle_r2",
-            "leaky_relu_02", "subtract", "transpose_2d", "reparameterize_inference", "squeeze_unsqueeze", "stack2"}
+            "leaky_relu_02", "subtract", "transpose_2d", "reparameterize_inference", "squeeze_unsqueeze", "stack2",
+            "embedding_bag_offsets", "embedding_bag_unsorted_offsets", "embedding_bag_single_bag", "maxpool1d_k3s2p1",
+            "maxpool1d_default_stride", "maxpool1d_k4s1p3"}
 
 
 @pytest.mark.parametrize("case", KATS, ids=[k[0] for k in KATS])
@@ -60,6 +62,13 @@ def test_compiled_reference_reproduces_committed_vectors(case):
     for i, w in enumerate(weights):
         if w is not None:
             m.set_weights(i, w)
+    if descs[0].type == b"MaxPool1d":
+        # the reference's layer switch has no case for it: the layer throws, its function is reached directly
+        with pytest.raises(RuntimeError, match="UNKNOWN"):
+            m.forward(inputs)
+        d = descs[0]
+        assert np.array_equal(ref.maxpool1d(inputs["x"], d.in_channels, d.raw_kernel_h, d.raw_stride_h, d.raw_pad_h), want), name
+        return
     assert np.array_equal(m.forward(inputs), want), name
 
 
@@ -87,3 +96,40 @@ def test_port_of_the_legacy_static_ops_matches_the_compiled_reference():
         var = (r.random(ch) + 0.05).astype(np.float32)
         np.testing.assert_allclose(port.batchnorm_running(x, g, b, m, var, batch, ch, spatial, 1e-5),
                                    ref.compute_batchnorm(x, g, b, m, var, batch, ch, spatial, 1e-5), atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.skipif(not ref.available(), reason="compiled reference (oracle/_ref) not built here")
+def test_port_of_the_static_conv_family_matches_the_compiled_reference():
+    """Model::computeConv2D (bias, dilation), computeConvTranspose2D (scatter form), computeBatchNorm with training = true and
+    computeActivation("elu") against their plain-C restatements."""
+    r = np.random.default_rng(11)
+    for ic, oc, h, wd, k, st, pad, dil, bias in [(3, 5, 9, 11, 3, 1, 1, 1, True), (2, 4, 12, 10, 3, 2, 2, 2, True), (4, 3, 7, 7, 1, 1, 0, 1, False),
+                                                  (1, 2, 15, 13, 5, 3, 4, 3, True), (2, 2, 20, 20, 9, 1, 4, 1, False)]:
+        x = r.standard_normal(ic * h * wd).astype(np.float32)
+        w = (r.standard_normal(oc * ic * k * k) * 0.3).astype(np.float32)
+        b = r.standard_normal(oc).astype(np.float32) if bias else None
+        # the compiled reference is an AVX2 build: its Conv::conv2d counts every remainder tap eight times (Layers.hpp:658-666)
+        want = ref.compute_conv2d(x, w, b, h, wd, ic, oc, k, st, pad, dil)
+        got = port.conv2d_dilated(x, w, b, ic, oc, h, wd, k, st, pad, dil, avx2_lanes=True)
+        assert got.shape == want.shape
+        np.testing.assert_allclose(got, want, atol=5e-5, rtol=5e-5)
+        if k < 8:  # then every tap is a remainder tap: 8 x the scalar branch's sum, plus the bias
+            scalar = port.conv2d_dilated(x, w, b, ic, oc, h, wd, k, st, pad, dil)
+            bb = np.repeat(b, scalar.size // oc) if b is not None else 0.0
+            np.testing.assert_allclose(8.0 * (scalar - bb) + bb, want, atol=5e-5, rtol=5e-5)
+    for ic, oc, h, wd, k, st, pad, bias in [(3, 4, 5, 6, 4, 2, 1, True), (2, 3, 7, 5, 3, 1, 0, False), (1, 2, 4, 4, 2, 3, 0, True), (4, 2, 6, 6, 3, 2, 2, True)]:
+        x = r.standard_normal(ic * h * wd).astype(np.float32)
+        w = (r.standard_normal(oc * ic * k * k) * 0.3).astype(np.float32)
+        b = r.standard_normal(oc).astype(np.float32) if bias else None
+        want = ref.compute_conv2d(x, w, b, h, wd, ic, oc, k, st, pad, transposed=True)
+        got = port.conv_transpose2d_scatter(x, w, b, ic, oc, h, wd, k, st, pad)
+        assert got.shape == want.shape
+        np.testing.assert_allclose(got, want, atol=5e-6, rtol=2e-5)
+    for batch, ch, spatial in [(1, 1, 2), (3, 5, 17), (4, 16, 64)]:
+        x = (r.standard_normal(batch * ch * spatial) * 2 + 0.5).astype(np.float32)
+        g, b = (r.standard_normal(ch).astype(np.float32) for _ in range(2))
+        np.testing.assert_allclose(port.batchnorm_batchstats(x, g, b, batch, ch, spatial, 1e-5),
+                                   ref.compute_batchnorm_training(x, g, b, batch, ch, spatial, 1e-5), atol=2e-6, rtol=2e-6)
+    x = (r.standard_normal(300) * 3).astype(np.float32)
+    np.testing.assert_allclose(port.elu(x, 1.3), ref.compute_activation("elu", x, 1.3), atol=1e-6, rtol=1e-6)
+    assert np.array_equal(ref.compute_activation("no_such_activation", x), x)  # an unknown name leaves the data alone

@@ -53,14 +53,33 @@ int main() {
   a = x;
   computeLayerNorm(a, g, b, 8, 1e-5f);
   dump("layernorm", a);
-  try { computeActivation(a, "elu", 1.0f); std::printf("elu no-throw\n"); } catch (const std::exception& e) { std::printf("elu throws\n"); }
+  a = x;
+  computeActivation(a, "elu", 1.3f);
+  dump("elu", a);
+  a = x;
+  computeActivation(a, "no_such_activation");
+  dump("unknown_activation", a);
   { std::vector<float> o, kk(x.rbegin(), x.rend()); computeAttention(x, kk, x, o, 5, 8, 2); dump("attention", o); }
   {
     std::vector<float> d = x, gm{1.5f, -0.5f}, bt{0.1f, 0.2f}, mu{0.25f, -0.75f}, vr{0.5f, 2.0f};
     computeBatchNorm(d, gm, bt, mu, vr, 4, 2, 5, 1e-5f);
     dump("batchnorm", d);
-    try { computeBatchNorm(d, gm, bt, mu, vr, 4, 2, 5, 1e-5f, true); std::printf("bn_training no-throw\n"); }
-    catch (const std::exception& e) { std::printf("bn_training throws\n"); }
+    d = x;
+    computeBatchNorm(d, gm, bt, mu, vr, 4, 2, 5, 1e-5f, true);
+    dump("bn_training", d);
+  }
+  {
+    // 2 x 5 x 4 input, 3 output channels, 3 x 3 kernel, stride 2, padding 2, dilation 2, with bias
+    LayerParams cp;
+    cp.kernel_size = 3; cp.stride = 2; cp.padding = 2; cp.dilation = 2;
+    cp.weights.resize(3 * 2 * 9); cp.bias = {0.5f, -0.25f, 0.125f};
+    for (size_t i = 0; i < cp.weights.size(); ++i) cp.weights[i] = 0.05f * static_cast<float>((i * 11) % 19) - 0.4f;
+    std::vector<float> o;
+    computeConv2D(x, o, cp, 5, 4, 2, 3);
+    dump("conv2d", o);
+    cp.dilation = 1; cp.padding = 1;
+    computeConvTranspose2D(x, o, cp, 5, 4, 2, 3);
+    dump("conv_transpose2d", o);
   }
   mimir_b200_shutdown();
   return 0;
@@ -89,7 +108,7 @@ def test_static_ops_against_the_oracle(tmp_path):
     got = {}
     for line in out.splitlines():
         name, *vals = line.split()
-        got[name] = np.array([float(v) for v in vals], np.float32) if vals and name not in ("elu", "bn_training") else " ".join(vals)
+        got[name] = np.array([float(v) for v in vals], np.float32)
     x = np.array([0.25 * ((i * 7) % 11) - 1.0 for i in range(40)], np.float32)
     w = np.array([0.01 * ((i * 13) % 17) - 0.05 for i in range(240)], np.float32)
     b = np.array([0.1 * i for i in range(6)], np.float32)
@@ -106,4 +125,10 @@ def test_static_ops_against_the_oracle(tmp_path):
     np.testing.assert_allclose(got["attention"], port.attention_qkv(x, x[::-1].copy(), x, 5, 8, 2), atol=1e-5, rtol=1e-4)
     np.testing.assert_allclose(got["batchnorm"], port.batchnorm_running(x, [1.5, -0.5], [0.1, 0.2], [0.25, -0.75], [0.5, 2.0], 4, 2, 5, 1e-5),
                                atol=1e-6, rtol=1e-6)
-    assert got["elu"] == "throws" and got["bn_training"] == "throws"
+    np.testing.assert_allclose(got["elu"], port.elu(x, 1.3), atol=1e-6, rtol=1e-6)
+    assert np.array_equal(got["unknown_activation"], x)
+    np.testing.assert_allclose(got["bn_training"], port.batchnorm_batchstats(x, [1.5, -0.5], [0.1, 0.2], 4, 2, 5, 1e-5), atol=2e-6, rtol=2e-6)
+    cw = np.array([0.05 * ((i * 11) % 19) - 0.4 for i in range(54)], np.float32)
+    cb = np.array([0.5, -0.25, 0.125], np.float32)
+    np.testing.assert_allclose(got["conv2d"], port.conv2d_dilated(x, cw, cb, 2, 3, 5, 4, 3, 2, 2, 2), atol=2e-6, rtol=1e-5)
+    np.testing.assert_allclose(got["conv_transpose2d"], port.conv_transpose2d_scatter(x, cw, cb, 2, 3, 5, 4, 3, 2, 1), atol=2e-6, rtol=1e-5)
