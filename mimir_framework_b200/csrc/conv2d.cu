@@ -94,22 +94,28 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* _
   const bool row_in = y >= 0 && y < h;
   const float* src = x + ((static_cast<long long>(n) * c + cb) * h + (row_in ? y : 0)) * w;
   const long long ch_stride = static_cast<long long>(h) * w;
-  // this thread's 16 elements of a tile belong to 16 fixed channels: their scale / shift once per CTA
+  // scale / shift of the CTA's 64 channels once, in shared memory; a thread's 16 elements of a tile belong to 16 fixed
+  // channels ((tid >> 6) + 4 i), so it keeps those 16 pairs in registers for every tile of the row
+  __shared__ float2 s_aff[TP_C];
   float sc[16], sh[16];
   if (pre.stats != nullptr) {
-    const int cpg = c / pre.groups;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const int ch = cb + ((threadIdx.x + 256 * i) >> 6);
-      sc[i] = 0.0f; sh[i] = 0.0f;
+    if (threadIdx.x < TP_C) {
+      const int ch = cb + threadIdx.x;
+      float2 a = make_float2(0.0f, 0.0f);
       if (ch < c) {
-        const float* st = pre.stats + (static_cast<long long>(n) * pre.groups + ch / cpg) * 2;
+        const float* st = pre.stats + (static_cast<long long>(n) * pre.groups + ch / (c / pre.groups)) * 2;
         const float mean = __ldg(st), inv = __ldg(st + 1);
         const float g = pre.gamma != nullptr ? __ldg(pre.gamma + ch) : 1.0f;
         const float b = (pre.gamma != nullptr && pre.beta != nullptr) ? __ldg(pre.beta + ch) : 0.0f;
-        sc[i] = inv * g;
-        sh[i] = b - mean * inv * g;
+        a = make_float2(inv * g, b - mean * inv * g);
       }
+      s_aff[threadIdx.x] = a;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float2 a = s_aff[(threadIdx.x >> 6) + 4 * i];
+      sc[i] = a.x; sh[i] = a.y;
     }
   }
   for (int x0 = 0; x0 < wp; x0 += TP_X) {

@@ -282,21 +282,13 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         float* tbuf = reinterpret_cast<float*>(epi_tiles) + ew * (32 * 33);
         const int oc0 = row0;  // first output channel of this warp's 32 lanes
         const long long hw = (p.conv_ks > 0) ? static_cast<long long>(p.conv_h) * p.conv_w : static_cast<long long>(p.ohw);
-#pragma unroll 1
-        for (int ci = 0; ci < (BN / 32) / 2; ++ci) {
-          const int c0 = (half * (BN / 64) + ci) * 32;
+        // where this lane's pixel of chunk ci lands in the NCHW output; false = the chunk is past the matrix (warp-uniform)
+        auto geom = [&](int ci, int& c0, bool& pv, long long& o0) -> bool {
+          c0 = (half * (BN / 64) + ci) * 32;
           const int r0 = tn * BN + c0;
-          if (r0 >= p.m || oc0 >= p.n) break;  // warp-uniform
-          float v[32];
-          tmem_ld_32x32(taddr0 + c0, v);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) tbuf[j * 33 + lane] = v[j] * p.acc_scale;  // [pixel][channel]
-          __syncwarp();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = tbuf[lane * 33 + j];  // lane = pixel r0 + lane, j = channel oc0 + j
-          __syncwarp();
+          if (r0 >= p.m || oc0 >= p.n) return false;
           const int prow = r0 + lane;
-          bool pv = prow < p.m;
+          pv = prow < p.m;
           long long pbase = 0;
           if (p.conv_ks > 0) {
             const int per = p.conv_hp * p.conv_wp;
@@ -309,17 +301,45 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const long long smp = prow / p.ohw;
             pbase = smp * p.n * hw + (prow - smp * p.ohw);
           }
+          o0 = pbase + static_cast<long long>(oc0) * hw;
+          return true;
+        };
+        const bool full = oc0 + 32 <= p.n;
+        // With a short K the epilogue, not the MMA, sets the pace.  The residual of a chunk is requested before the chunk
+        // is read out of tensor memory and turned around, and the lines of the next chunk are pulled into L2 meanwhile, so
+        // that the loads do not each wait a full memory latency.
+        constexpr int NCH = (BN / 32) / 2;
+#pragma unroll 1
+        for (int ci = 0; ci < NCH; ++ci) {
+          int c0; bool pv; long long o0;
+          if (!geom(ci, c0, pv, o0)) break;
+          float q[32];
+          if (p.residual != nullptr) {
+            if (pv) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) q[j] = (full || oc0 + j < p.n) ? __ldg(p.residual + o0 + j * hw) : 0.0f;
+            }
+            int c1; bool pv1; long long o1;
+            if (ci + 1 < NCH && geom(ci + 1, c1, pv1, o1) && pv1) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (full || oc0 + j < p.n) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + o1 + j * hw));
+            }
+          }
+          float v[32];
+          tmem_ld_32x32(taddr0 + c0, v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tbuf[j * 33 + lane] = v[j] * p.acc_scale;  // [pixel][channel]
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = tbuf[lane * 33 + j];  // lane = pixel r0 + lane, j = channel oc0 + j
+          __syncwarp();
           if (p.activation != -1) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.activation);
           }
           if (pv) {
-            const long long o0 = pbase + static_cast<long long>(oc0) * hw;
-            const bool full = oc0 + 32 <= p.n;
             if (p.residual != nullptr) {
-              float q[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) q[j] = (full || oc0 + j < p.n) ? __ldg(p.residual + o0 + j * hw) : 0.0f;
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] += q[j];
             }

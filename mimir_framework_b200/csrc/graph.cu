@@ -902,6 +902,10 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     if (C.lt != LT::Conv2d || C.skip || C.pre_norm >= 0 || C.in_v[0] != pv) continue;
     if (!conv_uses_shifted(C.d.in_channels, C.d.kernel, C.d.stride, C.d.padding)) continue;
     if (C.d.in_channels != P.ch || C.h != P.h || C.w != P.w) continue;
+    // a convolution that takes the direct fp32 kernel reads the normalised tensor itself: it has no layout pass to fold into
+    if (conv_small_oc_supported(C.d.out_channels, C.d.kernel, C.d.stride, C.d.padding, C.h, C.w, batch,
+                                C.d.activation ? MIMIR_B200_ELT_RELU : C.fused_act))
+      continue;
     const int xin = P.in_v[0];
     C.pre_norm = li;
     C.in_v[0] = xin;
