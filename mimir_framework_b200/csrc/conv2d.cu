@@ -29,17 +29,22 @@ __global__ void im2col_split_kernel(const float* __restrict__ x, __nv_bfloat16* 
     const float* xs = x + smp * ic * h * w;
     __align__(16) uint16_t hi[8];
     __align__(16) uint16_t lo[8];
+    // (ci, ky, kx) of the chunk's first entry by division, of the other seven by stepping
+    int ci = (c * 8) / kk, t = c * 8 - ci * kk;
+    int ky = t / ks, kx = t - ky * ks;
+    const int iy0 = oy * stride - pad, ix0 = ox * stride - pad;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int kidx = c * 8 + j;
       float v = 0.0f;
-      if (kidx < k) {
-        const int ci = kidx / kk, t = kidx - ci * kk;
-        const int ky = t / ks, kx = t - ky * ks;
-        const int iy = oy * stride + ky - pad, ix = ox * stride + kx - pad;
+      if (c * 8 + j < k) {
+        const int iy = iy0 + ky, ix = ix0 + kx;
         if (iy >= 0 && iy < h && ix >= 0 && ix < w) v = __ldg(xs + (static_cast<long long>(ci) * h + iy) * w + ix);
       }
       split_one(v, f16, hi[j], lo[j]);
+      if (++kx == ks) {
+        kx = 0;
+        if (++ky == ks) { ky = 0; ++ci; }
+      }
     }
     __nv_bfloat16* d = dst + r * kp + c * 8;
     *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(hi);

@@ -74,6 +74,7 @@ struct GemmParams {
   __nv_bfloat16* out_split;  // [2][m][np]
   long long np;              // round_up(n, 64)
   int ohw;                   // > 0: fp32 output (and residual) are NCHW, row = sample * ohw + pixel
+  int bn;                    // columns of an output tile = N of one MMA: BN, or 192 on request (plain row-major form only)
   // Convolution as a sum of shifted GEMMs (conv_ks > 0): A is the zero-padded NHWC activation matrix
   // [samples * hp * wp, C]; k-block kb belongs to tap t = kb / conv_cblocks and reads A rows shifted by
   // (kh - pad) * wp + (kw - pad); output rows live on the padded grid, border rows are dropped.
@@ -165,7 +166,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   // planes on the M side (128-row tiles) and on the N side (256-row tiles) of the MMA
   const int m_planes = p.swap ? p.w_planes : p.a_planes, n_planes = p.swap ? p.a_planes : p.w_planes;
-  const uint32_t tx_bytes = static_cast<uint32_t>(m_planes * A_TILE + n_planes * W_TILE);
+  const uint32_t tx_bytes = static_cast<uint32_t>(m_planes * A_TILE + n_planes * (p.bn * BK * 2));
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
@@ -191,7 +192,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int pl = 0; pl < p.a_planes; ++pl)
               tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
             for (int pl = 0; pl < p.w_planes; ++pl)
-              tma_load_3d(sbase + m_planes * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * BN, pl);
+              tma_load_3d(sbase + m_planes * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * p.bn, pl);
           } else {
             // 128 weight rows into the M-side tiles, 256 activation rows (tile tn) into the N-side tiles
             a_row += tn * BN - tm * BM;
@@ -213,7 +214,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------------------
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, BN, p.f16);
+      const uint32_t idesc = make_idesc(BM, p.bn, p.f16);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -376,9 +377,9 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         }
       }
 #pragma unroll 1
-      for (int ci = 0; ci < (BN / 32) / 2; ++ci) {
-        const int c0 = (half * (BN / 64) + ci) * 32;
-        const int col0 = tn * BN + c0;
+      for (int ci = 0; ci < (p.bn / 32) / 2; ++ci) {
+        const int c0 = (half * (p.bn / 64) + ci) * 32;
+        const int col0 = tn * p.bn + c0;
         if (col0 >= col_limit) break;  // warp-uniform
         float v[32];
         tmem_ld_32x32(taddr0 + c0, v);
@@ -638,7 +639,6 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   const bool swap = (conv || g.out_nchw_hw > 0) && g.n <= BM && g.bias == nullptr && g.out_split == nullptr && g.out_f32 != nullptr &&
                     g.m >= 4 * BN && kblocks_all * BK >= 256 && !(noswap && noswap[0] == '1');
   MB_TRY(make_plane_map(&map_a, g.a, g.a_planes, g.m, conv ? g.conv_c : kp, BK, swap ? BN : BM));
-  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : BN));
   // Optional (MIMIR_B200_GEMM_TMA_STORE=1): row-major fp32 outputs leave through TMA stores.  Measured neutral on the
   // decoder's K = 768 layers (1 078 vs 1 100 TFLOP/s issued): what slows those layers is not the shape of the stores but
   // their bytes - the operand loads alone run at ~62 B per cycle and SM, next to what an SM can take from L2, and the
@@ -651,6 +651,17 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   GemmParams p;
   p.tma_store = tma_store ? 1 : 0;
   p.swap = swap ? 1 : 0;
+  p.tiles_m = swap ? (g.n + BM - 1) / BM : (g.m + BM - 1) / BM;
+  p.bn = BN;
+  if (!swap && !conv && !tma_store) {
+    // MIMIR_B200_GEMM_BN=192: 192-column tiles.  On paper they shorten launches whose last wave is mostly empty (N = 768
+    // over 256 row tiles: 7 waves of 192 columns instead of 6 of 256, 12.5 % less work per SM); measured, the
+    // 32768 x 768 x 768 projection takes 0.076 ms either way and the K = 3072 one 0.243 against 0.251: an N = 192
+    // instruction costs the tensor pipe about what an N = 256 one does.  Kept as a switch, off by default.
+    static const int force = env_int("MIMIR_B200_GEMM_BN", 0);
+    if (force == 192) p.bn = 192;
+  }
+  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : p.bn));
   p.m = g.m;
   p.n = g.n;
   p.kblocks = conv ? g.conv_ks * g.conv_ks * (g.conv_c / BK) : kp / BK;
@@ -663,8 +674,7 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.conv_w = g.conv_w;
   p.a_planes = g.a_planes;
   p.w_planes = g.w_planes;
-  p.tiles_m = swap ? (g.n + BM - 1) / BM : (g.m + BM - 1) / BM;
-  p.tiles_n = swap ? (g.m + BN - 1) / BN : (g.n + BN - 1) / BN;
+  p.tiles_n = swap ? (g.m + BN - 1) / BN : (g.n + p.bn - 1) / p.bn;
   p.group_n = env_int("MIMIR_B200_GEMM_GROUP_N", 8);
   if (p.group_n < 1) p.group_n = 1;
   if (p.group_n > p.tiles_n) p.group_n = p.tiles_n;

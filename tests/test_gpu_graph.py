@@ -371,8 +371,8 @@ def test_repeated_forwards_replay_a_cuda_graph_with_identical_results(backend):
 
 @pytest.mark.parametrize("shared_output,fuse", [(False, "0"), (False, "1"), (True, "1")])
 def test_groupnorm_silu_applied_inside_the_convolution(backend, monkeypatch, shared_output, fuse):
-    """UNet-style ResBlock: GroupNorm -> SiLU -> Conv3x3 -> GroupNorm -> SiLU -> Conv3x3 + skip.  With
-    MIMIR_B200_FUSE_GN_CONV=1 a GroupNorm whose output feeds nothing but the convolution is folded into the
+    """UNet-style ResBlock: GroupNorm -> SiLU -> Conv3x3 -> GroupNorm -> SiLU -> Conv3x3 + skip.  Unless
+    MIMIR_B200_FUSE_GN_CONV=0, a GroupNorm whose output feeds nothing but the convolution is folded into the
     convolution's layout kernel (statistics pass + normalise on the fly); with a second consumer of the normalised
     tensor it must stay a layer of its own."""
     monkeypatch.setenv("MIMIR_B200_FUSE_GN_CONV", fuse)
