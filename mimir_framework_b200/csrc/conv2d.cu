@@ -86,7 +86,7 @@ namespace {
 // 128 contiguous bytes per pixel and plane as packed bf16x2.
 constexpr int TP_C = 64, TP_X = 64;
 
-__global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
+__global__ void __launch_bounds__(256, 3) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
                                                                   int c, int h, int w, int pad, int planes, long long plane_stride,
                                                                   const PreNorm pre, int f16) {
   __shared__ float tile[TP_C][TP_X + 1];
@@ -171,6 +171,104 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_kernel(const float* _
   }
 }
 
+// The same layout pass with 16-byte accesses on both sides, for widths that are a multiple of 4 and channel counts that
+// are a multiple of 8: tiles are aligned to the INPUT pixels (so a thread's float4 is four consecutive pixels of one
+// channel), the shift by the padding happens on the way out, where a thread owns eight consecutive channels of one pixel
+// (one 16-byte store per plane).  The padding ring is written as zeros by the CTAs of the border rows and by the first
+// and last tile of every interior row.
+__global__ void __launch_bounds__(256) nchw_to_padded_nhwc_vec_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
+                                                                      int c, int h, int w, int pad, int planes, long long plane_stride,
+                                                                      const PreNorm pre, int f16) {
+  __shared__ float tile[TP_C][TP_X + 1];
+  __shared__ float2 s_aff[TP_C];
+  const int hp = h + 2 * pad, wp = w + 2 * pad;
+  const int cb = blockIdx.x * TP_C;
+  const int yp = blockIdx.y;
+  const int n = blockIdx.z;
+  const int y = yp - pad;
+  const long long row_o = (static_cast<long long>(n) * hp + yp) * wp;  // first padded pixel of this output row
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  auto store8 = [&](long long pixel, int ch, const uint4& hi, const uint4& lo) {
+    __nv_bfloat16* o = dst + pixel * c + ch;
+    *reinterpret_cast<uint4*>(o) = hi;
+    if (planes == 2) *reinterpret_cast<uint4*>(o + plane_stride) = lo;
+  };
+  if (y < 0 || y >= h) {  // a border row: zeros
+    for (int r = threadIdx.x; r < wp * (TP_C / 8); r += 256) {
+      const int xp = r >> 3, ch = cb + 8 * (r & 7);
+      if (ch < c) store8(row_o + xp, ch, zero4, zero4);
+    }
+    return;
+  }
+  for (int r = threadIdx.x; r < 2 * pad * (TP_C / 8); r += 256) {  // the row's left and right padding pixels
+    const int q = r >> 3, ch = cb + 8 * (r & 7);
+    const int xp = q < pad ? q : w + q;  // q - pad + (w + pad)
+    if (ch < c) store8(row_o + xp, ch, zero4, zero4);
+  }
+  const float* src = x + ((static_cast<long long>(n) * c + cb) * h + y) * w;
+  const long long ch_stride = static_cast<long long>(h) * w;
+  // a thread's four float4 of a tile belong to the channels (tid >> 4) + 16 i
+  float sc[4], sh[4];
+  if (pre.stats != nullptr) {
+    if (threadIdx.x < TP_C) {
+      const int ch = cb + threadIdx.x;
+      float2 a = make_float2(0.0f, 0.0f);
+      if (ch < c) {
+        const float* st = pre.stats + (static_cast<long long>(n) * pre.groups + ch / (c / pre.groups)) * 2;
+        const float mean = __ldg(st), inv = __ldg(st + 1);
+        const float g = pre.gamma != nullptr ? __ldg(pre.gamma + ch) : 1.0f;
+        const float b = (pre.gamma != nullptr && pre.beta != nullptr) ? __ldg(pre.beta + ch) : 0.0f;
+        a = make_float2(inv * g, b - mean * inv * g);
+      }
+      s_aff[threadIdx.x] = a;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = s_aff[(threadIdx.x >> 4) + 16 * i];
+      sc[i] = a.x; sh[i] = a.y;
+    }
+  }
+  for (int x0 = 0; x0 < w; x0 += TP_X) {
+    float4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int cc = (threadIdx.x >> 4) + 16 * i, xs = x0 + 4 * (threadIdx.x & 15);
+      v[i] = (xs < w && cb + cc < c) ? __ldg(reinterpret_cast<const float4*>(src + cc * ch_stride + xs)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (pre.stats != nullptr) {  // GroupNorm (+ SiLU) of the producer applied here
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float* e = reinterpret_cast<float*>(&v[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float r = fmaf(e[j], sc[i], sh[i]);
+          if (pre.act == MIMIR_B200_ELT_SILU) r = r * __fdividef(1.0f, 1.0f + __expf(-r));
+          e[j] = r;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float* t = &tile[(threadIdx.x >> 4) + 16 * i][4 * (threadIdx.x & 15)];
+      t[0] = v[i].x; t[1] = v[i].y; t[2] = v[i].z; t[3] = v[i].w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = threadIdx.x + 256 * i;
+      const int xx = r >> 3, ch8 = 8 * (r & 7);
+      if (x0 + xx < w && cb + ch8 < c) {
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) split_pair(tile[ch8 + 2 * j][xx], tile[ch8 + 2 * j + 1][xx], f16, hi[j], lo[j]);
+        store8(row_o + pad + x0 + xx, cb + ch8, make_uint4(hi[0], hi[1], hi[2], hi[3]), make_uint4(lo[0], lo[1], lo[2], lo[3]));
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // dst[pl][o][(kh*ks + kw)*ic + i] = split(w[o][i][kh][kw]); the padded tail of K is zero
 __global__ void conv_weight_planes_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ dst, int oc, int ic, int ks,
                                           int kp, int planes, int f16, float scale) {
@@ -201,7 +299,14 @@ int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int bat
   if (hp > 65535 || batch > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: image too tall for the layout kernel");
   dim3 grid((c + TP_C - 1) / TP_C, hp, batch);
   if (pre.stats != nullptr && (pre.groups <= 0 || c % pre.groups != 0)) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad fused GroupNorm");
-  nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, static_cast<long long>(batch) * hp * wp * c, pre, plane_format() == PLANES_F16);
+  static const bool no_vec = [] { const char* e = getenv("MIMIR_B200_LAYOUT_VEC"); return e && e[0] == '0'; }();
+  const long long plane_stride = static_cast<long long>(batch) * hp * wp * c;
+  const bool vec = !no_vec && (w & 3) == 0 && (c & 7) == 0 && (plane_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+  if (vec)
+    nchw_to_padded_nhwc_vec_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16);
+  else
+    nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
