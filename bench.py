@@ -296,7 +296,8 @@ def _cpu_sample(descs, weights, inputs, registry=None, cfg=None):
 
 
 def bench_graph_config(h: Harness, rt, peaks, name, descs, weights, inputs, batch, out_n, precision, flops_per_sample=None,
-                       weight_stream_bytes=None, e2e="host", pipeline=1, steps=5, cpu=True, registry=None, registry_cfg=None):
+                       weight_stream_bytes=None, e2e="host", pipeline=1, steps=5, cpu=True, registry=None, registry_cfg=None,
+                       one_mma_arm=False, gemm_flops_per_sample=None):
     """One configuration on this rank's GPU with its stated per-GPU batch.  `inputs`: name -> (array [batch, per] or
     broadcast vector, broadcast flag).  e2e = "host": the host-pointer forward (pipelined when `pipeline` > 1) from and
     to pinned buffers; "argmax": pinned ids -> device -> forward -> per-position argmax on the device -> ids to pinned
@@ -361,7 +362,8 @@ def bench_graph_config(h: Harness, rt, peaks, name, descs, weights, inputs, batc
         tf = flops_per_sample * batch / (ms * 1e-3) / 1e12
         rec["roofline"] = {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_sustained"],
                            "note": "algorithmic flops of the contraction layers over the whole step (norms, layout and copies included in the time)",
-                           "gemm_only_tflops": (flops_per_sample * batch / (gemm_ms / 2 * 1e-3) / 1e12) if gemm_n else None}
+                           "gemm_only_tflops": ((gemm_flops_per_sample or flops_per_sample) * batch / (gemm_ms / 2 * 1e-3) / 1e12) if gemm_n else None,
+                           "gemm_only_note": "flops of the layers that run in the GEMM kernel over the time inside that kernel (CUDA events around every launch)"}
     if weight_stream_bytes:
         gbs, frac = hbm_frac(weight_stream_bytes, ms, peaks)
         rec["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s", "frac": frac,
@@ -375,6 +377,40 @@ def bench_graph_config(h: Harness, rt, peaks, name, descs, weights, inputs, batc
                                     "sample": "sample 0 of the batch, one forward of the reference's CPU code"}
             rec["parity_sample0"] = _parity(got0, want)
     model.close()
+    if one_mma_arm and flops_per_sample:
+        # The same configuration with ONE 16-bit plane per operand (one MMA per product): outside the fp32 gate by
+        # construction (its checker is the oracle with the same operand rounding, tests/test_gpu_precision_modes.py);
+        # measured beside the strict arm so that the GEMM fraction of the tensor-core peak is on record for both.
+        from mimir_framework_b200 import abi
+
+        m1 = rt.GraphModel(descs, abi.PREC_BF16)
+        for i, w in enumerate(weights):
+            m1.upload_weights(i, w)
+        m1.plan(spec, batch)
+        ms1 = h.time_steps(lambda: m1.forward_device(dspec, batch, d_out.data_ptr(), d_out.numel(), h.stream), steps)
+        rt.profile_gemm(True)
+        for _ in range(2):
+            m1.forward_device(dspec, batch, d_out.data_ptr(), d_out.numel(), h.stream)
+        g1_ms, g1_n = rt.profile_read()
+        rt.profile_gemm(False)
+        rt.check(rt.lib().mimir_b200_check_device(None))
+        got1 = d_out[:out_n].cpu().numpy()
+        m1.close()
+        mmas = {0: 3, 1: 2, 2: 1}[precision]
+        strict_gemm_tf = rec["roofline"]["gemm_only_tflops"]
+        one_gemm_tf = ((gemm_flops_per_sample or flops_per_sample) * batch / (g1_ms / 2 * 1e-3) / 1e12) if g1_n else None
+        pk = peaks["bf16_sustained"]
+        rec["gemm_fraction_of_peak"] = {
+            "peak_tflops": pk, "strict": {"precision": rec["precision"], "mma_per_product": mmas, "algorithmic": strict_gemm_tf / pk if strict_gemm_tf else None,
+                                          "issued": mmas * strict_gemm_tf / pk if strict_gemm_tf else None},
+            "one_mma": {"precision": "BF16", "mma_per_product": 1, "algorithmic": one_gemm_tf / pk if one_gemm_tf else None}}
+        rec["one_mma_arm"] = {"precision": "BF16", "ms_per_step": ms1, "samples_per_s": h.world * batch / (ms1 * 1e-3),
+                              "gemm_share_of_step": (g1_ms / 2) / ms1 if g1_n else 0.0, "gemm_only_tflops": one_gemm_tf,
+                              "step_tflops": flops_per_sample * batch / (ms1 * 1e-3) / 1e12,
+                              "vs_strict_arm_sample0": _parity(got1, got0),
+                              "note": "one 16-bit plane per operand; checked against the oracle with the same operand rounding, not against the fp32 gate"}
+        if "parity_sample0" in rec:
+            rec["one_mma_arm"]["vs_cpu_reference_sample0"] = _parity(got1, want)
     return rec
 
 
@@ -426,7 +462,8 @@ def _bench_c3(h, rt, peaks, abi, seed0, cpu, batch):
     ids = np.random.default_rng(seed0).integers(0, cfg["vocab"], (batch, cfg["seq"])).astype(np.float32)
     return bench_graph_config(h, rt, peaks, "3 GPT decoder prefill: 12 layers d768 h12 ffn3072 vocab32000 seq1024, bf16-exact weights, whole-sample RMSNorm", descs,
                               weights, {"x": (ids, False)}, batch, cfg["seq"] * cfg["vocab"], abi.PREC_BF16W,
-                              flops_per_sample=configs.gpt_decoder_flops(**cfg), e2e="argmax", steps=5, registry_cfg=cfg, cpu=cpu)
+                              flops_per_sample=configs.gpt_decoder_flops(**cfg), e2e="argmax", steps=5, registry_cfg=cfg, cpu=cpu, one_mma_arm=True,
+                              gemm_flops_per_sample=configs.gpt_decoder_gemm_flops(**cfg))
 
 
 def _bench_c4(h, rt, peaks, abi, seed0, cpu, batch):
@@ -444,7 +481,8 @@ def _bench_c5(h, rt, peaks, abi, seed0, cpu, batch):
     weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
     x = np.random.default_rng(seed0).standard_normal((batch, 4 * 64 * 64), dtype=np.float32)
     return bench_graph_config(h, rt, peaks, "5 UNet mid+up: latent 4x64x64 -> 3x256x256, channels 512/256/128, bf16-exact weights", descs, weights,
-                              {"x": (x, False)}, batch, 3 * 256 * 256, abi.PREC_BF16W, flops_per_sample=configs.conv_flops(descs), pipeline=4, steps=5, cpu=cpu)
+                              {"x": (x, False)}, batch, 3 * 256 * 256, abi.PREC_BF16W, flops_per_sample=configs.conv_flops(descs), pipeline=4, steps=5, cpu=cpu,
+                              one_mma_arm=True)
 
 
 def bench_norms(h: Harness, rt, peaks):

@@ -42,12 +42,15 @@ typedef enum MimirB200Status {
   MIMIR_B200_E_NOT_INIT = 6
 } MimirB200Status;
 
-/* GEMM operand precision.  All modes accumulate in fp32 in tensor memory.
- *   BF16X2 : both operands split into bf16 hi+lo, three MMAs (hi*hi + lo*hi + hi*lo); error ~2^-16
- *            per product — the default for fp32 graphs (within rel 1e-3 / abs 1e-4 of the CPU path).
- *   BF16W  : weights stored as single bf16 (exact when the checkpoint was pre-rounded to bf16),
- *            activations split hi+lo, two MMAs.
- *   BF16   : both operands rounded to bf16, one MMA (fastest, not within the fp32 tolerance). */
+/* GEMM operand precision.  All modes accumulate in fp32 in tensor memory.  Operands travel as 16-bit planes: IEEE half
+ * by default (weights through a per-layer power-of-two scale), bfloat16 with MIMIR_B200_PLANES=bf16; the names date
+ * from the bfloat16 planes and describe the number of MMAs per product.
+ *   BF16X2 : both operands split into hi + lo planes, three MMAs (hi*hi + lo*hi + hi*lo) — the default for fp32
+ *            graphs (within rel 1e-3 / abs 1e-4 of the CPU path).
+ *   BF16W  : weights in one plane (exact when the checkpoint was pre-rounded to bf16), activations split hi + lo,
+ *            two MMAs.
+ *   BF16   : one plane per operand, one MMA (fastest; not within the fp32 tolerance: it is checked against the
+ *            reference's arithmetic with the same operand rounding applied, not against the fp32 gate). */
 typedef enum MimirB200Precision {
   MIMIR_B200_PREC_BF16X2 = 0,
   MIMIR_B200_PREC_BF16W = 1,

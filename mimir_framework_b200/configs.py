@@ -179,6 +179,11 @@ def gpt_decoder_flops(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, s
     return layers * per_layer + 2 * S * E * vocab
 
 
+def gpt_decoder_gemm_flops(layers=12, d_model=768, heads=12, ffn=3072, vocab=32000, seq=1024):
+    """The part of gpt_decoder_flops that runs in the projection GEMMs (everything but the attention core)."""
+    return gpt_decoder_flops(layers, d_model, heads, ffn, vocab, seq) - layers * 2 * seq * seq * d_model
+
+
 # ---- configuration 4: conv vision block stack ------------------------------------------------------
 def conv_stack(image=224, channels=(64, 128, 128, 256, 256), groups=32):
     """Stem Conv 7x7 s2 p3 3->C0, then per block [Conv 3x3 s1 p1 -> GroupNorm -> SiLU -> Add residual]; where

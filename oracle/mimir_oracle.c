@@ -63,11 +63,21 @@ void mo_matmul(const float* A, const float* B, float* C, long M, long K, long N)
  * alias, :1100-1113).  wqkv is [E][3E] input-major, wout [E][E]; no biases (Model.cpp:5916-5921). */
 void mo_attention(const float* x, const float* wqkv, const float* wout, float* y, int seq, int E, int heads,
                   int causal) {
-  const int hd = E / heads;
   const int qd = 3 * E;
   float* qkv = (float*)malloc(sizeof(float) * (size_t)seq * qd);
   float* att = (float*)calloc((size_t)seq * E, sizeof(float));
   mo_matmul(x, wqkv, qkv, seq, E, qd);
+  mo_attention_core(qkv, att, seq, E, heads, causal);
+  mo_matmul(att, wout, y, seq, E, E);
+  free(qkv);
+  free(att);
+}
+
+/* The part of self_attention_forward between the two projections (LayerOps.hpp:1044-1090): qkv is [seq][3E] with Q, K, V
+ * as column thirds, att [seq][E] with the heads side by side. */
+void mo_attention_core(const float* qkv, float* att, int seq, int E, int heads, int causal) {
+  const int hd = E / heads;
+  const int qd = 3 * E;
   const float scale = 1.0f / sqrtf((float)hd);
   /* the reference runs the head loop on one thread (:1049); rows are independent, so threading
    * over (h, i) changes nothing numerically */
@@ -109,9 +119,6 @@ void mo_attention(const float* x, const float* wqkv, const float* wout, float* y
     }
     free(row);
   }
-  mo_matmul(att, wout, y, seq, E, E);
-  free(qkv);
-  free(att);
 }
 
 /* Inline Conv2d case, Model.cpp:4897-5089: OIHW weights, CHW activations, square kernel, zero

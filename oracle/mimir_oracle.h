@@ -43,6 +43,7 @@ void mo_patch_embed(const float* x, const float* w, float* y, int d_model, int s
 void mo_bilinear(const float* x1, const float* x2, const float* w, const float* bias, float* y, long rows, int in1, int in2,
                  int out_f);
 void mo_maxpool1d(const float* x, float* y, int ch, long len, int k, int stride, int pad);
+void mo_attention_core(const float* qkv, float* att, int seq, int E, int heads, int causal);
 void mo_conv2d_dilated(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int h, int wd, int k, int stride,
                        int pad, int dil, int avx2_lanes);
 void mo_conv_transpose2d_scatter(const float* x, const float* w, const float* bias, float* y, int ic, int oc, int h, int wd, int k,

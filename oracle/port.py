@@ -364,10 +364,72 @@ def _dflt(v, default):
     return v if v > 0 else default
 
 
-def run_layer(d, ins, w):
-    """One layer of the switch in Model::forwardPassView (Model.cpp:4891-6291) on one sample."""
+class OperandRounding:
+    """What a single 16-bit operand plane does to the contractions of the CUDA backend's one-MMA precision mode: the
+    activation operand of every Linear, Conv2d and attention projection is rounded to nearest-even in the plane format
+    ("f16": 11 significant bits, "bf16": 8), the weights to the same format after a per-layer power-of-two scale that
+    brings the largest magnitude of the block into [2^13, 2^14).  Everything else (the attention core, norms,
+    accumulation) stays the reference's fp32 arithmetic.  Used only to check that mode of the backend; the reference
+    itself has no reduced-precision path."""
+
+    def __init__(self, fmt="f16"):
+        if fmt not in ("f16", "bf16"):
+            raise ValueError(fmt)
+        self.fmt = fmt
+
+    def act(self, x):
+        x = _f(x)
+        if self.fmt == "f16":
+            with np.errstate(over="ignore"):
+                return x.astype(np.float16).astype(np.float32)
+        u = x.view(np.uint32).astype(np.uint64)
+        u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000  # round to nearest even on the upper 16 bits
+        return u.astype(np.uint32).view(np.float32)
+
+    def weight(self, w):
+        w = _f(w)
+        amax = float(np.max(np.abs(w))) if w.size else 0.0
+        if self.fmt != "f16" or not amax > 0.0:
+            return self.act(w)
+        e = int(np.frexp(np.float32(amax))[1])  # amax = f * 2^e, f in [0.5, 1)
+        s = float(np.ldexp(1.0, min(60, max(-60, 14 - e))))
+        return (self.act(w * np.float32(s)) / np.float32(s)).astype(np.float32)
+
+
+def attention_core(qkv, seq, E, heads, causal):
+    qkv = _f(qkv)
+    att = np.empty(seq * E, np.float32)
+    lib().mo_attention_core(_p(qkv), _p(att), C.c_int(seq), C.c_int(E), C.c_int(heads), C.c_int(int(causal)))
+    return att
+
+
+def run_layer(d, ins, w, rounding=None):
+    """One layer of the switch in Model::forwardPassView (Model.cpp:4891-6291) on one sample.  `rounding`
+    (an OperandRounding) restates the backend's one-MMA mode instead of the reference's fp32 contractions."""
     t = d.type.decode()
     x = ins[0]
+    if rounding is not None:
+        if t == "Linear":
+            in_f = d.in_features if d.in_features > 0 else x.size
+            nw = in_f * d.out_features
+            w = np.concatenate([rounding.weight(w[:nw]), w[nw:]])
+            ins = [rounding.act(x)] + list(ins[1:])
+            x = ins[0]
+        elif t in ("SelfAttention", "MultiHeadAttention"):
+            seq = d.seq_len if d.seq_len > 0 else 1
+            E = d.embed_dim if d.embed_dim > 0 else x.size
+            heads = d.num_heads if d.num_heads > 0 else 1
+            wr = rounding.weight(w[: 4 * E * E])  # one scale for the whole block, as the backend takes it
+            qkv = matmul(rounding.act(x), wr[: 3 * E * E], seq, E, 3 * E)
+            att = attention_core(qkv, seq, E, heads, d.causal)
+            return matmul(rounding.act(att), np.ascontiguousarray(wr[3 * E * E :]), seq, E, E)
+        elif t == "Conv2d":
+            nw = d.out_channels * d.in_channels * d.kernel * d.kernel
+            w = rounding.weight(w[:nw])
+            ins = [rounding.act(x)] + list(ins[1:])
+            x = ins[0]
+        elif t in ("CrossAttention",):
+            raise NotImplementedError("operand rounding is not restated for " + t)
     if t == "Linear":
         in_f = d.in_features if d.in_features > 0 else x.size
         rows = d.seq_len if (d.seq_len > 0 and x.size == d.seq_len * in_f) else 1
@@ -524,7 +586,7 @@ def run_layer(d, ins, w):
     raise NotImplementedError(t)
 
 
-def run_graph(descs, weights, inputs):
+def run_graph(descs, weights, inputs, rounding=None):
     """descs: list of MimirLayerDesc; weights: list of arrays (or None); inputs: name -> array."""
     store = {}
     main = inputs.get("x", inputs.get("__input__"))
@@ -546,6 +608,6 @@ def run_graph(descs, weights, inputs):
                 off += sz
             out = store[out_name + "_0"].copy()
         else:
-            out = run_layer(d, [store[n] for n in names], None if w is None else _f(w))
+            out = run_layer(d, [store[n] for n in names], None if w is None else _f(w), rounding)
         store[out_name] = out
     return store["x"]

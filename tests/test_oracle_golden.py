@@ -133,3 +133,15 @@ def test_port_of_the_static_conv_family_matches_the_compiled_reference():
     x = (r.standard_normal(300) * 3).astype(np.float32)
     np.testing.assert_allclose(port.elu(x, 1.3), ref.compute_activation("elu", x, 1.3), atol=1e-6, rtol=1e-6)
     assert np.array_equal(ref.compute_activation("no_such_activation", x), x)  # an unknown name leaves the data alone
+
+
+def test_operand_rounding_restatement_on_cpu_values():
+    """The rounding the checker applies: nearest-even to 8 (bf16) or 11 (half) significant bits; weights through the
+    power-of-two scale."""
+    x = np.array([1.0, 1.00390625, 1.01171875, 3.14159, -2.71828e-5, 0.0], np.float32)
+    b = port.OperandRounding("bf16").act(x)
+    assert np.array_equal(b, np.array([1.0, 1.0, 1.015625, 3.140625, -2.7179718e-05, 0.0], np.float32))
+    h = port.OperandRounding("f16").act(x)
+    assert np.array_equal(h[:3], x[:3]) and h[3] == np.float32(3.140625)
+    w = port.OperandRounding("f16").weight(x * np.float32(1e-6))  # far below half's normal range without the scale
+    np.testing.assert_allclose(w, x * np.float32(1e-6), rtol=2.0 ** -11)
