@@ -424,11 +424,11 @@ def bench_other_configs(h: Harness, rt, peaks, args):
     if want("c1"):
         out.append(_bench_c1(h, rt, peaks, abi, seed0, cpu))
     if want("c3"):
-        out.append(_bench_c3(h, rt, peaks, abi, seed0, cpu, args.decoder_batch))
+        out.append(_bench_c3(h, rt, peaks, abi, seed0, cpu, args.decoder_batch, args.precision == "one-mma"))
     if want("c4"):
         out.append(_bench_c4(h, rt, peaks, abi, seed0, cpu, args.conv_batch))
     if want("c5"):
-        out.append(_bench_c5(h, rt, peaks, abi, seed0, cpu, args.unet_batch))
+        out.append(_bench_c5(h, rt, peaks, abi, seed0, cpu, args.unet_batch, args.precision == "one-mma"))
     return out
 
 
@@ -454,15 +454,16 @@ def _bench_c1(h, rt, peaks, abi, seed0, cpu):
                               weight_stream_bytes=wbytes, steps=20, registry="transformer", registry_cfg=cfg, cpu=cpu)
 
 
-def _bench_c3(h, rt, peaks, abi, seed0, cpu, batch):
+def _bench_c3(h, rt, peaks, abi, seed0, cpu, batch, one_mma_only=False):
     # 3: GPT decoder prefill, batch 32
     cfg = configs.DECODER_CFG
     descs = configs.gpt_decoder(**cfg)
     weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
     ids = np.random.default_rng(seed0).integers(0, cfg["vocab"], (batch, cfg["seq"])).astype(np.float32)
     return bench_graph_config(h, rt, peaks, "3 GPT decoder prefill: 12 layers d768 h12 ffn3072 vocab32000 seq1024, bf16-exact weights, whole-sample RMSNorm", descs,
-                              weights, {"x": (ids, False)}, batch, cfg["seq"] * cfg["vocab"], abi.PREC_BF16W,
-                              flops_per_sample=configs.gpt_decoder_flops(**cfg), e2e="argmax", steps=5, registry_cfg=cfg, cpu=cpu, one_mma_arm=True,
+                              weights, {"x": (ids, False)}, batch, cfg["seq"] * cfg["vocab"], abi.PREC_BF16 if one_mma_only else abi.PREC_BF16W,
+                              flops_per_sample=configs.gpt_decoder_flops(**cfg), e2e="argmax", steps=5, registry_cfg=cfg, cpu=cpu and not one_mma_only,
+                              one_mma_arm=not one_mma_only,
                               gemm_flops_per_sample=configs.gpt_decoder_gemm_flops(**cfg))
 
 
@@ -475,14 +476,14 @@ def _bench_c4(h, rt, peaks, abi, seed0, cpu, batch):
                               {"x": (x, False)}, batch, 256 * 112 * 112, abi.PREC_BF16X2, flops_per_sample=configs.conv_flops(descs), pipeline=8, steps=5, cpu=cpu)
 
 
-def _bench_c5(h, rt, peaks, abi, seed0, cpu, batch):
+def _bench_c5(h, rt, peaks, abi, seed0, cpu, batch, one_mma_only=False):
     # 5: UNet mid + up, batch 16
     descs = configs.unet_mid_up()
     weights = configs.seeded_weights(descs, seed=1, std=0.02, bf16=True)
     x = np.random.default_rng(seed0).standard_normal((batch, 4 * 64 * 64), dtype=np.float32)
     return bench_graph_config(h, rt, peaks, "5 UNet mid+up: latent 4x64x64 -> 3x256x256, channels 512/256/128, bf16-exact weights", descs, weights,
-                              {"x": (x, False)}, batch, 3 * 256 * 256, abi.PREC_BF16W, flops_per_sample=configs.conv_flops(descs), pipeline=4, steps=5, cpu=cpu,
-                              one_mma_arm=True)
+                              {"x": (x, False)}, batch, 3 * 256 * 256, abi.PREC_BF16 if one_mma_only else abi.PREC_BF16W,
+                              flops_per_sample=configs.conv_flops(descs), pipeline=4, steps=5, cpu=cpu and not one_mma_only, one_mma_arm=not one_mma_only)
 
 
 def bench_norms(h: Harness, rt, peaks):
@@ -795,6 +796,9 @@ def main():
     ap.add_argument("--headline-only", action="store_true", help="skip the other configurations, the norm kernels and the single-process leg")
     ap.add_argument("--only", default="all", choices=["all", "headline", "configs", "c1", "c3", "c4", "c5", "norms", "decode"],
                     help="run one leg alone and print its records (no headline line)")
+    ap.add_argument("--precision", default="default", choices=["default", "one-mma"],
+                    help="configs 3 and 5: 'one-mma' runs the one-plane-per-operand mode as the only arm (for profiling it); "
+                         "the default runs the strict mode and the one-MMA mode as a second arm beside it")
     ap.add_argument("--decoder-batch", type=int, default=32, help="samples per GPU of the decoder configuration")
     ap.add_argument("--conv-batch", type=int, default=64, help="samples per GPU of the conv vision stack")
     ap.add_argument("--unet-batch", type=int, default=16, help="samples per GPU of the UNet mid+up path")

@@ -278,7 +278,8 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
   const int ow = (e.w + 2 * e.pad - e.ks) / e.stride + 1;
   if (oh <= 0 || ow <= 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: empty output");
   const int ohw = oh * ow, k = e.ic * e.ks * e.ks;
-  if (e.w_f32 != nullptr && e.pre_groups == 0 && conv_small_oc_supported(e.oc, e.ks, e.stride, e.pad, e.h, e.w, e.batch, e.activation))
+  if (e.in_up && !conv_uses_shifted(e.ic, e.ks, e.stride, e.pad)) return fail(MIMIR_B200_E_INVALID, "Conv2d: an upsampled input needs the shifted-GEMM path");
+  if (e.w_f32 != nullptr && e.pre_groups == 0 && !e.in_up && conv_small_oc_supported(e.oc, e.ks, e.stride, e.pad, e.h, e.w, e.batch, e.activation))
     return launch_conv_small_oc(e.x, e.w_f32, e.y, e.residual, e.batch, e.ic, e.oc, e.h, e.w, e.ks, e.pad, e.activation, st);
   if (conv_uses_shifted(e.ic, e.ks, e.stride, e.pad)) {
     // NCHW fp32 -> zero-padded NHWC planes, then one GEMM that walks the taps as shifted row offsets
@@ -288,10 +289,11 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
     if (e.pre_groups > 0) {
       // statistics live behind the operand planes in the workspace
       float* stats = reinterpret_cast<float*>(static_cast<uint8_t*>(e.ws) + align256(static_cast<size_t>(ap) * rows * e.ic * sizeof(__nv_bfloat16)));
-      MB_TRY(launch_groupnorm_stats(e.x, stats, e.batch, e.ic, e.h * e.w, e.pre_groups, e.pre_eps, st));
+      // (of an upsampled input: over the source image, whose values are the same ones four times)
+      MB_TRY(launch_groupnorm_stats(e.x, stats, e.batch, e.ic, e.in_up ? (e.h >> 1) * (e.w >> 1) : e.h * e.w, e.pre_groups, e.pre_eps, st));
       pre.stats = stats; pre.gamma = e.pre_gamma; pre.beta = e.pre_gamma ? e.pre_beta : nullptr; pre.groups = e.pre_groups; pre.act = e.pre_act;
     }
-    MB_TRY(launch_nchw_to_padded_nhwc_split(e.x, static_cast<__nv_bfloat16*>(e.ws), e.batch, e.ic, e.h, e.w, e.pad, ap, st, pre));
+    MB_TRY(launch_nchw_to_padded_nhwc_split(e.x, static_cast<__nv_bfloat16*>(e.ws), e.batch, e.ic, e.h, e.w, e.pad, ap, st, pre, e.in_up));
     GemmArgs g;
     g.a = static_cast<const __nv_bfloat16*>(e.ws);
     g.w = e.w_split;

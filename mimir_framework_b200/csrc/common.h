@@ -231,8 +231,9 @@ struct PreNorm {
   int groups = 1;
   int act = -1;                  // -1 or MIMIR_B200_ELT_SILU
 };
+// up != 0: x is [batch][c][h/2][w/2] and every source pixel covers a 2 x 2 block of the h x w image (nearest-neighbour upsample)
 int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int batch, int c, int h, int w, int pad, int planes,
-                                     cudaStream_t st, const PreNorm& pre = PreNorm());
+                                     cudaStream_t st, const PreNorm& pre = PreNorm(), int up = 0);
 // OIHW fp32 -> planes [planes][oc][round_up(ks*ks*ic, 64)] with K ordered (kh, kw, ic)
 int launch_conv_weight_planes(const float* w, __nv_bfloat16* dst, int oc, int ic, int ks, int planes, cudaStream_t st, float scale = 1.0f);
 

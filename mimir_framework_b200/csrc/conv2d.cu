@@ -88,7 +88,7 @@ constexpr int TP_C = 64, TP_X = 64;
 
 __global__ void __launch_bounds__(256, 3) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
                                                                   int c, int h, int w, int pad, int planes, long long plane_stride,
-                                                                  const PreNorm pre, int f16) {
+                                                                  const PreNorm pre, int f16, int up) {
   __shared__ float tile[TP_C][TP_X + 1];
   const int hp = h + 2 * pad, wp = w + 2 * pad;
   const int cb = blockIdx.x * TP_C;
@@ -97,8 +97,10 @@ __global__ void __launch_bounds__(256, 3) nchw_to_padded_nhwc_kernel(const float
   const int y = yp - pad;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool row_in = y >= 0 && y < h;
-  const float* src = x + ((static_cast<long long>(n) * c + cb) * h + (row_in ? y : 0)) * w;
-  const long long ch_stride = static_cast<long long>(h) * w;
+  // up: the source is the half-size image, a source pixel feeds a 2 x 2 block
+  const int sh_ = up ? h >> 1 : h, sw_ = up ? w >> 1 : w;
+  const float* src = x + ((static_cast<long long>(n) * c + cb) * sh_ + (row_in ? (up ? y >> 1 : y) : 0)) * sw_;
+  const long long ch_stride = static_cast<long long>(sh_) * sw_;
   // scale / shift of the CTA's 64 channels once, in shared memory; a thread's 16 elements of a tile belong to 16 fixed
   // channels ((tid >> 6) + 4 i), so it keeps those 16 pairs in registers for every tile of the row
   __shared__ float2 s_aff[TP_C];
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(256, 3) nchw_to_padded_nhwc_kernel(const float
       const int idx = threadIdx.x + 256 * i;
       const int cc = idx >> 6, xx = idx & 63;
       const int xs = x0 + xx - pad;
-      v[i] = (row_in && xs >= 0 && xs < w && cb + cc < c) ? __ldg(src + cc * ch_stride + xs) : 0.0f;
+      v[i] = (row_in && xs >= 0 && xs < w && cb + cc < c) ? __ldg(src + cc * ch_stride + (up ? xs >> 1 : xs)) : 0.0f;
     }
     if (pre.stats != nullptr) {
       // GroupNorm (+ SiLU) of the producer applied here; the zero padding ring stays zero
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(256, 3) nchw_to_padded_nhwc_kernel(const float
 // and last tile of every interior row.
 __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_vec_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
                                                                       int c, int h, int w, int pad, int planes, long long plane_stride,
-                                                                      const PreNorm pre, int f16) {
+                                                                      const PreNorm pre, int f16, int up) {
   __shared__ float tile[TP_C][TP_X + 1];
   __shared__ float2 s_aff[TP_C];
   const int hp = h + 2 * pad, wp = w + 2 * pad;
@@ -205,8 +207,10 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_vec_kernel(const floa
     const int xp = q < pad ? q : w + q;  // q - pad + (w + pad)
     if (ch < c) store8(row_o + xp, ch, zero4, zero4);
   }
-  const float* src = x + ((static_cast<long long>(n) * c + cb) * h + y) * w;
-  const long long ch_stride = static_cast<long long>(h) * w;
+  // up: the source is the half-size image; four consecutive output pixels are two source pixels, each used twice
+  const int sh_ = up ? h >> 1 : h, sw_ = up ? w >> 1 : w;
+  const float* src = x + ((static_cast<long long>(n) * c + cb) * sh_ + (up ? y >> 1 : y)) * sw_;
+  const long long ch_stride = static_cast<long long>(sh_) * sw_;
   // a thread's four float4 of a tile belong to the channels (tid >> 4) + 16 i
   float sc[4], sh[4];
   if (pre.stats != nullptr) {
@@ -234,7 +238,16 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_vec_kernel(const floa
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int cc = (threadIdx.x >> 4) + 16 * i, xs = x0 + 4 * (threadIdx.x & 15);
-      v[i] = (xs < w && cb + cc < c) ? __ldg(reinterpret_cast<const float4*>(src + cc * ch_stride + xs)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (xs < w && cb + cc < c) {
+        if (up) {
+          const float2 t = __ldg(reinterpret_cast<const float2*>(src + cc * ch_stride + (xs >> 1)));
+          v[i] = make_float4(t.x, t.x, t.y, t.y);
+        } else {
+          v[i] = __ldg(reinterpret_cast<const float4*>(src + cc * ch_stride + xs));
+        }
+      } else {
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
     if (pre.stats != nullptr) {  // GroupNorm (+ SiLU) of the producer applied here
 #pragma unroll
@@ -293,8 +306,9 @@ __global__ void conv_weight_planes_kernel(const float* __restrict__ w, __nv_bflo
 }  // namespace
 
 int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int batch, int c, int h, int w, int pad, int planes,
-                                     cudaStream_t st, const PreNorm& pre) {
+                                     cudaStream_t st, const PreNorm& pre, int up) {
   if (batch <= 0 || c <= 0 || h <= 0 || w <= 0 || pad < 0) return fail(MIMIR_B200_E_INVALID, "Conv2d: bad activation shape");
+  if (up && ((h | w) & 1)) return fail(MIMIR_B200_E_INVALID, "Conv2d: an upsampled input needs even dimensions");
   const int hp = h + 2 * pad, wp = w + 2 * pad;
   if (hp > 65535 || batch > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: image too tall for the layout kernel");
   dim3 grid((c + TP_C - 1) / TP_C, hp, batch);
@@ -304,9 +318,9 @@ int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int bat
   const bool vec = !no_vec && (w & 3) == 0 && (c & 7) == 0 && (plane_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
   if (vec)
-    nchw_to_padded_nhwc_vec_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16);
+    nchw_to_padded_nhwc_vec_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16, up);
   else
-    nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16);
+    nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16, up);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;

@@ -133,6 +133,7 @@ struct LayerRT {
   bool read_split = false;            // Linear reads the producer's planes
   int res_v = -1;                     // residual tensor folded in from a following Add
   int pre_norm = -1;                  // Conv2d: index of the GroupNorm layer applied while its operand planes are laid out
+  bool in_up = false;                 // Conv2d: in_v[0] is the INPUT of a 2 x 2 nearest upsample that the layout pass applies
   // decode twin (see mimir_b200_model_decode_begin): weights borrowed from the main model, key / value caches owned
   bool borrowed_f32 = false, borrowed_planes = false;
   float* kcache = nullptr;
@@ -782,7 +783,7 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     LayerRT& L = m->layers[li];
     L.in_v.clear();
     L.out_v = -1;
-    L.skip = false; L.fused_act = -1; L.emit_split = false; L.emit_f32 = true; L.read_split = false; L.res_v = -1; L.pre_norm = -1;
+    L.skip = false; L.fused_act = -1; L.emit_split = false; L.emit_f32 = true; L.read_split = false; L.res_v = -1; L.pre_norm = -1; L.in_up = false;
     L.ws_off = 0; L.ws_bytes = 0;
     std::vector<std::string> names = L.inputs;
     if (names.empty()) names.push_back("x");
@@ -914,6 +915,46 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
     pt.want_f32 = false;
     pt.producer = -2;  // dead
     P.skip = true;
+  }
+  // ---- fusion 1d: a 2 x 2 nearest upsample read by shifted-GEMM convolutions: their layout pass gathers from the
+  //      half-size source (and a folded GroupNorm takes its statistics there: the same values, each four times), so the
+  //      upsampled tensor is read by nobody but residual adds - and is not produced at all when there are none ----
+  static const bool fuse_up = [] { const char* e = getenv("MIMIR_B200_FUSE_UPSAMPLE"); return !(e && e[0] == '0'); }();
+  for (int li = 0; li < nl && fuse_up; ++li) {
+    LayerRT& U = m->layers[li];
+    if (U.lt != LT::UpsampleNearest || U.skip || U.oh != 2 * U.h || U.ow != 2 * U.w) continue;
+    const int uv = U.out_v, sv = root_of(m->tensors, U.in_v[0]);
+    TensorV& ut = m->tensors[uv];
+    if (ut.alias_of >= 0 || uv == out_root || !m->tensors[sv].want_f32 || m->tensors[sv].producer == -2) continue;
+    bool aliased = false;
+    for (const TensorV& t : m->tensors) aliased = aliased || t.alias_of == uv;
+    if (aliased) continue;
+    std::vector<int> keep;
+    for (int ci : ut.consumers) {
+      LayerRT& C = m->layers[ci];
+      const bool conv_in = C.lt == LT::Conv2d && !C.skip && !C.in_up && C.in_v[0] == uv && C.res_v != uv && C.d.in_channels == U.ch &&
+                           C.h == U.oh && C.w == U.ow && conv_uses_shifted(C.d.in_channels, C.d.kernel, C.d.stride, C.d.padding) &&
+                           (C.pre_norm >= 0 || !conv_small_oc_supported(C.d.out_channels, C.d.kernel, C.d.stride, C.d.padding, C.h, C.w, batch,
+                                                                        C.d.activation ? MIMIR_B200_ELT_RELU : C.fused_act));
+      if (!conv_in) {
+        keep.push_back(ci);
+        continue;
+      }
+      C.in_up = true;
+      C.in_v[0] = sv;
+      m->tensors[sv].consumers.push_back(ci);
+    }
+    if (keep.size() == ut.consumers.size()) continue;  // nothing changed
+    ut.consumers = keep;
+    if (keep.empty()) {
+      for (int& c : m->tensors[U.in_v[0]].consumers)
+        if (c == li) c = -1;
+      auto& sc = m->tensors[U.in_v[0]].consumers;
+      sc.erase(std::remove(sc.begin(), sc.end(), -1), sc.end());
+      ut.want_f32 = false;
+      ut.producer = -2;  // dead
+      U.skip = true;
+    }
   }
   // ---- fusion 2: hi/lo planes straight from one GEMM epilogue into the next Linear -------------
   for (int li = 0; li < nl; ++li) {
@@ -1171,6 +1212,7 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
           e.pre_eps = G.d.eps;
           e.pre_act = G.fused_act;
         }
+        e.in_up = L.in_up ? 1 : 0;
         s = conv_exec(e, st);
         break;
       }

@@ -97,6 +97,9 @@ struct ConvExec {
   const float* pre_beta = nullptr;
   float pre_eps = 1e-5f;
   int pre_act = -1;
+  // x is [ic][h/2][w/2]: the 2 x 2 nearest-neighbour upsample of the producing layer is applied while the operand planes
+  // are laid out (shifted path only); h and w stay the convolution's own input size
+  int in_up = 0;
 };
 size_t conv_prenorm_bytes(int batch, int groups);
 // stride-1 "same" convolutions with a channel count that is a multiple of 32 run as shifted GEMMs over the

@@ -398,6 +398,46 @@ def test_groupnorm_silu_applied_inside_the_convolution(backend, monkeypatch, sha
                  f"resblock, shared={shared_output}")
 
 
+@pytest.mark.parametrize("conv_skip,fuse", [(False, "1"), (True, "1"), (True, "0")])
+def test_nearest_upsample_gathered_by_the_convolutions_that_read_it(backend, monkeypatch, conv_skip, fuse):
+    """UNet up block: UpsampleNearest 2x -> [GroupNorm -> SiLU -> Conv3x3 -> GroupNorm -> SiLU -> Conv3x3] + skip.  The
+    convolutions that read the upsampled tensor take it from the half-size source while their operand planes are laid out
+    (the folded GroupNorm's statistics too); with a 1x1 convolution on the skip path the upsampled tensor is never
+    produced, with an identity skip it is still produced for the residual add.  MIMIR_B200_FUSE_UPSAMPLE=0 keeps the
+    upsample a layer of its own."""
+    monkeypatch.setenv("MIMIR_B200_FUSE_UPSAMPLE", fuse)
+    ic, hw, batch, groups = 64, 8, 3, 8
+    oc = 32 if conv_skip else ic
+    up = 2 * hw
+    gn = lambda c: dict(in_channels=c, input_height=up, input_width=up, num_groups=groups, params_count=2 * c)  # noqa: E731
+    cv = lambda i, o, k: dict(in_channels=i, out_channels=o, input_height=up, input_width=up, kernel=k, stride=1, padding=k // 2,  # noqa: E731
+                              params_count=o * i * k * k)
+    descs = [
+        make_desc("up", "UpsampleNearest", inputs=["x"], output="u", in_channels=ic, out_h=hw, out_w=hw, scale_h=2, scale_w=2),
+        make_desc("gn1", "GroupNorm", inputs=["u"], output="n1", **gn(ic)),
+        make_desc("act1", "SiLU", inputs=["n1"], output="a1"),
+        make_desc("conv1", "Conv2d", inputs=["a1"], output="c1", **cv(ic, oc, 3)),
+        make_desc("gn2", "GroupNorm", inputs=["c1"], output="n2", **gn(oc)),
+        make_desc("act2", "SiLU", inputs=["n2"], output="a2"),
+        make_desc("conv2", "Conv2d", inputs=["a2"], output="c2", **cv(oc, oc, 3)),
+    ]
+    r = np.random.default_rng(31)
+    gw = lambda c: np.concatenate([1 + 0.2 * r.standard_normal(c), 0.1 * r.standard_normal(c)]).astype(np.float32)  # noqa: E731
+    cw = lambda i, o, k: (r.standard_normal(o * i * k * k) * np.sqrt(2 / (i * k * k))).astype(np.float32)  # noqa: E731
+    weights = [None, gw(ic), None, cw(ic, oc, 3), gw(oc), None, cw(oc, oc, 3)]
+    if conv_skip:
+        descs.append(make_desc("skip", "Conv2d", inputs=["u"], output="s", **cv(ic, oc, 1)))
+        weights.append(cw(ic, oc, 1))
+        descs.append(make_desc("add", "Add", inputs=["c2", "s"], output="x"))
+    else:
+        descs.append(make_desc("add", "Add", inputs=["c2", "u"], output="x"))
+    weights.append(None)
+    x = (r.standard_normal((batch, ic * hw * hw)) * 1.5 + 0.3).astype(np.float32)
+    inputs = {"x": (x.ravel(), False)}
+    assert_close(gpu_batch(backend, descs, weights, inputs, batch, oc * up * up), oracle_batch(descs, weights, inputs, batch),
+                 f"up block, conv_skip={conv_skip}, fuse={fuse}")
+
+
 def test_replayed_graph_with_one_pass_rmsnorm_and_cluster_layernorm(backend):
     """The captured layer loop holds a memset node + the ticketed single-pass RMSNorm, and a cluster-launched
     LayerNorm: five forwards (run, capture, three replays) must agree bit for bit and with the oracle."""
