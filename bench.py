@@ -539,6 +539,66 @@ def bench_norms(h: Harness, rt, peaks):
     return out
 
 
+def bench_gemm_shapes(h: Harness, rt, peaks, rows=32768):
+    """The decoder configuration's projection shapes as single Linear layers (M = rows), in the strict two-MMA mode (bf16-exact
+    weights) and in the one-MMA mode: time inside the GEMM kernel (CUDA events around every launch), algorithmic and issued
+    fraction of the sustained bf16 peak.  The last record is configuration 2's layer in its three-MMA mode."""
+    from mimir_framework_b200 import abi
+
+    torch = h.torch
+    shapes = [("qkv", rows, 768, 2304, False), ("attention out-projection", rows, 768, 768, False), ("ffn up + GELU", rows, 768, 3072, True),
+              ("ffn down", rows, 3072, 768, False), ("lm head", rows, 768, 32000, False)]
+    out = []
+    r = np.random.default_rng(4)
+
+    def one(name, M, K, N, gelu, precision, mmas):
+        w = configs.round_to_bf16((r.standard_normal(K * N + N) * 0.02).astype(np.float32)) if precision != abi.PREC_BF16X2 else \
+            (r.standard_normal(K * N + N) * 0.02).astype(np.float32)
+        descs = [abi.make_desc("l", "Linear", inputs=["x"], output="h" if gelu else "x", in_features=K, out_features=N, seq_len=M, use_bias=1, params_count=K * N + N)]
+        weights = [w]
+        if gelu:  # folded into the GEMM's epilogue by the planner
+            descs.append(abi.make_desc("a", "GELU", inputs=["h"], output="x"))
+            weights.append(None)
+        m = rt.GraphModel(descs, precision)
+        for i, wt in enumerate(weights):
+            m.upload_weights(i, wt)
+        m.plan({"x": (M * K, False)}, 1)
+        x = torch.randn(M * K, device="cuda")
+        n_out = M * N
+        y = torch.empty(n_out, device="cuda")
+        spec = {"x": (x.data_ptr(), M * K, False)}
+        for _ in range(3):
+            m.forward_device(spec, 1, y.data_ptr(), n_out, h.stream)
+        torch.cuda.synchronize()
+        # one launch at a time under the profile switch: the first GEMM of the graph is the shape under study
+        rt.profile_gemm(True)
+        m.forward_device(spec, 1, y.data_ptr(), n_out, h.stream)
+        rt.profile_read()
+        times = []
+        for _ in range(10):
+            m.forward_device(spec, 1, y.data_ptr(), n_out, h.stream)
+            ms, n = rt.profile_read()
+            times.append(ms)
+        rt.profile_gemm(False)
+        m.close()
+        del x, y
+        return times
+
+    for name, M, K, N, gelu in shapes:
+        for precision, label, mmas in ((abi.PREC_BF16W, "BF16W", 2), (abi.PREC_BF16, "BF16", 1)):
+            times = one(name, M, K, N, gelu, precision, mmas)
+            ms = float(np.median(times))
+            tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+            out.append({"layer": name, "m": M, "k": K, "n": N, "precision": label, "mma_per_product": mmas, "ms": ms, "tflops_algorithmic": tf,
+                        "frac_algorithmic": tf / peaks["bf16_sustained"], "frac_issued": mmas * tf / peaks["bf16_sustained"]})
+    times = one("config 2 layer", 65536, 4096, 4096, False, abi.PREC_BF16X2, 3)
+    ms = float(np.median(times))
+    tf = 2.0 * 65536 * 4096 * 4096 / (ms * 1e-3) / 1e12
+    out.append({"layer": "config 2 layer (Linear + bias)", "m": 65536, "k": 4096, "n": 4096, "precision": "BF16X2", "mma_per_product": 3, "ms": ms,
+                "tflops_algorithmic": tf, "frac_algorithmic": tf / peaks["bf16_sustained"], "frac_issued": 3 * tf / peaks["bf16_sustained"]})
+    return out
+
+
 def bench_decode_steps(h: Harness, rt, peaks, batch=16):
     """Token-by-token generation on the decoder configuration's shape with token-wise LayerNorm (the reference's
     whole-sample RMSNorm makes every row depend on later tokens, so that graph cannot be decoded incrementally):
@@ -645,6 +705,8 @@ def run_ours(args):
             rec["norms"] = bench_norms(h, rt, peaks)
         if args.only == "decode":
             rec["decode"] = bench_decode_steps(h, rt, peaks)
+        if args.only == "gemm":
+            rec["gemm_shapes"] = bench_gemm_shapes(h, rt, peaks)
         if rank == 0:
             print(json.dumps(rec))
         if world > 1:
@@ -741,6 +803,7 @@ def run_ours(args):
         extras["norms"] = bench_norms(h, rt, peaks)
         if world == 1:
             extras["decode"] = bench_decode_steps(h, rt, peaks)
+            extras["gemm_shapes"] = bench_gemm_shapes(h, rt, peaks)
         if world > 1:
             extras["single_process"] = bench_single_process(h, rt, args.single_process_rows, e2e_steps, args.pipeline)
 
@@ -794,7 +857,7 @@ def main():
     ap.add_argument("--ref-rows", type=int, default=1024, help="rows per step of --impl reference")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--headline-only", action="store_true", help="skip the other configurations, the norm kernels and the single-process leg")
-    ap.add_argument("--only", default="all", choices=["all", "headline", "configs", "c1", "c3", "c4", "c5", "norms", "decode"],
+    ap.add_argument("--only", default="all", choices=["all", "headline", "configs", "c1", "c3", "c4", "c5", "norms", "decode", "gemm"],
                     help="run one leg alone and print its records (no headline line)")
     ap.add_argument("--precision", default="default", choices=["default", "one-mma"],
                     help="configs 3 and 5: 'one-mma' runs the one-plane-per-operand mode as the only arm (for profiling it); "
