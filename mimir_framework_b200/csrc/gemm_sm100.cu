@@ -117,7 +117,10 @@ struct SmemLayout {
 
 constexpr int MAX_STAGES = 8;
 
-template <int BK, int RING_BYTES>
+// CM = 1 compiles the channel-major forms in (NCHW output, convolution as shifted GEMMs, swapped operands); the plain
+// row-major form (CM = 0: every Linear and attention projection) is built without them, so that the two families
+// neither share a register budget nor slow each other's epilogue down.
+template <int BK, int RING_BYTES, int CM>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_o, const GemmParams p) {
@@ -165,7 +168,9 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const uint32_t tmem_base = *tmem_slot;
 
   // planes on the M side (128-row tiles) and on the N side (256-row tiles) of the MMA
-  const int m_planes = p.swap ? p.w_planes : p.a_planes, n_planes = p.swap ? p.a_planes : p.w_planes;
+  const bool swapped = CM && p.swap;
+  const bool conv = CM && p.conv_ks > 0;
+  const int m_planes = swapped ? p.w_planes : p.a_planes, n_planes = swapped ? p.a_planes : p.w_planes;
   const uint32_t tx_bytes = static_cast<uint32_t>(m_planes * A_TILE + n_planes * (p.bn * BK * 2));
 
   if (warp == 0) {
@@ -182,13 +187,13 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           uint8_t* sbase = smem + stage * STAGE_BYTES;
           mbar_expect_tx(&full_bar[stage], tx_bytes);
           int a_col = kb * BK, a_row = tm * BM;
-          if (p.conv_ks > 0) {
+          if (conv) {
             const int t = kb / p.conv_cblocks, cb = kb - t * p.conv_cblocks;
             const int kh = t / p.conv_ks, kw = t - kh * p.conv_ks;
             a_row += (kh - p.conv_pad) * p.conv_wp + (kw - p.conv_pad);  // may be negative: TMA zero-fills
             a_col = cb * BK;
           }
-          if (!p.swap) {
+          if (!swapped) {
             for (int pl = 0; pl < p.a_planes; ++pl)
               tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
             for (int pl = 0; pl < p.w_planes; ++pl)
@@ -260,7 +265,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const int ew = warp - 2;
     const int quad = warp & 3;   // TMEM lane quadrant this warp may read
     const int half = ew >> 2;    // which half of the columns
-    const bool chan_major = (p.ohw > 0 || p.conv_ks > 0);
+    const bool chan_major = CM && (p.ohw > 0 || p.conv_ks > 0);
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
@@ -276,13 +281,13 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       tcgen05_fence_after();
       const int row0 = tm * BM + quad * 32;
       const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      if (p.swap) {
+      if (swapped) {
         // TMEM lane = output channel, column = activation row (pixel).  Each 32 x 32 chunk is turned around
         // through a padded shared-memory tile so that a lane owns a pixel again and the NCHW stores (and
         // residual loads) of a warp are 128 contiguous bytes per channel, as in the unswapped form.
         float* tbuf = reinterpret_cast<float*>(epi_tiles) + ew * (32 * 33);
         const int oc0 = row0;  // first output channel of this warp's 32 lanes
-        const long long hw = (p.conv_ks > 0) ? static_cast<long long>(p.conv_h) * p.conv_w : static_cast<long long>(p.ohw);
+        const long long hw = conv ? static_cast<long long>(p.conv_h) * p.conv_w : static_cast<long long>(p.ohw);
         // where this lane's pixel of chunk ci lands in the NCHW output; false = the chunk is past the matrix (warp-uniform)
         auto geom = [&](int ci, int& c0, bool& pv, long long& o0) -> bool {
           c0 = (half * (BN / 64) + ci) * 32;
@@ -291,7 +296,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           const int prow = r0 + lane;
           pv = prow < p.m;
           long long pbase = 0;
-          if (p.conv_ks > 0) {
+          if (conv) {
             const int per = p.conv_hp * p.conv_wp;
             const int smp = prow / per, rem = prow - smp * per;
             const int yq = rem / p.conv_wp;
@@ -362,7 +367,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (chan_major) {
         const int row = row0 + lane;
         cm_ok = row < p.m;
-        if (p.conv_ks > 0) {
+        if (conv) {
           const int per = p.conv_hp * p.conv_wp;
           const int smp = row / per, rem = row - smp * per;
           const int yq = rem / p.conv_wp;
@@ -376,13 +381,9 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           cm_o0 = smp * p.n * cm_stride + (row - smp * p.ohw);
         }
       }
-#pragma unroll 1
-      for (int ci = 0; ci < (p.bn / 32) / 2; ++ci) {
-        const int c0 = (half * (p.bn / 64) + ci) * 32;
-        const int col0 = tn * p.bn + c0;
-        if (col0 >= col_limit) break;  // warp-uniform
-        float v[32];
-        tmem_ld_32x32(taddr0 + c0, v);
+      // one 32-column chunk of this lane's row: scale, bias, activation, residual, stores
+      auto process = [&](const int c0, const int col0, float (&v)[32]) {
+        (void)c0;
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] *= p.acc_scale;
         const bool full_cols = (col0 + 32 <= p.n);
@@ -496,6 +497,19 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             }
           }
         }
+      };
+      // (Tried: the next chunk's tensor-memory load in flight while this one is processed - two register sets, the
+      // plain form has the room.  Measured neutral to 7 % slower on the K = 768 layers: the load's latency is not what
+      // the short-K tiles wait for; operand and store bytes per MMA cycle are.)
+      const int nch = (p.bn / 32) / 2;
+#pragma unroll 1
+      for (int ci = 0; ci < nch; ++ci) {
+        const int c0 = (half * (p.bn / 64) + ci) * 32;
+        const int col0 = tn * p.bn + c0;
+        if (col0 >= col_limit) break;  // warp-uniform
+        float v[32];
+        tmem_ld_32x32(taddr0 + c0, v);
+        process(c0, col0, v);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -710,10 +724,12 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
     const int want = env_int("MIMIR_B200_GEMM_STAGES", 0);
     if (want >= 2 && want < p.stages) p.stages = want;
   }
-  auto kern = gemm_tn_bf16split_kernel<BK, RING_BYTES>;
+  const bool cm = swap || conv || g.out_nchw_hw > 0;
+  auto kern = cm ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 0>;
   static PerDeviceOnce attr_once;
   MB_TRY(attr_once.run([&]() -> int {
-    MB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     return MIMIR_B200_OK;
   }));
   const int tiles = p.tiles_m * p.tiles_n;
