@@ -120,14 +120,21 @@ constexpr int MAX_STAGES = 8;
 // CM = 1 compiles the channel-major forms in (NCHW output, convolution as shifted GEMMs, swapped operands); the plain
 // row-major form (CM = 0: every Linear and attention projection) is built without them, so that the two families
 // neither share a register budget nor slow each other's epilogue down.
-template <int BK, int RING_BYTES, int CM>
+// PAIR = 1 (not with swapped operands): the kernel runs as clusters of two CTAs on neighbouring SMs that share one 256-row x 256-column
+// tile (tcgen05 with cta_group::2).  Each CTA loads its own 128 rows of A and only HALF of the W tile; the even-ranked
+// CTA issues the MMAs for both, each CTA reads its 128 accumulator rows out of its own tensor memory.  The operand
+// bytes an SM pulls from L2 per MMA cycle drop by a quarter to a third, which is what the short-K layers are short of.
+template <int BK, int RING_BYTES, int CM, int PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_o, const GemmParams p) {
   constexpr int SWZ = BK * 2;                      // bytes per smem row = swizzle span
   constexpr int A_TILE = BM * BK * 2;
-  constexpr int W_TILE = BN * BK * 2;
+  constexpr int W_TILE = (PAIR ? BN / 2 : BN) * BK * 2;  // a CTA of a pair holds half of the N side
   const int STAGES = p.stages, STAGE_BYTES = p.stage_bytes;
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;  // 0 = the pair's leader
+  const int t_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int t_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -152,18 +159,24 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
     for (int a = 0; a < NUM_ACC; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], EPI_WARPS);
+      mbar_init(&acc_empty[a], PAIR ? 2 * EPI_WARPS : EPI_WARPS);  // the leader's collects both CTAs' epilogue warps
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -171,7 +184,8 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   const bool swapped = CM && p.swap;
   const bool conv = CM && p.conv_ks > 0;
   const int m_planes = swapped ? p.w_planes : p.a_planes, n_planes = swapped ? p.a_planes : p.w_planes;
-  const uint32_t tx_bytes = static_cast<uint32_t>(m_planes * A_TILE + n_planes * (p.bn * BK * 2));
+  const uint32_t tx_bytes = PAIR ? static_cast<uint32_t>(2 * (m_planes * A_TILE + n_planes * W_TILE))  // both CTAs' loads land on the leader's barrier
+                                 : static_cast<uint32_t>(m_planes * A_TILE + n_planes * (p.bn * BK * 2));
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
@@ -179,13 +193,13 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = t_first; t < num_tiles && ok; t += t_step) {
         int tm, tn;
         tile_coords(t, p, tm, tn);
+        if (PAIR) tm = tm * 2 + static_cast<int>(crank);  // p.tiles_m counts row PAIRS
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err_word, 1)) { ok = false; break; }
           uint8_t* sbase = smem + stage * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[stage], tx_bytes);
           int a_col = kb * BK, a_row = tm * BM;
           if (conv) {
             const int t = kb / p.conv_cblocks, cb = kb - t * p.conv_cblocks;
@@ -193,6 +207,19 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             a_row += (kh - p.conv_pad) * p.conv_wp + (kw - p.conv_pad);  // may be negative: TMA zero-fills
             a_col = cb * BK;
           }
+          if (PAIR) {
+            // the leader arms its barrier for the bytes of both CTAs; this CTA's bytes are counted there whichever
+            // of the two arrives first (the phase cannot complete before the leader's arrive)
+            if (crank == 0) mbar_expect_tx(&full_bar[stage], tx_bytes);
+            const uint32_t fb = mapa_shared(smem_u32(&full_bar[stage]), 0);
+            for (int pl = 0; pl < p.a_planes; ++pl)
+              tma_load_3d_pair(sbase + pl * A_TILE, &map_a, fb, a_col, a_row, pl);
+            for (int pl = 0; pl < p.w_planes; ++pl)
+              tma_load_3d_pair(sbase + m_planes * A_TILE + pl * W_TILE, &map_w, fb, kb * BK, tn * BN + static_cast<int>(crank) * (BN / 2), pl);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
+          mbar_expect_tx(&full_bar[stage], tx_bytes);
           if (!swapped) {
             for (int pl = 0; pl < p.a_planes; ++pl)
               tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
@@ -218,14 +245,14 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(BM, p.bn, p.f16);
+    if (lane == 0 && crank == 0) {
+      const uint32_t idesc = make_idesc(PAIR ? 2 * BM : BM, p.bn, p.f16);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = t_first; t < num_tiles && ok; t += t_step) {
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.err_word, 3)) break;
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -239,20 +266,31 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             const uint32_t koff = k * UMMA_K * 2;  // bytes along K inside the swizzled row
             const uint64_t a_hi = make_smem_desc(sa + koff, SWZ);
             const uint64_t w_hi = make_smem_desc(sw + koff, SWZ);
-            umma_bf16(d_tmem, a_hi, w_hi, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (PAIR) umma_bf16_pair(d_tmem, a_hi, w_hi, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_bf16(d_tmem, a_hi, w_hi, idesc, (kb | k) != 0 ? 1u : 0u);
             if (m_planes == 2) {
               const uint64_t a_lo = make_smem_desc(sa + A_TILE + koff, SWZ);
-              umma_bf16(d_tmem, a_lo, w_hi, idesc, 1u);
+              if (PAIR) umma_bf16_pair(d_tmem, a_lo, w_hi, idesc, 1u);
+              else umma_bf16(d_tmem, a_lo, w_hi, idesc, 1u);
             }
             if (n_planes == 2) {
               const uint64_t w_lo = make_smem_desc(sw + W_TILE + koff, SWZ);
-              umma_bf16(d_tmem, a_hi, w_lo, idesc, 1u);
+              if (PAIR) umma_bf16_pair(d_tmem, a_hi, w_lo, idesc, 1u);
+              else umma_bf16(d_tmem, a_hi, w_lo, idesc, 1u);
             }
           }
+          if (PAIR) {  // frees the stage in both CTAs when these MMAs have read it
+            umma_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 0));
+            umma_commit_pair(mapa_shared(smem_u32(&empty_bar[stage]), 1));
+          } else
           umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
+        if (PAIR) {
+          umma_commit_pair(mapa_shared(smem_u32(&acc_full[acc]), 0));
+          umma_commit_pair(mapa_shared(smem_u32(&acc_full[acc]), 1));
+        } else
         umma_commit(&acc_full[acc]);
         if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
       }
@@ -268,9 +306,10 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const bool chan_major = CM && (p.ohw > 0 || p.conv_ks > 0);
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int t = t_first; t < num_tiles; t += t_step) {
       int tm, tn;
       tile_coords(t, p, tm, tn);
+      if (PAIR) tm = tm * 2 + static_cast<int>(crank);
       // lane 0 does the bounded wait; the verdict is made warp-uniform because tcgen05.ld below
       // is a warp-collective instruction
       int ok = 1;
@@ -513,7 +552,10 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[acc]), 0));  // the leader's MMA thread waits for both CTAs
+        else mbar_arrive(&acc_empty[acc]);
+      }
       if (++acc == NUM_ACC) { acc = 0; acc_phase ^= 1; }
     }
     if (lane == 0) bulk_wait_read0();  // no copy may still be reading shared memory when the CTA exits
@@ -521,9 +563,11 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
   tcgen05_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still signal it
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -675,7 +719,17 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
     static const int force = env_int("MIMIR_B200_GEMM_BN", 0);
     if (force == 192) p.bn = 192;
   }
-  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : p.bn));
+  // CTA pairs: every form but the swapped one, full-width tiles.  Taken by default where they were measured to pay: launches of at least one
+  // full wave of tiles in the modes with two or three MMAs per product (same-run A/B: the K = N = 4096 layer 14.9-15.0
+  // -> 14.5 ms per three-layer step = 0.333 of the sustained peak, the whole ceiling of the three-MMA scheme; the decoder
+  // step 18.51 -> 18.2 ms).  The one-MMA mode (14.78 -> 14.88 ms) and launches of a few tiles (the registry
+  // transformer's 1024-row layers: 0.290 -> 0.295 ms per step) are better off alone.  MIMIR_B200_GEMM_PAIR=0 turns pairs
+  // off, =1 takes them wherever the form allows.
+  static const int pair_env = env_int("MIMIR_B200_GEMM_PAIR", -1);
+  const bool pair_can = !swap && !tma_store && p.bn == BN && p.tiles_m >= 2;
+  const long long tiles_all = static_cast<long long>(p.tiles_m) * ((g.n + BN - 1) / BN);
+  const bool pair = pair_can && (pair_env == 1 || (pair_env != 0 && g.a_planes + g.w_planes >= 3 && tiles_all >= ctx().sm_count));
+  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : (pair ? BN / 2 : p.bn)));
   p.m = g.m;
   p.n = g.n;
   p.kblocks = conv ? g.conv_ks * g.conv_ks * (g.conv_c / BK) : kp / BK;
@@ -689,6 +743,7 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.a_planes = g.a_planes;
   p.w_planes = g.w_planes;
   p.tiles_n = swap ? (g.m + BN - 1) / BN : (g.n + p.bn - 1) / p.bn;
+  if (pair) p.tiles_m = (p.tiles_m + 1) / 2;  // row PAIRS: the CTA of rank r takes row tile 2 * pair + r
   p.group_n = env_int("MIMIR_B200_GEMM_GROUP_N", 8);
   if (p.group_n < 1) p.group_n = 1;
   if (p.group_n > p.tiles_n) p.group_n = p.tiles_n;
@@ -718,29 +773,52 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   static_assert(SMEM <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   {
     const int m_pl = swap ? g.w_planes : g.a_planes, n_pl = swap ? g.a_planes : g.w_planes;
-    p.stage_bytes = m_pl * BM * BK * 2 + n_pl * BN * BK * 2;
+    p.stage_bytes = m_pl * BM * BK * 2 + n_pl * (pair ? BN / 2 : BN) * BK * 2;
     p.stages = RING_BYTES / p.stage_bytes;
     if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
     const int want = env_int("MIMIR_B200_GEMM_STAGES", 0);
     if (want >= 2 && want < p.stages) p.stages = want;
   }
   const bool cm = swap || conv || g.out_nchw_hw > 0;
-  auto kern = cm ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 0>;
+  auto kern = cm ? (pair ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 0>)
+                 : (pair ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 0, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 0, 0>);
   static PerDeviceOnce attr_once;
   MB_TRY(attr_once.run([&]() -> int {
-    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
-    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     return MIMIR_B200_OK;
   }));
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
+  int grid = tiles < ctx().sm_count ? tiles : ctx().sm_count;
+  if (pair) {
+    const int pairs = ctx().sm_count / 2;
+    grid = 2 * (tiles < pairs ? tiles : pairs);
+  }
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   if (ctx().prof_gemm) {
     MB_CUDA(cudaEventCreate(&e0));
     MB_CUDA(cudaEventCreate(&e1));
     MB_CUDA(cudaEventRecord(e0, st));
   }
-  kern<<<grid, NUM_THREADS, SMEM, st>>>(map_a, map_w, map_o, p);
+  if (pair) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MB_CUDA(cudaLaunchKernelEx(&cfg, kern, map_a, map_w, map_o, p));
+  } else {
+    kern<<<grid, NUM_THREADS, SMEM, st>>>(map_a, map_w, map_o, p);
+  }
   MB_CUDA(cudaGetLastError());
   if (e0) {
     MB_CUDA(cudaEventRecord(e1, st));
