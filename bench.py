@@ -48,7 +48,7 @@ K = configs.LINEAR_STACK_K
 
 # DRAM bytes (read + write) of one GEMM launch of this workload at M = 8192 rows, from the ncu capture
 # summarised in profiles/gemm_tn_bf16split_linear_stack.md
-NCU_TRAFFIC_BYTES_AT_8192_ROWS = 627.6e6
+NCU_TRAFFIC_BYTES_AT_8192_ROWS = 656.9e6
 NCU_WEIGHT_BYTES = 2 * 2 * 4096 * 4096  # the hi and lo weight planes, read once per launch whatever the row count
 
 
