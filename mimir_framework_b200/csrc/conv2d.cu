@@ -52,6 +52,57 @@ __global__ void im2col_split_kernel(const float* __restrict__ x, __nv_bfloat16* 
   }
 }
 
+// The same rows from a staged input patch: a CTA owns I2C_TPX consecutive output pixels of one output row and a block of
+// `cb` input channels (a multiple of 8, or all of them), loads the patch those pixels read - cb x ks rows of
+// (I2C_TPX - 1) * stride + ks input pixels, coalesced - into shared memory once, and assembles the 16-byte chunks of its K
+// range from there (consecutive threads: consecutive chunks of one pixel, i.e. contiguous stores).  The input is read
+// once per channel block instead of once per K entry through the caches, and the index arithmetic is per chunk.
+constexpr int I2C_TPX = 32;
+
+__global__ void __launch_bounds__(256) im2col_tile_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst, long long rows,
+                                                          int ic, int h, int w, int ks, int stride, int pad, int oh, int ow, int k,
+                                                          int kp, int planes, int f16, int cb, int nblocks) {
+  extern __shared__ float patch[];  // [cbn][ks][pw]
+  const int ox0 = blockIdx.x * I2C_TPX, oy = blockIdx.y;
+  const int smp = blockIdx.z / nblocks, blk = blockIdx.z - smp * nblocks;
+  const int c0 = blk * cb, cbn = min(cb, ic - c0);
+  const int kk = ks * ks, pw = (I2C_TPX - 1) * stride + ks;
+  const int iy0 = oy * stride - pad, ix0 = ox0 * stride - pad;
+  const float* xs = x + (static_cast<long long>(smp) * ic + c0) * h * w;
+  for (int i = threadIdx.x; i < cbn * ks * pw; i += 256) {
+    const int c = i / (ks * pw), r = i - c * (ks * pw);
+    const int ky = r / pw, px = r - ky * pw;
+    const int iy = iy0 + ky, ix = ix0 + px;
+    patch[i] = (iy >= 0 && iy < h && ix >= 0 && ix < w) ? __ldg(xs + (static_cast<long long>(c) * h + iy) * w + ix) : 0.0f;
+  }
+  __syncthreads();
+  // this block's chunks of a row: its channels' K range; the last block also writes the zero padding up to kp
+  const int ch_lo = (c0 * kk) >> 3, ch_hi = (blk == nblocks - 1) ? (kp >> 3) : (((c0 + cbn) * kk) >> 3);
+  const int nch = ch_hi - ch_lo, npx = min(I2C_TPX, ow - ox0);
+  const long long plane_stride = rows * static_cast<long long>(kp);
+  const long long row0 = (static_cast<long long>(smp) * oh + oy) * ow + ox0;
+  for (int item = threadIdx.x; item < npx * nch; item += 256) {
+    const int p = item / nch, chunk = ch_lo + (item - p * nch);
+    const int kidx0 = chunk * 8 - c0 * kk;  // relative to this block's first channel
+    int ci = kidx0 / kk, t = kidx0 - ci * kk;
+    int ky = t / ks, kx = t - ky * ks;
+    __align__(16) uint16_t hi[8];
+    __align__(16) uint16_t lo[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = (ci < cbn) ? patch[(ci * ks + ky) * pw + p * stride + kx] : 0.0f;  // past the last channel: K padding
+      split_one(v, f16, hi[j], lo[j]);
+      if (++kx == ks) {
+        kx = 0;
+        if (++ky == ks) { ky = 0; ++ci; }
+      }
+    }
+    __nv_bfloat16* d = dst + (row0 + p) * kp + chunk * 8;
+    *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(hi);
+    if (planes == 2) *reinterpret_cast<uint4*>(d + plane_stride) = *reinterpret_cast<const uint4*>(lo);
+  }
+}
+
 }  // namespace
 
 int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, int h, int w, int ks, int stride, int pad,
@@ -60,6 +111,23 @@ int launch_im2col_split(const float* x, __nv_bfloat16* dst, int batch, int ic, i
     return fail(MIMIR_B200_E_INVALID, "Conv2d: in_channels and out_channels must be set");
   const int k = ic * ks * ks, kp = round_up(k, 64);
   const long long rows = static_cast<long long>(batch) * oh * ow;
+  {
+    // the staged form: channel blocks of a multiple of 8 (so that every block starts on a chunk boundary) within 48 KB
+    static const bool off = [] { const char* e = getenv("MIMIR_B200_IM2COL_TILED"); return e && e[0] == '0'; }();
+    const int pw = (I2C_TPX - 1) * stride + ks;
+    const long long per_ch = static_cast<long long>(ks) * pw * 4;
+    int cb = static_cast<int>(std::min<long long>(ic, (48 * 1024) / per_ch));
+    if (cb < ic) cb &= ~7;
+    const int nblocks = cb > 0 ? (ic + cb - 1) / cb : 0;
+    if (!off && cb > 0 && static_cast<long long>(batch) * nblocks <= 65535 && oh <= 65535) {
+      dim3 grid((ow + I2C_TPX - 1) / I2C_TPX, oh, batch * nblocks);
+      im2col_tile_kernel<<<grid, 256, static_cast<size_t>(cb) * per_ch, st>>>(x, dst, rows, ic, h, w, ks, stride, pad, oh, ow, k, kp, planes,
+                                                                              plane_format() == PLANES_F16, cb, nblocks);
+      MB_CUDA(cudaGetLastError());
+      count_launch();
+      return MIMIR_B200_OK;
+    }
+  }
   const long long total = rows * (kp >> 3);
   long long blocks = (total + 255) / 256;
   const long long cap = static_cast<long long>(ctx().sm_count) * 32;
