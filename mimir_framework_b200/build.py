@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 INCLUDE = os.path.join(ROOT, "include")
 OUT = os.path.join(HERE, "libmimir_b200.so")
-SOURCES = ["gemm_sm100.cu", "skinny.cu", "pointwise.cu", "norms.cu", "attention.cu", "attention_tc.cu", "conv2d.cu", "spatial.cu", "capi.cu", "capi_ext.cu", "graph.cu", "safetensors.cu", "replicas.cu", "sequence.cu"]
+SOURCES = ["gemm_sm100.cu", "skinny.cu", "pointwise.cu", "norms.cu", "attention.cu", "attention_tc.cu", "attention_gemm.cu", "conv2d.cu", "spatial.cu", "capi.cu", "capi_ext.cu", "graph.cu", "safetensors.cu", "replicas.cu", "sequence.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-I" + INCLUDE, "-I" + CSRC,

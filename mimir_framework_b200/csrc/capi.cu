@@ -166,6 +166,7 @@ size_t attention_ws_bytes(int batch, int seq, int embed, int heads, int precisio
   const size_t rows = static_cast<size_t>(batch) * seq;
   size_t b = align256(split_bytes(static_cast<int64_t>(rows), embed, ap)) + align256(rows * 3 * embed * 4) + align256(rows * embed * 4);
   if (attention_tc_supported(seq, embed, heads)) b += align256(attention_tc_ws_bytes(batch, seq, embed));
+  else if (attention_gemm_supported(batch, seq, embed, heads)) b += align256(attention_gemm_ws_bytes(batch, seq, embed));
   return b;
 }
 
@@ -231,6 +232,9 @@ int attention_exec(const AttentionExec& e, cudaStream_t st) {
   if (attention_tc_supported(e.seq, e.embed, e.heads)) {
     MB_TRY(launch_attention_core_tc(qkv, nullptr, e.batch, e.seq, e.embed, e.heads, e.causal, tc_ws, st, xs, ap,
                                     qkv_as_planes ? reinterpret_cast<const __nv_bfloat16*>(qkv) : nullptr));
+  } else if (attention_gemm_supported(e.batch, e.seq, e.embed, e.heads) && !e.kcache) {
+    // one wide head: scores and P.V as block-diagonal GEMMs; the second one writes the output projection's planes
+    MB_TRY(launch_attention_core_gemm(qkv, e.batch, e.seq, e.embed, e.causal, tc_ws, xs, st));
   } else {
     MB_TRY(launch_attention_core(qkv, att, e.batch, e.seq, e.embed, e.heads, e.causal, st));
     MB_TRY(launch_split(att, xs, rows, e.embed, ap, st));

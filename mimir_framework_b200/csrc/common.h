@@ -136,6 +136,11 @@ struct GemmArgs {
   // Shifted-GEMM convolution (conv_ks > 0): `a` is the zero-padded NHWC activation [samples*(h+2p)*(w+2p)][conv_c],
   // m counts padded-grid rows, k = conv_ks^2 * conv_c ordered (tap, channel), output is NCHW [samples][n][h][w].
   int conv_ks = 0, conv_c = 0, conv_pad = 0, conv_h = 0, conv_w = 0;
+  // Grouped form (a_group_rows > 0, plain row-major GEMM only): the rows of `a` come in groups of a_group_rows, and group g
+  // multiplies the w rows [g * w_group_rows, g * w_group_rows + n): a block-diagonal batch of small GEMMs in one launch
+  // (attention scores Q_b K_b^T and P_b V_b per sample).  `w` then holds w_rows_total rows.
+  int a_group_rows = 0, w_group_rows = 0;
+  long long w_rows_total = 0;
 };
 // y = act(a · wᵀ + bias) (+ residual); tcgen05 / TMEM / TMA.
 int launch_gemm(const GemmArgs& g, cudaStream_t st);
@@ -211,6 +216,11 @@ int launch_attention_core(const float* qkv, float* out, int batch, int seq, int 
 // general form (cross attention: queries and keys/values from different projections and lengths)
 int launch_attention_core_view(const AttnView& a, float* out, int batch, int embed, int heads, int causal, cudaStream_t st);
 // attention_tc.cu: the same core on tcgen05 (head_dim 64); `ws` holds the bf16 operand planes
+// a single wide head as two block-diagonal GEMMs around a row softmax (attention_gemm.cu)
+bool attention_gemm_supported(int batch, int seq, int embed, int heads);
+size_t attention_gemm_ws_bytes(int batch, int seq, int embed);
+int launch_attention_core_gemm(const float* qkv, int batch, int seq, int embed, int causal, void* ws, __nv_bfloat16* out_split,
+                               cudaStream_t st);
 bool attention_tc_supported(int seq, int embed, int heads);
 size_t attention_tc_ws_bytes(int batch, int seq, int embed);
 int launch_attention_core_tc(const float* qkv, float* out, int batch, int seq, int embed, int heads, int causal, void* ws,

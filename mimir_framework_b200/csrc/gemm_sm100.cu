@@ -95,6 +95,8 @@ struct GemmParams {
   // starved of operands with four (the MMA thread spent a quarter of every tile waiting on a full barrier).
   int stages, stage_bytes;
   int* err_word;
+  // grouped form: W rows of tile (tm, tn) start at (tm * BM / a_group_rows) * w_group_rows + tn * bn (0 = one group)
+  int a_group_rows, w_group_rows;
 };
 
 // Tile order: groups of `group_n` column tiles; inside a group the row tile runs fastest, so the
@@ -224,7 +226,8 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int pl = 0; pl < p.a_planes; ++pl)
               tma_load_3d(sbase + pl * A_TILE, &map_a, &full_bar[stage], a_col, a_row, pl);
             for (int pl = 0; pl < p.w_planes; ++pl)
-              tma_load_3d(sbase + m_planes * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK, tn * p.bn, pl);
+              tma_load_3d(sbase + m_planes * A_TILE + pl * W_TILE, &map_w, &full_bar[stage], kb * BK,
+                          tn * p.bn + (p.a_group_rows > 0 ? (tm * BM / p.a_group_rows) * p.w_group_rows : 0), pl);
           } else {
             // 128 weight rows into the M-side tiles, 256 activation rows (tile tn) into the N-side tiles
             a_row += tn * BN - tm * BM;
@@ -726,10 +729,13 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   // transformer's 1024-row layers: 0.290 -> 0.295 ms per step) are better off alone.  MIMIR_B200_GEMM_PAIR=0 turns pairs
   // off, =1 takes them wherever the form allows.
   static const int pair_env = env_int("MIMIR_B200_GEMM_PAIR", -1);
-  const bool pair_can = !swap && !tma_store && p.bn == BN && p.tiles_m >= 2;
+  const bool pair_can = !swap && !tma_store && p.bn == BN && p.tiles_m >= 2 && g.a_group_rows <= 0;
   const long long tiles_all = static_cast<long long>(p.tiles_m) * ((g.n + BN - 1) / BN);
   const bool pair = pair_can && (pair_env == 1 || (pair_env != 0 && g.a_planes + g.w_planes >= 3 && tiles_all >= ctx().sm_count));
-  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.n, kp, BK, swap ? BM : (pair ? BN / 2 : p.bn)));
+  if (g.a_group_rows > 0 && (swap || conv || g.out_nchw_hw > 0 || g.a_group_rows % BM != 0 || g.w_group_rows <= 0 ||
+                             g.w_rows_total < static_cast<long long>((g.m + g.a_group_rows - 1) / g.a_group_rows - 1) * g.w_group_rows + g.n))
+    return fail(MIMIR_B200_E_INVALID, "gemm: bad grouped-form arguments");
+  MB_TRY(make_plane_map(&map_w, g.w, g.w_planes, g.a_group_rows > 0 ? g.w_rows_total : g.n, kp, BK, swap ? BM : (pair ? BN / 2 : p.bn)));
   p.m = g.m;
   p.n = g.n;
   p.kblocks = conv ? g.conv_ks * g.conv_ks * (g.conv_c / BK) : kp / BK;
@@ -756,6 +762,8 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.np = round_up(g.n, 64);
   p.ohw = g.out_nchw_hw;
   p.err_word = ctx().dev_error_word;
+  p.a_group_rows = g.a_group_rows;
+  p.w_group_rows = g.w_group_rows;
   {
     // Measured on B200 against fp64 products of the same operand planes (random normal operands, K = 256 ... 4096,
     // two and three MMAs per 16-wide K step): the accumulated result is low by 1.47e-8 ... 1.58e-8 of its value per

@@ -94,7 +94,10 @@ def test_matmul_reference_known_answer(backend):
     (2, 200, 128, 2, 1),                      # ragged seq, causal, head_dim 64
     (1, 96, 128, 4, 1),                       # head_dim 32
     (1, 70, 256, 2, 0),                       # head_dim 128
-    (1, 64, 512, 1, 0),                       # single head, head_dim 512 (UNet mid-block shape class)
+    (1, 64, 512, 1, 0),                       # single head, head_dim 512 (UNet mid-block shape class), row kernel (seq % 128 != 0)
+    (3, 256, 512, 1, 0),                      # the UNet mid block itself: one wide head as two block-diagonal GEMMs
+    (2, 128, 128, 1, 1),                      # the same form, causal, one 128-row tile per sample
+    (2, 384, 192, 1, 1),                      # three row tiles per sample, score rows of 384 (K of the second GEMM a multiple of 128 only)
     (3, 129, 192, 3, 1),                      # tensor-core core (head_dim 64): one row past a query tile
     (1, 1, 64, 1, 0),                         # tensor-core core: a single token
     (2, 63, 128, 2, 0),                       # tensor-core core: ragged key tile
