@@ -123,6 +123,34 @@ int mimir_b200_guard_freeze(int freeze);
 int mimir_b200_guard_reset(void);
 int mimir_b200_guard_state(int* blocked, int* frozen, size_t* blocked_attempts, size_t* frozen_attempts);
 
+/* RuntimeAllocator on the device (RuntimeAllocator.hpp:176-310): guarded device buffers with the reference's verbs,
+ * for a host that keeps tensors of its own in HBM beside the planner's arena (the `mimir_b200_dev_*` calls and
+ * `mimir_b200_model_forward_device` take such pointers).  Every verb acts on the calling thread's current device.
+ *   tensor_alloc        allocate_tensor (RuntimeAllocator.hpp:191-225): fp32 tensor of `rank` extents, zero-filled like the
+ *                       reference's std::vector<float>(numel, 0); refused with E_OOM_BUDGET when the local cap
+ *                       (allocator_set_local_cap; the reference's max_ram_mb, 0 = none, which is the default here) or the
+ *                       guard says no.  A non-positive extent or an element count that overflows is E_INVALID.
+ *   buffer_alloc        allocate_buffer (RuntimeAllocator.hpp:228-260): raw bytes, zero-filled.
+ *   buffer_free         what ~TensorHandle / ~BufferHandle do: frees and releases the bytes at the guard.  A pointer the
+ *                       allocator does not own is E_INVALID.
+ *   scratchpad_get      get_scratchpad (RuntimeAllocator.hpp:264-276): the pooled buffer of that tag when it holds at least
+ *                       min_bytes, else a new buffer (a pooled one that is too small stays pooled, as in the reference).
+ *   scratchpad_return   return_scratchpad (RuntimeAllocator.hpp:279-282): back to the pool under the tag it was allocated
+ *                       with; the pool keeps one buffer per tag, a second one of the same tag is freed.
+ *   allocator_stats     get_total_allocated / get_num_allocations (cumulative, reset by allocator_reset_stats) and the
+ *                       guard's peak / current (get_peak_usage / get_current_usage).
+ *   allocator_check_no_leaks   check_no_leaks (RuntimeAllocator.hpp:299-304): 1 when less than 10 MB are in use.
+ * mimir_b200_shutdown frees what is still pooled or live. */
+int mimir_b200_tensor_alloc(const int* shape, int rank, const char* name_or_null, float** device_ptr, size_t* bytes_or_null);
+int mimir_b200_buffer_alloc(size_t bytes, const char* tag_or_null, void** device_ptr);
+int mimir_b200_buffer_free(void* device_ptr);
+int mimir_b200_scratchpad_get(size_t min_bytes, const char* tag_or_null, void** device_ptr, size_t* bytes_or_null);
+int mimir_b200_scratchpad_return(void* device_ptr);
+int mimir_b200_allocator_set_local_cap(size_t bytes);
+int mimir_b200_allocator_stats(size_t* total_allocated, size_t* num_allocations, size_t* peak, size_t* current);
+int mimir_b200_allocator_reset_stats(void);
+int mimir_b200_allocator_check_no_leaks(int* ok);
+
 /* ---------------------------------------------------------------------------------------------
  * 2. Per-op entry points, HOST pointers, synchronous (copy in, run, copy out).
  *    Drop-in for the Vulkan/OpenCL hook `bool ComputeEngine::linearForward(const float* input,

@@ -84,6 +84,15 @@ void dev_free(void* p, size_t bytes) {
   ctx().guard.release(bytes);
 }
 
+void release_owned_buffers() {
+  OwnedBuffers& ob = ctx().owned;
+  std::lock_guard<std::mutex> lk(ob.mu);
+  for (auto& kv : ob.live) dev_free(kv.first, kv.second.bytes);
+  for (auto& kv : ob.pool) dev_free(kv.second.first, kv.second.second);
+  ob.live.clear();
+  ob.pool.clear();
+}
+
 // Reads (and clears) the word that kernels with bounded waits set when a wait gave up.
 int check_device_error_word(cudaStream_t st) {
   int w = 0;
@@ -476,6 +485,119 @@ int mimir_b200_guard_state(int* blocked, int* frozen, size_t* blocked_attempts, 
   if (frozen) *frozen = ctx().guard.frozen ? 1 : 0;
   if (blocked_attempts) *blocked_attempts = ctx().guard.blocked_attempts;
   if (frozen_attempts) *frozen_attempts = ctx().guard.frozen_attempts;
+  return MIMIR_B200_OK;
+}
+
+/* RuntimeAllocator on the device (RuntimeAllocator.hpp:176-310). */
+static int owned_alloc(size_t bytes, const char* tag, void** out) {
+  if (!out) return fail(MIMIR_B200_E_INVALID, "allocator: null result pointer");
+  *out = nullptr;
+  MB_REQUIRE_INIT();
+  if (bytes == 0) return fail(MIMIR_B200_E_INVALID, "allocator: zero bytes asked for %s", tag);
+  OwnedBuffers& ob = ctx().owned;
+  {
+    // the optional local cap comes before the guard, as in allocate_tensor / allocate_buffer
+    std::lock_guard<std::mutex> lk(ob.mu);
+    size_t current = 0;
+    mimir_b200_guard_stats(nullptr, &current, nullptr);
+    if (ob.local_cap > 0 && current + bytes > ob.local_cap)
+      return fail(MIMIR_B200_E_OOM_BUDGET, "allocator: %zu bytes for %s would exceed the local cap (%zu in use of %zu)", bytes, tag,
+                  current, ob.local_cap);
+  }
+  void* p = nullptr;
+  MB_TRY(dev_alloc(&p, bytes, tag));
+  if (cudaMemset(p, 0, bytes) != cudaSuccess) {
+    dev_free(p, bytes);
+    return fail(MIMIR_B200_E_CUDA, "allocator: clearing %zu bytes for %s failed", bytes, tag);
+  }
+  std::lock_guard<std::mutex> lk(ob.mu);
+  ob.live[p] = OwnedBuffers::Buf{bytes, tag};
+  ob.total_allocated += bytes;
+  ob.num_allocations += 1;
+  *out = p;
+  return MIMIR_B200_OK;
+}
+
+int mimir_b200_tensor_alloc(const int* shape, int rank, const char* name, float** device_ptr, size_t* bytes_out) {
+  if (!shape || rank <= 0 || !device_ptr) return fail(MIMIR_B200_E_INVALID, "tensor_alloc: bad arguments");
+  size_t numel = 1;
+  for (int i = 0; i < rank; ++i) {
+    if (shape[i] <= 0) return fail(MIMIR_B200_E_INVALID, "tensor_alloc: extent %d of %s is %d", i, name ? name : "?", shape[i]);
+    if (numel > (static_cast<size_t>(1) << 60) / static_cast<size_t>(shape[i]))
+      return fail(MIMIR_B200_E_INVALID, "tensor_alloc: element count of %s overflows", name ? name : "?");
+    numel *= static_cast<size_t>(shape[i]);
+  }
+  void* p = nullptr;
+  MB_TRY(owned_alloc(numel * sizeof(float), name ? name : "", &p));
+  *device_ptr = static_cast<float*>(p);
+  if (bytes_out) *bytes_out = numel * sizeof(float);
+  return MIMIR_B200_OK;
+}
+int mimir_b200_buffer_alloc(size_t bytes, const char* tag, void** device_ptr) { return owned_alloc(bytes, tag ? tag : "", device_ptr); }
+int mimir_b200_buffer_free(void* device_ptr) {
+  if (!device_ptr) return MIMIR_B200_OK;
+  OwnedBuffers& ob = ctx().owned;
+  std::lock_guard<std::mutex> lk(ob.mu);
+  auto it = ob.live.find(device_ptr);
+  if (it == ob.live.end()) return fail(MIMIR_B200_E_INVALID, "buffer_free: %p was not handed out by the allocator (or sits in the pool)", device_ptr);
+  dev_free(device_ptr, it->second.bytes);
+  ob.live.erase(it);
+  return MIMIR_B200_OK;
+}
+int mimir_b200_scratchpad_get(size_t min_bytes, const char* tag, void** device_ptr, size_t* bytes_out) {
+  if (!device_ptr) return fail(MIMIR_B200_E_INVALID, "scratchpad_get: null result pointer");
+  const std::string t = tag ? tag : "scratchpad";
+  OwnedBuffers& ob = ctx().owned;
+  {
+    std::lock_guard<std::mutex> lk(ob.mu);
+    auto it = ob.pool.find(t);
+    if (it != ob.pool.end() && it->second.second >= min_bytes) {
+      *device_ptr = it->second.first;
+      if (bytes_out) *bytes_out = it->second.second;
+      ob.live[it->second.first] = OwnedBuffers::Buf{it->second.second, t};
+      ob.pool.erase(it);
+      return MIMIR_B200_OK;
+    }
+  }
+  MB_TRY(owned_alloc(min_bytes, t.c_str(), device_ptr));
+  if (bytes_out) *bytes_out = min_bytes;
+  return MIMIR_B200_OK;
+}
+int mimir_b200_scratchpad_return(void* device_ptr) {
+  if (!device_ptr) return MIMIR_B200_OK;
+  OwnedBuffers& ob = ctx().owned;
+  std::lock_guard<std::mutex> lk(ob.mu);
+  auto it = ob.live.find(device_ptr);
+  if (it == ob.live.end()) return fail(MIMIR_B200_E_INVALID, "scratchpad_return: %p was not handed out by the allocator", device_ptr);
+  if (ob.pool.count(it->second.tag)) dev_free(device_ptr, it->second.bytes);  // one pooled buffer per tag
+  else ob.pool[it->second.tag] = std::make_pair(device_ptr, it->second.bytes);
+  ob.live.erase(it);
+  return MIMIR_B200_OK;
+}
+int mimir_b200_allocator_set_local_cap(size_t bytes) {
+  std::lock_guard<std::mutex> lk(ctx().owned.mu);
+  ctx().owned.local_cap = bytes;
+  return MIMIR_B200_OK;
+}
+int mimir_b200_allocator_stats(size_t* total_allocated, size_t* num_allocations, size_t* peak, size_t* current) {
+  {
+    std::lock_guard<std::mutex> lk(ctx().owned.mu);
+    if (total_allocated) *total_allocated = ctx().owned.total_allocated;
+    if (num_allocations) *num_allocations = ctx().owned.num_allocations;
+  }
+  return mimir_b200_guard_stats(nullptr, current, peak);
+}
+int mimir_b200_allocator_reset_stats(void) {
+  std::lock_guard<std::mutex> lk(ctx().owned.mu);
+  ctx().owned.total_allocated = 0;
+  ctx().owned.num_allocations = 0;
+  return MIMIR_B200_OK;
+}
+int mimir_b200_allocator_check_no_leaks(int* ok) {
+  if (!ok) return fail(MIMIR_B200_E_INVALID, "check_no_leaks: null result pointer");
+  size_t current = 0;
+  mimir_b200_guard_stats(nullptr, &current, nullptr);
+  *ok = (current / (1024 * 1024)) < 10 ? 1 : 0;
   return MIMIR_B200_OK;
 }
 

@@ -9,8 +9,11 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <mutex>
 #include <string>
+#include <unordered_map>
+#include <utility>
 #include <vector>
 
 #include "mimir_b200.h"
@@ -48,11 +51,21 @@ struct Guard {
   void reset();                                // MemoryGuard::reset (MemoryGuard.hpp:181-186): usage and peak to zero
 };
 
+// Device buffers handed out by the RuntimeAllocator verbs (capi.cu): live ones by address, pooled scratchpads by tag.
+struct OwnedBuffers {
+  struct Buf { size_t bytes; std::string tag; };
+  std::mutex mu;
+  std::unordered_map<void*, Buf> live;
+  std::map<std::string, std::pair<void*, size_t>> pool;
+  size_t total_allocated = 0, num_allocations = 0, local_cap = 0;
+};
+
 struct Context {
   bool initialised = false;
   int device = 0;
   int sm_count = 148;
   Guard guard;
+  OwnedBuffers owned;
   std::atomic<uint64_t> launches{0};
   // One device word that kernels with bounded waits set when a wait gives up.
   int* dev_error_word = nullptr;
@@ -99,6 +112,8 @@ int model_device(MimirB200ModelHandle m);
 // Budgeted device allocation: every cudaMalloc of the backend goes through these.
 int dev_alloc(void** p, size_t bytes, const char* tag);
 void dev_free(void* p, size_t bytes);
+// Frees every buffer of the RuntimeAllocator verbs on the current device (shutdown).
+void release_owned_buffers();
 
 inline void count_launch(int n = 1) { ctx().launches.fetch_add(static_cast<uint64_t>(n), std::memory_order_relaxed); }
 

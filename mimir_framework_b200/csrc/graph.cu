@@ -1969,6 +1969,11 @@ int mimir_b200_shutdown(void) {
     cudaSetDevice(m->device);
     destroy_model(m);
   }
+  for (int d = 0; d < MAX_DEVICES; ++d) {
+    if (!ctx_of(d).initialised) continue;
+    cudaSetDevice(d);
+    release_owned_buffers();
+  }
   if (have_prev) cudaSetDevice(prev); else cudaGetLastError();
   return MIMIR_B200_OK;
 }

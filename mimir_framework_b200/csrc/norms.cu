@@ -769,25 +769,42 @@ __global__ void __launch_bounds__(256) meanvar_cluster_kernel(const float* __res
   for (unsigned k = 0; k < ncl; ++k) var += *cl.map_shared_rank(&part[1], k);
   const float inv = 1.0f / sqrtf(var / static_cast<float>(len) + eps);
   float* o = y + base + off;
-  const bool vec = !a.per_channel && a.act < 0 && (n & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0 &&
-                   (a.gamma == nullptr || (reinterpret_cast<uintptr_t>(a.gamma + off) & 15) == 0) &&
-                   (a.beta == nullptr || (reinterpret_cast<uintptr_t>(a.beta + off) & 15) == 0) &&
-                   (a.residual == nullptr || (reinterpret_cast<uintptr_t>(a.residual + base + off) & 15) == 0);
+  // 16-byte path: four neighbours share a channel when the plane size is a multiple of 4 (slices start on multiples of 4)
+  const bool vec = (n & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0 &&
+                   (a.residual == nullptr || (reinterpret_cast<uintptr_t>(a.residual + base + off) & 15) == 0) &&
+                   (a.per_channel ? (a.hw & 3) == 0
+                                  : ((a.gamma == nullptr || (reinterpret_cast<uintptr_t>(a.gamma + off) & 15) == 0) &&
+                                     (a.beta == nullptr || (reinterpret_cast<uintptr_t>(a.beta + off) & 15) == 0)));
   if (vec) {
     const float4* s4 = reinterpret_cast<const float4*>(sx);
-    const float4* g4 = a.gamma ? reinterpret_cast<const float4*>(a.gamma + off) : nullptr;
-    const float4* b4 = a.beta ? reinterpret_cast<const float4*>(a.beta + off) : nullptr;
+    const float4* g4 = (a.gamma && !a.per_channel) ? reinterpret_cast<const float4*>(a.gamma + off) : nullptr;
+    const float4* b4 = (a.beta && !a.per_channel) ? reinterpret_cast<const float4*>(a.beta + off) : nullptr;
     const float4* r4 = a.residual ? reinterpret_cast<const float4*>(a.residual + base + off) : nullptr;
+    const int ch0 = a.per_channel ? static_cast<int>(row % a.groups) * a.cpg : 0;
+    const unsigned off_u = static_cast<unsigned>(off);
     for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
       const float4 v = s4[i];
       float4 r = make_float4((v.x - mean) * inv, (v.y - mean) * inv, (v.z - mean) * inv, (v.w - mean) * inv);
-      if (g4 != nullptr) {
+      if (a.per_channel) {
+        if (a.gamma != nullptr) {
+          const int gi = ch0 + static_cast<int>((off_u + 4u * static_cast<unsigned>(i)) / static_cast<unsigned>(a.hw));
+          const float w = __ldg(a.gamma + gi);
+          r.x *= w; r.y *= w; r.z *= w; r.w *= w;
+          if (a.beta != nullptr) {
+            const float b = __ldg(a.beta + gi);
+            r.x += b; r.y += b; r.z += b; r.w += b;
+          }
+        }
+      } else if (g4 != nullptr) {
         const float4 w = __ldg(g4 + i);
         r.x *= w.x; r.y *= w.y; r.z *= w.z; r.w *= w.w;
         if (b4 != nullptr) {
           const float4 b = __ldg(b4 + i);
           r.x += b.x; r.y += b.y; r.z += b.z; r.w += b.w;
         }
+      }
+      if (a.act == MIMIR_B200_ELT_SILU) {
+        r.x = silu(r.x); r.y = silu(r.y); r.z = silu(r.z); r.w = silu(r.w);
       }
       if (r4 != nullptr) {
         const float4 t = __ldg(r4 + i);

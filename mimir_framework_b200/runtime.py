@@ -34,6 +34,15 @@ _SIGS = {
     "mimir_b200_guard_freeze": [C.c_int],
     "mimir_b200_guard_reset": [],
     "mimir_b200_guard_state": [_P, _P, _P, _P],
+    "mimir_b200_tensor_alloc": [_P, C.c_int, C.c_char_p, _P, _P],
+    "mimir_b200_buffer_alloc": [C.c_size_t, C.c_char_p, _P],
+    "mimir_b200_buffer_free": [_P],
+    "mimir_b200_scratchpad_get": [C.c_size_t, C.c_char_p, _P, _P],
+    "mimir_b200_scratchpad_return": [_P],
+    "mimir_b200_allocator_set_local_cap": [C.c_size_t],
+    "mimir_b200_allocator_stats": [_P, _P, _P, _P],
+    "mimir_b200_allocator_reset_stats": [],
+    "mimir_b200_allocator_check_no_leaks": [_P],
     "mimir_b200_current_device": [_P],
     "mimir_b200_env_selection": [_P, _P, _P],
     "mimir_b200_init_from_env": [_P],
@@ -143,6 +152,46 @@ def guard_stats():
     a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
     check(lib().mimir_b200_guard_stats(C.byref(a), C.byref(b), C.byref(c)))
     return dict(limit=a.value, current=b.value, peak=c.value)
+
+
+# ---- RuntimeAllocator verbs (device pointers as integers) ------------------------------------------
+def tensor_alloc(shape, name=None):
+    arr = (C.c_int * len(shape))(*shape)
+    ptr, nbytes = C.c_void_p(), C.c_size_t()
+    check(lib().mimir_b200_tensor_alloc(arr, len(shape), name.encode() if name else None, C.byref(ptr), C.byref(nbytes)))
+    return ptr.value, nbytes.value
+
+
+def buffer_alloc(nbytes, tag=None):
+    ptr = C.c_void_p()
+    check(lib().mimir_b200_buffer_alloc(nbytes, tag.encode() if tag else None, C.byref(ptr)))
+    return ptr.value
+
+
+def buffer_free(ptr):
+    check(lib().mimir_b200_buffer_free(C.c_void_p(ptr)))
+
+
+def scratchpad_get(min_bytes, tag=None):
+    ptr, nbytes = C.c_void_p(), C.c_size_t()
+    check(lib().mimir_b200_scratchpad_get(min_bytes, tag.encode() if tag else None, C.byref(ptr), C.byref(nbytes)))
+    return ptr.value, nbytes.value
+
+
+def scratchpad_return(ptr):
+    check(lib().mimir_b200_scratchpad_return(C.c_void_p(ptr)))
+
+
+def allocator_stats():
+    a, b, c, d = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+    check(lib().mimir_b200_allocator_stats(C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+    return dict(total_allocated=a.value, num_allocations=b.value, peak=c.value, current=d.value)
+
+
+def allocator_check_no_leaks():
+    ok = C.c_int()
+    check(lib().mimir_b200_allocator_check_no_leaks(C.byref(ok)))
+    return bool(ok.value)
 
 
 def stats() -> dict:

@@ -178,7 +178,8 @@ def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
         np.testing.assert_allclose(got, [2, 4, 6, 8], atol=1e-6)
 
 
-@pytest.mark.parametrize("rows,n", [(4, 300), (3, 768), (2, 32768), (1, 40000), (9, 5), (3, 98304), (5, 98301), (2, 200000), (150, 5000)])
+@pytest.mark.parametrize("rows,n", [(4, 300), (3, 768), (2, 32768), (1, 40000), (9, 5), (3, 98304), (5, 98301), (2, 200000), (150, 5000),
+                                    (150, 40000), (149, 40002)])  # a row shared by the CTAs of a cluster; ragged slices
 def test_layernorm(backend, rows, n):
     r = rng(n)
     x = (r.standard_normal(rows * n) * 2 + 0.5).astype(np.float32)
@@ -220,6 +221,7 @@ def test_rmsnorm_reference_known_answer(backend):
 
 @pytest.mark.parametrize("batch,ch,h,w,groups,act", [
     (1, 4, 2, 2, 2, -1), (2, 16, 9, 9, 4, -1), (2, 64, 28, 28, 32, abi.ELT_SILU), (1, 256, 56, 56, 32, abi.ELT_SILU),
+    (5, 64, 160, 120, 32, abi.ELT_SILU), (10, 32, 180, 110, 16, -1),  # >= one row per SM, rows of 150 KB: the cluster sweep
 ])
 def test_groupnorm(backend, batch, ch, h, w, groups, act):
     r = rng(ch + h)
@@ -230,6 +232,16 @@ def test_groupnorm(backend, batch, ch, h, w, groups, act):
     if act >= 0:
         want = port.eltwise(act, want)
     assert_close(backend.groupnorm(x, g, b, batch, ch, h, w, groups, 1e-5, act), want, f"groupnorm C{ch} {h}x{w}")
+
+
+def test_layernorm_long_rows_far_from_zero(backend):
+    """Rows whose first element (the shift of the one-sweep statistics) lies five standard deviations from the mean: the
+    shifted sums give way to a second, centred sweep (LayerOps.hpp:287-300 takes the variance around the mean), and every
+    CTA that shares a row must take that decision alike."""
+    rows, n = 150, 40000
+    x = (rng(3).standard_normal(rows * n) + 5.0).astype(np.float32)
+    x[::n] = 0.0
+    assert_close(backend.layernorm(x, None, None, rows, n), port.layernorm(x, None, None, rows, n, 1e-5), "layernorm, poor shift")
 
 
 @pytest.mark.parametrize("batch,n,log", [(3, 7, False), (2, 1200, True), (2, 32000, False), (1, 70000, False), (1, 70000, True)])
