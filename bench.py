@@ -745,10 +745,9 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         model.forward_device(spec_dev, 1, y_dev.data_ptr(), M * K, stream)
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.25)
+    sampler = ClockSampler(local_rank)  # every rank watches its own GPU: the step time is the slowest rank's
+    sampler.start()
+    time.sleep(0.25)
     launches0 = rt.stats()["kernels_launched"]
     rt.profile_gemm(True)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -764,8 +763,15 @@ def run_ours(args):
     gemm_ms, gemm_launches = rt.profile_read()
     rt.check(rt.lib().mimir_b200_check_device(None))
     launches = rt.stats()["kernels_launched"] - launches0
-    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
-    ms_total = h.max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop(t_wall0, t_wall1)
+    ms_local = e0.elapsed_time(e1)
+    ms_total = h.max_over_ranks(ms_local)
+    per_rank = None
+    if world > 1:
+        mine = {"rank": rank, "ms_per_step": ms_local / args.steps, "sm_mhz": (clocks or {}).get("sm_mhz"),
+                "power_w_max": (clocks or {}).get("power_w_max"), "reasons": (clocks or {}).get("reasons")}
+        per_rank = [None] * world
+        h.dist.all_gather_object(per_rank, mine, group=h.host_group)
     ms_per_step = ms_total / args.steps
     value = world * M / (ms_per_step * 1e-3)
 
@@ -836,6 +842,7 @@ def run_ours(args):
             "roofline": roofline,
             "cpu_baseline": cpu,
             "clocks": clocks,
+            **({"per_rank": per_rank} if per_rank else {}),
         }
         line.update(extras)
         print(json.dumps(line))
