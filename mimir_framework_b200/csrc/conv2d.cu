@@ -431,19 +431,31 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) 
                : "memory");
 }
 
-template <int KS, int R>
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
+  // 16 bytes, or 16 zero bytes when !valid (source size 0: nothing is read)
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gmem_src), "r"(valid ? 16 : 0)
+               : "memory");
+}
+
+// VEC = 0: tile rows of TW = 128 + KS - 1 pixels copied element by element, a pad word after every SO_PX pixels (the lanes of a
+//          warp then read their segments SO_PX + 1 words apart: no bank conflicts).  Any image width and alignment.
+// VEC = 1: image rows that are whole 16-byte chunks (width a multiple of 4, aligned base): a tile row is the 136 pixels from
+//          x0 - 4, copied as 34 aligned 16-byte chunks (zero-filled outside the image); a lane reads its four pixels with one
+//          128-bit load and takes the halo from its neighbours' registers.
+template <int KS, int R, int VEC>
 struct SmallOcGeom {
   static constexpr int PAD = KS / 2, TW = SO_TX * SO_PX + KS - 1, TH = SO_TY * R + KS - 1, SEG = SO_PX + KS - 1;
-  // a pad word after every SO_PX pixels: the lanes of a warp then read their segments SO_PX + 1 words apart (no bank conflicts)
-  static constexpr int TWP = TW + TW / SO_PX + 1;
+  static constexpr int TWV = SO_TX * SO_PX + 8, CHUNKS = TWV / 4;
+  static constexpr int TWP = VEC ? TWV : TW + TW / SO_PX + 1;  // row stride in shared memory
   static constexpr int TILE = SO_CC * TH * TWP, WOFF = (SO_NBUF * TILE + 3) & ~3;
 };
 
-template <int OC, int KS, int R>
+template <int OC, int KS, int R, int VEC>
 __global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                                        float* __restrict__ y, const float* __restrict__ residual, int ic,
                                                                        int h, int wd, int act) {
-  using G = SmallOcGeom<KS, R>;
+  using G = SmallOcGeom<KS, R, VEC>;
   constexpr int PAD = G::PAD, TW = G::TW, TH = G::TH, TWP = G::TWP, TILE = G::TILE, SEG = G::SEG, KK = KS * KS;
   constexpr int WROW = (KS * OC + 3) & ~3;  // the weights of one (channel, kernel row) as [kw][o], padded to whole float4s
   constexpr int WCH = SO_CC * KS * WROW;
@@ -473,6 +485,14 @@ __global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const floa
   auto fetch = [&](int c0, int buf) {
     const int cc = min(SO_CC, ic - c0);
     float* tile = so_smem + buf * TILE;
+    if (VEC) {
+      for (int idx = threadIdx.x; idx < SO_CC * TH * G::CHUNKS; idx += SO_TX * SO_TY) {
+        const int row = idx / G::CHUNKS, ch = idx - row * G::CHUNKS;
+        const int c = row / TH, yy = row - c * TH, gy = y0 + yy - PAD, gx = x0 - 4 + 4 * ch;
+        const bool ok = c < cc && gy >= 0 && gy < h && gx >= 0 && gx < wd;  // a chunk is wholly inside or wholly outside
+        cp_async16_zfill(tile + row * TWP + 4 * ch, ok ? xs + (static_cast<long long>(c0 + c) * h + gy) * wd + gx : xs, ok);
+      }
+    } else
     for (int row = ty; row < SO_CC * TH; row += SO_TY) {  // one warp per tile row
       const int c = row / TH, yy = row - c * TH, gy = y0 + yy - PAD;
       const bool row_ok = c < cc && gy >= 0 && gy < h;
@@ -512,9 +532,26 @@ __global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const floa
 #pragma unroll
       for (int r = 0; r < R + KS - 1; ++r) {  // input rows ascending = kernel rows ascending for every output row
         float seg[SEG];
-        const float* row = tile + (c * TH + ty * R + r) * TWP + tx * (SO_PX + 1);
+        if (VEC) {
+          // pixels x0 + 4 tx .. + 3 sit at tile columns 4 tx + 4 .. 4 tx + 7; the PAD values either side come from the neighbour
+          // lanes' vectors (from shared memory at the two ends of the warp)
+          const float* rowp = tile + (c * TH + ty * R + r) * TWP + 4 * tx;
+          const float4 m = *reinterpret_cast<const float4*>(rowp + 4);
+          const float mv[4] = {m.x, m.y, m.z, m.w};
 #pragma unroll
-        for (int i = 0; i < SEG; ++i) seg[i] = row[i + i / SO_PX];
+          for (int i = 0; i < SO_PX; ++i) seg[PAD + i] = mv[i];
+#pragma unroll
+          for (int i = 0; i < PAD; ++i) {
+            const float lft = __shfl_up_sync(0xffffffffu, mv[SO_PX - PAD + i], 1);
+            const float rgt = __shfl_down_sync(0xffffffffu, mv[i], 1);
+            seg[i] = tx == 0 ? rowp[4 - PAD + i] : lft;
+            seg[PAD + SO_PX + i] = tx == SO_TX - 1 ? rowp[8 + i] : rgt;
+          }
+        } else {
+          const float* row = tile + (c * TH + ty * R + r) * TWP + tx * (SO_PX + 1);
+#pragma unroll
+          for (int i = 0; i < SEG; ++i) seg[i] = row[i + i / SO_PX];
+        }
 #pragma unroll
         for (int j = 0; j < R; ++j) {
           const int kh = r - j;
@@ -558,22 +595,32 @@ __global__ void __launch_bounds__(SO_TX * SO_TY) conv_small_oc_kernel(const floa
   }
 }
 
-template <int OC, int KS>
-int launch_small_oc_k(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int h, int wd, int act,
+template <int OC, int KS, int VEC>
+int launch_small_oc_v(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int h, int wd, int act,
                       cudaStream_t st) {
   constexpr int R = so_rows(OC);
-  using G = SmallOcGeom<KS, R>;
+  using G = SmallOcGeom<KS, R, VEC>;
   constexpr int SMEM = (G::WOFF + SO_NBUF * SO_CC * KS * ((KS * OC + 3) & ~3)) * static_cast<int>(sizeof(float));
   static PerDeviceOnce attr_once;
   MB_TRY(attr_once.run([&]() -> int {
-    MB_CUDA(cudaFuncSetAttribute(conv_small_oc_kernel<OC, KS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(conv_small_oc_kernel<OC, KS, R, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     return MIMIR_B200_OK;
   }));
   dim3 grid((wd + SO_TX * SO_PX - 1) / (SO_TX * SO_PX), (h + SO_TY * R - 1) / (SO_TY * R), batch);
-  conv_small_oc_kernel<OC, KS, R><<<grid, SO_TX * SO_TY, SMEM, st>>>(x, w, y, residual, ic, h, wd, act);
+  conv_small_oc_kernel<OC, KS, R, VEC><<<grid, SO_TX * SO_TY, SMEM, st>>>(x, w, y, residual, ic, h, wd, act);
   MB_CUDA(cudaGetLastError());
   count_launch();
   return MIMIR_B200_OK;
+}
+
+template <int OC, int KS>
+int launch_small_oc_k(const float* x, const float* w, float* y, const float* residual, int batch, int ic, int h, int wd, int act,
+                      cudaStream_t st) {
+  // whole 16-byte chunks per image row and an aligned base: the vector form (MIMIR_B200_CONV_SMALL_OC_VEC=0 turns it off)
+  static const bool vec_off = [] { const char* e = getenv("MIMIR_B200_CONV_SMALL_OC_VEC"); return e && e[0] == '0'; }();
+  if (!vec_off && (wd & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
+    return launch_small_oc_v<OC, KS, 1>(x, w, y, residual, batch, ic, h, wd, act, st);
+  return launch_small_oc_v<OC, KS, 0>(x, w, y, residual, batch, ic, h, wd, act, st);
 }
 
 template <int OC>

@@ -162,6 +162,9 @@ def test_attention_identity_weights(backend):
     (2, 40, 3, 70, 66, 3, 1, 1, 0),   # an RGB head on a large image: direct fp32 kernel, ragged tiles, channel tail (40 = 5 x 8)
     (1, 19, 8, 64, 64, 5, 1, 2, 1),   # direct kernel: eight output channels, 5x5, channel count not a multiple of 8, ReLU
     (2, 12, 1, 96, 50, 1, 1, 0, 0),   # direct kernel: one output channel, 1x1
+    (2, 40, 3, 72, 68, 3, 1, 1, 0),   # direct kernel, rows of whole 16-byte chunks: the vector form, one ragged tile
+    (1, 16, 3, 66, 260, 3, 1, 1, 1),  # vector form: three tiles across (128 + 128 + 4), halo values cross tile and lane borders
+    (1, 6, 2, 65, 132, 7, 1, 3, 0),   # vector form, 7x7: three halo values either side
 ])
 def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
     r = rng(ic * oc + h)
