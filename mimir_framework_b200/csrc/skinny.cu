@@ -159,8 +159,25 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// Which CTA of a grid of `grid` owns item `i` when `items` items are dealt out as contiguous, balanced ranges (the first
+// items % grid CTAs take one more), and the range of CTA `b`.  Used by the streaming kernel and by the finishing kernel alike.
+struct ItemSplit {
+  int base, rem;  // items / grid, items % grid
+  __host__ __device__ ItemSplit(int items, int grid) : base(items / grid), rem(items % grid) {}
+  __host__ __device__ int first(int b) const { return b * base + (b < rem ? b : rem); }
+  __host__ __device__ int count(int b) const { return base + (b < rem ? 1 : 0); }
+  __host__ __device__ int owner(int i) const {
+    const int big = rem * (base + 1);
+    return i < big ? i / (base + 1) : rem + (i - big) / base;
+  }
+};
+
 // Persistent form for 16-byte aligned operands with k % 4 == 0.  Shared memory: x double buffer
 // [2][MT][SK_SLICE], then the rings [warp][SK_STAGES][WR][SK_STEP].
+// A CTA owns a CONTIGUOUS range of items (item = tile * kslices + ks): consecutive items are consecutive K slices of the same
+// output tile, so their partial sums stay in the accumulators and the exchange between lanes and the write of the partials
+// happen once per (CTA, tile) instead of once per item.  Partial p of a tile is the one of the p-th CTA that touched it, in K
+// order: part[(p * m + r) * n + o].
 template <int MT, int WR>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 skinny_stream_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ part, int m, int k, int n,
@@ -172,57 +189,67 @@ skinny_stream_kernel(const float* __restrict__ x, const float* __restrict__ w, f
   float* xs = sk_smem;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float* ring = sk_smem + 2 * MT * SK_SLICE + warp * (SK_STAGES * WR * SK_STEP);
-  const int my_items = (items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const ItemSplit split(items, static_cast<int>(gridDim.x));
+  const int my_first = split.first(static_cast<int>(blockIdx.x)), my_items = split.count(static_cast<int>(blockIdx.x));
   const int total_steps = my_items * SK_STEPS;
+  const long long kk = k;
 
-  // copy group of global step g (= this CTA's item g / SK_STEPS, step g % SK_STEPS): this warp's WR rows, and with
-  // the first step of an item every thread's share of that item's x slice
-  auto issue = [&](int g) {
-    if (g < total_steps) {
-      const int j = g / SK_STEPS, st = g - j * SK_STEPS;
-      const int item = blockIdx.x + j * gridDim.x;
-      const int tile = item / kslices, ks = item - tile * kslices;
-      const int c = ks * SK_SLICE + st * SK_STEP + lane * 4;
-      const long long o0 = (static_cast<long long>(tile) * SK_WARPS + warp) * WR;
-      float* dst = ring + (g % SK_STAGES) * (WR * SK_STEP) + lane * 4;
+  // Copy group of this CTA's step g (item g / SK_STEPS, step g % SK_STEPS): this warp's WR rows of W, and with the first step
+  // of an item every thread's share of that item's x slice.  The groups are issued in order, so (tile, ks, step) of the next
+  // group and the address of its first row advance incrementally.
+  int ig = 0, i_st = 0, i_j = 0;
+  int i_tile = my_first / kslices, i_ks = my_first - i_tile * kslices;
+  auto issue = [&]() {
+    if (ig < total_steps) {
+      const int c = i_ks * SK_SLICE + i_st * SK_STEP + lane * 4;
+      const int o0 = (i_tile * SK_WARPS + warp) * WR;
+      const float* src = w + static_cast<long long>(o0) * kk + c;
+      float* dst = ring + (ig % SK_STAGES) * (WR * SK_STEP) + lane * 4;
+      const bool col_ok = c < k;
 #pragma unroll
       for (int jj = 0; jj < WR; ++jj) {
-        const bool ok = (o0 + jj < n) && (c < k);
-        cp_async16_zfill(dst + jj * SK_STEP, ok ? (w + (o0 + jj) * k + c) : w, ok);
+        const bool ok = col_ok && (o0 + jj < n);
+        cp_async16_zfill(dst + jj * SK_STEP, ok ? src : w, ok);
+        src += kk;
       }
-      if (st == 0) {
-        float* xd = xs + (j & 1) * (MT * SK_SLICE);
+      if (i_st == 0) {
+        float* xd = xs + (i_j & 1) * (MT * SK_SLICE);
         for (int i = threadIdx.x; i < MT * (SK_SLICE / 4); i += SK_THREADS) {
           const int r = i / (SK_SLICE / 4), cc = (i - r * (SK_SLICE / 4)) << 2;
-          const int kc = ks * SK_SLICE + cc;
+          const int kc = i_ks * SK_SLICE + cc;
           const bool ok = (r < m) && (kc < k);
-          cp_async16_zfill(xd + r * SK_SLICE + cc, ok ? (x + static_cast<long long>(r) * k + kc) : x, ok);
+          cp_async16_zfill(xd + r * SK_SLICE + cc, ok ? (x + r * kk + kc) : x, ok);
         }
       }
+      if (++i_st == SK_STEPS) {
+        i_st = 0;
+        ++i_j;
+        if (++i_ks == kslices) { i_ks = 0; ++i_tile; }
+      }
     }
+    ++ig;
     cp_async_commit();  // one group per step, empty past the end, so that the wait count stays fixed
   };
 #pragma unroll
-  for (int i = 0; i < SK_STAGES - 1; ++i) issue(i);
+  for (int i = 0; i < SK_STAGES - 1; ++i) issue();
 
   float acc[N];
 #pragma unroll
   for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+  int tile = my_first / kslices, ks = my_first - tile * kslices;
   for (int j = 0; j < my_items; ++j) {
-    const int item = blockIdx.x + j * gridDim.x;
-    const int tile = item / kslices, ks = item - tile * kslices;
     const float* xj = xs + (j & 1) * (MT * SK_SLICE);
 #pragma unroll
     for (int st = 0; st < SK_STEPS; ++st) {
       const int g = j * SK_STEPS + st;
-      if (st == 1) issue(g + SK_STAGES - 1);  // (after the item's barrier: it may overwrite the x buffer of item j - 1)
-      else if (st != 0) issue(g + SK_STAGES - 1);
       if (st == 0) {
         // the group of step g carries this item's x slice: wait for it, then let every thread's share become visible
+        // (the next group may overwrite the x buffer of item j - 1: issued after the barrier)
         cp_async_wait<SK_STAGES - 2>();
         __syncthreads();
-        issue(g + SK_STAGES - 1);
+        issue();
       } else {
+        issue();
         cp_async_wait<SK_STAGES - 1>();
       }
       const float* src = ring + (g % SK_STAGES) * (WR * SK_STEP) + lane * 4;
@@ -231,46 +258,60 @@ skinny_stream_kernel(const float* __restrict__ x, const float* __restrict__ w, f
       for (int jj = 0; jj < WR; ++jj) wv[jj] = *reinterpret_cast<const float4*>(src + jj * SK_STEP);
       sk_fma_step<MT, WR>(acc, wv, xj, st * SK_STEP + lane * 4);
     }
+    const bool tile_ends = (ks + 1 == kslices) || (j + 1 == my_items);
+    if (tile_ends) {
 #pragma unroll
-    for (int half = N / 2, mask = 16; mask >= 1; half >>= 1, mask >>= 1) {
-      const bool upper = (lane & mask) != 0;
+      for (int half = N / 2, mask = 16; mask >= 1; half >>= 1, mask >>= 1) {
+        const bool upper = (lane & mask) != 0;
 #pragma unroll
-      for (int i = 0; i < half; ++i) {
-        const float send = upper ? acc[i] : acc[i + half];
-        const float keep = upper ? acc[i + half] : acc[i];
-        acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+        for (int i = 0; i < half; ++i) {
+          const float send = upper ? acc[i] : acc[i + half];
+          const float keep = upper ? acc[i + half] : acc[i];
+          acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+        }
       }
-    }
-    const long long o0 = (static_cast<long long>(tile) * SK_WARPS + warp) * WR;
+      // this CTA's place among the CTAs that touch the tile (they hold consecutive K ranges of it)
+      const int p = static_cast<int>(blockIdx.x) - split.owner(tile * kslices);
+      const int o0 = (tile * SK_WARPS + warp) * WR;
 #pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      const int idx = lane * PER + t, jj = idx / MT, r = idx - jj * MT;
-      if (r < m && o0 + jj < n) part[(static_cast<long long>(ks) * m + r) * n + o0 + jj] = acc[t];
-    }
+      for (int t = 0; t < PER; ++t) {
+        const int idx = lane * PER + t, jj = idx / MT, r = idx - jj * MT;
+        if (r < m && o0 + jj < n) part[(static_cast<long long>(p) * m + r) * n + o0 + jj] = acc[t];
+      }
 #pragma unroll
-    for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+      for (int i = 0; i < N; ++i) acc[i] = 0.0f;
+    }
+    if (++ks == kslices) { ks = 0; ++tile; }
   }
   cp_async_wait<0>();
 }
 
+// y = sum of a tile's partials in K order (+ bias, activation, folded residual).  grid > 0: the partials come from the
+// streaming kernel launched with that many CTAs (one partial per CTA that touched the tile); grid == 0: one partial per K slice.
 __global__ void skinny_finish_kernel(const float* __restrict__ part, const float* __restrict__ bias, const float* __restrict__ residual,
-                                     float* __restrict__ y, int m, int n, int kslices, int act) {
+                                     float* __restrict__ y, int m, int n, int kslices, int act, int grid, int items, int tile_cols) {
   const long long total = static_cast<long long>(m) * n;
+  const ItemSplit split(grid > 0 ? items : 1, grid > 0 ? grid : 1);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const int o = static_cast<int>(i % n);
-    // slices are added in slice order; eight loads are issued before the first add so that a long K (64 slices for
-    // in_features = 32768) does not pay the memory latency once per slice
+    int np = kslices;
+    if (grid > 0) {
+      const int tile = o / tile_cols;
+      np = split.owner((tile + 1) * kslices - 1) - split.owner(tile * kslices) + 1;
+    }
+    // the partials are added in K order; eight loads are issued before the first add so that a long chain does not pay
+    // the memory latency once per partial
     float s = 0.0f;
     int ks = 0;
-    for (; ks + 8 <= kslices; ks += 8) {
+    for (; ks + 8 <= np; ks += 8) {
       float v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u) v[u] = __ldcs(part + static_cast<long long>(ks + u) * total + i);
 #pragma unroll
       for (int u = 0; u < 8; ++u) s += v[u];
     }
-    for (; ks < kslices; ++ks) s += __ldcs(part + static_cast<long long>(ks) * total + i);
+    for (; ks < np; ++ks) s += __ldcs(part + static_cast<long long>(ks) * total + i);
     if (bias != nullptr) s += __ldg(bias + o);
     s = sk_act(s, act);
     if (residual != nullptr) s += __ldg(residual + i);  // a residual Add folded into this layer
@@ -279,10 +320,14 @@ __global__ void skinny_finish_kernel(const float* __restrict__ part, const float
 }
 
 template <int MT, int WR>
-int launch_partial(const float* x, const float* w, float* scratch, int m, int k, int n, cudaStream_t st) {
+int launch_partial(const float* x, const float* w, float* scratch, int m, int k, int n, cudaStream_t st, int* stream_grid, int* stream_items,
+                   int* tile_cols) {
   const int tiles = (n + SK_WARPS * WR - 1) / (SK_WARPS * WR), kslices = (k + SK_SLICE - 1) / SK_SLICE;
   const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 && (k & 3) == 0;
   const char* plain = getenv("MIMIR_B200_SKINNY_PLAIN");
+  *stream_grid = 0;
+  *stream_items = 0;
+  *tile_cols = SK_WARPS * WR;
   if (vec && !(plain && plain[0] == '1') && static_cast<long long>(tiles) * kslices < (1LL << 30)) {
     constexpr int SMEM = (2 * MT * SK_SLICE + SK_WARPS * SK_STAGES * WR * SK_STEP) * 4;
     static PerDeviceOnce attr_once;
@@ -293,6 +338,8 @@ int launch_partial(const float* x, const float* w, float* scratch, int m, int k,
     const int items = tiles * kslices;
     const int grid = items < ctx().sm_count ? items : ctx().sm_count;
     skinny_stream_kernel<MT, WR><<<grid, SK_THREADS, SMEM, st>>>(x, w, scratch, m, k, n, kslices, items);
+    *stream_grid = grid;
+    *stream_items = items;
   } else {
     constexpr int SMEM = MT * SK_SLICE * 4;
     dim3 grid(tiles, kslices);
@@ -315,13 +362,15 @@ int launch_skinny_linear(const float* x, const float* w, const float* bias, floa
   if (scratch == nullptr || scratch_bytes < skinny_scratch_bytes(m, k, n))
     return fail(MIMIR_B200_E_INVALID, "skinny linear: scratch too small");
   if ((k + SK_SLICE - 1) / SK_SLICE > 65535) return fail(MIMIR_B200_E_UNSUPPORTED, "skinny linear: in_features %d too large", k);
-  if (m <= 4) MB_TRY((launch_partial<4, 8>(x, w, scratch, m, k, n, st)));
-  else if (m <= 8) MB_TRY((launch_partial<8, 8>(x, w, scratch, m, k, n, st)));
-  else MB_TRY((launch_partial<16, 4>(x, w, scratch, m, k, n, st)));
+  int sgrid = 0, sitems = 0, tile_cols = 0;
+  if (m <= 4) MB_TRY((launch_partial<4, 8>(x, w, scratch, m, k, n, st, &sgrid, &sitems, &tile_cols)));
+  else if (m <= 8) MB_TRY((launch_partial<8, 8>(x, w, scratch, m, k, n, st, &sgrid, &sitems, &tile_cols)));
+  else MB_TRY((launch_partial<16, 4>(x, w, scratch, m, k, n, st, &sgrid, &sitems, &tile_cols)));
   const long long total = static_cast<long long>(m) * n;
   int fb = static_cast<int>((total + 255) / 256);
   if (fb > ctx().sm_count * 8) fb = ctx().sm_count * 8;
-  skinny_finish_kernel<<<fb, 256, 0, st>>>(scratch, bias, residual, y, m, n, (k + SK_SLICE - 1) / SK_SLICE, activation);
+  skinny_finish_kernel<<<fb, 256, 0, st>>>(scratch, bias, residual, y, m, n, (k + SK_SLICE - 1) / SK_SLICE, activation, sgrid, sitems,
+                                           tile_cols);
   MB_CUDA(cudaGetLastError());
   count_launch(2);
   return MIMIR_B200_OK;
