@@ -865,8 +865,8 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
       if (ut.alias_of >= 0 || ut.producer < 0 || uv == out_root || uv == ov || total_consumers(uv) != 1) continue;
       LayerRT& P = m->layers[ut.producer];
       if (P.out_v != uv || P.res_v >= 0 || P.skip) continue;
-      const bool gemm_like = (P.lt == LT::Linear && !linear_uses_skinny(P.rows_ps * batch, m->precision)) ||
-                             P.lt == LT::Attention || P.lt == LT::CrossAttention || P.lt == LT::Conv2d;
+      // (a Linear on the weight-streaming path adds the residual in its finishing kernel)
+      const bool gemm_like = P.lt == LT::Linear || P.lt == LT::Attention || P.lt == LT::CrossAttention || P.lt == LT::Conv2d;
       if (!gemm_like && P.lt != LT::GroupNorm) continue;
       // the other operand must already exist when P runs
       const int orr = root_of(m->tensors, ov);
