@@ -154,6 +154,13 @@ namespace {
 // 128 contiguous bytes per pixel and plane as packed bf16x2.
 constexpr int TP_C = 64, TP_X = 64;
 
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
+  // 16 bytes, or 16 zero bytes when !valid (source size 0: nothing is read)
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gmem_src), "r"(valid ? 16 : 0)
+               : "memory");
+}
+
 __global__ void __launch_bounds__(256, 3) nchw_to_padded_nhwc_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
                                                                   int c, int h, int w, int pad, int planes, long long plane_stride,
                                                                   const PreNorm pre, int f16, int up) {
@@ -350,6 +357,116 @@ __global__ void __launch_bounds__(256) nchw_to_padded_nhwc_vec_kernel(const floa
   }
 }
 
+// The streaming form of the same pass: a CTA owns LR_ROWS output rows of one sample and 64 channels and walks their tiles
+// (64 channels x 64 pixels) as one sequence; the source of tile t + 1 is on its way into the second shared-memory buffer
+// (16-byte cp.async, zero-filled past the image or the channel count) while tile t is normalised, split and stored, so the
+// loads of a CTA never stop for its stores (the kernel above alternates the two and sat at 30 % issue utilisation with
+// 15 stall cycles per issue on memory).  The tile is stored with its 16-byte column groups XOR-ed with the channel's octet:
+// the eight lanes that write one pixel's 64 channels then read eight different bank groups.  UP = 1 gathers the 2 x 2 nearest
+// upsample: a tile's source is 32 pixels of the half-size row, each read twice.
+constexpr int LR_ROWS = 4, LR_TS = TP_X + 4;
+template <int UP>
+__global__ void __launch_bounds__(256, 5) nchw_to_padded_nhwc_stream_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ dst,
+                                                                           int c, int h, int w, int pad, int planes,
+                                                                           long long plane_stride, const PreNorm pre, int f16) {
+  __shared__ __align__(16) float tile[2][TP_C][LR_TS];
+  const int hp = h + 2 * pad, wp = w + 2 * pad;
+  const int cb = blockIdx.x * TP_C, n = blockIdx.z;
+  const int yp0 = blockIdx.y * LR_ROWS, yp1 = min(hp, yp0 + LR_ROWS);
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  auto store8 = [&](long long pixel, int ch, const uint4& hi, const uint4& lo) {
+    __nv_bfloat16* o = dst + pixel * c + ch;
+    *reinterpret_cast<uint4*>(o) = hi;
+    if (planes == 2) *reinterpret_cast<uint4*>(o + plane_stride) = lo;
+  };
+  // the padding ring of these rows: whole border rows, and the left and right padding pixels of the interior ones
+  for (int yp = yp0; yp < yp1; ++yp) {
+    const long long row_o = (static_cast<long long>(n) * hp + yp) * wp;
+    const bool border = yp < pad || yp >= h + pad;
+    const int npix = border ? wp : 2 * pad;
+    for (int r = threadIdx.x; r < npix * (TP_C / 8); r += 256) {
+      const int q = r >> 3, ch = cb + 8 * (r & 7);
+      const int xp = border ? q : (q < pad ? q : w + q);
+      if (ch < c) store8(row_o + xp, ch, zero4, zero4);
+    }
+  }
+  const int y_lo = max(yp0, pad), y_hi = min(yp1, h + pad);  // interior rows (padded numbering)
+  if (y_lo >= y_hi) return;
+  const int tiles_x = (w + TP_X - 1) / TP_X, ntiles = (y_hi - y_lo) * tiles_x;
+  const int sh_ = UP ? h >> 1 : h, sw_ = UP ? w >> 1 : w;
+  const float* src_n = x + (static_cast<long long>(n) * c + cb) * sh_ * sw_;
+  const long long ch_stride = static_cast<long long>(sh_) * sw_;
+  // this thread's eight channels on the way out, and their GroupNorm scale / shift
+  const int ch8 = 8 * (threadIdx.x & 7), oct = threadIdx.x & 7;
+  float sc[8], sf[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { sc[k] = 1.0f; sf[k] = 0.0f; }
+  if (pre.stats != nullptr) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int ch = cb + ch8 + k;
+      if (ch < c) {
+        const float* st = pre.stats + (static_cast<long long>(n) * pre.groups + ch / (c / pre.groups)) * 2;
+        const float mean = __ldg(st), inv = __ldg(st + 1);
+        const float g = pre.gamma != nullptr ? __ldg(pre.gamma + ch) : 1.0f;
+        const float b = (pre.gamma != nullptr && pre.beta != nullptr) ? __ldg(pre.beta + ch) : 0.0f;
+        sc[k] = inv * g;
+        sf[k] = b - mean * inv * g;
+      }
+    }
+  }
+  constexpr int SRC_CHUNKS = UP ? TP_X / 8 : TP_X / 4;  // 16-byte chunks of one channel's tile source
+  auto issue = [&](int t) {
+    const int ty = t / tiles_x, x0 = (t - ty * tiles_x) * TP_X;
+    const int y = y_lo + ty - pad;
+    const float* srow = src_n + static_cast<long long>(UP ? y >> 1 : y) * sw_ + (UP ? x0 >> 1 : x0);
+    float(*buf)[LR_TS] = tile[t & 1];
+#pragma unroll
+    for (int i = 0; i < TP_C * SRC_CHUNKS / 256; ++i) {
+      const int idx = threadIdx.x + 256 * i;
+      const int cc = idx / SRC_CHUNKS, q = idx - cc * SRC_CHUNKS;
+      const int xs = (UP ? x0 >> 1 : x0) + 4 * q;
+      const bool ok = xs < sw_ && cb + cc < c;
+      cp_async16_zfill(&buf[cc][4 * (q ^ ((cc >> 3) & 7))], ok ? srow + cc * ch_stride + 4 * q : x, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  issue(0);
+  for (int t = 0; t < ntiles; ++t) {
+    if (t + 1 < ntiles) issue(t + 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();
+    const int ty = t / tiles_x, x0 = (t - ty * tiles_x) * TP_X;
+    const long long row_o = (static_cast<long long>(n) * hp + y_lo + ty) * wp + pad + x0;
+    const float(*buf)[LR_TS] = tile[t & 1];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int xx = (threadIdx.x + 256 * i) >> 3;
+      if (x0 + xx < w && cb + ch8 < c) {
+        const int sx = UP ? xx >> 1 : xx;
+        const int col = 4 * ((sx >> 2) ^ oct) + (sx & 3);  // (ch8 + k) >> 3 = oct for every k
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = buf[ch8 + k][col];
+        if (pre.stats != nullptr) {  // GroupNorm (+ SiLU) of the producer applied here
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            float r = fmaf(v[k], sc[k], sf[k]);
+            if (pre.act == MIMIR_B200_ELT_SILU) r = r * __fdividef(1.0f, 1.0f + __expf(-r));
+            v[k] = r;
+          }
+        }
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) split_pair(v[2 * j], v[2 * j + 1], f16, hi[j], lo[j]);
+        store8(row_o + xx, cb + ch8, make_uint4(hi[0], hi[1], hi[2], hi[3]), make_uint4(lo[0], lo[1], lo[2], lo[3]));
+      }
+    }
+    __syncthreads();  // the buffer is refilled by the copy issued at the top of the next iteration
+  }
+}
+
 // dst[pl][o][(kh*ks + kw)*ic + i] = split(w[o][i][kh][kw]); the padded tail of K is zero
 __global__ void conv_weight_planes_kernel(const float* __restrict__ w, __nv_bfloat16* __restrict__ dst, int oc, int ic, int ks,
                                           int kp, int planes, int f16, float scale) {
@@ -385,7 +502,15 @@ int launch_nchw_to_padded_nhwc_split(const float* x, __nv_bfloat16* dst, int bat
   const long long plane_stride = static_cast<long long>(batch) * hp * wp * c;
   const bool vec = !no_vec && (w & 3) == 0 && (c & 7) == 0 && (plane_stride & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
-  if (vec)
+  // rows streamed through a double buffer (MIMIR_B200_LAYOUT_STREAM=0 turns it off); the upsampling form needs the half-size
+  // rows to be whole 16-byte chunks too
+  static const bool no_stream = [] { const char* e = getenv("MIMIR_B200_LAYOUT_STREAM"); return e && e[0] == '0'; }();
+  if (vec && !no_stream && (!up || ((w >> 1) & 3) == 0) && (hp + LR_ROWS - 1) / LR_ROWS <= 65535) {
+    dim3 sgrid((c + TP_C - 1) / TP_C, (hp + LR_ROWS - 1) / LR_ROWS, batch);
+    const int f16 = plane_format() == PLANES_F16;
+    if (up) nchw_to_padded_nhwc_stream_kernel<1><<<sgrid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, f16);
+    else nchw_to_padded_nhwc_stream_kernel<0><<<sgrid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, f16);
+  } else if (vec)
     nchw_to_padded_nhwc_vec_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16, up);
   else
     nchw_to_padded_nhwc_kernel<<<grid, 256, 0, st>>>(x, dst, c, h, w, pad, planes, plane_stride, pre, plane_format() == PLANES_F16, up);
@@ -431,12 +556,6 @@ __device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) 
                : "memory");
 }
 
-__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
-  // 16 bytes, or 16 zero bytes when !valid (source size 0: nothing is read)
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
-               "l"(gmem_src), "r"(valid ? 16 : 0)
-               : "memory");
-}
 
 // VEC = 0: tile rows of TW = 128 + KS - 1 pixels copied element by element, a pad word after every SO_PX pixels (the lanes of a
 //          warp then read their segments SO_PX + 1 words apart: no bank conflicts).  Any image width and alignment.
