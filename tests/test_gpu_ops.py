@@ -165,6 +165,9 @@ def test_attention_identity_weights(backend):
     (2, 40, 3, 72, 68, 3, 1, 1, 0),   # direct kernel, rows of whole 16-byte chunks: the vector form, one ragged tile
     (1, 16, 3, 66, 260, 3, 1, 1, 1),  # vector form: three tiles across (128 + 128 + 4), halo values cross tile and lane borders
     (1, 6, 2, 65, 132, 7, 1, 3, 0),   # vector form, 7x7: three halo values either side
+    (2, 40, 24, 10, 12, 3, 1, 1, 0),  # streamed layout pass: 40 channels (a partial channel block), one short pixel tile
+    (1, 72, 32, 9, 68, 3, 1, 1, 1),   # streamed layout pass: two channel blocks (64 + 8), two pixel tiles (64 + 4), 11 padded rows
+    (2, 16, 32, 6, 8, 1, 1, 0, 0),    # streamed layout pass without a padding ring (1x1)
 ])
 def test_conv2d(backend, batch, ic, oc, h, w, k, s, p, relu):
     r = rng(ic * oc + h)
