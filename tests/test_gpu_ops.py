@@ -26,6 +26,9 @@ def rng(seed):
     (3, 77, 5, True),         # skinny path, K not a multiple of 4 (scalar loads), fewer outputs than a row group
     (8, 33000, 24, True),     # skinny path, one row group spread over many warps
     (5, 130, 1000, False),    # skinny path, warps that span several row groups
+    (8, 8192, 1000, True),    # skinny path, 256 items on 148 CTAs: ranges of one and two items, some across a tile border
+    (16, 3000, 2000, False),  # skinny path, 378 items (ranges of 2 and 3), ragged K slice and ragged last tile
+    (3, 20000, 300, True),    # skinny path, 40 K slices per tile: a tile's partials come from many CTAs
     (128, 64, 256, True),     # exactly one tile
     (129, 65, 257, True),     # one past a tile in every dimension
     (300, 1000, 515, True),
