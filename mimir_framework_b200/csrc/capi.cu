@@ -274,6 +274,20 @@ bool conv_uses_shifted(int ic, int ks, int stride, int pad) {
 
 size_t conv_prenorm_bytes(int batch, int groups) { return align256(static_cast<size_t>(batch) * groups * 2 * sizeof(float)); }
 
+size_t conv_gn_emit_bytes(int batch, int oc, int h, int w, int pad, int groups) {
+  const long long rows = static_cast<long long>(batch) * (h + 2 * pad) * (w + 2 * pad);
+  return align256(gemm_gn_part_bytes(rows, oc, oc / groups));
+}
+
+bool conv_can_emit_gn(int batch, int ic, int oc, int h, int w, int ks, int stride, int pad, int groups, int act) {
+  static const bool on = [] { const char* e = getenv("MIMIR_B200_GN_EPILOGUE"); return e && e[0] == '1'; }();
+  if (!on || groups <= 0 || oc % groups != 0) return false;
+  const int cpg = oc / groups;
+  if (!(cpg == 4 || cpg == 8 || cpg == 16 || cpg == 32)) return false;
+  if (!conv_uses_shifted(ic, ks, stride, pad) || conv_small_oc_supported(oc, ks, stride, pad, h, w, batch, act)) return false;
+  return static_cast<long long>(h + 2 * pad) * (w + 2 * pad) >= 64 && batch <= 65535;
+}
+
 size_t conv_ws_bytes(int batch, int ic, int h, int w, int ks, int stride, int pad, int precision) {
   int ap, wp;
   precision_planes(precision, &ap, &wp);
@@ -299,12 +313,14 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
     const long long rows = static_cast<long long>(e.batch) * (e.h + 2 * e.pad) * (e.w + 2 * e.pad);
     if (rows > 0x7fffffffLL) return fail(MIMIR_B200_E_UNSUPPORTED, "Conv2d: batch too large for one launch");
     PreNorm pre;
+    const size_t planes_bytes = align256(static_cast<size_t>(ap) * rows * e.ic * sizeof(__nv_bfloat16));
     if (e.pre_groups > 0) {
-      // statistics live behind the operand planes in the workspace
-      float* stats = reinterpret_cast<float*>(static_cast<uint8_t*>(e.ws) + align256(static_cast<size_t>(ap) * rows * e.ic * sizeof(__nv_bfloat16)));
+      // statistics live behind the operand planes in the workspace (unless the producer's epilogue delivered them)
+      float* stats = reinterpret_cast<float*>(static_cast<uint8_t*>(e.ws) + planes_bytes);
       // (of an upsampled input: over the source image, whose values are the same ones four times)
-      MB_TRY(launch_groupnorm_stats(e.x, stats, e.batch, e.ic, e.in_up ? (e.h >> 1) * (e.w >> 1) : e.h * e.w, e.pre_groups, e.pre_eps, st));
-      pre.stats = stats; pre.gamma = e.pre_gamma; pre.beta = e.pre_gamma ? e.pre_beta : nullptr; pre.groups = e.pre_groups; pre.act = e.pre_act;
+      if (e.pre_stats == nullptr)
+        MB_TRY(launch_groupnorm_stats(e.x, stats, e.batch, e.ic, e.in_up ? (e.h >> 1) * (e.w >> 1) : e.h * e.w, e.pre_groups, e.pre_eps, st));
+      pre.stats = e.pre_stats ? e.pre_stats : stats; pre.gamma = e.pre_gamma; pre.beta = e.pre_gamma ? e.pre_beta : nullptr; pre.groups = e.pre_groups; pre.act = e.pre_act;
     }
     MB_TRY(launch_nchw_to_padded_nhwc_split(e.x, static_cast<__nv_bfloat16*>(e.ws), e.batch, e.ic, e.h, e.w, e.pad, ap, st, pre, e.in_up));
     GemmArgs g;
@@ -317,6 +333,13 @@ int conv_exec(const ConvExec& e, cudaStream_t st) {
     g.residual = e.residual;
     g.ldo = e.oc;
     g.conv_ks = e.ks; g.conv_c = e.ic; g.conv_pad = e.pad; g.conv_h = e.h; g.conv_w = e.w;
+    if (e.gn_stats_out != nullptr) {
+      g.gn_part = reinterpret_cast<float*>(static_cast<uint8_t*>(e.ws) + planes_bytes + (e.pre_groups > 0 ? conv_prenorm_bytes(e.batch, e.pre_groups) : 0));
+      g.gn_cpg = e.oc / e.gn_groups;
+      MB_TRY(launch_gemm(g, st));
+      return launch_gn_stats_from_partials(g.gn_part, e.gn_stats_out, e.batch, e.gn_groups, g.gn_cpg, rows, e.oc,
+                                           (e.h + 2 * e.pad) * (e.w + 2 * e.pad), e.gn_eps, st);
+    }
     return launch_gemm(g, st);
   }
   const int chunk = conv_chunk_samples(e.batch, ohw, k, e.precision);

@@ -156,7 +156,17 @@ struct GemmArgs {
   // (attention scores Q_b K_b^T and P_b V_b per sample).  `w` then holds w_rows_total rows.
   int a_group_rows = 0, w_group_rows = 0;
   long long w_rows_total = 0;
+  // Channel-major outputs (out_nchw_hw > 0 or conv_ks > 0): GroupNorm partials of the values stored, per 32-pixel block and
+  // 32-channel chunk, for the GroupNorm that reads this output; gemm_gn_part_bytes() of scratch.  gn_cpg in {4, 8, 16, 32}.
+  float* gn_part = nullptr;
+  int gn_cpg = 0;
 };
+inline size_t gemm_gn_part_bytes(long long m, int n, int cpg) {
+  return static_cast<size_t>((m + 31) / 32) * static_cast<size_t>((n + 31) / 32) * static_cast<size_t>(2 * (1 + 64 / cpg)) * sizeof(float);
+}
+// (mean, 1 / sqrt(var + eps)) per (sample, group) from those partials; `per` = rows of the GEMM's M index per sample
+int launch_gn_stats_from_partials(const float* part, float* stats, int batch, int groups, int cpg, long long m, int n, int per, float eps,
+                                  cudaStream_t st);
 // y = act(a · wᵀ + bias) (+ residual); tcgen05 / TMEM / TMA.
 int launch_gemm(const GemmArgs& g, cudaStream_t st);
 // Runs the bounded-wait give-up path on purpose: one CTA waits `limit_ns` on a barrier nobody arrives on, sets the device
@@ -203,6 +213,8 @@ int launch_groupnorm(const float* x, const float* gamma, const float* beta, floa
 int launch_softmax(const float* x, float* y, int batch, int64_t n, int log_softmax, cudaStream_t st);
 // stats[(sample * groups + g) * 2 + {0, 1}] = mean, 1 / sqrt(var + eps) of each GroupNorm slab
 int launch_groupnorm_stats(const float* x, float* stats, int batch, int ch, int hw, int groups, float eps, cudaStream_t st);
+int launch_groupnorm_apply(const float* x, const float* stats, const float* gamma, const float* beta, float* y, int batch, int ch, int hw,
+                           int groups, float eps, int act, const float* residual, cudaStream_t st);
 
 // attention.cu ---------------------------------------------------------------------------------
 // Where the projected queries, keys and values of one attention call live: row-major fp32, sample b at

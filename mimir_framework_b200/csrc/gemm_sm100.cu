@@ -97,6 +97,11 @@ struct GemmParams {
   int* err_word;
   // grouped form: W rows of tile (tm, tn) start at (tm * BM / a_group_rows) * w_group_rows + tn * bn (0 = one group)
   int a_group_rows, w_group_rows;
+  // Channel-major forms: per-(32-pixel block, 32-channel chunk) GroupNorm partials of the values stored, for the GroupNorm that
+  // reads this output (gn_part != null): entry [block * chunks + chunk][set][pixels, (sum, sum of squares) per group],
+  // set 0 = the sample of the block's first row, set 1 = the next sample where a block straddles two.
+  float* gn_part;
+  int gn_cpg;  // channels per group (4, 8, 16 or 32)
 };
 
 // Tile order: groups of `group_n` column tiles; inside a group the row tile runs fastest, so the
@@ -119,7 +124,59 @@ struct SmemLayout {
 
 constexpr int MAX_STAGES = 8;
 
-// CM = 1 compiles the channel-major forms in (NCHW output, convolution as shifted GEMMs, swapped operands); the plain
+// GroupNorm partials of one 32-pixel x 32-channel chunk (a lane = a pixel, v = its 32 channels as stored): per group of CPG
+// channels the sum and the sum of squares over the lanes of the set, plus the set's pixel count.  The 2 * (32 / CPG) per-lane
+// values meet by recursive halving (a lane hands over half of what it holds per round: 2G - 1 shuffles, not 5 per value), the
+// lanes that end up with a total store it.  Entry of a set: [pixels, S_0, Q_0, S_1, Q_1, ...].
+template <int CPG>
+__device__ __forceinline__ void gn_emit_set(const float (&v)[32], bool in, int nvalid_ch, int lane, float* dst) {
+  constexpr int G = 32 / CPG, G2 = 2 * G;
+  float a[G2];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float s = 0.0f, q = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CPG; ++j)
+      if (in && g * CPG + j < nvalid_ch) { s += v[g * CPG + j]; q = fmaf(v[g * CPG + j], v[g * CPG + j], q); }
+    a[2 * g] = s;
+    a[2 * g + 1] = q;
+  }
+  int mask = 16;
+#pragma unroll
+  for (int half = G2 / 2; half >= 1; half >>= 1, mask >>= 1) {
+    const bool upper = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float send = upper ? a[i] : a[i + half];
+      const float keep = upper ? a[i + half] : a[i];
+      a[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+    }
+  }
+  for (; mask >= 1; mask >>= 1) a[0] += __shfl_xor_sync(0xffffffffu, a[0], mask);  // the lanes that hold the same value index
+  const unsigned bal = __ballot_sync(0xffffffffu, in);
+  if (lane == 0) dst[0] = static_cast<float>(__popc(bal));
+  if ((lane & (32 / G2 - 1)) == 0) dst[1 + lane / (32 / G2)] = a[0];
+}
+// smp: the sample of this lane's row (rows past the matrix included: row / per); row_in: the row exists; pix_ok: it is a stored pixel
+__device__ __forceinline__ void gn_emit_chunk(const float (&v)[32], bool pix_ok, bool row_in, int smp, int nvalid_ch, int lane, int cpg,
+                                              float* dst) {
+  const int smp0 = __shfl_sync(0xffffffffu, smp, 0);
+  const bool next = __any_sync(0xffffffffu, row_in && smp != smp0);
+  const int es = 1 + 64 / cpg;  // floats per set
+  for (int set = 0; set < (next ? 2 : 1); ++set) {
+    const bool in = pix_ok && smp == smp0 + set;
+    float* d = dst + set * es;
+    switch (cpg) {
+      case 4: gn_emit_set<4>(v, in, nvalid_ch, lane, d); break;
+      case 8: gn_emit_set<8>(v, in, nvalid_ch, lane, d); break;
+      case 16: gn_emit_set<16>(v, in, nvalid_ch, lane, d); break;
+      default: gn_emit_set<32>(v, in, nvalid_ch, lane, d); break;
+    }
+  }
+}
+
+// CM = 1 compiles the channel-major forms in (NCHW output, convolution as shifted GEMMs, swapped operands; CM = 2: the same
+// plus GroupNorm partials of the stored values from the epilogue); the plain
 // row-major form (CM = 0: every Linear and attention projection) is built without them, so that the two families
 // neither share a register budget nor slow each other's epilogue down.
 // PAIR = 1 (not with swapped operands): the kernel runs as clusters of two CTAs on neighbouring SMs that share one 256-row x 256-column
@@ -331,22 +388,27 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const int oc0 = row0;  // first output channel of this warp's 32 lanes
         const long long hw = conv ? static_cast<long long>(p.conv_h) * p.conv_w : static_cast<long long>(p.ohw);
         // where this lane's pixel of chunk ci lands in the NCHW output; false = the chunk is past the matrix (warp-uniform)
+        int g_smp = 0;       // sample of this lane's row in the chunk geom() was last asked about
+        bool g_row_in = false;
         auto geom = [&](int ci, int& c0, bool& pv, long long& o0) -> bool {
           c0 = (half * (BN / 64) + ci) * 32;
           const int r0 = tn * BN + c0;
           if (r0 >= p.m || oc0 >= p.n) return false;
           const int prow = r0 + lane;
           pv = prow < p.m;
+          g_row_in = pv;
           long long pbase = 0;
           if (conv) {
             const int per = p.conv_hp * p.conv_wp;
             const int smp = prow / per, rem = prow - smp * per;
+            g_smp = smp;
             const int yq = rem / p.conv_wp;
             const int yy = yq - p.conv_pad, xx = rem - yq * p.conv_wp - p.conv_pad;
             pv = pv && yy >= 0 && yy < p.conv_h && xx >= 0 && xx < p.conv_w;
             pbase = static_cast<long long>(smp) * p.n * hw + static_cast<long long>(yy) * p.conv_w + xx;
           } else {
             const long long smp = prow / p.ohw;
+            g_smp = static_cast<int>(smp);
             pbase = smp * p.n * hw + (prow - smp * p.ohw);
           }
           o0 = pbase + static_cast<long long>(oc0) * hw;
@@ -361,6 +423,8 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         for (int ci = 0; ci < NCH; ++ci) {
           int c0; bool pv; long long o0;
           if (!geom(ci, c0, pv, o0)) break;
+          const int my_smp = g_smp;
+          const bool my_row_in = g_row_in;
           float q[32];
           if (p.residual != nullptr) {
             if (pv) {
@@ -395,6 +459,11 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (int j = 0; j < 32; ++j)
               if (full || oc0 + j < p.n) p.out_f32[o0 + j * hw] = v[j];
           }
+          if (CM == 2 && p.gn_part != nullptr) {
+            const long long blk = (tn * BN + c0) >> 5;
+            float* gd = p.gn_part + (blk * ((p.n + 31) >> 5) + (oc0 >> 5)) * (2 * (1 + 64 / p.gn_cpg));
+            gn_emit_chunk(v, pv, my_row_in, my_smp, min(32, p.n - oc0), lane, p.gn_cpg, gd);
+          }
         }
         tcgen05_fence_before();
         __syncwarp();
@@ -404,14 +473,17 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       }
       const int col_limit = (p.out_split != nullptr) ? static_cast<int>(p.np) : p.n;
       // channel-major addressing of this lane's row
-      bool cm_ok = false;
+      bool cm_ok = false, cm_row_in = false;
+      int cm_smp = 0;
       long long cm_o0 = 0, cm_stride = 0;
       if (chan_major) {
         const int row = row0 + lane;
         cm_ok = row < p.m;
+        cm_row_in = cm_ok;
         if (conv) {
           const int per = p.conv_hp * p.conv_wp;
           const int smp = row / per, rem = row - smp * per;
+          cm_smp = smp;
           const int yq = rem / p.conv_wp;
           const int yy = yq - p.conv_pad, xx = rem - yq * p.conv_wp - p.conv_pad;
           cm_ok = cm_ok && yy >= 0 && yy < p.conv_h && xx >= 0 && xx < p.conv_w;
@@ -419,6 +491,7 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
           cm_o0 = static_cast<long long>(smp) * p.n * cm_stride + static_cast<long long>(yy) * p.conv_w + xx;
         } else {
           const long long smp = row / p.ohw;
+          cm_smp = static_cast<int>(smp);
           cm_stride = p.ohw;
           cm_o0 = smp * p.n * cm_stride + (row - smp * p.ohw);
         }
@@ -470,6 +543,10 @@ gemm_tn_bf16split_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (full_cols || col0 + j < p.n) p.out_f32[o0 + j * cm_stride] = v[j];
+          }
+          if (CM == 2 && p.gn_part != nullptr && row0 < p.m && col0 < p.n) {  // warp-uniform
+            float* gd = p.gn_part + (static_cast<long long>(row0 >> 5) * ((p.n + 31) >> 5) + (col0 >> 5)) * (2 * (1 + 64 / p.gn_cpg));
+            gn_emit_chunk(v, cm_ok, cm_row_in, cm_smp, min(32, p.n - col0), lane, p.gn_cpg, gd);
           }
         } else {
           // row-major: this lane owns 32 consecutive columns of its row = one 128-byte line, moved with
@@ -762,6 +839,14 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
   p.np = round_up(g.n, 64);
   p.ohw = g.out_nchw_hw;
   p.err_word = ctx().dev_error_word;
+  p.gn_part = nullptr;
+  p.gn_cpg = 0;
+  if (g.gn_part != nullptr) {
+    if (!(g.conv_ks > 0 || g.out_nchw_hw > 0) || !(g.gn_cpg == 4 || g.gn_cpg == 8 || g.gn_cpg == 16 || g.gn_cpg == 32))
+      return fail(MIMIR_B200_E_INVALID, "GEMM: GroupNorm partials need a channel-major output and 4, 8, 16 or 32 channels per group");
+    p.gn_part = g.gn_part;
+    p.gn_cpg = g.gn_cpg;
+  }
   p.a_group_rows = g.a_group_rows;
   p.w_group_rows = g.w_group_rows;
   {
@@ -788,7 +873,11 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
     if (want >= 2 && want < p.stages) p.stages = want;
   }
   const bool cm = swap || conv || g.out_nchw_hw > 0;
-  auto kern = cm ? (pair ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 0>)
+  // CM = 2: the channel-major form with the GroupNorm partials compiled into its epilogue (a form of its own, so that the
+  // convolutions that do not emit them run the code they always ran)
+  auto kern = cm ? (p.gn_part != nullptr
+                        ? (pair ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 2, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 2, 0>)
+                        : (pair ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 0>))
                  : (pair ? gemm_tn_bf16split_kernel<BK, RING_BYTES, 0, 1> : gemm_tn_bf16split_kernel<BK, RING_BYTES, 0, 0>);
   static PerDeviceOnce attr_once;
   MB_TRY(attr_once.run([&]() -> int {
@@ -796,6 +885,8 @@ int launch_gemm_t(const GemmArgs& g, cudaStream_t st) {
     MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 0, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    MB_CUDA(cudaFuncSetAttribute(gemm_tn_bf16split_kernel<BK, RING_BYTES, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     return MIMIR_B200_OK;
   }));
   const int tiles = p.tiles_m * p.tiles_n;

@@ -134,6 +134,9 @@ struct LayerRT {
   int res_v = -1;                     // residual tensor folded in from a following Add
   int pre_norm = -1;                  // Conv2d: index of the GroupNorm layer applied while its operand planes are laid out
   bool in_up = false;                 // Conv2d: in_v[0] is the INPUT of a 2 x 2 nearest upsample that the layout pass applies
+  int gn_emit_for = -1;               // Conv2d: index of the GroupNorm layer whose statistics this layer's GEMM epilogue emits
+  int gn_stats_from = -1;             // GroupNorm: index of the Conv2d layer that emits its statistics
+  size_t gn_stats_off = 0;            // Conv2d with gn_emit_for >= 0: offset of the statistics [batch][groups][2] in the arena
   // decode twin (see mimir_b200_model_decode_begin): weights borrowed from the main model, key / value caches owned
   bool borrowed_f32 = false, borrowed_planes = false;
   float* kcache = nullptr;
@@ -1023,6 +1026,33 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
   m->tensors[out_root].last = nl;
 
   // ---- offsets ---------------------------------------------------------------------------------------
+  // ---- fusion 1e: GroupNorm statistics out of the producing convolution's GEMM epilogue (MIMIR_B200_GN_EPILOGUE=1) ----
+  //      A GroupNorm (folded into a convolution's layout pass or running on its own) whose input is the output of a shifted-GEMM
+  //      convolution does not sweep that tensor for its mean and variance: the convolution's epilogue leaves per-block partials
+  //      behind, a small kernel merges them, and the GroupNorm (or the layout pass) reads (mean, 1 / std) from there.
+  for (auto& L : m->layers) { L.gn_emit_for = -1; L.gn_stats_from = -1; }
+  for (int li = 0; li < nl; ++li) {
+    LayerRT& G = m->layers[li];
+    if (G.lt != LT::GroupNorm) continue;
+    int xin = -1;
+    if (G.skip) {  // folded: the statistics are taken over the consuming convolution's (possibly pre-upsample) input
+      for (int ci = 0; ci < nl; ++ci)
+        if (m->layers[ci].lt == LT::Conv2d && !m->layers[ci].skip && m->layers[ci].pre_norm == li) xin = m->layers[ci].in_v[0];
+    } else {
+      xin = G.in_v[0];
+    }
+    if (xin < 0) continue;
+    const int xr = root_of(m->tensors, xin);
+    const TensorV& xt = m->tensors[xr];
+    if (xt.producer < 0) continue;
+    LayerRT& P = m->layers[xt.producer];
+    if (P.lt != LT::Conv2d || P.skip || P.gn_emit_for >= 0 || root_of(m->tensors, P.out_v) != xr || P.d.out_channels != G.ch) continue;
+    if (!conv_can_emit_gn(batch, P.d.in_channels, P.d.out_channels, P.h, P.w, P.d.kernel, P.d.stride, P.d.padding, G.d.num_groups,
+                          P.d.activation ? MIMIR_B200_ELT_RELU : P.fused_act))
+      continue;
+    P.gn_emit_for = li;
+    G.gn_stats_from = xt.producer;
+  }
   ArenaSim sim;
   auto place = [&](int v) {
     TensorV& t = m->tensors[v];
@@ -1069,6 +1099,8 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
           const int k = L.d.in_channels * L.d.kernel * L.d.kernel;
           L.ws_bytes = conv_ws_bytes(batch, L.d.in_channels, L.h, L.w, L.d.kernel, L.d.stride, L.d.padding, m->precision);
           if (L.pre_norm >= 0) L.ws_bytes += conv_prenorm_bytes(batch, m->layers[L.pre_norm].d.num_groups);
+          if (L.gn_emit_for >= 0)
+            L.ws_bytes += conv_gn_emit_bytes(batch, L.d.out_channels, L.h, L.w, L.d.padding, m->layers[L.gn_emit_for].d.num_groups);
           flops += 2ull * batch * L.oh * L.ow * k * L.d.out_channels;
           break;
         }
@@ -1108,7 +1140,14 @@ int plan_model(MimirB200Model* m, const MimirNamedInput* inputs, int n_inputs, i
   m->hbm_bytes = hbm;
 
   // ---- budget check before anything is launched, then (re)allocate the arena -------------------------
-  const size_t need = sim.peak + 256;
+  size_t need = sim.peak + 256;
+  for (auto& L : m->layers) {  // the emitted GroupNorm statistics live behind the simulated arena for the whole forward
+    if (L.gn_emit_for < 0) continue;
+    need = (need + 255) & ~static_cast<size_t>(255);
+    L.gn_stats_off = need;
+    need += static_cast<size_t>(batch) * m->layers[L.gn_emit_for].d.num_groups * 2 * sizeof(float);
+  }
+  need += 256;
   if (m->arena && m->arena_bytes < need) {
     dev_free(m->arena, m->arena_bytes);
     if (m->arena2) dev_free(m->arena2, m->arena_bytes);
@@ -1211,8 +1250,14 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
           e.pre_beta = (G.d.affine && G.d.use_bias) ? G.w_f32 + G.ch : nullptr;
           e.pre_eps = G.d.eps;
           e.pre_act = G.fused_act;
+          if (G.gn_stats_from >= 0) e.pre_stats = reinterpret_cast<const float*>(arena + m->layers[G.gn_stats_from].gn_stats_off);
         }
         e.in_up = L.in_up ? 1 : 0;
+        if (L.gn_emit_for >= 0) {
+          e.gn_stats_out = reinterpret_cast<float*>(arena + L.gn_stats_off);
+          e.gn_groups = m->layers[L.gn_emit_for].d.num_groups;
+          e.gn_eps = m->layers[L.gn_emit_for].d.eps;
+        }
         s = conv_exec(e, st);
         break;
       }
@@ -1236,8 +1281,9 @@ int run_layers(MimirB200Model* m, int batch, const Bound& bnd, cudaStream_t st, 
       case LT::GroupNorm: {
         const float* g = d.affine ? L.w_f32 : nullptr;
         const float* b = (d.affine && d.use_bias) ? L.w_f32 + L.ch : nullptr;
-        s = launch_groupnorm(f32p(L.in_v[0]), g, b, f32p(L.out_v), batch, L.ch, L.h * L.w, d.num_groups, d.eps, L.fused_act,
-                             L.res_v >= 0 ? f32p(L.res_v) : nullptr, st);
+        const float* stats = L.gn_stats_from >= 0 ? reinterpret_cast<const float*>(arena + m->layers[L.gn_stats_from].gn_stats_off) : nullptr;
+        s = launch_groupnorm_apply(f32p(L.in_v[0]), stats, g, b, f32p(L.out_v), batch, L.ch, L.h * L.w, d.num_groups, d.eps, L.fused_act,
+                                   L.res_v >= 0 ? f32p(L.res_v) : nullptr, st);
         break;
       }
       case LT::Softmax:

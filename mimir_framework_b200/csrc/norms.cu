@@ -590,6 +590,7 @@ struct RowParams {
   long long n_gamma;     // FAM_RMS
   int log_softmax;       // FAM_SOFTMAX
   float* stats_out;      // FAM_MEANVAR: when set, only (mean, 1/std) of every row is written, no output sweep
+  const float* stats_in; // FAM_MEANVAR: when set, (mean, 1/std) of every row are read here, no statistics sweep
 };
 
 __device__ __forceinline__ float silu_fast(float v) { return v * __fdividef(1.0f, 1.0f + __expf(-v)); }
@@ -834,6 +835,10 @@ __global__ void __launch_bounds__(THREADS, (THREADS <= 512) ? 2 : 1) sweep_row_k
       // is exact algebra for mean and variance and loses nothing as long as K is within a few standard
       // deviations of the mean.  When the shift turns out to be poor (the correction term eats more than
       // 3/4 of the second moment) the variance is recomputed centred on the mean, as the reference does.
+      if (p.stats_in != nullptr) {  // the statistics came with the producer's epilogue: one sweep only
+        meanvar_write_row(g, o, n, vec, __ldg(p.stats_in + 2 * row), __ldg(p.stats_in + 2 * row + 1), row, base, p.aff);
+        continue;
+      }
       const float shift = __ldg(g);
       float s = 0.0f, q = 0.0f;
       sweep_read(g, n, vec, [&](float v) { const float d = v - shift; s += d; q = fmaf(d, d, q); });
@@ -1163,6 +1168,20 @@ int launch_groupnorm(const float* x, const float* gamma, const float* beta, floa
   return meanvar_dispatch(x, y, static_cast<long long>(batch) * groups, static_cast<long long>(cpg) * hw, eps, a, st);
 }
 
+// GroupNorm whose statistics [batch][groups][2] already exist (they came out of the producing convolution's epilogue): the
+// output sweep alone.  Shapes the row sweeps do not take fall back to the full GroupNorm.
+int launch_groupnorm_apply(const float* x, const float* stats, const float* gamma, const float* beta, float* y, int batch, int ch, int hw,
+                           int groups, float eps, int act, const float* residual, cudaStream_t st) {
+  if (groups <= 0 || ch % groups != 0) return fail(MIMIR_B200_E_INVALID, "GroupNorm: channels must be divisible by num_groups");
+  const long long rows = static_cast<long long>(batch) * groups, len = static_cast<long long>(ch / groups) * hw;
+  if (stats == nullptr || !use_sweeps(rows, len)) return launch_groupnorm(x, gamma, beta, y, batch, ch, hw, groups, eps, act, residual, st);
+  RowParams p{};
+  p.x = x; p.y = y; p.rows = rows; p.len = len; p.eps = eps;
+  p.aff = Affine{gamma, gamma ? beta : nullptr, 1, groups, ch / groups, hw, act, residual};
+  p.stats_in = stats;
+  return launch_sweep_rows<FAM_MEANVAR>(p, st);
+}
+
 // (mean, 1 / sqrt(var + eps)) of every (sample, group) slab, for consumers that normalise on the fly
 int launch_groupnorm_stats(const float* x, float* stats, int batch, int ch, int hw, int groups, float eps, cudaStream_t st) {
   if (groups <= 0 || ch % groups != 0) return fail(MIMIR_B200_E_INVALID, "GroupNorm: channels must be divisible by num_groups");
@@ -1175,6 +1194,57 @@ int launch_groupnorm_stats(const float* x, float* stats, int batch, int ch, int 
   p.aff = Affine{nullptr, nullptr, 1, groups, ch / groups, hw, -1, nullptr};
   p.stats_out = stats;
   return launch_sweep_rows<FAM_MEANVAR>(p, st);
+}
+
+// ---- GroupNorm statistics from the partials a convolution's GEMM epilogue left behind ----------------------------------------
+// One CTA per (group, sample) merges the (pixels, sum, sum of squares) entries of the 32-pixel blocks that hold the sample's rows
+// with the pairwise formula of Chan et al., in double and in a fixed order: a thread takes blocks t, t + 128, ... and thread 0
+// folds the 128 thread results in thread order.  A block belongs to the sample with its set 0 when its first row does, and
+// with its set 1 when it starts in the sample before.
+namespace {
+struct Moments { double n, mean, m2; };
+__device__ __forceinline__ void moments_merge(Moments& a, double nb, double mb, double m2b) {
+  if (nb <= 0.0) return;
+  const double nt = a.n + nb, delta = mb - a.mean;
+  a.mean += delta * (nb / nt);
+  a.m2 += m2b + delta * delta * (a.n * nb / nt);
+  a.n = nt;
+}
+__global__ void __launch_bounds__(128) gn_stats_from_partials_kernel(const float* __restrict__ part, float* __restrict__ stats, int groups,
+                                                                     int cpg, long long m, int nchunks, int per, float eps) {
+  __shared__ Moments sh[128];
+  const int g = blockIdx.x, smp = blockIdx.y, es = 1 + 64 / cpg;  // es: floats of one set's entry
+  const int cc = (g * cpg) >> 5, gi = ((g * cpg) & 31) / cpg;
+  const long long r_first = static_cast<long long>(smp) * per, r_last = min(m, r_first + per) - 1;
+  const long long b0 = r_first >> 5, b1 = r_last >> 5;
+  Moments acc{0.0, 0.0, 0.0};
+  for (long long b = b0 + threadIdx.x; b <= b1; b += 128) {
+    const int set = ((b << 5) / per == smp) ? 0 : 1;
+    const float* e = part + (b * nchunks + cc) * (2 * es) + set * es;
+    const double cnt = static_cast<double>(__ldg(e)) * cpg, sum = __ldg(e + 1 + 2 * gi), sq = __ldg(e + 2 + 2 * gi);
+    if (cnt > 0.0) moments_merge(acc, cnt, sum / cnt, fmax(sq - sum * sum / cnt, 0.0));
+  }
+  sh[threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    Moments t = sh[0];
+    for (int i = 1; i < 128; ++i) moments_merge(t, sh[i].n, sh[i].mean, sh[i].m2);
+    float* o = stats + (static_cast<long long>(smp) * groups + g) * 2;
+    o[0] = static_cast<float>(t.mean);
+    o[1] = 1.0f / sqrtf(static_cast<float>(t.n > 0.0 ? t.m2 / t.n : 0.0) + eps);
+  }
+}
+}  // namespace
+
+int launch_gn_stats_from_partials(const float* part, float* stats, int batch, int groups, int cpg, long long m, int n, int per, float eps,
+                                  cudaStream_t st) {
+  if (!part || !stats || batch <= 0 || groups <= 0 || per < 64 || !(cpg == 4 || cpg == 8 || cpg == 16 || cpg == 32) || groups * cpg != n ||
+      batch > 65535)
+    return fail(MIMIR_B200_E_INVALID, "GroupNorm statistics from partials: bad arguments");
+  gn_stats_from_partials_kernel<<<dim3(groups, batch), 128, 0, st>>>(part, stats, groups, cpg, m, (n + 31) / 32, per, eps);
+  MB_CUDA(cudaGetLastError());
+  count_launch();
+  return MIMIR_B200_OK;
 }
 
 // The one-pass kernel needs every CTA of a sample resident at once and a slot pair per chunk.

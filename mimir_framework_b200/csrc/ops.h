@@ -100,8 +100,19 @@ struct ConvExec {
   // x is [ic][h/2][w/2]: the 2 x 2 nearest-neighbour upsample of the producing layer is applied while the operand planes
   // are laid out (shifted path only); h and w stay the convolution's own input size
   int in_up = 0;
+  // The statistics of the folded GroupNorm already exist (the producer's epilogue emitted them): [batch][pre_groups][2]
+  const float* pre_stats = nullptr;
+  // This convolution's output feeds a GroupNorm of gn_groups groups: its GEMM epilogue leaves partials behind and
+  // (mean, 1 / std) per (sample, group) go to gn_stats_out (shifted-GEMM path only; the workspace holds the partials)
+  float* gn_stats_out = nullptr;
+  int gn_groups = 0;
+  float gn_eps = 1e-5f;
 };
 size_t conv_prenorm_bytes(int batch, int groups);
+// scratch of the GroupNorm partials a shifted-GEMM convolution emits (behind the planes and the pre-norm statistics)
+size_t conv_gn_emit_bytes(int batch, int oc, int h, int w, int pad, int groups);
+// can this convolution's epilogue emit the statistics of a GroupNorm with `groups` groups over its output?
+bool conv_can_emit_gn(int batch, int ic, int oc, int h, int w, int ks, int stride, int pad, int groups, int act);
 // stride-1 "same" convolutions with a channel count that is a multiple of 32 run as shifted GEMMs over the
 // padded NHWC activation; everything else goes through im2col planes.  The two paths want different
 // weight-plane orders ((kh, kw, ic) vs (ic, kh, kw)).
